@@ -1,0 +1,740 @@
+// C ABI of libeoq_b200.so (declarations and reference citations: include/eoq_b200.h).
+// Host-side validation mirrors the reference's checks and error codes; all
+// decoding runs on the GPU.
+#include "eoq_internal.h"
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <cuda_runtime.h>
+#include <memory>
+#include <mutex>
+#include <unistd.h>
+
+using namespace eoq;
+
+namespace {
+
+#define CU_TRY(call)                                                                          \
+    do {                                                                                      \
+        cudaError_t e__ = (call);                                                             \
+        if (e__ != cudaSuccess) {                                                             \
+            std::fprintf(stderr, "eoq_b200: %s failed: %s\n", #call, cudaGetErrorString(e__)); \
+            return EOQ_ERR_CUDA;                                                              \
+        }                                                                                     \
+    } while (0)
+
+bool have_device()
+{
+    int n = 0;
+    return cudaGetDeviceCount(&n) == cudaSuccess && n > 0;
+}
+
+// Owns a set of device allocations; frees them when it goes out of scope.
+struct DeviceBuf {
+    void *p = nullptr;
+    DeviceBuf() = default;
+    DeviceBuf(const DeviceBuf &) = delete;
+    DeviceBuf &operator=(const DeviceBuf &) = delete;
+    ~DeviceBuf() { if (p) cudaFree(p); }
+    cudaError_t alloc(size_t n) { return cudaMalloc(&p, n ? n : 1); }
+    template <typename T> T *as() const { return reinterpret_cast<T *>(p); }
+};
+
+// Pieces of a validated tensor payload `[u16 freq x A][u32 offsets x B][blocks]`.
+struct Payload {
+    uint32_t alphabet = 0, p = 0, block = 0, total = 0, nblocks = 0;
+    const uint16_t *freq = nullptr;
+    const uint8_t *offsets_raw = nullptr;   // may be unaligned
+    const uint8_t *stream = nullptr;
+    uint32_t stream_bytes = 0;
+    std::vector<uint32_t> offsets, sizes;
+};
+
+// Checks of eoq_decode_tensor_v2 (eoq_rans_v2.c:586-619), then the per-block
+// checks its workers make while decoding (:542-545 offsets, :392 state length),
+// done here on the host so nothing corrupt is ever launched.
+eoq_error_t parse_payload(const eoq_tensor_header_t *h, const uint8_t *comp, size_t comp_size, size_t out_cap, Payload &pl)
+{
+    eoq_error_t rc = eoq_validate_header(h);
+    if (rc != EOQ_OK) return rc;
+    if (out_cap < h->uncompressed_size) return EOQ_ERR_BUFFER_TOO_SMALL;
+    if (comp_size < h->compressed_size) return EOQ_ERR_CORRUPT_STREAM;
+    pl.alphabet = h->freq_table_size; pl.p = h->precision_bits; pl.block = h->rans_block_size;
+    pl.total = h->uncompressed_size;
+    pl.nblocks = (uint32_t)(((uint64_t)pl.total + pl.block - 1) / pl.block);
+    const uint64_t meta = (uint64_t)pl.alphabet * 2 + (uint64_t)pl.nblocks * 4;
+    if (meta > h->compressed_size) return EOQ_ERR_CORRUPT_STREAM;
+    pl.freq = reinterpret_cast<const uint16_t *>(comp);
+    pl.offsets_raw = comp + (size_t)pl.alphabet * 2;
+    pl.stream = comp + meta;
+    pl.stream_bytes = h->compressed_size - (uint32_t)meta;
+    pl.offsets.resize(pl.nblocks);
+    pl.sizes.resize(pl.nblocks);
+    std::memcpy(pl.offsets.data(), pl.offsets_raw, (size_t)pl.nblocks * 4);
+    for (uint32_t b = 0; b < pl.nblocks; b++) {
+        const uint32_t lo = pl.offsets[b];
+        const uint32_t hi = b + 1 < pl.nblocks ? pl.offsets[b + 1] : pl.stream_bytes;
+        if (hi < lo || hi > pl.stream_bytes) return EOQ_ERR_CORRUPT_STREAM;
+        pl.sizes[b] = hi - lo;
+        if (pl.sizes[b] && 1u + pl.stream[lo] > pl.sizes[b]) return EOQ_ERR_CORRUPT_STREAM;
+    }
+    return EOQ_OK;
+}
+
+void make_v1_table(const std::vector<uint32_t> &freq, const std::vector<uint32_t> &cdf, uint32_t p, std::vector<V1Table> &t)
+{
+    t.assign((size_t)1 << p, V1Table{1, 0});
+    for (uint32_t s = 0; s + 1 < cdf.size(); s++)
+        for (uint32_t k = cdf[s]; k < cdf[s + 1]; k++) t[k] = V1Table{freq[s], (s << 16) | (k - cdf[s])};
+}
+
+eoq_error_t table_from_u16(const uint16_t *raw16, uint32_t alphabet, uint32_t p, std::vector<V1Table> &t)
+{
+    std::vector<uint32_t> raw(alphabet), freq, cdf;
+    for (uint32_t s = 0; s < alphabet; s++) { uint16_t v; std::memcpy(&v, raw16 + s, 2); raw[s] = v; }
+    eoq_error_t rc = normalize_reference(raw.data(), alphabet, p, freq, cdf);
+    if (rc != EOQ_OK) return rc;
+    make_v1_table(freq, cdf, p, t);
+    return EOQ_OK;
+}
+
+// Device-side copy of one tensor's inputs, ready to launch.
+struct StagedTensor {
+    DeviceBuf stream, offsets, sizes, table, out;
+    Payload pl;
+    bool own_out = true;
+    uint8_t *d_out = nullptr;
+};
+
+eoq_error_t stage_tensor(const eoq_tensor_header_t *h, const uint8_t *comp, size_t comp_size, size_t out_cap,
+                         uint8_t *d_out_or_null, cudaStream_t st, StagedTensor &s)
+{
+    eoq_error_t rc = parse_payload(h, comp, comp_size, out_cap, s.pl);
+    if (rc != EOQ_OK) return rc;
+    std::vector<V1Table> table;
+    rc = table_from_u16(s.pl.freq, s.pl.alphabet, s.pl.p, table);
+    if (rc != EOQ_OK) return rc;
+    if (!have_device()) return EOQ_ERR_CUDA;
+    const Payload &pl = s.pl;
+    if (s.stream.alloc(pl.stream_bytes) != cudaSuccess || s.offsets.alloc((size_t)pl.nblocks * 4) != cudaSuccess ||
+        s.sizes.alloc((size_t)pl.nblocks * 4) != cudaSuccess || s.table.alloc(table.size() * sizeof(V1Table)) != cudaSuccess)
+        return EOQ_ERR_ALLOC;
+    if (d_out_or_null) { s.own_out = false; s.d_out = d_out_or_null; }
+    else { if (s.out.alloc(pl.total) != cudaSuccess) return EOQ_ERR_ALLOC; s.d_out = s.out.as<uint8_t>(); }
+    CU_TRY(cudaMemcpyAsync(s.stream.p, pl.stream, pl.stream_bytes, cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaMemcpyAsync(s.offsets.p, pl.offsets.data(), (size_t)pl.nblocks * 4, cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaMemcpyAsync(s.sizes.p, pl.sizes.data(), (size_t)pl.nblocks * 4, cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaMemcpyAsync(s.table.p, table.data(), table.size() * sizeof(V1Table), cudaMemcpyHostToDevice, st));
+    // the pageable sources above are consumed before cudaMemcpyAsync returns
+    return EOQ_OK;
+}
+
+eoq_error_t launch_staged(const StagedTensor &s, cudaStream_t st)
+{
+    const Payload &pl = s.pl;
+    int e = launch_decode_v1(s.stream.as<uint8_t>(), s.offsets.as<uint32_t>(), s.sizes.as<uint32_t>(), s.table.as<V1Table>(),
+                             s.d_out, 1, pl.nblocks, pl.block, pl.total, pl.p, st);
+    if (e != 0) { std::fprintf(stderr, "eoq_b200: decode launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
+    return EOQ_OK;
+}
+
+eoq_error_t decode_host_to_host(const eoq_tensor_header_t *h, const uint8_t *comp, size_t comp_size, void *output,
+                                size_t out_cap, cudaStream_t st)
+{
+    StagedTensor s;
+    eoq_error_t rc = stage_tensor(h, comp, comp_size, out_cap, nullptr, st, s);
+    if (rc != EOQ_OK) return rc;
+    rc = launch_staged(s, st);
+    if (rc != EOQ_OK) return rc;
+    CU_TRY(cudaMemcpyAsync(output, s.d_out, s.pl.total, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    return EOQ_OK;
+}
+
+}  // namespace
+
+// =========================================================================
+// Part 1: the reference's C interface
+// =========================================================================
+
+extern "C" const char *eoq_error_string(eoq_error_t err)
+{
+    switch (err) {
+        case EOQ_OK: return "success";
+        case EOQ_ERR_NULL_PTR: return "null pointer argument";
+        case EOQ_ERR_BUFFER_TOO_SMALL: return "output buffer too small";
+        case EOQ_ERR_CORRUPT_STREAM: return "corrupt compressed stream";
+        case EOQ_ERR_INVALID_HEADER: return "invalid tensor header";
+        case EOQ_ERR_ALLOC: return "memory allocation failed";
+        case EOQ_ERR_THREAD: return "threading error";
+        case EOQ_ERR_OVERFLOW: return "integer overflow";
+        case EOQ_ERR_CUDA: return "CUDA device unavailable or CUDA call failed";
+        case EOQ_ERR_UNSUPPORTED: return "input not supported by this build";
+    }
+    return "unknown error";
+}
+
+extern "C" eoq_error_t eoq_validate_header(const eoq_tensor_header_t *h)
+{
+    if (!h) return EOQ_ERR_NULL_PTR;
+    if (h->freq_table_size == 0 || h->freq_table_size > 4096) return EOQ_ERR_INVALID_HEADER;
+    if (h->precision_bits == 0 || h->precision_bits > 16) return EOQ_ERR_INVALID_HEADER;
+    if (h->rans_block_size == 0) return EOQ_ERR_INVALID_HEADER;
+    if ((uint64_t)h->compressed_size < (uint64_t)h->freq_table_size * 2 + 4) return EOQ_ERR_INVALID_HEADER;
+    return EOQ_OK;
+}
+
+extern "C" int eoq_detect_num_threads(void)
+{
+    long n = sysconf(_SC_NPROCESSORS_ONLN);
+    if (n > 0) return (int)n;
+    n = sysconf(_SC_NPROCESSORS_CONF);
+    return n > 0 ? (int)n : 4;
+}
+
+extern "C" eoq_error_t eoq_decode_tensor_v2(const eoq_tensor_header_t *header, const uint8_t *compressed, size_t comp_size,
+                                            void *output, size_t out_cap, const eoq_decode_opts_t *opts)
+{
+    if (!header || !compressed || !output) return EOQ_ERR_NULL_PTR;
+    if (header->uncompressed_size == 0) return EOQ_OK;
+    eoq_error_t rc = decode_host_to_host(header, compressed, comp_size, output, out_cap, nullptr);
+    // the whole tensor is one launch, so progress is reported once, complete (eoq_rans_v2.c:757-762)
+    if (rc == EOQ_OK && opts && opts->progress_cb)
+        opts->progress_cb(header->uncompressed_size, header->uncompressed_size, opts->progress_ud);
+    return rc;
+}
+
+extern "C" int eoq_decode_tensor(const eoq_tensor_header_t *header, const uint8_t *compressed, void *output)
+{
+    if (!header) return (int)EOQ_ERR_NULL_PTR;
+    return (int)eoq_decode_tensor_v2(header, compressed, header->compressed_size, output, header->uncompressed_size, nullptr);
+}
+
+// Tensors are pipelined over a few CUDA streams: while one tensor decodes, the
+// next one's payload is uploaded.  A tensor counts as done, and the progress
+// callback runs (on the calling thread, so calls are serialised), when its
+// result has landed in the caller's output buffer.
+extern "C" eoq_error_t eoq_parallel_decode(eoq_decode_task_t *tasks, int num_tasks, const eoq_parallel_opts_t *opts)
+{
+    if (!tasks && num_tasks > 0) return EOQ_ERR_NULL_PTR;
+    if (num_tasks <= 0) return EOQ_OK;
+    int lanes = opts ? opts->num_threads : 0;
+    if (lanes <= 0) lanes = 4;
+    lanes = std::min(std::min(lanes, num_tasks), 8);
+    eoq_parallel_progress_fn cb = opts ? opts->progress_cb : nullptr;
+    void *ud = opts ? opts->progress_ud : nullptr;
+
+    struct Slot { cudaStream_t st = nullptr; std::unique_ptr<StagedTensor> staged; int task = -1; };
+    std::vector<Slot> slots((size_t)lanes);
+    bool streams_ok = have_device();
+    if (streams_ok)
+        for (auto &s : slots)
+            if (cudaStreamCreateWithFlags(&s.st, cudaStreamNonBlocking) != cudaSuccess) { streams_ok = false; break; }
+
+    int done = 0;
+    bool cancelled = false;
+    auto retire = [&](Slot &s) {
+        if (s.task < 0) return;
+        eoq_decode_task_t &t = tasks[s.task];
+        if (t.result == EOQ_OK && s.staged && cudaStreamSynchronize(s.st) != cudaSuccess) t.result = EOQ_ERR_CUDA;
+        s.staged.reset();
+        s.task = -1;
+        done++;
+        if (cb && !cancelled && cb(done, num_tasks, ud)) cancelled = true;
+    };
+
+    for (int i = 0; i < num_tasks; i++) {
+        Slot &s = slots[(size_t)(i % lanes)];
+        retire(s);
+        eoq_decode_task_t &t = tasks[i];
+        if (cancelled) { t.result = EOQ_ERR_THREAD; continue; }      // eoq_parallel_decode.c:72-82
+        t.task_index = i;
+        s.task = i;
+        if (!t.header || !t.compressed_data || !t.output) { t.result = EOQ_ERR_NULL_PTR; continue; }
+        if (t.header->uncompressed_size == 0) { t.result = EOQ_OK; continue; }
+        s.staged.reset(new StagedTensor());
+        t.result = streams_ok ? stage_tensor(t.header, t.compressed_data, t.compressed_size, t.output_capacity, nullptr, s.st, *s.staged)
+                              : parse_payload(t.header, t.compressed_data, t.compressed_size, t.output_capacity, s.staged->pl);
+        if (t.result == EOQ_OK && !streams_ok) t.result = EOQ_ERR_CUDA;
+        if (t.result == EOQ_OK) t.result = launch_staged(*s.staged, s.st);
+        if (t.result == EOQ_OK &&
+            cudaMemcpyAsync(t.output, s.staged->d_out, s.staged->pl.total, cudaMemcpyDeviceToHost, s.st) != cudaSuccess)
+            t.result = EOQ_ERR_CUDA;
+        if (t.result != EOQ_OK) s.staged.reset();
+    }
+    // drain in task order so `done` counts up as the reference's does
+    for (int k = 0; k < lanes; k++) {
+        int oldest = -1;
+        for (int j = 0; j < lanes; j++)
+            if (slots[(size_t)j].task >= 0 && (oldest < 0 || slots[(size_t)j].task < slots[(size_t)oldest].task)) oldest = j;
+        if (oldest < 0) break;
+        retire(slots[(size_t)oldest]);
+    }
+    for (auto &s : slots) if (s.st) cudaStreamDestroy(s.st);
+
+    for (int i = 0; i < num_tasks; i++)
+        if (tasks[i].result != EOQ_OK) return tasks[i].result;        // eoq_parallel_decode.c:290-300
+    return EOQ_OK;
+}
+
+// -- incremental single-block decoder --------------------------------------
+namespace {
+struct DecoderDev {
+    DeviceBuf table, block, state_pos, out;
+    size_t out_cap = 0;
+    uint32_t stream_off = 0;
+};
+}
+
+extern "C" eoq_error_t eoq_decoder_init(eoq_decoder_t *dec, const uint16_t *freq_table, uint32_t alphabet_size,
+                                        uint32_t precision_bits, const uint8_t *block_data, size_t block_size)
+{
+    if (!dec || !freq_table || !block_data) return EOQ_ERR_NULL_PTR;
+    if (alphabet_size == 0 || alphabet_size > 4096) return EOQ_ERR_INVALID_HEADER;
+    if (precision_bits == 0 || precision_bits > 16) return EOQ_ERR_INVALID_HEADER;
+    dec->precision_bits = precision_bits;
+    dec->precision_mask = (1u << precision_bits) - 1;
+    dec->sym_info = nullptr;
+    dec->state = 0; dec->stream = block_data; dec->stream_pos = 0; dec->stream_end = 0;
+    std::vector<V1Table> table;
+    eoq_error_t rc = table_from_u16(freq_table, alphabet_size, precision_bits, table);
+    if (rc != EOQ_OK) return rc;
+    uint32_t state = 0, off = 0;
+    if (block_size > 0) {
+        const uint32_t sl = block_data[0];
+        if ((size_t)1 + sl > block_size) return EOQ_ERR_CORRUPT_STREAM;
+        for (uint32_t i = 0; i < sl; i++) state = (state << 8) | block_data[1 + i];
+        off = 1 + sl;
+        dec->stream = block_data + off;
+        dec->stream_end = block_size - off;
+    }
+    dec->state = state;
+    if (!have_device()) return EOQ_ERR_CUDA;
+    std::unique_ptr<DecoderDev> d(new DecoderDev());
+    d->stream_off = off;
+    if (d->table.alloc(table.size() * sizeof(V1Table)) != cudaSuccess || d->block.alloc(block_size) != cudaSuccess ||
+        d->state_pos.alloc(8) != cudaSuccess)
+        return EOQ_ERR_ALLOC;
+    const uint32_t sp[2] = {state, 0};
+    CU_TRY(cudaMemcpy(d->table.p, table.data(), table.size() * sizeof(V1Table), cudaMemcpyHostToDevice));
+    if (block_size) CU_TRY(cudaMemcpy(d->block.p, block_data, block_size, cudaMemcpyHostToDevice));
+    CU_TRY(cudaMemcpy(d->state_pos.p, sp, 8, cudaMemcpyHostToDevice));
+    dec->sym_info = reinterpret_cast<struct eoq_sym_info *>(d.release());
+    return EOQ_OK;
+}
+
+extern "C" eoq_error_t eoq_decoder_decode(eoq_decoder_t *dec, uint8_t *out, uint32_t count)
+{
+    if (!dec || !out) return EOQ_ERR_NULL_PTR;
+    if (!dec->sym_info) return EOQ_ERR_NULL_PTR;
+    if (count == 0) return EOQ_OK;
+    DecoderDev *d = reinterpret_cast<DecoderDev *>(dec->sym_info);
+    if (d->out_cap < count) {
+        if (d->out.p) { cudaFree(d->out.p); d->out.p = nullptr; }
+        if (d->out.alloc(count) != cudaSuccess) return EOQ_ERR_ALLOC;
+        d->out_cap = count;
+    }
+    int e = launch_decode_v1_resume(d->block.as<uint8_t>() + d->stream_off, (uint32_t)dec->stream_end, d->table.as<V1Table>(),
+                                    d->state_pos.as<uint32_t>(), d->out.as<uint8_t>(), count, dec->precision_bits, nullptr);
+    if (e != 0) return EOQ_ERR_CUDA;
+    uint32_t sp[2];
+    CU_TRY(cudaMemcpy(out, d->out.p, count, cudaMemcpyDeviceToHost));
+    CU_TRY(cudaMemcpy(sp, d->state_pos.p, 8, cudaMemcpyDeviceToHost));
+    dec->state = sp[0];
+    dec->stream_pos = sp[1];
+    return EOQ_OK;
+}
+
+extern "C" void eoq_decoder_free(eoq_decoder_t *dec)
+{
+    if (dec && dec->sym_info) {
+        delete reinterpret_cast<DecoderDev *>(dec->sym_info);
+        dec->sym_info = nullptr;
+    }
+}
+
+// -- eoq_cuda_* family -------------------------------------------------------
+
+extern "C" int eoq_cuda_decode_tensor(const eoq_tensor_header_t *header, const uint8_t *compressed, uint8_t *output, void *stream)
+{
+    if (!header || !compressed || !output) return -1;
+    if (header->uncompressed_size == 0) return 0;
+    return decode_host_to_host(header, compressed, header->compressed_size, output, header->uncompressed_size,
+                               reinterpret_cast<cudaStream_t>(stream)) == EOQ_OK ? 0 : -1;
+}
+
+extern "C" int eoq_cuda_decode_tensor_device(const uint8_t *d_compressed_stream, const uint32_t *d_block_offsets,
+                                             const uint32_t *d_block_sizes, const eoq_sym_info_packed *d_sym_info,
+                                             uint8_t *d_output, uint32_t num_rans_blocks, uint32_t rans_block_size,
+                                             uint32_t total_symbols, uint32_t precision_bits, void *cuda_stream)
+{
+    if (total_symbols == 0) return 0;
+    if (!d_compressed_stream || !d_block_offsets || !d_block_sizes || !d_sym_info || !d_output) return -1;
+    if (precision_bits == 0 || precision_bits > 16 || rans_block_size == 0) return -1;
+    if (!have_device()) return -1;
+    int e = launch_decode_v1_syminfo(d_compressed_stream, d_block_offsets, d_block_sizes, d_sym_info, d_output,
+                                     num_rans_blocks, rans_block_size, total_symbols, precision_bits, cuda_stream);
+    if (e != 0) { std::fprintf(stderr, "eoq_cuda_decode_tensor_device: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return -1; }
+    return 0;
+}
+
+struct eoq_cuda_batch_ctx {
+    std::vector<std::unique_ptr<StagedTensor>> tensors;
+    cudaStream_t stream = nullptr;
+};
+
+extern "C" eoq_cuda_batch_ctx_t *eoq_cuda_batch_create(void *stream)
+{
+    eoq_cuda_batch_ctx *c = new (std::nothrow) eoq_cuda_batch_ctx();
+    if (c) c->stream = reinterpret_cast<cudaStream_t>(stream);
+    return c;
+}
+
+extern "C" int eoq_cuda_batch_prepare_tensor(eoq_cuda_batch_ctx_t *ctx, const eoq_tensor_header_t *header,
+                                             const uint8_t *compressed_host, uint8_t *d_output)
+{
+    if (!ctx || !header || !compressed_host || !d_output) return -1;
+    if (ctx->tensors.size() >= 1024) {                                   // eoq_cuda_decompress.cu:862
+        std::fprintf(stderr, "eoq_cuda_batch_prepare_tensor: batch full (1024 tensors)\n");
+        return -1;
+    }
+    if (header->uncompressed_size == 0) return 0;
+    std::unique_ptr<StagedTensor> s(new StagedTensor());
+    if (stage_tensor(header, compressed_host, header->compressed_size, header->uncompressed_size, d_output, ctx->stream, *s) != EOQ_OK)
+        return -1;
+    ctx->tensors.push_back(std::move(s));
+    return 0;
+}
+
+extern "C" int eoq_cuda_batch_launch(eoq_cuda_batch_ctx_t *ctx)
+{
+    if (!ctx) return -1;
+    for (auto &s : ctx->tensors)
+        if (launch_staged(*s, ctx->stream) != EOQ_OK) return -1;
+    return 0;
+}
+
+extern "C" int eoq_cuda_batch_sync_and_free(eoq_cuda_batch_ctx_t *ctx)
+{
+    if (!ctx) return -1;
+    int rc = 0;
+    if (!ctx->tensors.empty() && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = -1;
+    ctx->tensors.clear();          // frees the staging copies; outputs belong to the caller
+    return rc;
+}
+
+extern "C" void eoq_cuda_batch_destroy(eoq_cuda_batch_ctx_t *ctx) { delete ctx; }
+
+// =========================================================================
+// Part 2: Python-facing codec entry points and the fused path
+// =========================================================================
+
+extern "C" eoq_error_t eoq_b200_decode_blocked(const uint32_t *freq, uint32_t alphabet, uint32_t precision_bits,
+                                               const uint8_t *data, size_t data_len, const uint32_t *offsets,
+                                               uint32_t num_blocks, uint32_t block_size, uint32_t num_symbols,
+                                               void *out, int out_elem_bytes, int out_on_device, void *stream)
+{
+    if (num_symbols == 0) return EOQ_OK;
+    if (!freq || !data || !offsets || !out) return EOQ_ERR_NULL_PTR;
+    if (alphabet == 0 || block_size == 0) return EOQ_ERR_INVALID_HEADER;
+    if (precision_bits < 1 || precision_bits > 16) return EOQ_ERR_UNSUPPORTED;   // 32-bit device state
+    if (out_elem_bytes != 1 && out_elem_bytes != 2) return EOQ_ERR_UNSUPPORTED;
+    if (alphabet > (out_elem_bytes == 1 ? 256u : 65536u)) return EOQ_ERR_UNSUPPORTED;
+    if (data_len > 0xFFFFFFFFull) return EOQ_ERR_OVERFLOW;
+    if (num_blocks != (uint32_t)(((uint64_t)num_symbols + block_size - 1) / block_size)) return EOQ_ERR_INVALID_HEADER;
+    uint64_t sum = 0;
+    std::vector<uint32_t> f(freq, freq + alphabet), cdf(alphabet + 1, 0);
+    for (uint32_t s = 0; s < alphabet; s++) { sum += f[s]; cdf[s + 1] = cdf[s] + f[s]; }
+    if (sum != (1ull << precision_bits)) return EOQ_ERR_INVALID_HEADER;
+    std::vector<uint32_t> sizes(num_blocks);
+    for (uint32_t b = 0; b < num_blocks; b++) {
+        const uint64_t lo = offsets[b], hi = b + 1 < num_blocks ? offsets[b + 1] : data_len;
+        if (hi < lo || hi > data_len) return EOQ_ERR_CORRUPT_STREAM;
+        sizes[b] = (uint32_t)(hi - lo);
+        if (sizes[b] && 1u + data[lo] > sizes[b]) return EOQ_ERR_CORRUPT_STREAM;
+        if (sizes[b] && data[lo] > 4) return EOQ_ERR_UNSUPPORTED;                  // state wider than 32 bits
+    }
+    std::vector<V1Table> table;
+    make_v1_table(f, cdf, precision_bits, table);
+    if (!have_device()) return EOQ_ERR_CUDA;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    DeviceBuf d_data, d_off, d_sizes, d_table, d_out;
+    if (d_data.alloc(data_len) != cudaSuccess || d_off.alloc((size_t)num_blocks * 4) != cudaSuccess ||
+        d_sizes.alloc((size_t)num_blocks * 4) != cudaSuccess || d_table.alloc(table.size() * sizeof(V1Table)) != cudaSuccess)
+        return EOQ_ERR_ALLOC;
+    void *dst = out;
+    if (!out_on_device) {
+        if (d_out.alloc((size_t)num_symbols * out_elem_bytes) != cudaSuccess) return EOQ_ERR_ALLOC;
+        dst = d_out.p;
+    }
+    CU_TRY(cudaMemcpyAsync(d_data.p, data, data_len, cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaMemcpyAsync(d_off.p, offsets, (size_t)num_blocks * 4, cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaMemcpyAsync(d_sizes.p, sizes.data(), (size_t)num_blocks * 4, cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaMemcpyAsync(d_table.p, table.data(), table.size() * sizeof(V1Table), cudaMemcpyHostToDevice, st));
+    int e = launch_decode_v1(d_data.as<uint8_t>(), d_off.as<uint32_t>(), d_sizes.as<uint32_t>(), d_table.as<V1Table>(), dst,
+                             out_elem_bytes, num_blocks, block_size, num_symbols, precision_bits, st);
+    if (e != 0) return EOQ_ERR_CUDA;
+    if (!out_on_device) CU_TRY(cudaMemcpyAsync(out, dst, (size_t)num_symbols * out_elem_bytes, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));   // the staging buffers are freed on return
+    return EOQ_OK;
+}
+
+extern "C" eoq_error_t eoq_b200_encode_blocked(const uint32_t *freq, uint32_t alphabet, uint32_t precision_bits,
+                                               const uint32_t *symbols, uint32_t num_symbols, uint32_t block_size,
+                                               uint8_t *out, size_t *out_len, uint32_t *offsets)
+{
+    if (!out_len) return EOQ_ERR_NULL_PTR;
+    if (num_symbols == 0) { *out_len = 0; return EOQ_OK; }
+    if (!freq || !symbols || !out || !offsets) return EOQ_ERR_NULL_PTR;
+    if (alphabet == 0 || block_size == 0 || precision_bits < 1 || precision_bits > 20) return EOQ_ERR_INVALID_HEADER;
+    std::vector<uint32_t> cdf(alphabet + 1, 0);
+    uint64_t sum = 0;
+    for (uint32_t s = 0; s < alphabet; s++) { if (!freq[s]) return EOQ_ERR_INVALID_HEADER; sum += freq[s]; cdf[s + 1] = cdf[s] + freq[s]; }
+    if (sum != (1ull << precision_bits)) return EOQ_ERR_INVALID_HEADER;
+    for (uint32_t i = 0; i < num_symbols; i++) if (symbols[i] >= alphabet) return EOQ_ERR_CORRUPT_STREAM;
+    const uint32_t nb = (uint32_t)(((uint64_t)num_symbols + block_size - 1) / block_size);
+    size_t at = 0;
+    std::vector<uint8_t> blk;
+    for (uint32_t b = 0; b < nb; b++) {
+        const uint32_t first = b * block_size, n = std::min(block_size, num_symbols - first);
+        encode_block_v1(freq, cdf.data(), precision_bits, symbols + first, n, blk);
+        if (at + blk.size() > *out_len) return EOQ_ERR_BUFFER_TOO_SMALL;
+        if (at > 0xFFFFFFFFull) return EOQ_ERR_OVERFLOW;
+        offsets[b] = (uint32_t)at;
+        std::memcpy(out + at, blk.data(), blk.size());
+        at += blk.size();
+    }
+    *out_len = at;
+    return EOQ_OK;
+}
+
+// -- resident weights ---------------------------------------------------------
+
+struct eoq_b200_weight {
+    int device = 0;
+    uint32_t N = 0, K = 0, Npad = 0, G = 0, bits = 0, p = 0, group = 0, kind = 0, alphabet = 0;
+    uint32_t ntiles = 0, nseg = 0, nrb = 0;
+    DeviceBuf table, tiles, stream, scales, centroids, partials, counters, xbuf, ybuf, biasbuf;
+    size_t stream_bytes = 0, scale_bytes = 0, partial_bytes = 0;
+    std::mutex mu;   // one call at a time may use the scratch of a weight
+};
+
+namespace {
+
+eoq_error_t resolve_opts(const eoq_b200_weight_opts_t *o, uint32_t &bits, uint32_t &G, uint32_t &p, uint32_t &target, uint8_t &pad)
+{
+    if (!o) return EOQ_ERR_NULL_PTR;
+    if (o->kind == EOQ_B200_KIND_INT4_ABSMAX) { bits = 4; G = o->symbols_per_step ? o->symbols_per_step : 3; pad = 7; }
+    else if (o->kind == EOQ_B200_KIND_Q5_POLAR) { bits = 5; G = o->symbols_per_step ? o->symbols_per_step : 2; pad = 16; if (!o->centroids) return EOQ_ERR_NULL_PTR; }
+    else return EOQ_ERR_UNSUPPORTED;
+    if (G < 1 || G > (bits == 4 ? 3u : 2u)) return EOQ_ERR_UNSUPPORTED;
+    p = o->precision_bits ? o->precision_bits : std::min(16u, std::max(12u, bits * G + 2));
+    if (p > 14 || p < bits * G) return EOQ_ERR_UNSUPPORTED;        // table must fit shared memory beside x
+    target = o->target_tiles;
+    return EOQ_OK;
+}
+
+eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const float *centroids, eoq_b200_weight_t **out)
+{
+    std::unique_ptr<eoq_b200_weight> w(new eoq_b200_weight());
+    CU_TRY(cudaGetDevice(&w->device));
+    w->N = tw.N; w->K = tw.K; w->Npad = tw.Npad; w->G = tw.G; w->bits = tw.bits; w->p = tw.p; w->group = tw.group;
+    w->kind = tw.kind; w->alphabet = tw.alphabet; w->ntiles = (uint32_t)tw.tiles.size(); w->nseg = tw.nseg; w->nrb = tw.nrb;
+    w->stream_bytes = tw.stream.size();
+    w->scale_bytes = (size_t)tw.N * (tw.K / tw.group) * 2;
+    w->partial_bytes = tw.nseg > 1 ? (size_t)tw.nseg * tw.Npad * 8 * sizeof(float) : 0;
+    if (w->table.alloc(tw.table.size() * 4) != cudaSuccess || w->tiles.alloc(tw.tiles.size() * sizeof(TileDesc)) != cudaSuccess ||
+        w->stream.alloc(tw.stream.size()) != cudaSuccess || w->scales.alloc(w->scale_bytes) != cudaSuccess ||
+        w->partials.alloc(w->partial_bytes) != cudaSuccess || w->counters.alloc((size_t)tw.nrb * 4) != cudaSuccess ||
+        w->xbuf.alloc((size_t)8 * tw.K * 4) != cudaSuccess || w->ybuf.alloc((size_t)8 * tw.N * 4) != cudaSuccess ||
+        w->biasbuf.alloc((size_t)tw.N * 4) != cudaSuccess)
+        return EOQ_ERR_ALLOC;
+    if (centroids) {
+        if (w->centroids.alloc(32 * 4) != cudaSuccess) return EOQ_ERR_ALLOC;
+        CU_TRY(cudaMemcpy(w->centroids.p, centroids, 32 * 4, cudaMemcpyHostToDevice));
+    }
+    CU_TRY(cudaMemcpy(w->table.p, tw.table.data(), tw.table.size() * 4, cudaMemcpyHostToDevice));
+    CU_TRY(cudaMemcpy(w->tiles.p, tw.tiles.data(), tw.tiles.size() * sizeof(TileDesc), cudaMemcpyHostToDevice));
+    CU_TRY(cudaMemcpy(w->stream.p, tw.stream.data(), tw.stream.size(), cudaMemcpyHostToDevice));
+    CU_TRY(cudaMemcpy(w->scales.p, scales, w->scale_bytes, cudaMemcpyHostToDevice));
+    CU_TRY(cudaMemset(w->counters.p, 0, (size_t)tw.nrb * 4));
+    *out = w.release();
+    return EOQ_OK;
+}
+
+}  // namespace
+
+struct eoq_b200_tiles { TiledWeights tw; };
+
+extern "C" eoq_error_t eoq_b200_tiles_build(const uint8_t *symbols, const eoq_b200_weight_opts_t *opts, eoq_b200_tiles_t **out)
+{
+    if (!symbols || !opts || !out) return EOQ_ERR_NULL_PTR;
+    *out = nullptr;
+    uint32_t bits, G, p, target; uint8_t pad;
+    eoq_error_t rc = resolve_opts(opts, bits, G, p, target, pad);
+    if (rc != EOQ_OK) return rc;
+    if (opts->rows == 0 || opts->cols == 0 || opts->group == 0) return EOQ_ERR_INVALID_HEADER;
+    if (target == 0) {
+        const int sms = have_device() ? device_sm_count() : 0;
+        target = (uint32_t)(sms > 0 ? sms : 148) * 16;
+    }
+    std::unique_ptr<eoq_b200_tiles> t(new eoq_b200_tiles());
+    rc = build_tiled(symbols, opts->rows, opts->cols, bits, G, p, opts->group, opts->kind, target, pad, t->tw);
+    if (rc != EOQ_OK) return rc;
+    *out = t.release();
+    return EOQ_OK;
+}
+
+extern "C" eoq_error_t eoq_b200_tiles_view(const eoq_b200_tiles_t *t, eoq_b200_tiles_view_t *v)
+{
+    if (!t || !v) return EOQ_ERR_NULL_PTR;
+    const TiledWeights &tw = t->tw;
+    v->rows = tw.N; v->cols = tw.K; v->padded_rows = tw.Npad; v->group = tw.group; v->kind = tw.kind; v->bits = tw.bits;
+    v->symbols_per_step = tw.G; v->precision_bits = tw.p;
+    v->num_tiles = (uint32_t)tw.tiles.size(); v->num_col_segments = tw.nseg;
+    v->table = tw.table.data();
+    static_assert(sizeof(eoq_b200_tile_desc_t) == sizeof(TileDesc), "tile descriptor layout");
+    v->tiles = reinterpret_cast<const eoq_b200_tile_desc_t *>(tw.tiles.data());
+    v->stream = tw.stream.data();
+    v->stream_bytes = tw.stream.size();
+    return EOQ_OK;
+}
+
+extern "C" void eoq_b200_tiles_free(eoq_b200_tiles_t *t) { delete t; }
+
+extern "C" eoq_error_t eoq_b200_weight_from_symbols(const uint8_t *symbols, const uint16_t *scales_fp16,
+                                                    const eoq_b200_weight_opts_t *opts, eoq_b200_weight_t **out)
+{
+    if (!symbols || !scales_fp16 || !opts || !out) return EOQ_ERR_NULL_PTR;
+    *out = nullptr;
+    if (!have_device()) {
+        uint32_t bits, G, p, target; uint8_t pad;
+        eoq_error_t rc = resolve_opts(opts, bits, G, p, target, pad);
+        return rc != EOQ_OK ? rc : EOQ_ERR_CUDA;
+    }
+    eoq_b200_tiles_t *t = nullptr;
+    eoq_error_t rc = eoq_b200_tiles_build(symbols, opts, &t);
+    if (rc != EOQ_OK) return rc;
+    rc = upload_weight(t->tw, scales_fp16, opts->kind == EOQ_B200_KIND_Q5_POLAR ? opts->centroids : nullptr, out);
+    eoq_b200_tiles_free(t);
+    return rc;
+}
+
+extern "C" eoq_error_t eoq_b200_weight_from_rans(const uint8_t *c, size_t size, const uint16_t *scales_fp16,
+                                                 const eoq_b200_weight_opts_t *opts, eoq_b200_weight_t **out)
+{
+    if (!c || !scales_fp16 || !opts || !out) return EOQ_ERR_NULL_PTR;
+    *out = nullptr;
+    // `RANS` container: magic, then 7 x u32 (version, num_symbols, block_size, num_blocks, alphabet,
+    // precision_bits, data_size), u32 freq[alphabet], u32 offsets[num_blocks], data  (core/rans_blocked.py:176-214)
+    if (size < 32 || std::memcmp(c, "RANS", 4) != 0) return EOQ_ERR_INVALID_HEADER;
+    uint32_t h[7];
+    std::memcpy(h, c + 4, 28);
+    if (h[0] != 1) return EOQ_ERR_INVALID_HEADER;
+    const uint32_t n = h[1], bs = h[2], nb = h[3], a = h[4], p = h[5], dsz = h[6];
+    if ((uint64_t)32 + (uint64_t)a * 4 + (uint64_t)nb * 4 + dsz > size) return EOQ_ERR_CORRUPT_STREAM;
+    if ((uint64_t)opts->rows * opts->cols != n) return EOQ_ERR_INVALID_HEADER;
+    if (a == 0 || a > 256) return EOQ_ERR_UNSUPPORTED;
+    std::vector<uint32_t> raw(a), freq, cdf, offs(nb);
+    std::memcpy(raw.data(), c + 32, (size_t)a * 4);
+    std::memcpy(offs.data(), c + 32 + (size_t)a * 4, (size_t)nb * 4);
+    eoq_error_t rc = normalize_reference(raw.data(), a, p, freq, cdf);
+    if (rc != EOQ_OK) return rc;
+    std::vector<uint8_t> sym(n);
+    rc = eoq_b200_decode_blocked(freq.data(), a, p, c + 32 + (size_t)a * 4 + (size_t)nb * 4, dsz, offs.data(), nb, bs, n,
+                                 sym.data(), 1, 0, nullptr);
+    if (rc != EOQ_OK) return rc;
+    return eoq_b200_weight_from_symbols(sym.data(), scales_fp16, opts, out);
+}
+
+extern "C" void eoq_b200_weight_destroy(eoq_b200_weight_t *w) { delete w; }
+
+extern "C" eoq_error_t eoq_b200_weight_info(const eoq_b200_weight_t *w, eoq_b200_weight_info_t *info)
+{
+    if (!w || !info) return EOQ_ERR_NULL_PTR;
+    info->rows = w->N; info->cols = w->K; info->padded_rows = w->Npad; info->group = w->group; info->kind = w->kind;
+    info->symbols_per_step = w->G; info->precision_bits = w->p; info->alphabet = w->alphabet;
+    info->num_tiles = w->ntiles; info->num_col_segments = w->nseg;
+    info->stream_bytes = w->stream_bytes;
+    info->table_bytes = (uint64_t)4 << w->p;
+    info->scale_bytes = w->scale_bytes;
+    info->desc_bytes = (uint64_t)w->ntiles * sizeof(TileDesc);
+    info->scratch_bytes = w->partial_bytes + (uint64_t)w->nrb * 4;
+    info->bits_per_weight = (double)w->stream_bytes * 8.0 / ((double)w->N * w->K);
+    return EOQ_OK;
+}
+
+extern "C" eoq_error_t eoq_b200_gemv(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch, void *y, int y_dtype,
+                                     const float *bias, void *stream)
+{
+    if (!w || !x || !y) return EOQ_ERR_NULL_PTR;
+    if (batch == 0) return EOQ_OK;
+    if (batch > 8) return EOQ_ERR_UNSUPPORTED;
+    if (x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2) return EOQ_ERR_UNSUPPORTED;
+    const uint32_t bt = batch <= 1 ? 1 : batch <= 2 ? 2 : batch <= 4 ? 4 : 8;
+    if (gemv_smem_bytes(w->K, w->p, bt, w->kind) > 227 * 1024) return EOQ_ERR_UNSUPPORTED;
+    GemvArgs a;
+    a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
+    a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
+    a.x = x; a.y = y; a.bias = bias; a.partials = w->partials.as<float>(); a.counters = w->counters.as<uint32_t>();
+    a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
+    a.x_dtype = x_dtype; a.y_dtype = y_dtype;
+    int e = launch_gemv(a, w->G, w->bits, w->kind, stream);
+    if (e != 0) { std::fprintf(stderr, "eoq_b200_gemv: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
+    return EOQ_OK;
+}
+
+extern "C" eoq_error_t eoq_b200_gemv_host(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch, void *y, int y_dtype,
+                                          const float *bias_host, void *stream)
+{
+    if (!w || !x || !y) return EOQ_ERR_NULL_PTR;
+    if (batch == 0) return EOQ_OK;
+    if (batch > 8 || x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2) return EOQ_ERR_UNSUPPORTED;
+    static const size_t esz[3] = {2, 2, 4};
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    std::lock_guard<std::mutex> lock(w->mu);
+    CU_TRY(cudaMemcpyAsync(w->xbuf.p, x, (size_t)batch * w->K * esz[x_dtype], cudaMemcpyHostToDevice, st));
+    if (bias_host) CU_TRY(cudaMemcpyAsync(w->biasbuf.p, bias_host, (size_t)w->N * 4, cudaMemcpyHostToDevice, st));
+    eoq_error_t rc = eoq_b200_gemv(w, w->xbuf.p, x_dtype, batch, w->ybuf.p, y_dtype, bias_host ? w->biasbuf.as<float>() : nullptr, stream);
+    if (rc != EOQ_OK) return rc;
+    CU_TRY(cudaMemcpyAsync(y, w->ybuf.p, (size_t)batch * w->N * esz[y_dtype], cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    return EOQ_OK;
+}
+
+extern "C" eoq_error_t eoq_b200_weight_decode(eoq_b200_weight_t *w, uint8_t *d_sym, int packed, void *d_dequant, int out_dtype, void *stream)
+{
+    if (!w) return EOQ_ERR_NULL_PTR;
+    if (!d_sym && !d_dequant) return EOQ_OK;
+    if (packed && w->bits != 4) return EOQ_ERR_UNSUPPORTED;
+    if (d_dequant && w->kind != EOQ_B200_KIND_INT4_ABSMAX) return EOQ_ERR_UNSUPPORTED;
+    if (out_dtype < 0 || out_dtype > 2) return EOQ_ERR_UNSUPPORTED;
+    DecodeArgs a;
+    a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
+    a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
+    a.out_sym = d_sym; a.out_deq = d_dequant; a.N = w->N; a.K = w->K; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles;
+    a.packed = packed; a.out_dtype = out_dtype;
+    int e = launch_decode_tiles(a, w->G, w->bits, w->kind, stream);
+    if (e != 0) { std::fprintf(stderr, "eoq_b200_weight_decode: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
+    return EOQ_OK;
+}
+
+extern "C" eoq_error_t eoq_b200_dequant_packed(const uint8_t *d_packed, const uint16_t *d_scales_fp16, uint32_t rows, uint32_t cols,
+                                               uint32_t bits, uint32_t group, uint32_t row_lo, uint32_t row_hi, void *d_out,
+                                               int out_dtype, void *stream)
+{
+    if (!d_packed || !d_scales_fp16 || !d_out) return EOQ_ERR_NULL_PTR;
+    if (bits < 2 || bits > 8 || group == 0 || cols == 0) return EOQ_ERR_INVALID_HEADER;
+    if (row_lo > row_hi || row_hi > rows) return EOQ_ERR_INVALID_HEADER;
+    if (out_dtype < 0 || out_dtype > 2) return EOQ_ERR_UNSUPPORTED;
+    if (!have_device()) return EOQ_ERR_CUDA;
+    // row stride of QuantizedLinear.packed_weight (core/quantized_linear.py:49-66)
+    const uint32_t row_bytes = bits == 4 ? (cols + 1) / 2 : bits == 2 ? (cols + 3) / 4 : cols;
+    int e = launch_dequant_packed(d_packed, d_scales_fp16, cols, row_bytes, bits, group, row_lo, row_hi, d_out, out_dtype, stream);
+    if (e != 0) { std::fprintf(stderr, "eoq_b200_dequant_packed: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
+    return EOQ_OK;
+}
+
+extern "C" uint64_t eoq_b200_launch_count(void) { return launch_counter(); }

@@ -1,0 +1,124 @@
+// Internal declarations shared by the host codec, the kernels and the C ABI.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "../../include/eoq_b200.h"
+
+namespace eoq {
+
+// ---------------------------------------------------------------------------
+// Tiled device layout ("v2").
+//
+// A weight matrix [N, K] is cut into tiles of (32*G rows) x (ncols columns).
+// One warp decodes one tile; lane l owns rows row0 + l*G .. row0 + l*G + G-1
+// and walks the tile's columns left to right.  Each rANS step decodes ONE joint
+// symbol holding the G weights of the lane's rows at the current column:
+//     sym = n_0 | n_1 << bits | ... | n_{G-1} << (G-1)*bits.
+// Every lane has its own rANS stream: 32-bit state in [2^16, 2^32), 16-bit
+// renormalisation words, at most one word per step (precision <= 16).
+//
+// Tile bytes:  [32 x u32 initial states][rows of 32 x u16]
+// where row k holds, for lane l, that lane's k-th renormalisation word; lanes
+// that need fewer words than the longest lane are padded with zeros, and the
+// row count is even so every tile starts on a 128-byte boundary.
+//
+// Table entry (one 32-bit word per slot, 2^p slots):
+//     [31:23] freq (1..511)   [22:23-G*bits] sym   [low bits] slot - cum(sym)
+// so that one shared-memory load yields everything a step needs, and the INT4
+// fields sit in float mantissa bits (see kernels.cu).
+// ---------------------------------------------------------------------------
+struct TileDesc {
+    uint32_t row0;    // first row of the tile (multiple of 32*G)
+    uint32_t col0;    // first column
+    uint32_t ncols;   // columns (= rANS steps per lane), multiple of 16
+    uint32_t seg;     // column-segment index (same for all row blocks)
+    uint32_t off64;   // byte offset of the tile in the stream, divided by 64
+    uint32_t rb;      // row-block index
+};
+
+constexpr uint32_t kMaxFreq = 511;
+constexpr uint32_t kColGranule = 16;   // tile column boundaries are multiples of this
+
+struct TiledWeights {
+    uint32_t N = 0, K = 0, Npad = 0, G = 0, bits = 0, p = 0, group = 0, kind = 0;
+    uint32_t alphabet = 0;       // (1 << bits*G) slots in the joint symbol space
+    uint32_t nrb = 0, nseg = 0;
+    std::vector<uint32_t> table;     // 1 << p entries
+    std::vector<TileDesc> tiles;     // nrb * nseg
+    std::vector<uint32_t> seg_start; // nseg + 1 column boundaries
+    std::vector<uint8_t>  stream;    // all tiles + 256 bytes of tail padding
+};
+
+// Host codec (rans_host.cpp) -------------------------------------------------
+
+// Reference normalisation (core/rans.py:85-153; stable descending order as
+// eoq_rans_v2.c:78-141).  raw has `alphabet` entries; freq/cdf are resized.
+eoq_error_t normalize_reference(const uint32_t *raw, uint32_t alphabet, uint32_t p,
+                                std::vector<uint32_t> &freq, std::vector<uint32_t> &cdf);
+
+// Wire-format ("v1") block encoder, byte-identical to core/rans.py:210-276.
+void encode_block_v1(const uint32_t *freq, const uint32_t *cdf, uint32_t p,
+                     const uint32_t *syms, uint32_t n, std::vector<uint8_t> &out);
+
+// Build the tiled layout from one symbol per byte, row-major [N, K].
+eoq_error_t build_tiled(const uint8_t *symbols, uint32_t N, uint32_t K, uint32_t bits, uint32_t G,
+                        uint32_t p, uint32_t group, uint32_t kind, uint32_t target_tiles,
+                        uint8_t pad_symbol, TiledWeights &out);
+
+// Kernels (kernels.cu) --------------------------------------------------------
+
+struct V1Table {          // wire-format decode table entry, one per slot
+    uint32_t freq;        // 1..65536
+    uint32_t sym_bias;    // sym << 16 | (slot - cum)
+};
+
+struct GemvArgs {
+    const uint32_t *table;
+    const TileDesc *tiles;
+    const uint8_t  *stream;
+    const uint16_t *scales;     // fp16 bits, [N * K/group]
+    const float    *centroids;  // polar: 32 floats, else null
+    const void     *x;          // [batch, K]
+    void           *y;          // [batch, N]
+    const float    *bias;       // [N] or null
+    float          *partials;   // [nseg][Npad][BT]
+    uint32_t       *counters;   // [nrb], zero on entry, zero on exit
+    uint32_t N, K, Npad, group, p, ntiles, nseg, batch;
+    int x_dtype, y_dtype;
+};
+
+struct DecodeArgs {
+    const uint32_t *table;
+    const TileDesc *tiles;
+    const uint8_t  *stream;
+    const uint16_t *scales;
+    const float    *centroids;  // unused for INT4
+    uint8_t        *out_sym;    // packed nibbles [N, K/2] or bytes [N, K], or null
+    void           *out_deq;    // [N, K] or null
+    uint32_t N, K, group, p, ntiles;
+    int packed, out_dtype;
+};
+
+int  device_sm_count();
+// Each returns a cudaError_t as int; launches are asynchronous on `stream`.
+int launch_gemv(const GemvArgs &a, uint32_t G, uint32_t bits, uint32_t kind, void *stream);
+int launch_decode_tiles(const DecodeArgs &a, uint32_t G, uint32_t bits, uint32_t kind, void *stream);
+int launch_decode_v1(const uint8_t *d_stream, const uint32_t *d_offsets, const uint32_t *d_sizes,
+                     const V1Table *d_table, void *d_out, int out_elem_bytes, uint32_t nblocks,
+                     uint32_t block_size, uint32_t total, uint32_t p, void *stream);
+int launch_decode_v1_syminfo(const uint8_t *d_stream, const uint32_t *d_offsets, const uint32_t *d_sizes,
+                             const eoq_sym_info_packed *d_info, uint8_t *d_out, uint32_t nblocks,
+                             uint32_t block_size, uint32_t total, uint32_t p, void *stream);
+int launch_decode_v1_resume(const uint8_t *d_block, uint32_t stream_end, const V1Table *d_table,
+                            uint32_t *d_state_pos /* [2]: state, pos */, uint8_t *d_out, uint32_t count,
+                            uint32_t p, void *stream);
+int launch_dequant_packed(const uint8_t *packed, const uint16_t *scales, uint32_t K, uint32_t row_bytes, uint32_t bits,
+                          uint32_t group, uint32_t row_lo, uint32_t row_hi, void *out, int out_dtype, void *stream);
+size_t gemv_smem_bytes(uint32_t K, uint32_t p, uint32_t bt, uint32_t kind);
+uint64_t launch_counter();
+
+}  // namespace eoq

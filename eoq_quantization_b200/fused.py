@@ -1,0 +1,168 @@
+"""Python face of the fused path: a weight matrix resident in HBM as
+entropy-coded tiles (``eoq_b200_weight_t``) and the calls that consume it.
+
+torch is used for device memory and streams only; every computation is a call
+into ``libeoq_b200.so``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
+_NP_DTYPES = {np.dtype(np.float16): _lib.F16, np.dtype(np.float32): _lib.F32}
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def require_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{what}: tensor is on {t.device}; this implementation computes on a CUDA device only "
+                           "(there is no CPU path)")
+
+
+class EOQWeight:
+    """Owner of one ``eoq_b200_weight_t``."""
+
+    def __init__(self, handle: int, kind: int):
+        self._h = C.c_void_p(handle)
+        self.kind = kind
+        info = _lib.WeightInfo()
+        _lib.check(_lib.lib().eoq_b200_weight_info(self._h, C.byref(info)), "eoq_b200_weight_info")
+        self.info = info
+        self.rows, self.cols = info.rows, info.cols
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            try:
+                _lib.lib().eoq_b200_weight_destroy(h)
+            except Exception:
+                pass
+
+    # -- construction --------------------------------------------------------
+    @staticmethod
+    def _opts(kind: int, rows: int, cols: int, group: int, symbols_per_step: int, precision_bits: int,
+              target_tiles: int, centroids: Optional[Sequence[float]]):
+        cent = None
+        if centroids is not None:
+            cent = (C.c_float * 32)(*[float(v) for v in centroids])
+        o = _lib.WeightOpts(kind, rows, cols, group, symbols_per_step, precision_bits, target_tiles,
+                            C.cast(cent, C.POINTER(C.c_float)) if cent is not None else None)
+        return o, cent
+
+    @classmethod
+    def from_symbols(cls, symbols, scales_fp16, *, kind: int = _lib.KIND_INT4_ABSMAX, group: int = 128,
+                     symbols_per_step: int = 0, precision_bits: int = 0, target_tiles: int = 0,
+                     centroids: Optional[Sequence[float]] = None) -> "EOQWeight":
+        """symbols: uint8 [N, K] (INT4: code+7; polar: centroid index); scales_fp16: float16 [N*K/group]."""
+        sym = np.ascontiguousarray(symbols.detach().cpu().numpy() if isinstance(symbols, torch.Tensor) else symbols,
+                                   dtype=np.uint8)
+        sc = scales_fp16.detach().cpu().numpy() if isinstance(scales_fp16, torch.Tensor) else np.asarray(scales_fp16)
+        sc = np.ascontiguousarray(sc.astype(np.float16, copy=False))
+        n, k = sym.shape
+        if sc.size != n * k // group:
+            raise ValueError(f"expected {n * k // group} scales, got {sc.size}")
+        o, keep = cls._opts(kind, n, k, group, symbols_per_step, precision_bits, target_tiles, centroids)
+        h = C.c_void_p()
+        _lib.check(_lib.lib().eoq_b200_weight_from_symbols(sym.ctypes.data, sc.ctypes.data, C.byref(o), C.byref(h)),
+                   "eoq_b200_weight_from_symbols")
+        return cls(h.value, kind)
+
+    @classmethod
+    def from_int4_packed(cls, packed, scales_fp16, in_features: int, *, group: int = 128, **kw) -> "EOQWeight":
+        """packed: QuantizedLinear.packed_weight, uint8 [N, K/2], low nibble = even column, value code+7."""
+        pk = packed.detach().cpu().numpy() if isinstance(packed, torch.Tensor) else np.asarray(packed)
+        sym = np.stack([pk & 0x0F, pk >> 4], axis=-1).reshape(pk.shape[0], -1)[:, :in_features]
+        return cls.from_symbols(sym, scales_fp16, kind=_lib.KIND_INT4_ABSMAX, group=group, **kw)
+
+    @classmethod
+    def from_rans(cls, rans_bytes: bytes, scales_fp16, shape, *, kind: int = _lib.KIND_INT4_ABSMAX, group: int = 128,
+                  symbols_per_step: int = 0, precision_bits: int = 0, target_tiles: int = 0,
+                  centroids: Optional[Sequence[float]] = None) -> "EOQWeight":
+        """rans_bytes: the reference's serialised `RANS` container of the symbols of an [N, K] matrix."""
+        buf = np.frombuffer(rans_bytes, dtype=np.uint8)
+        sc = np.frombuffer(scales_fp16, dtype=np.float16) if isinstance(scales_fp16, (bytes, bytearray)) else \
+            np.ascontiguousarray(np.asarray(scales_fp16).astype(np.float16, copy=False))
+        n, k = shape
+        o, keep = cls._opts(kind, n, k, group, symbols_per_step, precision_bits, target_tiles, centroids)
+        h = C.c_void_p()
+        _lib.check(_lib.lib().eoq_b200_weight_from_rans(buf.ctypes.data, buf.size, sc.ctypes.data, C.byref(o), C.byref(h)),
+                   "eoq_b200_weight_from_rans")
+        return cls(h.value, kind)
+
+    # -- use -------------------------------------------------------------------
+    def gemv(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """y = x @ W.T (+ bias) for x of shape (..., K) with at most 8 rows in total."""
+        require_cuda(x, "EOQWeight.gemv")
+        if x.shape[-1] != self.cols:
+            raise ValueError(f"expected last dimension {self.cols}, got {x.shape[-1]}")
+        if x.dtype not in _DTYPES:
+            raise TypeError(f"unsupported activation dtype {x.dtype}")
+        x2 = x.reshape(-1, self.cols).contiguous()
+        rows = x2.shape[0]
+        out_dtype = out_dtype or x.dtype
+        y = torch.empty((rows, self.rows), dtype=out_dtype, device=x.device)
+        b = None
+        if bias is not None:
+            b = bias.to(device=x.device, dtype=torch.float32).contiguous()
+        for lo in range(0, rows, 8):
+            hi = min(rows, lo + 8)
+            _lib.check(_lib.lib().eoq_b200_gemv(self._h, x2[lo:hi].data_ptr(), _DTYPES[x.dtype], hi - lo,
+                                                y[lo:hi].data_ptr(), _DTYPES[out_dtype],
+                                                b.data_ptr() if b is not None else None, _stream_ptr()), "eoq_b200_gemv")
+        return y.reshape(*x.shape[:-1], self.rows)
+
+    def gemv_host(self, x: np.ndarray, bias: Optional[np.ndarray] = None) -> np.ndarray:
+        """Same with numpy buffers on the host (copies in, runs, copies out, synchronises)."""
+        x2 = np.ascontiguousarray(x).reshape(-1, self.cols)
+        if x2.dtype not in _NP_DTYPES:
+            raise TypeError(f"unsupported activation dtype {x2.dtype}")
+        if x2.shape[0] > 8:
+            raise ValueError("at most 8 rows per call")
+        y = np.empty((x2.shape[0], self.rows), x2.dtype)
+        b = None if bias is None else np.ascontiguousarray(bias, np.float32)
+        code = _NP_DTYPES[x2.dtype]
+        _lib.check(_lib.lib().eoq_b200_gemv_host(self._h, x2.ctypes.data, code, x2.shape[0], y.ctypes.data, code,
+                                                 b.ctypes.data if b is not None else None, None), "eoq_b200_gemv_host")
+        return y.reshape(*np.shape(x)[:-1], self.rows)
+
+    def decode_symbols(self, packed: bool = False, device=None) -> torch.Tensor:
+        """Decoded symbols: uint8 [N, K], or packed two per byte [N, K/2] as QuantizedLinear stores them."""
+        dev = torch.device(device or "cuda")
+        shape = (self.rows, self.cols // 2) if packed else (self.rows, self.cols)
+        out = torch.empty(shape, dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().eoq_b200_weight_decode(self._h, out.data_ptr(), int(packed), None, 0, _stream_ptr()),
+                       "eoq_b200_weight_decode")
+        return out
+
+    def dequantize(self, dtype: torch.dtype = torch.float16, device=None) -> torch.Tensor:
+        """Dense [N, K] matrix (INT4 kind): (sym - 7) * scale."""
+        dev = torch.device(device or "cuda")
+        out = torch.empty((self.rows, self.cols), dtype=dtype, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().eoq_b200_weight_decode(self._h, None, 0, out.data_ptr(), _DTYPES[dtype], _stream_ptr()),
+                       "eoq_b200_weight_decode")
+        return out
+
+
+def dequant_packed(packed: torch.Tensor, scales: torch.Tensor, rows: int, cols: int, bits: int, group: int,
+                   row_lo: int = 0, row_hi: Optional[int] = None, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Dense rows [row_lo, row_hi) of a packed QuantizedLinear weight, computed by the library's kernel."""
+    require_cuda(packed, "dequant_packed")
+    row_hi = rows if row_hi is None else row_hi
+    pk = packed.contiguous()
+    sc = scales.to(device=packed.device, dtype=torch.float16).contiguous()
+    out = torch.empty((row_hi - row_lo, cols), dtype=dtype, device=packed.device)
+    with torch.cuda.device(packed.device):
+        _lib.check(_lib.lib().eoq_b200_dequant_packed(pk.data_ptr(), sc.data_ptr(), rows, cols, bits, group, row_lo, row_hi,
+                                                      out.data_ptr(), _DTYPES[dtype], _stream_ptr()), "eoq_b200_dequant_packed")
+    return out

@@ -1,0 +1,296 @@
+/*
+ * eoq_b200.h -- C ABI of libeoq_b200.so, the sm_100a implementation of EOQ's
+ * inference hot path: blocked rANS decode of entropy-coded quantised weights,
+ * fused with per-group dequantisation and the GEMV that consumes them.
+ *
+ * Plain C: pointers and sizes only.  Every compute entry point runs on the
+ * GPU; there is no CPU fallback.  On a machine without a CUDA device the
+ * compute entry points return EOQ_ERR_CUDA (or -1 for the eoq_cuda_* family),
+ * after argument validation, which never touches the device.
+ *
+ * Part 1 mirrors the reference's C interface one-for-one (same names, argument
+ * meaning and error behaviour); each declaration cites the reference
+ * declaration it replaces.  Part 2 is the fused path, which the reference
+ * plans (PLANO_NIVEL2.md:19, core/eoq_linear.py:49-51) but does not have.
+ */
+#ifndef EOQ_B200_H
+#define EOQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ===================================================================== *
+ * Part 1 -- drop-in for llamacpp_integration/eoq_rans_v2.h,
+ *           eoq_parallel_decode.h and eoq_cuda_decompress.cu
+ * ===================================================================== */
+
+/* eoq_rans_v2.h:36-45.  EOQ_ERR_CUDA and EOQ_ERR_UNSUPPORTED are additions. */
+typedef enum {
+    EOQ_OK                   =  0,
+    EOQ_ERR_NULL_PTR         = -1,
+    EOQ_ERR_BUFFER_TOO_SMALL = -2,
+    EOQ_ERR_CORRUPT_STREAM   = -3,
+    EOQ_ERR_INVALID_HEADER   = -4,
+    EOQ_ERR_ALLOC            = -5,
+    EOQ_ERR_THREAD           = -6,   /* also: task skipped after a cancel request */
+    EOQ_ERR_OVERFLOW         = -7,
+    EOQ_ERR_CUDA             = -8,   /* no device, or a CUDA call failed */
+    EOQ_ERR_UNSUPPORTED      = -9    /* legal input this build does not handle */
+} eoq_error_t;
+
+/* eoq_rans_v2.h:48 */
+const char *eoq_error_string(eoq_error_t err);
+
+/* eoq_rans_v2.h:54-62 (same field order and widths). */
+typedef struct {
+    uint32_t original_type;
+    uint32_t num_blocks;
+    uint32_t freq_table_size;    /* alphabet, 1..4096 (symbols are written as bytes) */
+    uint32_t precision_bits;     /* 1..16 */
+    uint32_t rans_block_size;    /* symbols per independent rANS block */
+    uint32_t compressed_size;    /* bytes of payload, metadata included */
+    uint32_t uncompressed_size;  /* symbols == output bytes */
+} eoq_tensor_header_t;
+
+/* eoq_rans_v2.h:77-81 */
+typedef int (*eoq_progress_fn)(size_t bytes_decoded, size_t bytes_total, void *user_data);
+
+/* eoq_rans_v2.h:87-91.  n_threads is accepted and ignored: every rANS block of
+ * the tensor is decoded by its own GPU thread in one launch. */
+typedef struct {
+    uint32_t        n_threads;
+    eoq_progress_fn progress_cb;
+    void           *progress_ud;
+} eoq_decode_opts_t;
+
+/* eoq_rans_v2.h:116-123.  Host buffers in, host buffer out.  Payload layout
+ * [u16 freq x A][u32 block_offsets x B][blocks] (eoq_rans_v2.c:606-619).
+ * Checks, in the reference's order: NULL -> zero length (OK) -> header ->
+ * out_cap -> comp_size -> metadata size -> offsets monotone and in range
+ * (eoq_rans_v2.c:586-599, :542-545) -> 1+state_len <= block bytes (:392). */
+eoq_error_t eoq_decode_tensor_v2(const eoq_tensor_header_t *header, const uint8_t *compressed,
+                                 size_t comp_size, void *output, size_t out_cap,
+                                 const eoq_decode_opts_t *opts);
+
+/* eoq_rans_v2.h:129-133 */
+int eoq_decode_tensor(const eoq_tensor_header_t *header, const uint8_t *compressed, void *output);
+
+/* eoq_rans_v2.h:139 */
+eoq_error_t eoq_validate_header(const eoq_tensor_header_t *header);
+
+/* eoq_rans_v2.h:155-160 */
+struct eoq_sym_info {
+    uint16_t symbol;
+    uint16_t freq;
+    uint16_t cum_freq;
+    uint16_t _pad;
+};
+
+/* eoq_rans_v2.h:166-174.  Same fields; `stream` and `sym_info` are owned by
+ * the decoder object (device-side state is kept behind `sym_info`). */
+typedef struct {
+    uint32_t             state;
+    const uint8_t       *stream;
+    size_t               stream_pos;
+    size_t               stream_end;
+    uint32_t             precision_bits;
+    uint32_t             precision_mask;
+    struct eoq_sym_info *sym_info;
+} eoq_decoder_t;
+
+/* eoq_rans_v2.h:187-208: single-block decoder for advanced use. */
+eoq_error_t eoq_decoder_init(eoq_decoder_t *dec, const uint16_t *freq_table, uint32_t alphabet_size,
+                             uint32_t precision_bits, const uint8_t *block_data, size_t block_size);
+eoq_error_t eoq_decoder_decode(eoq_decoder_t *dec, uint8_t *out, uint32_t count);
+void        eoq_decoder_free(eoq_decoder_t *dec);
+
+/* eoq_parallel_decode.h:35-46 */
+typedef struct {
+    const eoq_tensor_header_t *header;
+    const uint8_t             *compressed_data;
+    size_t                     compressed_size;
+    void                      *output;
+    size_t                     output_capacity;
+    eoq_error_t                result;
+    int                        task_index;
+} eoq_decode_task_t;
+
+/* eoq_parallel_decode.h:64-68: nonzero return requests cancellation; calls are
+ * serialised and tensors_done increases by one per call. */
+typedef int (*eoq_parallel_progress_fn)(int tensors_done, int tensors_total, void *user_data);
+
+/* eoq_parallel_decode.h:74-78.  num_threads bounds the number of CUDA streams
+ * (and pinned staging slots) tensors are pipelined over; 0 = automatic. */
+typedef struct {
+    int                      num_threads;
+    eoq_parallel_progress_fn progress_cb;
+    void                    *progress_ud;
+} eoq_parallel_opts_t;
+
+/* eoq_parallel_decode.h:100-104.  Returns the first non-OK task result
+ * (eoq_parallel_decode.c:290-300); num_tasks <= 0 is OK; NULL tasks with
+ * num_tasks > 0 is EOQ_ERR_NULL_PTR (:155-156); tasks not started after a
+ * cancel request get EOQ_ERR_THREAD (:72-82, :197-205). */
+eoq_error_t eoq_parallel_decode(eoq_decode_task_t *tasks, int num_tasks, const eoq_parallel_opts_t *opts);
+
+/* eoq_parallel_decode.h:121 */
+int eoq_detect_num_threads(void);
+
+/* eoq_cuda_decompress.cu:405-410.  `stream` is a cudaStream_t passed as void*. */
+int eoq_cuda_decode_tensor(const eoq_tensor_header_t *header, const uint8_t *compressed,
+                           uint8_t *output, void *stream);
+
+/* eoq_cuda_decompress.cu:213-221: device table entry {symbol, freq, cum}. */
+typedef struct {
+    uint16_t symbol;
+    uint16_t freq;
+    uint16_t cum_freq;
+    uint16_t _pad;
+} eoq_sym_info_packed;
+
+/* eoq_cuda_decompress.cu:529-540.  All pointers are device pointers; asynchronous. */
+int eoq_cuda_decode_tensor_device(const uint8_t *d_compressed_stream, const uint32_t *d_block_offsets,
+                                  const uint32_t *d_block_sizes, const eoq_sym_info_packed *d_sym_info,
+                                  uint8_t *d_output, uint32_t num_rans_blocks, uint32_t rans_block_size,
+                                  uint32_t total_symbols, uint32_t precision_bits, void *cuda_stream);
+
+/* eoq_cuda_decompress.cu:864-1021: batch context (opaque here; at most 1024 tensors). */
+typedef struct eoq_cuda_batch_ctx eoq_cuda_batch_ctx_t;
+eoq_cuda_batch_ctx_t *eoq_cuda_batch_create(void *stream);      /* replaces the caller-allocated struct + _init (:882-887) */
+int  eoq_cuda_batch_prepare_tensor(eoq_cuda_batch_ctx_t *ctx, const eoq_tensor_header_t *header,
+                                   const uint8_t *compressed_host, uint8_t *d_output);   /* :900-975 */
+int  eoq_cuda_batch_launch(eoq_cuda_batch_ctx_t *ctx);           /* :985-1003 */
+int  eoq_cuda_batch_sync_and_free(eoq_cuda_batch_ctx_t *ctx);    /* :1008-1021 */
+void eoq_cuda_batch_destroy(eoq_cuda_batch_ctx_t *ctx);
+
+/* ===================================================================== *
+ * Part 2 -- the fused path and the Python-facing codec entry points
+ * ===================================================================== */
+
+/* Blocked decode behind core/rans_blocked.py:124-165 (BlockedRANSDecoder) and
+ * core/rans_bitpacked.py:126-154.  `freq` is the NORMALISED table (sum 2^p, all
+ * >= 1; the caller normalises as core/rans.py:85-153 does).  `data`/`offsets`
+ * are host pointers.  out_elem_bytes is 1 or 2.  If out_on_device is nonzero
+ * `out` is a device pointer and the call is asynchronous on `stream`. */
+eoq_error_t eoq_b200_decode_blocked(const uint32_t *freq, uint32_t alphabet, uint32_t precision_bits,
+                                    const uint8_t *data, size_t data_len, const uint32_t *offsets,
+                                    uint32_t num_blocks, uint32_t block_size, uint32_t num_symbols,
+                                    void *out, int out_elem_bytes, int out_on_device, void *stream);
+
+/* Host encoder behind core/rans_blocked.py:72-114 (wire-compatible with
+ * core/rans.py:210-276).  Writes blocks back to back into `out` and their
+ * offsets into `offsets`; *out_len in = capacity, out = bytes used. */
+eoq_error_t eoq_b200_encode_blocked(const uint32_t *freq, uint32_t alphabet, uint32_t precision_bits,
+                                    const uint32_t *symbols, uint32_t num_symbols, uint32_t block_size,
+                                    uint8_t *out, size_t *out_len, uint32_t *offsets);
+
+/* A weight matrix resident in HBM as entropy-coded tiles. */
+typedef struct eoq_b200_weight eoq_b200_weight_t;
+
+#define EOQ_B200_KIND_INT4_ABSMAX 0   /* w = (sym - 7) * scale[flat/group], core/quantized_linear.py:189-217 */
+#define EOQ_B200_KIND_Q5_POLAR    1   /* w_block = norm/sqrt(d) * (centroid[sym] @ H), core/polar_quant.py:216-264 */
+
+#define EOQ_B200_F16  0
+#define EOQ_B200_BF16 1
+#define EOQ_B200_F32  2
+
+typedef struct {
+    uint32_t kind;             /* EOQ_B200_KIND_* */
+    uint32_t rows, cols;       /* N (out_features), K (in_features) */
+    uint32_t group;            /* quantisation group: 128 (INT4) or 64 (polar) */
+    uint32_t symbols_per_step; /* 0 = choose; weights coded jointly per rANS step */
+    uint32_t precision_bits;   /* 0 = choose */
+    uint32_t target_tiles;     /* 0 = choose from the device's SM count */
+    const float *centroids;    /* polar only: 32 floats (host) */
+} eoq_b200_weight_opts_t;
+
+typedef struct {
+    uint32_t rows, cols, padded_rows, group, kind;
+    uint32_t symbols_per_step, precision_bits, alphabet;
+    uint32_t num_tiles, num_col_segments;
+    uint64_t stream_bytes;     /* entropy-coded tiles incl. initial states and padding */
+    uint64_t table_bytes, scale_bytes, desc_bytes;
+    uint64_t scratch_bytes;    /* per-call partial sums + counters (batch 8) */
+    double   bits_per_weight;  /* stream_bytes*8 / (rows*cols) */
+} eoq_b200_weight_info_t;
+
+/* The tiled layout on the host, before upload: lets a loader build it once,
+ * keep it (the arrays may be written to a cache file) and inspect it without a
+ * device.  Tile t: rows [row0, row0 + 32*G), columns [col0, col0 + ncols);
+ * its bytes start at stream + 64*off64: 32 x u32 initial states, then rows of
+ * 32 x u16 renormalisation words (lane l reads column l, top to bottom). */
+typedef struct eoq_b200_tiles eoq_b200_tiles_t;
+typedef struct { uint32_t row0, col0, ncols, seg, off64, rb; } eoq_b200_tile_desc_t;
+typedef struct {
+    uint32_t rows, cols, padded_rows, group, kind, bits;
+    uint32_t symbols_per_step, precision_bits;
+    uint32_t num_tiles, num_col_segments;
+    const uint32_t *table;               /* 1 << precision_bits entries: freq<<23 | sym<<(23-G*bits) | slot-cum */
+    const eoq_b200_tile_desc_t *tiles;
+    const uint8_t *stream;
+    uint64_t stream_bytes;
+} eoq_b200_tiles_view_t;
+eoq_error_t eoq_b200_tiles_build(const uint8_t *symbols, const eoq_b200_weight_opts_t *opts, eoq_b200_tiles_t **out);
+eoq_error_t eoq_b200_tiles_view(const eoq_b200_tiles_t *t, eoq_b200_tiles_view_t *view);
+void        eoq_b200_tiles_free(eoq_b200_tiles_t *t);
+
+/* Build from decoded symbols (host, one byte per weight, row-major N x K;
+ * INT4: code+7 in 0..14, polar: centroid index 0..31) and fp16 scales (host;
+ * flat N*K/group, as QuantizedLinear.scales / PolarQuantResult.norms). */
+eoq_error_t eoq_b200_weight_from_symbols(const uint8_t *symbols, const uint16_t *scales_fp16,
+                                         const eoq_b200_weight_opts_t *opts, eoq_b200_weight_t **out);
+
+/* Build from the reference's serialised `RANS` container
+ * (core/rans_blocked.py:176-214), i.e. what .eoq files and
+ * CompressedTensorData.rans_bytes hold: the wire-format blocks are decoded on
+ * the GPU and re-tiled once, at load time. */
+eoq_error_t eoq_b200_weight_from_rans(const uint8_t *rans_container, size_t size,
+                                      const uint16_t *scales_fp16, const eoq_b200_weight_opts_t *opts,
+                                      eoq_b200_weight_t **out);
+
+void        eoq_b200_weight_destroy(eoq_b200_weight_t *w);
+eoq_error_t eoq_b200_weight_info(const eoq_b200_weight_t *w, eoq_b200_weight_info_t *info);
+
+/* y[b, :] = W x[b, :] (+ bias), the fused replacement for
+ * QuantizedLinear.forward (core/quantized_linear.py:222-228) at batch 1..8:
+ * decode -> unpack -> scale -> dot product in one kernel; decoded symbols are
+ * never written to memory.  x is [batch, K], y is [batch, N], row-major, device
+ * pointers of the given element types; bias is fp32 [N] or NULL; accumulation
+ * is fp32.  Asynchronous on `stream`. */
+eoq_error_t eoq_b200_gemv(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch,
+                          void *y, int y_dtype, const float *bias, void *stream);
+
+/* Same with host buffers: copies x in, runs, copies y out, synchronises. */
+eoq_error_t eoq_b200_gemv_host(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch,
+                               void *y, int y_dtype, const float *bias_host, void *stream);
+
+/* Decode the tiles back to the reference's in-memory forms (device pointers,
+ * asynchronous): packed INT4 as QuantizedLinear.packed_weight
+ * (core/quantized_linear.py:76-91: uint8 [N, K/2], low nibble = even column),
+ * or one symbol per byte [N, K], and/or the dequantised matrix [N, K] in
+ * out_dtype (core/fast_dequant.py:47-87).  Either output may be NULL. */
+eoq_error_t eoq_b200_weight_decode(eoq_b200_weight_t *w, uint8_t *d_symbols_or_packed, int packed,
+                                   void *d_dequant, int out_dtype, void *stream);
+
+/* Dequantise QuantizedLinear's in-memory form on the GPU, any shape and any
+ * bit width the reference stores (2 and 4 packed, others one int8 per code):
+ * rows [row_lo, row_hi) of d_packed [rows, row_bytes] with scales indexed over
+ * the flattened matrix -> dense [row_hi-row_lo, cols] in out_dtype.  Behind
+ * core/fast_dequant.py:47-87, core/quantized_matmul.py:123-225 and
+ * QuantizedLinear._dequantize_weight (core/quantized_linear.py:189-217).
+ * Device pointers; asynchronous. */
+eoq_error_t eoq_b200_dequant_packed(const uint8_t *d_packed, const uint16_t *d_scales_fp16, uint32_t rows, uint32_t cols,
+                                    uint32_t bits, uint32_t group, uint32_t row_lo, uint32_t row_hi, void *d_out,
+                                    int out_dtype, void *stream);
+
+/* Number of kernels launched by this library since load (for benchmarks). */
+uint64_t eoq_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EOQ_B200_H */

@@ -368,3 +368,22 @@ class RefC:
         rc = self.v2.eoq_parallel_decode(tasks, n, C.byref(opts))
         dt = time.perf_counter() - t0
         return rc, [o[:int(h[6])] for o, (h, _) in zip(outs, items)], dt
+
+
+def decode_tiles(table: np.ndarray, p: int, g: int, bits: int, desc: np.ndarray, stream: np.ndarray,
+                 rows: int, cols: int) -> np.ndarray:
+    """Scalar decode of the product's tiled device layout -> uint8 [rows, cols] (orc_decode_tiles)."""
+    L = lib()
+    L.orc_decode_tiles.restype = C.c_int
+    L.orc_decode_tiles.argtypes = [C.POINTER(C.c_uint32), C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32),
+                                   C.c_uint32, C.POINTER(C.c_uint8), C.c_size_t, C.c_uint32, C.c_uint32,
+                                   C.POINTER(C.c_uint8)]
+    table = np.ascontiguousarray(table, np.uint32)
+    desc = np.ascontiguousarray(desc, np.uint32).reshape(-1, 6)
+    stream = np.ascontiguousarray(stream, np.uint8)
+    out = np.full((rows, cols), 255, np.uint8)
+    rc = L.orc_decode_tiles(_p(table, C.c_uint32), p, g, bits, _p(desc, C.c_uint32), desc.shape[0],
+                            _p(stream, C.c_uint8), stream.size, rows, cols, _p(out, C.c_uint8))
+    if rc != 0:
+        raise ValueError(f"orc_decode_tiles failed: {rc}")
+    return out
