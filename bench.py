@@ -1,0 +1,358 @@
+#!/usr/bin/env python3
+"""Benchmark of the EOQ hot path on B200: fused rANS-decode + INT4 dequantise + GEMV at batch 1.
+
+Workload (the one the headline metric is quoted on): a Llama-7B-shape MLP pair --
+an 11008 x 4096 weight times x ~ N(0,1) of length 4096, and the transposed 4096 x 11008
+down-projection times a vector of length 11008; weights N(0, 0.02), INT4 symmetric absmax,
+group 128, fp16 scales, entropy-coded; activations and outputs fp16.  A step is one pass
+over both products.  All data is synthetic and seeded.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+value   = algorithmic bytes per step / device time per step (CUDA events, max over ranks),
+          with every input already resident in HBM; "algorithmic bytes" are the bytes the
+          reference's own wire format needs for the same tensors (rANS blocks of 4096 symbols at
+          12-bit precision + block offsets + fp16 scales + x + y), not this library's tile bytes.
+e2e     = the same metric through the C ABI with HOST buffers (eoq_b200_gemv_host): x copied in
+          from pinned memory and y copied out inside the timed region, every step.
+N > 1   : each layer is sharded by output rows over the ranks (strong scaling); a step is the
+          two local products plus the NCCL all-gather of the output slices.
+--impl reference : the reference's CPU path for the same step -- eoq_parallel_decode
+          (compiled from the reference's C sources when available, else the C restatement)
+          followed by torch dequantise + F.linear -- on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_UP, K_UP = 11008, 4096          # gate/up projection
+N_DN, K_DN = 4096, 11008          # down projection
+GROUP = 128
+REPLICAS = 8                       # weight copies cycled through so that the working set exceeds L2
+WORKLOAD = "llama7b_mlp_pair_int4_g128_rans_b1"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the fused kernel, from the ncu capture
+# summarised under profiles/ (None until a capture has been taken)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def make_layer(n, k, seed):
+    """Seeded synthetic layer: symbols (uint8 code+7), fp16 scales."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(n, k, generator=g) * 0.02
+    blocks = w.view(-1, GROUP)
+    scale = (blocks.abs().amax(dim=1) / 7).clamp(min=1e-10)
+    codes = (blocks / scale[:, None]).round().clamp(-7, 7).to(torch.int8).view(n, k)
+    return (codes + 7).to(torch.uint8).numpy(), scale.half().numpy()
+
+
+def wire_bytes(sym, scales, n, k, batch=1):
+    """Bytes the reference's wire format needs for this tensor and one GEMV: stream + offsets + scales + x + y."""
+    from eoq_quantization_b200.core import rans_blocked as RB
+    data = RB.BlockedRANSEncoder(block_size=4096, precision_bits=12).encode(sym.ravel().astype(np.int64), 15)
+    return len(data.compressed_blocks) + 4 * data.num_blocks + scales.size * 2 + batch * (k + n) * 2, data
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle sampling during the timed region."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index, self.lines, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=lambda: [self.lines.append(l) for l in self.proc.stdout], daemon=True).start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in self.lines:
+            p = [s.strip() for s in l.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1])); mx.append(float(p[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, p[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measured_peak():
+    try:
+        d = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        return float(d["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------- CPU reference arm
+class CpuReference:
+    """The reference's CPU path for one step: eoq_parallel_decode over row-chunk tasks, then torch
+    dequantise ((sym - 7) * scale) and F.linear (core/quantized_linear.py:189-228)."""
+
+    def __init__(self, layers, rows_per_task=64):
+        import torch
+        from oracle import oracle as O
+        self.torch, self.O = torch, O
+        self.kind = "reference" if O.RefC.available() else "port"
+        self.ref = O.RefC() if self.kind == "reference" else None
+        self.cores = self.ref.threads() if self.ref else 1
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
+        self.layers = []
+        for sym, scales, n, k in layers:
+            items = []
+            for lo in range(0, n, rows_per_task):
+                chunk = sym[lo:lo + rows_per_task].ravel().astype(np.int64)
+                items.append(O.make_c_payload(O.encode_blocked(chunk, 15, 4096, 12)))
+            self.layers.append((items, torch.from_numpy(scales.astype(np.float32)), n, k))
+
+    def step(self, xs):
+        torch = self.torch
+        outs = []
+        for (items, scales, n, k), x in zip(self.layers, xs):
+            if self.ref:
+                rc, decoded, _ = self.ref.parallel_decode(items, 0)
+                assert rc == 0
+            else:
+                decoded = [self.O.decode_c_payload(h, b)[1] for h, b in items]
+            sym = torch.from_numpy(np.concatenate(decoded)).view(n, k)
+            w = ((sym.float() - 7.0).view(-1, GROUP) * scales[:, None]).view(n, k)
+            outs.append(torch.nn.functional.linear(x, w))
+        return outs
+
+
+def run_reference_arm(args):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    layers = [(*make_layer(N_UP, K_UP, 1), N_UP, K_UP), (*make_layer(N_DN, K_DN, 2), N_DN, K_DN)]
+    alg = sum(wire_bytes(s, sc, n, k)[0] for s, sc, n, k in layers)
+    cpu = CpuReference(layers)
+    xs = [torch.randn(1, K_UP), torch.randn(1, K_DN)]
+    for _ in range(args.warmup):
+        cpu.step(xs)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu.step(xs)
+    dt = (time.perf_counter() - t0) / args.steps
+    gbs = alg / dt / 1e9
+    sample = "whole step: both 11008x4096 and 4096x11008 layers, 64-row decode tasks, fp32 activations"
+    line = {"impl": "reference", "metric": "fused decode+INT4 GEMV effective HBM GB/s", "value": gbs, "unit": "GB/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u32 rANS state, fp32 accumulate",
+            "data": "synthetic", "config": {"workload": WORKLOAD, "batch": 1, "group": GROUP},
+            "tokens_per_s": 1.0 / dt,
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cpu.cores, "kind": cpu.kind, "sample": sample},
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- GPU arm
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    from eoq_quantization_b200 import _lib
+    from eoq_quantization_b200.fused import EOQWeight
+    from eoq_quantization_b200.tp import gather_rows, shard_rows
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product has no CPU path (use --impl reference for the CPU baseline)")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    lib = _lib.lib()
+
+    layers = [(*make_layer(N_UP, K_UP, 1), N_UP, K_UP), (*make_layer(N_DN, K_DN, 2), N_DN, K_DN)]
+    alg_bytes = [wire_bytes(s, sc, n, k)[0] for s, sc, n, k in layers]
+    alg_step = sum(alg_bytes)
+
+    # this rank's row shard of each layer, REPLICAS copies each
+    shards = []
+    for sym, scales, n, k in layers:
+        lo, hi = shard_rows(n, world, rank)
+        per_row = k // GROUP
+        shards.append(EOQWeight.replicas(REPLICAS, sym[lo:hi], scales[lo * per_row:hi * per_row]))
+    g = torch.Generator(device="cuda").manual_seed(1234)
+    xs = [torch.randn(1, K_UP, device="cuda", generator=g).half(), torch.randn(1, K_DN, device="cuda", generator=g).half()]
+
+    def step(i):
+        r = i % REPLICAS
+        outs = []
+        for li in range(2):
+            y = shards[li][r].gemv(xs[li])
+            if world > 1:
+                y = gather_rows(y)
+            outs.append(y)
+        return outs
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    launches0 = lib.eoq_b200_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        ev0.record()
+        for i in range(args.steps):
+            step(i)
+        ev1.record()
+        barrier()
+        # keep sampling for at least half a second of load so that the clock record is meaningful
+        t_end = time.time() + 0.6
+        i = 0
+        while time.time() < t_end:
+            step(i); i += 1
+        torch.cuda.synchronize()
+    launches = lib.eoq_b200_launch_count() - launches0
+    ms = ev0.elapsed_time(ev1) / args.steps
+    launches_timed = 2 * args.steps
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = alg_step / (ms * 1e-3) / 1e9
+
+    # per-kernel device time, for the roofline of the dominant kernel (the fused GEMV; the larger share is the
+    # 11008 x 4096 launch, the other launch is the same kernel on the transposed shape)
+    barrier()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for i in range(args.steps):
+        shards[0][i % REPLICAS].gemv(xs[0])
+    k1.record()
+    torch.cuda.synchronize()
+    up_ms = k0.elapsed_time(k1) / args.steps
+    peak, peak_src = measured_peak()
+    up_alg = alg_bytes[0] / world
+    roof = {"bound": "hbm", "kernel": "gemv_tiles_kernel<3,4,1,int4>", "achieved": up_alg / (up_ms * 1e-3) / 1e9, "peak": peak,
+            "unit": "GB/s", "frac": up_alg / (up_ms * 1e-3) / 1e9 / peak, "peak_source": peak_src,
+            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "launch_us": up_ms * 1e3, "algorithmic_bytes_per_launch": up_alg,
+            "fp16_gemv_bytes": N_UP * K_UP * 2 // world}
+
+    # end to end through the C ABI with host buffers (pinned x in, y out, every step)
+    hx = [torch.randn(1, K_UP).half().pin_memory(), torch.randn(1, K_DN).half().pin_memory()]
+    hy = [torch.empty(1, (N_UP // world)).half().pin_memory(), torch.empty(1, (N_DN // world)).half().pin_memory()]
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def e2e_step(i):
+        r = i % REPLICAS
+        for li in range(2):
+            _lib.check(lib.eoq_b200_gemv_host(shards[li][r]._h, hx[li].data_ptr(), _lib.F16, 1, hy[li].data_ptr(), _lib.F16,
+                                              None, stream), "eoq_b200_gemv_host")
+    for i in range(args.warmup):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(i)
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / args.steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e = {"value": alg_step / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": (K_UP + K_DN) * 2,
+           "d2h_bytes_per_step": (N_UP + N_DN) * 2 // world, "ms_per_step": e2e_s * 1e3,
+           "note": "per-rank output slices are read back; no gather on the host path" if world > 1 else ""}
+
+    if rank == 0:
+        cpu_line = None
+        if world == 1 and not args.no_cpu_baseline:
+            cpu = CpuReference(layers)
+            cx = [x.float().cpu() for x in xs]
+            outs = cpu.step(cx)                                   # also a last parity check of the timed kernels
+            got = step(0)
+            for a, b in zip(got, outs):
+                err = float((a.float().cpu() - b).norm() / b.norm())
+                assert err < 1e-3, f"bench parity check failed: rel-L2 {err}"
+            reps = 3
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                cpu.step(cx)
+            cdt = (time.perf_counter() - t0) / reps
+            cpu_line = {"value": alg_step / cdt / 1e9, "unit": "GB/s", "cores": cpu.cores, "kind": cpu.kind,
+                        "sample": f"whole step ({reps} repetitions): eoq_parallel_decode over 64-row tasks + torch dequantise + F.linear, fp32 activations",
+                        "ms_per_step": cdt * 1e3}
+        info = shards[0][0].info
+        line = {"metric": "fused decode+INT4 GEMV effective HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "u32 rANS state, fp32 accumulate, fp16 in/out",
+                "data": "synthetic",
+                "config": {"workload": WORKLOAD, "batch": 1, "group": GROUP, "shapes": [[N_UP, K_UP], [N_DN, K_DN]],
+                           "l2": f"{REPLICAS} weight copies cycled (working set {REPLICAS * sum(s[0].info.stream_bytes for s in shards) >> 20} MiB per rank > L2)",
+                           "parallelism": f"row-sharded tp{world}" + (" + NCCL all-gather per layer" if world > 1 else ""),
+                           "symbols_per_step": int(info.symbols_per_step), "precision_bits": int(info.precision_bits)},
+                "tokens_per_s": 1e3 / ms, "pct_of_hbm_peak": 100.0 * value / (peak * world),
+                "algorithmic_bytes_per_step": alg_step,
+                "tile_bytes_per_step": int(sum(s[0].info.stream_bytes + s[0].info.scale_bytes for s in shards)) * world,
+                "clocks": clocks.summary(), "roofline": roof, "e2e": e2e, "gpu_launches": int(launches_timed) * world,
+                "launches_counted_by_library": int(launches)}
+        if cpu_line:
+            line["cpu_baseline"] = cpu_line
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if args.steps > 20:
+            args.steps = 20
+        args.warmup = min(args.warmup, 3)
+        run_reference_arm(args)
+    else:
+        args.warmup = max(args.warmup, 3)
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -38,7 +38,7 @@ EXPORTS = [
     "eoq_cuda_batch_sync_and_free", "eoq_cuda_batch_destroy",
     "eoq_b200_decode_blocked", "eoq_b200_encode_blocked",
     "eoq_b200_tiles_build", "eoq_b200_tiles_view", "eoq_b200_tiles_free",
-    "eoq_b200_weight_from_symbols", "eoq_b200_weight_from_rans", "eoq_b200_weight_destroy",
+    "eoq_b200_weight_from_tiles", "eoq_b200_weight_from_symbols", "eoq_b200_weight_from_rans", "eoq_b200_weight_destroy",
     "eoq_b200_weight_info", "eoq_b200_gemv", "eoq_b200_gemv_host", "eoq_b200_weight_decode",
     "eoq_b200_dequant_packed",
     "eoq_b200_launch_count",
@@ -139,6 +139,7 @@ def lib() -> C.CDLL:
         "eoq_b200_tiles_build": (C.c_int, [vp, C.POINTER(WeightOpts), C.POINTER(vp)]),
         "eoq_b200_tiles_view": (C.c_int, [vp, C.POINTER(TilesView)]),
         "eoq_b200_tiles_free": (None, [vp]),
+        "eoq_b200_weight_from_tiles": (C.c_int, [vp, vp, vp, C.POINTER(vp)]),
         "eoq_b200_weight_from_symbols": (C.c_int, [vp, vp, C.POINTER(WeightOpts), C.POINTER(vp)]),
         "eoq_b200_weight_from_rans": (C.c_int, [vp, C.c_size_t, vp, C.POINTER(WeightOpts), C.POINTER(vp)]),
         "eoq_b200_weight_destroy": (None, [vp]),

@@ -604,6 +604,16 @@ extern "C" eoq_error_t eoq_b200_tiles_view(const eoq_b200_tiles_t *t, eoq_b200_t
 
 extern "C" void eoq_b200_tiles_free(eoq_b200_tiles_t *t) { delete t; }
 
+extern "C" eoq_error_t eoq_b200_weight_from_tiles(const eoq_b200_tiles_t *t, const uint16_t *scales_fp16, const float *centroids,
+                                                  eoq_b200_weight_t **out)
+{
+    if (!t || !scales_fp16 || !out) return EOQ_ERR_NULL_PTR;
+    *out = nullptr;
+    if (t->tw.kind == EOQ_B200_KIND_Q5_POLAR && !centroids) return EOQ_ERR_NULL_PTR;
+    if (!have_device()) return EOQ_ERR_CUDA;
+    return upload_weight(t->tw, scales_fp16, t->tw.kind == EOQ_B200_KIND_Q5_POLAR ? centroids : nullptr, out);
+}
+
 extern "C" eoq_error_t eoq_b200_weight_from_symbols(const uint8_t *symbols, const uint16_t *scales_fp16,
                                                     const eoq_b200_weight_opts_t *opts, eoq_b200_weight_t **out)
 {

@@ -77,6 +77,30 @@ class EOQWeight:
         return cls(h.value, kind)
 
     @classmethod
+    def replicas(cls, count: int, symbols, scales_fp16, *, kind: int = _lib.KIND_INT4_ABSMAX, group: int = 128,
+                 symbols_per_step: int = 0, precision_bits: int = 0, target_tiles: int = 0,
+                 centroids: Optional[Sequence[float]] = None) -> list:
+        """Encode once on the host, upload `count` independent copies to the current device."""
+        sym = np.ascontiguousarray(symbols.detach().cpu().numpy() if isinstance(symbols, torch.Tensor) else symbols,
+                                   dtype=np.uint8)
+        sc = scales_fp16.detach().cpu().numpy() if isinstance(scales_fp16, torch.Tensor) else np.asarray(scales_fp16)
+        sc = np.ascontiguousarray(sc.astype(np.float16, copy=False))
+        n, k = sym.shape
+        o, keep = cls._opts(kind, n, k, group, symbols_per_step, precision_bits, target_tiles, centroids)
+        L = _lib.lib()
+        tiles = C.c_void_p()
+        _lib.check(L.eoq_b200_tiles_build(sym.ctypes.data, C.byref(o), C.byref(tiles)), "eoq_b200_tiles_build")
+        out = []
+        try:
+            for _ in range(count):
+                h = C.c_void_p()
+                _lib.check(L.eoq_b200_weight_from_tiles(tiles, sc.ctypes.data, keep, C.byref(h)), "eoq_b200_weight_from_tiles")
+                out.append(cls(h.value, kind))
+        finally:
+            L.eoq_b200_tiles_free(tiles)
+        return out
+
+    @classmethod
     def from_int4_packed(cls, packed, scales_fp16, in_features: int, *, group: int = 128, **kw) -> "EOQWeight":
         """packed: QuantizedLinear.packed_weight, uint8 [N, K/2], low nibble = even column, value code+7."""
         pk = packed.detach().cpu().numpy() if isinstance(packed, torch.Tensor) else np.asarray(packed)

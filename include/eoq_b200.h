@@ -244,6 +244,11 @@ void        eoq_b200_tiles_free(eoq_b200_tiles_t *t);
 eoq_error_t eoq_b200_weight_from_symbols(const uint8_t *symbols, const uint16_t *scales_fp16,
                                          const eoq_b200_weight_opts_t *opts, eoq_b200_weight_t **out);
 
+/* Upload tiles built by eoq_b200_tiles_build to the current device (may be called
+ * repeatedly, e.g. once per GPU that holds a replica).  centroids: polar only. */
+eoq_error_t eoq_b200_weight_from_tiles(const eoq_b200_tiles_t *tiles, const uint16_t *scales_fp16,
+                                       const float *centroids, eoq_b200_weight_t **out);
+
 /* Build from the reference's serialised `RANS` container
  * (core/rans_blocked.py:176-214), i.e. what .eoq files and
  * CompressedTensorData.rans_bytes hold: the wire-format blocks are decoded on
