@@ -227,23 +227,56 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        step(i)
+    # Warm up eagerly, then capture the steps into CUDA graphs (REPLICAS steps per graph, plus single steps for the
+    # remainder) so that the timed region measures the device, not the Python launch path.
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(max(args.warmup, REPLICAS)):
+            step(i)
+    torch.cuda.current_stream().wait_stream(side)
+    barrier()
+    launch_mode = "cuda-graph"
+    try:
+        g_full = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_full):
+            for i in range(REPLICAS):
+                step(i)
+        g_one = []
+        for r in range(args.steps % REPLICAS):
+            g1 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g1):
+                step(r)
+            g_one.append(g1)
+    except Exception as exc:                                     # pragma: no cover - depends on the driver stack
+        launch_mode = f"eager ({type(exc).__name__})"
+        g_full, g_one = None, []
+
+    def run_steps(nsteps):
+        if g_full is None:
+            for i in range(nsteps):
+                step(i)
+            return
+        for _ in range(nsteps // REPLICAS):
+            g_full.replay()
+        for g1 in g_one[:nsteps % REPLICAS]:
+            g1.replay()
+
+    for _ in range(3):
+        run_steps(args.steps)
     barrier()
     launches0 = lib.eoq_b200_launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
         barrier()
         ev0.record()
-        for i in range(args.steps):
-            step(i)
+        run_steps(args.steps)
         ev1.record()
         barrier()
-        # keep sampling for at least half a second of load so that the clock record is meaningful
+        # keep the same load running for at least half a second so that the clock record is meaningful
         t_end = time.time() + 0.6
-        i = 0
         while time.time() < t_end:
-            step(i); i += 1
+            run_steps(args.steps)
         torch.cuda.synchronize()
     launches = lib.eoq_b200_launch_count() - launches0
     ms = ev0.elapsed_time(ev1) / args.steps
@@ -258,12 +291,31 @@ def run_gpu_arm(args):
     # 11008 x 4096 launch, the other launch is the same kernel on the transposed shape)
     barrier()
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    y_up = torch.empty(1, N_UP // world, device="cuda", dtype=torch.float16)
+    cur = torch.cuda.current_stream().cuda_stream
+
+    def up_only():
+        for r in range(REPLICAS):
+            _lib.check(lib.eoq_b200_gemv(shards[0][r]._h, xs[0].data_ptr(), _lib.F16, 1, y_up.data_ptr(), _lib.F16, None,
+                                         torch.cuda.current_stream().cuda_stream), "eoq_b200_gemv")
+    g_up = None
+    if g_full is not None:
+        try:
+            g_up = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_up):
+                up_only()
+        except Exception:
+            g_up = None
+    reps = max(1, args.steps // REPLICAS)
+    for _ in range(2):
+        g_up.replay() if g_up is not None else up_only()
+    torch.cuda.synchronize()
     k0.record()
-    for i in range(args.steps):
-        shards[0][i % REPLICAS].gemv(xs[0])
+    for _ in range(reps):
+        g_up.replay() if g_up is not None else up_only()
     k1.record()
     torch.cuda.synchronize()
-    up_ms = k0.elapsed_time(k1) / args.steps
+    up_ms = k0.elapsed_time(k1) / (reps * REPLICAS)
     peak, peak_src = measured_peak()
     up_alg = alg_bytes[0] / world
     roof = {"bound": "hbm", "kernel": "gemv_tiles_kernel<3,4,1,int4>", "achieved": up_alg / (up_ms * 1e-3) / 1e9, "peak": peak,
@@ -323,7 +375,7 @@ def run_gpu_arm(args):
                 "config": {"workload": WORKLOAD, "batch": 1, "group": GROUP, "shapes": [[N_UP, K_UP], [N_DN, K_DN]],
                            "l2": f"{REPLICAS} weight copies cycled (working set {REPLICAS * sum(s[0].info.stream_bytes for s in shards) >> 20} MiB per rank > L2)",
                            "parallelism": f"row-sharded tp{world}" + (" + NCCL all-gather per layer" if world > 1 else ""),
-                           "symbols_per_step": int(info.symbols_per_step), "precision_bits": int(info.precision_bits)},
+                           "launch": launch_mode, "symbols_per_step": int(info.symbols_per_step), "precision_bits": int(info.precision_bits)},
                 "tokens_per_s": 1e3 / ms, "pct_of_hbm_peak": 100.0 * value / (peak * world),
                 "algorithmic_bytes_per_step": alg_step,
                 "tile_bytes_per_step": int(sum(s[0].info.stream_bytes + s[0].info.scale_bytes for s in shards)) * world,

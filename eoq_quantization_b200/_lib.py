@@ -41,7 +41,7 @@ EXPORTS = [
     "eoq_b200_weight_from_tiles", "eoq_b200_weight_from_symbols", "eoq_b200_weight_from_rans", "eoq_b200_weight_destroy",
     "eoq_b200_weight_info", "eoq_b200_gemv", "eoq_b200_gemv_host", "eoq_b200_weight_decode",
     "eoq_b200_dequant_packed",
-    "eoq_b200_launch_count",
+    "eoq_b200_weight_status", "eoq_b200_tune", "eoq_b200_launch_count",
 ]
 
 
@@ -149,6 +149,8 @@ def lib() -> C.CDLL:
         "eoq_b200_weight_decode": (C.c_int, [vp, vp, C.c_int, vp, C.c_int, vp]),
         "eoq_b200_dequant_packed": (C.c_int, [vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                               C.c_uint32, vp, C.c_int, vp]),
+        "eoq_b200_weight_status": (C.c_int, [vp, vp]),
+        "eoq_b200_tune": (C.c_int, [C.c_char_p, C.c_int]),
         "eoq_b200_launch_count": (C.c_uint64, []),
     }
     for name, (res, args) in sig.items():

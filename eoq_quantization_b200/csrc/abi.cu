@@ -516,7 +516,7 @@ struct eoq_b200_weight {
     int device = 0;
     uint32_t N = 0, K = 0, Npad = 0, G = 0, bits = 0, p = 0, group = 0, kind = 0, alphabet = 0;
     uint32_t ntiles = 0, nseg = 0, nrb = 0;
-    DeviceBuf table, tiles, stream, scales, centroids, partials, counters, xbuf, ybuf, biasbuf;
+    DeviceBuf table, tiles, stream, scales, centroids, partials, counters, status, xbuf, ybuf, biasbuf;
     size_t stream_bytes = 0, scale_bytes = 0, partial_bytes = 0;
     std::mutex mu;   // one call at a time may use the scratch of a weight
 };
@@ -548,6 +548,7 @@ eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const 
     if (w->table.alloc(tw.table.size() * 4) != cudaSuccess || w->tiles.alloc(tw.tiles.size() * sizeof(TileDesc)) != cudaSuccess ||
         w->stream.alloc(tw.stream.size()) != cudaSuccess || w->scales.alloc(w->scale_bytes) != cudaSuccess ||
         w->partials.alloc(w->partial_bytes) != cudaSuccess || w->counters.alloc((size_t)tw.nrb * 4) != cudaSuccess ||
+        w->status.alloc(4) != cudaSuccess ||
         w->xbuf.alloc((size_t)8 * tw.K * 4) != cudaSuccess || w->ybuf.alloc((size_t)8 * tw.N * 4) != cudaSuccess ||
         w->biasbuf.alloc((size_t)tw.N * 4) != cudaSuccess)
         return EOQ_ERR_ALLOC;
@@ -560,6 +561,7 @@ eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const 
     CU_TRY(cudaMemcpy(w->stream.p, tw.stream.data(), tw.stream.size(), cudaMemcpyHostToDevice));
     CU_TRY(cudaMemcpy(w->scales.p, scales, w->scale_bytes, cudaMemcpyHostToDevice));
     CU_TRY(cudaMemset(w->counters.p, 0, (size_t)tw.nrb * 4));
+    CU_TRY(cudaMemset(w->status.p, 0, 4));
     *out = w.release();
     return EOQ_OK;
 }
@@ -684,11 +686,20 @@ extern "C" eoq_error_t eoq_b200_gemv(eoq_b200_weight_t *w, const void *x, int x_
     if (batch > 8) return EOQ_ERR_UNSUPPORTED;
     if (x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2) return EOQ_ERR_UNSUPPORTED;
     const uint32_t bt = batch <= 1 ? 1 : batch <= 2 ? 2 : batch <= 4 ? 4 : 8;
-    if (gemv_smem_bytes(w->K, w->p, bt, w->kind) > 227 * 1024) return EOQ_ERR_UNSUPPORTED;
+    if (gemv_smem_bytes(w->K, w->p, bt, w->kind) > 227 * 1024) {
+        // x for this many rows does not fit shared memory beside the table: run the rows in two halves
+        if (bt == 1) return EOQ_ERR_UNSUPPORTED;
+        static const size_t esz[3] = {2, 2, 4};
+        const uint32_t half = bt / 2, first = std::min(batch, half);
+        eoq_error_t rc = eoq_b200_gemv(w, x, x_dtype, first, y, y_dtype, bias, stream);
+        if (rc != EOQ_OK || batch <= half) return rc;
+        return eoq_b200_gemv(w, static_cast<const uint8_t *>(x) + (size_t)first * w->K * esz[x_dtype], x_dtype, batch - first,
+                             static_cast<uint8_t *>(y) + (size_t)first * w->N * esz[y_dtype], y_dtype, bias, stream);
+    }
     GemvArgs a;
     a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
     a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
-    a.x = x; a.y = y; a.bias = bias; a.partials = w->partials.as<float>(); a.counters = w->counters.as<uint32_t>();
+    a.x = x; a.y = y; a.bias = bias; a.partials = w->partials.as<float>(); a.counters = w->counters.as<uint32_t>(); a.status = w->status.as<uint32_t>();
     a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
     a.x_dtype = x_dtype; a.y_dtype = y_dtype;
     int e = launch_gemv(a, w->G, w->bits, w->kind, stream);
@@ -710,8 +721,10 @@ extern "C" eoq_error_t eoq_b200_gemv_host(eoq_b200_weight_t *w, const void *x, i
     eoq_error_t rc = eoq_b200_gemv(w, w->xbuf.p, x_dtype, batch, w->ybuf.p, y_dtype, bias_host ? w->biasbuf.as<float>() : nullptr, stream);
     if (rc != EOQ_OK) return rc;
     CU_TRY(cudaMemcpyAsync(y, w->ybuf.p, (size_t)batch * w->N * esz[y_dtype], cudaMemcpyDeviceToHost, st));
+    uint32_t status = 0;
+    CU_TRY(cudaMemcpyAsync(&status, w->status.p, 4, cudaMemcpyDeviceToHost, st));
     CU_TRY(cudaStreamSynchronize(st));
-    return EOQ_OK;
+    return status ? EOQ_ERR_CUDA : EOQ_OK;
 }
 
 extern "C" eoq_error_t eoq_b200_weight_decode(eoq_b200_weight_t *w, uint8_t *d_sym, int packed, void *d_dequant, int out_dtype, void *stream)
@@ -724,6 +737,7 @@ extern "C" eoq_error_t eoq_b200_weight_decode(eoq_b200_weight_t *w, uint8_t *d_s
     DecodeArgs a;
     a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
     a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
+    a.status = w->status.as<uint32_t>();
     a.out_sym = d_sym; a.out_deq = d_dequant; a.N = w->N; a.K = w->K; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles;
     a.packed = packed; a.out_dtype = out_dtype;
     int e = launch_decode_tiles(a, w->G, w->bits, w->kind, stream);
@@ -745,6 +759,23 @@ extern "C" eoq_error_t eoq_b200_dequant_packed(const uint8_t *d_packed, const ui
     int e = launch_dequant_packed(d_packed, d_scales_fp16, cols, row_bytes, bits, group, row_lo, row_hi, d_out, out_dtype, stream);
     if (e != 0) { std::fprintf(stderr, "eoq_b200_dequant_packed: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
     return EOQ_OK;
+}
+
+extern "C" eoq_error_t eoq_b200_weight_status(eoq_b200_weight_t *w, void *stream)
+{
+    if (!w) return EOQ_ERR_NULL_PTR;
+    uint32_t status = 0;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    CU_TRY(cudaMemcpyAsync(&status, w->status.p, 4, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    return status ? EOQ_ERR_CUDA : EOQ_OK;
+}
+
+extern "C" int eoq_b200_tune(const char *key, int value)
+{
+    if (!key) return -1;
+    if (std::strcmp(key, "gemv_ctas_per_sm") == 0) { set_gemv_ctas_per_sm(value); return 0; }
+    return -1;
 }
 
 extern "C" uint64_t eoq_b200_launch_count(void) { return launch_counter(); }

@@ -35,12 +35,14 @@ struct TileDesc {
     uint32_t row0;    // first row of the tile (multiple of 32*G)
     uint32_t col0;    // first column
     uint32_t ncols;   // columns (= rANS steps per lane), multiple of 16
-    uint32_t seg;     // column-segment index (same for all row blocks)
+    uint32_t seg;     // column-segment index (same for all row blocks); top bit: kTileDirectFlag
     uint32_t off64;   // byte offset of the tile in the stream, divided by 64
-    uint32_t rb;      // row-block index
+    uint32_t len64;   // bytes of the tile, divided by 64
 };
 
 constexpr uint32_t kMaxFreq = 511;
+constexpr uint32_t kMaxRingDrift = 43;           // rows the lanes of a ring-mode tile may be apart at any step
+constexpr uint32_t kTileDirectFlag = 0x80000000u; // set in TileDesc::seg when the tile breaks that bound
 constexpr uint32_t kColGranule = 16;   // tile column boundaries are multiples of this
 
 struct TiledWeights {
@@ -50,7 +52,7 @@ struct TiledWeights {
     std::vector<uint32_t> table;     // 1 << p entries
     std::vector<TileDesc> tiles;     // nrb * nseg
     std::vector<uint32_t> seg_start; // nseg + 1 column boundaries
-    std::vector<uint8_t>  stream;    // all tiles + 256 bytes of tail padding
+    std::vector<uint8_t>  stream;    // all tiles + 4096 bytes of tail padding (read-ahead never leaves it)
 };
 
 // Host codec (rans_host.cpp) -------------------------------------------------
@@ -87,6 +89,7 @@ struct GemvArgs {
     const float    *bias;       // [N] or null
     float          *partials;   // [nseg][Npad][BT]
     uint32_t       *counters;   // [nrb], zero on entry, zero on exit
+    uint32_t       *status;     // one word, set nonzero if a bounded wait expired
     uint32_t N, K, Npad, group, p, ntiles, nseg, batch;
     int x_dtype, y_dtype;
 };
@@ -97,6 +100,7 @@ struct DecodeArgs {
     const uint8_t  *stream;
     const uint16_t *scales;
     const float    *centroids;  // unused for INT4
+    uint32_t       *status;
     uint8_t        *out_sym;    // packed nibbles [N, K/2] or bytes [N, K], or null
     void           *out_deq;    // [N, K] or null
     uint32_t N, K, group, p, ntiles;
@@ -120,5 +124,6 @@ int launch_dequant_packed(const uint8_t *packed, const uint16_t *scales, uint32_
                           uint32_t group, uint32_t row_lo, uint32_t row_hi, void *out, int out_dtype, void *stream);
 size_t gemv_smem_bytes(uint32_t K, uint32_t p, uint32_t bt, uint32_t kind);
 uint64_t launch_counter();
+void set_gemv_ctas_per_sm(int v);
 
 }  // namespace eoq

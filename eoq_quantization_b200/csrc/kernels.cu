@@ -13,6 +13,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <mutex>
 
 namespace eoq {
 
@@ -85,13 +86,20 @@ __device__ __forceinline__ void store_y(void *p, size_t i, float v, int dtype)
 
 __device__ __forceinline__ float half_bits_to_float(uint16_t h) { return __half2float(__ushort_as_half(h)); }
 
+// Geometry of the per-warp word ring (see "Streaming a tile's renormalisation words" below).
+constexpr uint32_t kRingRows = 64, kChunkRows = 16, kRingChunks = kRingRows / kChunkRows, kSyncSteps = 4;
+constexpr uint32_t kRingBytes = kRingRows * 64, kChunkBytes = kChunkRows * 64;
+static_assert(kMaxRingDrift + kSyncSteps + 1 + kChunkRows <= kRingRows, "ring too small for the drift bound");
+
+__host__ __device__ inline size_t ring_smem_bytes(uint32_t warps) { return (size_t)warps * (kRingBytes + kRingChunks * 8) + kRingBytes; }
+
 // Shared-memory carve-up of the fused kernel (bytes).
 __host__ __device__ inline size_t smem_table_bytes(uint32_t p) { return (size_t)4 << p; }
 size_t gemv_smem_bytes(uint32_t K, uint32_t p, uint32_t bt, uint32_t kind)
 {
     size_t b = smem_table_bytes(p) + (size_t)K * bt * 4;
     b += kind == EOQ_B200_KIND_Q5_POLAR ? 32 * 32 * 4 : (size_t)(K / 16) * bt * 4;
-    return b;
+    return b + ring_smem_bytes(kWarps);
 }
 
 // One rANS step: table lookup, state update; returns the entry.
@@ -102,14 +110,142 @@ __device__ __forceinline__ uint32_t rans_step(const uint32_t *tab, uint32_t &x, 
     return e;
 }
 
-// Renormalise from the lane's private word column (one 16-bit word at most,
-// since p <= 16).  `w` always holds the lane's next unread word.
-__device__ __forceinline__ void rans_renorm(uint32_t &x, uint32_t &w, const uint16_t *&ptr)
+// ---------------------------------------------------------------------------
+// Streaming a tile's renormalisation words.
+//
+// Ring mode (the normal case): each warp owns a 4 KB ring in shared memory (64 rows of
+// 32 x u16) filled by bulk asynchronous copies (cp.async.bulk, the 1-D TMA path) of 1 KB
+// chunks, each completing on its own mbarrier.  Lane l reads column l; `koff` is 64 x the row
+// of the word the lane currently holds in `w`, counted from the warp's first chunk so that
+// ring position = koff mod 4096 across tiles.  Every kSyncSteps steps the warp takes the min and
+// max of koff over its lanes: chunks wholly below the min are refilled, and the chunk the
+// fastest lane can reach before the next check is waited for.  The host encoder guarantees that
+// lanes of a ring-mode tile never drift more than kMaxRingDrift rows apart, which is what makes
+// four chunks enough; tiles that break the bound are flagged and read their words straight from
+// global memory instead (direct mode).  Waits are bounded: on expiry a status word is set and
+// the kernel carries on with whatever the ring holds, so it always terminates.
+// ---------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory"); }
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t *status)
+{
+    for (uint32_t i = 0; i < (1u << 22); i++)
+        if (mbar_test(bar, parity)) return;
+    *status = 1u;   // gave up; the host turns this into an error
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr)
+{
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+struct WordState {            // per lane
+    uint32_t w;               // the lane's next unread word
+    const uint16_t *ptr;      // direct mode: where w came from
+    uint32_t koff, ring_lane; // ring mode: see above; ring_lane = shared address of the ring | lane*2
+};
+
+struct RingCtl {              // per warp (all fields warp-uniform)
+    uint32_t ring_base, bar0; // shared addresses
+    uint32_t issued, ready;   // chunks issued / known complete since the kernel started
+    uint32_t tile_first, nchunks, row_bytes;
+    const uint8_t *src;       // global address of the tile's first word row
+    uint32_t *status;
+};
+
+__device__ __forceinline__ void ring_setup(RingCtl &r, uint8_t *ring_area, uint32_t warp, uint32_t nwarps, uint32_t lane, uint32_t *status)
+{
+    const uint32_t base = (smem_addr(ring_area) + kRingBytes - 1) & ~(kRingBytes - 1);
+    r.ring_base = base + warp * kRingBytes;
+    r.bar0 = base + nwarps * kRingBytes + warp * kRingChunks * 8;
+    r.issued = r.ready = 0;
+    r.status = status;
+    if (lane == 0) {
+#pragma unroll
+        for (uint32_t i = 0; i < kRingChunks; i++) mbar_init(r.bar0 + i * 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+}
+
+__device__ __forceinline__ void ring_sync(RingCtl &r, const WordState &s, uint32_t lane)
+{
+    const uint32_t first_row = r.tile_first * kChunkRows;
+    const uint32_t kmin = (__reduce_min_sync(0xffffffffu, s.koff) >> 6) - first_row;
+    const uint32_t kmax = (__reduce_max_sync(0xffffffffu, s.koff) >> 6) - first_row;
+    const uint32_t limit = r.tile_first + min(r.nchunks, kmin / kChunkRows + kRingChunks);
+    while (r.issued < limit) {
+        if (lane == 0) {
+            const uint32_t c = r.issued - r.tile_first, slot = r.issued % kRingChunks;
+            const uint32_t bytes = min(kChunkBytes, r.row_bytes - c * kChunkBytes);
+            mbar_expect_tx(r.bar0 + slot * 8, bytes);
+            bulk_copy_g2s(r.ring_base + slot * kChunkBytes, r.src + (size_t)c * kChunkBytes, bytes, r.bar0 + slot * 8);
+        }
+        r.issued++;
+    }
+    const uint32_t need = min(r.issued, r.tile_first + min(r.nchunks, (kmax + kSyncSteps + 1) / kChunkRows + 1));
+    while (r.ready < need) {
+        mbar_wait_bounded(r.bar0 + (r.ready % kRingChunks) * 8, (r.ready / kRingChunks) & 1u, r.status);
+        r.ready++;
+    }
+}
+
+// Start of a tile.  Returns true if the tile runs in ring mode.
+__device__ __forceinline__ bool tile_begin(RingCtl &r, WordState &s, const TileDesc &d, const uint8_t *base, uint32_t lane, uint32_t &x)
+{
+    if (lane == 0) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base), "r"(d.len64 << 6) : "memory");
+    x = __ldg(reinterpret_cast<const uint32_t *>(base) + lane);
+    const bool ring = (d.seg & kTileDirectFlag) == 0;
+    if (ring) {
+        r.tile_first = r.issued;
+        r.row_bytes = (d.len64 << 6) - 128;
+        r.nchunks = (r.row_bytes + kChunkBytes - 1) / kChunkBytes;
+        r.src = base + 128;
+        s.koff = r.tile_first * kChunkBytes;
+        s.ring_lane = r.ring_base | (lane * 2);
+        ring_sync(r, s, lane);
+        s.w = lds_u16((s.koff & (kRingBytes - 1)) | s.ring_lane);
+    } else {
+        s.ptr = reinterpret_cast<const uint16_t *>(base + 128) + lane;
+        s.w = __ldg(s.ptr);
+    }
+    return ring;
+}
+
+__device__ __forceinline__ void tile_end(RingCtl &r, bool ring)
+{
+    if (!ring) return;
+    while (r.ready < r.issued) {       // nothing of this tile may still be in flight when the next one starts
+        mbar_wait_bounded(r.bar0 + (r.ready % kRingChunks) * 8, (r.ready / kRingChunks) & 1u, r.status);
+        r.ready++;
+    }
+}
+
+// Renormalise: at most one 16-bit word per step, since p <= 16.
+template <bool RING>
+__device__ __forceinline__ void rans_renorm(uint32_t &x, WordState &s)
 {
     if (x < 65536u) {
-        x = (x << 16) | w;
-        ptr += 32;
-        w = __ldg(ptr);
+        x = (x << 16) | s.w;
+        if (RING) {
+            s.koff += 64;
+            s.w = lds_u16((s.koff & (kRingBytes - 1)) | s.ring_lane);
+        } else {
+            s.ptr += 32;
+            s.w = __ldg(s.ptr);
+        }
     }
 }
 
@@ -126,68 +262,13 @@ __device__ __forceinline__ void rans_renorm(uint32_t &x, uint32_t &w, const uint
 // arrive (a ticket on `counters`) adds them up in segment order, so results do
 // not depend on scheduling.
 // ---------------------------------------------------------------------------
-template <int G, int BITS, int BT, int KIND>
-__global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs a)
+// The column loop of one tile: decode, unpack, multiply-accumulate, fold per scale group.
+template <int G, int BITS, int BT, int KIND, bool RING>
+__device__ __forceinline__ void gemv_tile_columns(const GemvArgs &a, const TileDesc &d, const uint32_t *tab, const float *xs,
+                                                  const float *aux, uint32_t lane, uint32_t row, uint32_t mask, uint32_t p,
+                                                  uint32_t sgroups, uint32_t &x, WordState &ws, RingCtl &ring, float (&y)[G][BT])
 {
     using F = Fmt<G, BITS>;
-    extern __shared__ __align__(16) uint8_t smem[];
-    uint32_t *tab = reinterpret_cast<uint32_t *>(smem);
-    float *xs = reinterpret_cast<float *>(smem + smem_table_bytes(a.p));
-    float *aux = xs + (size_t)a.K * BT;   // INT4: [K/16][BT] sums; polar: [32][32] centroids
-
-    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t K = a.K, M = 1u << a.p;
-
-    for (uint32_t i = tid * 4; i < M; i += kThreads * 4)
-        *reinterpret_cast<uint4 *>(tab + i) = __ldg(reinterpret_cast<const uint4 *>(a.table + i));
-    for (uint32_t i = tid; i < K * BT; i += kThreads) {
-        const uint32_t c = i / BT, b = i % BT;
-        xs[i] = b < a.batch ? load_x(a.x, (size_t)b * K + c, a.x_dtype) : 0.0f;
-    }
-    if (KIND == EOQ_B200_KIND_Q5_POLAR)
-        for (uint32_t i = tid; i < 32 * 32; i += kThreads) aux[i] = __ldg(a.centroids + (i >> 5));
-    __syncthreads();
-    if (KIND == EOQ_B200_KIND_Q5_POLAR) {
-        // x'' = H64 x / 64 per 64-column block (unnormalised Sylvester butterflies), so that
-        // W_block . x_block = norm * sum_j centroid[code_j] * x''_j   (core/polar_quant.py:242-262)
-        for (uint32_t h = 1; h < 64; h <<= 1) {
-            for (uint32_t q = tid; q < K / 2 * BT; q += kThreads) {
-                const uint32_t b = q % BT, pr = q / BT;
-                const uint32_t c = 2 * (pr - (pr % h)) + (pr % h);
-                const float u = xs[c * BT + b], v = xs[(c + h) * BT + b];
-                const float s = h == 32 ? 1.0f / 64.0f : 1.0f;
-                xs[c * BT + b] = (u + v) * s;
-                xs[(c + h) * BT + b] = (u - v) * s;
-            }
-            __syncthreads();
-        }
-    } else {
-        for (uint32_t i = tid; i < K / 16 * BT; i += kThreads) {
-            const uint32_t u = i / BT, b = i % BT;
-            float s = 0.0f;
-#pragma unroll
-            for (int k = 0; k < 16; k++) s += xs[(u * 16 + k) * BT + b];
-            aux[i] = s;
-        }
-        __syncthreads();
-    }
-
-    const uint32_t mask = M - 1u, p = a.p;
-    const uint32_t sgroups = K / a.group;
-    for (uint32_t t = blockIdx.x + gridDim.x * warp; t < a.ntiles; t += gridDim.x * kWarps) {
-        const TileDesc d = a.tiles[t];
-        const uint8_t *base = a.stream + ((size_t)d.off64 << 6);
-        uint32_t x = __ldg(reinterpret_cast<const uint32_t *>(base) + lane);
-        const uint16_t *ptr = reinterpret_cast<const uint16_t *>(base + 128) + lane;
-        uint32_t w = __ldg(ptr);
-        const uint32_t row = d.row0 + lane * G;
-
-        float y[G][BT];
-#pragma unroll
-        for (int j = 0; j < G; j++)
-#pragma unroll
-            for (int b = 0; b < BT; b++) y[j][b] = 0.0f;
-
         uint32_t c = d.col0;
         const uint32_t cend = c + d.ncols;
         while (c < cend) {
@@ -205,6 +286,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs 
 
 #pragma unroll 2
             for (; c < rend; c += 4) {
+                if (RING) ring_sync(ring, ws, lane);
                 float xv[4][BT];
                 if (BT == 1) {
                     const float4 v = *reinterpret_cast<const float4 *>(xs + c);
@@ -251,7 +333,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs 
                             for (int b = 0; b < BT; b++) acc[j][b] = fmaf(m, xv[s][b], acc[j][b]);
                         }
                     }
-                    rans_renorm(x, w, ptr);
+                    rans_renorm<RING>(x, ws);
                 }
             }
 
@@ -277,8 +359,81 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs 
             }
         }
 
+}
+
+template <int G, int BITS, int BT, int KIND>
+__global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs a)
+{
+    using F = Fmt<G, BITS>;
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint32_t *tab = reinterpret_cast<uint32_t *>(smem);
+    float *xs = reinterpret_cast<float *>(smem + smem_table_bytes(a.p));
+    float *aux = xs + (size_t)a.K * BT;   // INT4: [K/16][BT] sums; polar: [32][32] centroids
+    uint8_t *ring_area = reinterpret_cast<uint8_t *>(aux + (KIND == EOQ_B200_KIND_Q5_POLAR ? 32 * 32 : (size_t)(a.K / 16) * BT));
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t K = a.K, M = 1u << a.p;
+    RingCtl ring;
+    ring_setup(ring, ring_area, warp, kWarps, lane, a.status);
+
+    for (uint32_t i = tid * 4; i < M; i += kThreads * 4)
+        *reinterpret_cast<uint4 *>(tab + i) = __ldg(reinterpret_cast<const uint4 *>(a.table + i));
+    for (uint32_t i = tid; i < K * BT; i += kThreads) {
+        const uint32_t c = i / BT, b = i % BT;
+        xs[i] = b < a.batch ? load_x(a.x, (size_t)b * K + c, a.x_dtype) : 0.0f;
+    }
+    if (KIND == EOQ_B200_KIND_Q5_POLAR)
+        for (uint32_t i = tid; i < 32 * 32; i += kThreads) aux[i] = __ldg(a.centroids + (i >> 5));
+    __syncthreads();
+    if (KIND == EOQ_B200_KIND_Q5_POLAR) {
+        // x'' = H64 x / 64 per 64-column block (unnormalised Sylvester butterflies), so that
+        // W_block . x_block = norm * sum_j centroid[code_j] * x''_j   (core/polar_quant.py:242-262)
+        for (uint32_t h = 1; h < 64; h <<= 1) {
+            for (uint32_t q = tid; q < K / 2 * BT; q += kThreads) {
+                const uint32_t b = q % BT, pr = q / BT;
+                const uint32_t c = 2 * (pr - (pr % h)) + (pr % h);
+                const float u = xs[c * BT + b], v = xs[(c + h) * BT + b];
+                const float s = h == 32 ? 1.0f / 64.0f : 1.0f;
+                xs[c * BT + b] = (u + v) * s;
+                xs[(c + h) * BT + b] = (u - v) * s;
+            }
+            __syncthreads();
+        }
+    } else {
+        for (uint32_t i = tid; i < K / 16 * BT; i += kThreads) {
+            const uint32_t u = i / BT, b = i % BT;
+            float s = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 16; k++) s += xs[(u * 16 + k) * BT + b];
+            aux[i] = s;
+        }
+        __syncthreads();
+    }
+
+    const uint32_t mask = M - 1u, p = a.p;
+    const uint32_t sgroups = K / a.group;
+    for (uint32_t t = blockIdx.x + gridDim.x * warp; t < a.ntiles; t += gridDim.x * kWarps) {
+        const TileDesc d = a.tiles[t];
+        const uint8_t *base = a.stream + ((size_t)d.off64 << 6);
+        uint32_t x;
+        WordState ws;
+        const bool ring_mode = tile_begin(ring, ws, d, base, lane, x);
+        const uint32_t row = d.row0 + lane * G;
+        const uint32_t rb = d.row0 / (32u * G);
+        const uint32_t seg = d.seg & ~kTileDirectFlag;
+
+        float y[G][BT];
+#pragma unroll
+        for (int j = 0; j < G; j++)
+#pragma unroll
+            for (int b = 0; b < BT; b++) y[j][b] = 0.0f;
+
+        if (ring_mode) gemv_tile_columns<G, BITS, BT, KIND, true>(a, d, tab, xs, aux, lane, row, mask, p, sgroups, x, ws, ring, y);
+        else gemv_tile_columns<G, BITS, BT, KIND, false>(a, d, tab, xs, aux, lane, row, mask, p, sgroups, x, ws, ring, y);
+        tile_end(ring, ring_mode);
+
         if (a.nseg > 1) {
-            float *mine = a.partials + ((size_t)d.seg * a.Npad + row) * BT;
+            float *mine = a.partials + ((size_t)seg * a.Npad + row) * BT;
 #pragma unroll
             for (int j = 0; j < G; j++)
 #pragma unroll
@@ -286,7 +441,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs 
             __threadfence();
             __syncwarp();
             uint32_t ticket = 0;
-            if (lane == 0) ticket = atomicAdd(a.counters + d.rb, 1u);
+            if (lane == 0) ticket = atomicAdd(a.counters + rb, 1u);
             ticket = __shfl_sync(0xffffffffu, ticket, 0);
             if (ticket != a.nseg - 1) continue;
             __threadfence();
@@ -301,7 +456,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs 
 #pragma unroll
                     for (int b = 0; b < BT; b++) y[j][b] += __ldcg(src + j * BT + b);
             }
-            if (lane == 0) a.counters[d.rb] = 0u;
+            if (lane == 0) a.counters[rb] = 0u;
         }
 #pragma unroll
         for (int j = 0; j < G; j++) {
@@ -316,31 +471,55 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs 
     }
 }
 
-template <int G, int BITS, int KIND>
-static int launch_gemv_bt(const GemvArgs &a, cudaStream_t st)
+// Launch configuration is resolved once per (kernel, device, shared-memory size) and cached,
+// so that a steady-state launch is nothing but the launch itself (and can be stream-captured).
+static std::atomic<int> g_gemv_ctas_per_sm{0};   // 0 = as many as fit
+void set_gemv_ctas_per_sm(int v) { g_gemv_ctas_per_sm.store(v < 0 ? 0 : v); }
+
+template <int G, int BITS, int BT, int KIND>
+static int launch_gemv_one(const GemvArgs &a, cudaStream_t st)
 {
-    const uint32_t bt = a.batch <= 1 ? 1 : a.batch <= 2 ? 2 : a.batch <= 4 ? 4 : 8;
-    const size_t smem = gemv_smem_bytes(a.K, a.p, bt, KIND);
-    void (*kern)(const GemvArgs) = nullptr;
-    switch (bt) {
-        case 1: kern = gemv_tiles_kernel<G, BITS, 1, KIND>; break;
-        case 2: kern = gemv_tiles_kernel<G, BITS, 2, KIND>; break;
-        case 4: kern = gemv_tiles_kernel<G, BITS, 4, KIND>; break;
-        default: kern = gemv_tiles_kernel<G, BITS, 8, KIND>; break;
-    }
+    struct Cfg { size_t smem = 0; int per_sm = 0, sms = 0; };
+    static Cfg cfg[16];
+    static std::mutex mu;
+    auto kern = gemv_tiles_kernel<G, BITS, BT, KIND>;
+    const size_t smem = gemv_smem_bytes(a.K, a.p, BT, KIND);
     if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
-    int per_sm = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem);
-    if (e != cudaSuccess) return (int)e;
-    if (per_sm < 1) return (int)cudaErrorLaunchOutOfResources;
-    const int sms = device_sm_count();
-    uint32_t grid = (uint32_t)(sms * per_sm);
+    Cfg c;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        Cfg &slot = cfg[dev & 15];
+        if (slot.smem != smem || slot.per_sm == 0) {
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            int per_sm = 0;
+            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem);
+            if (e != cudaSuccess) return (int)e;
+            if (per_sm < 1) return (int)cudaErrorLaunchOutOfResources;
+            slot.smem = smem; slot.per_sm = per_sm; slot.sms = device_sm_count();
+        }
+        c = slot;
+    }
+    int per_sm = c.per_sm;
+    const int want = g_gemv_ctas_per_sm.load();
+    if (want > 0) per_sm = std::min(per_sm, want);
+    uint32_t grid = (uint32_t)(c.sms * per_sm);
     grid = max(1u, min(grid, a.ntiles));
     kern<<<grid, kThreads, smem, st>>>(a);
     g_launches++;
     return (int)cudaGetLastError();
+}
+
+template <int G, int BITS, int KIND>
+static int launch_gemv_bt(const GemvArgs &a, cudaStream_t st)
+{
+    if (a.batch <= 1) return launch_gemv_one<G, BITS, 1, KIND>(a, st);
+    if (a.batch <= 2) return launch_gemv_one<G, BITS, 2, KIND>(a, st);
+    if (a.batch <= 4) return launch_gemv_one<G, BITS, 4, KIND>(a, st);
+    return launch_gemv_one<G, BITS, 8, KIND>(a, st);
 }
 
 int launch_gemv(const GemvArgs &a, uint32_t G, uint32_t bits, uint32_t kind, void *stream)
@@ -374,24 +553,37 @@ __global__ void __launch_bounds__(256) decode_tiles_kernel(const DecodeArgs a)
     const uint32_t K = a.K, M = 1u << a.p;
     for (uint32_t i = tid * 4; i < M; i += blockDim.x * 4)
         *reinterpret_cast<uint4 *>(tab + i) = __ldg(reinterpret_cast<const uint4 *>(a.table + i));
+    RingCtl ring;
+    ring_setup(ring, smem + smem_table_bytes(a.p), warp, nwarps, lane, a.status);
     __syncthreads();
 
     const uint32_t mask = M - 1u, p = a.p, sgroups = K / a.group;
     for (uint32_t t = blockIdx.x + gridDim.x * warp; t < a.ntiles; t += gridDim.x * nwarps) {
         const TileDesc d = a.tiles[t];
         const uint8_t *base = a.stream + ((size_t)d.off64 << 6);
-        uint32_t x = __ldg(reinterpret_cast<const uint32_t *>(base) + lane);
-        const uint16_t *ptr = reinterpret_cast<const uint16_t *>(base + 128) + lane;
-        uint32_t w = __ldg(ptr);
+        uint32_t x;
+        WordState ws;
+        const bool ring_mode = tile_begin(ring, ws, d, base, lane, x);
         const uint32_t row = d.row0 + lane * G;
         for (uint32_t c = d.col0; c < d.col0 + d.ncols; c += 8) {
             uint32_t sym[G][8];
+            if (ring_mode) {
 #pragma unroll
-            for (int s = 0; s < 8; s++) {
-                const uint32_t e = rans_step(tab, x, mask, p, F::kBiasMask);
+                for (int s = 0; s < 8; s++) {
+                    if (s % kSyncSteps == 0) ring_sync(ring, ws, lane);
+                    const uint32_t e = rans_step(tab, x, mask, p, F::kBiasMask);
 #pragma unroll
-                for (int j = 0; j < G; j++) sym[j][s] = (e >> F::field_bit(j)) & F::kFieldMask;
-                rans_renorm(x, w, ptr);
+                    for (int j = 0; j < G; j++) sym[j][s] = (e >> F::field_bit(j)) & F::kFieldMask;
+                    rans_renorm<true>(x, ws);
+                }
+            } else {
+#pragma unroll
+                for (int s = 0; s < 8; s++) {
+                    const uint32_t e = rans_step(tab, x, mask, p, F::kBiasMask);
+#pragma unroll
+                    for (int j = 0; j < G; j++) sym[j][s] = (e >> F::field_bit(j)) & F::kFieldMask;
+                    rans_renorm<false>(x, ws);
+                }
             }
 #pragma unroll
             for (int j = 0; j < G; j++) {
@@ -435,13 +627,14 @@ __global__ void __launch_bounds__(256) decode_tiles_kernel(const DecodeArgs a)
                 }
             }
         }
+        tile_end(ring, ring_mode);
     }
 }
 
 template <int G, int BITS, int KIND>
 static int launch_decode_tiles_t(const DecodeArgs &a, cudaStream_t st)
 {
-    const size_t smem = smem_table_bytes(a.p);
+    const size_t smem = smem_table_bytes(a.p) + ring_smem_bytes(256 / 32);
     auto kern = decode_tiles_kernel<G, BITS, KIND>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;

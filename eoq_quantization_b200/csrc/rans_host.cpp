@@ -219,6 +219,7 @@ eoq_error_t build_tiled(const uint8_t *symbols, uint32_t N, uint32_t K, uint32_t
         const uint32_t rb = (uint32_t)(t / nseg), seg = (uint32_t)(t % nseg);
         const uint32_t col0 = out.seg_start[seg], ncols = out.seg_start[seg + 1] - col0;
         std::vector<uint16_t> words[32];
+        std::vector<uint8_t> took(32 * (size_t)ncols, 0);    // took[l*ncols + c] = lane l reads a word after step c
         uint32_t state[32];
         size_t longest = 0;
         for (uint32_t l = 0; l < 32; l++) {
@@ -228,7 +229,7 @@ eoq_error_t build_tiled(const uint8_t *symbols, uint32_t N, uint32_t K, uint32_t
             w.reserve(ncols);
             for (uint32_t c = ncols; c-- > 0;) {
                 const uint64_t f = freq[src[c]], cm = cum[src[c]];
-                if (x >= (f << (32 - p))) { w.push_back((uint16_t)x); x >>= 16; }
+                if (x >= (f << (32 - p))) { w.push_back((uint16_t)x); x >>= 16; took[l * (size_t)ncols + c] = 1; }
                 x = ((x / f) << p) + (x % f) + cm;
             }
             state[l] = (uint32_t)x;
@@ -243,8 +244,18 @@ eoq_error_t build_tiled(const uint8_t *symbols, uint32_t N, uint32_t K, uint32_t
             const auto &w = words[l];
             for (size_t k = 0; k < w.size(); k++) rows[k * 32 + l] = w[w.size() - 1 - k];
         }
+        // how far apart the lanes' read positions get; beyond the bound the tile is read without the ring
+        uint32_t pos[32] = {0}, drift = 0;
+        for (uint32_t c = 0; c < ncols; c++) {
+            uint32_t lo = ~0u, hi = 0;
+            for (uint32_t l = 0; l < 32; l++) {
+                pos[l] += took[l * (size_t)ncols + c];
+                lo = std::min(lo, pos[l]); hi = std::max(hi, pos[l]);
+            }
+            drift = std::max(drift, hi - lo);
+        }
         TileDesc d;
-        d.row0 = rb * rows_per_tile; d.col0 = col0; d.ncols = ncols; d.seg = seg; d.off64 = 0; d.rb = rb;
+        d.row0 = rb * rows_per_tile; d.col0 = col0; d.ncols = ncols; d.seg = seg | (drift > kMaxRingDrift ? kTileDirectFlag : 0u); d.off64 = 0; d.len64 = (uint32_t)(tb.size() >> 6);
         out.tiles[t] = d;
     });
     size_t total = 0;
@@ -253,7 +264,7 @@ eoq_error_t build_tiled(const uint8_t *symbols, uint32_t N, uint32_t K, uint32_t
         out.tiles[t].off64 = (uint32_t)(total >> 6);
         total += tile_bytes[t].size();
     }
-    out.stream.assign(total + 256, 0);
+    out.stream.assign(total + 4096, 0);
     parallel_for(ntiles, [&](size_t t) {
         std::memcpy(out.stream.data() + ((size_t)out.tiles[t].off64 << 6), tile_bytes[t].data(), tile_bytes[t].size());
     });

@@ -224,7 +224,7 @@ typedef struct {
  * its bytes start at stream + 64*off64: 32 x u32 initial states, then rows of
  * 32 x u16 renormalisation words (lane l reads column l, top to bottom). */
 typedef struct eoq_b200_tiles eoq_b200_tiles_t;
-typedef struct { uint32_t row0, col0, ncols, seg, off64, rb; } eoq_b200_tile_desc_t;
+typedef struct { uint32_t row0, col0, ncols, seg, off64, len64; } eoq_b200_tile_desc_t;   /* len64: tile bytes / 64 */
 typedef struct {
     uint32_t rows, cols, padded_rows, group, kind, bits;
     uint32_t symbols_per_step, precision_bits;
@@ -291,6 +291,16 @@ eoq_error_t eoq_b200_weight_decode(eoq_b200_weight_t *w, uint8_t *d_symbols_or_p
 eoq_error_t eoq_b200_dequant_packed(const uint8_t *d_packed, const uint16_t *d_scales_fp16, uint32_t rows, uint32_t cols,
                                     uint32_t bits, uint32_t group, uint32_t row_lo, uint32_t row_hi, void *d_out,
                                     int out_dtype, void *stream);
+
+/* Synchronises `stream` and reports whether any kernel that used this weight gave up on a
+ * bounded wait for its staged data (EOQ_ERR_CUDA; outputs of that launch are then invalid).
+ * The kernels never spin without a limit, so a fault in the copy engine ends in this error
+ * rather than in a hang. */
+eoq_error_t eoq_b200_weight_status(eoq_b200_weight_t *w, void *stream);
+
+/* Diagnostic knob for sweeps; returns 0 if the key is known.  Keys:
+ * "gemv_ctas_per_sm" (0 = as many CTAs of the fused kernel as fit on an SM). */
+int eoq_b200_tune(const char *key, int value);
 
 /* Number of kernels launched by this library since load (for benchmarks). */
 uint64_t eoq_b200_launch_count(void);

@@ -285,7 +285,7 @@ void orc_int4_linear(const uint8_t *packed /* [N, ceil(K/2)] */, const float *sc
  * G consecutive rows row0 + l*G + j and reads column l of the word rows.  Step:
  *   e = table[x & (2^p - 1)];  x = (e >> 23) * (x >> p) + (e & bias_mask);
  *   symbols = (e >> (23 - G*bits)) fields;  if x < 2^16: x = x << 16 | next word.
- * desc[t] = {row0, col0, ncols, seg, off64, rb}.  out is [rows, cols] bytes.
+ * desc[t] = {row0, col0, ncols, seg, off64, len64}.  out is [rows, cols] bytes.
  * ---------------------------------------------------------------------- */
 int orc_decode_tiles(const uint32_t *table, uint32_t p, uint32_t G, uint32_t bits,
                      const uint32_t *desc, uint32_t ntiles, const uint8_t *stream, size_t stream_bytes,
