@@ -238,6 +238,8 @@ def run_gpu_arm(args):
     barrier()
     launch_mode = "cuda-graph"
     try:
+        if args.eager:
+            raise RuntimeError("eager launches requested")
         g_full = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g_full):
             for i in range(REPLICAS):
@@ -395,6 +397,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="plain launches instead of CUDA graphs (for profilers)")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps > 20:

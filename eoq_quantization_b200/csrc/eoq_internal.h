@@ -41,7 +41,7 @@ struct TileDesc {
 };
 
 constexpr uint32_t kMaxFreq = 511;
-constexpr uint32_t kMaxRingDrift = 43;           // rows the lanes of a ring-mode tile may be apart at any step
+constexpr uint32_t kMaxRingDrift = 39;           // rows the lanes of a ring-mode tile may be apart at any step
 constexpr uint32_t kTileDirectFlag = 0x80000000u; // set in TileDesc::seg when the tile breaks that bound
 constexpr uint32_t kColGranule = 16;   // tile column boundaries are multiples of this
 

@@ -28,7 +28,14 @@ int device_sm_count()
     return sms;
 }
 
-constexpr int kThreads = 512;
+// Build-time tuning (defaults are what the committed measurements use).
+#ifndef EOQ_GEMV_THREADS
+#define EOQ_GEMV_THREADS 512
+#endif
+#ifndef EOQ_SHIFT_BY_MULHI
+#define EOQ_SHIFT_BY_MULHI 0     // 1: do the two right shifts of a step as IMAD.HI (FMA pipe) instead of SHF (ALU pipe)
+#endif
+constexpr int kThreads = EOQ_GEMV_THREADS;
 constexpr int kWarps = kThreads / 32;
 
 // ---------------------------------------------------------------------------
@@ -87,7 +94,7 @@ __device__ __forceinline__ void store_y(void *p, size_t i, float v, int dtype)
 __device__ __forceinline__ float half_bits_to_float(uint16_t h) { return __half2float(__ushort_as_half(h)); }
 
 // Geometry of the per-warp word ring (see "Streaming a tile's renormalisation words" below).
-constexpr uint32_t kRingRows = 64, kChunkRows = 16, kRingChunks = kRingRows / kChunkRows, kSyncSteps = 4;
+constexpr uint32_t kRingRows = 64, kChunkRows = 16, kRingChunks = kRingRows / kChunkRows, kSyncSteps = 8;
 constexpr uint32_t kRingBytes = kRingRows * 64, kChunkBytes = kChunkRows * 64;
 static_assert(kMaxRingDrift + kSyncSteps + 1 + kChunkRows <= kRingRows, "ring too small for the drift bound");
 
@@ -106,7 +113,11 @@ size_t gemv_smem_bytes(uint32_t K, uint32_t p, uint32_t bt, uint32_t kind)
 __device__ __forceinline__ uint32_t rans_step(const uint32_t *tab, uint32_t &x, uint32_t mask, uint32_t p, uint32_t bias_mask)
 {
     const uint32_t e = tab[x & mask];
+#if EOQ_SHIFT_BY_MULHI
+    x = __umulhi(e, 1u << 9) * __umulhi(x, 1u << (32 - p)) + (e & bias_mask);
+#else
     x = (e >> 23) * (x >> p) + (e & bias_mask);
+#endif
     return e;
 }
 
@@ -161,8 +172,8 @@ struct WordState {            // per lane
 struct RingCtl {              // per warp (all fields warp-uniform)
     uint32_t ring_base, bar0; // shared addresses
     uint32_t issued, ready;   // chunks issued / known complete since the kernel started
-    uint32_t tile_first, nchunks, row_bytes;
-    const uint8_t *src;       // global address of the tile's first word row
+    uint32_t tile_first, tile_last, tile_bytes;  // chunk range [first, last) and byte length of the open tile
+    const uint8_t *src;       // global address of the open tile
     uint32_t *status;
 };
 
@@ -178,46 +189,72 @@ __device__ __forceinline__ void ring_setup(RingCtl &r, uint8_t *ring_area, uint3
         for (uint32_t i = 0; i < kRingChunks; i++) mbar_init(r.bar0 + i * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    __syncwarp();
 }
 
-__device__ __forceinline__ void ring_sync(RingCtl &r, const WordState &s, uint32_t lane)
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr)
 {
-    const uint32_t first_row = r.tile_first * kChunkRows;
-    const uint32_t kmin = (__reduce_min_sync(0xffffffffu, s.koff) >> 6) - first_row;
-    const uint32_t kmax = (__reduce_max_sync(0xffffffffu, s.koff) >> 6) - first_row;
-    const uint32_t limit = r.tile_first + min(r.nchunks, kmin / kChunkRows + kRingChunks);
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+// Start copies for every chunk of the current tile below `limit` that has not been started yet.
+__device__ __forceinline__ void ring_issue(RingCtl &r, uint32_t limit, uint32_t lane)
+{
     while (r.issued < limit) {
         if (lane == 0) {
             const uint32_t c = r.issued - r.tile_first, slot = r.issued % kRingChunks;
-            const uint32_t bytes = min(kChunkBytes, r.row_bytes - c * kChunkBytes);
+            const uint32_t bytes = min(kChunkBytes, r.tile_bytes - c * kChunkBytes);
             mbar_expect_tx(r.bar0 + slot * 8, bytes);
             bulk_copy_g2s(r.ring_base + slot * kChunkBytes, r.src + (size_t)c * kChunkBytes, bytes, r.bar0 + slot * 8);
         }
         r.issued++;
     }
-    const uint32_t need = min(r.issued, r.tile_first + min(r.nchunks, (kmax + kSyncSteps + 1) / kChunkRows + 1));
+}
+
+__device__ __forceinline__ void ring_sync(RingCtl &r, const WordState &s, uint32_t lane)
+{
+    // chunk numbers count from the warp's first chunk of the kernel; koff is in the same frame
+    const uint32_t cmin = __reduce_min_sync(0xffffffffu, s.koff) / kChunkBytes;
+    const uint32_t cmax = (__reduce_max_sync(0xffffffffu, s.koff) + (kSyncSteps + 1) * 64) / kChunkBytes;
+    ring_issue(r, min(r.tile_last, cmin + kRingChunks), lane);
+    const uint32_t need = min(r.issued, cmax + 1);
     while (r.ready < need) {
         mbar_wait_bounded(r.bar0 + (r.ready % kRingChunks) * 8, (r.ready / kRingChunks) & 1u, r.status);
         r.ready++;
     }
 }
 
-// Start of a tile.  Returns true if the tile runs in ring mode.
-__device__ __forceinline__ bool tile_begin(RingCtl &r, WordState &s, const TileDesc &d, const uint8_t *base, uint32_t lane, uint32_t &x)
+// Open a tile: ask L2 for all of it and, in ring mode, start its first copies.  Waits for nothing, so it
+// can run well before the tile is decoded (before the kernel's prologue, or while the previous tile's
+// results are being written).  The whole tile goes through the ring, its 128-byte state header included.
+__device__ __forceinline__ void tile_open(RingCtl &r, const TileDesc &d, const uint8_t *base, uint32_t lane)
 {
     if (lane == 0) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base), "r"(d.len64 << 6) : "memory");
-    x = __ldg(reinterpret_cast<const uint32_t *>(base) + lane);
+    if ((d.seg & kTileDirectFlag) == 0) {
+        r.tile_first = r.issued;
+        r.tile_bytes = d.len64 << 6;
+        r.tile_last = r.tile_first + (r.tile_bytes + kChunkBytes - 1) / kChunkBytes;
+        r.src = base;
+        ring_issue(r, min(r.tile_last, r.tile_first + kRingChunks), lane);
+    }
+}
+
+// Begin decoding an opened tile: wait for its first chunk, read the lane's state and first word.
+// Returns true if the tile runs in ring mode.
+__device__ __forceinline__ bool tile_begin(RingCtl &r, WordState &s, const TileDesc &d, const uint8_t *base, uint32_t lane, uint32_t &x)
+{
     const bool ring = (d.seg & kTileDirectFlag) == 0;
     if (ring) {
-        r.tile_first = r.issued;
-        r.row_bytes = (d.len64 << 6) - 128;
-        r.nchunks = (r.row_bytes + kChunkBytes - 1) / kChunkBytes;
-        r.src = base + 128;
-        s.koff = r.tile_first * kChunkBytes;
+        const uint32_t start = r.tile_first * kChunkBytes;
+        s.koff = start + 128;                                   // word row 0 sits behind the two header rows
         s.ring_lane = r.ring_base | (lane * 2);
         ring_sync(r, s, lane);
+        x = lds_u32(r.ring_base + (start & (kRingBytes - 1)) + lane * 4);
         s.w = lds_u16((s.koff & (kRingBytes - 1)) | s.ring_lane);
     } else {
+        x = __ldg(reinterpret_cast<const uint32_t *>(base) + lane);
         s.ptr = reinterpret_cast<const uint16_t *>(base + 128) + lane;
         s.w = __ldg(s.ptr);
     }
@@ -237,15 +274,20 @@ __device__ __forceinline__ void tile_end(RingCtl &r, bool ring)
 template <bool RING>
 __device__ __forceinline__ void rans_renorm(uint32_t &x, WordState &s)
 {
-    if (x < 65536u) {
+    if (RING) {
+        // predicated, branch-free: x = x * 65536 + w; koff += 64; w = ring[(koff mod ring) | lane*2]
+        asm volatile("{\n\t.reg .pred p;\n\t.reg .b32 t;\n\t"
+                     "setp.lt.u32 p, %0, 65536;\n\t"
+                     "@p mad.lo.u32 %0, %0, 65536, %1;\n\t"
+                     "@p add.u32 %2, %2, 64;\n\t"
+                     "@p lop3.b32 t, %2, %4, %3, 0xEA;\n\t"
+                     "@p ld.shared.u16 %1, [t];\n\t}"
+                     : "+r"(x), "+r"(s.w), "+r"(s.koff)
+                     : "r"(s.ring_lane), "n"(kRingBytes - 1));
+    } else if (x < 65536u) {
         x = (x << 16) | s.w;
-        if (RING) {
-            s.koff += 64;
-            s.w = lds_u16((s.koff & (kRingBytes - 1)) | s.ring_lane);
-        } else {
-            s.ptr += 32;
-            s.w = __ldg(s.ptr);
-        }
+        s.ptr += 32;
+        s.w = __ldg(s.ptr);
     }
 }
 
@@ -286,7 +328,8 @@ __device__ __forceinline__ void gemv_tile_columns(const GemvArgs &a, const TileD
 
 #pragma unroll 2
             for (; c < rend; c += 4) {
-                if (RING) ring_sync(ring, ws, lane);
+                // runs start on multiples of 16 columns, so this fires every kSyncSteps = 8 steps
+                if (RING && (c & 4u) == 0) ring_sync(ring, ws, lane);
                 float xv[4][BT];
                 if (BT == 1) {
                     const float4 v = *reinterpret_cast<const float4 *>(xs + c);
@@ -375,6 +418,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs 
     const uint32_t K = a.K, M = 1u << a.p;
     RingCtl ring;
     ring_setup(ring, ring_area, warp, kWarps, lane, a.status);
+    // this warp's first tile starts streaming before the table and x are staged
+    uint32_t t = blockIdx.x + gridDim.x * warp;
+    bool have = t < a.ntiles;
+    TileDesc d;
+    if (have) {
+        d = a.tiles[t];
+        tile_open(ring, d, a.stream + ((size_t)d.off64 << 6), lane);
+    }
 
     for (uint32_t i = tid * 4; i < M; i += kThreads * 4)
         *reinterpret_cast<uint4 *>(tab + i) = __ldg(reinterpret_cast<const uint4 *>(a.table + i));
@@ -412,15 +463,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs 
 
     const uint32_t mask = M - 1u, p = a.p;
     const uint32_t sgroups = K / a.group;
-    for (uint32_t t = blockIdx.x + gridDim.x * warp; t < a.ntiles; t += gridDim.x * kWarps) {
-        const TileDesc d = a.tiles[t];
-        const uint8_t *base = a.stream + ((size_t)d.off64 << 6);
+    while (have) {
+        const TileDesc cur = d;
         uint32_t x;
         WordState ws;
-        const bool ring_mode = tile_begin(ring, ws, d, base, lane, x);
-        const uint32_t row = d.row0 + lane * G;
-        const uint32_t rb = d.row0 / (32u * G);
-        const uint32_t seg = d.seg & ~kTileDirectFlag;
+        const bool ring_mode = tile_begin(ring, ws, cur, a.stream + ((size_t)cur.off64 << 6), lane, x);
+        const uint32_t row = cur.row0 + lane * G;
+        const uint32_t rb = cur.row0 / (32u * G);
+        const uint32_t seg = cur.seg & ~kTileDirectFlag;
 
         float y[G][BT];
 #pragma unroll
@@ -428,10 +478,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs 
 #pragma unroll
             for (int b = 0; b < BT; b++) y[j][b] = 0.0f;
 
-        if (ring_mode) gemv_tile_columns<G, BITS, BT, KIND, true>(a, d, tab, xs, aux, lane, row, mask, p, sgroups, x, ws, ring, y);
-        else gemv_tile_columns<G, BITS, BT, KIND, false>(a, d, tab, xs, aux, lane, row, mask, p, sgroups, x, ws, ring, y);
+        if (ring_mode) gemv_tile_columns<G, BITS, BT, KIND, true>(a, cur, tab, xs, aux, lane, row, mask, p, sgroups, x, ws, ring, y);
+        else gemv_tile_columns<G, BITS, BT, KIND, false>(a, cur, tab, xs, aux, lane, row, mask, p, sgroups, x, ws, ring, y);
         tile_end(ring, ring_mode);
 
+        // the next tile's copies start now and overlap the write-back of this one
+        t += gridDim.x * kWarps;
+        have = t < a.ntiles;
+        if (have) {
+            d = a.tiles[t];
+            tile_open(ring, d, a.stream + ((size_t)d.off64 << 6), lane);
+        }
+
+        bool write_out = true;
         if (a.nseg > 1) {
             float *mine = a.partials + ((size_t)seg * a.Npad + row) * BT;
 #pragma unroll
@@ -443,29 +502,48 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs 
             uint32_t ticket = 0;
             if (lane == 0) ticket = atomicAdd(a.counters + rb, 1u);
             ticket = __shfl_sync(0xffffffffu, ticket, 0);
-            if (ticket != a.nseg - 1) continue;
-            __threadfence();
-#pragma unroll
-            for (int j = 0; j < G; j++)
-#pragma unroll
-                for (int b = 0; b < BT; b++) y[j][b] = 0.0f;
-            for (uint32_t s = 0; s < a.nseg; s++) {
-                const float *src = a.partials + ((size_t)s * a.Npad + row) * BT;
+            write_out = ticket == a.nseg - 1;
+            if (write_out) {
+                // last warp of the row block: add the segments' partial sums, always in segment order;
+                // loads are issued kU segments at a time so their latencies overlap
+                __threadfence();
+                constexpr int kU = G * BT <= 3 ? 8 : G * BT <= 6 ? 4 : G * BT <= 12 ? 2 : 1;
 #pragma unroll
                 for (int j = 0; j < G; j++)
 #pragma unroll
-                    for (int b = 0; b < BT; b++) y[j][b] += __ldcg(src + j * BT + b);
+                    for (int b = 0; b < BT; b++) y[j][b] = 0.0f;
+                for (uint32_t s0 = 0; s0 < a.nseg; s0 += kU) {
+                    float v[kU][G][BT];
+#pragma unroll
+                    for (int u = 0; u < kU; u++) {
+                        const uint32_t sidx = min(s0 + u, a.nseg - 1);
+                        const float *src = a.partials + ((size_t)sidx * a.Npad + row) * BT;
+#pragma unroll
+                        for (int j = 0; j < G; j++)
+#pragma unroll
+                            for (int b = 0; b < BT; b++) v[u][j][b] = __ldcg(src + j * BT + b);
+                    }
+#pragma unroll
+                    for (int u = 0; u < kU; u++)
+                        if (s0 + u < a.nseg)
+#pragma unroll
+                            for (int j = 0; j < G; j++)
+#pragma unroll
+                                for (int b = 0; b < BT; b++) y[j][b] += v[u][j][b];
+                }
+                if (lane == 0) a.counters[rb] = 0u;
             }
-            if (lane == 0) a.counters[rb] = 0u;
         }
+        if (write_out) {
 #pragma unroll
-        for (int j = 0; j < G; j++) {
-            const uint32_t r = row + j;
-            if (r < a.N) {
-                const float bv = a.bias ? __ldg(a.bias + r) : 0.0f;
+            for (int j = 0; j < G; j++) {
+                const uint32_t r = row + j;
+                if (r < a.N) {
+                    const float bv = a.bias ? __ldg(a.bias + r) : 0.0f;
 #pragma unroll
-                for (int b = 0; b < BT; b++)
-                    if ((uint32_t)b < a.batch) store_y(a.y, (size_t)b * a.N + r, y[j][b] + bv, a.y_dtype);
+                    for (int b = 0; b < BT; b++)
+                        if ((uint32_t)b < a.batch) store_y(a.y, (size_t)b * a.N + r, y[j][b] + bv, a.y_dtype);
+                }
             }
         }
     }
@@ -563,6 +641,7 @@ __global__ void __launch_bounds__(256) decode_tiles_kernel(const DecodeArgs a)
         const uint8_t *base = a.stream + ((size_t)d.off64 << 6);
         uint32_t x;
         WordState ws;
+        tile_open(ring, d, base, lane);
         const bool ring_mode = tile_begin(ring, ws, d, base, lane, x);
         const uint32_t row = d.row0 + lane * G;
         for (uint32_t c = d.col0; c < d.col0 + d.ncols; c += 8) {

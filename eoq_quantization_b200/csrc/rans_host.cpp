@@ -152,6 +152,7 @@ eoq_error_t build_tiled(const uint8_t *symbols, uint32_t N, uint32_t K, uint32_t
                         uint32_t p, uint32_t group, uint32_t kind, uint32_t target_tiles,
                         uint8_t pad_symbol, TiledWeights &out)
 {
+    (void)pad_symbol;
     if (!symbols) return EOQ_ERR_NULL_PTR;
     if (N == 0 || K == 0) return EOQ_ERR_INVALID_HEADER;
     if (G < 1 || G > 3 || bits < 1 || bits * G > 12 || p < bits * G || p > 16) return EOQ_ERR_UNSUPPORTED;
@@ -182,7 +183,9 @@ eoq_error_t build_tiled(const uint8_t *symbols, uint32_t N, uint32_t K, uint32_t
             uint32_t v = 0;
             for (uint32_t j = 0; j < G; j++) {
                 const size_t r = rg * G + j;
-                const uint32_t n = r < N ? (symbols[r * K + c] & sym_mask) : pad_symbol;
+                // rows past the end are never written back; they repeat real rows so that their lanes
+                // consume words at the same rate as their neighbours
+                const uint32_t n = symbols[(r < N ? r : r % N) * K + c] & sym_mask;
                 v |= n << (bits * j);
             }
             dst[c] = (uint16_t)v;
