@@ -779,3 +779,93 @@ extern "C" int eoq_b200_tune(const char *key, int value)
 }
 
 extern "C" uint64_t eoq_b200_launch_count(void) { return launch_counter(); }
+
+// =========================================================================
+// Fused GEMV for callers that must not allocate
+// =========================================================================
+//
+// Some callers cannot let a library reach the device allocator: a serving loop that has
+// handed all of HBM to its own arena, a real-time thread where an allocator lock is a
+// latency hazard, or code running under a framework that forbids allocation while it
+// replays recorded work.  For them the cross-tile scratch of the fused kernel (the partial
+// row sums of the column segments and the per-row-block arrival counters) lives in one
+// fixed array in device global memory that is part of the loaded library.  Every GPU that
+// loads the library holds the array until the process exits.
+//
+// In host code `g_gemv_scratch` is only a handle for the symbol, never a device address: its
+// address is looked up once per device with cudaGetSymbolAddress (with that device
+// current) and the resulting pointer is what the kernel receives.
+constexpr size_t kGemvStaticScratchBytes = EOQ_B200_GEMV_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_gemv_scratch[kGemvStaticScratchBytes];
+
+namespace {
+struct StaticScratchMap {
+    std::mutex mu;
+    void *dev_ptr[64] = {nullptr};
+} g_static_scratch;
+
+// First use on a device resolves the symbol; later calls are a table lookup.
+eoq_error_t static_scratch_for_current_device(unsigned char **out)
+{
+    int dev = 0;
+    CU_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return EOQ_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_static_scratch.mu);
+    if (!g_static_scratch.dev_ptr[dev]) {
+        void *p = nullptr;
+        CU_TRY(cudaGetSymbolAddress(&p, g_gemv_scratch));
+        g_static_scratch.dev_ptr[dev] = p;
+    }
+    *out = static_cast<unsigned char *>(g_static_scratch.dev_ptr[dev]);
+    return EOQ_OK;
+}
+}  // namespace
+
+extern "C" eoq_error_t eoq_b200_gemv_static_scratch(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch,
+                                                    void *y, int y_dtype, const float *bias, void *stream)
+{
+    if (!w || !x || !y) return EOQ_ERR_NULL_PTR;
+    if (batch == 0) return EOQ_OK;
+    if (batch > 8) return EOQ_ERR_UNSUPPORTED;
+    if (x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2) return EOQ_ERR_UNSUPPORTED;
+    const uint32_t bt = batch <= 1 ? 1 : batch <= 2 ? 2 : batch <= 4 ? 4 : 8;
+    if (gemv_smem_bytes(w->K, w->p, bt, w->kind) > 227 * 1024) {
+        // same rule as eoq_b200_gemv: rows that do not fit shared memory together run in two halves
+        if (bt == 1) return EOQ_ERR_UNSUPPORTED;
+        static const size_t esz[3] = {2, 2, 4};
+        const uint32_t half = bt / 2, first = std::min(batch, half);
+        eoq_error_t rc = eoq_b200_gemv_static_scratch(w, x, x_dtype, first, y, y_dtype, bias, stream);
+        if (rc != EOQ_OK || batch <= half) return rc;
+        return eoq_b200_gemv_static_scratch(w, static_cast<const uint8_t *>(x) + (size_t)first * w->K * esz[x_dtype], x_dtype,
+                                            batch - first, static_cast<uint8_t *>(y) + (size_t)first * w->N * esz[y_dtype],
+                                            y_dtype, bias, stream);
+    }
+    // layout of the array: [arrival counters, one u32 per row block, padded to 256 B][partial sums nseg x Npad x bt floats]
+    const size_t counter_bytes = (((size_t)w->nrb * 4) + 255) & ~(size_t)255;
+    const size_t partial_bytes = w->nseg > 1 ? (size_t)w->nseg * w->Npad * bt * sizeof(float) : 0;
+    if (counter_bytes + partial_bytes > kGemvStaticScratchBytes) {
+        std::fprintf(stderr,
+                     "eoq_b200_gemv_static_scratch: this weight needs %zu bytes of scratch for %u rows of x, the built-in array holds %zu; "
+                     "use eoq_b200_gemv\n",
+                     counter_bytes + partial_bytes, batch, kGemvStaticScratchBytes);
+        return EOQ_ERR_BUFFER_TOO_SMALL;
+    }
+    unsigned char *scratch = nullptr;
+    eoq_error_t rc = static_scratch_for_current_device(&scratch);
+    if (rc != EOQ_OK) return rc;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    // the array keeps whatever the last call left; the counters are the only part that must start at zero
+    CU_TRY(cudaMemsetAsync(scratch, 0, counter_bytes, st));
+    GemvArgs a;
+    a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
+    a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
+    a.x = x; a.y = y; a.bias = bias;
+    a.partials = reinterpret_cast<float *>(scratch + counter_bytes);
+    a.counters = reinterpret_cast<uint32_t *>(scratch);
+    a.status = w->status.as<uint32_t>();
+    a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
+    a.x_dtype = x_dtype; a.y_dtype = y_dtype;
+    int e = launch_gemv(a, w->G, w->bits, w->kind, stream);
+    if (e != 0) { std::fprintf(stderr, "eoq_b200_gemv_static_scratch: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
+    return EOQ_OK;
+}

@@ -273,6 +273,31 @@ eoq_error_t eoq_b200_gemv(eoq_b200_weight_t *w, const void *x, int x_dtype, uint
 eoq_error_t eoq_b200_gemv_host(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch,
                                void *y, int y_dtype, const float *bias_host, void *stream);
 
+/* The same product for callers that must not allocate device memory (no counterpart in the
+ * reference).  A serving process that has given all of HBM to its own arena, a latency-critical
+ * thread that may not take the allocator's lock, or a framework that forbids allocation while it
+ * replays recorded work cannot let a library call cudaMalloc behind its back.  This entry point
+ * calls no allocator at all -- neither cudaMalloc/cudaFree nor any allocating library routine:
+ * the scratch the kernel needs across tiles (partial row sums per column segment and arrival
+ * counters per row block) is a fixed array of EOQ_B200_GEMV_STATIC_SCRATCH_BYTES in device
+ * global memory that belongs to the library image, so every GPU that loads the library
+ * carries it until the process exits.  x, y and bias are still the caller's buffers.
+ *
+ *  - A weight whose scratch need exceeds the array (it grows with rows x column segments x
+ *    batch) is refused with EOQ_ERR_BUFFER_TOO_SMALL and a message on stderr; use
+ *    eoq_b200_gemv for it.
+ *  - The first call on each device looks up the array's device address (one
+ *    cudaGetSymbolAddress with that device current).  Make that first call outside any
+ *    stream capture.
+ *  - All calls on a device share the one array, and it keeps the previous call's contents.
+ *    The counters are cleared on `stream` before each launch; the partial sums are always
+ *    written before they are read.  Two calls that overlap on the GPU (different streams,
+ *    or different weights at the same time) race on the array: serialise them.
+ *  - Results are identical to eoq_b200_gemv. */
+#define EOQ_B200_GEMV_STATIC_SCRATCH_BYTES (8u << 20)
+eoq_error_t eoq_b200_gemv_static_scratch(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch,
+                                         void *y, int y_dtype, const float *bias, void *stream);
+
 /* Decode the tiles back to the reference's in-memory forms (device pointers,
  * asynchronous): packed INT4 as QuantizedLinear.packed_weight
  * (core/quantized_linear.py:76-91: uint8 [N, K/2], low nibble = even column),
