@@ -548,7 +548,11 @@ eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const 
     if (w->table.alloc(tw.table.size() * 4) != cudaSuccess || w->tiles.alloc(tw.tiles.size() * sizeof(TileDesc)) != cudaSuccess ||
         w->stream.alloc(tw.stream.size()) != cudaSuccess || w->scales.alloc(w->scale_bytes) != cudaSuccess ||
         w->partials.alloc(w->partial_bytes) != cudaSuccess || w->counters.alloc((size_t)tw.nrb * 4) != cudaSuccess ||
+#ifdef EOQ_STAMPS
+        w->status.alloc(4u << 20) != cudaSuccess ||
+#else
         w->status.alloc(4) != cudaSuccess ||
+#endif
         w->xbuf.alloc((size_t)8 * tw.K * 4) != cudaSuccess || w->ybuf.alloc((size_t)8 * tw.N * 4) != cudaSuccess ||
         w->biasbuf.alloc((size_t)tw.N * 4) != cudaSuccess)
         return EOQ_ERR_ALLOC;
@@ -771,10 +775,18 @@ extern "C" eoq_error_t eoq_b200_weight_status(eoq_b200_weight_t *w, void *stream
     return status ? EOQ_ERR_CUDA : EOQ_OK;
 }
 
+#ifdef EOQ_STAMPS
+extern "C" int eoq_b200_debug_read_stamps(eoq_b200_weight_t *w, void *host, size_t bytes)
+{
+    return cudaMemcpy(host, w->status.as<uint8_t>() + 64, bytes, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
+}
+#endif
+
 extern "C" int eoq_b200_tune(const char *key, int value)
 {
     if (!key) return -1;
     if (std::strcmp(key, "gemv_ctas_per_sm") == 0) { set_gemv_ctas_per_sm(value); return 0; }
+    if (std::strcmp(key, "gemv_threads") == 0) { if (value != 0 && value != 512 && value != 1024) return -1; set_gemv_threads(value); return 0; }
     return -1;
 }
 

@@ -125,5 +125,6 @@ int launch_dequant_packed(const uint8_t *packed, const uint16_t *scales, uint32_
 size_t gemv_smem_bytes(uint32_t K, uint32_t p, uint32_t bt, uint32_t kind);
 uint64_t launch_counter();
 void set_gemv_ctas_per_sm(int v);
+void set_gemv_threads(int v);
 
 }  // namespace eoq

@@ -36,7 +36,15 @@ int device_sm_count()
 #define EOQ_SHIFT_BY_MULHI 0     // 1: do the two right shifts of a step as IMAD.HI (FMA pipe) instead of SHF (ALU pipe)
 #endif
 constexpr int kThreads = EOQ_GEMV_THREADS;
-constexpr int kWarps = kThreads / 32;
+
+// Debug builds only (-DEOQ_STAMPS): per-warp phase timestamps (ns) written behind the status word.
+#ifdef EOQ_STAMPS
+__device__ __forceinline__ unsigned long long stamp_now() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define EOQ_STAMP(slot) do { if (lane == 0) reinterpret_cast<unsigned long long *>(a.status + 16)[(size_t)(blockIdx.x * kWarps + warp) * 8 + (slot)] = stamp_now(); } while (0)
+#else
+#define EOQ_STAMP(slot) do { } while (0)
+#endif
+
 
 // ---------------------------------------------------------------------------
 // Table-entry geometry for G weights of BITS bits per rANS step.
@@ -64,10 +72,18 @@ struct Int4Field {
     static constexpr float kBase = (float)(1u << (23 - B));
     static constexpr bool kPreSubtract = B < 15;
     static constexpr float kCorr = kPreSubtract ? 0.0f : kBase + 7.0f;
-    __device__ __forceinline__ static float value(uint32_t e)
+    // `magic` is kMagic held in a register: the mask is the instruction's one immediate, so with the
+    // exponent in a register the extraction stays a single LOP3
+    __device__ __forceinline__ static float value(uint32_t e, uint32_t magic)
     {
-        float m = __uint_as_float((e & kMask) | kMagic);
+        float m = __uint_as_float((e & kMask) | magic);
         if (kPreSubtract) m -= kBase + 7.0f;
+        return m;
+    }
+    __device__ __forceinline__ static uint32_t magic_reg()
+    {
+        uint32_t m;
+        asm volatile("mov.b32 %0, %1;" : "=r"(m) : "n"(kMagic));   // opaque to constant propagation
         return m;
     }
 };
@@ -102,12 +118,13 @@ __host__ __device__ inline size_t ring_smem_bytes(uint32_t warps) { return (size
 
 // Shared-memory carve-up of the fused kernel (bytes).
 __host__ __device__ inline size_t smem_table_bytes(uint32_t p) { return (size_t)4 << p; }
-size_t gemv_smem_bytes(uint32_t K, uint32_t p, uint32_t bt, uint32_t kind)
+static size_t gemv_smem_bytes_for(uint32_t K, uint32_t p, uint32_t bt, uint32_t kind, uint32_t threads)
 {
-    size_t b = smem_table_bytes(p) + (size_t)K * bt * 4;
+    size_t b = smem_table_bytes(p) + 16 + (size_t)K * bt * 4;      // table, its arrival barrier, x
     b += kind == EOQ_B200_KIND_Q5_POLAR ? 32 * 32 * 4 : (size_t)(K / 16) * bt * 4;
-    return b + ring_smem_bytes(kWarps);
+    return b + ring_smem_bytes(threads / 32);
 }
+size_t gemv_smem_bytes(uint32_t K, uint32_t p, uint32_t bt, uint32_t kind) { return gemv_smem_bytes_for(K, p, bt, kind, kThreads); }
 
 // One rANS step: table lookup, state update; returns the entry.
 __device__ __forceinline__ uint32_t rans_step(const uint32_t *tab, uint32_t &x, uint32_t mask, uint32_t p, uint32_t bias_mask)
@@ -119,6 +136,28 @@ __device__ __forceinline__ uint32_t rans_step(const uint32_t *tab, uint32_t &x, 
     x = (e >> 23) * (x >> p) + (e & bias_mask);
 #endif
     return e;
+}
+
+// The same step with the INT4 fields of the entry turned into float bit patterns, written out
+// instruction by instruction so that a step is exactly: AND, IMAD (address), LDS, 2 x SHR, AND, IMAD
+// (state), and one LOP3 per field ((e & mask) | exponent, exponent in a register).
+template <uint32_t MASK0, uint32_t MASK1, uint32_t MASK2>
+__device__ __forceinline__ void rans_step_int4(uint32_t tab_addr, uint32_t &x, uint32_t mask, uint32_t p, uint32_t bias_mask,
+                                               uint32_t mg0, uint32_t mg1, uint32_t mg2, uint32_t &m0, uint32_t &m1, uint32_t &m2)
+{
+    asm("{\n\t.reg .b32 s, e, q, f, b;\n\t"
+        "and.b32 s, %0, %4;\n\t"
+        "mad.lo.u32 s, s, 4, %5;\n\t"
+        "ld.shared.u32 e, [s];\n\t"
+        "shr.u32 q, %0, %6;\n\t"
+        "shr.u32 f, e, 23;\n\t"
+        "and.b32 b, e, %7;\n\t"
+        "mad.lo.u32 %0, f, q, b;\n\t"
+        "lop3.b32 %1, e, %8, %11, 0xEA;\n\t"
+        "lop3.b32 %2, e, %9, %12, 0xEA;\n\t"
+        "lop3.b32 %3, e, %10, %13, 0xEA;\n\t}"
+        : "+r"(x), "=r"(m0), "=r"(m1), "=r"(m2)
+        : "r"(mask), "r"(tab_addr), "r"(p), "r"(bias_mask), "n"(MASK0), "n"(MASK1), "n"(MASK2), "r"(mg0), "r"(mg1), "r"(mg2));
 }
 
 // ---------------------------------------------------------------------------
@@ -213,14 +252,15 @@ __device__ __forceinline__ void ring_issue(RingCtl &r, uint32_t limit, uint32_t 
     }
 }
 
+// Keep the ring ahead of the readers.  Two warp votes against warp-uniform thresholds: a chunk is
+// refilled once every lane has left the chunk it replaces, and the next chunk is waited for as soon as
+// any lane could reach it within kSyncSteps steps.
 __device__ __forceinline__ void ring_sync(RingCtl &r, const WordState &s, uint32_t lane)
 {
     // chunk numbers count from the warp's first chunk of the kernel; koff is in the same frame
-    const uint32_t cmin = __reduce_min_sync(0xffffffffu, s.koff) / kChunkBytes;
-    const uint32_t cmax = (__reduce_max_sync(0xffffffffu, s.koff) + (kSyncSteps + 1) * 64) / kChunkBytes;
-    ring_issue(r, min(r.tile_last, cmin + kRingChunks), lane);
-    const uint32_t need = min(r.issued, cmax + 1);
-    while (r.ready < need) {
+    while (r.issued < r.tile_last && __all_sync(0xffffffffu, s.koff >= (r.issued + 1 - kRingChunks) * kChunkBytes))
+        ring_issue(r, r.issued + 1, lane);
+    while (r.ready < r.issued && __any_sync(0xffffffffu, s.koff + (kSyncSteps + 1) * 64 >= r.ready * kChunkBytes)) {
         mbar_wait_bounded(r.bar0 + (r.ready % kRingChunks) * 8, (r.ready / kRingChunks) & 1u, r.status);
         r.ready++;
     }
@@ -311,6 +351,10 @@ __device__ __forceinline__ void gemv_tile_columns(const GemvArgs &a, const TileD
                                                   uint32_t sgroups, uint32_t &x, WordState &ws, RingCtl &ring, float (&y)[G][BT])
 {
     using F = Fmt<G, BITS>;
+    const uint32_t magic0 = Int4Field<F::field_bit(0)>::magic_reg();
+    const uint32_t magic1 = Int4Field<F::field_bit(G > 1 ? 1 : 0)>::magic_reg();
+    const uint32_t magic2 = Int4Field<F::field_bit(G > 2 ? 2 : 0)>::magic_reg();
+    const uint32_t tab_addr = smem_addr(tab);
         uint32_t c = d.col0;
         const uint32_t cend = c + d.ncols;
         while (c < cend) {
@@ -350,24 +394,33 @@ __device__ __forceinline__ void gemv_tile_columns(const GemvArgs &a, const TileD
                             xv[s][(q * 4 + 2) % BT] = v.z; xv[s][(q * 4 + 3) % BT] = v.w;
                         }
                     }
-                    const uint32_t e = rans_step(tab, x, mask, p, F::kBiasMask);
                     if (KIND == EOQ_B200_KIND_INT4_ABSMAX) {
+                        using F0 = Int4Field<F::field_bit(0)>;
+                        using F1 = Int4Field<F::field_bit(G > 1 ? 1 : 0)>;
+                        using F2 = Int4Field<F::field_bit(G > 2 ? 2 : 0)>;
+                        constexpr uint32_t kM1 = (G > 1) ? F1::kMask : 0u, kM2 = (G > 2) ? F2::kMask : 0u;
+                        uint32_t u0, u1, u2;
+                        rans_step_int4<F0::kMask, kM1, kM2>(tab_addr, x, mask, p, F::kBiasMask, magic0, magic1, magic2, u0, u1, u2);
                         {
-                            const float m = Int4Field<F::field_bit(0)>::value(e);
+                            float m = __uint_as_float(u0);
+                            if (F0::kPreSubtract) m -= F0::kBase + 7.0f;
 #pragma unroll
                             for (int b = 0; b < BT; b++) acc[0][b] = fmaf(m, xv[s][b], acc[0][b]);
                         }
                         if (G > 1) {
-                            const float m = Int4Field<F::field_bit(G > 1 ? 1 : 0)>::value(e);
+                            float m = __uint_as_float(u1);
+                            if (F1::kPreSubtract) m -= F1::kBase + 7.0f;
 #pragma unroll
                             for (int b = 0; b < BT; b++) acc[G > 1 ? 1 : 0][b] = fmaf(m, xv[s][b], acc[G > 1 ? 1 : 0][b]);
                         }
                         if (G > 2) {
-                            const float m = Int4Field<F::field_bit(G > 2 ? 2 : 0)>::value(e);
+                            float m = __uint_as_float(u2);
+                            if (F2::kPreSubtract) m -= F2::kBase + 7.0f;
 #pragma unroll
                             for (int b = 0; b < BT; b++) acc[G > 2 ? 2 : 0][b] = fmaf(m, xv[s][b], acc[G > 2 ? 2 : 0][b]);
                         }
                     } else {
+                        const uint32_t e = rans_step(tab, x, mask, p, F::kBiasMask);
 #pragma unroll
                         for (int j = 0; j < G; j++) {
                             const uint32_t code = (e >> F::field_bit(j)) & F::kFieldMask;
@@ -404,21 +457,43 @@ __device__ __forceinline__ void gemv_tile_columns(const GemvArgs &a, const TileD
 
 }
 
-template <int G, int BITS, int BT, int KIND>
-__global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs a)
+template <int G, int BITS, int BT, int KIND, int THREADS>
+__global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a)
 {
+    constexpr int kThreads = THREADS, kWarps = THREADS / 32;
     using F = Fmt<G, BITS>;
     extern __shared__ __align__(16) uint8_t smem[];
     uint32_t *tab = reinterpret_cast<uint32_t *>(smem);
-    float *xs = reinterpret_cast<float *>(smem + smem_table_bytes(a.p));
+    float *xs = reinterpret_cast<float *>(smem + smem_table_bytes(a.p) + 16);
     float *aux = xs + (size_t)a.K * BT;   // INT4: [K/16][BT] sums; polar: [32][32] centroids
     uint8_t *ring_area = reinterpret_cast<uint8_t *>(aux + (KIND == EOQ_B200_KIND_Q5_POLAR ? 32 * 32 : (size_t)(a.K / 16) * BT));
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t K = a.K, M = 1u << a.p;
+    EOQ_STAMP(0);
+    // Prologue: everything that has to come from global memory is requested before anything is waited for --
+    // the decode table (one bulk copy onto a barrier), x (vector loads into registers) and this warp's first tile
+    // (descriptor, L2 prefetch, first ring chunks) -- so the prologue costs about one memory round trip.
+    const uint32_t tab_bar = smem_addr(smem + smem_table_bytes(a.p));
+    if (tid == 0) {
+        mbar_init(tab_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_expect_tx(tab_bar, 4u << a.p);
+        for (uint32_t off = 0; off < (4u << a.p); off += 16384u)
+            bulk_copy_g2s(smem_addr(tab) + off, reinterpret_cast<const uint8_t *>(a.table) + off, min(16384u, (4u << a.p) - off), tab_bar);
+    }
+    const bool x_vec = a.x_dtype != EOQ_B200_F32 && K % 16 == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0;
+    const uint32_t vec_per_row = K / 8, nvec = vec_per_row * a.batch;
+    constexpr int kXV = 3;                       // 16-byte x loads in flight per thread
+    uint4 xq[kXV];
+    if (x_vec) {
+#pragma unroll
+        for (int u = 0; u < kXV; u++)
+            if (tid + u * kThreads < nvec) xq[u] = __ldg(reinterpret_cast<const uint4 *>(a.x) + tid + u * kThreads);
+    }
+
     RingCtl ring;
     ring_setup(ring, ring_area, warp, kWarps, lane, a.status);
-    // this warp's first tile starts streaming before the table and x are staged
     uint32_t t = blockIdx.x + gridDim.x * warp;
     bool have = t < a.ntiles;
     TileDesc d;
@@ -426,16 +501,69 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs 
         d = a.tiles[t];
         tile_open(ring, d, a.stream + ((size_t)d.off64 << 6), lane);
     }
+    EOQ_STAMP(6);
 
-    for (uint32_t i = tid * 4; i < M; i += kThreads * 4)
-        *reinterpret_cast<uint4 *>(tab + i) = __ldg(reinterpret_cast<const uint4 *>(a.table + i));
-    for (uint32_t i = tid; i < K * BT; i += kThreads) {
-        const uint32_t c = i / BT, b = i % BT;
-        xs[i] = b < a.batch ? load_x(a.x, (size_t)b * K + c, a.x_dtype) : 0.0f;
+    if (x_vec) {
+        // 8 columns per vector: convert, store as fp32 [K][BT], and (INT4) add up 16-column sums with the neighbour lane
+        for (uint32_t v0 = 0; v0 < nvec; v0 += kThreads * kXV) {
+            if (v0 > 0) {
+#pragma unroll
+                for (int u = 0; u < kXV; u++)
+                    if (v0 + tid + u * kThreads < nvec) xq[u] = __ldg(reinterpret_cast<const uint4 *>(a.x) + v0 + tid + u * kThreads);
+            }
+#pragma unroll
+            for (int u = 0; u < kXV; u++) {
+                const uint32_t v = v0 + tid + u * kThreads;
+                const bool on = v < nvec;
+                const uint32_t b = on ? v / vec_per_row : 0, c0 = on ? (v % vec_per_row) * 8 : 0;
+                const uint32_t wds[4] = {xq[u].x, xq[u].y, xq[u].z, xq[u].w};
+                float sum = 0.0f;
+#pragma unroll
+                for (int h = 0; h < 4; h++) {
+                    float lo, hi;
+                    if (a.x_dtype == EOQ_B200_F16) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&wds[h]));
+                        lo = f.x; hi = f.y;
+                    } else {
+                        lo = __uint_as_float(wds[h] << 16); hi = __uint_as_float(wds[h] & 0xFFFF0000u);
+                    }
+                    if (on) {
+                        xs[(c0 + 2 * h) * BT + b] = lo;
+                        xs[(c0 + 2 * h + 1) * BT + b] = hi;
+                        sum += lo + hi;
+                    }
+                }
+                if (KIND == EOQ_B200_KIND_INT4_ABSMAX) {
+                    // vectors v and v^1 are the two halves of one 16-column unit (same row: K is a multiple of 16)
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                    if (on && (v & 1u) == 0) aux[(c0 / 16) * BT + b] = sum;
+                }
+            }
+        }
+        if (BT > 1) {
+            for (uint32_t i = tid; i < K * BT; i += kThreads)
+                if (i % BT >= a.batch) xs[i] = 0.0f;
+            if (KIND == EOQ_B200_KIND_INT4_ABSMAX)
+                for (uint32_t i = tid; i < K / 16 * BT; i += kThreads)
+                    if (i % BT >= a.batch) aux[i] = 0.0f;
+        }
+    } else {
+        for (uint32_t i0 = tid; i0 < K * BT; i0 += kThreads * 8) {      // eight independent loads in flight per thread
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const uint32_t i = i0 + u * kThreads, c = i / BT, b = i % BT;
+                v[u] = (i < K * BT && b < a.batch) ? load_x(a.x, (size_t)b * K + c, a.x_dtype) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                if (i0 + u * kThreads < K * BT) xs[i0 + u * kThreads] = v[u];
+        }
     }
     if (KIND == EOQ_B200_KIND_Q5_POLAR)
         for (uint32_t i = tid; i < 32 * 32; i += kThreads) aux[i] = __ldg(a.centroids + (i >> 5));
     __syncthreads();
+    EOQ_STAMP(7);
     if (KIND == EOQ_B200_KIND_Q5_POLAR) {
         // x'' = H64 x / 64 per 64-column block (unnormalised Sylvester butterflies), so that
         // W_block . x_block = norm * sum_j centroid[code_j] * x''_j   (core/polar_quant.py:242-262)
@@ -444,30 +572,33 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs 
                 const uint32_t b = q % BT, pr = q / BT;
                 const uint32_t c = 2 * (pr - (pr % h)) + (pr % h);
                 const float u = xs[c * BT + b], v = xs[(c + h) * BT + b];
-                const float s = h == 32 ? 1.0f / 64.0f : 1.0f;
-                xs[c * BT + b] = (u + v) * s;
-                xs[(c + h) * BT + b] = (u - v) * s;
+                const float sc = h == 32 ? 1.0f / 64.0f : 1.0f;
+                xs[c * BT + b] = (u + v) * sc;
+                xs[(c + h) * BT + b] = (u - v) * sc;
             }
             __syncthreads();
         }
-    } else {
+    } else if (!x_vec) {
         for (uint32_t i = tid; i < K / 16 * BT; i += kThreads) {
             const uint32_t u = i / BT, b = i % BT;
-            float s = 0.0f;
+            float sm = 0.0f;
 #pragma unroll
-            for (int k = 0; k < 16; k++) s += xs[(u * 16 + k) * BT + b];
-            aux[i] = s;
+            for (int k = 0; k < 16; k++) sm += xs[(u * 16 + k) * BT + b];
+            aux[i] = sm;
         }
         __syncthreads();
     }
 
+    mbar_wait_bounded(tab_bar, 0u, a.status);
     const uint32_t mask = M - 1u, p = a.p;
     const uint32_t sgroups = K / a.group;
+    EOQ_STAMP(1);
     while (have) {
         const TileDesc cur = d;
         uint32_t x;
         WordState ws;
         const bool ring_mode = tile_begin(ring, ws, cur, a.stream + ((size_t)cur.off64 << 6), lane, x);
+        EOQ_STAMP(2);
         const uint32_t row = cur.row0 + lane * G;
         const uint32_t rb = cur.row0 / (32u * G);
         const uint32_t seg = cur.seg & ~kTileDirectFlag;
@@ -481,6 +612,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs 
         if (ring_mode) gemv_tile_columns<G, BITS, BT, KIND, true>(a, cur, tab, xs, aux, lane, row, mask, p, sgroups, x, ws, ring, y);
         else gemv_tile_columns<G, BITS, BT, KIND, false>(a, cur, tab, xs, aux, lane, row, mask, p, sgroups, x, ws, ring, y);
         tile_end(ring, ring_mode);
+        EOQ_STAMP(3);
 
         // the next tile's copies start now and overlap the write-back of this one
         t += gridDim.x * kWarps;
@@ -502,12 +634,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs 
             uint32_t ticket = 0;
             if (lane == 0) ticket = atomicAdd(a.counters + rb, 1u);
             ticket = __shfl_sync(0xffffffffu, ticket, 0);
+            EOQ_STAMP(4);
             write_out = ticket == a.nseg - 1;
             if (write_out) {
                 // last warp of the row block: add the segments' partial sums, always in segment order;
                 // loads are issued kU segments at a time so their latencies overlap
                 __threadfence();
-                constexpr int kU = G * BT <= 3 ? 8 : G * BT <= 6 ? 4 : G * BT <= 12 ? 2 : 1;
+                constexpr int kU = G * BT <= 3 ? 16 : G * BT <= 6 ? 8 : G * BT <= 12 ? 4 : 2;
 #pragma unroll
                 for (int j = 0; j < G; j++)
 #pragma unroll
@@ -546,6 +679,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs 
                 }
             }
         }
+        EOQ_STAMP(5);
     }
 }
 
@@ -554,14 +688,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_tiles_kernel(const GemvArgs 
 static std::atomic<int> g_gemv_ctas_per_sm{0};   // 0 = as many as fit
 void set_gemv_ctas_per_sm(int v) { g_gemv_ctas_per_sm.store(v < 0 ? 0 : v); }
 
-template <int G, int BITS, int BT, int KIND>
-static int launch_gemv_one(const GemvArgs &a, cudaStream_t st)
+static std::atomic<int> g_gemv_threads{0};       // 0 = choose; otherwise 512 or 1024
+void set_gemv_threads(int v) { g_gemv_threads.store(v); }
+
+template <int G, int BITS, int BT, int KIND, int THREADS>
+static int launch_gemv_cfg(const GemvArgs &a, cudaStream_t st)
 {
     struct Cfg { size_t smem = 0; int per_sm = 0, sms = 0; };
     static Cfg cfg[16];
     static std::mutex mu;
-    auto kern = gemv_tiles_kernel<G, BITS, BT, KIND>;
-    const size_t smem = gemv_smem_bytes(a.K, a.p, BT, KIND);
+    auto kern = gemv_tiles_kernel<G, BITS, BT, KIND, THREADS>;
+    const size_t smem = gemv_smem_bytes_for(a.K, a.p, BT, KIND, THREADS);
     if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -574,7 +711,7 @@ static int launch_gemv_one(const GemvArgs &a, cudaStream_t st)
             e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
             int per_sm = 0;
-            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem);
+            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, smem);
             if (e != cudaSuccess) return (int)e;
             if (per_sm < 1) return (int)cudaErrorLaunchOutOfResources;
             slot.smem = smem; slot.per_sm = per_sm; slot.sms = device_sm_count();
@@ -586,9 +723,21 @@ static int launch_gemv_one(const GemvArgs &a, cudaStream_t st)
     if (want > 0) per_sm = std::min(per_sm, want);
     uint32_t grid = (uint32_t)(c.sms * per_sm);
     grid = max(1u, min(grid, a.ntiles));
-    kern<<<grid, kThreads, smem, st>>>(a);
+    kern<<<grid, THREADS, smem, st>>>(a);
     g_launches++;
     return (int)cudaGetLastError();
+}
+
+// 32 warps per SM hide the step's dependency chain better than 16; they are used when their rings and
+// the table fit shared memory beside x and the tile count gives every warp work.
+template <int G, int BITS, int BT, int KIND>
+static int launch_gemv_one(const GemvArgs &a, cudaStream_t st)
+{
+    const int forced = g_gemv_threads.load();
+    const bool fits = gemv_smem_bytes_for(a.K, a.p, BT, KIND, 1024) <= 227 * 1024;
+    const bool enough = a.ntiles > (uint32_t)device_sm_count() * 16u;
+    if (BT <= 2 && fits && (forced == 1024 || (forced == 0 && enough))) return launch_gemv_cfg<G, BITS, BT <= 2 ? BT : 1, KIND, 1024>(a, st);
+    return launch_gemv_cfg<G, BITS, BT, KIND, 512>(a, st);
 }
 
 template <int G, int BITS, int KIND>

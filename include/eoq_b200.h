@@ -324,7 +324,8 @@ eoq_error_t eoq_b200_dequant_packed(const uint8_t *d_packed, const uint16_t *d_s
 eoq_error_t eoq_b200_weight_status(eoq_b200_weight_t *w, void *stream);
 
 /* Diagnostic knob for sweeps; returns 0 if the key is known.  Keys:
- * "gemv_ctas_per_sm" (0 = as many CTAs of the fused kernel as fit on an SM). */
+ * "gemv_ctas_per_sm" (0 = as many CTAs of the fused kernel as fit on an SM),
+ * "gemv_threads" (0 = choose, 512 or 1024 threads per CTA of the fused kernel). */
 int eoq_b200_tune(const char *key, int value);
 
 /* Number of kernels launched by this library since load (for benchmarks). */
