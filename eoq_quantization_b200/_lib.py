@@ -98,7 +98,7 @@ class TilesView(C.Structure):
                 ("kind", C.c_uint32), ("bits", C.c_uint32), ("symbols_per_step", C.c_uint32),
                 ("precision_bits", C.c_uint32), ("num_tiles", C.c_uint32), ("num_col_segments", C.c_uint32),
                 ("table", C.POINTER(C.c_uint32)), ("tiles", C.POINTER(C.c_uint32)), ("stream", C.POINTER(C.c_uint8)),
-                ("stream_bytes", C.c_uint64)]
+                ("stream_bytes", C.c_uint64), ("max_lane_drift", C.c_uint32)]
 
 
 _LIB: Optional[C.CDLL] = None

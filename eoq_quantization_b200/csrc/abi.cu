@@ -605,6 +605,7 @@ extern "C" eoq_error_t eoq_b200_tiles_view(const eoq_b200_tiles_t *t, eoq_b200_t
     v->tiles = reinterpret_cast<const eoq_b200_tile_desc_t *>(tw.tiles.data());
     v->stream = tw.stream.data();
     v->stream_bytes = tw.stream.size();
+    v->max_lane_drift = tw.max_drift;
     return EOQ_OK;
 }
 
@@ -786,7 +787,6 @@ extern "C" int eoq_b200_tune(const char *key, int value)
 {
     if (!key) return -1;
     if (std::strcmp(key, "gemv_ctas_per_sm") == 0) { set_gemv_ctas_per_sm(value); return 0; }
-    if (std::strcmp(key, "gemv_threads") == 0) { if (value != 0 && value != 512 && value != 1024) return -1; set_gemv_threads(value); return 0; }
     return -1;
 }
 

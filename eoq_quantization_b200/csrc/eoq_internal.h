@@ -41,7 +41,7 @@ struct TileDesc {
 };
 
 constexpr uint32_t kMaxFreq = 511;
-constexpr uint32_t kMaxRingDrift = 39;           // rows the lanes of a ring-mode tile may be apart at any step
+constexpr uint32_t kMaxRingDrift = 31;           // rows the lanes of a ring-mode tile may be apart at any step
 constexpr uint32_t kTileDirectFlag = 0x80000000u; // set in TileDesc::seg when the tile breaks that bound
 constexpr uint32_t kColGranule = 16;   // tile column boundaries are multiples of this
 
@@ -49,6 +49,7 @@ struct TiledWeights {
     uint32_t N = 0, K = 0, Npad = 0, G = 0, bits = 0, p = 0, group = 0, kind = 0;
     uint32_t alphabet = 0;       // (1 << bits*G) slots in the joint symbol space
     uint32_t nrb = 0, nseg = 0;
+    uint32_t max_drift = 0;      // largest distance (rows) between lanes' read positions in any tile
     std::vector<uint32_t> table;     // 1 << p entries
     std::vector<TileDesc> tiles;     // nrb * nseg
     std::vector<uint32_t> seg_start; // nseg + 1 column boundaries
@@ -125,6 +126,5 @@ int launch_dequant_packed(const uint8_t *packed, const uint16_t *scales, uint32_
 size_t gemv_smem_bytes(uint32_t K, uint32_t p, uint32_t bt, uint32_t kind);
 uint64_t launch_counter();
 void set_gemv_ctas_per_sm(int v);
-void set_gemv_threads(int v);
 
 }  // namespace eoq

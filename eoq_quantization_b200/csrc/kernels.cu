@@ -109,8 +109,16 @@ __device__ __forceinline__ void store_y(void *p, size_t i, float v, int dtype)
 
 __device__ __forceinline__ float half_bits_to_float(uint16_t h) { return __half2float(__ushort_as_half(h)); }
 
+// A read-only global load that stays where it is written (volatile asm), for prefetching into registers.
+__device__ __forceinline__ uint16_t ldg_u16_pinned(const uint16_t *p)
+{
+    uint16_t v;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+
 // Geometry of the per-warp word ring (see "Streaming a tile's renormalisation words" below).
-constexpr uint32_t kRingRows = 64, kChunkRows = 16, kRingChunks = kRingRows / kChunkRows, kSyncSteps = 8;
+constexpr uint32_t kRingRows = 64, kChunkRows = 16, kRingChunks = kRingRows / kChunkRows, kSyncSteps = 16;
 constexpr uint32_t kRingBytes = kRingRows * 64, kChunkBytes = kChunkRows * 64;
 static_assert(kMaxRingDrift + kSyncSteps + 1 + kChunkRows <= kRingRows, "ring too small for the drift bound");
 
@@ -206,6 +214,7 @@ struct WordState {            // per lane
     uint32_t w;               // the lane's next unread word
     const uint16_t *ptr;      // direct mode: where w came from
     uint32_t koff, ring_lane; // ring mode: see above; ring_lane = shared address of the ring | lane*2
+    uint32_t c64, c1;         // the constants 64 and 1 in registers the compiler cannot see through
 };
 
 struct RingCtl {              // per warp (all fields warp-uniform)
@@ -290,6 +299,7 @@ __device__ __forceinline__ bool tile_begin(RingCtl &r, WordState &s, const TileD
         const uint32_t start = r.tile_first * kChunkBytes;
         s.koff = start + 128;                                   // word row 0 sits behind the two header rows
         s.ring_lane = r.ring_base | (lane * 2);
+        asm volatile("mov.b32 %0, 64;\n\tmov.b32 %1, 1;" : "=r"(s.c64), "=r"(s.c1));
         ring_sync(r, s, lane);
         x = lds_u32(r.ring_base + (start & (kRingBytes - 1)) + lane * 4);
         s.w = lds_u16((s.koff & (kRingBytes - 1)) | s.ring_lane);
@@ -319,11 +329,11 @@ __device__ __forceinline__ void rans_renorm(uint32_t &x, WordState &s)
         asm volatile("{\n\t.reg .pred p;\n\t.reg .b32 t;\n\t"
                      "setp.lt.u32 p, %0, 65536;\n\t"
                      "@p mad.lo.u32 %0, %0, 65536, %1;\n\t"
-                     "@p add.u32 %2, %2, 64;\n\t"
+                     "@p mad.lo.u32 %2, %5, %6, %2;\n\t"     // koff += 64 as a multiply-add: keeps it off the ALU pipe
                      "@p lop3.b32 t, %2, %4, %3, 0xEA;\n\t"
                      "@p ld.shared.u16 %1, [t];\n\t}"
                      : "+r"(x), "+r"(s.w), "+r"(s.koff)
-                     : "r"(s.ring_lane), "n"(kRingBytes - 1));
+                     : "r"(s.ring_lane), "n"(kRingBytes - 1), "r"(s.c64), "r"(s.c1));
     } else if (x < 65536u) {
         x = (x << 16) | s.w;
         s.ptr += 32;
@@ -345,7 +355,7 @@ __device__ __forceinline__ void rans_renorm(uint32_t &x, WordState &s)
 // not depend on scheduling.
 // ---------------------------------------------------------------------------
 // The column loop of one tile: decode, unpack, multiply-accumulate, fold per scale group.
-template <int G, int BITS, int BT, int KIND, bool RING>
+template <int G, int BITS, int BT, int KIND, bool RING, int UNROLL>
 __device__ __forceinline__ void gemv_tile_columns(const GemvArgs &a, const TileDesc &d, const uint32_t *tab, const float *xs,
                                                   const float *aux, uint32_t lane, uint32_t row, uint32_t mask, uint32_t p,
                                                   uint32_t sgroups, uint32_t &x, WordState &ws, RingCtl &ring, float (&y)[G][BT])
@@ -357,23 +367,31 @@ __device__ __forceinline__ void gemv_tile_columns(const GemvArgs &a, const TileD
     const uint32_t tab_addr = smem_addr(tab);
         uint32_t c = d.col0;
         const uint32_t cend = c + d.ncols;
+        // The group scales are fetched one run ahead with loads the compiler may not move: left to itself it
+        // sinks them to their use at the end of the run, where each costs a full memory round trip.
+        uint16_t sc_next[G];
+#pragma unroll
+        for (int j = 0; j < G; j++) sc_next[j] = ldg_u16_pinned(a.scales + (size_t)min(row + j, a.N - 1) * sgroups + c / a.group);
         while (c < cend) {
             const uint32_t g = c / a.group;
             const uint32_t rstart = c, rend = min(cend, (g + 1) * a.group);
-            float sc[G];
+            uint16_t sc_bits[G];
 #pragma unroll
-            for (int j = 0; j < G; j++)
-                sc[j] = row + j < a.N ? half_bits_to_float(__ldg(a.scales + (size_t)(row + j) * sgroups + g)) : 0.0f;
+            for (int j = 0; j < G; j++) sc_bits[j] = sc_next[j];
+            if (rend < cend) {
+#pragma unroll
+                for (int j = 0; j < G; j++) sc_next[j] = ldg_u16_pinned(a.scales + (size_t)min(row + j, a.N - 1) * sgroups + g + 1);
+            }
             float acc[G][BT];
 #pragma unroll
             for (int j = 0; j < G; j++)
 #pragma unroll
                 for (int b = 0; b < BT; b++) acc[j][b] = 0.0f;
 
-#pragma unroll 2
+#pragma unroll UNROLL
             for (; c < rend; c += 4) {
-                // runs start on multiples of 16 columns, so this fires every kSyncSteps = 8 steps
-                if (RING && (c & 4u) == 0) ring_sync(ring, ws, lane);
+                // runs start on multiples of 16 columns, so this fires every kSyncSteps = 16 steps
+                if (RING && (c & 12u) == 0) ring_sync(ring, ws, lane);
                 float xv[4][BT];
                 if (BT == 1) {
                     const float4 v = *reinterpret_cast<const float4 *>(xs + c);
@@ -433,6 +451,9 @@ __device__ __forceinline__ void gemv_tile_columns(const GemvArgs &a, const TileD
                 }
             }
 
+            float sc[G];
+#pragma unroll
+            for (int j = 0; j < G; j++) sc[j] = row + j < a.N ? half_bits_to_float(sc_bits[j]) : 0.0f;
             if (KIND == EOQ_B200_KIND_INT4_ABSMAX) {
                 float rs[BT];
 #pragma unroll
@@ -461,6 +482,7 @@ template <int G, int BITS, int BT, int KIND, int THREADS>
 __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a)
 {
     constexpr int kThreads = THREADS, kWarps = THREADS / 32;
+    constexpr int kUnroll = THREADS <= 512 ? 4 : THREADS <= 768 ? 2 : 1;   // fewer registers per thread as the CTA grows
     using F = Fmt<G, BITS>;
     extern __shared__ __align__(16) uint8_t smem[];
     uint32_t *tab = reinterpret_cast<uint32_t *>(smem);
@@ -609,8 +631,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
 #pragma unroll
             for (int b = 0; b < BT; b++) y[j][b] = 0.0f;
 
-        if (ring_mode) gemv_tile_columns<G, BITS, BT, KIND, true>(a, cur, tab, xs, aux, lane, row, mask, p, sgroups, x, ws, ring, y);
-        else gemv_tile_columns<G, BITS, BT, KIND, false>(a, cur, tab, xs, aux, lane, row, mask, p, sgroups, x, ws, ring, y);
+        if (ring_mode) gemv_tile_columns<G, BITS, BT, KIND, true, kUnroll>(a, cur, tab, xs, aux, lane, row, mask, p, sgroups, x, ws, ring, y);
+        else gemv_tile_columns<G, BITS, BT, KIND, false, 1>(a, cur, tab, xs, aux, lane, row, mask, p, sgroups, x, ws, ring, y);
         tile_end(ring, ring_mode);
         EOQ_STAMP(3);
 
@@ -688,9 +710,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
 static std::atomic<int> g_gemv_ctas_per_sm{0};   // 0 = as many as fit
 void set_gemv_ctas_per_sm(int v) { g_gemv_ctas_per_sm.store(v < 0 ? 0 : v); }
 
-static std::atomic<int> g_gemv_threads{0};       // 0 = choose; otherwise 512 or 1024
-void set_gemv_threads(int v) { g_gemv_threads.store(v); }
-
 template <int G, int BITS, int BT, int KIND, int THREADS>
 static int launch_gemv_cfg(const GemvArgs &a, cudaStream_t st)
 {
@@ -728,16 +747,13 @@ static int launch_gemv_cfg(const GemvArgs &a, cudaStream_t st)
     return (int)cudaGetLastError();
 }
 
-// 32 warps per SM hide the step's dependency chain better than 16; they are used when their rings and
-// the table fit shared memory beside x and the tile count gives every warp work.
+// 16 warps per CTA, one CTA per SM.  CTAs of 24 and 32 warps (with proportionally more, shorter tiles) were
+// measured and are no faster: the step rate is bounded by the SM's shared-memory and ALU pipes, not by the
+// number of resident warps, and shorter tiles pay the per-tile costs more often.
 template <int G, int BITS, int BT, int KIND>
 static int launch_gemv_one(const GemvArgs &a, cudaStream_t st)
 {
-    const int forced = g_gemv_threads.load();
-    const bool fits = gemv_smem_bytes_for(a.K, a.p, BT, KIND, 1024) <= 227 * 1024;
-    const bool enough = a.ntiles > (uint32_t)device_sm_count() * 16u;
-    if (BT <= 2 && fits && (forced == 1024 || (forced == 0 && enough))) return launch_gemv_cfg<G, BITS, BT <= 2 ? BT : 1, KIND, 1024>(a, st);
-    return launch_gemv_cfg<G, BITS, BT, KIND, 512>(a, st);
+    return launch_gemv_cfg<G, BITS, BT, KIND, kThreads>(a, st);
 }
 
 template <int G, int BITS, int KIND>
@@ -798,7 +814,7 @@ __global__ void __launch_bounds__(256) decode_tiles_kernel(const DecodeArgs a)
             if (ring_mode) {
 #pragma unroll
                 for (int s = 0; s < 8; s++) {
-                    if (s % kSyncSteps == 0) ring_sync(ring, ws, lane);
+                    if (s == 0 && ((c - d.col0) & 8u) == 0) ring_sync(ring, ws, lane);
                     const uint32_t e = rans_step(tab, x, mask, p, F::kBiasMask);
 #pragma unroll
                     for (int j = 0; j < G; j++) sym[j][s] = (e >> F::field_bit(j)) & F::kFieldMask;

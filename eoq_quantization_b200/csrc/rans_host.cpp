@@ -218,6 +218,7 @@ eoq_error_t build_tiled(const uint8_t *symbols, uint32_t N, uint32_t K, uint32_t
     const size_t ntiles = (size_t)nrb * nseg;
     out.tiles.resize(ntiles);
     std::vector<std::vector<uint8_t>> tile_bytes(ntiles);
+    std::vector<uint32_t> tile_drift(ntiles, 0);
     parallel_for(ntiles, [&](size_t t) {
         const uint32_t rb = (uint32_t)(t / nseg), seg = (uint32_t)(t % nseg);
         const uint32_t col0 = out.seg_start[seg], ncols = out.seg_start[seg + 1] - col0;
@@ -257,10 +258,12 @@ eoq_error_t build_tiled(const uint8_t *symbols, uint32_t N, uint32_t K, uint32_t
             }
             drift = std::max(drift, hi - lo);
         }
+        tile_drift[t] = drift;
         TileDesc d;
         d.row0 = rb * rows_per_tile; d.col0 = col0; d.ncols = ncols; d.seg = seg | (drift > kMaxRingDrift ? kTileDirectFlag : 0u); d.off64 = 0; d.len64 = (uint32_t)(tb.size() >> 6);
         out.tiles[t] = d;
     });
+    for (uint32_t v : tile_drift) out.max_drift = std::max(out.max_drift, v);
     size_t total = 0;
     for (size_t t = 0; t < ntiles; t++) {
         if ((total >> 6) > 0xFFFFFFFFull) return EOQ_ERR_OVERFLOW;

@@ -233,6 +233,7 @@ typedef struct {
     const eoq_b200_tile_desc_t *tiles;
     const uint8_t *stream;
     uint64_t stream_bytes;
+    uint32_t max_lane_drift;             /* largest gap, in word rows, between two lanes' read positions in any tile */
 } eoq_b200_tiles_view_t;
 eoq_error_t eoq_b200_tiles_build(const uint8_t *symbols, const eoq_b200_weight_opts_t *opts, eoq_b200_tiles_t **out);
 eoq_error_t eoq_b200_tiles_view(const eoq_b200_tiles_t *t, eoq_b200_tiles_view_t *view);
@@ -324,8 +325,7 @@ eoq_error_t eoq_b200_dequant_packed(const uint8_t *d_packed, const uint16_t *d_s
 eoq_error_t eoq_b200_weight_status(eoq_b200_weight_t *w, void *stream);
 
 /* Diagnostic knob for sweeps; returns 0 if the key is known.  Keys:
- * "gemv_ctas_per_sm" (0 = as many CTAs of the fused kernel as fit on an SM),
- * "gemv_threads" (0 = choose, 512 or 1024 threads per CTA of the fused kernel). */
+ * "gemv_ctas_per_sm" (0 = as many CTAs of the fused kernel as fit on an SM). */
 int eoq_b200_tune(const char *key, int value);
 
 /* Number of kernels launched by this library since load (for benchmarks). */
