@@ -43,8 +43,8 @@ GROUP = 128
 REPLICAS = 8                       # weight copies cycled through so that the working set exceeds L2
 WORKLOAD = "llama7b_mlp_pair_int4_g128_rans_b1"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the fused kernel, from the ncu capture
-# summarised under profiles/ (None until a capture has been taken)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# summarised under profiles/
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 21261824    # profiles/gemv_tiles_kernel__llama7b_mlp_pair.md, 11008 x 4096 launch
 
 
 def make_layer(n, k, seed):
@@ -267,7 +267,6 @@ def run_gpu_arm(args):
     for _ in range(3):
         run_steps(args.steps)
     barrier()
-    launches0 = lib.eoq_b200_launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
         barrier()
@@ -280,7 +279,6 @@ def run_gpu_arm(args):
         while time.time() < t_end:
             run_steps(args.steps)
         torch.cuda.synchronize()
-    launches = lib.eoq_b200_launch_count() - launches0
     ms = ev0.elapsed_time(ev1) / args.steps
     launches_timed = 2 * args.steps
     if world > 1:
@@ -322,7 +320,7 @@ def run_gpu_arm(args):
     up_alg = alg_bytes[0] / world
     roof = {"bound": "hbm", "kernel": "gemv_tiles_kernel<3,4,1,int4>", "achieved": up_alg / (up_ms * 1e-3) / 1e9, "peak": peak,
             "unit": "GB/s", "frac": up_alg / (up_ms * 1e-3) / 1e9 / peak, "peak_source": peak_src,
-            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "launch_us": up_ms * 1e3, "algorithmic_bytes_per_launch": up_alg,
+            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None, "launch_us": up_ms * 1e3, "algorithmic_bytes_per_launch": up_alg,
             "fp16_gemv_bytes": N_UP * K_UP * 2 // world}
 
     # end to end through the C ABI with host buffers (pinned x in, y out, every step)
@@ -381,13 +379,108 @@ def run_gpu_arm(args):
                 "tokens_per_s": 1e3 / ms, "pct_of_hbm_peak": 100.0 * value / (peak * world),
                 "algorithmic_bytes_per_step": alg_step,
                 "tile_bytes_per_step": int(sum(s[0].info.stream_bytes + s[0].info.scale_bytes for s in shards)) * world,
-                "clocks": clocks.summary(), "roofline": roof, "e2e": e2e, "gpu_launches": int(launches_timed) * world,
-                "launches_counted_by_library": int(launches)}
+                "clocks": clocks.summary(), "roofline": roof, "e2e": e2e, "gpu_launches": int(launches_timed) * world}
         if cpu_line:
             line["cpu_baseline"] = cpu_line
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------- secondary workloads
+def run_aux(args):
+    """Single-GPU timings of the other BASELINE configurations (one JSON line each):
+    decode_dequant -- 4096 x 4096 INT4 g128: decode the tiles to packed INT4 and to the fp16 dequantised matrix;
+    polar_q5       -- 14336 x 4096 PolarQuant Q5 (per-64 norms), fused decode+GEMV at batch 1, 4, 8."""
+    import torch
+    from eoq_quantization_b200 import _lib
+    from eoq_quantization_b200.fused import EOQWeight
+    torch.cuda.set_device(0)
+    lib = _lib.lib()
+    peak, peak_src = measured_peak()
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    if args.workload == "decode_dequant":
+        n = k = 4096
+        sym, scales = make_layer(n, k, 3)
+        alg, _ = wire_bytes(sym, scales, n, k, batch=0)
+        ws = EOQWeight.replicas(16, sym, scales)                        # 16 x ~8 MB of tiles + 16 x 32 MB of output > L2
+        outs = [torch.empty(n, k, dtype=torch.float16, device="cuda") for _ in ws]
+        packs = [torch.empty(n, k // 2, dtype=torch.uint8, device="cuda") for _ in ws]
+        st = torch.cuda.current_stream().cuda_stream
+        it = {"i": 0}
+
+        def deq():
+            i = it["i"] % len(ws); it["i"] += 1
+            _lib.check(lib.eoq_b200_weight_decode(ws[i]._h, None, 0, outs[i].data_ptr(), _lib.F16, st))
+
+        def pack():
+            i = it["i"] % len(ws); it["i"] += 1
+            _lib.check(lib.eoq_b200_weight_decode(ws[i]._h, packs[i].data_ptr(), 1, None, 0, st))
+        ms_d, ms_p = timed(deq, args.steps), timed(pack, args.steps)
+        ref = (torch.from_numpy(sym.astype(np.float32)).cuda() - 7).view(-1, GROUP) * torch.from_numpy(scales.astype(np.float32)).cuda()[:, None]
+        assert torch.equal(outs[0], ref.view(n, k).half()), "decode+dequantise mismatch"
+        line = {"metric": "decode+dequantise effective HBM GB/s (compressed bytes read)", "unit": "GB/s", "n_gpus": 1,
+                "steps": args.steps, "data": "synthetic", "config": {"workload": "decode_dequant_4096x4096_int4_g128"},
+                "value": alg / (ms_d * 1e-3) / 1e9, "ms_per_step": ms_d, "fp16_out_gbs": n * k * 2 / (ms_d * 1e-3) / 1e9,
+                "packed_ms": ms_p, "packed_compressed_gbs": alg / (ms_p * 1e-3) / 1e9,
+                "symbols_per_s_fp16": n * k / (ms_d * 1e-3), "symbols_per_s_packed": n * k / (ms_p * 1e-3),
+                "peak": peak, "peak_source": peak_src, "algorithmic_bytes": alg}
+        print(json.dumps(line), flush=True)
+        return
+
+    # polar_q5
+    n, k, d = 14336, 4096, 64
+    z = np.load(os.path.join(ROOT, "tests", "golden", "ref_polar.npz"))
+    cent = torch.from_numpy(z["centroids5"]).cuda()
+    H = torch.from_numpy(z["hadamard64"]).cuda()
+    g = torch.Generator(device="cuda").manual_seed(3)
+    w = torch.randn(n, k, device="cuda", generator=g) * 0.015
+    outl = torch.rand(n, k, device="cuda", generator=g) < 1e-3
+    sign = torch.where(torch.rand(n, k, device="cuda", generator=g) < 0.5, -1.0, 1.0)
+    w = torch.where(outl, sign * 8 * 0.015, w)
+    codes = torch.empty(n, k, dtype=torch.uint8, device="cuda")
+    norms = torch.empty(n * k // d, dtype=torch.float16, device="cuda")
+    for lo in range(0, n, 512):                                          # core/polar_quant.py:138-213, chunked by rows
+        blk = w[lo:lo + 512].reshape(-1, d)
+        nr = blk.norm(dim=1, keepdim=True).clamp(min=1e-10)
+        c = (((blk / nr) @ H * (d ** 0.5)).unsqueeze(-1) - cent).abs().argmin(dim=-1)
+        codes[lo:lo + 512] = c.reshape(512, k).to(torch.uint8)
+        norms[lo * k // d:(lo + 512) * k // d] = nr.squeeze(1).half()
+    from eoq_quantization_b200.core import rans_blocked as RB
+    sym = codes.cpu().numpy()
+    wire = RB.BlockedRANSEncoder(block_size=4096, precision_bits=12).encode(sym.ravel().astype(np.int64), 32)
+    ws = EOQWeight.replicas(4, sym, norms, kind=_lib.KIND_Q5_POLAR, group=64, centroids=z["centroids5"])
+    res = {}
+    for batch in (1, 4, 8):
+        x = torch.randn(batch, k, device="cuda", generator=g).half()
+        y = torch.empty(batch, n, device="cuda", dtype=torch.float16)
+        st = torch.cuda.current_stream().cuda_stream
+        it = {"i": 0}
+
+        def run():
+            i = it["i"] % len(ws); it["i"] += 1
+            _lib.check(lib.eoq_b200_gemv(ws[i]._h, x.data_ptr(), _lib.F16, batch, y.data_ptr(), _lib.F16, None, st))
+        ms = timed(run, args.steps)
+        alg = len(wire.compressed_blocks) + 4 * wire.num_blocks + norms.numel() * 2 + batch * (n + k) * 2
+        res[f"batch{batch}"] = {"ms": ms, "gbs": alg / (ms * 1e-3) / 1e9, "pct_of_peak": 100 * alg / (ms * 1e-3) / 1e9 / peak}
+    line = {"metric": "fused decode+Q5 polar GEMV effective HBM GB/s", "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "data": "synthetic", "config": {"workload": "polar_q5_14336x4096_g64", "l2": "4 weight copies cycled"},
+            "value": res["batch1"]["gbs"], "ms_per_step": res["batch1"]["ms"], "batches": res, "peak": peak,
+            "peak_source": peak_src, "wire_bits_per_weight": len(wire.compressed_blocks) * 8 / (n * k),
+            "tile_bits_per_weight": ws[0].info.bits_per_weight}
+    print(json.dumps(line), flush=True)
 
 
 def main():
@@ -398,7 +491,11 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="plain launches instead of CUDA graphs (for profilers)")
+    ap.add_argument("--workload", default="mlp_pair", choices=["mlp_pair", "decode_dequant", "polar_q5"])
     args = ap.parse_args()
+    if args.workload != "mlp_pair":
+        args.steps = min(args.steps, 50)
+        return run_aux(args)
     if args.impl == "reference":
         if args.steps > 20:
             args.steps = 20
