@@ -483,6 +483,132 @@ def run_aux(args):
     print(json.dumps(line), flush=True)
 
 
+def run_llama_step(args):
+    """Llama-7B-shape decode step, random init (BASELINE config 4): 32 layers, hidden 4096, 32 heads, SwiGLU 11008,
+    vocabulary 32000, KV length 1024, batch 1.  Every linear is INT4 g128 entropy-coded and runs through the fused
+    kernel; norms, rotary embedding, attention (torch SDPA) and the activation are torch ops.  All 32 layers hold
+    their own copy of the tiles in HBM (one set of values, 32 uploads), so every byte of weight is read from DRAM.
+    With N ranks every linear is row-sharded and followed by an all-gather of the output slices.  The same step
+    with dense fp16 weights (torch matmul) is timed beside it."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from eoq_quantization_b200.fused import EOQWeight
+    from eoq_quantization_b200.tp import gather_rows, shard_rows
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    H, NH, HD, FF, V, L, KV = 4096, 32, 128, 11008, 32000, 32, 1024
+    shapes = {"qkv": (3 * H, H), "o": (H, H), "gate_up": (2 * FF, H), "down": (H, FF)}
+    layers, alg_layer = {}, 0
+    for i, (name, (n, k)) in enumerate(shapes.items()):
+        sym, scales = make_layer(n, k, 10 + i)
+        alg_layer += wire_bytes(sym, scales, n, k)[0]
+        lo, hi = shard_rows(n, world, rank)
+        layers[name] = EOQWeight.replicas(L, sym[lo:hi], scales[lo * (k // GROUP):hi * (k // GROUP)])
+    sym, scales = make_layer(V, H, 20)
+    alg_head = wire_bytes(sym, scales, V, H)[0]
+    lo, hi = shard_rows(V, world, rank)
+    head = EOQWeight.from_symbols(sym[lo:hi], scales[lo * (H // GROUP):hi * (H // GROUP)])
+    alg_step = L * alg_layer + alg_head
+
+    g = torch.Generator(device="cuda").manual_seed(5)
+    kc = [torch.randn(1, NH // world, KV, HD, device="cuda", generator=g).half() for _ in range(L)]
+    vc = [torch.randn(1, NH // world, KV, HD, device="cuda", generator=g).half() for _ in range(L)]
+    nw = torch.ones(H, device="cuda", dtype=torch.float16)
+    x0 = torch.randn(1, H, device="cuda", generator=g).half()
+
+    def norm(x):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5)).half() * nw
+
+    def linear(w, x):
+        y = w.gemv(x)
+        return gather_rows(y) if world > 1 else y
+
+    def step(x, lin):
+        for i in range(L):
+            h = norm(x)
+            qkv = lin("qkv", i, h)
+            q, k, v = qkv.view(1, 3, NH, HD).unbind(1)
+            hs = NH // world                                       # attention is sharded by heads
+            qs = q[:, rank * hs:(rank + 1) * hs].transpose(0, 1).reshape(1, hs, 1, HD)
+            att = F.scaled_dot_product_attention(qs, kc[i], vc[i])  # new k/v of this token would be appended here
+            att = att.reshape(1, hs * HD)
+            if world > 1:
+                att = gather_rows(att)
+            x = x + lin("o", i, att)
+            h = norm(x)
+            gu = lin("gate_up", i, h)
+            x = x + lin("down", i, F.silu(gu[:, :FF]) * gu[:, FF:])
+        return lin("head", 0, norm(x))
+
+    def lin_eoq(name, i, x):
+        return linear(head if name == "head" else layers[name][i], x)
+
+    def timed(fn, steps):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph, mode = torch.cuda.CUDAGraph(), "cuda-graph"
+        try:
+            with torch.cuda.graph(graph):
+                fn()
+            run = graph.replay
+        except Exception as exc:                               # pragma: no cover
+            run, mode = fn, f"eager ({type(exc).__name__})"
+        for _ in range(3):
+            run()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, mode
+
+    steps = min(args.steps, 50)
+    ms, mode = timed(lambda: step(x0, lin_eoq), steps)
+    line = {"metric": "Llama-7B-shape decode step, tokens/s at batch 1", "unit": "tokens/s", "value": 1e3 / ms,
+            "ms_per_step": ms, "n_gpus": world, "steps": steps, "data": "synthetic", "scaling": "strong",
+            "config": {"workload": "llama7b_decode_step_int4_g128_rans", "layers": L, "hidden": H, "kv_len": KV,
+                       "launch": mode, "parallelism": f"row-sharded tp{world}"},
+            "algorithmic_weight_bytes_per_step": alg_step, "weight_gbs": alg_step / (ms * 1e-3) / 1e9}
+    if world == 1 and not args.no_cpu_baseline:
+        # dense fp16 comparator: same step, weights as fp16 matrices (one copy per layer)
+        del layers
+        torch.cuda.empty_cache()
+        dense = {n_: [torch.randn(s_[0], s_[1], device="cuda", dtype=torch.float16) * 0.02 for _ in range(L)] for n_, s_ in shapes.items()}
+        dhead = torch.randn(V, H, device="cuda", dtype=torch.float16) * 0.02
+
+        def lin_f16(name, i, x):
+            return x @ (dhead if name == "head" else dense[name][i]).T
+        ms16, _ = timed(lambda: step(x0, lin_f16), steps)
+        line["fp16_dense_ms_per_step"] = ms16
+        line["fp16_dense_tokens_per_s"] = 1e3 / ms16
+        line["speedup_vs_fp16_dense"] = ms16 / ms
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -491,8 +617,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="plain launches instead of CUDA graphs (for profilers)")
-    ap.add_argument("--workload", default="mlp_pair", choices=["mlp_pair", "decode_dequant", "polar_q5"])
+    ap.add_argument("--workload", default="mlp_pair", choices=["mlp_pair", "decode_dequant", "polar_q5", "llama7b_step"])
     args = ap.parse_args()
+    if args.workload == "llama7b_step":
+        return run_llama_step(args)
     if args.workload != "mlp_pair":
         args.steps = min(args.steps, 50)
         return run_aux(args)

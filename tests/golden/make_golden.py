@@ -194,7 +194,28 @@ def polar():
     print("ref_polar: codes", r.codes.shape)
 
 
+def eoq_container():
+    """A small .eoq file written by the reference's own writer (core/eoq_format.py:117-184)."""
+    from core import eoq as E
+    from core import eoq_format as EF
+    torch.manual_seed(21)
+    comp = E.EOQCompressor(E.EOQConfig(bits=4, block_size=128, rans_block_size=256, precision_bits=14))
+    model = E.EOQCompressedModel(config=comp.config, metadata={"model_name": "synthetic"})
+    tensors = {"layers.0.mlp.up.weight": torch.randn(48, 256) * 0.02,
+               "layers.0.mlp.down.weight": torch.randn(32, 384) * 0.02,
+               "layers.0.norm.weight": torch.randn(100) * 0.1 + 1.0,
+               "embed.weight": torch.randn(10, 30) * 0.02}
+    for name, t in tensors.items():
+        model.tensors[name] = comp.compress_tensor(name, t)
+    path = os.path.join(OUT, "sample.eoq")
+    EF.save_eoq(model, path)
+    back = E.EOQDecompressor().decompress_model(EF.load_eoq(path))
+    np.savez_compressed(os.path.join(OUT, "ref_eoq_file.npz"), **{k: v.numpy() for k, v in back.items()})
+    print("sample.eoq:", os.path.getsize(path), "bytes,", list(tensors))
+
+
 if __name__ == "__main__":
+    eoq_container()
     xval_vectors()
     normalisation()
     blocked()

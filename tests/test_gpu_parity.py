@@ -424,3 +424,20 @@ def test_full_size_polar_q5_gemv_batches():
         y = ew.gemv(x)
         assert O.rel_l2(y.float().cpu().numpy(), ref.cpu().numpy()) < TOL, batch
     assert L.lib().eoq_b200_weight_status(ew._h, None) == 0
+
+
+def test_eoq_file_loads_straight_to_device():
+    from eoq_quantization_b200 import eoq_file as EF
+    z = _z("ref_eoq_file")
+    loaded = EF.load_eoq_to_device(f"{GOLDEN}/sample.eoq", dense_dtype=torch.float32)
+    assert set(loaded) == set(z.files)
+    for name in z.files:
+        ref = z[name]
+        got = loaded[name]
+        if isinstance(got, EOQWeight):
+            assert ref.ndim == 2 and (got.rows, got.cols) == ref.shape
+            assert np.array_equal(got.dequantize(torch.float32).cpu().numpy(), ref), name
+            x = torch.randn(2, ref.shape[1], device="cuda")
+            assert O.rel_l2(got.gemv(x).cpu().numpy(), x.cpu().numpy() @ ref.T) < 1e-4
+        else:
+            assert got.is_cuda and np.array_equal(got.cpu().numpy(), ref), name

@@ -235,3 +235,32 @@ def test_quantized_linear_host_packing_matches_reference():
     assert replace_linear_with_quantized(m, min_size=100) == 2
     mem = get_model_memory(m)
     assert mem["quantized_layers"] == 2 and mem["regular_layers"] == 1 and mem["compression_ratio"] > 1
+
+
+def test_eoq_container_reader_parses_reference_file(tmp_path):
+    from eoq_quantization_b200 import eoq_file as EF
+    path = f"{GOLDEN}/sample.eoq"
+    header, recs = EF.read_eoq(path)
+    assert header["config"] == {"bits": 4, "block_size": 128, "rans_block_size": 256, "precision_bits": 14}
+    assert [r.name for r in recs] == ["layers.0.mlp.up.weight", "layers.0.mlp.down.weight", "layers.0.norm.weight", "embed.weight"]
+    assert recs[0].shape == (48, 256) and recs[0].bits == 4 and recs[0].quant_block_size == 128
+    assert len(recs[0].scales) == 48 * 256 // 128 * 2 and recs[0].rans_data[:4] == b"RANS"
+    assert [EF.fusable(r) for r in recs] == [True, True, False, False]
+    # the symbols inside decode (with the oracle) to what the reference's own loader reconstructs
+    z = _z("ref_eoq_file")
+    for r in recs:
+        d = O.deserialize_rans_v1(r.rans_data)
+        codes = O.decode_blocked(d) - 7
+        sc = np.frombuffer(r.scales, np.float16).astype(np.float32)
+        assert np.array_equal(O.dequantize(codes.reshape(r.shape), sc, 128), z[r.name]), r.name
+    raw = bytearray(open(path, "rb").read())
+    raw[40] ^= 0xFF
+    bad = tmp_path / "bad.eoq"
+    bad.write_bytes(bytes(raw))
+    with pytest.raises(ValueError, match="Checksum"):
+        EF.read_eoq(bad)
+    import struct, zlib
+    body = b"NOPE" + bytes(raw[4:-4])
+    bad.write_bytes(body + struct.pack("<I", zlib.crc32(body) & 0xFFFFFFFF))
+    with pytest.raises(ValueError, match="magic"):
+        EF.read_eoq(bad)
