@@ -110,6 +110,28 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def shutdown_distributed(world):
+    """Leave the process group without ever blocking the job: captured CUDA graphs that contain NCCL kernels can make
+    communicator teardown wait for ever, so the graphs are dropped first, the teardown gets a deadline, and a rank
+    that misses it exits on its own (rank 0 has printed its line by then)."""
+    if world <= 1:
+        return
+    import gc
+    import torch
+    import torch.distributed as dist
+    sys.stdout.flush()
+    gc.collect()
+    torch.cuda.synchronize()
+    timer = threading.Timer(20.0, lambda: os._exit(0))
+    timer.daemon = True
+    timer.start()
+    try:
+        dist.barrier()
+        dist.destroy_process_group()
+    finally:
+        timer.cancel()
+
+
 def measured_peak():
     try:
         d = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -383,8 +405,8 @@ def run_gpu_arm(args):
         if cpu_line:
             line["cpu_baseline"] = cpu_line
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    g_full = g_one = g_up = None                                 # drop the captured graphs before the communicator goes
+    shutdown_distributed(world)
 
 
 # --------------------------------------------------------------------------- secondary workloads
@@ -605,8 +627,7 @@ def run_llama_step(args):
         line["speedup_vs_fp16_dense"] = ms16 / ms
     if rank == 0:
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    shutdown_distributed(world)
 
 
 def main():
