@@ -712,6 +712,27 @@ extern "C" eoq_error_t eoq_b200_gemv(eoq_b200_weight_t *w, const void *x, int x_
     return EOQ_OK;
 }
 
+extern "C" eoq_error_t eoq_b200_gemm(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t m, void *y, int y_dtype,
+                                     const float *bias, void *stream)
+{
+    if (!w || !x || !y) return EOQ_ERR_NULL_PTR;
+    if (m == 0) return EOQ_OK;
+    if (x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2) return EOQ_ERR_UNSUPPORTED;
+    // the tensor-core path is built for the default INT4 layout: 3 weights per step, 96-row tiles
+    if (w->kind != EOQ_B200_KIND_INT4_ABSMAX || w->G != 3 || w->bits != 4 || w->Npad != w->nrb * 96u || (w->K & 15u)) return EOQ_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0) return EOQ_ERR_UNSUPPORTED;
+    static const size_t esz[3] = {2, 2, 4};
+    for (uint32_t m0 = 0; m0 < m; m0 += 128) {     // 128 activation rows share one pass over the compressed weight
+        const uint32_t mb = std::min(128u, m - m0);
+        int e = launch_gemm_tc(w->table.as<uint32_t>(), w->tiles.as<TileDesc>(), w->stream.as<uint8_t>(), w->scales.as<uint16_t>(),
+                               static_cast<const uint8_t *>(x) + (size_t)m0 * w->K * esz[x_dtype],
+                               static_cast<uint8_t *>(y) + (size_t)m0 * w->N * esz[y_dtype], bias, w->status.as<uint32_t>(),
+                               w->N, w->K, w->group, w->p, w->nseg, w->nrb, mb, x_dtype, y_dtype, stream);
+        if (e != 0) { std::fprintf(stderr, "eoq_b200_gemm: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
+    }
+    return EOQ_OK;
+}
+
 extern "C" eoq_error_t eoq_b200_gemv_host(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch, void *y, int y_dtype,
                                           const float *bias_host, void *stream)
 {

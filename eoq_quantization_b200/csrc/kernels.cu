@@ -1087,4 +1087,277 @@ int launch_dequant_packed(const uint8_t *packed, const uint16_t *scales, uint32_
     return (int)cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------
+// Fused decode -> fp16 operand tiles -> tcgen05 MMA (TMEM accumulator), for 9..128 activation rows.
+//
+//   Y[m, n] = sum_k X[m, k] * W[n, k]        (INT4 weights, G = 3)
+//
+// One 8-warp CTA per SM walks row blocks of 96 weight rows.  Within a row block warp w decodes the tiles of
+// column segments w, w+8, ...; every 16 decoded columns it has a 96 x 16 fp16 piece of W ((n - 7) * scale) in shared
+// memory next to the matching 128 x 16 piece of X, and one elected lane issues
+//     tcgen05.mma.cta_group::1.kind::f16   D[128 tokens x 96 rows] (fp32, TMEM) += Xpiece * Wpiece^T
+// (M = 128, N = 96, K = 16; both operands K-major, no swizzle: 8 x 16-byte core matrices, 128 bytes apart along K,
+// 256 bytes apart along rows).  All eight warps accumulate into the same TMEM tile, which is what lets every warp
+// work at a different K position: accumulator space (512 columns per SM) is the scarce resource, not tensor time.
+// Two accumulators alternate between row blocks.  tcgen05.commit onto mbarriers tells a warp when a staging
+// buffer may be overwritten and tells the CTA when a row block is complete; the epilogue reads TMEM with
+// tcgen05.ld and writes Y.  Every wait is bounded; TMEM is always released.
+// ---------------------------------------------------------------------------
+constexpr int kGemmThreads = 256, kGemmWarps = kGemmThreads / 32;
+constexpr uint32_t kGemmTokens = 128, kGemmRows = 96;
+constexpr uint32_t kXPieceBytes = kGemmTokens * 16 * 2, kWPieceBytes = kGemmRows * 16 * 2;
+constexpr uint32_t kTmemCols = 256;                      // two accumulators of 128 columns (96 used)
+
+__host__ __device__ inline size_t gemm_smem_bytes(uint32_t p)
+{
+    return smem_table_bytes(p) + 256 /* barriers, TMEM slot */ + (size_t)kGemmWarps * 2 * (kXPieceBytes + kWPieceBytes) +
+           ring_smem_bytes(kGemmWarps);
+}
+
+// K-major, no-swizzle shared-memory matrix descriptor: start address, leading (K) and stride (row-group) byte offsets
+// in units of 16 bytes, descriptor version 1.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo)
+{
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46);
+}
+__device__ __forceinline__ uint32_t piece_offset(uint32_t row, uint32_t col) { return (row >> 3) * 256u + (col >> 3) * 128u + (row & 7u) * 16u + (col & 7u) * 2u; }
+
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void gemm_wait(uint32_t bar, uint32_t parity, uint32_t *status, bool &dead)
+{
+    if (dead) return;
+    for (uint32_t i = 0; i < (1u << 22); i++)
+        if (mbar_test(bar, parity)) return;
+    *status = 2u;
+    dead = true;
+}
+
+template <bool RING>
+__device__ __forceinline__ void gemm_decode_piece(uint32_t tab_addr, uint32_t &x, WordState &ws, uint32_t mask, uint32_t p,
+                                                  const float (&sc)[3], uint32_t wp_addr, uint32_t lane)
+{
+    using F = Fmt<3, 4>;
+    using F0 = Int4Field<F::field_bit(0)>;
+    using F1 = Int4Field<F::field_bit(1)>;
+    using F2 = Int4Field<F::field_bit(2)>;
+    const uint32_t mg0 = F0::magic_reg(), mg1 = F1::magic_reg(), mg2 = F2::magic_reg();
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+        float w[3][8];
+#pragma unroll
+        for (int s = 0; s < 8; s++) {
+            uint32_t u0, u1, u2;
+            rans_step_int4<F0::kMask, F1::kMask, F2::kMask>(tab_addr, x, mask, p, F::kBiasMask, mg0, mg1, mg2, u0, u1, u2);
+            w[0][s] = (__uint_as_float(u0) - (F0::kBase + 7.0f)) * sc[0];      // (base + n) - (base + 7) is exact
+            w[1][s] = (__uint_as_float(u1) - (F1::kBase + 7.0f)) * sc[1];
+            w[2][s] = (__uint_as_float(u2) - (F2::kBase + 7.0f)) * sc[2];
+            rans_renorm<RING>(x, ws);
+        }
+#pragma unroll
+        for (int j = 0; j < 3; j++) {
+            __half2 h[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) h[q] = __floats2half2_rn(w[j][2 * q], w[j][2 * q + 1]);
+            const uint4 v = *reinterpret_cast<const uint4 *>(h);
+            const uint32_t addr = wp_addr + piece_offset(lane * 3 + j, half * 8);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+        }
+    }
+}
+
+struct GemmArgs {
+    const uint32_t *table;
+    const TileDesc *tiles;
+    const uint8_t  *stream;
+    const uint16_t *scales;
+    const void     *x;        // [M, K]
+    void           *y;        // [M, N]
+    const float    *bias;
+    uint32_t       *status;
+    uint32_t N, K, group, p, nseg, nrb, M;
+    int x_dtype, y_dtype;
+};
+
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_tiles_kernel(const GemmArgs a)
+{
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    uint32_t *tab = reinterpret_cast<uint32_t *>(smem);
+    uint8_t *ctl = smem + smem_table_bytes(a.p);                 // [0]: table barrier, [16]: TMEM slot, [32..]: barriers
+    uint8_t *wp_base = ctl + 256;
+    uint8_t *xp_base = wp_base + kGemmWarps * 2 * kWPieceBytes;
+    uint8_t *ring_area = xp_base + kGemmWarps * 2 * kXPieceBytes;
+
+    const uint32_t tab_bar = smem_addr(ctl), slot_addr = smem_addr(ctl + 16);
+    const uint32_t mma_bar0 = smem_addr(ctl + 32);                // [warp][stage], 8 bytes each
+    const uint32_t acc_bar0 = smem_addr(ctl + 32 + kGemmWarps * 2 * 8);
+
+    if (tid == 0) {
+        mbar_init(tab_bar, 1);
+        for (uint32_t i = 0; i < kGemmWarps * 2; i++) mbar_init(mma_bar0 + i * 8, 1);
+        mbar_init(acc_bar0, kGemmWarps);
+        mbar_init(acc_bar0 + 8, kGemmWarps);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_expect_tx(tab_bar, 4u << a.p);
+        for (uint32_t off = 0; off < (4u << a.p); off += 16384u)
+            bulk_copy_g2s(smem_addr(tab) + off, reinterpret_cast<const uint8_t *>(a.table) + off, min(16384u, (4u << a.p) - off), tab_bar);
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_addr), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    RingCtl ring;
+    ring_setup(ring, ring_area, warp, kGemmWarps, lane, a.status);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = lds_u32(slot_addr);
+    bool dead = false;       // a wait gave up: stop waiting, finish quickly, report through the status word
+    gemm_wait(tab_bar, 0u, a.status, dead);
+
+    const uint32_t mask = (1u << a.p) - 1u, p = a.p, sgroups = a.K / a.group, tab_addr = smem_addr(tab);
+    const uint32_t idesc = (1u << 4) | ((kGemmRows >> 3) << 17) | ((kGemmTokens >> 4) << 24);   // fp32 accumulate, fp16 x fp16, K-major both
+    const uint32_t wp_addr0 = smem_addr(wp_base) + warp * 2 * kWPieceBytes, xp_addr0 = smem_addr(xp_base) + warp * 2 * kXPieceBytes;
+    uint32_t np = 0;         // pieces this warp has issued; piece i uses stage i % 2 and is that stage's (i / 2)-th commit
+
+    uint32_t rbi = 0;
+    for (uint32_t rb = blockIdx.x; rb < a.nrb; rb += gridDim.x, rbi++) {
+        const uint32_t acc = rbi & 1u, d_tmem = tmem_base + acc * 128u;
+        // warp w owns TMEM lanes 32*(w%4).. (tokens) and columns 48*(w/4).. (weight rows of the block): it clears them
+        // here and reads them back in the epilogue
+        const uint32_t t = (warp & 3u) * 32u + lane, col0 = (warp >> 2) * 48u;
+        const uint32_t taddr0 = d_tmem + (((warp & 3u) * 32u) << 16) + col0;
+#pragma unroll
+        for (uint32_t i = 0; i < 3; i++)
+            asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+                         ::"r"(taddr0 + i * 16u), "r"(0u) : "memory");
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+        for (uint32_t seg = warp; seg < a.nseg; seg += kGemmWarps) {
+            const TileDesc d = a.tiles[rb * a.nseg + seg];
+            const uint8_t *base = a.stream + ((size_t)d.off64 << 6);
+            uint32_t x;
+            WordState ws;
+            tile_open(ring, d, base, lane);
+            const bool ring_mode = tile_begin(ring, ws, d, base, lane, x);
+            const uint32_t row = d.row0 + lane * 3;
+            for (uint32_t c = d.col0; c < d.col0 + d.ncols; c += 16) {
+                const uint32_t stage = np & 1u;
+                if (np >= 2)              // the MMA that last read this stage must be done before it is overwritten
+                    gemm_wait(mma_bar0 + (warp * 2 + stage) * 8, ((np >> 1) - 1u) & 1u, a.status, dead);
+                const uint32_t wp = wp_addr0 + stage * kWPieceBytes, xp = xp_addr0 + stage * kXPieceBytes;
+                // X piece: 128 tokens x 16 columns as fp16, rows past M are zero
+#pragma unroll
+                for (uint32_t i = 0; i < 4; i++) {
+                    const uint32_t t = lane + 32 * i;
+                    uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+                    if (t < a.M) {
+                        const size_t e0 = (size_t)t * a.K + c;
+                        if (a.x_dtype == EOQ_B200_F16) {
+                            lo = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(a.x) + e0));
+                            hi = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(a.x) + e0 + 8));
+                        } else {
+                            __half2 hh[8];
+#pragma unroll
+                            for (int q = 0; q < 8; q++)
+                                hh[q] = __floats2half2_rn(load_x(a.x, e0 + 2 * q, a.x_dtype), load_x(a.x, e0 + 2 * q + 1, a.x_dtype));
+                            lo = *reinterpret_cast<const uint4 *>(hh);
+                            hi = *reinterpret_cast<const uint4 *>(hh + 4);
+                        }
+                    }
+                    const uint32_t addr = xp + piece_offset(t, 0);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr + 128), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
+                }
+                float sc[3];
+#pragma unroll
+                for (int j = 0; j < 3; j++)
+                    sc[j] = row + j < a.N ? half_bits_to_float(__ldg(a.scales + (size_t)(row + j) * sgroups + c / a.group)) : 0.0f;
+                if (ring_mode) {
+                    ring_sync(ring, ws, lane);
+                    gemm_decode_piece<true>(tab_addr, x, ws, mask, p, sc, wp, lane);
+                } else {
+                    gemm_decode_piece<false>(tab_addr, x, ws, mask, p, sc, wp, lane);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    umma_f16(d_tmem, umma_desc(xp, 128, 256), umma_desc(wp, 128, 256), idesc, 1u);
+                    umma_commit(mma_bar0 + (warp * 2 + stage) * 8);
+                }
+                np++;
+            }
+            tile_end(ring, ring_mode);
+        }
+        // every MMA this warp issued for the row block is behind this commit
+        if (lane == 0) umma_commit(acc_bar0 + acc * 8);
+        __syncwarp();
+        gemm_wait(acc_bar0 + acc * 8, (rbi >> 1) & 1u, a.status, dead);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+#pragma unroll
+        for (uint32_t i = 0; i < 3; i++) {
+            uint32_t r[16];
+            const uint32_t taddr = taddr0 + i * 16u;
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                         : "r"(taddr) : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (t < a.M) {
+#pragma unroll
+                for (uint32_t q = 0; q < 16; q++) {
+                    const uint32_t n = rb * kGemmRows + col0 + i * 16u + q;
+                    if (n < a.N) store_y(a.y, (size_t)t * a.N + n, __uint_as_float(r[q]) + (a.bias ? __ldg(a.bias + n) : 0.0f), a.y_dtype);
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+}
+
+int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *stream, const uint16_t *scales, const void *x,
+                   void *y, const float *bias, uint32_t *status, uint32_t N, uint32_t K, uint32_t group, uint32_t p, uint32_t nseg,
+                   uint32_t nrb, uint32_t M, int x_dtype, int y_dtype, void *stream_)
+{
+    static std::mutex mu;
+    static size_t attr_set[16] = {0};
+    const size_t smem = gemm_smem_bytes(p);
+    if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (attr_set[dev & 15] != smem) {
+            e = cudaFuncSetAttribute(gemm_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            attr_set[dev & 15] = smem;
+        }
+    }
+    GemmArgs a;
+    a.table = table; a.tiles = tiles; a.stream = stream; a.scales = scales; a.x = x; a.y = y; a.bias = bias; a.status = status;
+    a.N = N; a.K = K; a.group = group; a.p = p; a.nseg = nseg; a.nrb = nrb; a.M = M; a.x_dtype = x_dtype; a.y_dtype = y_dtype;
+    const uint32_t grid = max(1u, min((uint32_t)device_sm_count(), nrb));
+    gemm_tiles_kernel<<<grid, kGemmThreads, smem, reinterpret_cast<cudaStream_t>(stream_)>>>(a);
+    g_launches++;
+    return (int)cudaGetLastError();
+}
+
 }  // namespace eoq

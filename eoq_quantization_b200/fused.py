@@ -144,6 +144,30 @@ class EOQWeight:
                                                 b.data_ptr() if b is not None else None, _stream_ptr()), "eoq_b200_gemv")
         return y.reshape(*x.shape[:-1], self.rows)
 
+    def gemm(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """y = x @ W.T (+ bias) for any number of rows: decoded fp16 tiles feed tcgen05 MMAs (INT4 kind only).
+
+        The fused counterpart of dequantize-then-matmul (core/quantized_linear.py:222-228) for prefill.
+        """
+        require_cuda(x, "EOQWeight.gemm")
+        if x.shape[-1] != self.cols:
+            raise ValueError(f"expected last dimension {self.cols}, got {x.shape[-1]}")
+        if x.dtype not in _DTYPES:
+            raise TypeError(f"unsupported activation dtype {x.dtype}")
+        x2 = x.reshape(-1, self.cols).contiguous()
+        out_dtype = out_dtype or x.dtype
+        y = torch.empty((x2.shape[0], self.rows), dtype=out_dtype, device=x.device)
+        b = None
+        if bias is not None:
+            b = bias.to(device=x.device, dtype=torch.float32).contiguous()
+        _lib.check(_lib.lib().eoq_b200_gemm(self._h, x2.data_ptr(), _DTYPES[x.dtype], x2.shape[0], y.data_ptr(), _DTYPES[out_dtype],
+                                            b.data_ptr() if b is not None else None, _stream_ptr()), "eoq_b200_gemm")
+        return y.reshape(*x.shape[:-1], self.rows)
+
+    def status(self) -> int:
+        """0, or the status word a kernel left after a bounded wait gave up (synchronises the current stream)."""
+        return int(_lib.lib().eoq_b200_weight_status(self._h, _stream_ptr()))
+
     def gemv_host(self, x: np.ndarray, bias: Optional[np.ndarray] = None) -> np.ndarray:
         """Same with numpy buffers on the host (copies in, runs, copies out, synchronises)."""
         x2 = np.ascontiguousarray(x).reshape(-1, self.cols)

@@ -270,6 +270,18 @@ eoq_error_t eoq_b200_weight_info(const eoq_b200_weight_t *w, eoq_b200_weight_inf
 eoq_error_t eoq_b200_gemv(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch,
                           void *y, int y_dtype, const float *bias, void *stream);
 
+/* Y = X W^T (+ bias) for many activation rows (prefill), the fused replacement for
+ * dequantize-then-matmul (core/quantized_linear.py:222-228, core/quantized_matmul.py:91-176)
+ * when m is too large for the GEMV kernel: the compressed tiles are decoded once per 128
+ * activation rows and the decoded fp16 pieces go from shared memory straight into tensor-core
+ * MMAs (tcgen05, fp32 accumulator in tensor memory); the dequantised matrix never exists in
+ * HBM.  x is [m, K], y is [m, N], row-major device pointers; x must be 16-byte aligned and is
+ * rounded to fp16 before the product (weights are (q - 7) * scale in fp16).  INT4 weights in the
+ * default layout (3 weights per step) only; others return EOQ_ERR_UNSUPPORTED.  Asynchronous
+ * on `stream`. */
+eoq_error_t eoq_b200_gemm(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t m,
+                          void *y, int y_dtype, const float *bias, void *stream);
+
 /* Same with host buffers: copies x in, runs, copies y out, synchronises. */
 eoq_error_t eoq_b200_gemv_host(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch,
                                void *y, int y_dtype, const float *bias_host, void *stream);
