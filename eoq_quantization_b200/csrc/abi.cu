@@ -517,6 +517,7 @@ struct eoq_b200_weight {
     uint32_t N = 0, K = 0, Npad = 0, G = 0, bits = 0, p = 0, group = 0, kind = 0, alphabet = 0;
     uint32_t ntiles = 0, nseg = 0, nrb = 0;
     DeviceBuf table, tiles, stream, scales, centroids, partials, counters, status, xbuf, ybuf, biasbuf;
+    DeviceBuf gemm_x, gemm_partials, gemm_counters;   // scratch of the tensor-core path, allocated by its first call
     size_t stream_bytes = 0, scale_bytes = 0, partial_bytes = 0;
     std::mutex mu;   // one call at a time may use the scratch of a weight
 };
@@ -530,7 +531,7 @@ eoq_error_t resolve_opts(const eoq_b200_weight_opts_t *o, uint32_t &bits, uint32
     else if (o->kind == EOQ_B200_KIND_Q5_POLAR) { bits = 5; G = o->symbols_per_step ? o->symbols_per_step : 2; pad = 16; if (!o->centroids) return EOQ_ERR_NULL_PTR; }
     else return EOQ_ERR_UNSUPPORTED;
     if (G < 1 || G > (bits == 4 ? 3u : 2u)) return EOQ_ERR_UNSUPPORTED;
-    p = o->precision_bits ? o->precision_bits : std::min(16u, std::max(12u, bits * G + 2));
+    p = o->precision_bits ? o->precision_bits : std::min(16u, std::max(12u, bits * G + 1));   // INT4 x 3: 13 bits, a 32 KB table
     if (p > 14 || p < bits * G) return EOQ_ERR_UNSUPPORTED;        // table must fit shared memory beside x
     target = o->target_tiles;
     return EOQ_OK;
@@ -720,12 +721,23 @@ extern "C" eoq_error_t eoq_b200_gemm(eoq_b200_weight_t *w, const void *x, int x_
     if (x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2) return EOQ_ERR_UNSUPPORTED;
     // the tensor-core path is built for the default INT4 layout: 3 weights per step, 96-row tiles
     if (w->kind != EOQ_B200_KIND_INT4_ABSMAX || w->G != 3 || w->bits != 4 || w->Npad != w->nrb * 96u || (w->K & 15u)) return EOQ_ERR_UNSUPPORTED;
-    if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0) return EOQ_ERR_UNSUPPORTED;
+    if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u) != 0) return EOQ_ERR_UNSUPPORTED;
     static const size_t esz[3] = {2, 2, 4};
+    {
+        std::lock_guard<std::mutex> lock(w->mu);
+        if (!w->gemm_x.p) {
+            // fp16 copy of up to 128 fp32 or bf16 activation rows, one fp32 partial tile pair per CTA, one arrival counter per row block
+            CU_TRY(w->gemm_x.alloc((size_t)128 * w->K * 2));
+            CU_TRY(w->gemm_partials.alloc(gemm_partial_bytes(gemm_grid(w->nrb, w->nseg))));
+            CU_TRY(w->gemm_counters.alloc((size_t)w->nrb * 4));
+            CU_TRY(cudaMemset(w->gemm_counters.p, 0, (size_t)w->nrb * 4));
+        }
+    }
     for (uint32_t m0 = 0; m0 < m; m0 += 128) {     // 128 activation rows share one pass over the compressed weight
         const uint32_t mb = std::min(128u, m - m0);
         int e = launch_gemm_tc(w->table.as<uint32_t>(), w->tiles.as<TileDesc>(), w->stream.as<uint8_t>(), w->scales.as<uint16_t>(),
-                               static_cast<const uint8_t *>(x) + (size_t)m0 * w->K * esz[x_dtype],
+                               static_cast<const uint8_t *>(x) + (size_t)m0 * w->K * esz[x_dtype], w->gemm_x.p,
+                               w->gemm_partials.as<float>(), w->gemm_counters.as<uint32_t>(),
                                static_cast<uint8_t *>(y) + (size_t)m0 * w->N * esz[y_dtype], bias, w->status.as<uint32_t>(),
                                w->N, w->K, w->group, w->p, w->nseg, w->nrb, mb, x_dtype, y_dtype, stream);
         if (e != 0) { std::fprintf(stderr, "eoq_b200_gemm: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
@@ -808,6 +820,7 @@ extern "C" int eoq_b200_tune(const char *key, int value)
 {
     if (!key) return -1;
     if (std::strcmp(key, "gemv_ctas_per_sm") == 0) { set_gemv_ctas_per_sm(value); return 0; }
+    if (std::strcmp(key, "gemm_warps") == 0) { set_gemm_warps(value); return 0; }
     return -1;
 }
 

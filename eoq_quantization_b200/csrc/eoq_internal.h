@@ -124,10 +124,13 @@ int launch_decode_v1_resume(const uint8_t *d_block, uint32_t stream_end, const V
 int launch_dequant_packed(const uint8_t *packed, const uint16_t *scales, uint32_t K, uint32_t row_bytes, uint32_t bits,
                           uint32_t group, uint32_t row_lo, uint32_t row_hi, void *out, int out_dtype, void *stream);
 int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *stream, const uint16_t *scales, const void *x,
-                   void *y, const float *bias, uint32_t *status, uint32_t N, uint32_t K, uint32_t group, uint32_t p, uint32_t nseg,
-                   uint32_t nrb, uint32_t M, int x_dtype, int y_dtype, void *stream_);
+                   void *xhalf, float *partials, uint32_t *counters, void *y, const float *bias, uint32_t *status, uint32_t N,
+                   uint32_t K, uint32_t group, uint32_t p, uint32_t nseg, uint32_t nrb, uint32_t M, int x_dtype, int y_dtype, void *stream_);
+uint32_t gemm_grid(uint32_t nrb, uint32_t nseg);
+size_t gemm_partial_bytes(uint32_t grid);
 size_t gemv_smem_bytes(uint32_t K, uint32_t p, uint32_t bt, uint32_t kind);
 uint64_t launch_counter();
 void set_gemv_ctas_per_sm(int v);
+void set_gemm_warps(int v);
 
 }  // namespace eoq

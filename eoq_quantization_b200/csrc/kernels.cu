@@ -1088,31 +1088,44 @@ int launch_dequant_packed(const uint8_t *packed, const uint16_t *scales, uint32_
 }
 
 // ---------------------------------------------------------------------------
-// Fused decode -> fp16 operand tiles -> tcgen05 MMA (TMEM accumulator), for 9..128 activation rows.
+// Fused decode -> fp16 operand pieces -> tcgen05 MMA (accumulator in tensor memory), for up to 128 activation rows.
 //
-//   Y[m, n] = sum_k X[m, k] * W[n, k]        (INT4 weights, G = 3)
+//   Y[m, n] = sum_k X[m, k] * W[n, k]        (INT4 weights, 3 per step, 96-row tiles)
 //
-// One 8-warp CTA per SM walks row blocks of 96 weight rows.  Within a row block warp w decodes the tiles of
-// column segments w, w+8, ...; every 16 decoded columns it has a 96 x 16 fp16 piece of W ((n - 7) * scale) in shared
-// memory next to the matching 128 x 16 piece of X, and one elected lane issues
+// Work split (stream-K): the tiles, in (row block, column segment) order, are cut into one contiguous range per
+// CTA, one persistent CTA per SM, so every SM decodes the same number of tiles whatever the shape.  A range covers
+// parts of one or more row blocks; up to four row blocks (one TMEM accumulator each) are in flight at a time and
+// the warps take the tiles of the range round-robin.  Every 16 decoded columns a warp has a 96 x 16 fp16 piece of
+// W ((q - 7) * scale) in shared memory, has fetched the matching piece of X (16-byte asynchronous copies straight
+// from the row-major activations), and one elected lane issues
 //     tcgen05.mma.cta_group::1.kind::f16   D[128 tokens x 96 rows] (fp32, TMEM) += Xpiece * Wpiece^T
-// (M = 128, N = 96, K = 16; both operands K-major, no swizzle: 8 x 16-byte core matrices, 128 bytes apart along K,
-// 256 bytes apart along rows).  All eight warps accumulate into the same TMEM tile, which is what lets every warp
-// work at a different K position: accumulator space (512 columns per SM) is the scarce resource, not tensor time.
-// Two accumulators alternate between row blocks.  tcgen05.commit onto mbarriers tells a warp when a staging
-// buffer may be overwritten and tells the CTA when a row block is complete; the epilogue reads TMEM with
-// tcgen05.ld and writes Y.  Every wait is bounded; TMEM is always released.
+// (M = 128, N = 96, K = 16; both operands K-major without swizzle: 8 x 16-byte core matrices, 128 bytes apart
+// along K, 256 bytes apart along rows).  Rows of D depend only on the same rows of X, so token rows past the
+// batch are never staged: the MMA reads whatever follows in shared memory and those rows of D are never stored.
+// All warps of the CTA accumulate into the same TMEM tile, which is what lets each of them be at a different K
+// position: accumulator space (512 columns per SM), not tensor time, is the scarce resource.  tcgen05.commit onto
+// mbarriers tells a warp when its staging buffers may be overwritten and tells the CTA when a group is complete;
+// the epilogue reads TMEM with tcgen05.ld.  A row block that one CTA decoded alone is written straight to Y;
+// otherwise each contributor stores its fp32 partial tile and takes a ticket, and the last one to arrive adds the
+// partial tiles in CTA order and writes Y (no CTA ever waits for another).  Every wait is bounded; TMEM is always
+// released.
 // ---------------------------------------------------------------------------
-constexpr int kGemmThreads = 256, kGemmWarps = kGemmThreads / 32;
+constexpr int kGemmMaxThreads = 512;
 constexpr uint32_t kGemmTokens = 128, kGemmRows = 96;
 constexpr uint32_t kXPieceBytes = kGemmTokens * 16 * 2, kWPieceBytes = kGemmRows * 16 * 2;
-constexpr uint32_t kTmemCols = 256;                      // two accumulators of 128 columns (96 used)
+constexpr uint32_t kGemmAccs = 4, kTmemCols = 128 * kGemmAccs;   // four accumulators, 128 columns apart (96 used): all of TMEM
+constexpr uint32_t kGemmMaxContrib = 160, kGemmCtlBytes = 256 + 2 * kGemmMaxContrib * 4;
+constexpr uint32_t kGemmSlotFloats = kGemmTokens * kGemmRows;
 
-__host__ __device__ inline size_t gemm_smem_bytes(uint32_t p)
+// bytes of one warp's X staging piece: the staged token rows, rounded up to 8
+__host__ __device__ inline uint32_t gemm_x_stride(uint32_t m) { return ((m + 7u) & ~7u) * 32u; }
+
+size_t gemm_smem_bytes(uint32_t p, uint32_t warps, uint32_t m)
 {
-    return smem_table_bytes(p) + 256 /* barriers, TMEM slot */ + (size_t)kGemmWarps * 2 * (kXPieceBytes + kWPieceBytes) +
-           ring_smem_bytes(kGemmWarps);
+    // the last warp's MMA reads a full 128-row piece: keep that much behind the last staged piece
+    return smem_table_bytes(p) + kGemmCtlBytes + (size_t)warps * (kWPieceBytes + gemm_x_stride(m)) + kXPieceBytes + ring_smem_bytes(warps);
 }
+size_t gemm_partial_bytes(uint32_t grid) { return (size_t)grid * 2 * kGemmSlotFloats * sizeof(float); }
 
 // K-major, no-swizzle shared-memory matrix descriptor: start address, leading (K) and stride (row-group) byte offsets
 // in units of 16 bytes, descriptor version 1.
@@ -1120,7 +1133,7 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint
 {
     return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46);
 }
-__device__ __forceinline__ uint32_t piece_offset(uint32_t row, uint32_t col) { return (row >> 3) * 256u + (col >> 3) * 128u + (row & 7u) * 16u + (col & 7u) * 2u; }
+__host__ __device__ __forceinline__ uint32_t piece_offset(uint32_t row, uint32_t col) { return (row >> 3) * 256u + (col >> 3) * 128u + (row & 7u) * 16u + (col & 7u) * 2u; }
 
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
 {
@@ -1142,9 +1155,48 @@ __device__ __forceinline__ void gemm_wait(uint32_t bar, uint32_t parity, uint32_
     dead = true;
 }
 
+struct GemmArgs {
+    const uint32_t *table;
+    const TileDesc *tiles;
+    const uint8_t  *stream;
+    const uint16_t *scales;
+    const uint16_t *x;        // [M, K] fp16, rows 16-byte aligned
+    void           *y;        // [M, N]
+    const float    *bias;
+    float          *partials; // [grid][2][128][96]
+    uint32_t       *counters; // [nrb], zero between launches
+    uint32_t       *status;
+    uint32_t N, K, group, p, nseg, nrb, M;
+    int y_dtype;
+};
+
+// X [M, K] fp32 or bf16 -> fp16, same layout: kind::f16 MMAs take both operands in one 16-bit format, and the weight
+// pieces are fp16 ((q - 7) * scale is exact to fp16 rounding, bf16 would lose three bits of it)
+__global__ void gemm_x_to_half_kernel(const void *x, int x_dtype, __half *out, size_t n)
+{
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;
+    if (i + 3 < n && x_dtype == EOQ_B200_F32) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(x) + i / 4);
+        __half2 h[2] = {__floats2half2_rn(v.x, v.y), __floats2half2_rn(v.z, v.w)};
+        *reinterpret_cast<uint2 *>(out + i) = *reinterpret_cast<const uint2 *>(h);
+    } else {
+        for (size_t k = i; k < min(i + 4, n); k++) out[k] = __float2half_rn(load_x(x, k, x_dtype));
+    }
+}
+
+struct GemmWarp {             // per warp, warp-uniform
+    uint32_t wp, xp;          // shared addresses of the W and X staging pieces
+    uint32_t mma_bar;
+    uint32_t np;              // pieces issued so far: piece i is the barrier's i-th completion
+};
+
+// Decode 16 columns of the warp's tile into its W piece.  A few steps in, once the previous MMA is known to have read
+// both staging pieces, the copies of this piece's X are started so that they land while the rest decodes.
 template <bool RING>
 __device__ __forceinline__ void gemm_decode_piece(uint32_t tab_addr, uint32_t &x, WordState &ws, uint32_t mask, uint32_t p,
-                                                  const float (&sc)[3], uint32_t wp_addr, uint32_t lane)
+                                                  const float (&sc)[3], const GemmWarp &gw, const uint16_t *xsrc, uint32_t K,
+                                                  uint32_t M, uint32_t lane, uint32_t *status, bool &dead)
 {
     using F = Fmt<3, 4>;
     using F0 = Int4Field<F::field_bit(0)>;
@@ -1162,6 +1214,16 @@ __device__ __forceinline__ void gemm_decode_piece(uint32_t tab_addr, uint32_t &x
             w[1][s] = (__uint_as_float(u1) - (F1::kBase + 7.0f)) * sc[1];
             w[2][s] = (__uint_as_float(u2) - (F2::kBase + 7.0f)) * sc[2];
             rans_renorm<RING>(x, ws);
+            if (half == 0 && s == 3) {
+                // the previous MMA was issued four steps ago: it has read both staging pieces by now
+                if (gw.np > 0) gemm_wait(gw.mma_bar, (gw.np - 1u) & 1u, status, dead);
+                // 16-byte chunk q of the piece: token q / 2, columns 8 * (q % 2) ..
+                for (uint32_t q = lane; q < 2u * M; q += 32u) {
+                    const uint32_t t = q >> 1, h = q & 1u;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(gw.xp + piece_offset(t, h * 8u)),
+                                 "l"(xsrc + (size_t)t * K + h * 8u) : "memory");
+                }
+            }
         }
 #pragma unroll
         for (int j = 0; j < 3; j++) {
@@ -1169,55 +1231,117 @@ __device__ __forceinline__ void gemm_decode_piece(uint32_t tab_addr, uint32_t &x
 #pragma unroll
             for (int q = 0; q < 4; q++) h[q] = __floats2half2_rn(w[j][2 * q], w[j][2 * q + 1]);
             const uint4 v = *reinterpret_cast<const uint4 *>(h);
-            const uint32_t addr = wp_addr + piece_offset(lane * 3 + j, half * 8);
+            const uint32_t addr = gw.wp + piece_offset(lane * 3 + j, half * 8);
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
         }
     }
 }
 
-struct GemmArgs {
-    const uint32_t *table;
-    const TileDesc *tiles;
-    const uint8_t  *stream;
-    const uint16_t *scales;
-    const void     *x;        // [M, K]
-    void           *y;        // [M, N]
-    const float    *bias;
-    uint32_t       *status;
-    uint32_t N, K, group, p, nseg, nrb, M;
-    int x_dtype, y_dtype;
-};
+// 16 consecutive outputs of one token row: y[idx .. idx+15] = v + bias, as two 16-byte stores when the row allows
+__device__ __forceinline__ void gemm_store16(void *y, size_t idx, const float (&v)[16], uint32_t n0, uint32_t N, int dtype)
+{
+    if (dtype != EOQ_B200_F32 && n0 + 16u <= N && (idx & 7u) == 0) {
+        uint32_t pk[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            if (dtype == EOQ_B200_F16) {
+                const __half2 h = __floats2half2_rn(v[2 * q], v[2 * q + 1]);
+                pk[q] = *reinterpret_cast<const uint32_t *>(&h);
+            } else {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
+                pk[q] = *reinterpret_cast<const uint32_t *>(&h);
+            }
+        }
+        uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(y) + idx);
+        dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+    } else {
+#pragma unroll
+        for (uint32_t q = 0; q < 16; q++)
+            if (n0 + q < N) store_y(y, idx + q, v[q], dtype);
+    }
+}
 
-__global__ void __launch_bounds__(kGemmThreads, 1) gemm_tiles_kernel(const GemmArgs a)
+// The last contributor of a shared row block adds the partial tiles (slots listed in `contrib`, CTA order) and writes Y.
+__device__ __forceinline__ void gemm_sum_partials(const GemmArgs &a, uint32_t rb, const volatile uint32_t *contrib, uint32_t n)
+{
+    constexpr uint32_t kU = 6;                       // float4 loads in flight per thread and contributor
+    const uint32_t nvec = a.M * (kGemmRows / 4);
+    for (uint32_t v0 = threadIdx.x; v0 < nvec; v0 += blockDim.x * kU) {
+        float4 acc[kU];
+#pragma unroll
+        for (uint32_t u = 0; u < kU; u++) acc[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (uint32_t k = 0; k < n; k++) {
+            const float4 *src = reinterpret_cast<const float4 *>(a.partials + (size_t)contrib[k] * kGemmSlotFloats);
+            float4 t[kU];
+#pragma unroll
+            for (uint32_t u = 0; u < kU; u++) {
+                const uint32_t v = v0 + u * blockDim.x;
+                t[u] = v < nvec ? __ldcg(src + v) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (uint32_t u = 0; u < kU; u++) { acc[u].x += t[u].x; acc[u].y += t[u].y; acc[u].z += t[u].z; acc[u].w += t[u].w; }
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < kU; u++) {
+            const uint32_t v = v0 + u * blockDim.x;
+            if (v >= nvec) continue;
+            const uint32_t tt = v / (kGemmRows / 4), col = rb * kGemmRows + (v % (kGemmRows / 4)) * 4u;
+            const float o[4] = {acc[u].x, acc[u].y, acc[u].z, acc[u].w};
+#pragma unroll
+            for (uint32_t q = 0; q < 4; q++)
+                if (col + q < a.N) store_y(a.y, (size_t)tt * a.N + col + q, o[q] + (a.bias ? __ldg(a.bias + col + q) : 0.0f), a.y_dtype);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const GemmArgs a)
 {
     extern __shared__ __align__(16) uint8_t smem[];
-    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, nwarps = blockDim.x >> 5;
     uint32_t *tab = reinterpret_cast<uint32_t *>(smem);
-    uint8_t *ctl = smem + smem_table_bytes(a.p);                 // [0]: table barrier, [16]: TMEM slot, [32..]: barriers
-    uint8_t *wp_base = ctl + 256;
-    uint8_t *xp_base = wp_base + kGemmWarps * 2 * kWPieceBytes;
-    uint8_t *ring_area = xp_base + kGemmWarps * 2 * kXPieceBytes;
+    uint8_t *ctl = smem + smem_table_bytes(a.p);
+    uint8_t *wp_base = ctl + kGemmCtlBytes;
+    uint8_t *xp_base = wp_base + nwarps * kWPieceBytes;
+    uint8_t *ring_area = xp_base + nwarps * gemm_x_stride(a.M) + kXPieceBytes;
 
-    const uint32_t tab_bar = smem_addr(ctl), slot_addr = smem_addr(ctl + 16);
-    const uint32_t mma_bar0 = smem_addr(ctl + 32);                // [warp][stage], 8 bytes each
-    const uint32_t acc_bar0 = smem_addr(ctl + 32 + kGemmWarps * 2 * 8);
+    // control block: table barrier, TMEM slot, group barrier, ticket flags, per-warp barriers, two contributor lists
+    const uint32_t tab_bar = smem_addr(ctl), slot_addr = smem_addr(ctl + 16), grp_bar = smem_addr(ctl + 32);
+    volatile uint32_t *flag = reinterpret_cast<volatile uint32_t *>(ctl + 48);          // [2]
+    const uint32_t mma_bar0 = smem_addr(ctl + 64);
+    volatile uint32_t *contrib = reinterpret_cast<volatile uint32_t *>(ctl + 256);      // [2][kGemmMaxContrib]
+
+    // this CTA's range of tiles; the warp's first tile is requested before anything else
+    const uint64_t T = (uint64_t)a.nrb * a.nseg;
+    const uint32_t t_lo = (uint32_t)(T * blockIdx.x / gridDim.x), t_hi = (uint32_t)(T * (blockIdx.x + 1) / gridDim.x);
+    const uint32_t rb_first = t_lo / a.nseg, rb_last = (t_hi - 1u) / a.nseg;
+    RingCtl ring;
+    ring_setup(ring, ring_area, warp, nwarps, lane, a.status);
+    uint32_t tile = t_lo + warp;
+    const uint32_t g0_hi = min(t_hi, (rb_first + kGemmAccs) * a.nseg);
+    bool have = tile < g0_hi;
+    TileDesc d;
+    if (have) {
+        d = a.tiles[tile];
+        tile_open(ring, d, a.stream + ((size_t)d.off64 << 6), lane);
+    }
 
     if (tid == 0) {
         mbar_init(tab_bar, 1);
-        for (uint32_t i = 0; i < kGemmWarps * 2; i++) mbar_init(mma_bar0 + i * 8, 1);
-        mbar_init(acc_bar0, kGemmWarps);
-        mbar_init(acc_bar0 + 8, kGemmWarps);
+        mbar_init(grp_bar, nwarps);
+        for (uint32_t i = 0; i < nwarps; i++) mbar_init(mma_bar0 + i * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         mbar_expect_tx(tab_bar, 4u << a.p);
         for (uint32_t off = 0; off < (4u << a.p); off += 16384u)
             bulk_copy_g2s(smem_addr(tab) + off, reinterpret_cast<const uint8_t *>(a.table) + off, min(16384u, (4u << a.p) - off), tab_bar);
     }
+    // the .sync.aligned tensor-memory instructions below need the whole warp at the same instruction: lanes that took
+    // a lane-0-only branch or left a polling loop at different times are brought back together first
+    __syncwarp();
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_addr), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    RingCtl ring;
-    ring_setup(ring, ring_area, warp, kGemmWarps, lane, a.status);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -1226,136 +1350,230 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tiles_kernel(const GemmA
     gemm_wait(tab_bar, 0u, a.status, dead);
 
     const uint32_t mask = (1u << a.p) - 1u, p = a.p, sgroups = a.K / a.group, tab_addr = smem_addr(tab);
-    const uint32_t idesc = (1u << 4) | ((kGemmRows >> 3) << 17) | ((kGemmTokens >> 4) << 24);   // fp32 accumulate, fp16 x fp16, K-major both
-    const uint32_t wp_addr0 = smem_addr(wp_base) + warp * 2 * kWPieceBytes, xp_addr0 = smem_addr(xp_base) + warp * 2 * kXPieceBytes;
-    uint32_t np = 0;         // pieces this warp has issued; piece i uses stage i % 2 and is that stage's (i / 2)-th commit
+    // fp32 accumulate, A = X and B = W both fp16 and K-major, N = 96, M = 128
+    const uint32_t idesc = (1u << 4) | ((kGemmRows >> 3) << 17) | ((kGemmTokens >> 4) << 24);
+    GemmWarp gw;
+    gw.wp = smem_addr(wp_base) + warp * kWPieceBytes;
+    gw.xp = smem_addr(xp_base) + warp * gemm_x_stride(a.M);
+    gw.mma_bar = mma_bar0 + warp * 8;
+    gw.np = 0;
+    // warps 0..7: warp w owns TMEM lanes 32*(w%4).. (tokens) and columns 48*(w/4).. (weight rows of a block) of every
+    // accumulator; it clears them before a group and reads them back after it
+    const uint32_t tok = (warp & 3u) * 32u + lane, col0 = (warp >> 2) * 48u;
+    const uint32_t taddr_w = tmem_base + (((warp & 3u) * 32u) << 16) + col0;
 
-    uint32_t rbi = 0;
-    for (uint32_t rb = blockIdx.x; rb < a.nrb; rb += gridDim.x, rbi++) {
-        const uint32_t acc = rbi & 1u, d_tmem = tmem_base + acc * 128u;
-        // warp w owns TMEM lanes 32*(w%4).. (tokens) and columns 48*(w/4).. (weight rows of the block): it clears them
-        // here and reads them back in the epilogue
-        const uint32_t t = (warp & 3u) * 32u + lane, col0 = (warp >> 2) * 48u;
-        const uint32_t taddr0 = d_tmem + (((warp & 3u) * 32u) << 16) + col0;
+    uint32_t grp = 0;
+    for (uint32_t rb0 = rb_first; t_lo < t_hi && rb0 <= rb_last; rb0 += kGemmAccs, grp++) {
+        const uint32_t g_lo = max(t_lo, rb0 * a.nseg), g_hi = min(t_hi, (rb0 + kGemmAccs) * a.nseg);
+        const uint32_t nparts = (g_hi - 1u) / a.nseg - rb0 + 1u;
+        if (grp > 0) {
+            tile = g_lo + warp;
+            have = tile < g_hi;
+            if (have) {
+                d = a.tiles[tile];
+                tile_open(ring, d, a.stream + ((size_t)d.off64 << 6), lane);
+            }
+        }
+        __syncwarp();
+        if (warp < 8) {
+            for (uint32_t pa = 0; pa < nparts; pa++)
 #pragma unroll
-        for (uint32_t i = 0; i < 3; i++)
-            asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
-                         ::"r"(taddr0 + i * 16u), "r"(0u) : "memory");
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                for (uint32_t i = 0; i < 3; i++)
+                    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+                                 ::"r"(taddr_w + pa * 128u + i * 16u), "r"(0u) : "memory");
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-        for (uint32_t seg = warp; seg < a.nseg; seg += kGemmWarps) {
-            const TileDesc d = a.tiles[rb * a.nseg + seg];
+        while (have) {
             const uint8_t *base = a.stream + ((size_t)d.off64 << 6);
+            const uint32_t d_tmem = tmem_base + (tile / a.nseg - rb0) * 128u;
             uint32_t x;
             WordState ws;
-            tile_open(ring, d, base, lane);
             const bool ring_mode = tile_begin(ring, ws, d, base, lane, x);
+            // ask L2 for the warp's next tile while this one decodes
+            const uint32_t next = tile + nwarps;
+            if (next < g_hi && lane == 0) {
+                const TileDesc nd = a.tiles[next];
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.stream + ((size_t)nd.off64 << 6)), "r"(nd.len64 << 6) : "memory");
+            }
             const uint32_t row = d.row0 + lane * 3;
-            for (uint32_t c = d.col0; c < d.col0 + d.ncols; c += 16) {
-                const uint32_t stage = np & 1u;
-                if (np >= 2)              // the MMA that last read this stage must be done before it is overwritten
-                    gemm_wait(mma_bar0 + (warp * 2 + stage) * 8, ((np >> 1) - 1u) & 1u, a.status, dead);
-                const uint32_t wp = wp_addr0 + stage * kWPieceBytes, xp = xp_addr0 + stage * kXPieceBytes;
-                // X piece: 128 tokens x 16 columns as fp16, rows past M are zero
+            const uint16_t *srow[3];
 #pragma unroll
-                for (uint32_t i = 0; i < 4; i++) {
-                    const uint32_t t = lane + 32 * i;
-                    uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-                    if (t < a.M) {
-                        const size_t e0 = (size_t)t * a.K + c;
-                        if (a.x_dtype == EOQ_B200_F16) {
-                            lo = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(a.x) + e0));
-                            hi = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(a.x) + e0 + 8));
-                        } else {
-                            __half2 hh[8];
+            for (int j = 0; j < 3; j++) srow[j] = a.scales + (size_t)min(row + j, a.N - 1u) * sgroups;
+            uint16_t sc_next[3];
 #pragma unroll
-                            for (int q = 0; q < 8; q++)
-                                hh[q] = __floats2half2_rn(load_x(a.x, e0 + 2 * q, a.x_dtype), load_x(a.x, e0 + 2 * q + 1, a.x_dtype));
-                            lo = *reinterpret_cast<const uint4 *>(hh);
-                            hi = *reinterpret_cast<const uint4 *>(hh + 4);
-                        }
+            for (int j = 0; j < 3; j++) sc_next[j] = ldg_u16_pinned(srow[j] + d.col0 / a.group);
+            float sc[3] = {0.0f, 0.0f, 0.0f};
+            const uint32_t cend = d.col0 + d.ncols;
+            for (uint32_t c = d.col0; c < cend; c += 16) {
+                if (c == d.col0 || c % a.group == 0) {
+                    // scales of this group were requested a group ago; request the next group's now
+                    const uint32_t g = c / a.group;
+#pragma unroll
+                    for (int j = 0; j < 3; j++) sc[j] = row + j < a.N ? half_bits_to_float(sc_next[j]) : 0.0f;
+                    if ((g + 1) * a.group < cend) {
+#pragma unroll
+                        for (int j = 0; j < 3; j++) sc_next[j] = ldg_u16_pinned(srow[j] + g + 1);
                     }
-                    const uint32_t addr = xp + piece_offset(t, 0);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr + 128), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
                 }
-                float sc[3];
-#pragma unroll
-                for (int j = 0; j < 3; j++)
-                    sc[j] = row + j < a.N ? half_bits_to_float(__ldg(a.scales + (size_t)(row + j) * sgroups + c / a.group)) : 0.0f;
                 if (ring_mode) {
                     ring_sync(ring, ws, lane);
-                    gemm_decode_piece<true>(tab_addr, x, ws, mask, p, sc, wp, lane);
+                    gemm_decode_piece<true>(tab_addr, x, ws, mask, p, sc, gw, a.x + c, a.K, a.M, lane, a.status, dead);
                 } else {
-                    gemm_decode_piece<false>(tab_addr, x, ws, mask, p, sc, wp, lane);
+                    gemm_decode_piece<false>(tab_addr, x, ws, mask, p, sc, gw, a.x + c, a.K, a.M, lane, a.status, dead);
                 }
+                asm volatile("cp.async.wait_all;" ::: "memory");
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) {
-                    umma_f16(d_tmem, umma_desc(xp, 128, 256), umma_desc(wp, 128, 256), idesc, 1u);
-                    umma_commit(mma_bar0 + (warp * 2 + stage) * 8);
+                    umma_f16(d_tmem, umma_desc(gw.xp, 128, 256), umma_desc(gw.wp, 128, 256), idesc, 1u);
+                    umma_commit(gw.mma_bar);
                 }
-                np++;
+                gw.np++;
             }
             tile_end(ring, ring_mode);
+            tile = next;
+            have = tile < g_hi;
+            if (have) {
+                d = a.tiles[tile];
+                tile_open(ring, d, a.stream + ((size_t)d.off64 << 6), lane);
+            }
         }
-        // every MMA this warp issued for the row block is behind this commit
-        if (lane == 0) umma_commit(acc_bar0 + acc * 8);
+        // every MMA this warp issued for the group is behind this commit
+        if (lane == 0) umma_commit(grp_bar);
         __syncwarp();
-        gemm_wait(acc_bar0 + acc * 8, (rbi >> 1) & 1u, a.status, dead);
+        gemm_wait(grp_bar, grp & 1u, a.status, dead);
+        __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
+        // a CTA's first row block and its last are the only ones it can share with other CTAs: partial slots 0 and 1
+        bool shared_any = false;
+        for (uint32_t pa = 0; pa < nparts; pa++) {
+            const uint32_t rb = rb0 + pa;
+            const bool full = max(t_lo, rb * a.nseg) == rb * a.nseg && min(t_hi, (rb + 1) * a.nseg) == (rb + 1) * a.nseg;
+            shared_any |= !full;
+            if (warp < 8) {
+                float *slot = a.partials + ((size_t)blockIdx.x * 2 + (rb == rb_first ? 0u : 1u)) * kGemmSlotFloats + (size_t)tok * kGemmRows + col0;
 #pragma unroll
-        for (uint32_t i = 0; i < 3; i++) {
-            uint32_t r[16];
-            const uint32_t taddr = taddr0 + i * 16u;
-            asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                         : "r"(taddr) : "memory");
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (t < a.M) {
+                for (uint32_t i = 0; i < 3; i++) {
+                    uint32_t r[16];
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                                 : "r"(taddr_w + pa * 128u + i * 16u) : "memory");
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (tok < a.M) {
+                        if (full) {
+                            const uint32_t n0 = rb * kGemmRows + col0 + i * 16u;
+                            float v[16];
 #pragma unroll
-                for (uint32_t q = 0; q < 16; q++) {
-                    const uint32_t n = rb * kGemmRows + col0 + i * 16u + q;
-                    if (n < a.N) store_y(a.y, (size_t)t * a.N + n, __uint_as_float(r[q]) + (a.bias ? __ldg(a.bias + n) : 0.0f), a.y_dtype);
+                            for (uint32_t q = 0; q < 16; q++) v[q] = __uint_as_float(r[q]) + (a.bias && n0 + q < a.N ? __ldg(a.bias + n0 + q) : 0.0f);
+                            gemm_store16(a.y, (size_t)tok * a.N + n0, v, n0, a.N, a.y_dtype);
+                        } else {
+#pragma unroll
+                            for (uint32_t q = 0; q < 16; q += 4)
+                                __stcg(reinterpret_cast<float4 *>(slot + i * 16u + q),
+                                       make_float4(__uint_as_float(r[q]), __uint_as_float(r[q + 1]), __uint_as_float(r[q + 2]), __uint_as_float(r[q + 3])));
+                        }
+                    }
+                    __syncwarp();      // lanes past the batch skipped the stores: rejoin before the next aligned load
                 }
             }
+        }
+        if (shared_any) {
+            // tickets: the last contributor of a row block to arrive adds the partial tiles, always in CTA order
+            __threadfence();
+            __syncthreads();
+            if (tid < 2) {
+                // thread 0 looks after the CTA's first row block, thread 1 after its last
+                const uint32_t rb = tid == 0 ? rb_first : rb_last;
+                const bool in_group = rb >= rb0 && rb < rb0 + nparts && (tid == 0 || rb_last != rb_first);
+                const bool full = max(t_lo, rb * a.nseg) == rb * a.nseg && min(t_hi, (rb + 1) * a.nseg) == (rb + 1) * a.nseg;
+                uint32_t result = 0;
+                if (in_group && !full) {
+                    const uint32_t g = gridDim.x;
+                    const uint32_t c_first = (uint32_t)((((uint64_t)rb * a.nseg + 1) * g - 1) / T);
+                    const uint32_t c_last = (uint32_t)((((uint64_t)(rb + 1) * a.nseg) * g - 1) / T);
+                    const uint32_t n = min(c_last - c_first + 1u, kGemmMaxContrib);
+                    const uint32_t old = atomicAdd(a.counters + rb, 1u);
+                    if (old == n - 1u) {
+                        a.counters[rb] = 0u;
+                        for (uint32_t i = 0; i < n; i++) {
+                            const uint32_t c = c_first + i;
+                            const uint32_t c_rb_first = (uint32_t)(T * c / g) / a.nseg;
+                            contrib[tid * kGemmMaxContrib + i] = c * 2u + (c_rb_first == rb ? 0u : 1u);
+                        }
+                        result = n;
+                    }
+                }
+                flag[tid] = result;
+            }
+            __syncthreads();
+            const uint32_t n0 = flag[0], n1 = flag[1];
+            if (n0 | n1) __threadfence();
+            if (n0) gemm_sum_partials(a, rb_first, contrib, n0);
+            if (n1) gemm_sum_partials(a, rb_last, contrib + kGemmMaxContrib, n1);
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    __syncwarp();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
+static std::atomic<int> g_gemm_warps{0};        // 0 = as many as fit shared memory
+void set_gemm_warps(int v) { g_gemm_warps.store(v < 0 ? 0 : v); }
+
+uint32_t gemm_grid(uint32_t nrb, uint32_t nseg)
+{
+    const uint64_t T = (uint64_t)nrb * nseg;
+    return (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)device_sm_count(), T));
+}
+
+// x: [M, K] row-major, M <= 128.  fp32 and bf16 activations are first rounded to fp16 into `xhalf` ([128, K] fp16 scratch).
 int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *stream, const uint16_t *scales, const void *x,
-                   void *y, const float *bias, uint32_t *status, uint32_t N, uint32_t K, uint32_t group, uint32_t p, uint32_t nseg,
-                   uint32_t nrb, uint32_t M, int x_dtype, int y_dtype, void *stream_)
+                   void *xhalf, float *partials, uint32_t *counters, void *y, const float *bias, uint32_t *status, uint32_t N,
+                   uint32_t K, uint32_t group, uint32_t p, uint32_t nseg, uint32_t nrb, uint32_t M, int x_dtype, int y_dtype, void *stream_)
 {
     static std::mutex mu;
     static size_t attr_set[16] = {0};
-    const size_t smem = gemm_smem_bytes(p);
+    if (M == 0 || M > kGemmTokens) return (int)cudaErrorInvalidValue;
+    uint32_t warps = 16;
+    const int want = g_gemm_warps.load();
+    if (want >= 2 && want <= 16) warps = (uint32_t)want;
+    while (warps > 2 && gemm_smem_bytes(p, warps, M) > 227 * 1024) warps -= 2;
+    const size_t smem = gemm_smem_bytes(p, warps, M);
     if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
+    if (std::min<uint64_t>((uint64_t)nseg + 1, gemm_grid(nrb, nseg)) > kGemmMaxContrib) return (int)cudaErrorInvalidValue;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     {
         std::lock_guard<std::mutex> lock(mu);
-        if (attr_set[dev & 15] != smem) {
-            e = cudaFuncSetAttribute(gemm_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (attr_set[dev & 15] < smem) {
+            e = cudaFuncSetAttribute(gemm_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
             if (e != cudaSuccess) return (int)e;
-            attr_set[dev & 15] = smem;
+            attr_set[dev & 15] = 227 * 1024;
         }
     }
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
     GemmArgs a;
-    a.table = table; a.tiles = tiles; a.stream = stream; a.scales = scales; a.x = x; a.y = y; a.bias = bias; a.status = status;
-    a.N = N; a.K = K; a.group = group; a.p = p; a.nseg = nseg; a.nrb = nrb; a.M = M; a.x_dtype = x_dtype; a.y_dtype = y_dtype;
-    const uint32_t grid = max(1u, min((uint32_t)device_sm_count(), nrb));
-    gemm_tiles_kernel<<<grid, kGemmThreads, smem, reinterpret_cast<cudaStream_t>(stream_)>>>(a);
+    a.x = reinterpret_cast<const uint16_t *>(x);
+    if (x_dtype != EOQ_B200_F16) {
+        const size_t n = (size_t)M * K;
+        gemm_x_to_half_kernel<<<(unsigned)((n / 4 + 256) / 256), 256, 0, st>>>(x, x_dtype, reinterpret_cast<__half *>(xhalf), n);
+        g_launches++;
+        a.x = reinterpret_cast<const uint16_t *>(xhalf);
+    }
+    a.table = table; a.tiles = tiles; a.stream = stream; a.scales = scales; a.y = y; a.bias = bias;
+    a.partials = partials; a.counters = counters; a.status = status;
+    a.N = N; a.K = K; a.group = group; a.p = p; a.nseg = nseg; a.nrb = nrb; a.M = M;
+    a.y_dtype = y_dtype;
+    gemm_tiles_kernel<<<gemm_grid(nrb, nseg), warps * 32, smem, st>>>(a);
     g_launches++;
     return (int)cudaGetLastError();
 }

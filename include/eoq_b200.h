@@ -275,8 +275,10 @@ eoq_error_t eoq_b200_gemv(eoq_b200_weight_t *w, const void *x, int x_dtype, uint
  * when m is too large for the GEMV kernel: the compressed tiles are decoded once per 128
  * activation rows and the decoded fp16 pieces go from shared memory straight into tensor-core
  * MMAs (tcgen05, fp32 accumulator in tensor memory); the dequantised matrix never exists in
- * HBM.  x is [m, K], y is [m, N], row-major device pointers; x must be 16-byte aligned and is
- * rounded to fp16 before the product (weights are (q - 7) * scale in fp16).  INT4 weights in the
+ * HBM.  x is [m, K], y is [m, N], row-major device pointers, both 16-byte aligned; fp16
+ * activations enter the tensor cores as they are, fp32 and bf16 ones are rounded to fp16 first
+ * (the tensor cores take both operands in one 16-bit format, and the weights are
+ * (q - 7) * scale in fp16), so |x| must stay below 65504.  INT4 weights in the
  * default layout (3 weights per step) only; others return EOQ_ERR_UNSUPPORTED.  Asynchronous
  * on `stream`. */
 eoq_error_t eoq_b200_gemm(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t m,
