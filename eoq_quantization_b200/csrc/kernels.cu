@@ -12,6 +12,7 @@
 #include <atomic>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <mutex>
 
@@ -1114,7 +1115,7 @@ constexpr int kGemmMaxThreads = 512;
 constexpr uint32_t kGemmTokens = 128, kGemmRows = 96;
 constexpr uint32_t kXPieceBytes = kGemmTokens * 16 * 2, kWPieceBytes = kGemmRows * 16 * 2;
 constexpr uint32_t kGemmAccs = 4, kTmemCols = 128 * kGemmAccs;   // four accumulators, 128 columns apart (96 used): all of TMEM
-constexpr uint32_t kGemmMaxContrib = 160, kGemmCtlBytes = 256 + 2 * kGemmMaxContrib * 4;
+constexpr uint32_t kGemmMaxContrib = 160, kGemmCtlBytes = 384 + 2 * kGemmMaxContrib * 4;   // 1664: keeps the pieces 128-byte aligned
 constexpr uint32_t kGemmSlotFloats = kGemmTokens * kGemmRows;
 
 // bytes of one warp's X staging piece: the staged token rows, rounded up to 8
@@ -1160,7 +1161,6 @@ struct GemmArgs {
     const TileDesc *tiles;
     const uint8_t  *stream;
     const uint16_t *scales;
-    const uint16_t *x;        // [M, K] fp16, rows 16-byte aligned
     void           *y;        // [M, N]
     const float    *bias;
     float          *partials; // [grid][2][128][96]
@@ -1187,16 +1187,28 @@ __global__ void gemm_x_to_half_kernel(const void *x, int x_dtype, __half *out, s
 
 struct GemmWarp {             // per warp, warp-uniform
     uint32_t wp, xp;          // shared addresses of the W and X staging pieces
-    uint32_t mma_bar;
-    uint32_t np;              // pieces issued so far: piece i is the barrier's i-th completion
+    uint32_t mma_bar, x_bar;
+    uint32_t np;              // pieces issued so far: piece i is the i-th completion on both barriers
 };
 
+// Two tiled bulk copies bring one X piece: box = [rows of the batch rounded up to 8] x [8 columns = 16 bytes] each, so
+// that shared memory holds it as K-major core matrices (8 rows x 16 bytes, contiguous); rows past the batch are
+// filled with zeros by the copy.  Columns c..c+7 land at dst, c+8..c+15 behind them.
+__device__ __forceinline__ void gemm_fetch_x(const CUtensorMap *xmap, uint32_t dst, uint32_t half_bytes, uint32_t c, uint32_t bar)
+{
+    mbar_expect_tx(bar, 2u * half_bytes);
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(xmap)), "r"(c), "r"(0), "r"(bar) : "memory");
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst + half_bytes), "l"(reinterpret_cast<uint64_t>(xmap)), "r"(c + 8u), "r"(0), "r"(bar) : "memory");
+}
+
 // Decode 16 columns of the warp's tile into its W piece.  A few steps in, once the previous MMA is known to have read
-// both staging pieces, the copies of this piece's X are started so that they land while the rest decodes.
+// both staging pieces, the copy of this piece's X is started so that it lands while the rest decodes.
 template <bool RING>
 __device__ __forceinline__ void gemm_decode_piece(uint32_t tab_addr, uint32_t &x, WordState &ws, uint32_t mask, uint32_t p,
-                                                  const float (&sc)[3], const GemmWarp &gw, const uint16_t *xsrc, uint32_t K,
-                                                  uint32_t M, uint32_t lane, uint32_t *status, bool &dead)
+                                                  const float (&sc)[3], const GemmWarp &gw, const CUtensorMap *xmap, uint32_t c,
+                                                  uint32_t x_half_bytes, uint32_t lane, uint32_t *status, bool &dead)
 {
     using F = Fmt<3, 4>;
     using F0 = Int4Field<F::field_bit(0)>;
@@ -1217,12 +1229,7 @@ __device__ __forceinline__ void gemm_decode_piece(uint32_t tab_addr, uint32_t &x
             if (half == 0 && s == 3) {
                 // the previous MMA was issued four steps ago: it has read both staging pieces by now
                 if (gw.np > 0) gemm_wait(gw.mma_bar, (gw.np - 1u) & 1u, status, dead);
-                // 16-byte chunk q of the piece: token q / 2, columns 8 * (q % 2) ..
-                for (uint32_t q = lane; q < 2u * M; q += 32u) {
-                    const uint32_t t = q >> 1, h = q & 1u;
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(gw.xp + piece_offset(t, h * 8u)),
-                                 "l"(xsrc + (size_t)t * K + h * 8u) : "memory");
-                }
+                if (lane == 0) gemm_fetch_x(xmap, gw.xp, x_half_bytes, c, gw.x_bar);
             }
         }
 #pragma unroll
@@ -1295,21 +1302,25 @@ __device__ __forceinline__ void gemm_sum_partials(const GemmArgs &a, uint32_t rb
     }
 }
 
-__global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const GemmArgs a)
+__global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap xmap)
 {
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, nwarps = blockDim.x >> 5;
     uint32_t *tab = reinterpret_cast<uint32_t *>(smem);
     uint8_t *ctl = smem + smem_table_bytes(a.p);
     uint8_t *wp_base = ctl + kGemmCtlBytes;
-    uint8_t *xp_base = wp_base + nwarps * kWPieceBytes;
+    uint8_t *xp_base = wp_base + nwarps * kWPieceBytes;     // 128-byte aligned, as tiled bulk copies require
     uint8_t *ring_area = xp_base + nwarps * gemm_x_stride(a.M) + kXPieceBytes;
 
+    if ((smem_addr(xp_base) & 127u) != 0) {      // tiled bulk copies need 128-byte aligned destinations: refuse rather than fault
+        if (tid == 0) *a.status = 3u;
+        return;
+    }
     // control block: table barrier, TMEM slot, group barrier, ticket flags, per-warp barriers, two contributor lists
     const uint32_t tab_bar = smem_addr(ctl), slot_addr = smem_addr(ctl + 16), grp_bar = smem_addr(ctl + 32);
     volatile uint32_t *flag = reinterpret_cast<volatile uint32_t *>(ctl + 48);          // [2]
-    const uint32_t mma_bar0 = smem_addr(ctl + 64);
-    volatile uint32_t *contrib = reinterpret_cast<volatile uint32_t *>(ctl + 256);      // [2][kGemmMaxContrib]
+    const uint32_t mma_bar0 = smem_addr(ctl + 64), x_bar0 = smem_addr(ctl + 64 + 128);
+    volatile uint32_t *contrib = reinterpret_cast<volatile uint32_t *>(ctl + 384);      // [2][kGemmMaxContrib]
 
     // this CTA's range of tiles; the warp's first tile is requested before anything else
     const uint64_t T = (uint64_t)a.nrb * a.nseg;
@@ -1329,7 +1340,7 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
     if (tid == 0) {
         mbar_init(tab_bar, 1);
         mbar_init(grp_bar, nwarps);
-        for (uint32_t i = 0; i < nwarps; i++) mbar_init(mma_bar0 + i * 8, 1);
+        for (uint32_t i = 0; i < nwarps; i++) { mbar_init(mma_bar0 + i * 8, 1); mbar_init(x_bar0 + i * 8, 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         mbar_expect_tx(tab_bar, 4u << a.p);
         for (uint32_t off = 0; off < (4u << a.p); off += 16384u)
@@ -1356,7 +1367,9 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
     gw.wp = smem_addr(wp_base) + warp * kWPieceBytes;
     gw.xp = smem_addr(xp_base) + warp * gemm_x_stride(a.M);
     gw.mma_bar = mma_bar0 + warp * 8;
+    gw.x_bar = x_bar0 + warp * 8;
     gw.np = 0;
+    const uint32_t x_half_bytes = gemm_x_stride(a.M) / 2;      // one 8-column half of an X piece
     // warps 0..7: warp w owns TMEM lanes 32*(w%4).. (tokens) and columns 48*(w/4).. (weight rows of a block) of every
     // accumulator; it clears them before a group and reads them back after it
     const uint32_t tok = (warp & 3u) * 32u + lane, col0 = (warp >> 2) * 48u;
@@ -1421,15 +1434,16 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
                 }
                 if (ring_mode) {
                     ring_sync(ring, ws, lane);
-                    gemm_decode_piece<true>(tab_addr, x, ws, mask, p, sc, gw, a.x + c, a.K, a.M, lane, a.status, dead);
+                    gemm_decode_piece<true>(tab_addr, x, ws, mask, p, sc, gw, &xmap, c, x_half_bytes, lane, a.status, dead);
                 } else {
-                    gemm_decode_piece<false>(tab_addr, x, ws, mask, p, sc, gw, a.x + c, a.K, a.M, lane, a.status, dead);
+                    gemm_decode_piece<false>(tab_addr, x, ws, mask, p, sc, gw, &xmap, c, x_half_bytes, lane, a.status, dead);
                 }
-                asm volatile("cp.async.wait_all;" ::: "memory");
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
+                gemm_wait(gw.x_bar, gw.np & 1u, a.status, dead);
                 if (lane == 0) {
-                    umma_f16(d_tmem, umma_desc(gw.xp, 128, 256), umma_desc(gw.wp, 128, 256), idesc, 1u);
+                    // X piece: 8-row groups 128 bytes apart, its two column halves x_half_bytes apart
+                    umma_f16(d_tmem, umma_desc(gw.xp, x_half_bytes, 128), umma_desc(gw.wp, 128, 256), idesc, 1u);
                     umma_commit(gw.mma_bar);
                 }
                 gw.np++;
@@ -1525,6 +1539,9 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
 static std::atomic<int> g_gemm_warps{0};        // 0 = as many as fit shared memory
 void set_gemm_warps(int v) { g_gemm_warps.store(v < 0 ? 0 : v); }
 
@@ -1562,18 +1579,36 @@ int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *
     }
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
     GemmArgs a;
-    a.x = reinterpret_cast<const uint16_t *>(x);
+    const void *x16 = x;
     if (x_dtype != EOQ_B200_F16) {
         const size_t n = (size_t)M * K;
         gemm_x_to_half_kernel<<<(unsigned)((n / 4 + 256) / 256), 256, 0, st>>>(x, x_dtype, reinterpret_cast<__half *>(xhalf), n);
         g_launches++;
-        a.x = reinterpret_cast<const uint16_t *>(xhalf);
+        x16 = xhalf;
     }
+    // tensor map over X [M, K] fp16: boxes of (M rounded up to 8) rows x 8 columns, rows past M read as zeros
+    static EncodeTiledFn encode = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!encode) {
+            void *fn = nullptr;
+            cudaDriverEntryPointQueryResult qres;
+            e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+            if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) return (int)cudaErrorNotSupported;
+            encode = reinterpret_cast<EncodeTiledFn>(fn);
+        }
+    }
+    CUtensorMap xmap;
+    const cuuint64_t gdim[2] = {K, M}, gstride[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {8, gemm_x_stride(M) / 32}, estride[2] = {1, 1};
+    if (encode(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x16), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return (int)cudaErrorInvalidValue;
     a.table = table; a.tiles = tiles; a.stream = stream; a.scales = scales; a.y = y; a.bias = bias;
     a.partials = partials; a.counters = counters; a.status = status;
     a.N = N; a.K = K; a.group = group; a.p = p; a.nseg = nseg; a.nrb = nrb; a.M = M;
     a.y_dtype = y_dtype;
-    gemm_tiles_kernel<<<gemm_grid(nrb, nseg), warps * 32, smem, st>>>(a);
+    gemm_tiles_kernel<<<gemm_grid(nrb, nseg), warps * 32, smem, st>>>(a, xmap);
     g_launches++;
     return (int)cudaGetLastError();
 }
