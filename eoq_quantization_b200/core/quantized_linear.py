@@ -12,7 +12,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..fused import EOQWeight, dequant_packed, require_cuda
+from ..fused import GEMM_MAX_ROWS, EOQWeight, dequant_packed, require_cuda
 
 
 class QuantizedLinear(nn.Module):
@@ -130,8 +130,14 @@ class QuantizedLinear(nn.Module):
         require_cuda(x, "QuantizedLinear.forward")
         require_cuda(self.packed_weight, "QuantizedLinear.forward")
         rows = x.numel() // max(self.in_features, 1)
-        if self._fusable() and 1 <= rows <= 8 and x.dtype in (torch.float16, torch.bfloat16, torch.float32):
-            return self.eoq_weight().gemv(x, self.bias_param)
+        if self._fusable() and 1 <= rows <= GEMM_MAX_ROWS and x.dtype in (torch.float16, torch.bfloat16, torch.float32):
+            # up to 8 rows: fused decode + GEMV (fp32 accumulate, any of the three dtypes); up to GEMM_MAX_ROWS of
+            # 16-bit activations: fused decode + tensor-core MMA (operands fp16); beyond that, and for fp32
+            # activations, one dequantisation amortises over enough rows for a library GEMM to win
+            if rows <= 8:
+                return self.eoq_weight().gemv(x, self.bias_param)
+            if x.dtype != torch.float32:
+                return self.eoq_weight().gemm(x, self.bias_param)
         weight = dequant_packed(self.packed_weight, self.scales, self.out_features, self.in_features, self.bits,
                                 self.block_size, dtype=x.dtype if x.dtype in (torch.float16, torch.bfloat16) else torch.float32)
         bias = self.bias_param.to(x.dtype) if self.bias_param is not None else None

@@ -28,6 +28,11 @@ def require_cuda(t: torch.Tensor, what: str) -> None:
                            "(there is no CPU path)")
 
 
+# Rows up to which the reference-API modules use the fused tensor-core path: it decodes the weight once per 128 rows,
+# while the modules also keep the packed INT4 copy, from which one dequantisation + a library GEMM is cheaper beyond.
+GEMM_MAX_ROWS = 128
+
+
 class EOQWeight:
     """Owner of one ``eoq_b200_weight_t``."""
 

@@ -88,3 +88,25 @@ def test_tensor_core_gemm_70b_shape_slice():
     assert O.rel_l2(y.double().cpu().numpy(), ref16) < 1e-5
     assert O.rel_l2(y.double().cpu().numpy(), ref32) < 1e-3
     assert w.status() == 0
+
+
+def test_reference_modules_take_the_tensor_core_path_for_prefill_rows():
+    """QuantizedLinear / QuantizedLinearFast (core/quantized_linear.py:222-228, core/quantized_matmul.py:179-260) with
+    9..128 rows of 16-bit activations agree with dequantize-then-matmul."""
+    from eoq_quantization_b200.core.quantized_linear import QuantizedLinear
+    from eoq_quantization_b200.core.quantized_matmul import QuantizedLinearFast
+    torch.manual_seed(3)
+    lin = torch.nn.Linear(512, 300, bias=True)
+    ql = QuantizedLinear.from_float(lin).cuda()
+    fast = QuantizedLinearFast.from_quantized_linear(ql)
+    launches = L.lib().eoq_b200_launch_count()
+    for rows, dt in ((33, torch.float16), (128, torch.bfloat16), (2 * 40, torch.float16)):
+        x = torch.randn(rows, 512, device="cuda", dtype=dt)
+        want = torch.nn.functional.linear(x.float(), ql._dequantize_weight().float(), ql.bias_param.float())
+        for mod in (ql, fast):
+            y = mod(x)
+            assert y.dtype == dt and y.shape == (rows, 300)
+            assert O.rel_l2(y.float().cpu().numpy(), want.to(dt).float().cpu().numpy()) < (4e-3 if dt == torch.bfloat16 else 1e-3)
+    assert L.lib().eoq_b200_launch_count() > launches
+    y3 = ql(torch.randn(2, 20, 512, device="cuda", dtype=torch.float16))       # 40 rows through a 3-D input
+    assert y3.shape == (2, 20, 300)
