@@ -339,7 +339,8 @@ eoq_error_t eoq_b200_dequant_packed(const uint8_t *d_packed, const uint16_t *d_s
 eoq_error_t eoq_b200_weight_status(eoq_b200_weight_t *w, void *stream);
 
 /* Diagnostic knob for sweeps; returns 0 if the key is known.  Keys:
- * "gemv_ctas_per_sm" (0 = as many CTAs of the fused kernel as fit on an SM). */
+ * "gemv_ctas_per_sm" (0 = as many CTAs of the fused kernel as fit on an SM),
+ * "gemm_warps" (warps per CTA of the tensor-core kernel, 2..16; 0 = as many as fit). */
 int eoq_b200_tune(const char *key, int value);
 
 /* Number of kernels launched by this library since load (for benchmarks). */
