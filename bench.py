@@ -746,8 +746,12 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="plain launches instead of CUDA graphs (for profilers)")
+    ap.add_argument("--no-pdl", action="store_true", help="plain launches instead of programmatic dependent launches")
     ap.add_argument("--workload", default="mlp_pair", choices=["mlp_pair", "decode_dequant", "polar_q5", "llama7b_step", "prefill_gemm"])
     args = ap.parse_args()
+    if args.no_pdl and args.impl != "reference":
+        from eoq_quantization_b200 import _lib
+        _lib.lib().eoq_b200_tune(b"pdl", 0)
     if args.workload == "llama7b_step":
         return run_llama_step(args)
     if args.workload != "mlp_pair":

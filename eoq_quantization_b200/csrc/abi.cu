@@ -821,6 +821,7 @@ extern "C" int eoq_b200_tune(const char *key, int value)
     if (!key) return -1;
     if (std::strcmp(key, "gemv_ctas_per_sm") == 0) { set_gemv_ctas_per_sm(value); return 0; }
     if (std::strcmp(key, "gemm_warps") == 0) { set_gemm_warps(value); return 0; }
+    if (std::strcmp(key, "pdl") == 0) { set_pdl(value); return 0; }
     return -1;
 }
 

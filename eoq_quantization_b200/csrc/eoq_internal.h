@@ -132,5 +132,6 @@ size_t gemv_smem_bytes(uint32_t K, uint32_t p, uint32_t bt, uint32_t kind);
 uint64_t launch_counter();
 void set_gemv_ctas_per_sm(int v);
 void set_gemm_warps(int v);
+void set_pdl(int v);
 
 }  // namespace eoq

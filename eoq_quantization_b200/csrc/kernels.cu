@@ -497,6 +497,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
     // Prologue: everything that has to come from global memory is requested before anything is waited for --
     // the decode table (one bulk copy onto a barrier), x (vector loads into registers) and this warp's first tile
     // (descriptor, L2 prefetch, first ring chunks) -- so the prologue costs about one memory round trip.
+    // The launch may be programmatic (see launch_with_pdl): this grid can start while the previous kernel of the
+    // stream is still finishing.  Everything up to griddepcontrol.wait (barrier set-up, the table copy, the first
+    // tile descriptor) touches only this weight's read-only data; x, bias and all global writes come after it.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t tab_bar = smem_addr(smem + smem_table_bytes(a.p));
     if (tid == 0) {
         mbar_init(tab_bar, 1);
@@ -505,6 +509,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
         for (uint32_t off = 0; off < (4u << a.p); off += 16384u)
             bulk_copy_g2s(smem_addr(tab) + off, reinterpret_cast<const uint8_t *>(a.table) + off, min(16384u, (4u << a.p) - off), tab_bar);
     }
+    RingCtl ring;
+    ring_setup(ring, ring_area, warp, kWarps, lane, a.status);
+    uint32_t t = blockIdx.x + gridDim.x * warp;
+    bool have = t < a.ntiles;
+    TileDesc d;
+    if (have) d = a.tiles[t];                    // requested here, needed by tile_open below
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const bool x_vec = a.x_dtype != EOQ_B200_F32 && K % 16 == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0;
     const uint32_t vec_per_row = K / 8, nvec = vec_per_row * a.batch;
     constexpr int kXV = 3;                       // 16-byte x loads in flight per thread
@@ -514,16 +525,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
         for (int u = 0; u < kXV; u++)
             if (tid + u * kThreads < nvec) xq[u] = __ldg(reinterpret_cast<const uint4 *>(a.x) + tid + u * kThreads);
     }
-
-    RingCtl ring;
-    ring_setup(ring, ring_area, warp, kWarps, lane, a.status);
-    uint32_t t = blockIdx.x + gridDim.x * warp;
-    bool have = t < a.ntiles;
-    TileDesc d;
-    if (have) {
-        d = a.tiles[t];
-        tile_open(ring, d, a.stream + ((size_t)d.off64 << 6), lane);
-    }
+    if (have) tile_open(ring, d, a.stream + ((size_t)d.off64 << 6), lane);
     EOQ_STAMP(6);
 
     if (x_vec) {
@@ -706,6 +708,29 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
     }
 }
 
+// Programmatic dependent launch: the grid may be scheduled as soon as the previous kernel of the stream lets go of
+// SMs (its CTAs exit one by one while the last ones still reduce), so that this kernel's table copy and first tile
+// fetch overlap the other's tail.  The kernels order themselves with griddepcontrol.wait before they read an
+// input or write anything.  "pdl" = 0 in eoq_b200_tune falls back to plain launches.
+static std::atomic<int> g_pdl{1};
+void set_pdl(int v) { g_pdl.store(v != 0); }
+
+template <typename Kern, typename... Args>
+static cudaError_t launch_with_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl.load() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 // Launch configuration is resolved once per (kernel, device, shared-memory size) and cached,
 // so that a steady-state launch is nothing but the launch itself (and can be stream-captured).
 static std::atomic<int> g_gemv_ctas_per_sm{0};   // 0 = as many as fit
@@ -743,9 +768,9 @@ static int launch_gemv_cfg(const GemvArgs &a, cudaStream_t st)
     if (want > 0) per_sm = std::min(per_sm, want);
     uint32_t grid = (uint32_t)(c.sms * per_sm);
     grid = max(1u, min(grid, a.ntiles));
-    kern<<<grid, THREADS, smem, st>>>(a);
+    e = launch_with_pdl(kern, dim3(grid), dim3(THREADS), smem, st, a);
     g_launches++;
-    return (int)cudaGetLastError();
+    return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 // 16 warps per CTA, one CTA per SM.  CTAs of 24 and 32 warps (with proportionally more, shorter tiles) were
@@ -1326,6 +1351,7 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
     const uint64_t T = (uint64_t)a.nrb * a.nseg;
     const uint32_t t_lo = (uint32_t)(T * blockIdx.x / gridDim.x), t_hi = (uint32_t)(T * (blockIdx.x + 1) / gridDim.x);
     const uint32_t rb_first = t_lo / a.nseg, rb_last = (t_hi - 1u) / a.nseg;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     // see launch_with_pdl
     RingCtl ring;
     ring_setup(ring, ring_area, warp, nwarps, lane, a.status);
     uint32_t tile = t_lo + warp;
@@ -1359,6 +1385,8 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
     const uint32_t tmem_base = lds_u32(slot_addr);
     bool dead = false;       // a wait gave up: stop waiting, finish quickly, report through the status word
     gemm_wait(tab_bar, 0u, a.status, dead);
+    // nothing above read an input of this call or wrote global memory; X, bias, Y and the scratch come after this
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const uint32_t mask = (1u << a.p) - 1u, p = a.p, sgroups = a.K / a.group, tab_addr = smem_addr(tab);
     // fp32 accumulate, A = X and B = W both fp16 and K-major, N = 96, M = 128
@@ -1608,9 +1636,9 @@ int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *
     a.partials = partials; a.counters = counters; a.status = status;
     a.N = N; a.K = K; a.group = group; a.p = p; a.nseg = nseg; a.nrb = nrb; a.M = M;
     a.y_dtype = y_dtype;
-    gemm_tiles_kernel<<<gemm_grid(nrb, nseg), warps * 32, smem, st>>>(a, xmap);
+    e = launch_with_pdl(gemm_tiles_kernel, dim3(gemm_grid(nrb, nseg)), dim3(warps * 32), smem, st, a, xmap);
     g_launches++;
-    return (int)cudaGetLastError();
+    return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 }  // namespace eoq

@@ -340,7 +340,9 @@ eoq_error_t eoq_b200_weight_status(eoq_b200_weight_t *w, void *stream);
 
 /* Diagnostic knob for sweeps; returns 0 if the key is known.  Keys:
  * "gemv_ctas_per_sm" (0 = as many CTAs of the fused kernel as fit on an SM),
- * "gemm_warps" (warps per CTA of the tensor-core kernel, 2..16; 0 = as many as fit). */
+ * "gemm_warps" (warps per CTA of the tensor-core kernel, 2..16; 0 = as many as fit),
+ * "pdl" (1 = launch the fused kernels with programmatic stream serialisation so that their
+ * set-up overlaps the previous kernel's tail, the default; 0 = plain launches). */
 int eoq_b200_tune(const char *key, int value);
 
 /* Number of kernels launched by this library since load (for benchmarks). */
