@@ -45,6 +45,17 @@ __device__ __forceinline__ unsigned long long stamp_now() { unsigned long long t
 #else
 #define EOQ_STAMP(slot) do { } while (0)
 #endif
+#ifdef EOQ_STAMPS
+#define GEMM_STAMP(slot) do { if (lane == 0) reinterpret_cast<unsigned long long *>(a.status + 16)[(size_t)(blockIdx.x * 16 + warp) * 8 + (slot)] = stamp_now(); } while (0)
+#define GEMM_CYC_BEGIN() const long long cyc0__ = clock64()
+#define GEMM_CYC_END(acc) (acc) += clock64() - cyc0__
+#define GEMM_CYC_WRITE(slot, v) do { if (lane == 0) reinterpret_cast<unsigned long long *>(a.status + 16)[(size_t)(148 * 16 + blockIdx.x * 16 + warp) * 8 + (slot)] = (unsigned long long)(v); } while (0)
+#else
+#define GEMM_STAMP(slot) do { } while (0)
+#define GEMM_CYC_BEGIN() do { } while (0)
+#define GEMM_CYC_END(acc) do { } while (0)
+#define GEMM_CYC_WRITE(slot, v) do { } while (0)
+#endif
 
 
 // ---------------------------------------------------------------------------
@@ -118,22 +129,31 @@ __device__ __forceinline__ uint16_t ldg_u16_pinned(const uint16_t *p)
     return v;
 }
 
-// Geometry of the per-warp word ring (see "Streaming a tile's renormalisation words" below).
-constexpr uint32_t kRingRows = 64, kChunkRows = 16, kRingChunks = kRingRows / kChunkRows, kSyncSteps = 16;
-constexpr uint32_t kRingBytes = kRingRows * 64, kChunkBytes = kChunkRows * 64;
-static_assert(kMaxRingDrift + kSyncSteps + 1 + kChunkRows <= kRingRows, "ring too small for the drift bound");
+// Geometry of the per-warp word ring (see "Streaming a tile's renormalisation words" below): rows of 32 x u16,
+// filled in chunks, checked every kSync steps.  64 rows in four chunks is the least that covers the encoder's drift
+// bound.
+template <uint32_t ROWS, uint32_t CHUNK_ROWS, uint32_t SYNC>
+struct RingGeom {
+    static constexpr uint32_t kRows = ROWS, kChunkRows = CHUNK_ROWS, kChunks = ROWS / CHUNK_ROWS, kSync = SYNC;
+    static constexpr uint32_t kBytes = ROWS * 64, kChunkBytes = CHUNK_ROWS * 64;
+    static_assert(kMaxRingDrift + SYNC + 1 + CHUNK_ROWS <= ROWS, "ring too small for the drift bound");
+    static_assert((ROWS & (ROWS - 1)) == 0, "ring positions are taken modulo a power of two");
+};
+using RingSmall = RingGeom<64, 16, 16>;
 
-__host__ __device__ inline size_t ring_smem_bytes(uint32_t warps) { return (size_t)warps * (kRingBytes + kRingChunks * 8) + kRingBytes; }
+template <typename R>
+__host__ __device__ inline size_t ring_smem_bytes(uint32_t warps) { return (size_t)warps * (R::kBytes + R::kChunks * 8) + R::kBytes; }
 
 // Shared-memory carve-up of the fused kernel (bytes).
 __host__ __device__ inline size_t smem_table_bytes(uint32_t p) { return (size_t)4 << p; }
+template <typename R>
 static size_t gemv_smem_bytes_for(uint32_t K, uint32_t p, uint32_t bt, uint32_t kind, uint32_t threads)
 {
     size_t b = smem_table_bytes(p) + 16 + (size_t)K * bt * 4;      // table, its arrival barrier, x
     b += kind == EOQ_B200_KIND_Q5_POLAR ? 32 * 32 * 4 : (size_t)(K / 16) * bt * 4;
-    return b + ring_smem_bytes(threads / 32);
+    return b + ring_smem_bytes<R>(threads / 32);
 }
-size_t gemv_smem_bytes(uint32_t K, uint32_t p, uint32_t bt, uint32_t kind) { return gemv_smem_bytes_for(K, p, bt, kind, kThreads); }
+size_t gemv_smem_bytes(uint32_t K, uint32_t p, uint32_t bt, uint32_t kind) { return gemv_smem_bytes_for<RingSmall>(K, p, bt, kind, kThreads); }
 
 // One rANS step: table lookup, state update; returns the entry.
 __device__ __forceinline__ uint32_t rans_step(const uint32_t *tab, uint32_t &x, uint32_t mask, uint32_t p, uint32_t bias_mask)
@@ -172,11 +192,11 @@ __device__ __forceinline__ void rans_step_int4(uint32_t tab_addr, uint32_t &x, u
 // ---------------------------------------------------------------------------
 // Streaming a tile's renormalisation words.
 //
-// Ring mode (the normal case): each warp owns a 4 KB ring in shared memory (64 rows of
-// 32 x u16) filled by bulk asynchronous copies (cp.async.bulk, the 1-D TMA path) of 1 KB
+// Ring mode (the normal case): each warp owns a ring in shared memory (RingGeom: 64 or 128 rows
+// of 32 x u16) filled by bulk asynchronous copies (cp.async.bulk, the 1-D TMA path) of four
 // chunks, each completing on its own mbarrier.  Lane l reads column l; `koff` is 64 x the row
 // of the word the lane currently holds in `w`, counted from the warp's first chunk so that
-// ring position = koff mod 4096 across tiles.  Every kSyncSteps steps the warp takes the min and
+// ring position = koff mod ring bytes across tiles.  Every kSync steps the warp takes the min and
 // max of koff over its lanes: chunks wholly below the min are refilled, and the chunk the
 // fastest lane can reach before the next check is waited for.  The host encoder guarantees that
 // lanes of a ring-mode tile never drift more than kMaxRingDrift rows apart, which is what makes
@@ -218,7 +238,9 @@ struct WordState {            // per lane
     uint32_t c64, c1;         // the constants 64 and 1 in registers the compiler cannot see through
 };
 
-struct RingCtl {              // per warp (all fields warp-uniform)
+template <typename R>
+struct RingCtlT {             // per warp (all fields warp-uniform)
+    using Geom = R;
     uint32_t ring_base, bar0; // shared addresses
     uint32_t issued, ready;   // chunks issued / known complete since the kernel started
     uint32_t tile_first, tile_last, tile_bytes;  // chunk range [first, last) and byte length of the open tile
@@ -226,16 +248,17 @@ struct RingCtl {              // per warp (all fields warp-uniform)
     uint32_t *status;
 };
 
-__device__ __forceinline__ void ring_setup(RingCtl &r, uint8_t *ring_area, uint32_t warp, uint32_t nwarps, uint32_t lane, uint32_t *status)
+template <typename R>
+__device__ __forceinline__ void ring_setup(RingCtlT<R> &r, uint8_t *ring_area, uint32_t warp, uint32_t nwarps, uint32_t lane, uint32_t *status)
 {
-    const uint32_t base = (smem_addr(ring_area) + kRingBytes - 1) & ~(kRingBytes - 1);
-    r.ring_base = base + warp * kRingBytes;
-    r.bar0 = base + nwarps * kRingBytes + warp * kRingChunks * 8;
+    const uint32_t base = (smem_addr(ring_area) + R::kBytes - 1) & ~(R::kBytes - 1);
+    r.ring_base = base + warp * R::kBytes;
+    r.bar0 = base + nwarps * R::kBytes + warp * R::kChunks * 8;
     r.issued = r.ready = 0;
     r.status = status;
     if (lane == 0) {
 #pragma unroll
-        for (uint32_t i = 0; i < kRingChunks; i++) mbar_init(r.bar0 + i * 8, 1);
+        for (uint32_t i = 0; i < R::kChunks; i++) mbar_init(r.bar0 + i * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
@@ -249,14 +272,15 @@ __device__ __forceinline__ uint32_t lds_u32(uint32_t addr)
 }
 
 // Start copies for every chunk of the current tile below `limit` that has not been started yet.
-__device__ __forceinline__ void ring_issue(RingCtl &r, uint32_t limit, uint32_t lane)
+template <typename R>
+__device__ __forceinline__ void ring_issue(RingCtlT<R> &r, uint32_t limit, uint32_t lane)
 {
     while (r.issued < limit) {
         if (lane == 0) {
-            const uint32_t c = r.issued - r.tile_first, slot = r.issued % kRingChunks;
-            const uint32_t bytes = min(kChunkBytes, r.tile_bytes - c * kChunkBytes);
+            const uint32_t c = r.issued - r.tile_first, slot = r.issued % R::kChunks;
+            const uint32_t bytes = min(R::kChunkBytes, r.tile_bytes - c * R::kChunkBytes);
             mbar_expect_tx(r.bar0 + slot * 8, bytes);
-            bulk_copy_g2s(r.ring_base + slot * kChunkBytes, r.src + (size_t)c * kChunkBytes, bytes, r.bar0 + slot * 8);
+            bulk_copy_g2s(r.ring_base + slot * R::kChunkBytes, r.src + (size_t)c * R::kChunkBytes, bytes, r.bar0 + slot * 8);
         }
         r.issued++;
     }
@@ -264,14 +288,29 @@ __device__ __forceinline__ void ring_issue(RingCtl &r, uint32_t limit, uint32_t 
 
 // Keep the ring ahead of the readers.  Two warp votes against warp-uniform thresholds: a chunk is
 // refilled once every lane has left the chunk it replaces, and the next chunk is waited for as soon as
-// any lane could reach it within kSyncSteps steps.
-__device__ __forceinline__ void ring_sync(RingCtl &r, const WordState &s, uint32_t lane)
+// any lane could reach it within kSync steps.
+template <typename R>
+__device__ __forceinline__ void ring_sync(RingCtlT<R> &r, const WordState &s, uint32_t lane)
 {
     // chunk numbers count from the warp's first chunk of the kernel; koff is in the same frame
-    while (r.issued < r.tile_last && __all_sync(0xffffffffu, s.koff >= (r.issued + 1 - kRingChunks) * kChunkBytes))
+    while (r.issued < r.tile_last && __all_sync(0xffffffffu, s.koff >= (r.issued + 1 - R::kChunks) * R::kChunkBytes))
         ring_issue(r, r.issued + 1, lane);
-    while (r.ready < r.issued && __any_sync(0xffffffffu, s.koff + (kSyncSteps + 1) * 64 >= r.ready * kChunkBytes)) {
-        mbar_wait_bounded(r.bar0 + (r.ready % kRingChunks) * 8, (r.ready / kRingChunks) & 1u, r.status);
+    while (r.ready < r.issued && __any_sync(0xffffffffu, s.koff + (R::kSync + 1) * 64 >= r.ready * R::kChunkBytes)) {
+        mbar_wait_bounded(r.bar0 + (r.ready % R::kChunks) * 8, (r.ready / R::kChunks) & 1u, r.status);
+        r.ready++;
+    }
+}
+
+// The same between two checks at most kSync = one chunk of steps apart: lanes consume at most one row per step,
+// so at most one chunk is freed and at most one more is needed -- one vote each instead of a loop.
+template <typename R>
+__device__ __forceinline__ void ring_sync_step(RingCtlT<R> &r, const WordState &s, uint32_t lane)
+{
+    static_assert(R::kSync <= R::kChunkRows, "a check period may not span more than one chunk");
+    if (r.issued < r.tile_last && __all_sync(0xffffffffu, s.koff >= (r.issued + 1 - R::kChunks) * R::kChunkBytes))
+        ring_issue(r, r.issued + 1, lane);
+    if (r.ready < r.issued && __any_sync(0xffffffffu, s.koff + (R::kSync + 1) * 64 >= r.ready * R::kChunkBytes)) {
+        mbar_wait_bounded(r.bar0 + (r.ready % R::kChunks) * 8, (r.ready / R::kChunks) & 1u, r.status);
         r.ready++;
     }
 }
@@ -279,31 +318,33 @@ __device__ __forceinline__ void ring_sync(RingCtl &r, const WordState &s, uint32
 // Open a tile: ask L2 for all of it and, in ring mode, start its first copies.  Waits for nothing, so it
 // can run well before the tile is decoded (before the kernel's prologue, or while the previous tile's
 // results are being written).  The whole tile goes through the ring, its 128-byte state header included.
-__device__ __forceinline__ void tile_open(RingCtl &r, const TileDesc &d, const uint8_t *base, uint32_t lane)
+template <typename R>
+__device__ __forceinline__ void tile_open(RingCtlT<R> &r, const TileDesc &d, const uint8_t *base, uint32_t lane)
 {
     if (lane == 0) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base), "r"(d.len64 << 6) : "memory");
     if ((d.seg & kTileDirectFlag) == 0) {
         r.tile_first = r.issued;
         r.tile_bytes = d.len64 << 6;
-        r.tile_last = r.tile_first + (r.tile_bytes + kChunkBytes - 1) / kChunkBytes;
+        r.tile_last = r.tile_first + (r.tile_bytes + R::kChunkBytes - 1) / R::kChunkBytes;
         r.src = base;
-        ring_issue(r, min(r.tile_last, r.tile_first + kRingChunks), lane);
+        ring_issue(r, min(r.tile_last, r.tile_first + R::kChunks), lane);
     }
 }
 
 // Begin decoding an opened tile: wait for its first chunk, read the lane's state and first word.
 // Returns true if the tile runs in ring mode.
-__device__ __forceinline__ bool tile_begin(RingCtl &r, WordState &s, const TileDesc &d, const uint8_t *base, uint32_t lane, uint32_t &x)
+template <typename R>
+__device__ __forceinline__ bool tile_begin(RingCtlT<R> &r, WordState &s, const TileDesc &d, const uint8_t *base, uint32_t lane, uint32_t &x)
 {
     const bool ring = (d.seg & kTileDirectFlag) == 0;
     if (ring) {
-        const uint32_t start = r.tile_first * kChunkBytes;
+        const uint32_t start = r.tile_first * R::kChunkBytes;
         s.koff = start + 128;                                   // word row 0 sits behind the two header rows
         s.ring_lane = r.ring_base | (lane * 2);
         asm volatile("mov.b32 %0, 64;\n\tmov.b32 %1, 1;" : "=r"(s.c64), "=r"(s.c1));
         ring_sync(r, s, lane);
-        x = lds_u32(r.ring_base + (start & (kRingBytes - 1)) + lane * 4);
-        s.w = lds_u16((s.koff & (kRingBytes - 1)) | s.ring_lane);
+        x = lds_u32(r.ring_base + (start & (R::kBytes - 1)) + lane * 4);
+        s.w = lds_u16((s.koff & (R::kBytes - 1)) | s.ring_lane);
     } else {
         x = __ldg(reinterpret_cast<const uint32_t *>(base) + lane);
         s.ptr = reinterpret_cast<const uint16_t *>(base + 128) + lane;
@@ -312,17 +353,18 @@ __device__ __forceinline__ bool tile_begin(RingCtl &r, WordState &s, const TileD
     return ring;
 }
 
-__device__ __forceinline__ void tile_end(RingCtl &r, bool ring)
+template <typename R>
+__device__ __forceinline__ void tile_end(RingCtlT<R> &r, bool ring)
 {
     if (!ring) return;
     while (r.ready < r.issued) {       // nothing of this tile may still be in flight when the next one starts
-        mbar_wait_bounded(r.bar0 + (r.ready % kRingChunks) * 8, (r.ready / kRingChunks) & 1u, r.status);
+        mbar_wait_bounded(r.bar0 + (r.ready % R::kChunks) * 8, (r.ready / R::kChunks) & 1u, r.status);
         r.ready++;
     }
 }
 
 // Renormalise: at most one 16-bit word per step, since p <= 16.
-template <bool RING>
+template <bool RING, uint32_t RING_BYTES = RingSmall::kBytes>
 __device__ __forceinline__ void rans_renorm(uint32_t &x, WordState &s)
 {
     if (RING) {
@@ -334,7 +376,7 @@ __device__ __forceinline__ void rans_renorm(uint32_t &x, WordState &s)
                      "@p lop3.b32 t, %2, %4, %3, 0xEA;\n\t"
                      "@p ld.shared.u16 %1, [t];\n\t}"
                      : "+r"(x), "+r"(s.w), "+r"(s.koff)
-                     : "r"(s.ring_lane), "n"(kRingBytes - 1), "r"(s.c64), "r"(s.c1));
+                     : "r"(s.ring_lane), "n"(RING_BYTES - 1), "r"(s.c64), "r"(s.c1));
     } else if (x < 65536u) {
         x = (x << 16) | s.w;
         s.ptr += 32;
@@ -356,10 +398,10 @@ __device__ __forceinline__ void rans_renorm(uint32_t &x, WordState &s)
 // not depend on scheduling.
 // ---------------------------------------------------------------------------
 // The column loop of one tile: decode, unpack, multiply-accumulate, fold per scale group.
-template <int G, int BITS, int BT, int KIND, bool RING, int UNROLL>
+template <int G, int BITS, int BT, int KIND, bool RING, int UNROLL, typename R>
 __device__ __forceinline__ void gemv_tile_columns(const GemvArgs &a, const TileDesc &d, const uint32_t *tab, const float *xs,
                                                   const float *aux, uint32_t lane, uint32_t row, uint32_t mask, uint32_t p,
-                                                  uint32_t sgroups, uint32_t &x, WordState &ws, RingCtl &ring, float (&y)[G][BT])
+                                                  uint32_t sgroups, uint32_t &x, WordState &ws, RingCtlT<R> &ring, float (&y)[G][BT])
 {
     using F = Fmt<G, BITS>;
     const uint32_t magic0 = Int4Field<F::field_bit(0)>::magic_reg();
@@ -391,8 +433,8 @@ __device__ __forceinline__ void gemv_tile_columns(const GemvArgs &a, const TileD
 
 #pragma unroll UNROLL
             for (; c < rend; c += 4) {
-                // runs start on multiples of 16 columns, so this fires every kSyncSteps = 16 steps
-                if (RING && (c & 12u) == 0) ring_sync(ring, ws, lane);
+                // runs start on multiples of 16 columns, so this fires at least every kSync (16 or 32) steps
+                if (RING && (c & (R::kSync - 4u)) == 0) ring_sync_step(ring, ws, lane);
                 float xv[4][BT];
                 if (BT == 1) {
                     const float4 v = *reinterpret_cast<const float4 *>(xs + c);
@@ -448,7 +490,7 @@ __device__ __forceinline__ void gemv_tile_columns(const GemvArgs &a, const TileD
                             for (int b = 0; b < BT; b++) acc[j][b] = fmaf(m, xv[s][b], acc[j][b]);
                         }
                     }
-                    rans_renorm<RING>(x, ws);
+                    rans_renorm<RING, R::kBytes>(x, ws);
                 }
             }
 
@@ -479,7 +521,7 @@ __device__ __forceinline__ void gemv_tile_columns(const GemvArgs &a, const TileD
 
 }
 
-template <int G, int BITS, int BT, int KIND, int THREADS>
+template <int G, int BITS, int BT, int KIND, int THREADS, typename R>
 __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a)
 {
     constexpr int kThreads = THREADS, kWarps = THREADS / 32;
@@ -509,7 +551,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
         for (uint32_t off = 0; off < (4u << a.p); off += 16384u)
             bulk_copy_g2s(smem_addr(tab) + off, reinterpret_cast<const uint8_t *>(a.table) + off, min(16384u, (4u << a.p) - off), tab_bar);
     }
-    RingCtl ring;
+    RingCtlT<R> ring;
     ring_setup(ring, ring_area, warp, kWarps, lane, a.status);
     uint32_t t = blockIdx.x + gridDim.x * warp;
     bool have = t < a.ntiles;
@@ -736,14 +778,14 @@ static cudaError_t launch_with_pdl(Kern kern, dim3 grid, dim3 block, size_t smem
 static std::atomic<int> g_gemv_ctas_per_sm{0};   // 0 = as many as fit
 void set_gemv_ctas_per_sm(int v) { g_gemv_ctas_per_sm.store(v < 0 ? 0 : v); }
 
-template <int G, int BITS, int BT, int KIND, int THREADS>
+template <int G, int BITS, int BT, int KIND, int THREADS, typename R>
 static int launch_gemv_cfg(const GemvArgs &a, cudaStream_t st)
 {
     struct Cfg { size_t smem = 0; int per_sm = 0, sms = 0; };
     static Cfg cfg[16];
     static std::mutex mu;
-    auto kern = gemv_tiles_kernel<G, BITS, BT, KIND, THREADS>;
-    const size_t smem = gemv_smem_bytes_for(a.K, a.p, BT, KIND, THREADS);
+    auto kern = gemv_tiles_kernel<G, BITS, BT, KIND, THREADS, R>;
+    const size_t smem = gemv_smem_bytes_for<R>(a.K, a.p, BT, KIND, THREADS);
     if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -779,7 +821,9 @@ static int launch_gemv_cfg(const GemvArgs &a, cudaStream_t st)
 template <int G, int BITS, int BT, int KIND>
 static int launch_gemv_one(const GemvArgs &a, cudaStream_t st)
 {
-    return launch_gemv_cfg<G, BITS, BT, KIND, kThreads>(a, st);
+    // A 128-row ring checked every 32 steps (RingGeom<128, 32, 32>) was measured for batch 1: within 1 % on
+    // 11008x4096 and 8 % slower on 4096x11008, so every launch uses the 64-row ring.
+    return launch_gemv_cfg<G, BITS, BT, KIND, kThreads, RingSmall>(a, st);
 }
 
 template <int G, int BITS, int KIND>
@@ -822,7 +866,7 @@ __global__ void __launch_bounds__(256) decode_tiles_kernel(const DecodeArgs a)
     const uint32_t K = a.K, M = 1u << a.p;
     for (uint32_t i = tid * 4; i < M; i += blockDim.x * 4)
         *reinterpret_cast<uint4 *>(tab + i) = __ldg(reinterpret_cast<const uint4 *>(a.table + i));
-    RingCtl ring;
+    RingCtlT<RingSmall> ring;
     ring_setup(ring, smem + smem_table_bytes(a.p), warp, nwarps, lane, a.status);
     __syncthreads();
 
@@ -840,7 +884,7 @@ __global__ void __launch_bounds__(256) decode_tiles_kernel(const DecodeArgs a)
             if (ring_mode) {
 #pragma unroll
                 for (int s = 0; s < 8; s++) {
-                    if (s == 0 && ((c - d.col0) & 8u) == 0) ring_sync(ring, ws, lane);
+                    if (s == 0 && ((c - d.col0) & 8u) == 0) ring_sync_step(ring, ws, lane);
                     const uint32_t e = rans_step(tab, x, mask, p, F::kBiasMask);
 #pragma unroll
                     for (int j = 0; j < G; j++) sym[j][s] = (e >> F::field_bit(j)) & F::kFieldMask;
@@ -904,7 +948,7 @@ __global__ void __launch_bounds__(256) decode_tiles_kernel(const DecodeArgs a)
 template <int G, int BITS, int KIND>
 static int launch_decode_tiles_t(const DecodeArgs &a, cudaStream_t st)
 {
-    const size_t smem = smem_table_bytes(a.p) + ring_smem_bytes(256 / 32);
+    const size_t smem = smem_table_bytes(a.p) + ring_smem_bytes<RingSmall>(256 / 32);
     auto kern = decode_tiles_kernel<G, BITS, KIND>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -1149,7 +1193,7 @@ __host__ __device__ inline uint32_t gemm_x_stride(uint32_t m) { return ((m + 7u)
 size_t gemm_smem_bytes(uint32_t p, uint32_t warps, uint32_t m)
 {
     // the last warp's MMA reads a full 128-row piece: keep that much behind the last staged piece
-    return smem_table_bytes(p) + kGemmCtlBytes + (size_t)warps * (kWPieceBytes + gemm_x_stride(m)) + kXPieceBytes + ring_smem_bytes(warps);
+    return smem_table_bytes(p) + kGemmCtlBytes + (size_t)warps * (kWPieceBytes + gemm_x_stride(m)) + kXPieceBytes + ring_smem_bytes<RingSmall>(warps);
 }
 size_t gemm_partial_bytes(uint32_t grid) { return (size_t)grid * 2 * kGemmSlotFloats * sizeof(float); }
 
@@ -1233,7 +1277,7 @@ __device__ __forceinline__ void gemm_fetch_x(const CUtensorMap *xmap, uint32_t d
 template <bool RING>
 __device__ __forceinline__ void gemm_decode_piece(uint32_t tab_addr, uint32_t &x, WordState &ws, uint32_t mask, uint32_t p,
                                                   const float (&sc)[3], const GemmWarp &gw, const CUtensorMap *xmap, uint32_t c,
-                                                  uint32_t x_half_bytes, uint32_t lane, uint32_t *status, bool &dead)
+                                                  uint32_t x_half_bytes, uint32_t lane, uint32_t *status, bool &dead, long long (&cyc)[4])
 {
     using F = Fmt<3, 4>;
     using F0 = Int4Field<F::field_bit(0)>;
@@ -1253,8 +1297,13 @@ __device__ __forceinline__ void gemm_decode_piece(uint32_t tab_addr, uint32_t &x
             rans_renorm<RING>(x, ws);
             if (half == 0 && s == 3) {
                 // the previous MMA was issued four steps ago: it has read both staging pieces by now
-                if (gw.np > 0) gemm_wait(gw.mma_bar, (gw.np - 1u) & 1u, status, dead);
-                if (lane == 0) gemm_fetch_x(xmap, gw.xp, x_half_bytes, c, gw.x_bar);
+                {
+                    GEMM_CYC_BEGIN();
+                    if (gw.np > 0) gemm_wait(gw.mma_bar, (gw.np - 1u) & 1u, status, dead);
+                    if (lane == 0) gemm_fetch_x(xmap, gw.xp, x_half_bytes, c, gw.x_bar);
+                    __syncwarp();
+                    GEMM_CYC_END(cyc[0]);
+                }
             }
         }
 #pragma unroll
@@ -1352,7 +1401,8 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
     const uint32_t t_lo = (uint32_t)(T * blockIdx.x / gridDim.x), t_hi = (uint32_t)(T * (blockIdx.x + 1) / gridDim.x);
     const uint32_t rb_first = t_lo / a.nseg, rb_last = (t_hi - 1u) / a.nseg;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     // see launch_with_pdl
-    RingCtl ring;
+    GEMM_STAMP(0);
+    RingCtlT<RingSmall> ring;
     ring_setup(ring, ring_area, warp, nwarps, lane, a.status);
     uint32_t tile = t_lo + warp;
     const uint32_t g0_hi = min(t_hi, (rb_first + kGemmAccs) * a.nseg);
@@ -1387,6 +1437,7 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
     gemm_wait(tab_bar, 0u, a.status, dead);
     // nothing above read an input of this call or wrote global memory; X, bias, Y and the scratch come after this
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    GEMM_STAMP(1);
 
     const uint32_t mask = (1u << a.p) - 1u, p = a.p, sgroups = a.K / a.group, tab_addr = smem_addr(tab);
     // fp32 accumulate, A = X and B = W both fp16 and K-major, N = 96, M = 128
@@ -1397,6 +1448,7 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
     gw.mma_bar = mma_bar0 + warp * 8;
     gw.x_bar = x_bar0 + warp * 8;
     gw.np = 0;
+    long long cyc[4] = {0, 0, 0, 0};      // debug builds: cycles in the per-piece synchronisation points
     const uint32_t x_half_bytes = gemm_x_stride(a.M) / 2;      // one 8-column half of an X piece
     // warps 0..7: warp w owns TMEM lanes 32*(w%4).. (tokens) and columns 48*(w/4).. (weight rows of a block) of every
     // accumulator; it clears them before a group and reads them back after it
@@ -1434,6 +1486,7 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
             uint32_t x;
             WordState ws;
             const bool ring_mode = tile_begin(ring, ws, d, base, lane, x);
+            if (gw.np == 0) GEMM_STAMP(2);
             // ask L2 for the warp's next tile while this one decodes
             const uint32_t next = tile + nwarps;
             if (next < g_hi && lane == 0) {
@@ -1461,18 +1514,31 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
                     }
                 }
                 if (ring_mode) {
-                    ring_sync(ring, ws, lane);
-                    gemm_decode_piece<true>(tab_addr, x, ws, mask, p, sc, gw, &xmap, c, x_half_bytes, lane, a.status, dead);
+                    {
+                        GEMM_CYC_BEGIN();
+                        ring_sync_step(ring, ws, lane);
+                        GEMM_CYC_END(cyc[1]);
+                    }
+                    gemm_decode_piece<true>(tab_addr, x, ws, mask, p, sc, gw, &xmap, c, x_half_bytes, lane, a.status, dead, cyc);
                 } else {
-                    gemm_decode_piece<false>(tab_addr, x, ws, mask, p, sc, gw, &xmap, c, x_half_bytes, lane, a.status, dead);
+                    gemm_decode_piece<false>(tab_addr, x, ws, mask, p, sc, gw, &xmap, c, x_half_bytes, lane, a.status, dead, cyc);
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                gemm_wait(gw.x_bar, gw.np & 1u, a.status, dead);
-                if (lane == 0) {
-                    // X piece: 8-row groups 128 bytes apart, its two column halves x_half_bytes apart
-                    umma_f16(d_tmem, umma_desc(gw.xp, x_half_bytes, 128), umma_desc(gw.wp, 128, 256), idesc, 1u);
-                    umma_commit(gw.mma_bar);
+                {
+                    GEMM_CYC_BEGIN();
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    gemm_wait(gw.x_bar, gw.np & 1u, a.status, dead);
+                    GEMM_CYC_END(cyc[2]);
+                }
+                {
+                    GEMM_CYC_BEGIN();
+                    if (lane == 0) {
+                        // X piece: 8-row groups 128 bytes apart, its two column halves x_half_bytes apart
+                        umma_f16(d_tmem, umma_desc(gw.xp, x_half_bytes, 128), umma_desc(gw.wp, 128, 256), idesc, 1u);
+                        umma_commit(gw.mma_bar);
+                    }
+                    __syncwarp();
+                    GEMM_CYC_END(cyc[3]);
                 }
                 gw.np++;
             }
@@ -1484,11 +1550,13 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
                 tile_open(ring, d, a.stream + ((size_t)d.off64 << 6), lane);
             }
         }
+        GEMM_STAMP(3);
         // every MMA this warp issued for the group is behind this commit
         if (lane == 0) umma_commit(grp_bar);
         __syncwarp();
         gemm_wait(grp_bar, grp & 1u, a.status, dead);
         __syncwarp();
+        GEMM_STAMP(4);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
         // a CTA's first row block and its last are the only ones it can share with other CTAs: partial slots 0 and 1
@@ -1525,6 +1593,7 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
                 }
             }
         }
+        GEMM_STAMP(5);
         if (shared_any) {
             // tickets: the last contributor of a row block to arrive adds the partial tiles, always in CTA order
             __threadfence();
@@ -1555,12 +1624,15 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
             }
             __syncthreads();
             const uint32_t n0 = flag[0], n1 = flag[1];
+            GEMM_STAMP(6);
             if (n0 | n1) __threadfence();
             if (n0) gemm_sum_partials(a, rb_first, contrib, n0);
             if (n1) gemm_sum_partials(a, rb_last, contrib + kGemmMaxContrib, n1);
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
+    GEMM_STAMP(7);
+    GEMM_CYC_WRITE(0, cyc[0]); GEMM_CYC_WRITE(1, cyc[1]); GEMM_CYC_WRITE(2, cyc[2]); GEMM_CYC_WRITE(3, cyc[3]); GEMM_CYC_WRITE(4, gw.np);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     __syncwarp();
