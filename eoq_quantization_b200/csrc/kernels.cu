@@ -1396,31 +1396,33 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
     const uint32_t mma_bar0 = smem_addr(ctl + 64), x_bar0 = smem_addr(ctl + 64 + 128);
     volatile uint32_t *contrib = reinterpret_cast<volatile uint32_t *>(ctl + 384);      // [2][kGemmMaxContrib]
 
-    // this CTA's range of tiles; the warp's first tile is requested before anything else
+    // Everything that has to come from global memory is requested before anything is waited for: the decode table
+    // (bulk copy onto a barrier), then each warp's first tile (descriptor, L2 prefetch, first ring chunks).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     // see launch_with_pdl
+    GEMM_STAMP(0);
+    if (tid == 0) {
+        mbar_init(tab_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_expect_tx(tab_bar, 4u << a.p);
+        for (uint32_t off = 0; off < (4u << a.p); off += 16384u)
+            bulk_copy_g2s(smem_addr(tab) + off, reinterpret_cast<const uint8_t *>(a.table) + off, min(16384u, (4u << a.p) - off), tab_bar);
+    }
+    // this CTA's range of tiles
     const uint64_t T = (uint64_t)a.nrb * a.nseg;
     const uint32_t t_lo = (uint32_t)(T * blockIdx.x / gridDim.x), t_hi = (uint32_t)(T * (blockIdx.x + 1) / gridDim.x);
     const uint32_t rb_first = t_lo / a.nseg, rb_last = (t_hi - 1u) / a.nseg;
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     // see launch_with_pdl
-    GEMM_STAMP(0);
     RingCtlT<RingSmall> ring;
     ring_setup(ring, ring_area, warp, nwarps, lane, a.status);
     uint32_t tile = t_lo + warp;
     const uint32_t g0_hi = min(t_hi, (rb_first + kGemmAccs) * a.nseg);
     bool have = tile < g0_hi;
     TileDesc d;
-    if (have) {
-        d = a.tiles[tile];
-        tile_open(ring, d, a.stream + ((size_t)d.off64 << 6), lane);
-    }
+    if (have) d = a.tiles[tile];           // requested here, needed by tile_open below
 
     if (tid == 0) {
-        mbar_init(tab_bar, 1);
         mbar_init(grp_bar, nwarps);
         for (uint32_t i = 0; i < nwarps; i++) { mbar_init(mma_bar0 + i * 8, 1); mbar_init(x_bar0 + i * 8, 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        mbar_expect_tx(tab_bar, 4u << a.p);
-        for (uint32_t off = 0; off < (4u << a.p); off += 16384u)
-            bulk_copy_g2s(smem_addr(tab) + off, reinterpret_cast<const uint8_t *>(a.table) + off, min(16384u, (4u << a.p) - off), tab_bar);
     }
     // the .sync.aligned tensor-memory instructions below need the whole warp at the same instruction: lanes that took
     // a lane-0-only branch or left a polling loop at different times are brought back together first
@@ -1429,6 +1431,7 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_addr), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    if (have) tile_open(ring, d, a.stream + ((size_t)d.off64 << 6), lane);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
