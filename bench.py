@@ -234,13 +234,30 @@ def run_gpu_arm(args):
     g = torch.Generator(device="cuda").manual_seed(1234)
     xs = [torch.randn(1, K_UP, device="cuda", generator=g).half(), torch.randn(1, K_DN, device="cuda", generator=g).half()]
 
+    # N > 1: the all-gather of the output slices is fused into the GEMV kernel (peer stores over NVLink + flags);
+    # --gather nccl, or a failure to set the shared buffers up, falls back to a library all-gather per layer
+    pg, gather_mode = None, "none"
+    if world > 1:
+        gather_mode = "nccl all-gather per layer"
+        if args.gather == "peer":
+            try:
+                from eoq_quantization_b200.tp import PeerGather
+                pg = PeerGather(slot_bytes=max(N_UP, N_DN) * 2, slots=2)
+                gather_mode = "all-gather fused into the kernel (peer stores + flags)"
+            except Exception as exc:                                 # pragma: no cover - depends on the box
+                gather_mode += f" (peer set-up failed: {type(exc).__name__})"
+    n_total = [N_UP, N_DN]
+
     def step(i):
         r = i % REPLICAS
         outs = []
         for li in range(2):
-            y = shards[li][r].gemv(xs[li])
-            if world > 1:
-                y = gather_rows(y)
+            if pg is not None:
+                y = pg.gemv(shards[li][r], xs[li], n_total[li], slot=li)
+            else:
+                y = shards[li][r].gemv(xs[li])
+                if world > 1:
+                    y = gather_rows(y)
             outs.append(y)
         return outs
 
@@ -248,6 +265,15 @@ def run_gpu_arm(args):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if pg is not None:
+        # the fused gather must give every rank exactly what a library all-gather of the slices gives
+        for li in range(2):
+            fused = pg.gemv(shards[li][0], xs[li], n_total[li], slot=li).clone()
+            plain = gather_rows(shards[li][0].gemv(xs[li]))
+            assert torch.equal(fused, plain), "fused all-gather differs from the library all-gather"
+        pg.check()
+        barrier()
 
     # Warm up eagerly, then capture the steps into CUDA graphs (REPLICAS steps per graph, plus single steps for the
     # remainder) so that the timed region measures the device, not the Python launch path.
@@ -302,7 +328,7 @@ def run_gpu_arm(args):
             run_steps(args.steps)
         torch.cuda.synchronize()
     ms = ev0.elapsed_time(ev1) / args.steps
-    launches_timed = 2 * args.steps
+    launches_timed = (4 if pg is not None else 2) * args.steps          # per rank: two GEMVs (+ two flag waits)
     if world > 1:
         t = torch.tensor([ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -396,7 +422,7 @@ def run_gpu_arm(args):
                 "data": "synthetic",
                 "config": {"workload": WORKLOAD, "batch": 1, "group": GROUP, "shapes": [[N_UP, K_UP], [N_DN, K_DN]],
                            "l2": f"{REPLICAS} weight copies cycled (working set {REPLICAS * sum(s[0].info.stream_bytes for s in shards) >> 20} MiB per rank > L2)",
-                           "parallelism": f"row-sharded tp{world}" + (" + NCCL all-gather per layer" if world > 1 else ""),
+                           "parallelism": f"row-sharded tp{world}" + (f" + {gather_mode}" if world > 1 else ""),
                            "launch": launch_mode, "symbols_per_step": int(info.symbols_per_step), "precision_bits": int(info.precision_bits)},
                 "tokens_per_s": 1e3 / ms, "pct_of_hbm_peak": 100.0 * value / (peak * world),
                 "algorithmic_bytes_per_step": alg_step,
@@ -746,6 +772,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="plain launches instead of CUDA graphs (for profilers)")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: how output slices are exchanged")
     ap.add_argument("--no-pdl", action="store_true", help="plain launches instead of programmatic dependent launches")
     ap.add_argument("--workload", default="mlp_pair", choices=["mlp_pair", "decode_dequant", "polar_q5", "llama7b_step", "prefill_gemm"])
     args = ap.parse_args()

@@ -39,7 +39,9 @@ EXPORTS = [
     "eoq_b200_decode_blocked", "eoq_b200_encode_blocked",
     "eoq_b200_tiles_build", "eoq_b200_tiles_view", "eoq_b200_tiles_free",
     "eoq_b200_weight_from_tiles", "eoq_b200_weight_from_symbols", "eoq_b200_weight_from_rans", "eoq_b200_weight_destroy",
-    "eoq_b200_weight_info", "eoq_b200_gemv", "eoq_b200_gemm", "eoq_b200_gemv_static_scratch", "eoq_b200_gemv_host", "eoq_b200_weight_decode",
+    "eoq_b200_weight_info", "eoq_b200_gemv", "eoq_b200_gemm",
+    "eoq_b200_gather_create", "eoq_b200_gather_connect", "eoq_b200_gather_destroy", "eoq_b200_gather_buffer",
+    "eoq_b200_gather_status", "eoq_b200_gemv_gather", "eoq_b200_gemv_static_scratch", "eoq_b200_gemv_host", "eoq_b200_weight_decode",
     "eoq_b200_dequant_packed",
     "eoq_b200_weight_status", "eoq_b200_tune", "eoq_b200_launch_count",
 ]
@@ -145,6 +147,12 @@ def lib() -> C.CDLL:
         "eoq_b200_weight_destroy": (None, [vp]),
         "eoq_b200_weight_info": (C.c_int, [vp, C.POINTER(WeightInfo)]),
         "eoq_b200_gemv": (C.c_int, [vp, vp, C.c_int, C.c_uint32, vp, C.c_int, vp, vp]),
+        "eoq_b200_gather_create": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_size_t, C.POINTER(vp), vp]),
+        "eoq_b200_gather_connect": (C.c_int, [vp, vp]),
+        "eoq_b200_gather_destroy": (None, [vp]),
+        "eoq_b200_gather_buffer": (vp, [vp, C.c_uint32]),
+        "eoq_b200_gather_status": (C.c_int, [vp, vp]),
+        "eoq_b200_gemv_gather": (C.c_int, [vp, vp, C.c_int, C.c_uint32, C.c_int, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, vp]),
         "eoq_b200_gemm": (C.c_int, [vp, vp, C.c_int, C.c_uint32, vp, C.c_int, vp, vp]),
         "eoq_b200_gemv_static_scratch": (C.c_int, [vp, vp, C.c_int, C.c_uint32, vp, C.c_int, vp, vp]),
         "eoq_b200_gemv_host": (C.c_int, [vp, vp, C.c_int, C.c_uint32, vp, C.c_int, vp, vp]),

@@ -702,7 +702,7 @@ extern "C" eoq_error_t eoq_b200_gemv(eoq_b200_weight_t *w, const void *x, int x_
         return eoq_b200_gemv(w, static_cast<const uint8_t *>(x) + (size_t)first * w->K * esz[x_dtype], x_dtype, batch - first,
                              static_cast<uint8_t *>(y) + (size_t)first * w->N * esz[y_dtype], y_dtype, bias, stream);
     }
-    GemvArgs a;
+    GemvArgs a = {};
     a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
     a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
     a.x = x; a.y = y; a.bias = bias; a.partials = w->partials.as<float>(); a.counters = w->counters.as<uint32_t>(); a.status = w->status.as<uint32_t>();
@@ -742,6 +742,121 @@ extern "C" eoq_error_t eoq_b200_gemm(eoq_b200_weight_t *w, const void *x, int x_
                                w->N, w->K, w->group, w->p, w->nseg, w->nrb, mb, x_dtype, y_dtype, stream);
         if (e != 0) { std::fprintf(stderr, "eoq_b200_gemm: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
     }
+    return EOQ_OK;
+}
+
+// =========================================================================
+// Row-sharded GEMV with the all-gather fused into the kernel (peer stores over NVLink)
+// =========================================================================
+//
+// Each rank owns one device allocation, opened by every other rank through CUDA IPC:
+//   [slots x slot_bytes of output][slots x 8 flags][slots epochs][slots done-counters]
+// A gather writes a slot of every rank's allocation; consecutive gathers must use different slots (a fast rank
+// may already be writing the next gather while a slow one still reads the previous one).
+struct eoq_b200_gather {
+    uint32_t world = 0, rank = 0, slots = 0;
+    size_t slot_bytes = 0, total = 0;
+    int device = 0;
+    uint8_t *base[kMaxPeers] = {};      // base[rank] is the local allocation
+    bool opened[kMaxPeers] = {};
+    DeviceBuf status;
+    size_t flags_off(uint32_t slot) const { return (size_t)slots * slot_bytes + (size_t)slot * kMaxPeers * 4; }
+    size_t epoch_off(uint32_t slot) const { return (size_t)slots * slot_bytes + (size_t)slots * kMaxPeers * 4 + (size_t)slot * 4; }
+    size_t done_off(uint32_t slot) const { return epoch_off(slots) + (size_t)slot * 4; }
+};
+
+extern "C" eoq_error_t eoq_b200_gather_create(uint32_t world, uint32_t rank, uint32_t slots, size_t slot_bytes,
+                                              eoq_b200_gather_t **out, void *ipc_handle_out)
+{
+    if (!out || !ipc_handle_out) return EOQ_ERR_NULL_PTR;
+    if (world < 2 || world > kMaxPeers || rank >= world || slots < 2 || slots > 16 || slot_bytes == 0) return EOQ_ERR_UNSUPPORTED;
+    static_assert(sizeof(cudaIpcMemHandle_t) == EOQ_B200_IPC_HANDLE_BYTES, "handle size");
+    std::unique_ptr<eoq_b200_gather> g(new eoq_b200_gather());
+    g->world = world; g->rank = rank; g->slots = slots;
+    g->slot_bytes = (slot_bytes + 255) & ~(size_t)255;
+    g->total = g->done_off(slots);
+    CU_TRY(cudaGetDevice(&g->device));
+    void *p = nullptr;
+    CU_TRY(cudaMalloc(&p, g->total));
+    g->base[rank] = static_cast<uint8_t *>(p);
+    g->opened[rank] = false;
+    CU_TRY(cudaMemset(p, 0, g->total));
+    CU_TRY(g->status.alloc(4));
+    CU_TRY(cudaMemset(g->status.p, 0, 4));
+    CU_TRY(cudaIpcGetMemHandle(reinterpret_cast<cudaIpcMemHandle_t *>(ipc_handle_out), p));
+    CU_TRY(cudaDeviceSynchronize());
+    *out = g.release();
+    return EOQ_OK;
+}
+
+extern "C" eoq_error_t eoq_b200_gather_connect(eoq_b200_gather_t *g, const void *all_handles)
+{
+    if (!g || !all_handles) return EOQ_ERR_NULL_PTR;
+    const cudaIpcMemHandle_t *h = reinterpret_cast<const cudaIpcMemHandle_t *>(all_handles);
+    for (uint32_t p = 0; p < g->world; p++) {
+        if (p == g->rank || g->base[p]) continue;
+        void *ptr = nullptr;
+        CU_TRY(cudaIpcOpenMemHandle(&ptr, h[p], cudaIpcMemLazyEnablePeerAccess));
+        g->base[p] = static_cast<uint8_t *>(ptr);
+        g->opened[p] = true;
+    }
+    return EOQ_OK;
+}
+
+extern "C" void eoq_b200_gather_destroy(eoq_b200_gather_t *g)
+{
+    if (!g) return;
+    for (uint32_t p = 0; p < g->world; p++)
+        if (g->opened[p] && g->base[p]) cudaIpcCloseMemHandle(g->base[p]);
+    if (g->base[g->rank]) cudaFree(g->base[g->rank]);
+    delete g;
+}
+
+extern "C" void *eoq_b200_gather_buffer(eoq_b200_gather_t *g, uint32_t slot)
+{
+    return g && slot < g->slots ? g->base[g->rank] + (size_t)slot * g->slot_bytes : nullptr;
+}
+
+extern "C" eoq_error_t eoq_b200_gather_status(eoq_b200_gather_t *g, void *stream)
+{
+    if (!g) return EOQ_ERR_NULL_PTR;
+    uint32_t st = 0;
+    CU_TRY(cudaMemcpyAsync(&st, g->status.p, 4, cudaMemcpyDeviceToHost, reinterpret_cast<cudaStream_t>(stream)));
+    CU_TRY(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)));
+    return st ? EOQ_ERR_CUDA : EOQ_OK;
+}
+
+extern "C" eoq_error_t eoq_b200_gemv_gather(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch, int y_dtype,
+                                            const float *bias, eoq_b200_gather_t *g, uint32_t slot, uint32_t row_offset,
+                                            uint32_t n_total, void *stream)
+{
+    if (!w || !x || !g) return EOQ_ERR_NULL_PTR;
+    if (batch == 0) return EOQ_OK;
+    if (batch > 8 || x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2 || slot >= g->slots) return EOQ_ERR_UNSUPPORTED;
+    static const size_t esz[3] = {2, 2, 4};
+    if ((size_t)row_offset + w->N > n_total || (size_t)batch * n_total * esz[y_dtype] > g->slot_bytes) return EOQ_ERR_BUFFER_TOO_SMALL;
+    for (uint32_t p = 0; p < g->world; p++)
+        if (!g->base[p]) return EOQ_ERR_UNSUPPORTED;                    // eoq_b200_gather_connect has not run
+    const uint32_t bt = batch <= 1 ? 1 : batch <= 2 ? 2 : batch <= 4 ? 4 : 8;
+    if (gemv_smem_bytes(w->K, w->p, bt, w->kind) > 227 * 1024) return EOQ_ERR_UNSUPPORTED;
+    GemvArgs a = {};
+    a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
+    a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
+    a.x = x; a.bias = bias; a.partials = w->partials.as<float>(); a.counters = w->counters.as<uint32_t>(); a.status = w->status.as<uint32_t>();
+    a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
+    a.x_dtype = x_dtype; a.y_dtype = y_dtype;
+    a.world = g->world; a.rank = g->rank; a.row_offset = row_offset; a.n_total = n_total;
+    for (uint32_t p = 0; p < g->world; p++) {
+        a.peer_y[p] = g->base[p] + (size_t)slot * g->slot_bytes;
+        a.peer_flags[p] = reinterpret_cast<uint32_t *>(g->base[p] + g->flags_off(slot));
+    }
+    a.y = a.peer_y[g->rank];
+    a.gather_done = reinterpret_cast<uint32_t *>(g->base[g->rank] + g->done_off(slot));
+    a.gather_epoch = reinterpret_cast<uint32_t *>(g->base[g->rank] + g->epoch_off(slot));
+    int e = launch_gemv(a, w->G, w->bits, w->kind, stream);
+    if (e == 0)
+        e = launch_gather_wait(a.peer_flags[g->rank], a.gather_epoch, g->world, g->status.as<uint32_t>(), stream);
+    if (e != 0) { std::fprintf(stderr, "eoq_b200_gemv_gather: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
     return EOQ_OK;
 }
 
@@ -903,7 +1018,7 @@ extern "C" eoq_error_t eoq_b200_gemv_static_scratch(eoq_b200_weight_t *w, const 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     // the array keeps whatever the last call left; the counters are the only part that must start at zero
     CU_TRY(cudaMemsetAsync(scratch, 0, counter_bytes, st));
-    GemvArgs a;
+    GemvArgs a = {};
     a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
     a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
     a.x = x; a.y = y; a.bias = bias;

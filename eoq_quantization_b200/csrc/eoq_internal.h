@@ -79,6 +79,8 @@ struct V1Table {          // wire-format decode table entry, one per slot
     uint32_t sym_bias;    // sym << 16 | (slot - cum)
 };
 
+constexpr uint32_t kMaxPeers = 8;
+
 struct GemvArgs {
     const uint32_t *table;
     const TileDesc *tiles;
@@ -93,6 +95,14 @@ struct GemvArgs {
     uint32_t       *status;     // one word, set nonzero if a bounded wait expired
     uint32_t N, K, Npad, group, p, ntiles, nseg, batch;
     int x_dtype, y_dtype;
+    // Fused all-gather of row-sharded outputs (world > 1): every value is also stored into the same place of
+    // each peer's buffer, and the launch's last writer raises this rank's flag on every peer.
+    uint32_t world, rank;        // world <= 1: plain output into y
+    uint32_t row_offset, n_total;// this shard's first row and the full row count: y index = b * n_total + row_offset + r
+    void     *peer_y[kMaxPeers];       // the slot's buffer on each rank ([rank] is the local one)
+    uint32_t *peer_flags[kMaxPeers];   // the slot's flag array on each rank; entry [rank] is ours to write
+    uint32_t *gather_done;       // local: row blocks written so far in this launch (zero between launches)
+    uint32_t *gather_epoch;      // local: how many gathers this slot has completed
 };
 
 struct DecodeArgs {
@@ -133,5 +143,6 @@ uint64_t launch_counter();
 void set_gemv_ctas_per_sm(int v);
 void set_gemm_warps(int v);
 void set_pdl(int v);
+int launch_gather_wait(const uint32_t *flags, const uint32_t *epoch, uint32_t world, uint32_t *status, void *stream);
 
 }  // namespace eoq

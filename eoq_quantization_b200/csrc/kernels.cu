@@ -734,7 +734,37 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
                 if (lane == 0) a.counters[rb] = 0u;
             }
         }
-        if (write_out) {
+        if (write_out && a.world > 1) {
+            // Row-sharded output with the all-gather fused in: the values go straight into every rank's copy of the
+            // full vector (plain stores over NVLink for the peers).  The warp that writes the launch's last row block
+            // then raises this rank's flag on every peer; gather_wait_kernel on each rank waits for all flags.
+#pragma unroll
+            for (int j = 0; j < G; j++) {
+                const uint32_t r = row + j;
+                if (r < a.N) {
+                    const float bv = a.bias ? __ldg(a.bias + r) : 0.0f;
+#pragma unroll
+                    for (int b = 0; b < BT; b++)
+                        if ((uint32_t)b < a.batch) {
+                            const size_t idx = (size_t)b * a.n_total + a.row_offset + r;
+                            for (uint32_t pr = 0; pr < a.world; pr++) store_y(a.peer_y[pr], idx, y[j][b] + bv, a.y_dtype);
+                        }
+                }
+            }
+            __threadfence_system();
+            __syncwarp();
+            if (lane == 0) {
+                const uint32_t nrb = a.Npad / (32u * G);
+                if (atomicAdd(a.gather_done, 1u) == nrb - 1u) {
+                    *a.gather_done = 0u;
+                    const uint32_t e = *a.gather_epoch + 1u;
+                    *a.gather_epoch = e;
+                    __threadfence_system();
+                    for (uint32_t pr = 0; pr < a.world; pr++)
+                        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.peer_flags[pr] + a.rank), "r"(e) : "memory");
+                }
+            }
+        } else if (write_out) {
 #pragma unroll
             for (int j = 0; j < G; j++) {
                 const uint32_t r = row + j;
@@ -848,6 +878,36 @@ int launch_gemv(const GemvArgs &a, uint32_t G, uint32_t bits, uint32_t kind, voi
         if (G == 2) return launch_gemv_bt<2, 5, EOQ_B200_KIND_Q5_POLAR>(a, st);
     }
     return (int)cudaErrorInvalidValue;
+}
+
+// ---------------------------------------------------------------------------
+// Second half of the fused all-gather: wait until every rank's flag of the slot has reached this rank's own epoch
+// (the local GEMV that precedes this kernel in the stream has set it).  One lane per rank polls with acquire loads;
+// the wait is bounded (about a second), after which the status word is set and the kernel returns.
+// ---------------------------------------------------------------------------
+__global__ void gather_wait_kernel(const uint32_t *flags, const uint32_t *epoch, uint32_t world, uint32_t *status)
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t lane = threadIdx.x;
+    if (lane >= world) return;
+    const uint32_t want = *reinterpret_cast<const volatile uint32_t *>(epoch);
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + lane) : "memory");
+        if ((int32_t)(v - want) >= 0) return;
+        if (clock64() - t0 > (1ll << 31)) {      // ~1 s at 2 GHz
+            *status = 4u;
+            return;
+        }
+    }
+}
+
+int launch_gather_wait(const uint32_t *flags, const uint32_t *epoch, uint32_t world, uint32_t *status, void *stream)
+{
+    gather_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flags, epoch, world, status);
+    g_launches++;
+    return (int)cudaGetLastError();
 }
 
 // ---------------------------------------------------------------------------

@@ -284,6 +284,32 @@ eoq_error_t eoq_b200_gemv(eoq_b200_weight_t *w, const void *x, int x_dtype, uint
 eoq_error_t eoq_b200_gemm(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t m,
                           void *y, int y_dtype, const float *bias, void *stream);
 
+/* Row-sharded GEMV with the all-gather of the output slices fused into the kernel (no
+ * counterpart in the reference, whose multi-GPU plan stops at "shard by rows").  One process
+ * per GPU; rank r holds the weight rows [row_offset, row_offset + N) of an n_total-row layer.
+ * Every rank creates a gather object (one device allocation of `slots` output buffers plus
+ * flags), passes the 64-byte handle it gets to all other ranks by any means (the Python side
+ * uses torch.distributed), and connects.  eoq_b200_gemv_gather then computes this rank's
+ * rows and stores them straight into slot `slot` of EVERY rank's buffer (peer stores over
+ * NVLink); the last writer raises this rank's flag on all peers, and a one-warp kernel
+ * queued behind the GEMV waits (bounded, ~1 s, then eoq_b200_gather_status reports an error)
+ * until all ranks' flags for the slot have arrived.  After the call, work queued on `stream`
+ * may read the full [batch, n_total] result at eoq_b200_gather_buffer(g, slot).
+ * Rules: all ranks make the same sequence of calls; consecutive calls use different slots
+ * (a fast rank may write the next gather while a slow one still reads the previous one);
+ * batch * n_total * sizeof(y) <= slot_bytes; world <= 8. */
+#define EOQ_B200_IPC_HANDLE_BYTES 64
+typedef struct eoq_b200_gather eoq_b200_gather_t;
+eoq_error_t eoq_b200_gather_create(uint32_t world, uint32_t rank, uint32_t slots, size_t slot_bytes,
+                                   eoq_b200_gather_t **out, void *ipc_handle_out);
+eoq_error_t eoq_b200_gather_connect(eoq_b200_gather_t *g, const void *all_handles /* world x 64 B, by rank */);
+void        eoq_b200_gather_destroy(eoq_b200_gather_t *g);
+void       *eoq_b200_gather_buffer(eoq_b200_gather_t *g, uint32_t slot);
+eoq_error_t eoq_b200_gather_status(eoq_b200_gather_t *g, void *stream);
+eoq_error_t eoq_b200_gemv_gather(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch, int y_dtype,
+                                 const float *bias, eoq_b200_gather_t *g, uint32_t slot, uint32_t row_offset,
+                                 uint32_t n_total, void *stream);
+
 /* Same with host buffers: copies x in, runs, copies y out, synchronises. */
 eoq_error_t eoq_b200_gemv_host(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch,
                                void *y, int y_dtype, const float *bias_host, void *stream);
