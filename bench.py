@@ -234,7 +234,8 @@ def run_gpu_arm(args):
     g = torch.Generator(device="cuda").manual_seed(1234)
     xs = [torch.randn(1, K_UP, device="cuda", generator=g).half(), torch.randn(1, K_DN, device="cuda", generator=g).half()]
 
-    # N > 1: the all-gather of the output slices is fused into the GEMV kernel (peer stores over NVLink + flags);
+    # N > 1: the all-gather of the output slices is fused into the GEMV kernel (value+epoch words stored into the
+    # peers' memory over NVLink, unpacked by a small kernel behind it);
     # --gather nccl, or a failure to set the shared buffers up, falls back to a library all-gather per layer
     pg, gather_mode = None, "none"
     if world > 1:
@@ -243,7 +244,7 @@ def run_gpu_arm(args):
             try:
                 from eoq_quantization_b200.tp import PeerGather
                 pg = PeerGather(slot_bytes=max(N_UP, N_DN) * 2, slots=2)
-                gather_mode = "all-gather fused into the kernel (peer stores + flags)"
+                gather_mode = "all-gather fused into the kernel (8-byte value+epoch stores into peer memory)"
             except Exception as exc:                                 # pragma: no cover - depends on the box
                 gather_mode += f" (peer set-up failed: {type(exc).__name__})"
     n_total = [N_UP, N_DN]
@@ -322,17 +323,17 @@ def run_gpu_arm(args):
         run_steps(args.steps)
         ev1.record()
         barrier()
-        # keep the same load running for at least half a second so that the clock record is meaningful
-        t_end = time.time() + 0.6
-        while time.time() < t_end:
+        ms = ev0.elapsed_time(ev1) / args.steps
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        # keep the same load running for at least half a second so that the clock record is meaningful; the number of
+        # repetitions comes from the all-reduced time, so every rank runs the same number of exchanges
+        for _ in range(int(0.6 / max(ms * 1e-3 * args.steps, 1e-6)) + 1):
             run_steps(args.steps)
         torch.cuda.synchronize()
-    ms = ev0.elapsed_time(ev1) / args.steps
     launches_timed = (4 if pg is not None else 2) * args.steps          # per rank: two GEMVs (+ two flag waits)
-    if world > 1:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
     value = alg_step / (ms * 1e-3) / 1e9
 
     # per-kernel device time, for the roofline of the dominant kernel (the fused GEMV; the larger share is the

@@ -750,18 +750,18 @@ extern "C" eoq_error_t eoq_b200_gemm(eoq_b200_weight_t *w, const void *x, int x_
 // =========================================================================
 //
 // Each rank owns one device allocation, opened by every other rank through CUDA IPC:
-//   [slots x slot_bytes of output][slots x 8 flags][slots epochs][slots done-counters]
-// A gather writes a slot of every rank's allocation; consecutive gathers must use different slots (a fast rank
-// may already be writing the next gather while a slow one still reads the previous one).
+//   [slots x slot_bytes of output][slots x receive buffer of 8-byte words][slots epochs][slots done-counters]
+// A gather sends into one slot of every peer's receive buffer; consecutive gathers must use different slots (a
+// fast rank may already be sending the next gather while a slow one still unpacks the previous one).
 struct eoq_b200_gather {
     uint32_t world = 0, rank = 0, slots = 0;
-    size_t slot_bytes = 0, total = 0;
+    size_t slot_bytes = 0, slot_elems = 0, total = 0;
     int device = 0;
     uint8_t *base[kMaxPeers] = {};      // base[rank] is the local allocation
     bool opened[kMaxPeers] = {};
     DeviceBuf status;
-    size_t flags_off(uint32_t slot) const { return (size_t)slots * slot_bytes + (size_t)slot * kMaxPeers * 4; }
-    size_t epoch_off(uint32_t slot) const { return (size_t)slots * slot_bytes + (size_t)slots * kMaxPeers * 4 + (size_t)slot * 4; }
+    size_t ll_off(uint32_t slot) const { return (size_t)slots * slot_bytes + (size_t)slot * slot_elems * 8; }
+    size_t epoch_off(uint32_t slot) const { return ll_off(slots) + (size_t)slot * 4; }
     size_t done_off(uint32_t slot) const { return epoch_off(slots) + (size_t)slot * 4; }
 };
 
@@ -774,6 +774,7 @@ extern "C" eoq_error_t eoq_b200_gather_create(uint32_t world, uint32_t rank, uin
     std::unique_ptr<eoq_b200_gather> g(new eoq_b200_gather());
     g->world = world; g->rank = rank; g->slots = slots;
     g->slot_bytes = (slot_bytes + 255) & ~(size_t)255;
+    g->slot_elems = g->slot_bytes / 2;                      // the narrowest output element is 2 bytes
     g->total = g->done_off(slots);
     CU_TRY(cudaGetDevice(&g->device));
     void *p = nullptr;
@@ -835,6 +836,7 @@ extern "C" eoq_error_t eoq_b200_gemv_gather(eoq_b200_weight_t *w, const void *x,
     if (batch > 8 || x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2 || slot >= g->slots) return EOQ_ERR_UNSUPPORTED;
     static const size_t esz[3] = {2, 2, 4};
     if ((size_t)row_offset + w->N > n_total || (size_t)batch * n_total * esz[y_dtype] > g->slot_bytes) return EOQ_ERR_BUFFER_TOO_SMALL;
+    if (row_offset != g->rank * w->N || (size_t)w->N * g->world != n_total) return EOQ_ERR_UNSUPPORTED;   // equal, rank-ordered shards
     for (uint32_t p = 0; p < g->world; p++)
         if (!g->base[p]) return EOQ_ERR_UNSUPPORTED;                    // eoq_b200_gather_connect has not run
     const uint32_t bt = batch <= 1 ? 1 : batch <= 2 ? 2 : batch <= 4 ? 4 : 8;
@@ -846,16 +848,14 @@ extern "C" eoq_error_t eoq_b200_gemv_gather(eoq_b200_weight_t *w, const void *x,
     a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
     a.x_dtype = x_dtype; a.y_dtype = y_dtype;
     a.world = g->world; a.rank = g->rank; a.row_offset = row_offset; a.n_total = n_total;
-    for (uint32_t p = 0; p < g->world; p++) {
-        a.peer_y[p] = g->base[p] + (size_t)slot * g->slot_bytes;
-        a.peer_flags[p] = reinterpret_cast<uint32_t *>(g->base[p] + g->flags_off(slot));
-    }
-    a.y = a.peer_y[g->rank];
-    a.gather_done = reinterpret_cast<uint32_t *>(g->base[g->rank] + g->done_off(slot));
-    a.gather_epoch = reinterpret_cast<uint32_t *>(g->base[g->rank] + g->epoch_off(slot));
+    for (uint32_t p = 0; p < g->world; p++) a.peer_ll[p] = reinterpret_cast<uint64_t *>(g->base[p] + g->ll_off(slot));
+    a.y = g->base[g->rank] + (size_t)slot * g->slot_bytes;
+    uint32_t *epoch = reinterpret_cast<uint32_t *>(g->base[g->rank] + g->epoch_off(slot));
+    uint32_t *done = reinterpret_cast<uint32_t *>(g->base[g->rank] + g->done_off(slot));
+    a.gather_epoch = epoch;
     int e = launch_gemv(a, w->G, w->bits, w->kind, stream);
     if (e == 0)
-        e = launch_gather_wait(a.peer_flags[g->rank], a.gather_epoch, g->world, g->status.as<uint32_t>(), stream);
+        e = launch_gather_wait(a.peer_ll[g->rank], a.y, epoch, done, g->rank, w->N, n_total, batch, y_dtype, g->status.as<uint32_t>(), stream);
     if (e != 0) { std::fprintf(stderr, "eoq_b200_gemv_gather: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
     return EOQ_OK;
 }

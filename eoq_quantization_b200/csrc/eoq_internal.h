@@ -95,14 +95,13 @@ struct GemvArgs {
     uint32_t       *status;     // one word, set nonzero if a bounded wait expired
     uint32_t N, K, Npad, group, p, ntiles, nseg, batch;
     int x_dtype, y_dtype;
-    // Fused all-gather of row-sharded outputs (world > 1): every value is also stored into the same place of
-    // each peer's buffer, and the launch's last writer raises this rank's flag on every peer.
+    // Fused all-gather of row-sharded outputs (world > 1): this rank's rows go into its own full-size output and,
+    // as 8-byte {value bits, epoch} words, into every peer's receive buffer; gather_wait_kernel on each rank
+    // unpacks what the others sent.  8-byte stores arrive whole, so no fence or separate flag is needed.
     uint32_t world, rank;        // world <= 1: plain output into y
     uint32_t row_offset, n_total;// this shard's first row and the full row count: y index = b * n_total + row_offset + r
-    void     *peer_y[kMaxPeers];       // the slot's buffer on each rank ([rank] is the local one)
-    uint32_t *peer_flags[kMaxPeers];   // the slot's flag array on each rank; entry [rank] is ours to write
-    uint32_t *gather_done;       // local: row blocks written so far in this launch (zero between launches)
-    uint32_t *gather_epoch;      // local: how many gathers this slot has completed
+    uint64_t *peer_ll[kMaxPeers];      // the slot's receive buffer on each rank, 8-byte words ([rank] unused)
+    const uint32_t *gather_epoch;      // local: gathers this slot has completed; this launch sends epoch + 1
 };
 
 struct DecodeArgs {
@@ -143,6 +142,7 @@ uint64_t launch_counter();
 void set_gemv_ctas_per_sm(int v);
 void set_gemm_warps(int v);
 void set_pdl(int v);
-int launch_gather_wait(const uint32_t *flags, const uint32_t *epoch, uint32_t world, uint32_t *status, void *stream);
+int launch_gather_wait(const void *ll, void *y, uint32_t *epoch, uint32_t *done, uint32_t rank, uint32_t rows_per_rank,
+                       uint32_t n_total, uint32_t batch, int y_dtype, uint32_t *status, void *stream);
 
 }  // namespace eoq

@@ -735,9 +735,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
             }
         }
         if (write_out && a.world > 1) {
-            // Row-sharded output with the all-gather fused in: the values go straight into every rank's copy of the
-            // full vector (plain stores over NVLink for the peers).  The warp that writes the launch's last row block
-            // then raises this rank's flag on every peer; gather_wait_kernel on each rank waits for all flags.
+            // Row-sharded output with the all-gather fused in: the values go into this rank's copy of the full vector
+            // and, as {value bits, epoch} words, straight into every peer's receive buffer (plain 8-byte stores over
+            // NVLink, which arrive whole: the epoch in the word is the flag).
+            const uint32_t epoch = __ldcg(a.gather_epoch) + 1u;
 #pragma unroll
             for (int j = 0; j < G; j++) {
                 const uint32_t r = row + j;
@@ -747,21 +748,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
                     for (int b = 0; b < BT; b++)
                         if ((uint32_t)b < a.batch) {
                             const size_t idx = (size_t)b * a.n_total + a.row_offset + r;
-                            for (uint32_t pr = 0; pr < a.world; pr++) store_y(a.peer_y[pr], idx, y[j][b] + bv, a.y_dtype);
+                            const float v = y[j][b] + bv;
+                            store_y(a.y, idx, v, a.y_dtype);
+                            const uint32_t bits = a.y_dtype == EOQ_B200_F16 ? (uint32_t)__half_as_ushort(__float2half_rn(v))
+                                                : a.y_dtype == EOQ_B200_BF16 ? (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v))
+                                                : __float_as_uint(v);
+                            for (uint32_t pr = 0; pr < a.world; pr++)
+                                if (pr != a.rank)
+                                    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(a.peer_ll[pr] + idx), "r"(bits), "r"(epoch) : "memory");
                         }
-                }
-            }
-            __threadfence_system();
-            __syncwarp();
-            if (lane == 0) {
-                const uint32_t nrb = a.Npad / (32u * G);
-                if (atomicAdd(a.gather_done, 1u) == nrb - 1u) {
-                    *a.gather_done = 0u;
-                    const uint32_t e = *a.gather_epoch + 1u;
-                    *a.gather_epoch = e;
-                    __threadfence_system();
-                    for (uint32_t pr = 0; pr < a.world; pr++)
-                        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.peer_flags[pr] + a.rank), "r"(e) : "memory");
                 }
             }
         } else if (write_out) {
@@ -881,33 +876,54 @@ int launch_gemv(const GemvArgs &a, uint32_t G, uint32_t bits, uint32_t kind, voi
 }
 
 // ---------------------------------------------------------------------------
-// Second half of the fused all-gather: wait until every rank's flag of the slot has reached this rank's own epoch
-// (the local GEMV that precedes this kernel in the stream has set it).  One lane per rank polls with acquire loads;
-// the wait is bounded (about a second), after which the status word is set and the kernel returns.
+// Second half of the fused all-gather: unpack what the other ranks sent.  Every element of the slot's receive
+// buffer that another rank owns is polled until its word carries this gather's epoch, and its value is written
+// into the full output vector.  Polls are bounded (about a second), after which the status word is set.  The CTA
+// that finishes last advances the slot's epoch.
 // ---------------------------------------------------------------------------
-__global__ void gather_wait_kernel(const uint32_t *flags, const uint32_t *epoch, uint32_t world, uint32_t *status)
+__global__ void __launch_bounds__(256) gather_wait_kernel(const uint2 *ll, void *y, uint32_t *epoch, uint32_t *done, uint32_t rank,
+                                                         uint32_t rows_per_rank, uint32_t n_total, uint32_t batch, int y_dtype,
+                                                         uint32_t *status)
 {
+    // Launched programmatically behind the GEMV: resident early, it lets the next kernel of the stream start its own
+    // set-up at once, and touches memory only after the GEMV has completed.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t lane = threadIdx.x;
-    if (lane >= world) return;
-    const uint32_t want = *reinterpret_cast<const volatile uint32_t *>(epoch);
+    const uint32_t want = *reinterpret_cast<const volatile uint32_t *>(epoch) + 1u;
+    const uint32_t total = batch * n_total;
     const long long t0 = clock64();
-    for (;;) {
-        uint32_t v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + lane) : "memory");
-        if ((int32_t)(v - want) >= 0) return;
-        if (clock64() - t0 > (1ll << 31)) {      // ~1 s at 2 GHz
-            *status = 4u;
-            return;
+    bool gave_up = false;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        if ((i % n_total) / rows_per_rank == rank) continue;          // our own rows are already in place
+        uint32_t bits = 0, fl = 0;
+        while (!gave_up) {
+            asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(fl) : "l"(ll + i) : "memory");
+            if (fl == want) break;
+            if (clock64() - t0 > (1ll << 31)) gave_up = true;          // ~1 s at 2 GHz
+        }
+        if (y_dtype == EOQ_B200_F32) reinterpret_cast<uint32_t *>(y)[i] = bits;
+        else reinterpret_cast<uint16_t *>(y)[i] = (uint16_t)bits;
+    }
+    if (gave_up) *status = 4u;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(done, 1u) == gridDim.x - 1u) {
+            *done = 0u;
+            *epoch = want;
         }
     }
 }
 
-int launch_gather_wait(const uint32_t *flags, const uint32_t *epoch, uint32_t world, uint32_t *status, void *stream)
+int launch_gather_wait(const void *ll, void *y, uint32_t *epoch, uint32_t *done, uint32_t rank, uint32_t rows_per_rank,
+                       uint32_t n_total, uint32_t batch, int y_dtype, uint32_t *status, void *stream)
 {
-    gather_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flags, epoch, world, status);
+    const uint32_t total = batch * n_total;
+    const uint32_t grid = std::max(1u, std::min(16u, (total + 2047u) / 2048u));
+    cudaError_t e = launch_with_pdl(gather_wait_kernel, dim3(grid), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+                                    reinterpret_cast<const uint2 *>(ll), y, epoch, done, rank, rows_per_rank, n_total, batch, y_dtype, status);
     g_launches++;
-    return (int)cudaGetLastError();
+    return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 // ---------------------------------------------------------------------------

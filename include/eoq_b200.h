@@ -290,13 +290,15 @@ eoq_error_t eoq_b200_gemm(eoq_b200_weight_t *w, const void *x, int x_dtype, uint
  * Every rank creates a gather object (one device allocation of `slots` output buffers plus
  * flags), passes the 64-byte handle it gets to all other ranks by any means (the Python side
  * uses torch.distributed), and connects.  eoq_b200_gemv_gather then computes this rank's
- * rows and stores them straight into slot `slot` of EVERY rank's buffer (peer stores over
- * NVLink); the last writer raises this rank's flag on all peers, and a one-warp kernel
- * queued behind the GEMV waits (bounded, ~1 s, then eoq_b200_gather_status reports an error)
- * until all ranks' flags for the slot have arrived.  After the call, work queued on `stream`
- * may read the full [batch, n_total] result at eoq_b200_gather_buffer(g, slot).
- * Rules: all ranks make the same sequence of calls; consecutive calls use different slots
- * (a fast rank may write the next gather while a slow one still reads the previous one);
+ * rows, writes them into its own full-size output and sends them as 8-byte {value, epoch}
+ * words straight into slot `slot` of every peer's receive buffer (plain stores over NVLink;
+ * an 8-byte store arrives whole, so the epoch is the flag and no fence is needed); a small
+ * kernel queued behind the GEMV polls the words the other ranks sent (bounded, ~1 s, then
+ * eoq_b200_gather_status reports an error) and unpacks them.  After the call, work queued
+ * on `stream` may read the full [batch, n_total] result at eoq_b200_gather_buffer(g, slot).
+ * Rules: shards are equal and in rank order (row_offset = rank * N, n_total = world * N); all
+ * ranks make the same sequence of calls; consecutive calls use different slots (a fast rank
+ * may send the next gather while a slow one still unpacks the previous one);
  * batch * n_total * sizeof(y) <= slot_bytes; world <= 8. */
 #define EOQ_B200_IPC_HANDLE_BYTES 64
 typedef struct eoq_b200_gather eoq_b200_gather_t;

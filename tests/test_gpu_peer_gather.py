@@ -49,6 +49,29 @@ def _worker(rank: int, world: int, port: int) -> None:
         refh = O.int4_linear(packed, s16.astype(np.float32).reshape(-1), n, k, 128, xh.float().cpu().numpy(), None)
         assert yh.dtype == torch.float16 and O.rel_l2(yh.float().cpu().numpy(), refh) < 1e-3
         pg.check()
+
+        # back to back, no host synchronisation in between (slots alternate; results are copied out in stream order)
+        xs = [torch.from_numpy(np.random.default_rng(200 + i).standard_normal((1, k)).astype(np.float32)).cuda() for i in range(6)]
+        refs = [O.int4_linear(packed, s16.astype(np.float32).reshape(-1), n, k, 128, xi.cpu().numpy(), None) for xi in xs]
+        outs = [pg.gemv(shard, xs[i % 6], n, slot=i & 1).clone() for i in range(24)]
+        torch.cuda.synchronize()
+        pg.check()
+        for i, o in enumerate(outs):
+            assert O.rel_l2(o.cpu().numpy(), refs[i % 6]) < 2e-5, (rank, i)
+
+        # the same inside a CUDA graph, replayed
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                gouts = [pg.gemv(shard, xs[i % 6], n, slot=i & 1).clone() for i in range(8)]
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        pg.check()
+        for i, o in enumerate(gouts):
+            assert O.rel_l2(o.cpu().numpy(), refs[i % 6]) < 2e-5, (rank, "graph", i)
         dist.barrier()
         pg.close()
     finally:
