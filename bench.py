@@ -267,13 +267,27 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    if pg is not None:
-        # the fused gather must give every rank exactly what a library all-gather of the slices gives
-        for li in range(2):
-            fused = pg.gemv(shards[li][0], xs[li], n_total[li], slot=li).clone()
-            plain = gather_rows(shards[li][0].gemv(xs[li]))
-            assert torch.equal(fused, plain), "fused all-gather differs from the library all-gather"
-        pg.check()
+    if world > 1:
+        # the fused gather must give every rank exactly what a library all-gather of the slices gives; if it does not
+        # (or could not be set up) on any rank, every rank falls back to the library all-gather
+        ok = 1 if pg is not None else 0
+        agree = torch.tensor([ok], device="cuda")
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        if int(agree.item()) == 0:
+            pg = None
+        if pg is not None:
+            try:
+                for li in range(2):
+                    fused = pg.gemv(shards[li][0], xs[li], n_total[li], slot=li).clone()
+                    plain = gather_rows(shards[li][0].gemv(xs[li]))
+                    ok = ok and bool(torch.equal(fused, plain))
+                pg.check()
+            except Exception:                                        # a bounded wait gave up
+                ok = 0
+            agree = torch.tensor([int(ok)], device="cuda")
+            dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+            if int(agree.item()) == 0:
+                pg, gather_mode = None, "nccl all-gather per layer (fused gather failed its check)"
         barrier()
 
     # Warm up eagerly, then capture the steps into CUDA graphs (REPLICAS steps per graph, plus single steps for the
