@@ -368,7 +368,8 @@ template <bool RING, uint32_t RING_BYTES = RingSmall::kBytes>
 __device__ __forceinline__ void rans_renorm(uint32_t &x, WordState &s)
 {
     if (RING) {
-        // predicated, branch-free: x = x * 65536 + w; koff += 64; w = ring[(koff mod ring) | lane*2]
+        // predicated, branch-free: x = x * 65536 + w; koff += 64; w = ring[(koff mod ring) | lane*2].  A plain C++
+        // conditional and a select-based form with an unconditional reload were measured: all three within 2 %.
         asm volatile("{\n\t.reg .pred p;\n\t.reg .b32 t;\n\t"
                      "setp.lt.u32 p, %0, 65536;\n\t"
                      "@p mad.lo.u32 %0, %0, 65536, %1;\n\t"
