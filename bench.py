@@ -592,11 +592,24 @@ def run_llama_step(args):
         xf = x.float()
         return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5)).half() * nw
 
-    def linear(w, x):
+    # N > 1: the output slices of every linear meet through the gather fused into the GEMV kernel (three slots in
+    # rotation: 129 gathers per step, so consecutive gathers never share a slot, also across steps); the attention
+    # output, which no GEMV produces, goes through a library all-gather
+    pg, call_no = None, [0]
+    if world > 1 and args.gather == "peer":
+        from eoq_quantization_b200.tp import PeerGather
+        pg = PeerGather(slot_bytes=V * 2, slots=3)
+
+    def linear(w, x, n_total):
+        if pg is not None:
+            slot = call_no[0] % 3
+            call_no[0] += 1
+            return pg.gemv(w, x, n_total, slot=slot)
         y = w.gemv(x)
         return gather_rows(y) if world > 1 else y
 
     def step(x, lin):
+        call_no[0] = 0
         for i in range(L):
             h = norm(x)
             qkv = lin("qkv", i, h)
@@ -614,7 +627,7 @@ def run_llama_step(args):
         return lin("head", 0, norm(x))
 
     def lin_eoq(name, i, x):
-        return linear(head if name == "head" else layers[name][i], x)
+        return linear(head if name == "head" else layers[name][i], x, V if name == "head" else shapes[name][0])
 
     def timed(fn, steps):
         side = torch.cuda.Stream()
@@ -651,10 +664,13 @@ def run_llama_step(args):
 
     steps = min(args.steps, 50)
     ms, mode = timed(lambda: step(x0, lin_eoq), steps)
+    if pg is not None:
+        pg.check()                                               # no gather may have given up waiting for a peer
     line = {"metric": "Llama-7B-shape decode step, tokens/s at batch 1", "unit": "tokens/s", "value": 1e3 / ms,
             "ms_per_step": ms, "n_gpus": world, "steps": steps, "data": "synthetic", "scaling": "strong",
             "config": {"workload": "llama7b_decode_step_int4_g128_rans", "layers": L, "hidden": H, "kv_len": KV,
-                       "launch": mode, "parallelism": f"row-sharded tp{world}"},
+                       "launch": mode, "parallelism": f"row-sharded tp{world}" + ("" if world == 1 else
+                                                   " + gather fused into the GEMVs" if pg is not None else " + nccl all-gather")},
             "algorithmic_weight_bytes_per_step": alg_step, "weight_gbs": alg_step / (ms * 1e-3) / 1e9}
     if world == 1 and not args.no_cpu_baseline:
         # dense fp16 comparator: same step, weights as fp16 matrices (one copy per layer)
