@@ -321,14 +321,20 @@ __device__ __forceinline__ void ring_sync_step(RingCtlT<R> &r, const WordState &
 template <typename R>
 __device__ __forceinline__ void tile_open(RingCtlT<R> &r, const TileDesc &d, const uint8_t *base, uint32_t lane)
 {
-    if (lane == 0) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base), "r"(d.len64 << 6) : "memory");
+    const uint32_t bytes = d.len64 << 6;
+    uint32_t ahead = 0;        // bytes already on their way through the ring
     if ((d.seg & kTileDirectFlag) == 0) {
         r.tile_first = r.issued;
-        r.tile_bytes = d.len64 << 6;
+        r.tile_bytes = bytes;
         r.tile_last = r.tile_first + (r.tile_bytes + R::kChunkBytes - 1) / R::kChunkBytes;
         r.src = base;
         ring_issue(r, min(r.tile_last, r.tile_first + R::kChunks), lane);
+        ahead = min(bytes, R::kBytes);
     }
+    // The rest of the tile is only asked into L2, and after the ring copies: when every warp of the grid opens its
+    // tile at the same moment, the copies that are needed first must not queue behind megabytes of prefetch.
+    if (lane == 0 && bytes > ahead)
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + ahead), "r"(bytes - ahead) : "memory");
 }
 
 // Begin decoding an opened tile: wait for its first chunk, read the lane's state and first word.
