@@ -390,12 +390,18 @@ def run_gpu_arm(args):
     hx = [torch.randn(1, K_UP).half().pin_memory(), torch.randn(1, K_DN).half().pin_memory()]
     hy = [torch.empty(1, (N_UP // world)).half().pin_memory(), torch.empty(1, (N_DN // world)).half().pin_memory()]
     stream = torch.cuda.current_stream().cuda_stream
+    e2e_streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    torch.cuda.synchronize()
 
     def e2e_step(i):
+        # each layer is queued on its own stream (x in, kernel, y out, from and to pinned host buffers), so one layer's
+        # copies overlap the other's kernel; then both streams are synchronised through their status words
         r = i % REPLICAS
         for li in range(2):
-            _lib.check(lib.eoq_b200_gemv_host(shards[li][r]._h, hx[li].data_ptr(), _lib.F16, 1, hy[li].data_ptr(), _lib.F16,
-                                              None, stream), "eoq_b200_gemv_host")
+            _lib.check(lib.eoq_b200_gemv_host_async(shards[li][r]._h, hx[li].data_ptr(), _lib.F16, 1, hy[li].data_ptr(), _lib.F16,
+                                                    None, e2e_streams[li].cuda_stream), "eoq_b200_gemv_host_async")
+        for li in range(2):
+            _lib.check(lib.eoq_b200_weight_status(shards[li][r]._h, e2e_streams[li].cuda_stream), "eoq_b200_weight_status")
     for i in range(args.warmup):
         e2e_step(i)
     barrier()

@@ -41,7 +41,7 @@ EXPORTS = [
     "eoq_b200_weight_from_tiles", "eoq_b200_weight_from_symbols", "eoq_b200_weight_from_rans", "eoq_b200_weight_destroy",
     "eoq_b200_weight_info", "eoq_b200_gemv", "eoq_b200_gemm",
     "eoq_b200_gather_create", "eoq_b200_gather_connect", "eoq_b200_gather_destroy", "eoq_b200_gather_buffer",
-    "eoq_b200_gather_status", "eoq_b200_gemv_gather", "eoq_b200_gemv_static_scratch", "eoq_b200_gemv_host", "eoq_b200_weight_decode",
+    "eoq_b200_gather_status", "eoq_b200_gemv_gather", "eoq_b200_gemv_static_scratch", "eoq_b200_gemv_host", "eoq_b200_gemv_host_async", "eoq_b200_weight_decode",
     "eoq_b200_dequant_packed",
     "eoq_b200_weight_status", "eoq_b200_tune", "eoq_b200_launch_count",
 ]
@@ -156,6 +156,7 @@ def lib() -> C.CDLL:
         "eoq_b200_gemm": (C.c_int, [vp, vp, C.c_int, C.c_uint32, vp, C.c_int, vp, vp]),
         "eoq_b200_gemv_static_scratch": (C.c_int, [vp, vp, C.c_int, C.c_uint32, vp, C.c_int, vp, vp]),
         "eoq_b200_gemv_host": (C.c_int, [vp, vp, C.c_int, C.c_uint32, vp, C.c_int, vp, vp]),
+        "eoq_b200_gemv_host_async": (C.c_int, [vp, vp, C.c_int, C.c_uint32, vp, C.c_int, vp, vp]),
         "eoq_b200_weight_decode": (C.c_int, [vp, vp, C.c_int, vp, C.c_int, vp]),
         "eoq_b200_dequant_packed": (C.c_int, [vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                               C.c_uint32, vp, C.c_int, vp]),

@@ -518,6 +518,8 @@ struct eoq_b200_weight {
     uint32_t ntiles = 0, nseg = 0, nrb = 0;
     DeviceBuf table, tiles, stream, scales, centroids, partials, counters, status, xbuf, ybuf, biasbuf;
     DeviceBuf gemm_x, gemm_partials, gemm_counters;   // scratch of the tensor-core path, allocated by its first call
+    uint32_t *status_host = nullptr;                  // pinned landing place of the status word (a pageable one makes the copy synchronous)
+    ~eoq_b200_weight() { if (status_host) cudaFreeHost(status_host); }
     size_t stream_bytes = 0, scale_bytes = 0, partial_bytes = 0;
     std::mutex mu;   // one call at a time may use the scratch of a weight
 };
@@ -567,6 +569,7 @@ eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const 
     CU_TRY(cudaMemcpy(w->scales.p, scales, w->scale_bytes, cudaMemcpyHostToDevice));
     CU_TRY(cudaMemset(w->counters.p, 0, (size_t)tw.nrb * 4));
     CU_TRY(cudaMemset(w->status.p, 0, 4));
+    CU_TRY(cudaMallocHost(reinterpret_cast<void **>(&w->status_host), 64));
     *out = w.release();
     return EOQ_OK;
 }
@@ -860,8 +863,8 @@ extern "C" eoq_error_t eoq_b200_gemv_gather(eoq_b200_weight_t *w, const void *x,
     return EOQ_OK;
 }
 
-extern "C" eoq_error_t eoq_b200_gemv_host(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch, void *y, int y_dtype,
-                                          const float *bias_host, void *stream)
+extern "C" eoq_error_t eoq_b200_gemv_host_async(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch, void *y, int y_dtype,
+                                                const float *bias_host, void *stream)
 {
     if (!w || !x || !y) return EOQ_ERR_NULL_PTR;
     if (batch == 0) return EOQ_OK;
@@ -874,10 +877,15 @@ extern "C" eoq_error_t eoq_b200_gemv_host(eoq_b200_weight_t *w, const void *x, i
     eoq_error_t rc = eoq_b200_gemv(w, w->xbuf.p, x_dtype, batch, w->ybuf.p, y_dtype, bias_host ? w->biasbuf.as<float>() : nullptr, stream);
     if (rc != EOQ_OK) return rc;
     CU_TRY(cudaMemcpyAsync(y, w->ybuf.p, (size_t)batch * w->N * esz[y_dtype], cudaMemcpyDeviceToHost, st));
-    uint32_t status = 0;
-    CU_TRY(cudaMemcpyAsync(&status, w->status.p, 4, cudaMemcpyDeviceToHost, st));
-    CU_TRY(cudaStreamSynchronize(st));
-    return status ? EOQ_ERR_CUDA : EOQ_OK;
+    return EOQ_OK;
+}
+
+extern "C" eoq_error_t eoq_b200_gemv_host(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch, void *y, int y_dtype,
+                                          const float *bias_host, void *stream)
+{
+    eoq_error_t rc = eoq_b200_gemv_host_async(w, x, x_dtype, batch, y, y_dtype, bias_host, stream);
+    if (rc != EOQ_OK || batch == 0) return rc;
+    return eoq_b200_weight_status(w, stream);       // reads the status word and synchronises the stream
 }
 
 extern "C" eoq_error_t eoq_b200_weight_decode(eoq_b200_weight_t *w, uint8_t *d_sym, int packed, void *d_dequant, int out_dtype, void *stream)
@@ -917,11 +925,12 @@ extern "C" eoq_error_t eoq_b200_dequant_packed(const uint8_t *d_packed, const ui
 extern "C" eoq_error_t eoq_b200_weight_status(eoq_b200_weight_t *w, void *stream)
 {
     if (!w) return EOQ_ERR_NULL_PTR;
-    uint32_t status = 0;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    CU_TRY(cudaMemcpyAsync(&status, w->status.p, 4, cudaMemcpyDeviceToHost, st));
+    std::lock_guard<std::mutex> lock(w->mu);
+    if (!w->status_host) return EOQ_ERR_ALLOC;
+    CU_TRY(cudaMemcpyAsync(w->status_host, w->status.p, 4, cudaMemcpyDeviceToHost, st));
     CU_TRY(cudaStreamSynchronize(st));
-    return status ? EOQ_ERR_CUDA : EOQ_OK;
+    return *w->status_host ? EOQ_ERR_CUDA : EOQ_OK;
 }
 
 #ifdef EOQ_STAMPS

@@ -316,6 +316,14 @@ eoq_error_t eoq_b200_gemv_gather(eoq_b200_weight_t *w, const void *x, int x_dtyp
 eoq_error_t eoq_b200_gemv_host(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch,
                                void *y, int y_dtype, const float *bias_host, void *stream);
 
+/* The same without the final synchronisation: copies and kernel are queued on `stream` and the
+ * call returns; x, y and bias_host must stay valid (and should be pinned) until the stream has
+ * been synchronised, e.g. by eoq_b200_weight_status, which also reports a failed launch.
+ * Several weights can be queued this way before one synchronisation; a weight must not be
+ * queued again before its previous call has completed (it owns one staging buffer). */
+eoq_error_t eoq_b200_gemv_host_async(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch,
+                               void *y, int y_dtype, const float *bias_host, void *stream);
+
 /* The same product for callers that must not allocate device memory (no counterpart in the
  * reference).  A serving process that has given all of HBM to its own arena, a latency-critical
  * thread that may not take the allocator's lock, or a framework that forbids allocation while it

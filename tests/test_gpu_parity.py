@@ -441,3 +441,22 @@ def test_eoq_file_loads_straight_to_device():
             assert O.rel_l2(got.gemv(x).cpu().numpy(), x.cpu().numpy() @ ref.T) < 1e-4
         else:
             assert got.is_cuda and np.array_equal(got.cpu().numpy(), ref), name
+
+
+def test_host_buffer_gemv_async_two_weights_one_sync():
+    """eoq_b200_gemv_host_async: two weights queued from pinned host buffers, one synchronisation."""
+    lib = L.lib()
+    cases = []
+    for seed, (n, k) in enumerate(((192, 512), (100, 1024))):
+        sym, s16, packed = _int4_case(n, k, 40 + seed)
+        w = EOQWeight.from_symbols(sym, s16)
+        x = torch.randn(2, k).half().pin_memory()
+        y = torch.empty(2, n).half().pin_memory()
+        cases.append((w, x, y, packed, s16, n, k))
+    for w, x, y, *_ in cases:
+        L.check(lib.eoq_b200_gemv_host_async(w._h, x.data_ptr(), L.F16, 2, y.data_ptr(), L.F16, None, None), "async")
+    for w, *_ in cases:
+        assert lib.eoq_b200_weight_status(w._h, None) == 0
+    for w, x, y, packed, s16, n, k in cases:
+        ref = O.int4_linear(packed, s16.astype(np.float32), n, k, 128, x.float().numpy())
+        assert O.rel_l2(y.float().numpy(), ref) < TOL
