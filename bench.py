@@ -812,7 +812,15 @@ def main():
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: how output slices are exchanged")
     ap.add_argument("--no-pdl", action="store_true", help="plain launches instead of programmatic dependent launches")
     ap.add_argument("--workload", default="mlp_pair", choices=["mlp_pair", "decode_dequant", "polar_q5", "llama7b_step", "prefill_gemm"])
+    ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
+                    help="pass a knob to eoq_b200_tune (e.g. gemv_pairs=0: the one-tile-per-warp ring kernel)")
     args = ap.parse_args()
+    if args.tune and args.impl != "reference":
+        from eoq_quantization_b200 import _lib
+        for kv in args.tune:
+            key, _, val = kv.partition("=")
+            if _lib.lib().eoq_b200_tune(key.encode(), int(val)) != 0:
+                raise SystemExit(f"unknown tuning knob {key!r}")
     if args.no_pdl and args.impl != "reference":
         from eoq_quantization_b200 import _lib
         _lib.lib().eoq_b200_tune(b"pdl", 0)

@@ -516,6 +516,7 @@ struct eoq_b200_weight {
     int device = 0;
     uint32_t N = 0, K = 0, Npad = 0, G = 0, bits = 0, p = 0, group = 0, kind = 0, alphabet = 0;
     uint32_t ntiles = 0, nseg = 0, nrb = 0;
+    uint32_t stage_bytes = 0, max_ncols = 0;          // geometry of the pair kernel's staging buffers (see GemvArgs)
     DeviceBuf table, tiles, stream, scales, centroids, partials, counters, status, xbuf, ybuf, biasbuf;
     DeviceBuf gemm_x, gemm_partials, gemm_counters;   // scratch of the tensor-core path, allocated by its first call
     uint32_t *status_host = nullptr;                  // pinned landing place of the status word (a pageable one makes the copy synchronous)
@@ -545,6 +546,10 @@ eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const 
     CU_TRY(cudaGetDevice(&w->device));
     w->N = tw.N; w->K = tw.K; w->Npad = tw.Npad; w->G = tw.G; w->bits = tw.bits; w->p = tw.p; w->group = tw.group;
     w->kind = tw.kind; w->alphabet = tw.alphabet; w->ntiles = (uint32_t)tw.tiles.size(); w->nseg = tw.nseg; w->nrb = tw.nrb;
+    for (const TileDesc &d : tw.tiles) {
+        w->stage_bytes = std::max(w->stage_bytes, ((d.len64 << 6) + 64u + 127u) & ~127u);
+        w->max_ncols = std::max(w->max_ncols, d.ncols);
+    }
     w->stream_bytes = tw.stream.size();
     w->scale_bytes = (size_t)tw.N * (tw.K / tw.group) * 2;
     w->partial_bytes = tw.nseg > 1 ? (size_t)tw.nseg * tw.Npad * 8 * sizeof(float) : 0;
@@ -588,7 +593,21 @@ extern "C" eoq_error_t eoq_b200_tiles_build(const uint8_t *symbols, const eoq_b2
     if (opts->rows == 0 || opts->cols == 0 || opts->group == 0) return EOQ_ERR_INVALID_HEADER;
     if (target == 0) {
         const int sms = have_device() ? device_sm_count() : 0;
-        target = (uint32_t)(sms > 0 ? sms : 148) * 16;
+        const uint32_t warps = (uint32_t)(sms > 0 ? sms : 148) * 16;      // one wave of 16-warp CTAs
+        target = warps;
+        if (opts->kind == EOQ_B200_KIND_INT4_ABSMAX && G == 3) {
+            // The pair kernel gives every warp two vertically adjacent tiles and stages them whole in shared memory,
+            // which holds tiles of up to 7 x 16 columns: take the fewest waves of pairs whose column segments are
+            // that narrow, and as many segments as fill those waves.
+            const uint32_t nrb = (opts->rows + 32 * G - 1) / (32 * G), nrbp = (nrb + 1) / 2;
+            const uint32_t units = opts->cols / 16, need = (units + 6) / 7;
+            uint32_t nseg = 1;
+            for (uint32_t waves = 1; waves <= 64; waves++) {
+                nseg = std::max(1u, waves * warps / nrbp);
+                if (nseg >= need) break;
+            }
+            target = nseg * nrb;
+        }
     }
     std::unique_ptr<eoq_b200_tiles> t(new eoq_b200_tiles());
     rc = build_tiled(symbols, opts->rows, opts->cols, bits, G, p, opts->group, opts->kind, target, pad, t->tw);
@@ -710,6 +729,7 @@ extern "C" eoq_error_t eoq_b200_gemv(eoq_b200_weight_t *w, const void *x, int x_
     a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
     a.x = x; a.y = y; a.bias = bias; a.partials = w->partials.as<float>(); a.counters = w->counters.as<uint32_t>(); a.status = w->status.as<uint32_t>();
     a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
+    a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols;
     a.x_dtype = x_dtype; a.y_dtype = y_dtype;
     int e = launch_gemv(a, w->G, w->bits, w->kind, stream);
     if (e != 0) { std::fprintf(stderr, "eoq_b200_gemv: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
@@ -849,6 +869,7 @@ extern "C" eoq_error_t eoq_b200_gemv_gather(eoq_b200_weight_t *w, const void *x,
     a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
     a.x = x; a.bias = bias; a.partials = w->partials.as<float>(); a.counters = w->counters.as<uint32_t>(); a.status = w->status.as<uint32_t>();
     a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
+    a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols;
     a.x_dtype = x_dtype; a.y_dtype = y_dtype;
     a.world = g->world; a.rank = g->rank; a.row_offset = row_offset; a.n_total = n_total;
     for (uint32_t p = 0; p < g->world; p++) a.peer_ll[p] = reinterpret_cast<uint64_t *>(g->base[p] + g->ll_off(slot));
@@ -946,6 +967,7 @@ extern "C" int eoq_b200_tune(const char *key, int value)
     if (std::strcmp(key, "gemv_ctas_per_sm") == 0) { set_gemv_ctas_per_sm(value); return 0; }
     if (std::strcmp(key, "gemm_warps") == 0) { set_gemm_warps(value); return 0; }
     if (std::strcmp(key, "pdl") == 0) { set_pdl(value); return 0; }
+    if (std::strcmp(key, "gemv_pairs") == 0) { set_gemv_pairs(value); return 0; }
     return -1;
 }
 
@@ -1035,6 +1057,7 @@ extern "C" eoq_error_t eoq_b200_gemv_static_scratch(eoq_b200_weight_t *w, const 
     a.counters = reinterpret_cast<uint32_t *>(scratch);
     a.status = w->status.as<uint32_t>();
     a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
+    a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols;
     a.x_dtype = x_dtype; a.y_dtype = y_dtype;
     int e = launch_gemv(a, w->G, w->bits, w->kind, stream);
     if (e != 0) { std::fprintf(stderr, "eoq_b200_gemv_static_scratch: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }

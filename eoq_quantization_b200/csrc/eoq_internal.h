@@ -95,6 +95,9 @@ struct GemvArgs {
     uint32_t       *status;     // one word, set nonzero if a bounded wait expired
     uint32_t N, K, Npad, group, p, ntiles, nseg, batch;
     int x_dtype, y_dtype;
+    // Pair kernel: row blocks, bytes of one staged-tile buffer (longest tile + one row, rounded to 128) and the
+    // widest column segment; zero if the caller has not worked them out (the ring kernel is used then).
+    uint32_t nrb, stage_bytes, max_ncols;
     // Fused all-gather of row-sharded outputs (world > 1): this rank's rows go into its own full-size output and,
     // as 8-byte {value bits, epoch} words, into every peer's receive buffer; gather_wait_kernel on each rank
     // unpacks what the others sent.  8-byte stores arrive whole, so no fence or separate flag is needed.
@@ -142,6 +145,7 @@ uint64_t launch_counter();
 void set_gemv_ctas_per_sm(int v);
 void set_gemm_warps(int v);
 void set_pdl(int v);
+void set_gemv_pairs(int v);
 int launch_gather_wait(const void *ll, void *y, uint32_t *epoch, uint32_t *done, uint32_t rank, uint32_t rows_per_rank,
                        uint32_t n_total, uint32_t batch, int y_dtype, uint32_t *status, void *stream);
 

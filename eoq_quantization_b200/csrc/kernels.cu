@@ -867,9 +867,542 @@ static int launch_gemv_bt(const GemvArgs &a, cudaStream_t st)
     return launch_gemv_one<G, BITS, 8, KIND>(a, st);
 }
 
+// ---------------------------------------------------------------------------
+// Fused decode + dequantise + GEMV, two tiles per warp, tiles staged whole ("pair kernel").
+//
+// The column loop of gemv_tiles_kernel is bound by the latency of one dependent chain per warp (table look-up ->
+// state update -> renormalisation) and by the integer pipe, a fifth of which goes into keeping the word ring ahead
+// of its readers.  This kernel removes both: a warp decodes TWO tiles at once -- the same column segment of two
+// adjacent row blocks, so that the activations of a step are loaded once and two independent chains are in flight
+// per lane -- and each tile is copied whole into its own shared-memory buffer by two bulk asynchronous copies
+// (cp.async.bulk, the 1-D TMA path): the first kilobyte (the 32 initial states and 14 rows of words) on one
+// mbarrier, the rest on a second one that is waited for after eight steps, by which time no lane can have read
+// past row 8.  No ring, no warp votes, no wrap-around of the read address.
+//
+// x is not staged for the whole CTA: each warp converts only the columns of its own segment to fp32 (at most a few
+// hundred values), so the kernel has no CTA-wide prologue besides the table copy.
+//
+// Pair q = (row-block pair q / nseg, segment q % nseg); warp w of CTA c owns pairs c + gridDim.x * (w + 16 i).
+// With an odd number of row blocks the last pair decodes its one tile twice and drops the second result.
+// Cross-segment reduction, output and the fused all-gather are those of gemv_tiles_kernel.
+// ---------------------------------------------------------------------------
+__host__ __device__ inline uint32_t pair_region_bytes(uint32_t stage, uint32_t max_ncols, uint32_t bt)
+{
+    // two stage buffers, 128 bytes of barriers, the warp's x segment [max_ncols][bt] and its 16-column sums
+    return 2u * stage + 128u + ((max_ncols * bt * 4u + (max_ncols / 16u) * bt * 4u + 127u) & ~127u);
+}
+static size_t pair_smem_bytes(uint32_t p, uint32_t bt, uint32_t stage, uint32_t max_ncols, uint32_t warps)
+{
+    return ((size_t)4 << p) + 128 + (size_t)warps * pair_region_bytes(stage, max_ncols, bt);
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+
+// Renormalise from a staged tile: x = x * 65536 + w; addr += 64; w = [addr]  (predicated, branch-free).
+__device__ __forceinline__ void staged_renorm(uint32_t &x, uint32_t &w, uint32_t &addr, uint32_t c64, uint32_t c1)
+{
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.lt.u32 p, %0, 65536;\n\t"
+                 "@p mad.lo.u32 %0, %0, 65536, %1;\n\t"
+                 "@p mad.lo.u32 %2, %3, %4, %2;\n\t"
+                 "@p ld.shared.u16 %1, [%2];\n\t}"
+                 : "+r"(x), "+r"(w), "+r"(addr)
+                 : "r"(c64), "r"(c1));
+}
+
+// Sum the partial results of all column segments for G rows of one lane, in segment order.
+template <int G, int BT>
+__device__ __forceinline__ void reduce_segments(const GemvArgs &a, uint32_t row, float (&y)[G][BT])
+{
+    constexpr int kU = G * BT <= 3 ? 16 : G * BT <= 6 ? 8 : G * BT <= 12 ? 4 : 2;
+#pragma unroll
+    for (int j = 0; j < G; j++)
+#pragma unroll
+        for (int b = 0; b < BT; b++) y[j][b] = 0.0f;
+    for (uint32_t s0 = 0; s0 < a.nseg; s0 += kU) {
+        float v[kU][G][BT];
+#pragma unroll
+        for (int u = 0; u < kU; u++) {
+            const uint32_t sidx = min(s0 + u, a.nseg - 1);
+            const float *src = a.partials + ((size_t)sidx * a.Npad + row) * BT;
+#pragma unroll
+            for (int j = 0; j < G; j++)
+#pragma unroll
+                for (int b = 0; b < BT; b++) v[u][j][b] = __ldcg(src + j * BT + b);
+        }
+#pragma unroll
+        for (int u = 0; u < kU; u++)
+            if (s0 + u < a.nseg)
+#pragma unroll
+                for (int j = 0; j < G; j++)
+#pragma unroll
+                    for (int b = 0; b < BT; b++) y[j][b] += v[u][j][b];
+    }
+}
+
+// Final values of G rows of one lane: bias, output type, and (row-sharded runs) the stores into the peers' buffers.
+template <int G, int BT>
+__device__ __forceinline__ void write_rows(const GemvArgs &a, uint32_t row, const float (&y)[G][BT])
+{
+    if (a.world > 1) {
+        const uint32_t epoch = __ldcg(a.gather_epoch) + 1u;
+#pragma unroll
+        for (int j = 0; j < G; j++) {
+            const uint32_t r = row + j;
+            if (r < a.N) {
+                const float bv = a.bias ? __ldg(a.bias + r) : 0.0f;
+#pragma unroll
+                for (int b = 0; b < BT; b++)
+                    if ((uint32_t)b < a.batch) {
+                        const size_t idx = (size_t)b * a.n_total + a.row_offset + r;
+                        const float v = y[j][b] + bv;
+                        store_y(a.y, idx, v, a.y_dtype);
+                        const uint32_t bits = a.y_dtype == EOQ_B200_F16 ? (uint32_t)__half_as_ushort(__float2half_rn(v))
+                                            : a.y_dtype == EOQ_B200_BF16 ? (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v))
+                                            : __float_as_uint(v);
+                        for (uint32_t pr = 0; pr < a.world; pr++)
+                            if (pr != a.rank)
+                                asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(a.peer_ll[pr] + idx), "r"(bits), "r"(epoch) : "memory");
+                    }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < G; j++) {
+            const uint32_t r = row + j;
+            if (r < a.N) {
+                const float bv = a.bias ? __ldg(a.bias + r) : 0.0f;
+#pragma unroll
+                for (int b = 0; b < BT; b++)
+                    if ((uint32_t)b < a.batch) store_y(a.y, (size_t)b * a.N + r, y[j][b] + bv, a.y_dtype);
+            }
+        }
+    }
+}
+
+struct PairChain {            // per lane, one per decoded tile
+    uint32_t x, w, addr;      // rANS state, next unread word, shared address that word came from
+};
+
+// Four columns of both chains: one activation load, then per column a step and a renormalisation of each chain.
+template <int G, int BT>
+__device__ __forceinline__ void pair_steps4(const float *xp, uint32_t tab_addr, uint32_t mask, uint32_t p, uint32_t magic0, uint32_t magic1,
+                                            uint32_t magic2, uint32_t c64, uint32_t c1, PairChain &ca, PairChain &cb,
+                                            float (&acc)[2][G][BT])
+{
+    using F = Fmt<G, 4>;
+    using F0 = Int4Field<F::field_bit(0)>;
+    using F1 = Int4Field<F::field_bit(G > 1 ? 1 : 0)>;
+    using F2 = Int4Field<F::field_bit(G > 2 ? 2 : 0)>;
+    constexpr uint32_t kM1 = (G > 1) ? F1::kMask : 0u, kM2 = (G > 2) ? F2::kMask : 0u;
+    float xv[4][BT];
+    if (BT == 1) {
+        const float4 v = *reinterpret_cast<const float4 *>(xp);
+        xv[0][0] = v.x; xv[1][0] = v.y; xv[2][0] = v.z; xv[3][0] = v.w;
+    } else if (BT == 2) {
+        const float4 v0 = *reinterpret_cast<const float4 *>(xp);
+        const float4 v1 = *reinterpret_cast<const float4 *>(xp + 4);
+        xv[0][0] = v0.x; xv[0][BT - 1] = v0.y; xv[1][0] = v0.z; xv[1][BT - 1] = v0.w;
+        xv[2][0] = v1.x; xv[2][BT - 1] = v1.y; xv[3][0] = v1.z; xv[3][BT - 1] = v1.w;
+    } else {
+#pragma unroll
+        for (int s = 0; s < 4; s++)
+#pragma unroll
+            for (int q = 0; q < BT / 4; q++) {
+                const float4 v = *reinterpret_cast<const float4 *>(xp + s * BT + q * 4);
+                xv[s][(q * 4 + 0) % BT] = v.x; xv[s][(q * 4 + 1) % BT] = v.y;
+                xv[s][(q * 4 + 2) % BT] = v.z; xv[s][(q * 4 + 3) % BT] = v.w;
+            }
+    }
+#pragma unroll
+    for (int s = 0; s < 4; s++) {
+        uint32_t u[2][3];
+        rans_step_int4<F0::kMask, kM1, kM2>(tab_addr, ca.x, mask, p, F::kBiasMask, magic0, magic1, magic2, u[0][0], u[0][1], u[0][2]);
+        rans_step_int4<F0::kMask, kM1, kM2>(tab_addr, cb.x, mask, p, F::kBiasMask, magic0, magic1, magic2, u[1][0], u[1][1], u[1][2]);
+#pragma unroll
+        for (int ch = 0; ch < 2; ch++) {
+            {
+                float m = __uint_as_float(u[ch][0]);
+                if (F0::kPreSubtract) m -= F0::kBase + 7.0f;
+#pragma unroll
+                for (int b = 0; b < BT; b++) acc[ch][0][b] = fmaf(m, xv[s][b], acc[ch][0][b]);
+            }
+            if (G > 1) {
+                float m = __uint_as_float(u[ch][1]);
+                if (F1::kPreSubtract) m -= F1::kBase + 7.0f;
+#pragma unroll
+                for (int b = 0; b < BT; b++) acc[ch][G > 1 ? 1 : 0][b] = fmaf(m, xv[s][b], acc[ch][G > 1 ? 1 : 0][b]);
+            }
+            if (G > 2) {
+                float m = __uint_as_float(u[ch][2]);
+                if (F2::kPreSubtract) m -= F2::kBase + 7.0f;
+#pragma unroll
+                for (int b = 0; b < BT; b++) acc[ch][G > 2 ? 2 : 0][b] = fmaf(m, xv[s][b], acc[ch][G > 2 ? 2 : 0][b]);
+            }
+        }
+        staged_renorm(ca.x, ca.w, ca.addr, c64, c1);
+        staged_renorm(cb.x, cb.w, cb.addr, c64, c1);
+    }
+}
+
+template <int G, int BT, int THREADS>
+__global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a)
+{
+    constexpr int kWarps = THREADS / 32;
+    constexpr uint32_t kChunk = 1024, kMaxChunks = 8;   // a tile arrives in kilobytes, each on its own barrier (the first: states + 14 rows of words)
+    using F = Fmt<G, 4>;
+    extern __shared__ __align__(128) uint8_t pair_smem[];
+    uint8_t *smem = pair_smem;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    EOQ_STAMP(0);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const uint32_t tab_bytes = 4u << a.p;
+    const uint32_t tab_addr = smem_addr(smem), tab_bar = tab_addr + tab_bytes;
+    const uint32_t region = pair_region_bytes(a.stage_bytes, a.max_ncols, BT);
+    uint8_t *mine = smem + tab_bytes + 128 + (size_t)warp * region;
+    const uint32_t stage[2] = {smem_addr(mine), smem_addr(mine) + a.stage_bytes};
+    const uint32_t bars = stage[0] + 2u * a.stage_bytes;       // [chain][chunk], 8 bytes each
+    float *xs = reinterpret_cast<float *>(mine + 2u * a.stage_bytes + 128);
+    float *aux = xs + (size_t)a.max_ncols * BT;
+
+    if (tid == 0) {
+        mbar_init(tab_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_expect_tx(tab_bar, tab_bytes);
+        for (uint32_t off = 0; off < tab_bytes; off += 16384u)
+            bulk_copy_g2s(tab_addr + off, reinterpret_cast<const uint8_t *>(a.table) + off, min(16384u, tab_bytes - off), tab_bar);
+    }
+    if (lane < 2 * kMaxChunks) {
+        mbar_init(bars + lane * 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+
+    const uint32_t nrbp = (a.nrb + 1u) / 2u, npairs = nrbp * a.nseg;
+    const uint32_t sgroups = a.K / a.group;
+    const uint32_t mask = (1u << a.p) - 1u, p = a.p;
+    const uint32_t magic0 = Int4Field<F::field_bit(0)>::magic_reg();
+    const uint32_t magic1 = Int4Field<F::field_bit(G > 1 ? 1 : 0)>::magic_reg();
+    const uint32_t magic2 = Int4Field<F::field_bit(G > 2 ? 2 : 0)>::magic_reg();
+    uint32_t c64, c1;
+    asm volatile("mov.b32 %0, 64;\n\tmov.b32 %1, 1;" : "=r"(c64), "=r"(c1));
+
+    TileDesc d[2];
+    bool has_b = false;
+    // Read a pair's descriptors and start the copy of the first kilobyte of both tiles.  Touches only this weight's
+    // read-only data.  Lane k * 8 + j owns chunk j of tile k, so copies are issued side by side.
+    auto chunk_copy = [&](bool first_only) {
+        if (lane < 2 * kMaxChunks) {
+            const uint32_t k = lane >> 3, j = lane & 7u;
+            if ((j == 0) == first_only) {
+                const uint32_t len64 = k ? d[1].len64 : d[0].len64, off64 = k ? d[1].off64 : d[0].off64, dst = k ? stage[1] : stage[0];
+                uint32_t bytes = len64 << 6;
+                if (bytes + 64u > a.stage_bytes) { *a.status = 2u; bytes = a.stage_bytes - 64u; }   // cannot happen with a host-computed stage size
+                const uint32_t bar = bars + lane * 8, off = j * kChunk;
+                if (off < bytes) {
+                    const uint32_t n = min(kChunk, bytes - off);
+                    mbar_expect_tx(bar, n);
+                    bulk_copy_g2s(dst + off, a.stream + ((size_t)off64 << 6) + off, n, bar);
+                } else {
+                    mbar_arrive(bar);                   // nothing to copy: complete the phase by hand
+                }
+            }
+        }
+    };
+    auto open_pair = [&](uint32_t qq) {
+        const uint32_t rbp = qq / a.nseg, seg = qq - rbp * a.nseg;
+        const uint32_t ta = (2u * rbp) * a.nseg + seg;
+        has_b = 2u * rbp + 1u < a.nrb;
+        d[0] = a.tiles[ta];
+        d[1] = a.tiles[has_b ? ta + a.nseg : ta];
+        chunk_copy(true);
+    };
+    // The pair's columns of x: loaded into registers (four columns per lane and batch row, up to 256 columns), then
+    // converted to fp32 [ncols][BT] in shared memory together with the 16-column sums the INT4 unpack needs.
+    const bool x_vec = a.x_dtype != EOQ_B200_F32 && (reinterpret_cast<uintptr_t>(a.x) & 7u) == 0;
+    auto load_x_segment = [&](bool then_rest) {
+        const uint32_t col0 = d[0].col0, ncols = d[0].ncols;
+        for (uint32_t base = 0; base < ncols; base += 128u) {
+            const uint32_t c = base + lane * 4u;
+            const bool on = c < ncols;
+            float v[BT][4];
+#pragma unroll
+            for (int b = 0; b < BT; b++) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) v[b][i] = 0.0f;
+                if (on && (uint32_t)b < a.batch) {
+                    const size_t i0 = (size_t)b * a.K + col0 + c;
+                    if (x_vec) {
+                        const uint2 r = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const uint16_t *>(a.x) + i0));
+                        if (a.x_dtype == EOQ_B200_F16) {
+                            const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&r.x));
+                            const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&r.y));
+                            v[b][0] = f0.x; v[b][1] = f0.y; v[b][2] = f1.x; v[b][3] = f1.y;
+                        } else {
+                            v[b][0] = __uint_as_float(r.x << 16); v[b][1] = __uint_as_float(r.x & 0xFFFF0000u);
+                            v[b][2] = __uint_as_float(r.y << 16); v[b][3] = __uint_as_float(r.y & 0xFFFF0000u);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; i++) v[b][i] = load_x(a.x, i0 + i, a.x_dtype);
+                    }
+                }
+            }
+            // the bulk of the tiles is requested behind the first x loads, so that these do not queue behind megabytes
+            if (then_rest && base == 0) chunk_copy(false);
+#pragma unroll
+            for (int b = 0; b < BT; b++) {
+                float sum = (v[b][0] + v[b][1]) + (v[b][2] + v[b][3]);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                if (on) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) xs[(c + i) * BT + b] = v[b][i];
+                    if ((lane & 3u) == 0) aux[(c / 16u) * BT + b] = sum;
+                }
+            }
+        }
+        __syncwarp();
+    };
+
+    // CTA c takes `cs` consecutive pairs at a time (sixteen, or fewer when there are not enough pairs to give every
+    // SM sixteen): neighbouring column segments of (mostly) one pair of row blocks, whose results it adds up in
+    // shared memory before anything goes to global memory.
+    const uint32_t cs = min((uint32_t)kWarps, (npairs + gridDim.x - 1u) / gridDim.x);
+    uint32_t base = blockIdx.x * cs;
+    uint32_t q = base + warp;
+    bool have = warp < cs && q < npairs;
+    if (have) open_pair(q);
+    EOQ_STAMP(6);
+    __syncthreads();                                   // the table barrier is initialised before anyone polls it
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    EOQ_STAMP(1);
+    if (have) load_x_segment(true);
+    EOQ_STAMP(7);
+    mbar_wait_bounded(tab_bar, 0u, a.status);
+
+    for (uint32_t it = 0; base < npairs; it++) {
+        const uint32_t parity = it & 1u;
+        const TileDesc da = d[0], db = d[1];
+        const bool cur_b = has_b, cur_have = have;
+        const uint32_t row[2] = {da.row0 + lane * G, db.row0 + lane * G};
+        float y[2][G][BT];
+#pragma unroll
+        for (int k = 0; k < 2; k++)
+#pragma unroll
+            for (int j = 0; j < G; j++)
+#pragma unroll
+                for (int b = 0; b < BT; b++) y[k][j][b] = 0.0f;
+
+        if (cur_have) {
+            PairChain ch[2];
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                mbar_wait_bounded(bars + k * 64, parity, a.status);
+                ch[k].x = lds_u32(stage[k] + lane * 4u);
+                ch[k].addr = stage[k] + 128u + lane * 2u;
+                ch[k].w = lds_u16(ch[k].addr);
+            }
+            EOQ_STAMP(2);
+            uint32_t c = da.col0;
+            const uint32_t col0 = da.col0, cend = da.col0 + da.ncols;
+            uint16_t sc_next[2][G];
+#pragma unroll
+            for (int k = 0; k < 2; k++)
+#pragma unroll
+                for (int j = 0; j < G; j++) sc_next[k][j] = ldg_u16_pinned(a.scales + (size_t)min(row[k] + j, a.N - 1) * sgroups + c / a.group);
+            const uint32_t nchunks0 = min(kMaxChunks, ((da.len64 << 6) + kChunk - 1) / kChunk), nchunks1 = min(kMaxChunks, ((db.len64 << 6) + kChunk - 1) / kChunk);
+            while (c < cend) {
+                const uint32_t g = c / a.group;
+                const uint32_t rstart = c, rend = min(cend, (g + 1) * a.group);
+                uint16_t sc_bits[2][G];
+#pragma unroll
+                for (int k = 0; k < 2; k++)
+#pragma unroll
+                    for (int j = 0; j < G; j++) sc_bits[k][j] = sc_next[k][j];
+                if (rend < cend) {
+#pragma unroll
+                    for (int k = 0; k < 2; k++)
+#pragma unroll
+                        for (int j = 0; j < G; j++) sc_next[k][j] = ldg_u16_pinned(a.scales + (size_t)min(row[k] + j, a.N - 1) * sgroups + g + 1);
+                }
+                float acc[2][G][BT];
+#pragma unroll
+                for (int k = 0; k < 2; k++)
+#pragma unroll
+                    for (int j = 0; j < G; j++)
+#pragma unroll
+                        for (int b = 0; b < BT; b++) acc[k][j][b] = 0.0f;
+
+                // Eight columns per trip.  After s steps no lane has read past word row s, and chunk j holds rows
+                // 16 j - 2 .. 16 j + 13: waiting for chunk j eight steps before column 16 j is always early enough.
+#pragma unroll 1
+                for (; c < rend; c += 8) {
+                    const float *xp = xs + (size_t)(c - col0) * BT;
+                    pair_steps4<G, BT>(xp, tab_addr, mask, p, magic0, magic1, magic2, c64, c1, ch[0], ch[1], acc);
+                    pair_steps4<G, BT>(xp + 4 * BT, tab_addr, mask, p, magic0, magic1, magic2, c64, c1, ch[0], ch[1], acc);
+                    if (((c - col0) & 8u) == 0) {
+                        const uint32_t j = (c - col0) / 16u + 1u;
+                        if (j < nchunks0) mbar_wait_bounded(bars + j * 8, parity, a.status);
+                        if (j < nchunks1) mbar_wait_bounded(bars + 64 + j * 8, parity, a.status);
+                    }
+                }
+
+                float rs[BT];
+#pragma unroll
+                for (int b = 0; b < BT; b++) rs[b] = 0.0f;
+                for (uint32_t u = (rstart - col0) / 16; u < (rend - col0) / 16; u++)
+#pragma unroll
+                    for (int b = 0; b < BT; b++) rs[b] += aux[u * BT + b];
+                const float corr[3] = {Int4Field<F::field_bit(0)>::kCorr,
+                                       Int4Field<F::field_bit(G > 1 ? 1 : 0)>::kCorr,
+                                       Int4Field<F::field_bit(G > 2 ? 2 : 0)>::kCorr};
+#pragma unroll
+                for (int k = 0; k < 2; k++)
+#pragma unroll
+                    for (int j = 0; j < G; j++) {
+                        const float sc = row[k] + j < a.N ? half_bits_to_float(sc_bits[k][j]) : 0.0f;
+#pragma unroll
+                        for (int b = 0; b < BT; b++) y[k][j][b] = fmaf(sc, acc[k][j][b] - corr[j] * rs[b], y[k][j][b]);
+                    }
+            }
+            __syncwarp();
+            EOQ_STAMP(3);
+            // this warp's sums go into its first stage buffer, which nothing reads any more: [tile][row j][batch][lane]
+            float *red = reinterpret_cast<float *>(mine);
+#pragma unroll
+            for (int k = 0; k < 2; k++)
+#pragma unroll
+                for (int j = 0; j < G; j++)
+#pragma unroll
+                    for (int b = 0; b < BT; b++) red[((k * G + j) * BT + b) * 32 + lane] = y[k][j][b];
+        }
+        __syncthreads();
+
+        // The first warp of each run of pairs that share a row-block pair adds the run up, in warp order.
+        const uint32_t rbp = q / a.nseg, seg = q - rbp * a.nseg;
+        const bool leader = cur_have && (warp == 0 || seg == 0);
+        if (leader) {
+            const uint32_t run = min(min(cs - warp, a.nseg - seg), npairs - q);
+            for (uint32_t w = 1; w < run; w++) {
+                const float *red = reinterpret_cast<const float *>(mine + (size_t)w * region);
+#pragma unroll
+                for (int k = 0; k < 2; k++)
+#pragma unroll
+                    for (int j = 0; j < G; j++)
+#pragma unroll
+                        for (int b = 0; b < BT; b++) y[k][j][b] += red[((k * G + j) * BT + b) * 32 + lane];
+            }
+            // runs of this row-block pair are numbered by the chunk of `cs` pairs they fall in
+            const uint32_t first_q = rbp * a.nseg;
+            const uint32_t slot = q / cs - first_q / cs, count = (first_q + a.nseg - 1u) / cs - first_q / cs + 1u;
+            bool last = true;
+            if (count > 1) {
+#pragma unroll
+                for (int k = 0; k < 2; k++) {
+                    if (k == 1 && !cur_b) continue;
+                    float *dst = a.partials + ((size_t)slot * a.Npad + row[k]) * BT;
+#pragma unroll
+                    for (int j = 0; j < G; j++)
+#pragma unroll
+                        for (int b = 0; b < BT; b++) __stcg(dst + j * BT + b, y[k][j][b]);
+                }
+                __threadfence();
+                __syncwarp();
+                uint32_t ticket = 0;
+                if (lane == 0) ticket = atomicAdd(a.counters + da.row0 / (32u * G), 1u);
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                EOQ_STAMP(4);
+                last = ticket == count - 1u;
+                if (last) {
+                    __threadfence();
+#pragma unroll
+                    for (int k = 0; k < 2; k++)
+#pragma unroll
+                        for (int j = 0; j < G; j++)
+#pragma unroll
+                            for (int b = 0; b < BT; b++) y[k][j][b] = 0.0f;
+                    for (uint32_t s = 0; s < count; s++) {
+#pragma unroll
+                        for (int k = 0; k < 2; k++) {
+                            if (k == 1 && !cur_b) continue;
+                            const float *src = a.partials + ((size_t)s * a.Npad + row[k]) * BT;
+#pragma unroll
+                            for (int j = 0; j < G; j++)
+#pragma unroll
+                                for (int b = 0; b < BT; b++) y[k][j][b] += __ldcg(src + j * BT + b);
+                        }
+                    }
+                    if (lane == 0) a.counters[da.row0 / (32u * G)] = 0u;
+                }
+            }
+            if (last) {
+                write_rows<G, BT>(a, row[0], y[0]);
+                if (cur_b) write_rows<G, BT>(a, row[1], y[1]);
+            }
+        }
+        EOQ_STAMP(5);
+
+        base += gridDim.x * cs;
+        if (base < npairs) {
+            __syncthreads();                           // every leader has read the sums before the buffers are refilled
+            q = base + warp;
+            have = warp < cs && q < npairs;
+            if (have) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the copies overwrite buffers read through ordinary loads
+                open_pair(q);
+                load_x_segment(true);
+            }
+        }
+    }
+}
+
+static std::atomic<int> g_gemv_pairs{1};
+void set_gemv_pairs(int v) { g_gemv_pairs.store(v != 0); }
+
+// Returns -1 if the pair kernel does not apply (shared memory), else a cudaError_t.
+template <int G, int BT>
+static int launch_gemv_pairs(const GemvArgs &a, cudaStream_t st)
+{
+    struct Cfg { size_t smem = 0; int sms = 0; };
+    static Cfg cfg[16];
+    static std::mutex mu;
+    constexpr int THREADS = 512;
+    auto kern = gemv_pairs_kernel<G, BT, THREADS>;
+    if (a.stage_bytes == 0 || a.stage_bytes > 8192u || a.max_ncols == 0 || a.nrb == 0) return -1;   // eight 1 KB chunks per tile
+    const size_t smem = pair_smem_bytes(a.p, BT, a.stage_bytes, a.max_ncols, THREADS / 32);
+    if (smem > 227 * 1024) return -1;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    Cfg c;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        Cfg &slot = cfg[dev & 15];
+        if (slot.smem < smem || slot.sms == 0) {
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            slot.smem = smem; slot.sms = device_sm_count();
+        }
+        c = slot;
+    }
+    const uint32_t npairs = ((a.nrb + 1u) / 2u) * a.nseg;
+    // sixteen pairs per CTA when there are that many per SM, else as few per CTA as still fills the SMs once
+    const uint32_t per_cta = max(1u, min((uint32_t)(THREADS / 32), (npairs + c.sms - 1) / c.sms));
+    const uint32_t grid = max(1u, min((uint32_t)c.sms, (npairs + per_cta - 1) / per_cta));
+    e = launch_with_pdl(kern, dim3(grid), dim3(THREADS), smem, st, a);
+    g_launches++;
+    return (int)(e != cudaSuccess ? e : cudaGetLastError());
+}
+
 int launch_gemv(const GemvArgs &a, uint32_t G, uint32_t bits, uint32_t kind, void *stream)
 {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 4 && G == 3 && a.batch <= 4 && g_gemv_pairs.load()) {
+        const int r = a.batch <= 1 ? launch_gemv_pairs<3, 1>(a, st) : a.batch <= 2 ? launch_gemv_pairs<3, 2>(a, st) : launch_gemv_pairs<3, 4>(a, st);
+        if (r != -1) return r;
+    }
     if (kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 4) {
         if (G == 1) return launch_gemv_bt<1, 4, EOQ_B200_KIND_INT4_ABSMAX>(a, st);
         if (G == 2) return launch_gemv_bt<2, 4, EOQ_B200_KIND_INT4_ABSMAX>(a, st);
