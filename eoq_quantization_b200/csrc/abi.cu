@@ -517,6 +517,7 @@ struct eoq_b200_weight {
     uint32_t N = 0, K = 0, Npad = 0, G = 0, bits = 0, p = 0, group = 0, kind = 0, alphabet = 0;
     uint32_t ntiles = 0, nseg = 0, nrb = 0;
     uint32_t stage_bytes = 0, max_ncols = 0;          // geometry of the pair kernel's staging buffers (see GemvArgs)
+    DeviceBuf scales_t;                               // transposed copy of the scales for the pair kernel (INT4 x 3 only)
     DeviceBuf table, tiles, stream, scales, centroids, partials, counters, status, xbuf, ybuf, biasbuf;
     DeviceBuf gemm_x, gemm_partials, gemm_counters;   // scratch of the tensor-core path, allocated by its first call
     uint32_t *status_host = nullptr;                  // pinned landing place of the status word (a pageable one makes the copy synchronous)
@@ -572,6 +573,21 @@ eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const 
     CU_TRY(cudaMemcpy(w->tiles.p, tw.tiles.data(), tw.tiles.size() * sizeof(TileDesc), cudaMemcpyHostToDevice));
     CU_TRY(cudaMemcpy(w->stream.p, tw.stream.data(), tw.stream.size(), cudaMemcpyHostToDevice));
     CU_TRY(cudaMemcpy(w->scales.p, scales, w->scale_bytes, cudaMemcpyHostToDevice));
+    if (tw.kind == EOQ_B200_KIND_INT4_ABSMAX && tw.G == 3) {
+        // [group][row triple] -> {s0 | s1 << 16, s2}, zero for rows past N: what a lane of the pair kernel needs for one
+        // run of columns, in one coalesced 8-byte load
+        const uint32_t sg = tw.K / tw.group, triples = tw.Npad / 3;
+        std::vector<uint32_t> t((size_t)sg * triples * 2, 0u);
+        for (uint32_t g = 0; g < sg; g++)
+            for (uint32_t i = 0; i < triples; i++) {
+                uint32_t v[3];
+                for (uint32_t j = 0; j < 3; j++) v[j] = 3 * i + j < tw.N ? scales[(size_t)(3 * i + j) * sg + g] : 0u;
+                t[((size_t)g * triples + i) * 2] = v[0] | (v[1] << 16);
+                t[((size_t)g * triples + i) * 2 + 1] = v[2];
+            }
+        if (w->scales_t.alloc(t.size() * 4) != cudaSuccess) return EOQ_ERR_ALLOC;
+        CU_TRY(cudaMemcpy(w->scales_t.p, t.data(), t.size() * 4, cudaMemcpyHostToDevice));
+    }
     CU_TRY(cudaMemset(w->counters.p, 0, (size_t)tw.nrb * 4));
     CU_TRY(cudaMemset(w->status.p, 0, 4));
     CU_TRY(cudaMallocHost(reinterpret_cast<void **>(&w->status_host), 64));
@@ -729,7 +745,7 @@ extern "C" eoq_error_t eoq_b200_gemv(eoq_b200_weight_t *w, const void *x, int x_
     a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
     a.x = x; a.y = y; a.bias = bias; a.partials = w->partials.as<float>(); a.counters = w->counters.as<uint32_t>(); a.status = w->status.as<uint32_t>();
     a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
-    a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols;
+    a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols; a.scales_t = w->scales_t.as<uint2>();
     a.x_dtype = x_dtype; a.y_dtype = y_dtype;
     int e = launch_gemv(a, w->G, w->bits, w->kind, stream);
     if (e != 0) { std::fprintf(stderr, "eoq_b200_gemv: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
@@ -869,7 +885,7 @@ extern "C" eoq_error_t eoq_b200_gemv_gather(eoq_b200_weight_t *w, const void *x,
     a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
     a.x = x; a.bias = bias; a.partials = w->partials.as<float>(); a.counters = w->counters.as<uint32_t>(); a.status = w->status.as<uint32_t>();
     a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
-    a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols;
+    a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols; a.scales_t = w->scales_t.as<uint2>();
     a.x_dtype = x_dtype; a.y_dtype = y_dtype;
     a.world = g->world; a.rank = g->rank; a.row_offset = row_offset; a.n_total = n_total;
     for (uint32_t p = 0; p < g->world; p++) a.peer_ll[p] = reinterpret_cast<uint64_t *>(g->base[p] + g->ll_off(slot));
@@ -1057,7 +1073,7 @@ extern "C" eoq_error_t eoq_b200_gemv_static_scratch(eoq_b200_weight_t *w, const 
     a.counters = reinterpret_cast<uint32_t *>(scratch);
     a.status = w->status.as<uint32_t>();
     a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
-    a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols;
+    a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols; a.scales_t = w->scales_t.as<uint2>();
     a.x_dtype = x_dtype; a.y_dtype = y_dtype;
     int e = launch_gemv(a, w->G, w->bits, w->kind, stream);
     if (e != 0) { std::fprintf(stderr, "eoq_b200_gemv_static_scratch: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }

@@ -6,6 +6,8 @@
 #include <string>
 #include <vector>
 
+#include <vector_types.h>
+
 #include "../../include/eoq_b200.h"
 
 namespace eoq {
@@ -98,6 +100,7 @@ struct GemvArgs {
     // Pair kernel: row blocks, bytes of one staged-tile buffer (longest tile + one row, rounded to 128) and the
     // widest column segment; zero if the caller has not worked them out (the ring kernel is used then).
     uint32_t nrb, stage_bytes, max_ncols;
+    const uint2 *scales_t;      // [K/group][Npad/3] words {s0 | s1 << 16, s2}: the fp16 scales of rows 3i..3i+2, zero past N; or null
     // Fused all-gather of row-sharded outputs (world > 1): this rank's rows go into its own full-size output and,
     // as 8-byte {value bits, epoch} words, into every peer's receive buffer; gather_wait_kernel on each rank
     // unpacks what the others sent.  8-byte stores arrive whole, so no fence or separate flag is needed.

@@ -129,6 +129,13 @@ __device__ __forceinline__ uint16_t ldg_u16_pinned(const uint16_t *p)
     return v;
 }
 
+__device__ __forceinline__ uint2 ldg_u32x2_pinned(const uint2 *p)
+{
+    uint2 v;
+    asm volatile("ld.global.nc.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+
 // Geometry of the per-warp word ring (see "Streaming a tile's renormalisation words" below): rows of 32 x u16,
 // filled in chunks, checked every kSync steps.  64 rows in four chunks is the least that covers the encoder's drift
 // bound.
@@ -896,6 +903,17 @@ static size_t pair_smem_bytes(uint32_t p, uint32_t bt, uint32_t stage, uint32_t 
     return ((size_t)4 << p) + 128 + (size_t)warps * pair_region_bytes(stage, max_ncols, bt);
 }
 
+// Bounded wait on try_wait: the warp is suspended by the hardware between polls instead of spinning through issue slots.
+__device__ __forceinline__ void mbar_wait_suspended(uint32_t bar, uint32_t parity, uint32_t *status)
+{
+    for (uint32_t i = 0; i < (1u << 20); i++) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return;
+    }
+    *status = 1u;   // gave up; the host turns this into an error
+}
+
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
 
 // Renormalise from a staged tile: x = x * 65536 + w; addr += 64; w = [addr]  (predicated, branch-free).
@@ -1080,7 +1098,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
     __syncwarp();
 
     const uint32_t nrbp = (a.nrb + 1u) / 2u, npairs = nrbp * a.nseg;
-    const uint32_t sgroups = a.K / a.group;
     const uint32_t mask = (1u << a.p) - 1u, p = a.p;
     const uint32_t magic0 = Int4Field<F::field_bit(0)>::magic_reg();
     const uint32_t magic1 = Int4Field<F::field_bit(G > 1 ? 1 : 0)>::magic_reg();
@@ -1166,13 +1183,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
         __syncwarp();
     };
 
-    // CTA c takes `cs` consecutive pairs at a time (sixteen, or fewer when there are not enough pairs to give every
-    // SM sixteen): neighbouring column segments of (mostly) one pair of row blocks, whose results it adds up in
-    // shared memory before anything goes to global memory.
-    const uint32_t cs = min((uint32_t)kWarps, (npairs + gridDim.x - 1u) / gridDim.x);
-    uint32_t base = blockIdx.x * cs;
-    uint32_t q = base + warp;
-    bool have = warp < cs && q < npairs;
+    // The pairs are cut into nchunks = waves x gridDim.x runs of consecutive pairs, as equal as possible and at most
+    // sixteen long; CTA c takes chunks c, c + gridDim.x, ...  A chunk holds neighbouring column segments of (mostly)
+    // one pair of row blocks, whose results the CTA adds up in shared memory before anything goes to global memory.
+    const uint32_t nchunks = ((npairs + kWarps * gridDim.x - 1u) / (kWarps * gridDim.x)) * gridDim.x;
+    auto chunk_lo = [&](uint32_t t) { return (uint32_t)((uint64_t)t * npairs / nchunks); };
+    auto chunk_of = [&](uint32_t qq) { return (uint32_t)((((uint64_t)qq + 1u) * nchunks - 1u) / npairs); };
+    uint32_t t = blockIdx.x;
+    uint32_t cs = chunk_lo(t + 1) - chunk_lo(t);
+    uint32_t q = chunk_lo(t) + warp;
+    bool have = warp < cs;
     if (have) open_pair(q);
     EOQ_STAMP(6);
     __syncthreads();                                   // the table barrier is initialised before anyone polls it
@@ -1180,9 +1200,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
     EOQ_STAMP(1);
     if (have) load_x_segment(true);
     EOQ_STAMP(7);
-    mbar_wait_bounded(tab_bar, 0u, a.status);
+    mbar_wait_suspended(tab_bar, 0u, a.status);
 
-    for (uint32_t it = 0; base < npairs; it++) {
+    for (uint32_t it = 0; t < nchunks; it++) {
         const uint32_t parity = it & 1u;
         const TileDesc da = d[0], db = d[1];
         const bool cur_b = has_b, cur_have = have;
@@ -1196,10 +1216,26 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                 for (int b = 0; b < BT; b++) y[k][j][b] = 0.0f;
 
         if (cur_have) {
+            // group scales of the first two runs: requested before anything is waited for, used at the end of a run
+            // (transposed copy of the scales: one 8-byte word holds the three scales of a lane's rows for one group, and the
+            // words of a warp's 32 lanes are contiguous, so a run's scales are one coalesced load per tile)
+            const uint32_t sc_stride = a.Npad / G;
+            const uint2 *sc_ptr[2];
+            uint2 sc_cur[2], sc_next[2];
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                sc_ptr[k] = a.scales_t + row[k] / G;
+                sc_cur[k] = ldg_u32x2_pinned(sc_ptr[k] + (size_t)(da.col0 / a.group) * sc_stride);
+                sc_next[k] = make_uint2(0u, 0u);
+            }
+            if ((da.col0 / a.group + 1) * a.group < da.col0 + da.ncols) {
+#pragma unroll
+                for (int k = 0; k < 2; k++) sc_next[k] = ldg_u32x2_pinned(sc_ptr[k] + (size_t)(da.col0 / a.group + 1) * sc_stride);
+            }
             PairChain ch[2];
 #pragma unroll
             for (int k = 0; k < 2; k++) {
-                mbar_wait_bounded(bars + k * 64, parity, a.status);
+                mbar_wait_suspended(bars + k * 64, parity, a.status);
                 ch[k].x = lds_u32(stage[k] + lane * 4u);
                 ch[k].addr = stage[k] + 128u + lane * 2u;
                 ch[k].w = lds_u16(ch[k].addr);
@@ -1207,26 +1243,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
             EOQ_STAMP(2);
             uint32_t c = da.col0;
             const uint32_t col0 = da.col0, cend = da.col0 + da.ncols;
-            uint16_t sc_next[2][G];
-#pragma unroll
-            for (int k = 0; k < 2; k++)
-#pragma unroll
-                for (int j = 0; j < G; j++) sc_next[k][j] = ldg_u16_pinned(a.scales + (size_t)min(row[k] + j, a.N - 1) * sgroups + c / a.group);
             const uint32_t nchunks0 = min(kMaxChunks, ((da.len64 << 6) + kChunk - 1) / kChunk), nchunks1 = min(kMaxChunks, ((db.len64 << 6) + kChunk - 1) / kChunk);
             while (c < cend) {
                 const uint32_t g = c / a.group;
                 const uint32_t rstart = c, rend = min(cend, (g + 1) * a.group);
-                uint16_t sc_bits[2][G];
-#pragma unroll
-                for (int k = 0; k < 2; k++)
-#pragma unroll
-                    for (int j = 0; j < G; j++) sc_bits[k][j] = sc_next[k][j];
-                if (rend < cend) {
-#pragma unroll
-                    for (int k = 0; k < 2; k++)
-#pragma unroll
-                        for (int j = 0; j < G; j++) sc_next[k][j] = ldg_u16_pinned(a.scales + (size_t)min(row[k] + j, a.N - 1) * sgroups + g + 1);
-                }
                 float acc[2][G][BT];
 #pragma unroll
                 for (int k = 0; k < 2; k++)
@@ -1244,8 +1264,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                     pair_steps4<G, BT>(xp + 4 * BT, tab_addr, mask, p, magic0, magic1, magic2, c64, c1, ch[0], ch[1], acc);
                     if (((c - col0) & 8u) == 0) {
                         const uint32_t j = (c - col0) / 16u + 1u;
-                        if (j < nchunks0) mbar_wait_bounded(bars + j * 8, parity, a.status);
-                        if (j < nchunks1) mbar_wait_bounded(bars + 64 + j * 8, parity, a.status);
+                        if (j < nchunks0) mbar_wait_suspended(bars + j * 8, parity, a.status);
+                        if (j < nchunks1) mbar_wait_suspended(bars + 64 + j * 8, parity, a.status);
                     }
                 }
 
@@ -1262,10 +1282,18 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                 for (int k = 0; k < 2; k++)
 #pragma unroll
                     for (int j = 0; j < G; j++) {
-                        const float sc = row[k] + j < a.N ? half_bits_to_float(sc_bits[k][j]) : 0.0f;
+                        // rows past the matrix have scale 0 in the transposed copy
+                        const float sc = half_bits_to_float((uint16_t)(j == 0 ? sc_cur[k].x : j == 1 ? sc_cur[k].x >> 16 : sc_cur[k].y));
 #pragma unroll
                         for (int b = 0; b < BT; b++) y[k][j][b] = fmaf(sc, acc[k][j][b] - corr[j] * rs[b], y[k][j][b]);
                     }
+                // rotate the scales at the end of the run, when the loads issued a run ago have long landed
+#pragma unroll
+                for (int k = 0; k < 2; k++) sc_cur[k] = sc_next[k];
+                if ((g + 2) * a.group < cend) {
+#pragma unroll
+                    for (int k = 0; k < 2; k++) sc_next[k] = ldg_u32x2_pinned(sc_ptr[k] + (size_t)(g + 2) * sc_stride);
+                }
             }
             __syncwarp();
             EOQ_STAMP(3);
@@ -1284,7 +1312,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
         const uint32_t rbp = q / a.nseg, seg = q - rbp * a.nseg;
         const bool leader = cur_have && (warp == 0 || seg == 0);
         if (leader) {
-            const uint32_t run = min(min(cs - warp, a.nseg - seg), npairs - q);
+            const uint32_t run = min(cs - warp, a.nseg - seg);
             for (uint32_t w = 1; w < run; w++) {
                 const float *red = reinterpret_cast<const float *>(mine + (size_t)w * region);
 #pragma unroll
@@ -1294,9 +1322,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
 #pragma unroll
                         for (int b = 0; b < BT; b++) y[k][j][b] += red[((k * G + j) * BT + b) * 32 + lane];
             }
-            // runs of this row-block pair are numbered by the chunk of `cs` pairs they fall in
+            // runs of this row-block pair are numbered by the chunk they fall in
             const uint32_t first_q = rbp * a.nseg;
-            const uint32_t slot = q / cs - first_q / cs, count = (first_q + a.nseg - 1u) / cs - first_q / cs + 1u;
+            const uint32_t slot = t - chunk_of(first_q), count = chunk_of(first_q + a.nseg - 1u) - chunk_of(first_q) + 1u;
             bool last = true;
             if (count > 1) {
 #pragma unroll
@@ -1323,16 +1351,28 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                         for (int j = 0; j < G; j++)
 #pragma unroll
                             for (int b = 0; b < BT; b++) y[k][j][b] = 0.0f;
-                    for (uint32_t s = 0; s < count; s++) {
+                    constexpr int kU = BT <= 2 ? 4 : 2;     // runs whose loads are in flight together
+                    for (uint32_t s0 = 0; s0 < count; s0 += kU) {
+                        float v[kU][2][G][BT];
 #pragma unroll
-                        for (int k = 0; k < 2; k++) {
-                            if (k == 1 && !cur_b) continue;
-                            const float *src = a.partials + ((size_t)s * a.Npad + row[k]) * BT;
+                        for (int u = 0; u < kU; u++)
 #pragma unroll
-                            for (int j = 0; j < G; j++)
+                            for (int k = 0; k < 2; k++) {
+                                const float *src = a.partials + ((size_t)min(s0 + u, count - 1u) * a.Npad + row[k]) * BT;
 #pragma unroll
-                                for (int b = 0; b < BT; b++) y[k][j][b] += __ldcg(src + j * BT + b);
-                        }
+                                for (int j = 0; j < G; j++)
+#pragma unroll
+                                    for (int b = 0; b < BT; b++) v[u][k][j][b] = (k == 0 || cur_b) ? __ldcg(src + j * BT + b) : 0.0f;
+                            }
+#pragma unroll
+                        for (int u = 0; u < kU; u++)
+                            if (s0 + u < count)
+#pragma unroll
+                                for (int k = 0; k < 2; k++)
+#pragma unroll
+                                    for (int j = 0; j < G; j++)
+#pragma unroll
+                                        for (int b = 0; b < BT; b++) y[k][j][b] += v[u][k][j][b];
                     }
                     if (lane == 0) a.counters[da.row0 / (32u * G)] = 0u;
                 }
@@ -1344,11 +1384,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
         }
         EOQ_STAMP(5);
 
-        base += gridDim.x * cs;
-        if (base < npairs) {
+        t += gridDim.x;
+        if (t < nchunks) {
             __syncthreads();                           // every leader has read the sums before the buffers are refilled
-            q = base + warp;
-            have = warp < cs && q < npairs;
+            cs = chunk_lo(t + 1) - chunk_lo(t);
+            q = chunk_lo(t) + warp;
+            have = warp < cs;
             if (have) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the copies overwrite buffers read through ordinary loads
                 open_pair(q);
@@ -1370,7 +1411,7 @@ static int launch_gemv_pairs(const GemvArgs &a, cudaStream_t st)
     static std::mutex mu;
     constexpr int THREADS = 512;
     auto kern = gemv_pairs_kernel<G, BT, THREADS>;
-    if (a.stage_bytes == 0 || a.stage_bytes > 8192u || a.max_ncols == 0 || a.nrb == 0) return -1;   // eight 1 KB chunks per tile
+    if (a.stage_bytes == 0 || a.stage_bytes > 8192u || a.max_ncols == 0 || a.nrb == 0 || !a.scales_t) return -1;   // eight 1 KB chunks per tile
     const size_t smem = pair_smem_bytes(a.p, BT, a.stage_bytes, a.max_ncols, THREADS / 32);
     if (smem > 227 * 1024) return -1;
     int dev = 0;
@@ -1388,9 +1429,7 @@ static int launch_gemv_pairs(const GemvArgs &a, cudaStream_t st)
         c = slot;
     }
     const uint32_t npairs = ((a.nrb + 1u) / 2u) * a.nseg;
-    // sixteen pairs per CTA when there are that many per SM, else as few per CTA as still fills the SMs once
-    const uint32_t per_cta = max(1u, min((uint32_t)(THREADS / 32), (npairs + c.sms - 1) / c.sms));
-    const uint32_t grid = max(1u, min((uint32_t)c.sms, (npairs + per_cta - 1) / per_cta));
+    const uint32_t grid = max(1u, min((uint32_t)c.sms, npairs));   // the kernel cuts the pairs into equal runs per CTA
     e = launch_with_pdl(kern, dim3(grid), dim3(THREADS), smem, st, a);
     g_launches++;
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
