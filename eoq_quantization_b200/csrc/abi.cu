@@ -774,7 +774,7 @@ extern "C" eoq_error_t eoq_b200_gemm(eoq_b200_weight_t *w, const void *x, int x_
     }
     for (uint32_t m0 = 0; m0 < m; m0 += 128) {     // 128 activation rows share one pass over the compressed weight
         const uint32_t mb = std::min(128u, m - m0);
-        int e = launch_gemm_tc(w->table.as<uint32_t>(), w->tiles.as<TileDesc>(), w->stream.as<uint8_t>(), w->scales.as<uint16_t>(),
+        int e = launch_gemm_tc(w->table.as<uint32_t>(), w->tiles.as<TileDesc>(), w->stream.as<uint8_t>(), w->scales_t.as<uint2>(),
                                static_cast<const uint8_t *>(x) + (size_t)m0 * w->K * esz[x_dtype], w->gemm_x.p,
                                w->gemm_partials.as<float>(), w->gemm_counters.as<uint32_t>(),
                                static_cast<uint8_t *>(y) + (size_t)m0 * w->N * esz[y_dtype], bias, w->status.as<uint32_t>(),

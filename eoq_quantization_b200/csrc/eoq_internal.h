@@ -138,7 +138,7 @@ int launch_decode_v1_resume(const uint8_t *d_block, uint32_t stream_end, const V
                             uint32_t p, void *stream);
 int launch_dequant_packed(const uint8_t *packed, const uint16_t *scales, uint32_t K, uint32_t row_bytes, uint32_t bits,
                           uint32_t group, uint32_t row_lo, uint32_t row_hi, void *out, int out_dtype, void *stream);
-int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *stream, const uint16_t *scales, const void *x,
+int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *stream, const uint2 *scales_t, const void *x,
                    void *xhalf, float *partials, uint32_t *counters, void *y, const float *bias, uint32_t *status, uint32_t N,
                    uint32_t K, uint32_t group, uint32_t p, uint32_t nseg, uint32_t nrb, uint32_t M, int x_dtype, int y_dtype, void *stream_);
 uint32_t gemm_grid(uint32_t nrb, uint32_t nseg);

@@ -1884,7 +1884,7 @@ struct GemmArgs {
     const uint32_t *table;
     const TileDesc *tiles;
     const uint8_t  *stream;
-    const uint16_t *scales;
+    const uint2    *scales_t; // [K/group][nrb * 32] words {s0 | s1 << 16, s2}: see GemvArgs::scales_t
     void           *y;        // [M, N]
     const float    *bias;
     float          *partials; // [grid][2][128][96]
@@ -2097,7 +2097,7 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
     asm volatile("griddepcontrol.wait;" ::: "memory");
     GEMM_STAMP(1);
 
-    const uint32_t mask = (1u << a.p) - 1u, p = a.p, sgroups = a.K / a.group, tab_addr = smem_addr(tab);
+    const uint32_t mask = (1u << a.p) - 1u, p = a.p, tab_addr = smem_addr(tab);
     // fp32 accumulate, A = X and B = W both fp16 and K-major, N = 96, M = 128
     const uint32_t idesc = (1u << 4) | ((kGemmRows >> 3) << 17) | ((kGemmTokens >> 4) << 24);
     GemmWarp gw;
@@ -2152,24 +2152,21 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
                 asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.stream + ((size_t)nd.off64 << 6)), "r"(nd.len64 << 6) : "memory");
             }
             const uint32_t row = d.row0 + lane * 3;
-            const uint16_t *srow[3];
-#pragma unroll
-            for (int j = 0; j < 3; j++) srow[j] = a.scales + (size_t)min(row + j, a.N - 1u) * sgroups;
-            uint16_t sc_next[3];
-#pragma unroll
-            for (int j = 0; j < 3; j++) sc_next[j] = ldg_u16_pinned(srow[j] + d.col0 / a.group);
+            // transposed copy of the scales: the three scales of a lane's rows for one group are one 8-byte word, the
+            // words of the 32 lanes contiguous (zero for rows past the matrix)
+            const uint2 *srow = a.scales_t + row / 3u;
+            const uint32_t sc_stride = a.nrb * 32u;
+            uint2 sc_next = ldg_u32x2_pinned(srow + (size_t)(d.col0 / a.group) * sc_stride);
             float sc[3] = {0.0f, 0.0f, 0.0f};
             const uint32_t cend = d.col0 + d.ncols;
             for (uint32_t c = d.col0; c < cend; c += 16) {
                 if (c == d.col0 || c % a.group == 0) {
                     // scales of this group were requested a group ago; request the next group's now
                     const uint32_t g = c / a.group;
-#pragma unroll
-                    for (int j = 0; j < 3; j++) sc[j] = row + j < a.N ? half_bits_to_float(sc_next[j]) : 0.0f;
-                    if ((g + 1) * a.group < cend) {
-#pragma unroll
-                        for (int j = 0; j < 3; j++) sc_next[j] = ldg_u16_pinned(srow[j] + g + 1);
-                    }
+                    sc[0] = half_bits_to_float((uint16_t)sc_next.x);
+                    sc[1] = half_bits_to_float((uint16_t)(sc_next.x >> 16));
+                    sc[2] = half_bits_to_float((uint16_t)sc_next.y);
+                    if ((g + 1) * a.group < cend) sc_next = ldg_u32x2_pinned(srow + (size_t)(g + 1) * sc_stride);
                 }
                 if (ring_mode) {
                     {
@@ -2310,7 +2307,7 @@ uint32_t gemm_grid(uint32_t nrb, uint32_t nseg)
 }
 
 // x: [M, K] row-major, M <= 128.  fp32 and bf16 activations are first rounded to fp16 into `xhalf` ([128, K] fp16 scratch).
-int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *stream, const uint16_t *scales, const void *x,
+int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *stream, const uint2 *scales_t, const void *x,
                    void *xhalf, float *partials, uint32_t *counters, void *y, const float *bias, uint32_t *status, uint32_t N,
                    uint32_t K, uint32_t group, uint32_t p, uint32_t nseg, uint32_t nrb, uint32_t M, int x_dtype, int y_dtype, void *stream_)
 {
@@ -2362,7 +2359,7 @@ int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *
     if (encode(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x16), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return (int)cudaErrorInvalidValue;
-    a.table = table; a.tiles = tiles; a.stream = stream; a.scales = scales; a.y = y; a.bias = bias;
+    a.table = table; a.tiles = tiles; a.stream = stream; a.scales_t = scales_t; a.y = y; a.bias = bias;
     a.partials = partials; a.counters = counters; a.status = status;
     a.N = N; a.K = K; a.group = group; a.p = p; a.nseg = nseg; a.nrb = nrb; a.M = M;
     a.y_dtype = y_dtype;
