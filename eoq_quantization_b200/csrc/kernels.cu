@@ -1438,9 +1438,23 @@ static int launch_gemv_pairs(const GemvArgs &a, cudaStream_t st)
 int launch_gemv(const GemvArgs &a, uint32_t G, uint32_t bits, uint32_t kind, void *stream)
 {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    if (kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 4 && G == 3 && a.batch <= 4 && g_gemv_pairs.load()) {
-        const int r = a.batch <= 1 ? launch_gemv_pairs<3, 1>(a, st) : a.batch <= 2 ? launch_gemv_pairs<3, 2>(a, st) : launch_gemv_pairs<3, 4>(a, st);
-        if (r != -1) return r;
+    if (kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 4 && G == 3 && g_gemv_pairs.load() && a.stage_bytes && a.scales_t) {
+        // The pair kernel takes as many activation rows per launch as leave room for its staging buffers (4, else 2);
+        // more rows run as consecutive launches over row slices, which is still faster than one launch of the ring kernel.
+        const uint32_t per = pair_smem_bytes(a.p, 4, a.stage_bytes, a.max_ncols, 16) <= 227 * 1024 ? 4u
+                           : pair_smem_bytes(a.p, 2, a.stage_bytes, a.max_ncols, 16) <= 227 * 1024 ? 2u : 0u;
+        if (per && a.stage_bytes <= 8192u && (a.batch <= per || a.world <= 1)) {
+            static const size_t esz[3] = {2, 2, 4};
+            for (uint32_t b0 = 0; b0 < a.batch; b0 += per) {
+                GemvArgs s = a;
+                s.batch = min(per, a.batch - b0);
+                s.x = static_cast<const uint8_t *>(a.x) + (size_t)b0 * a.K * esz[a.x_dtype];
+                s.y = static_cast<uint8_t *>(a.y) + (size_t)b0 * a.N * esz[a.y_dtype];
+                const int r = s.batch <= 1 ? launch_gemv_pairs<3, 1>(s, st) : s.batch <= 2 ? launch_gemv_pairs<3, 2>(s, st) : launch_gemv_pairs<3, 4>(s, st);
+                if (r != 0) return r == -1 ? (int)cudaErrorInvalidValue : r;
+            }
+            return 0;
+        }
     }
     if (kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 4) {
         if (G == 1) return launch_gemv_bt<1, 4, EOQ_B200_KIND_INT4_ABSMAX>(a, st);
