@@ -903,13 +903,17 @@ static size_t pair_smem_bytes(uint32_t p, uint32_t bt, uint32_t stage, uint32_t 
     return ((size_t)4 << p) + 128 + (size_t)warps * pair_region_bytes(stage, max_ncols, bt);
 }
 
-// Bounded wait on try_wait: the warp is suspended by the hardware between polls instead of spinning through issue slots.
+// Bounded wait on try_wait: the warp is suspended by the hardware between polls instead of spinning through issue
+// slots.  A poll may sleep for a system-dependent time, so the bound is on elapsed time (about a second), not on polls.
 __device__ __forceinline__ void mbar_wait_suspended(uint32_t bar, uint32_t parity, uint32_t *status)
 {
-    for (uint32_t i = 0; i < (1u << 20); i++) {
+    long long t0 = 0;
+    for (uint32_t i = 0;; i++) {
         uint32_t ok;
         asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return;
+        if (i == 0) t0 = clock64();
+        else if (clock64() - t0 > (1ll << 31)) break;      // ~1 s at 2 GHz
     }
     *status = 1u;   // gave up; the host turns this into an error
 }
@@ -1202,8 +1206,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
     EOQ_STAMP(7);
     mbar_wait_suspended(tab_bar, 0u, a.status);
 
-    for (uint32_t it = 0; t < nchunks; it++) {
-        const uint32_t parity = it & 1u;
+    // `uses` counts the pairs this warp has opened: a warp that sits out a short chunk does not arm its barriers,
+    // so their phase follows its own count, not the CTA's trip count
+    for (uint32_t uses = 0; t < nchunks;) {
+        const uint32_t parity = uses & 1u;
         const TileDesc da = d[0], db = d[1];
         const bool cur_b = has_b, cur_have = have;
         const uint32_t row[2] = {da.row0 + lane * G, db.row0 + lane * G};
@@ -1216,6 +1222,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                 for (int b = 0; b < BT; b++) y[k][j][b] = 0.0f;
 
         if (cur_have) {
+            uses++;
             // group scales of the first two runs: requested before anything is waited for, used at the end of a run
             // (transposed copy of the scales: one 8-byte word holds the three scales of a lane's rows for one group, and the
             // words of a warp's 32 lanes are contiguous, so a run's scales are one coalesced load per tile)

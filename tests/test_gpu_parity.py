@@ -389,6 +389,27 @@ def test_full_size_gate_projection_round_trip_and_gemv():
     assert O.rel_l2(y.float().cpu().numpy(), ref16.float().cpu().numpy()) < 2e-3
 
 
+@pytest.mark.parametrize("n,k,batch", [(22016, 4096, 1), (32000, 4096, 2), (7680, 2048, 4)])
+def test_fused_gemv_over_several_waves_of_tile_pairs(n, k, batch):
+    """Shapes whose tile pairs outnumber the resident warps (the gate/up projection and the vocabulary head of the
+    Llama-7B shape): the kernel makes several passes with chunks of unequal length, so some warps sit out a pass
+    and re-arm their copy barriers later.  Results must still match dequantise-then-matmul, run to run."""
+    g = torch.Generator(device="cuda").manual_seed(n + batch)
+    wt = torch.randn(n, k, device="cuda", generator=g) * 0.02
+    blocks = wt.view(-1, 128)
+    scale = (blocks.abs().amax(dim=1) / 7).clamp(min=1e-10)
+    codes = (blocks / scale[:, None]).round().clamp(-7, 7).to(torch.int8).view(n, k)
+    s16 = scale.half()
+    w = EOQWeight.from_symbols((codes + 7).to(torch.uint8), s16)
+    dense = (codes.float().view(-1, 128) * s16.float()[:, None]).view(n, k)
+    x = torch.randn(batch, k, device="cuda", generator=g).half()
+    ref = (x.float() @ dense.T).cpu().numpy()
+    y0 = w.gemv(x)
+    assert O.rel_l2(y0.float().cpu().numpy(), ref) < TOL
+    for _ in range(3):
+        assert torch.equal(w.gemv(x), y0)
+
+
 def test_full_size_polar_q5_gemv_batches():
     """BASELINE shape 14336 x 4096, N(0, 0.015) with 0.1 % outliers at 8 sigma, PolarQuant Q5 with
     per-64 norms (core/polar_quant.py:138-264 restated in torch on the GPU as the checker): symbols
