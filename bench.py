@@ -44,7 +44,7 @@ REPLICAS = 8                       # weight copies cycled through so that the wo
 WORKLOAD = "llama7b_mlp_pair_int4_g128_rans_b1"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the fused kernel, from the ncu capture
 # summarised under profiles/
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 21376256    # profiles/gemv_tiles_kernel__llama7b_mlp_pair.md, 11008 x 4096 launch
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 22154752    # profiles/gemv_pairs_kernel__llama7b_mlp_pair.md, 11008 x 4096 launch
 
 
 def make_layer(n, k, seed):
@@ -381,7 +381,7 @@ def run_gpu_arm(args):
     up_ms = k0.elapsed_time(k1) / (reps * REPLICAS)
     peak, peak_src = measured_peak()
     up_alg = alg_bytes[0] / world
-    roof = {"bound": "hbm", "kernel": "gemv_tiles_kernel<3,4,1,int4>", "achieved": up_alg / (up_ms * 1e-3) / 1e9, "peak": peak,
+    roof = {"bound": "hbm", "kernel": "gemv_pairs_kernel<3,1,512>", "achieved": up_alg / (up_ms * 1e-3) / 1e9, "peak": peak,
             "unit": "GB/s", "frac": up_alg / (up_ms * 1e-3) / 1e9 / peak, "peak_source": peak_src,
             "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None, "launch_us": up_ms * 1e3, "algorithmic_bytes_per_launch": up_alg,
             "fp16_gemv_bytes": N_UP * K_UP * 2 // world}

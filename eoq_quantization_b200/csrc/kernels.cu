@@ -185,15 +185,20 @@ __device__ __forceinline__ void rans_step_int4(uint32_t tab_addr, uint32_t &x, u
         "and.b32 s, %0, %4;\n\t"
         "mad.lo.u32 s, s, 4, %5;\n\t"
         "ld.shared.u32 e, [s];\n\t"
+#if EOQ_SHIFT_BY_MULHI
+        "mul.hi.u32 q, %0, %14;\n\t"
+        "mul.hi.u32 f, e, 512;\n\t"
+#else
         "shr.u32 q, %0, %6;\n\t"
         "shr.u32 f, e, 23;\n\t"
+#endif
         "and.b32 b, e, %7;\n\t"
         "mad.lo.u32 %0, f, q, b;\n\t"
         "lop3.b32 %1, e, %8, %11, 0xEA;\n\t"
         "lop3.b32 %2, e, %9, %12, 0xEA;\n\t"
         "lop3.b32 %3, e, %10, %13, 0xEA;\n\t}"
         : "+r"(x), "=r"(m0), "=r"(m1), "=r"(m2)
-        : "r"(mask), "r"(tab_addr), "r"(p), "r"(bias_mask), "n"(MASK0), "n"(MASK1), "n"(MASK2), "r"(mg0), "r"(mg1), "r"(mg2));
+        : "r"(mask), "r"(tab_addr), "r"(p), "r"(bias_mask), "n"(MASK0), "n"(MASK1), "n"(MASK2), "r"(mg0), "r"(mg1), "r"(mg2), "r"(1u << (32u - p)));
 }
 
 // ---------------------------------------------------------------------------
