@@ -266,7 +266,9 @@ eoq_error_t eoq_b200_weight_info(const eoq_b200_weight_t *w, eoq_b200_weight_inf
  * decode -> unpack -> scale -> dot product in one kernel; decoded symbols are
  * never written to memory.  x is [batch, K], y is [batch, N], row-major, device
  * pointers of the given element types; bias is fp32 [N] or NULL; accumulation
- * is fp32.  Asynchronous on `stream`. */
+ * is fp32.  Asynchronous on `stream`.  One launch serves up to 2 or 4 rows of x
+ * (INT4, depending on the tile size) or up to 8 (Q5 polar); larger batches are
+ * consecutive launches over row slices on the same stream. */
 eoq_error_t eoq_b200_gemv(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch,
                           void *y, int y_dtype, const float *bias, void *stream);
 
@@ -375,7 +377,9 @@ eoq_error_t eoq_b200_dequant_packed(const uint8_t *d_packed, const uint16_t *d_s
 eoq_error_t eoq_b200_weight_status(eoq_b200_weight_t *w, void *stream);
 
 /* Diagnostic knob for sweeps; returns 0 if the key is known.  Keys:
- * "gemv_ctas_per_sm" (0 = as many CTAs of the fused kernel as fit on an SM),
+ * "gemv_ctas_per_sm" (0 = as many CTAs of the one-tile-per-warp GEMV kernel as fit on an SM),
+ * "gemv_pairs" (1 = INT4 weights with three symbols per step run through the kernel that decodes two
+ * tiles per warp, the default; 0 = always the one-tile-per-warp kernel),
  * "gemm_warps" (warps per CTA of the tensor-core kernel, 2..16; 0 = as many as fit),
  * "pdl" (1 = launch the fused kernels with programmatic stream serialisation so that their
  * set-up overlaps the previous kernel's tail, the default; 0 = plain launches). */
