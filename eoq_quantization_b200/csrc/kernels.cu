@@ -1,11 +1,13 @@
 // sm_100a kernels of the EOQ hot path.
 //
-//   gemv_tiles_kernel     fused rANS decode -> unpack -> scale -> GEMV, batch 1..8
+//   gemv_pairs_kernel     fused rANS decode -> unpack -> scale -> GEMV, INT4, 1..4 rows: two tiles per warp, staged whole
+//   gemv_tiles_kernel     the same for every kind and 1..8 rows: one tile per warp through a word ring
+//   gemm_tiles_kernel     fused rANS decode -> fp16 pieces -> tcgen05 MMA (TMEM accumulator), 9..128 rows
 //   decode_tiles_kernel   rANS decode of the tiled layout to packed INT4 / bytes / dequantised matrix
 //   decode_v1_kernel      decode of the reference wire format (one thread per independent block)
 //
-// All three are integer/byte streaming kernels bounded by instruction issue and
-// by HBM, not by tensor throughput; nothing here is shaped into a GEMM.
+// The decode and GEMV kernels are integer/byte streaming kernels bounded by the SM's integer and
+// shared-memory pipes and by HBM, not by tensor throughput; only the many-row case is a contraction.
 #include "eoq_internal.h"
 
 #include <algorithm>
@@ -886,17 +888,20 @@ static int launch_gemv_bt(const GemvArgs &a, cudaStream_t st)
 // state update -> renormalisation) and by the integer pipe, a fifth of which goes into keeping the word ring ahead
 // of its readers.  This kernel removes both: a warp decodes TWO tiles at once -- the same column segment of two
 // adjacent row blocks, so that the activations of a step are loaded once and two independent chains are in flight
-// per lane -- and each tile is copied whole into its own shared-memory buffer by two bulk asynchronous copies
-// (cp.async.bulk, the 1-D TMA path): the first kilobyte (the 32 initial states and 14 rows of words) on one
-// mbarrier, the rest on a second one that is waited for after eight steps, by which time no lane can have read
-// past row 8.  No ring, no warp votes, no wrap-around of the read address.
+// per lane -- and each tile is copied whole into its own shared-memory buffer by bulk asynchronous copies
+// (cp.async.bulk, the 1-D TMA path) of one kilobyte each, every kilobyte completing on its own mbarrier.  All copies
+// of a tile are requested when it is opened; kilobyte j (word rows 16 j - 2 .. 16 j + 13) is waited for eight steps
+// before column 16 j, by which time no lane can have read past row 16 j - 8.  No ring, no warp votes, no wrap-around
+// of the read address.
 //
 // x is not staged for the whole CTA: each warp converts only the columns of its own segment to fp32 (at most a few
 // hundred values), so the kernel has no CTA-wide prologue besides the table copy.
 //
-// Pair q = (row-block pair q / nseg, segment q % nseg); warp w of CTA c owns pairs c + gridDim.x * (w + 16 i).
-// With an odd number of row blocks the last pair decodes its one tile twice and drops the second result.
-// Cross-segment reduction, output and the fused all-gather are those of gemv_tiles_kernel.
+// Pair q = (row-block pair q / nseg, segment q % nseg).  The pairs are cut into runs of at most sixteen consecutive
+// pairs; a CTA takes one run per pass, one pair per warp, adds the results of a run up in shared memory and only
+// then meets the other CTAs that hold segments of the same rows (partial rows + a ticket, summed in run order by
+// the last to arrive).  With an odd number of row blocks the last pair decodes its one tile twice and drops the
+// second result.  Output and the fused all-gather are those of gemv_tiles_kernel.
 // ---------------------------------------------------------------------------
 __host__ __device__ inline uint32_t pair_region_bytes(uint32_t stage, uint32_t max_ncols, uint32_t bt)
 {
