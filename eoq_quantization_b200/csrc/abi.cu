@@ -518,12 +518,15 @@ struct eoq_b200_weight {
     uint32_t ntiles = 0, nseg = 0, nrb = 0;
     uint32_t stage_bytes = 0, max_ncols = 0;          // geometry of the pair kernel's staging buffers (see GemvArgs)
     DeviceBuf scales_t;                               // transposed copy of the scales for the pair kernel (INT4 x 3 only)
+    DeviceBuf pair_partials;                          // partial rows of the pair kernel, every word 0xFFFFFFFF between launches
+    size_t pair_partial_bytes = 0;
     DeviceBuf table, tiles, stream, scales, centroids, partials, counters, status, xbuf, ybuf, biasbuf;
     DeviceBuf gemm_x, gemm_partials, gemm_counters;   // scratch of the tensor-core path, allocated by its first call
     uint32_t *status_host = nullptr;                  // pinned landing place of the status word (a pageable one makes the copy synchronous)
     ~eoq_b200_weight() { if (status_host) cudaFreeHost(status_host); }
     size_t stream_bytes = 0, scale_bytes = 0, partial_bytes = 0;
     std::mutex mu;   // one call at a time may use the scratch of a weight
+    std::mutex scratch_mu;   // guards the late allocation of `partials`
 };
 
 namespace {
@@ -554,9 +557,12 @@ eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const 
     w->stream_bytes = tw.stream.size();
     w->scale_bytes = (size_t)tw.N * (tw.K / tw.group) * 2;
     w->partial_bytes = tw.nseg > 1 ? (size_t)tw.nseg * tw.Npad * 8 * sizeof(float) : 0;
+    // INT4 x 3 weights run through the pair kernel, which meets in a few partial rows; the ring kernel's scratch (one
+    // row per column segment) is allocated by the first call that needs it (see ring_scratch)
+    const bool pairs_layout = tw.kind == EOQ_B200_KIND_INT4_ABSMAX && tw.G == 3;
     if (w->table.alloc(tw.table.size() * 4) != cudaSuccess || w->tiles.alloc(tw.tiles.size() * sizeof(TileDesc)) != cudaSuccess ||
         w->stream.alloc(tw.stream.size()) != cudaSuccess || w->scales.alloc(w->scale_bytes) != cudaSuccess ||
-        w->partials.alloc(w->partial_bytes) != cudaSuccess || w->counters.alloc((size_t)tw.nrb * 4) != cudaSuccess ||
+        (!pairs_layout && w->partials.alloc(w->partial_bytes) != cudaSuccess) || w->counters.alloc((size_t)tw.nrb * 4) != cudaSuccess ||
 #ifdef EOQ_STAMPS
         w->status.alloc(4u << 20) != cudaSuccess ||
 #else
@@ -573,7 +579,10 @@ eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const 
     CU_TRY(cudaMemcpy(w->tiles.p, tw.tiles.data(), tw.tiles.size() * sizeof(TileDesc), cudaMemcpyHostToDevice));
     CU_TRY(cudaMemcpy(w->stream.p, tw.stream.data(), tw.stream.size(), cudaMemcpyHostToDevice));
     CU_TRY(cudaMemcpy(w->scales.p, scales, w->scale_bytes, cudaMemcpyHostToDevice));
-    if (tw.kind == EOQ_B200_KIND_INT4_ABSMAX && tw.G == 3) {
+    if (pairs_layout) {
+        w->pair_partial_bytes = (size_t)pair_partial_slots(tw.nrb, tw.nseg) * tw.Npad * 4 * sizeof(float);
+        if (w->pair_partials.alloc(w->pair_partial_bytes) != cudaSuccess) return EOQ_ERR_ALLOC;
+        CU_TRY(cudaMemset(w->pair_partials.p, 0xFF, w->pair_partial_bytes));
         // [group][row triple] -> {s0 | s1 << 16, s2}, zero for rows past N: what a lane of the pair kernel needs for one
         // run of columns, in one coalesced 8-byte load
         const uint32_t sg = tw.K / tw.group, triples = tw.Npad / 3;
@@ -717,9 +726,18 @@ extern "C" eoq_error_t eoq_b200_weight_info(const eoq_b200_weight_t *w, eoq_b200
     info->table_bytes = (uint64_t)4 << w->p;
     info->scale_bytes = w->scale_bytes;
     info->desc_bytes = (uint64_t)w->ntiles * sizeof(TileDesc);
-    info->scratch_bytes = w->partial_bytes + (uint64_t)w->nrb * 4;
+    info->scratch_bytes = (w->partials.p ? w->partial_bytes : 0) + w->pair_partial_bytes + (uint64_t)w->nrb * 4;
     info->bits_per_weight = (double)w->stream_bytes * 8.0 / ((double)w->N * w->K);
     return EOQ_OK;
+}
+
+// Scratch of the one-tile-per-warp GEMV kernel: one partial row per column segment.  Weights laid out for the pair
+// kernel get it on the first call that falls back to the other kernel (an allocation: not inside stream capture).
+static eoq_error_t ring_scratch(eoq_b200_weight_t *w)
+{
+    std::lock_guard<std::mutex> lock(w->scratch_mu);
+    if (w->partials.p || w->partial_bytes == 0) return EOQ_OK;
+    return w->partials.alloc(w->partial_bytes) == cudaSuccess ? EOQ_OK : EOQ_ERR_ALLOC;
 }
 
 extern "C" eoq_error_t eoq_b200_gemv(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch, void *y, int y_dtype,
@@ -729,24 +747,30 @@ extern "C" eoq_error_t eoq_b200_gemv(eoq_b200_weight_t *w, const void *x, int x_
     if (batch == 0) return EOQ_OK;
     if (batch > 8) return EOQ_ERR_UNSUPPORTED;
     if (x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2) return EOQ_ERR_UNSUPPORTED;
-    const uint32_t bt = batch <= 1 ? 1 : batch <= 2 ? 2 : batch <= 4 ? 4 : 8;
-    if (gemv_smem_bytes(w->K, w->p, bt, w->kind) > 227 * 1024) {
-        // x for this many rows does not fit shared memory beside the table: run the rows in two halves
-        if (bt == 1) return EOQ_ERR_UNSUPPORTED;
-        static const size_t esz[3] = {2, 2, 4};
-        const uint32_t half = bt / 2, first = std::min(batch, half);
-        eoq_error_t rc = eoq_b200_gemv(w, x, x_dtype, first, y, y_dtype, bias, stream);
-        if (rc != EOQ_OK || batch <= half) return rc;
-        return eoq_b200_gemv(w, static_cast<const uint8_t *>(x) + (size_t)first * w->K * esz[x_dtype], x_dtype, batch - first,
-                             static_cast<uint8_t *>(y) + (size_t)first * w->N * esz[y_dtype], y_dtype, bias, stream);
-    }
     GemvArgs a = {};
     a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
     a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
-    a.x = x; a.y = y; a.bias = bias; a.partials = w->partials.as<float>(); a.counters = w->counters.as<uint32_t>(); a.status = w->status.as<uint32_t>();
+    a.x = x; a.y = y; a.bias = bias; a.counters = w->counters.as<uint32_t>(); a.status = w->status.as<uint32_t>();
     a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
     a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols; a.scales_t = w->scales_t.as<uint2>();
+    a.pair_partials = w->pair_partials.as<float>();
     a.x_dtype = x_dtype; a.y_dtype = y_dtype;
+    if (!gemv_takes_pairs(a, w->G, w->bits, w->kind)) {
+        const uint32_t bt = batch <= 1 ? 1 : batch <= 2 ? 2 : batch <= 4 ? 4 : 8;
+        if (gemv_smem_bytes(w->K, w->p, bt, w->kind) > 227 * 1024) {
+            // x for this many rows does not fit shared memory beside the table: run the rows in two halves
+            if (bt == 1) return EOQ_ERR_UNSUPPORTED;
+            static const size_t esz[3] = {2, 2, 4};
+            const uint32_t half = bt / 2, first = std::min(batch, half);
+            eoq_error_t rc = eoq_b200_gemv(w, x, x_dtype, first, y, y_dtype, bias, stream);
+            if (rc != EOQ_OK || batch <= half) return rc;
+            return eoq_b200_gemv(w, static_cast<const uint8_t *>(x) + (size_t)first * w->K * esz[x_dtype], x_dtype, batch - first,
+                                 static_cast<uint8_t *>(y) + (size_t)first * w->N * esz[y_dtype], y_dtype, bias, stream);
+        }
+        eoq_error_t rc = ring_scratch(w);
+        if (rc != EOQ_OK) return rc;
+        a.partials = w->partials.as<float>();
+    }
     int e = launch_gemv(a, w->G, w->bits, w->kind, stream);
     if (e != 0) { std::fprintf(stderr, "eoq_b200_gemv: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
     return EOQ_OK;
@@ -878,12 +902,11 @@ extern "C" eoq_error_t eoq_b200_gemv_gather(eoq_b200_weight_t *w, const void *x,
     if (row_offset != g->rank * w->N || (size_t)w->N * g->world != n_total) return EOQ_ERR_UNSUPPORTED;   // equal, rank-ordered shards
     for (uint32_t p = 0; p < g->world; p++)
         if (!g->base[p]) return EOQ_ERR_UNSUPPORTED;                    // eoq_b200_gather_connect has not run
-    const uint32_t bt = batch <= 1 ? 1 : batch <= 2 ? 2 : batch <= 4 ? 4 : 8;
-    if (gemv_smem_bytes(w->K, w->p, bt, w->kind) > 227 * 1024) return EOQ_ERR_UNSUPPORTED;
     GemvArgs a = {};
     a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
     a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
-    a.x = x; a.bias = bias; a.partials = w->partials.as<float>(); a.counters = w->counters.as<uint32_t>(); a.status = w->status.as<uint32_t>();
+    a.x = x; a.bias = bias; a.counters = w->counters.as<uint32_t>(); a.status = w->status.as<uint32_t>();
+    a.pair_partials = w->pair_partials.as<float>();
     a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
     a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols; a.scales_t = w->scales_t.as<uint2>();
     a.x_dtype = x_dtype; a.y_dtype = y_dtype;
@@ -893,6 +916,13 @@ extern "C" eoq_error_t eoq_b200_gemv_gather(eoq_b200_weight_t *w, const void *x,
     uint32_t *epoch = reinterpret_cast<uint32_t *>(g->base[g->rank] + g->epoch_off(slot));
     uint32_t *done = reinterpret_cast<uint32_t *>(g->base[g->rank] + g->done_off(slot));
     a.gather_epoch = epoch;
+    if (!gemv_takes_pairs(a, w->G, w->bits, w->kind)) {
+        const uint32_t bt = batch <= 1 ? 1 : batch <= 2 ? 2 : batch <= 4 ? 4 : 8;
+        if (gemv_smem_bytes(w->K, w->p, bt, w->kind) > 227 * 1024) return EOQ_ERR_UNSUPPORTED;
+        eoq_error_t rc = ring_scratch(w);
+        if (rc != EOQ_OK) return rc;
+        a.partials = w->partials.as<float>();
+    }
     int e = launch_gemv(a, w->G, w->bits, w->kind, stream);
     if (e == 0)
         e = launch_gather_wait(a.peer_ll[g->rank], a.y, epoch, done, g->rank, w->N, n_total, batch, y_dtype, g->status.as<uint32_t>(), stream);

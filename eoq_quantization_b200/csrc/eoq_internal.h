@@ -100,6 +100,7 @@ struct GemvArgs {
     // Pair kernel: row blocks, bytes of one staged-tile buffer (longest tile + one row, rounded to 128) and the
     // widest column segment; zero if the caller has not worked them out (the ring kernel is used then).
     uint32_t nrb, stage_bytes, max_ncols;
+    float *pair_partials;       // pair kernel: partial rows [slots][Npad][BT], every word 0xFFFFFFFF between launches; null: meet through `partials` with a fence
     const uint2 *scales_t;      // [K/group][Npad/3] words {s0 | s1 << 16, s2}: the fp16 scales of rows 3i..3i+2, zero past N; or null
     // Fused all-gather of row-sharded outputs (world > 1): this rank's rows go into its own full-size output and,
     // as 8-byte {value bits, epoch} words, into every peer's receive buffer; gather_wait_kernel on each rank
@@ -149,6 +150,8 @@ void set_gemv_ctas_per_sm(int v);
 void set_gemm_warps(int v);
 void set_pdl(int v);
 void set_gemv_pairs(int v);
+uint32_t pair_partial_slots(uint32_t nrb, uint32_t nseg);
+bool gemv_takes_pairs(const GemvArgs &a, uint32_t G, uint32_t bits, uint32_t kind);
 int launch_gather_wait(const void *ll, void *y, uint32_t *epoch, uint32_t *done, uint32_t rank, uint32_t rows_per_rank,
                        uint32_t n_total, uint32_t batch, int y_dtype, uint32_t *status, void *stream);
 

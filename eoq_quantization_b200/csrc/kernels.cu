@@ -1343,7 +1343,79 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
             const uint32_t first_q = rbp * a.nseg;
             const uint32_t slot = t - chunk_of(first_q), count = chunk_of(first_q + a.nseg - 1u) - chunk_of(first_q) + 1u;
             bool last = true;
-            if (count > 1) {
+            if (count > 1 && a.pair_partials) {
+                // Partial rows meet without a fence: an empty slot holds the pattern kEmpty, a contributor stores its
+                // values and takes a ticket, and the last to take one polls the others' slots until every value has
+                // arrived (their stores were issued before their tickets, so this is a matter of nanoseconds; bounded
+                // all the same), adds them in run order and leaves the slots empty for the next launch.
+                constexpr uint32_t kEmpty = 0xFFFFFFFFu;
+                uint32_t *slots = reinterpret_cast<uint32_t *>(a.pair_partials);
+#pragma unroll
+                for (int k = 0; k < 2; k++) {
+                    if (k == 1 && !cur_b) continue;
+                    uint32_t *dst = slots + ((size_t)slot * a.Npad + row[k]) * BT;
+#pragma unroll
+                    for (int j = 0; j < G; j++)
+#pragma unroll
+                        for (int b = 0; b < BT; b++) {
+                            const uint32_t bits = __float_as_uint(y[k][j][b]);
+                            __stcg(dst + j * BT + b, bits == kEmpty ? 0x7FC00000u : bits);     // a NaN stays a NaN
+                        }
+                }
+                __syncwarp();
+                uint32_t ticket = 0;
+                if (lane == 0) ticket = atomicAdd(a.counters + da.row0 / (32u * G), 1u);
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                EOQ_STAMP(4);
+                last = ticket == count - 1u;
+                if (last) {
+                    float own[2][G][BT];
+#pragma unroll
+                    for (int k = 0; k < 2; k++)
+#pragma unroll
+                        for (int j = 0; j < G; j++)
+#pragma unroll
+                            for (int b = 0; b < BT; b++) { own[k][j][b] = y[k][j][b]; y[k][j][b] = 0.0f; }
+                    const long long t0 = clock64();
+                    for (uint32_t s = 0; s < count; s++) {
+                        uint32_t v[2][G][BT];
+                        bool all = s == slot;
+                        while (!all) {
+                            all = true;
+#pragma unroll
+                            for (int k = 0; k < 2; k++)
+#pragma unroll
+                                for (int j = 0; j < G; j++)
+#pragma unroll
+                                    for (int b = 0; b < BT; b++) {
+                                        v[k][j][b] = 0u;
+                                        if (k == 0 || cur_b) {
+                                            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v[k][j][b])
+                                                         : "l"(slots + ((size_t)s * a.Npad + row[k]) * BT + j * BT + b) : "memory");
+                                            all = all && v[k][j][b] != kEmpty;
+                                        }
+                                    }
+                            if (!all && clock64() - t0 > (1ll << 31)) { *a.status = 3u; all = true; }   // ~1 s: give up, the host reports it
+                        }
+#pragma unroll
+                        for (int k = 0; k < 2; k++)
+#pragma unroll
+                            for (int j = 0; j < G; j++)
+#pragma unroll
+                                for (int b = 0; b < BT; b++) y[k][j][b] += s == slot ? own[k][j][b] : __uint_as_float(v[k][j][b]);
+                    }
+                    for (uint32_t s = 0; s < count; s++)
+#pragma unroll
+                        for (int k = 0; k < 2; k++) {
+                            if (k == 1 && !cur_b) continue;
+#pragma unroll
+                            for (int j = 0; j < G; j++)
+#pragma unroll
+                                for (int b = 0; b < BT; b++) __stcg(slots + ((size_t)s * a.Npad + row[k]) * BT + j * BT + b, kEmpty);
+                        }
+                    if (lane == 0) a.counters[da.row0 / (32u * G)] = 0u;
+                }
+            } else if (count > 1) {
 #pragma unroll
                 for (int k = 0; k < 2; k++) {
                     if (k == 1 && !cur_b) continue;
@@ -1419,6 +1491,29 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
 static std::atomic<int> g_gemv_pairs{1};
 void set_gemv_pairs(int v) { g_gemv_pairs.store(v != 0); }
 
+// Rows of partial sums a row-block pair can need: the most runs any pair's segments are cut into on this device.
+uint32_t pair_partial_slots(uint32_t nrb, uint32_t nseg)
+{
+    const uint32_t sms = (uint32_t)std::max(1, device_sm_count());
+    const uint32_t nrbp = (nrb + 1u) / 2u, npairs = nrbp * nseg;
+    if (npairs == 0) return 0;
+    const uint32_t grid = std::max(1u, std::min(sms, npairs));
+    const uint32_t nchunks = ((npairs + 16u * grid - 1u) / (16u * grid)) * grid;
+    auto chunk_of = [&](uint32_t q) { return (uint32_t)((((uint64_t)q + 1u) * nchunks - 1u) / npairs); };
+    uint32_t most = 1;
+    for (uint32_t r = 0; r < nrbp; r++) most = std::max(most, chunk_of(r * nseg + nseg - 1u) - chunk_of(r * nseg) + 1u);
+    return most;
+}
+
+// Whether launch_gemv would take the pair kernel for these arguments (the ring kernel needs a.partials instead).
+bool gemv_takes_pairs(const GemvArgs &a, uint32_t G, uint32_t bits, uint32_t kind)
+{
+    if (!(kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 4 && G == 3 && g_gemv_pairs.load() && a.stage_bytes && a.scales_t)) return false;
+    const uint32_t per = pair_smem_bytes(a.p, 4, a.stage_bytes, a.max_ncols, 16) <= 227 * 1024 ? 4u
+                       : pair_smem_bytes(a.p, 2, a.stage_bytes, a.max_ncols, 16) <= 227 * 1024 ? 2u : 0u;
+    return per && a.stage_bytes <= 8192u && (a.batch <= per || a.world <= 1);
+}
+
 // Returns -1 if the pair kernel does not apply (shared memory), else a cudaError_t.
 template <int G, int BT>
 static int launch_gemv_pairs(const GemvArgs &a, cudaStream_t st)
@@ -1455,24 +1550,22 @@ static int launch_gemv_pairs(const GemvArgs &a, cudaStream_t st)
 int launch_gemv(const GemvArgs &a, uint32_t G, uint32_t bits, uint32_t kind, void *stream)
 {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    if (kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 4 && G == 3 && g_gemv_pairs.load() && a.stage_bytes && a.scales_t) {
+    if (gemv_takes_pairs(a, G, bits, kind)) {
         // The pair kernel takes as many activation rows per launch as leave room for its staging buffers (4, else 2);
         // more rows run as consecutive launches over row slices, which is still faster than one launch of the ring kernel.
-        const uint32_t per = pair_smem_bytes(a.p, 4, a.stage_bytes, a.max_ncols, 16) <= 227 * 1024 ? 4u
-                           : pair_smem_bytes(a.p, 2, a.stage_bytes, a.max_ncols, 16) <= 227 * 1024 ? 2u : 0u;
-        if (per && a.stage_bytes <= 8192u && (a.batch <= per || a.world <= 1)) {
-            static const size_t esz[3] = {2, 2, 4};
-            for (uint32_t b0 = 0; b0 < a.batch; b0 += per) {
-                GemvArgs s = a;
-                s.batch = min(per, a.batch - b0);
-                s.x = static_cast<const uint8_t *>(a.x) + (size_t)b0 * a.K * esz[a.x_dtype];
-                s.y = static_cast<uint8_t *>(a.y) + (size_t)b0 * a.N * esz[a.y_dtype];
-                const int r = s.batch <= 1 ? launch_gemv_pairs<3, 1>(s, st) : s.batch <= 2 ? launch_gemv_pairs<3, 2>(s, st) : launch_gemv_pairs<3, 4>(s, st);
-                if (r != 0) return r == -1 ? (int)cudaErrorInvalidValue : r;
-            }
-            return 0;
+        const uint32_t per = pair_smem_bytes(a.p, 4, a.stage_bytes, a.max_ncols, 16) <= 227 * 1024 ? 4u : 2u;
+        static const size_t esz[3] = {2, 2, 4};
+        for (uint32_t b0 = 0; b0 < a.batch; b0 += per) {
+            GemvArgs s = a;
+            s.batch = min(per, a.batch - b0);
+            s.x = static_cast<const uint8_t *>(a.x) + (size_t)b0 * a.K * esz[a.x_dtype];
+            s.y = static_cast<uint8_t *>(a.y) + (size_t)b0 * a.N * esz[a.y_dtype];
+            const int r = s.batch <= 1 ? launch_gemv_pairs<3, 1>(s, st) : s.batch <= 2 ? launch_gemv_pairs<3, 2>(s, st) : launch_gemv_pairs<3, 4>(s, st);
+            if (r != 0) return r == -1 ? (int)cudaErrorInvalidValue : r;
         }
+        return 0;
     }
+    if (a.nseg > 1 && !a.partials) return (int)cudaErrorInvalidValue;      // the ring kernel has no scratch to meet in
     if (kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 4) {
         if (G == 1) return launch_gemv_bt<1, 4, EOQ_B200_KIND_INT4_ABSMAX>(a, st);
         if (G == 2) return launch_gemv_bt<2, 4, EOQ_B200_KIND_INT4_ABSMAX>(a, st);
