@@ -268,7 +268,11 @@ eoq_error_t eoq_b200_weight_info(const eoq_b200_weight_t *w, eoq_b200_weight_inf
  * pointers of the given element types; bias is fp32 [N] or NULL; accumulation
  * is fp32.  Asynchronous on `stream`.  One launch serves up to 2 or 4 rows of x
  * (INT4, depending on the tile size) or up to 8 (Q5 polar); larger batches are
- * consecutive launches over row slices on the same stream. */
+ * consecutive launches over row slices on the same stream.  Scratch is part of
+ * the weight and allocated when it is created, with one exception: an INT4
+ * weight whose tiles do not fit the two-tiles-per-warp kernel (or that is run
+ * with "gemv_pairs" = 0) allocates the other kernel's scratch in its first call,
+ * which should therefore not be made inside stream capture. */
 eoq_error_t eoq_b200_gemv(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch,
                           void *y, int y_dtype, const float *bias, void *stream);
 

@@ -158,6 +158,21 @@ def _tiles(sym, kind, group, g=0, p=0, target=0):
     return 0, got
 
 
+def test_default_int4_layout_keeps_tiles_short_enough_to_stage_two_per_warp():
+    """The fused GEMV stages two whole tiles per warp in shared memory, which holds tiles of up to 7 x 16 columns:
+    the default layout of an INT4 weight (three symbols per step) must respect that for wide matrices too, and still
+    decode back to the symbols it was built from."""
+    rng = np.random.default_rng(5)
+    codes, _ = O.quantize_absmax((rng.standard_normal((1152, 4096)) * 0.02).astype(np.float32), 4, 128)
+    sym = (codes + 7).astype(np.uint8)
+    rc, t = _tiles(sym, L.KIND_INT4_ABSMAX, 128)
+    assert rc == 0 and t["G"] == 3
+    desc = t["desc"].reshape(-1, 6)
+    assert desc[:, 2].max() <= 112 and (desc[:, 2] % 16 == 0).all()
+    assert (desc[:, 5].astype(np.int64) * 64).max() + 64 <= 8192          # eight one-kilobyte chunks per tile
+    assert np.array_equal(O.decode_tiles(t["table"], t["p"], t["G"], t["bits"], t["desc"], t["stream"], 1152, 4096), sym)
+
+
 @pytest.mark.parametrize("n,k,g", [(24, 256, 3), (100, 512, 2), (33, 128, 1), (97, 384, 3), (1, 128, 3), (96, 128, 3)])
 def test_tile_encoder_round_trips_through_oracle(n, k, g):
     rng = np.random.default_rng(n * 1000 + k)
