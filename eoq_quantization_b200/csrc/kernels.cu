@@ -903,14 +903,15 @@ static int launch_gemv_bt(const GemvArgs &a, cudaStream_t st)
 // the last to arrive).  With an odd number of row blocks the last pair decodes its one tile twice and drops the
 // second result.  Output and the fused all-gather are those of gemv_tiles_kernel.
 // ---------------------------------------------------------------------------
-__host__ __device__ inline uint32_t pair_region_bytes(uint32_t stage, uint32_t max_ncols, uint32_t bt)
+__host__ __device__ inline uint32_t pair_region_bytes(uint32_t stage, uint32_t max_ncols, uint32_t bt, uint32_t xbytes = 4)
 {
-    // two stage buffers, 128 bytes of barriers, the warp's x segment [max_ncols][bt] and its 16-column sums
-    return 2u * stage + 128u + ((max_ncols * bt * 4u + (max_ncols / 16u) * bt * 4u + 127u) & ~127u);
+    // two stage buffers, 128 bytes of barriers, the warp's x segment [max_ncols][bt] (fp32, or the caller's 16-bit values as
+    // they are) and its 16-column sums
+    return 2u * stage + 128u + ((max_ncols * bt * xbytes + (max_ncols / 16u) * bt * 4u + 127u) & ~127u);
 }
-static size_t pair_smem_bytes(uint32_t p, uint32_t bt, uint32_t stage, uint32_t max_ncols, uint32_t warps)
+static size_t pair_smem_bytes(uint32_t p, uint32_t bt, uint32_t stage, uint32_t max_ncols, uint32_t warps, uint32_t xbytes = 4)
 {
-    return ((size_t)4 << p) + 128 + (size_t)warps * pair_region_bytes(stage, max_ncols, bt);
+    return ((size_t)4 << p) + 128 + (size_t)warps * pair_region_bytes(stage, max_ncols, bt, xbytes);
 }
 
 // Bounded wait on try_wait: the warp is suspended by the hardware between polls instead of spinning through issue
@@ -1017,8 +1018,21 @@ struct PairChain {            // per lane, one per decoded tile
 };
 
 // Four columns of both chains: one activation load, then per column a step and a renormalisation of each chain.
-template <int G, int BT>
-__device__ __forceinline__ void pair_steps4(const float *xp, uint32_t tab_addr, uint32_t mask, uint32_t p, uint32_t magic0, uint32_t magic1,
+// XH: how the x segment is kept in shared memory -- 0: fp32; 1 / 2: the caller's fp16 / bf16 values, converted here
+// (four activation rows only; halves the segment so that four rows fit beside 112-column tiles).
+template <int XH>
+__device__ __forceinline__ void x16_pair_to_float(uint32_t w, float &lo, float &hi)
+{
+    if (XH == 1) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w));
+        lo = f.x; hi = f.y;
+    } else {
+        lo = __uint_as_float(w << 16); hi = __uint_as_float(w & 0xFFFF0000u);
+    }
+}
+
+template <int G, int BT, int XH>
+__device__ __forceinline__ void pair_steps4(const void *xptr, uint32_t tab_addr, uint32_t mask, uint32_t p, uint32_t magic0, uint32_t magic1,
                                             uint32_t magic2, uint32_t c64, uint32_t c1, PairChain &ca, PairChain &cb,
                                             float (&acc)[2][G][BT])
 {
@@ -1028,7 +1042,17 @@ __device__ __forceinline__ void pair_steps4(const float *xp, uint32_t tab_addr, 
     using F2 = Int4Field<F::field_bit(G > 2 ? 2 : 0)>;
     constexpr uint32_t kM1 = (G > 1) ? F1::kMask : 0u, kM2 = (G > 2) ? F2::kMask : 0u;
     float xv[4][BT];
-    if (BT == 1) {
+    const float *xp = reinterpret_cast<const float *>(xptr);
+    if (XH != 0) {
+        static_assert(XH == 0 || BT == 4, "16-bit x segments are built for four activation rows");
+        const uint4 v0 = reinterpret_cast<const uint4 *>(xptr)[0], v1 = reinterpret_cast<const uint4 *>(xptr)[1];
+        const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};       // column s: words 2 s, 2 s + 1
+#pragma unroll
+        for (int s = 0; s < 4; s++) {
+            x16_pair_to_float<XH>(w[2 * s], xv[s][0], xv[s][1 % BT]);
+            x16_pair_to_float<XH>(w[2 * s + 1], xv[s][2 % BT], xv[s][3 % BT]);
+        }
+    } else if (BT == 1) {
         const float4 v = *reinterpret_cast<const float4 *>(xp);
         xv[0][0] = v.x; xv[1][0] = v.y; xv[2][0] = v.z; xv[3][0] = v.w;
     } else if (BT == 2) {
@@ -1077,7 +1101,7 @@ __device__ __forceinline__ void pair_steps4(const float *xp, uint32_t tab_addr, 
     }
 }
 
-template <int G, int BT, int THREADS>
+template <int G, int BT, int THREADS, int XH = 0>
 __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a)
 {
     constexpr int kWarps = THREADS / 32;
@@ -1091,12 +1115,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
 
     const uint32_t tab_bytes = 4u << a.p;
     const uint32_t tab_addr = smem_addr(smem), tab_bar = tab_addr + tab_bytes;
-    const uint32_t region = pair_region_bytes(a.stage_bytes, a.max_ncols, BT);
+    constexpr uint32_t kXBytes = XH ? 2u : 4u;
+    const uint32_t region = pair_region_bytes(a.stage_bytes, a.max_ncols, BT, kXBytes);
     uint8_t *mine = smem + tab_bytes + 128 + (size_t)warp * region;
     const uint32_t stage[2] = {smem_addr(mine), smem_addr(mine) + a.stage_bytes};
     const uint32_t bars = stage[0] + 2u * a.stage_bytes;       // [chain][chunk], 8 bytes each
     float *xs = reinterpret_cast<float *>(mine + 2u * a.stage_bytes + 128);
-    float *aux = xs + (size_t)a.max_ncols * BT;
+    uint16_t *xs16 = reinterpret_cast<uint16_t *>(xs);
+    float *aux = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(xs) + (size_t)a.max_ncols * BT * kXBytes);
 
     if (tid == 0) {
         mbar_init(tab_bar, 1);
@@ -1158,14 +1184,17 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
             const uint32_t c = base + lane * 4u;
             const bool on = c < ncols;
             float v[BT][4];
+            uint32_t raw[BT][2];          // XH: the same four values as the caller's 16-bit patterns
 #pragma unroll
             for (int b = 0; b < BT; b++) {
 #pragma unroll
                 for (int i = 0; i < 4; i++) v[b][i] = 0.0f;
+                raw[b][0] = raw[b][1] = 0u;
                 if (on && (uint32_t)b < a.batch) {
                     const size_t i0 = (size_t)b * a.K + col0 + c;
                     if (x_vec) {
                         const uint2 r = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const uint16_t *>(a.x) + i0));
+                        raw[b][0] = r.x; raw[b][1] = r.y;
                         if (a.x_dtype == EOQ_B200_F16) {
                             const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&r.x));
                             const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&r.y));
@@ -1177,6 +1206,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                     } else {
 #pragma unroll
                         for (int i = 0; i < 4; i++) v[b][i] = load_x(a.x, i0 + i, a.x_dtype);
+                        if (XH != 0) {
+                            const uint16_t *h = reinterpret_cast<const uint16_t *>(a.x) + i0;
+                            raw[b][0] = (uint32_t)h[0] | ((uint32_t)h[1] << 16);
+                            raw[b][1] = (uint32_t)h[2] | ((uint32_t)h[3] << 16);
+                        }
                     }
                 }
             }
@@ -1189,7 +1223,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                 sum += __shfl_xor_sync(0xffffffffu, sum, 2);
                 if (on) {
 #pragma unroll
-                    for (int i = 0; i < 4; i++) xs[(c + i) * BT + b] = v[b][i];
+                    for (int i = 0; i < 4; i++) {
+                        if (XH != 0) xs16[(c + i) * BT + b] = (uint16_t)(raw[b][i >> 1] >> ((i & 1) * 16));
+                        else xs[(c + i) * BT + b] = v[b][i];
+                    }
                     if ((lane & 3u) == 0) aux[(c / 16u) * BT + b] = sum;
                 }
             }
@@ -1276,9 +1313,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                 // 16 j - 2 .. 16 j + 13: waiting for chunk j eight steps before column 16 j is always early enough.
 #pragma unroll 1
                 for (; c < rend; c += 8) {
-                    const float *xp = xs + (size_t)(c - col0) * BT;
-                    pair_steps4<G, BT>(xp, tab_addr, mask, p, magic0, magic1, magic2, c64, c1, ch[0], ch[1], acc);
-                    pair_steps4<G, BT>(xp + 4 * BT, tab_addr, mask, p, magic0, magic1, magic2, c64, c1, ch[0], ch[1], acc);
+                    const uint8_t *xp = reinterpret_cast<const uint8_t *>(xs) + (size_t)(c - col0) * BT * kXBytes;
+                    pair_steps4<G, BT, XH>(xp, tab_addr, mask, p, magic0, magic1, magic2, c64, c1, ch[0], ch[1], acc);
+                    pair_steps4<G, BT, XH>(xp + 4 * BT * kXBytes, tab_addr, mask, p, magic0, magic1, magic2, c64, c1, ch[0], ch[1], acc);
                     if (((c - col0) & 8u) == 0) {
                         const uint32_t j = (c - col0) / 16u + 1u;
                         if (j < nchunks0) mbar_wait_suspended(bars + j * 8, parity, a.status);
@@ -1323,11 +1360,18 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
 #pragma unroll
                     for (int b = 0; b < BT; b++) red[((k * G + j) * BT + b) * 32 + lane] = y[k][j][b];
         }
-        __syncthreads();
-
         // The first warp of each run of pairs that share a row-block pair adds the run up, in warp order.
         const uint32_t rbp = q / a.nseg, seg = q - rbp * a.nseg;
         const bool leader = cur_have && (warp == 0 || seg == 0);
+        // A leader that will meet other CTAs through the empty-slot scheme takes its ticket now: the ticket only elects
+        // who adds up (the last to take one; every other contributor is then at least this far and needs nothing from
+        // the elected one to deliver its row), so its round trip can overlap the barrier and the sums below.
+        uint32_t early_ticket = 0;
+        const uint32_t first_q = rbp * a.nseg;
+        const uint32_t count = leader ? chunk_of(first_q + a.nseg - 1u) - chunk_of(first_q) + 1u : 1u;
+        if (leader && count > 1 && a.pair_partials && lane == 0) early_ticket = atomicAdd(a.counters + da.row0 / (32u * G), 1u);
+        __syncthreads();
+
         if (leader) {
             const uint32_t run = min(cs - warp, a.nseg - seg);
             for (uint32_t w = 1; w < run; w++) {
@@ -1340,35 +1384,32 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                         for (int b = 0; b < BT; b++) y[k][j][b] += red[((k * G + j) * BT + b) * 32 + lane];
             }
             // runs of this row-block pair are numbered by the chunk they fall in
-            const uint32_t first_q = rbp * a.nseg;
-            const uint32_t slot = t - chunk_of(first_q), count = chunk_of(first_q + a.nseg - 1u) - chunk_of(first_q) + 1u;
+            const uint32_t slot = t - chunk_of(first_q);
             bool last = true;
             if (count > 1 && a.pair_partials) {
-                // Partial rows meet without a fence: an empty slot holds the pattern kEmpty, a contributor stores its
-                // values and takes a ticket, and the last to take one polls the others' slots until every value has
-                // arrived (their stores were issued before their tickets, so this is a matter of nanoseconds; bounded
-                // all the same), adds them in run order and leaves the slots empty for the next launch.
+                // Partial rows meet without a fence: an empty slot holds the pattern kEmpty; whoever took the last ticket
+                // keeps its row in registers and polls the others' slots until every value has arrived (the others are
+                // past their tickets and on their way to these stores, so this ends within their own remaining work;
+                // bounded all the same), adds the rows in run order and leaves the slots empty for the next launch.
                 constexpr uint32_t kEmpty = 0xFFFFFFFFu;
                 uint32_t *slots = reinterpret_cast<uint32_t *>(a.pair_partials);
-#pragma unroll
-                for (int k = 0; k < 2; k++) {
-                    if (k == 1 && !cur_b) continue;
-                    uint32_t *dst = slots + ((size_t)slot * a.Npad + row[k]) * BT;
-#pragma unroll
-                    for (int j = 0; j < G; j++)
-#pragma unroll
-                        for (int b = 0; b < BT; b++) {
-                            const uint32_t bits = __float_as_uint(y[k][j][b]);
-                            __stcg(dst + j * BT + b, bits == kEmpty ? 0x7FC00000u : bits);     // a NaN stays a NaN
-                        }
-                }
-                __syncwarp();
-                uint32_t ticket = 0;
-                if (lane == 0) ticket = atomicAdd(a.counters + da.row0 / (32u * G), 1u);
-                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                const uint32_t ticket = __shfl_sync(0xffffffffu, early_ticket, 0);
                 EOQ_STAMP(4);
                 last = ticket == count - 1u;
-                if (last) {
+                if (!last) {
+#pragma unroll
+                    for (int k = 0; k < 2; k++) {
+                        if (k == 1 && !cur_b) continue;
+                        uint32_t *dst = slots + ((size_t)slot * a.Npad + row[k]) * BT;
+#pragma unroll
+                        for (int j = 0; j < G; j++)
+#pragma unroll
+                            for (int b = 0; b < BT; b++) {
+                                const uint32_t bits = __float_as_uint(y[k][j][b]);
+                                __stcg(dst + j * BT + b, bits == kEmpty ? 0x7FC00000u : bits);     // a NaN stays a NaN
+                            }
+                    }
+                } else {
                     float own[2][G][BT];
 #pragma unroll
                     for (int k = 0; k < 2; k++)
@@ -1505,26 +1546,34 @@ uint32_t pair_partial_slots(uint32_t nrb, uint32_t nseg)
     return most;
 }
 
+// Activation rows one launch of the pair kernel can take: 4 if the staging buffers leave room for four fp32 x
+// segments, or for four 16-bit ones when x is fp16 / bf16; else 2; 0 if even two do not fit.
+static uint32_t pair_rows_per_launch(const GemvArgs &a)
+{
+    if (pair_smem_bytes(a.p, 4, a.stage_bytes, a.max_ncols, 16) <= 227 * 1024) return 4;
+    if (a.x_dtype != EOQ_B200_F32 && pair_smem_bytes(a.p, 4, a.stage_bytes, a.max_ncols, 16, 2) <= 227 * 1024) return 4;
+    return pair_smem_bytes(a.p, 2, a.stage_bytes, a.max_ncols, 16) <= 227 * 1024 ? 2u : 0u;
+}
+
 // Whether launch_gemv would take the pair kernel for these arguments (the ring kernel needs a.partials instead).
 bool gemv_takes_pairs(const GemvArgs &a, uint32_t G, uint32_t bits, uint32_t kind)
 {
     if (!(kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 4 && G == 3 && g_gemv_pairs.load() && a.stage_bytes && a.scales_t)) return false;
-    const uint32_t per = pair_smem_bytes(a.p, 4, a.stage_bytes, a.max_ncols, 16) <= 227 * 1024 ? 4u
-                       : pair_smem_bytes(a.p, 2, a.stage_bytes, a.max_ncols, 16) <= 227 * 1024 ? 2u : 0u;
+    const uint32_t per = pair_rows_per_launch(a);
     return per && a.stage_bytes <= 8192u && (a.batch <= per || a.world <= 1);
 }
 
 // Returns -1 if the pair kernel does not apply (shared memory), else a cudaError_t.
-template <int G, int BT>
+template <int G, int BT, int XH = 0>
 static int launch_gemv_pairs(const GemvArgs &a, cudaStream_t st)
 {
     struct Cfg { size_t smem = 0; int sms = 0; };
     static Cfg cfg[16];
     static std::mutex mu;
     constexpr int THREADS = 512;
-    auto kern = gemv_pairs_kernel<G, BT, THREADS>;
+    auto kern = gemv_pairs_kernel<G, BT, THREADS, XH>;
     if (a.stage_bytes == 0 || a.stage_bytes > 8192u || a.max_ncols == 0 || a.nrb == 0 || !a.scales_t) return -1;   // eight 1 KB chunks per tile
-    const size_t smem = pair_smem_bytes(a.p, BT, a.stage_bytes, a.max_ncols, THREADS / 32);
+    const size_t smem = pair_smem_bytes(a.p, BT, a.stage_bytes, a.max_ncols, THREADS / 32, XH ? 2 : 4);
     if (smem > 227 * 1024) return -1;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -1553,14 +1602,17 @@ int launch_gemv(const GemvArgs &a, uint32_t G, uint32_t bits, uint32_t kind, voi
     if (gemv_takes_pairs(a, G, bits, kind)) {
         // The pair kernel takes as many activation rows per launch as leave room for its staging buffers (4, else 2);
         // more rows run as consecutive launches over row slices, which is still faster than one launch of the ring kernel.
-        const uint32_t per = pair_smem_bytes(a.p, 4, a.stage_bytes, a.max_ncols, 16) <= 227 * 1024 ? 4u : 2u;
+        const uint32_t per = pair_rows_per_launch(a);
+        const bool x16 = per == 4 && pair_smem_bytes(a.p, 4, a.stage_bytes, a.max_ncols, 16) > 227 * 1024;   // four rows only as 16-bit segments
         static const size_t esz[3] = {2, 2, 4};
         for (uint32_t b0 = 0; b0 < a.batch; b0 += per) {
             GemvArgs s = a;
             s.batch = min(per, a.batch - b0);
             s.x = static_cast<const uint8_t *>(a.x) + (size_t)b0 * a.K * esz[a.x_dtype];
             s.y = static_cast<uint8_t *>(a.y) + (size_t)b0 * a.N * esz[a.y_dtype];
-            const int r = s.batch <= 1 ? launch_gemv_pairs<3, 1>(s, st) : s.batch <= 2 ? launch_gemv_pairs<3, 2>(s, st) : launch_gemv_pairs<3, 4>(s, st);
+            const int r = s.batch <= 1 ? launch_gemv_pairs<3, 1>(s, st) : s.batch <= 2 ? launch_gemv_pairs<3, 2>(s, st)
+                        : !x16 ? launch_gemv_pairs<3, 4>(s, st)
+                        : a.x_dtype == EOQ_B200_F16 ? launch_gemv_pairs<3, 4, 1>(s, st) : launch_gemv_pairs<3, 4, 2>(s, st);
             if (r != 0) return r == -1 ? (int)cudaErrorInvalidValue : r;
         }
         return 0;

@@ -389,6 +389,30 @@ def test_full_size_gate_projection_round_trip_and_gemv():
     assert O.rel_l2(y.float().cpu().numpy(), ref16.float().cpu().numpy()) < 2e-3
 
 
+@pytest.mark.parametrize("dt,batch", [(torch.float16, 4), (torch.bfloat16, 3), (torch.float32, 4), (torch.float16, 7)])
+def test_fused_gemv_four_rows_on_a_wide_layer(dt, batch):
+    """11008 x 4096 has 112-column tiles, beside which four fp32 activation segments per warp do not fit: fp16 and
+    bf16 activations are kept as 16-bit values in shared memory instead, fp32 ones run two rows per launch, and seven
+    rows are two launches.  All must agree with dequantise-then-matmul."""
+    n, k = 11008, 4096
+    g = torch.Generator(device="cuda").manual_seed(batch)
+    wt = torch.randn(n, k, device="cuda", generator=g) * 0.02
+    blocks = wt.view(-1, 128)
+    scale = (blocks.abs().amax(dim=1) / 7).clamp(min=1e-10)
+    codes = (blocks / scale[:, None]).round().clamp(-7, 7).to(torch.int8).view(n, k)
+    s16 = scale.half()
+    w = EOQWeight.from_symbols((codes + 7).to(torch.uint8), s16)
+    dense = (codes.float().view(-1, 128) * s16.float()[:, None]).view(n, k)
+    x = torch.randn(batch, k, device="cuda", generator=g).to(dt)
+    bias = torch.randn(n, device="cuda", generator=g)
+    ref = (x.float() @ dense.T + bias).cpu().numpy()
+    y = w.gemv(x, bias=bias, out_dtype=torch.float32)
+    assert O.rel_l2(y.cpu().numpy(), ref) < TOL
+    assert torch.equal(w.gemv(x, bias=bias, out_dtype=torch.float32), y)
+    for r in range(batch):                                   # every row equals the same row run on its own
+        assert O.rel_l2(w.gemv(x[r:r + 1], bias=bias, out_dtype=torch.float32).cpu().numpy(), ref[r:r + 1]) < TOL
+
+
 @pytest.mark.parametrize("n,k,batch", [(22016, 4096, 1), (32000, 4096, 2), (7680, 2048, 4)])
 def test_fused_gemv_over_several_waves_of_tile_pairs(n, k, batch):
     """Shapes whose tile pairs outnumber the resident warps (the gate/up projection and the vocabulary head of the
