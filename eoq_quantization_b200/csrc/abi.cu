@@ -522,7 +522,18 @@ struct eoq_b200_weight {
     size_t pair_partial_bytes = 0;
     DeviceBuf table, tiles, stream, scales, centroids, partials, counters, status, xbuf, ybuf, biasbuf;
     DeviceBuf gemm_x, gemm_partials, gemm_counters;   // scratch of the tensor-core path, allocated by its first call
-    uint32_t *status_host = nullptr;                  // pinned landing place of the status word (a pageable one makes the copy synchronous)
+    // The status word the kernels set when a bounded wait expires lives in pinned host memory that the device writes
+    // directly (pinned allocations are device-addressable): a healthy launch never touches it, and reading it after a
+    // stream synchronise needs no copy.  Debug builds with per-warp time stamps keep it at the head of a device buffer.
+    uint32_t *status_host = nullptr, *status_dev = nullptr;
+    uint32_t *status_word()
+    {
+#ifdef EOQ_STAMPS
+        return status.as<uint32_t>();
+#else
+        return status_dev;
+#endif
+    }
     ~eoq_b200_weight() { if (status_host) cudaFreeHost(status_host); }
     size_t stream_bytes = 0, scale_bytes = 0, partial_bytes = 0;
     std::mutex mu;   // one call at a time may use the scratch of a weight
@@ -600,6 +611,8 @@ eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const 
     CU_TRY(cudaMemset(w->counters.p, 0, (size_t)tw.nrb * 4));
     CU_TRY(cudaMemset(w->status.p, 0, 4));
     CU_TRY(cudaMallocHost(reinterpret_cast<void **>(&w->status_host), 64));
+    std::memset(w->status_host, 0, 64);
+    CU_TRY(cudaHostGetDevicePointer(reinterpret_cast<void **>(&w->status_dev), w->status_host, 0));
     *out = w.release();
     return EOQ_OK;
 }
@@ -750,7 +763,7 @@ extern "C" eoq_error_t eoq_b200_gemv(eoq_b200_weight_t *w, const void *x, int x_
     GemvArgs a = {};
     a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
     a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
-    a.x = x; a.y = y; a.bias = bias; a.counters = w->counters.as<uint32_t>(); a.status = w->status.as<uint32_t>();
+    a.x = x; a.y = y; a.bias = bias; a.counters = w->counters.as<uint32_t>(); a.status = w->status_word();
     a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
     a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols; a.scales_t = w->scales_t.as<uint2>();
     a.pair_partials = w->pair_partials.as<float>();
@@ -801,7 +814,7 @@ extern "C" eoq_error_t eoq_b200_gemm(eoq_b200_weight_t *w, const void *x, int x_
         int e = launch_gemm_tc(w->table.as<uint32_t>(), w->tiles.as<TileDesc>(), w->stream.as<uint8_t>(), w->scales_t.as<uint2>(),
                                static_cast<const uint8_t *>(x) + (size_t)m0 * w->K * esz[x_dtype], w->gemm_x.p,
                                w->gemm_partials.as<float>(), w->gemm_counters.as<uint32_t>(),
-                               static_cast<uint8_t *>(y) + (size_t)m0 * w->N * esz[y_dtype], bias, w->status.as<uint32_t>(),
+                               static_cast<uint8_t *>(y) + (size_t)m0 * w->N * esz[y_dtype], bias, w->status_word(),
                                w->N, w->K, w->group, w->p, w->nseg, w->nrb, mb, x_dtype, y_dtype, stream);
         if (e != 0) { std::fprintf(stderr, "eoq_b200_gemm: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
     }
@@ -905,7 +918,7 @@ extern "C" eoq_error_t eoq_b200_gemv_gather(eoq_b200_weight_t *w, const void *x,
     GemvArgs a = {};
     a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
     a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
-    a.x = x; a.bias = bias; a.counters = w->counters.as<uint32_t>(); a.status = w->status.as<uint32_t>();
+    a.x = x; a.bias = bias; a.counters = w->counters.as<uint32_t>(); a.status = w->status_word();
     a.pair_partials = w->pair_partials.as<float>();
     a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
     a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols; a.scales_t = w->scales_t.as<uint2>();
@@ -965,7 +978,7 @@ extern "C" eoq_error_t eoq_b200_weight_decode(eoq_b200_weight_t *w, uint8_t *d_s
     DecodeArgs a;
     a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
     a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
-    a.status = w->status.as<uint32_t>();
+    a.status = w->status_word();
     a.out_sym = d_sym; a.out_deq = d_dequant; a.N = w->N; a.K = w->K; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles;
     a.packed = packed; a.out_dtype = out_dtype;
     int e = launch_decode_tiles(a, w->G, w->bits, w->kind, stream);
@@ -995,9 +1008,11 @@ extern "C" eoq_error_t eoq_b200_weight_status(eoq_b200_weight_t *w, void *stream
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     std::lock_guard<std::mutex> lock(w->mu);
     if (!w->status_host) return EOQ_ERR_ALLOC;
+#ifdef EOQ_STAMPS
     CU_TRY(cudaMemcpyAsync(w->status_host, w->status.p, 4, cudaMemcpyDeviceToHost, st));
+#endif
     CU_TRY(cudaStreamSynchronize(st));
-    return *w->status_host ? EOQ_ERR_CUDA : EOQ_OK;
+    return *static_cast<volatile uint32_t *>(w->status_host) ? EOQ_ERR_CUDA : EOQ_OK;
 }
 
 #ifdef EOQ_STAMPS
@@ -1101,7 +1116,7 @@ extern "C" eoq_error_t eoq_b200_gemv_static_scratch(eoq_b200_weight_t *w, const 
     a.x = x; a.y = y; a.bias = bias;
     a.partials = reinterpret_cast<float *>(scratch + counter_bytes);
     a.counters = reinterpret_cast<uint32_t *>(scratch);
-    a.status = w->status.as<uint32_t>();
+    a.status = w->status_word();
     a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
     a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols; a.scales_t = w->scales_t.as<uint2>();
     a.x_dtype = x_dtype; a.y_dtype = y_dtype;
