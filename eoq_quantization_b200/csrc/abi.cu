@@ -954,9 +954,16 @@ extern "C" eoq_error_t eoq_b200_gemv_host_async(eoq_b200_weight_t *w, const void
     std::lock_guard<std::mutex> lock(w->mu);
     CU_TRY(cudaMemcpyAsync(w->xbuf.p, x, (size_t)batch * w->K * esz[x_dtype], cudaMemcpyHostToDevice, st));
     if (bias_host) CU_TRY(cudaMemcpyAsync(w->biasbuf.p, bias_host, (size_t)w->N * 4, cudaMemcpyHostToDevice, st));
-    eoq_error_t rc = eoq_b200_gemv(w, w->xbuf.p, x_dtype, batch, w->ybuf.p, y_dtype, bias_host ? w->biasbuf.as<float>() : nullptr, stream);
+    // A pinned (page-locked) y is device-addressable: the kernel then stores its results straight into it and the
+    // copy back is not needed.  Pageable memory goes through the weight's device buffer and a copy.
+    void *y_direct = nullptr;
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, y) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer) y_direct = attr.devicePointer;
+    else (void)cudaGetLastError();
+    eoq_error_t rc = eoq_b200_gemv(w, w->xbuf.p, x_dtype, batch, y_direct ? y_direct : w->ybuf.p, y_dtype,
+                                   bias_host ? w->biasbuf.as<float>() : nullptr, stream);
     if (rc != EOQ_OK) return rc;
-    CU_TRY(cudaMemcpyAsync(y, w->ybuf.p, (size_t)batch * w->N * esz[y_dtype], cudaMemcpyDeviceToHost, st));
+    if (!y_direct) CU_TRY(cudaMemcpyAsync(y, w->ybuf.p, (size_t)batch * w->N * esz[y_dtype], cudaMemcpyDeviceToHost, st));
     return EOQ_OK;
 }
 

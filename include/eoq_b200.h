@@ -326,7 +326,9 @@ eoq_error_t eoq_b200_gemv_host(eoq_b200_weight_t *w, const void *x, int x_dtype,
  * call returns; x, y and bias_host must stay valid (and should be pinned) until the stream has
  * been synchronised, e.g. by eoq_b200_weight_status, which also reports a failed launch.
  * Several weights can be queued this way before one synchronisation; a weight must not be
- * queued again before its previous call has completed (it owns one staging buffer). */
+ * queued again before its previous call has completed (it owns one staging buffer).  A pinned
+ * y is written by the kernel itself (pinned memory is device-addressable), so no copy back is
+ * queued; a pageable y is filled by a copy from the weight's device buffer. */
 eoq_error_t eoq_b200_gemv_host_async(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch,
                                void *y, int y_dtype, const float *bias_host, void *stream);
 
