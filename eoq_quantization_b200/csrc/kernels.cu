@@ -1674,7 +1674,9 @@ int launch_gather_wait(const void *ll, void *y, uint32_t *epoch, uint32_t *done,
                        uint32_t n_total, uint32_t batch, int y_dtype, uint32_t *status, void *stream)
 {
     const uint32_t total = batch * n_total;
-    const uint32_t grid = std::max(1u, std::min(16u, (total + 2047u) / 2048u));
+    // one element per thread where possible: a thread polls its elements one after the other, and a poll of a word a
+    // peer has just written takes a microsecond or two
+    const uint32_t grid = std::max(1u, std::min(128u, (total + 255u) / 256u));
     cudaError_t e = launch_with_pdl(gather_wait_kernel, dim3(grid), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
                                     reinterpret_cast<const uint2 *>(ll), y, epoch, done, rank, rows_per_rank, n_total, batch, y_dtype, status);
     g_launches++;
