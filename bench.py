@@ -44,7 +44,7 @@ REPLICAS = 8                       # weight copies cycled through so that the wo
 WORKLOAD = "llama7b_mlp_pair_int4_g128_rans_b1"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the fused kernel, from the ncu capture
 # summarised under profiles/
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 22154752    # profiles/gemv_pairs_kernel__llama7b_mlp_pair.md, 11008 x 4096 launch
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 22162176    # profiles/gemv_pairs_kernel__llama7b_mlp_pair.md, 11008 x 4096 launch
 
 
 def make_layer(n, k, seed):
