@@ -1712,12 +1712,13 @@ __global__ void __launch_bounds__(256) decode_tiles_kernel(const DecodeArgs a)
         tile_open(ring, d, base, lane);
         const bool ring_mode = tile_begin(ring, ws, d, base, lane, x);
         const uint32_t row = d.row0 + lane * G;
-        for (uint32_t c = d.col0; c < d.col0 + d.ncols; c += 8) {
-            uint32_t sym[G][8];
+        // sixteen columns at a time: a lane's fp16 / bf16 output for one row is then a whole 32-byte sector
+        for (uint32_t c = d.col0; c < d.col0 + d.ncols; c += 16) {
+            uint32_t sym[G][16];
             if (ring_mode) {
+                ring_sync_step(ring, ws, lane);
 #pragma unroll
-                for (int s = 0; s < 8; s++) {
-                    if (s == 0 && ((c - d.col0) & 8u) == 0) ring_sync_step(ring, ws, lane);
+                for (int s = 0; s < 16; s++) {
                     const uint32_t e = rans_step(tab, x, mask, p, F::kBiasMask);
 #pragma unroll
                     for (int j = 0; j < G; j++) sym[j][s] = (e >> F::field_bit(j)) & F::kFieldMask;
@@ -1725,7 +1726,7 @@ __global__ void __launch_bounds__(256) decode_tiles_kernel(const DecodeArgs a)
                 }
             } else {
 #pragma unroll
-                for (int s = 0; s < 8; s++) {
+                for (int s = 0; s < 16; s++) {
                     const uint32_t e = rans_step(tab, x, mask, p, F::kBiasMask);
 #pragma unroll
                     for (int j = 0; j < G; j++) sym[j][s] = (e >> F::field_bit(j)) & F::kFieldMask;
@@ -1738,38 +1739,45 @@ __global__ void __launch_bounds__(256) decode_tiles_kernel(const DecodeArgs a)
                 if (r >= a.N) continue;
                 if (a.out_sym) {
                     if (a.packed) {
-                        uint32_t v = 0;
-#pragma unroll
-                        for (int s = 0; s < 8; s++) v |= sym[j][s] << (4 * s);
-                        *reinterpret_cast<uint32_t *>(a.out_sym + (size_t)r * (K / 2) + c / 2) = v;
-                    } else {
                         uint2 v = make_uint2(0, 0);
 #pragma unroll
-                        for (int s = 0; s < 4; s++) { v.x |= sym[j][s] << (8 * s); v.y |= sym[j][s + 4] << (8 * s); }
-                        *reinterpret_cast<uint2 *>(a.out_sym + (size_t)r * K + c) = v;
+                        for (int s = 0; s < 8; s++) { v.x |= sym[j][s] << (4 * s); v.y |= sym[j][s + 8] << (4 * s); }
+                        *reinterpret_cast<uint2 *>(a.out_sym + (size_t)r * (K / 2) + c / 2) = v;
+                    } else {
+                        uint4 v = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                        for (int s = 0; s < 4; s++) {
+                            v.x |= sym[j][s] << (8 * s); v.y |= sym[j][s + 4] << (8 * s);
+                            v.z |= sym[j][s + 8] << (8 * s); v.w |= sym[j][s + 12] << (8 * s);
+                        }
+                        *reinterpret_cast<uint4 *>(a.out_sym + (size_t)r * K + c) = v;
                     }
                 }
                 if (a.out_deq && KIND == EOQ_B200_KIND_INT4_ABSMAX) {
-                    // group is a multiple of 16 and c of 8, so the eight columns share one scale
+                    // group is a multiple of 16 and so is c, so the sixteen columns share one scale
                     const float sc = half_bits_to_float(__ldg(a.scales + (size_t)r * sgroups + c / a.group));
-                    float v[8];
+                    float v[16];
 #pragma unroll
-                    for (int s = 0; s < 8; s++) v[s] = (float)((int)sym[j][s] - 7) * sc;
+                    for (int s = 0; s < 16; s++) v[s] = (float)((int)sym[j][s] - 7) * sc;
                     const size_t o = (size_t)r * K + c;
                     if (a.out_dtype == EOQ_B200_F32) {
                         float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(a.out_deq) + o);
-                        dst[0] = make_float4(v[0], v[1], v[2], v[3]);
-                        dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+#pragma unroll
+                        for (int q = 0; q < 4; q++) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                     } else if (a.out_dtype == EOQ_B200_F16) {
-                        __half2 h[4];
+                        __half2 h[8];
 #pragma unroll
-                        for (int s = 0; s < 4; s++) h[s] = __floats2half2_rn(v[2 * s], v[2 * s + 1]);
-                        *reinterpret_cast<uint4 *>(reinterpret_cast<__half *>(a.out_deq) + o) = *reinterpret_cast<uint4 *>(h);
+                        for (int s = 0; s < 8; s++) h[s] = __floats2half2_rn(v[2 * s], v[2 * s + 1]);
+                        uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<__half *>(a.out_deq) + o);
+                        dst[0] = reinterpret_cast<uint4 *>(h)[0];
+                        dst[1] = reinterpret_cast<uint4 *>(h)[1];
                     } else {
-                        __nv_bfloat162 h[4];
+                        __nv_bfloat162 h[8];
 #pragma unroll
-                        for (int s = 0; s < 4; s++) h[s] = __floats2bfloat162_rn(v[2 * s], v[2 * s + 1]);
-                        *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(a.out_deq) + o) = *reinterpret_cast<uint4 *>(h);
+                        for (int s = 0; s < 8; s++) h[s] = __floats2bfloat162_rn(v[2 * s], v[2 * s + 1]);
+                        uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(a.out_deq) + o);
+                        dst[0] = reinterpret_cast<uint4 *>(h)[0];
+                        dst[1] = reinterpret_cast<uint4 *>(h)[1];
                     }
                 }
             }
