@@ -34,14 +34,14 @@ EXPORTS = [
     "eoq_decoder_init", "eoq_decoder_decode", "eoq_decoder_free",
     "eoq_parallel_decode", "eoq_detect_num_threads",
     "eoq_cuda_decode_tensor", "eoq_cuda_decode_tensor_device",
-    "eoq_cuda_batch_create", "eoq_cuda_batch_prepare_tensor", "eoq_cuda_batch_launch",
+    "eoq_cuda_batch_init", "eoq_cuda_batch_create", "eoq_cuda_batch_prepare_tensor", "eoq_cuda_batch_launch",
     "eoq_cuda_batch_sync_and_free", "eoq_cuda_batch_destroy",
     "eoq_b200_decode_blocked", "eoq_b200_encode_blocked",
     "eoq_b200_tiles_build", "eoq_b200_tiles_view", "eoq_b200_tiles_free",
     "eoq_b200_weight_from_tiles", "eoq_b200_weight_from_symbols", "eoq_b200_weight_from_rans", "eoq_b200_weight_destroy",
     "eoq_b200_weight_info", "eoq_b200_gemv", "eoq_b200_gemm",
     "eoq_b200_gather_create", "eoq_b200_gather_connect", "eoq_b200_gather_destroy", "eoq_b200_gather_buffer",
-    "eoq_b200_gather_status", "eoq_b200_gemv_gather", "eoq_b200_gemv_static_scratch", "eoq_b200_gemv_host", "eoq_b200_gemv_host_async", "eoq_b200_weight_decode",
+    "eoq_b200_gather_status", "eoq_b200_gather_set_timeout_ms", "eoq_b200_gather_wait", "eoq_b200_gemv_gather", "eoq_b200_gemv_static_scratch", "eoq_b200_gemv_host", "eoq_b200_gemv_host_async", "eoq_b200_weight_decode",
     "eoq_b200_dequant_packed",
     "eoq_b200_weight_status", "eoq_b200_tune", "eoq_b200_launch_count",
 ]
@@ -100,7 +100,7 @@ class TilesView(C.Structure):
                 ("kind", C.c_uint32), ("bits", C.c_uint32), ("symbols_per_step", C.c_uint32),
                 ("precision_bits", C.c_uint32), ("num_tiles", C.c_uint32), ("num_col_segments", C.c_uint32),
                 ("table", C.POINTER(C.c_uint32)), ("tiles", C.POINTER(C.c_uint32)), ("stream", C.POINTER(C.c_uint8)),
-                ("stream_bytes", C.c_uint64), ("max_lane_drift", C.c_uint32)]
+                ("stream_bytes", C.c_uint64), ("max_lane_drift", C.c_uint32), ("head_bytes", C.c_uint32)]
 
 
 _LIB: Optional[C.CDLL] = None
@@ -129,6 +129,7 @@ def lib() -> C.CDLL:
         "eoq_detect_num_threads": (C.c_int, []),
         "eoq_cuda_decode_tensor": (C.c_int, [hp, vp, vp, vp]),
         "eoq_cuda_decode_tensor_device": (C.c_int, [vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, vp]),
+        "eoq_cuda_batch_init": (None, [vp, vp]),
         "eoq_cuda_batch_create": (vp, [vp]),
         "eoq_cuda_batch_prepare_tensor": (C.c_int, [vp, hp, vp, vp]),
         "eoq_cuda_batch_launch": (C.c_int, [vp]),
@@ -152,6 +153,8 @@ def lib() -> C.CDLL:
         "eoq_b200_gather_destroy": (None, [vp]),
         "eoq_b200_gather_buffer": (vp, [vp, C.c_uint32]),
         "eoq_b200_gather_status": (C.c_int, [vp, vp]),
+        "eoq_b200_gather_set_timeout_ms": (C.c_int, [vp, C.c_uint32]),
+        "eoq_b200_gather_wait": (C.c_int, [vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_int, C.c_uint32, vp]),
         "eoq_b200_gemv_gather": (C.c_int, [vp, vp, C.c_int, C.c_uint32, C.c_int, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, vp]),
         "eoq_b200_gemm": (C.c_int, [vp, vp, C.c_int, C.c_uint32, vp, C.c_int, vp, vp]),
         "eoq_b200_gemv_static_scratch": (C.c_int, [vp, vp, C.c_int, C.c_uint32, vp, C.c_int, vp, vp]),

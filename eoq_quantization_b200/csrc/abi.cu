@@ -380,15 +380,26 @@ extern "C" int eoq_cuda_decode_tensor_device(const uint8_t *d_compressed_stream,
     return 0;
 }
 
-struct eoq_cuda_batch_ctx {
-    std::vector<std::unique_ptr<StagedTensor>> tensors;
-    cudaStream_t stream = nullptr;
-};
+namespace {
+struct BatchImpl { std::vector<std::unique_ptr<StagedTensor>> tensors; };
+BatchImpl *batch_impl(eoq_cuda_batch_ctx_t *ctx, bool make)
+{
+    if (!ctx->impl && make) ctx->impl = new (std::nothrow) BatchImpl();
+    return static_cast<BatchImpl *>(ctx->impl);
+}
+}  // namespace
+
+extern "C" void eoq_cuda_batch_init(eoq_cuda_batch_ctx_t *ctx, void *stream)
+{
+    if (!ctx) return;
+    std::memset(ctx, 0, sizeof(*ctx));
+    ctx->stream = stream;
+}
 
 extern "C" eoq_cuda_batch_ctx_t *eoq_cuda_batch_create(void *stream)
 {
-    eoq_cuda_batch_ctx *c = new (std::nothrow) eoq_cuda_batch_ctx();
-    if (c) c->stream = reinterpret_cast<cudaStream_t>(stream);
+    eoq_cuda_batch_ctx_t *c = new (std::nothrow) eoq_cuda_batch_ctx_t();
+    if (c) eoq_cuda_batch_init(c, stream);
     return c;
 }
 
@@ -396,23 +407,29 @@ extern "C" int eoq_cuda_batch_prepare_tensor(eoq_cuda_batch_ctx_t *ctx, const eo
                                              const uint8_t *compressed_host, uint8_t *d_output)
 {
     if (!ctx || !header || !compressed_host || !d_output) return -1;
-    if (ctx->tensors.size() >= 1024) {                                   // eoq_cuda_decompress.cu:862
-        std::fprintf(stderr, "eoq_cuda_batch_prepare_tensor: batch full (1024 tensors)\n");
+    if (ctx->n_tensors >= EOQ_CUDA_MAX_BATCH_TENSORS) {                  // eoq_cuda_decompress.cu:906-910
+        std::fprintf(stderr, "eoq_cuda_batch_prepare_tensor: batch full (%d tensors)\n", EOQ_CUDA_MAX_BATCH_TENSORS);
         return -1;
     }
     if (header->uncompressed_size == 0) return 0;
+    BatchImpl *impl = batch_impl(ctx, true);
+    if (!impl) return -1;
     std::unique_ptr<StagedTensor> s(new StagedTensor());
-    if (stage_tensor(header, compressed_host, header->compressed_size, header->uncompressed_size, d_output, ctx->stream, *s) != EOQ_OK)
+    if (stage_tensor(header, compressed_host, header->compressed_size, header->uncompressed_size, d_output,
+                     reinterpret_cast<cudaStream_t>(ctx->stream), *s) != EOQ_OK)
         return -1;
-    ctx->tensors.push_back(std::move(s));
+    impl->tensors.push_back(std::move(s));
+    ctx->n_tensors = (uint32_t)impl->tensors.size();
     return 0;
 }
 
 extern "C" int eoq_cuda_batch_launch(eoq_cuda_batch_ctx_t *ctx)
 {
     if (!ctx) return -1;
-    for (auto &s : ctx->tensors)
-        if (launch_staged(*s, ctx->stream) != EOQ_OK) return -1;
+    BatchImpl *impl = batch_impl(ctx, false);
+    if (!impl) return 0;
+    for (auto &s : impl->tensors)
+        if (launch_staged(*s, reinterpret_cast<cudaStream_t>(ctx->stream)) != EOQ_OK) return -1;
     return 0;
 }
 
@@ -420,12 +437,20 @@ extern "C" int eoq_cuda_batch_sync_and_free(eoq_cuda_batch_ctx_t *ctx)
 {
     if (!ctx) return -1;
     int rc = 0;
-    if (!ctx->tensors.empty() && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = -1;
-    ctx->tensors.clear();          // frees the staging copies; outputs belong to the caller
+    BatchImpl *impl = batch_impl(ctx, false);
+    if (impl && !impl->tensors.empty() && cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(ctx->stream)) != cudaSuccess) rc = -1;
+    delete impl;                   // frees the staging copies; outputs belong to the caller
+    ctx->impl = nullptr;
+    ctx->n_tensors = 0;
     return rc;
 }
 
-extern "C" void eoq_cuda_batch_destroy(eoq_cuda_batch_ctx_t *ctx) { delete ctx; }
+extern "C" void eoq_cuda_batch_destroy(eoq_cuda_batch_ctx_t *ctx)
+{
+    if (!ctx) return;
+    delete batch_impl(ctx, false);
+    delete ctx;
+}
 
 // =========================================================================
 // Part 2: Python-facing codec entry points and the fused path
@@ -517,6 +542,7 @@ struct eoq_b200_weight {
     uint32_t N = 0, K = 0, Npad = 0, G = 0, bits = 0, p = 0, group = 0, kind = 0, alphabet = 0;
     uint32_t ntiles = 0, nseg = 0, nrb = 0;
     uint32_t stage_bytes = 0, max_ncols = 0;          // geometry of the pair kernel's staging buffers (see GemvArgs)
+    uint32_t head_bytes = 0;                          // TiledWeights::head_bytes
     DeviceBuf scales_t;                               // transposed copy of the scales for the pair kernel (INT4 x 3 only)
     DeviceBuf pair_partials;                          // partial rows of the pair kernel, every word 0xFFFFFFFF between launches
     size_t pair_partial_bytes = 0;
@@ -561,6 +587,7 @@ eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const 
     CU_TRY(cudaGetDevice(&w->device));
     w->N = tw.N; w->K = tw.K; w->Npad = tw.Npad; w->G = tw.G; w->bits = tw.bits; w->p = tw.p; w->group = tw.group;
     w->kind = tw.kind; w->alphabet = tw.alphabet; w->ntiles = (uint32_t)tw.tiles.size(); w->nseg = tw.nseg; w->nrb = tw.nrb;
+    w->head_bytes = tw.head_bytes;
     for (const TileDesc &d : tw.tiles) {
         w->stage_bytes = std::max(w->stage_bytes, ((d.len64 << 6) + 64u + 127u) & ~127u);
         w->max_ncols = std::max(w->max_ncols, d.ncols);
@@ -667,6 +694,7 @@ extern "C" eoq_error_t eoq_b200_tiles_view(const eoq_b200_tiles_t *t, eoq_b200_t
     v->stream = tw.stream.data();
     v->stream_bytes = tw.stream.size();
     v->max_lane_drift = tw.max_drift;
+    v->head_bytes = tw.head_bytes;
     return EOQ_OK;
 }
 
@@ -744,6 +772,30 @@ extern "C" eoq_error_t eoq_b200_weight_info(const eoq_b200_weight_t *w, eoq_b200
     return EOQ_OK;
 }
 
+// The arguments every fused GEMV launch shares (inputs, outputs and scratch are the caller's to add).
+static void weight_gemv_args(eoq_b200_weight_t *w, GemvArgs &a)
+{
+    a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
+    a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
+    a.status = w->status_word();
+    a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg;
+    a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols; a.head_bytes = w->head_bytes;
+    a.scales_t = w->scales_t.as<uint2>();
+}
+
+// A weight lives on the device it was uploaded to; launching its kernels with another device current would hand
+// that device pointers it cannot reach.  Refused on the host, before anything is launched.
+static eoq_error_t check_device(const eoq_b200_weight_t *w, const char *where)
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return EOQ_ERR_CUDA;
+    if (dev != w->device) {
+        std::fprintf(stderr, "%s: the weight lives on device %d but device %d is current\n", where, w->device, dev);
+        return EOQ_ERR_UNSUPPORTED;
+    }
+    return EOQ_OK;
+}
+
 // Scratch of the one-tile-per-warp GEMV kernel: one partial row per column segment.  Weights laid out for the pair
 // kernel get it on the first call that falls back to the other kernel (an allocation: not inside stream capture).
 static eoq_error_t ring_scratch(eoq_b200_weight_t *w)
@@ -760,12 +812,11 @@ extern "C" eoq_error_t eoq_b200_gemv(eoq_b200_weight_t *w, const void *x, int x_
     if (batch == 0) return EOQ_OK;
     if (batch > 8) return EOQ_ERR_UNSUPPORTED;
     if (x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2) return EOQ_ERR_UNSUPPORTED;
+    eoq_error_t drc = check_device(w, "eoq_b200_gemv");
+    if (drc != EOQ_OK) return drc;
     GemvArgs a = {};
-    a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
-    a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
-    a.x = x; a.y = y; a.bias = bias; a.counters = w->counters.as<uint32_t>(); a.status = w->status_word();
-    a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
-    a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols; a.scales_t = w->scales_t.as<uint2>();
+    weight_gemv_args(w, a);
+    a.x = x; a.y = y; a.bias = bias; a.counters = w->counters.as<uint32_t>(); a.batch = batch;
     a.pair_partials = w->pair_partials.as<float>();
     a.x_dtype = x_dtype; a.y_dtype = y_dtype;
     if (!gemv_takes_pairs(a, w->G, w->bits, w->kind)) {
@@ -798,6 +849,8 @@ extern "C" eoq_error_t eoq_b200_gemm(eoq_b200_weight_t *w, const void *x, int x_
     // the tensor-core path is built for the default INT4 layout: 3 weights per step, 96-row tiles
     if (w->kind != EOQ_B200_KIND_INT4_ABSMAX || w->G != 3 || w->bits != 4 || w->Npad != w->nrb * 96u || (w->K & 15u)) return EOQ_ERR_UNSUPPORTED;
     if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u) != 0) return EOQ_ERR_UNSUPPORTED;
+    eoq_error_t drc = check_device(w, "eoq_b200_gemm");
+    if (drc != EOQ_OK) return drc;
     static const size_t esz[3] = {2, 2, 4};
     {
         std::lock_guard<std::mutex> lock(w->mu);
@@ -815,7 +868,7 @@ extern "C" eoq_error_t eoq_b200_gemm(eoq_b200_weight_t *w, const void *x, int x_
                                static_cast<const uint8_t *>(x) + (size_t)m0 * w->K * esz[x_dtype], w->gemm_x.p,
                                w->gemm_partials.as<float>(), w->gemm_counters.as<uint32_t>(),
                                static_cast<uint8_t *>(y) + (size_t)m0 * w->N * esz[y_dtype], bias, w->status_word(),
-                               w->N, w->K, w->group, w->p, w->nseg, w->nrb, mb, x_dtype, y_dtype, stream);
+                               w->N, w->K, w->group, w->p, w->nseg, w->nrb, w->head_bytes, mb, x_dtype, y_dtype, stream);
         if (e != 0) { std::fprintf(stderr, "eoq_b200_gemm: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
     }
     return EOQ_OK;
@@ -836,6 +889,7 @@ struct eoq_b200_gather {
     uint8_t *base[kMaxPeers] = {};      // base[rank] is the local allocation
     bool opened[kMaxPeers] = {};
     DeviceBuf status;
+    long long limit_ticks = 1ll << 31;  // how long a kernel waits for the peers' words (about a second at 2 GHz)
     size_t ll_off(uint32_t slot) const { return (size_t)slots * slot_bytes + (size_t)slot * slot_elems * 8; }
     size_t epoch_off(uint32_t slot) const { return ll_off(slots) + (size_t)slot * 4; }
     size_t done_off(uint32_t slot) const { return epoch_off(slots) + (size_t)slot * 4; }
@@ -900,6 +954,7 @@ extern "C" eoq_error_t eoq_b200_gather_status(eoq_b200_gather_t *g, void *stream
     uint32_t st = 0;
     CU_TRY(cudaMemcpyAsync(&st, g->status.p, 4, cudaMemcpyDeviceToHost, reinterpret_cast<cudaStream_t>(stream)));
     CU_TRY(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)));
+    if (st) CU_TRY(cudaMemsetAsync(g->status.p, 0, 4, reinterpret_cast<cudaStream_t>(stream)));   // reported once; the object stays usable
     return st ? EOQ_ERR_CUDA : EOQ_OK;
 }
 
@@ -915,20 +970,25 @@ extern "C" eoq_error_t eoq_b200_gemv_gather(eoq_b200_weight_t *w, const void *x,
     if (row_offset != g->rank * w->N || (size_t)w->N * g->world != n_total) return EOQ_ERR_UNSUPPORTED;   // equal, rank-ordered shards
     for (uint32_t p = 0; p < g->world; p++)
         if (!g->base[p]) return EOQ_ERR_UNSUPPORTED;                    // eoq_b200_gather_connect has not run
+    eoq_error_t drc = check_device(w, "eoq_b200_gemv_gather");
+    if (drc != EOQ_OK) return drc;
+    if (g->device != w->device) return EOQ_ERR_UNSUPPORTED;
     GemvArgs a = {};
-    a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
-    a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
-    a.x = x; a.bias = bias; a.counters = w->counters.as<uint32_t>(); a.status = w->status_word();
+    weight_gemv_args(w, a);
+    a.x = x; a.bias = bias; a.counters = w->counters.as<uint32_t>(); a.batch = batch;
     a.pair_partials = w->pair_partials.as<float>();
-    a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
-    a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols; a.scales_t = w->scales_t.as<uint2>();
     a.x_dtype = x_dtype; a.y_dtype = y_dtype;
     a.world = g->world; a.rank = g->rank; a.row_offset = row_offset; a.n_total = n_total;
     for (uint32_t p = 0; p < g->world; p++) a.peer_ll[p] = reinterpret_cast<uint64_t *>(g->base[p] + g->ll_off(slot));
     a.y = g->base[g->rank] + (size_t)slot * g->slot_bytes;
-    uint32_t *epoch = reinterpret_cast<uint32_t *>(g->base[g->rank] + g->epoch_off(slot));
-    uint32_t *done = reinterpret_cast<uint32_t *>(g->base[g->rank] + g->done_off(slot));
-    a.gather_epoch = epoch;
+    a.gather_epoch = reinterpret_cast<uint32_t *>(g->base[g->rank] + g->epoch_off(slot));
+    a.gather_done = reinterpret_cast<uint32_t *>(g->base[g->rank] + g->done_off(slot));
+    a.gather_status = g->status.as<uint32_t>();
+    a.gather_g = w->G;
+    a.gather_limit = g->limit_ticks;
+    // words one sender occupies per activation row (see GemvArgs): must fit the slot's receive buffer
+    const size_t wpr = y_dtype == EOQ_B200_F32 ? w->N : w->Npad / w->G;
+    if ((size_t)batch * g->world * wpr > g->slot_elems) return EOQ_ERR_BUFFER_TOO_SMALL;
     if (!gemv_takes_pairs(a, w->G, w->bits, w->kind)) {
         const uint32_t bt = batch <= 1 ? 1 : batch <= 2 ? 2 : batch <= 4 ? 4 : 8;
         if (gemv_smem_bytes(w->K, w->p, bt, w->kind) > 227 * 1024) return EOQ_ERR_UNSUPPORTED;
@@ -936,10 +996,51 @@ extern "C" eoq_error_t eoq_b200_gemv_gather(eoq_b200_weight_t *w, const void *x,
         if (rc != EOQ_OK) return rc;
         a.partials = w->partials.as<float>();
     }
+    // one launch: the kernel sends this rank's rows, then waits for the others' and unpacks them
     int e = launch_gemv(a, w->G, w->bits, w->kind, stream);
-    if (e == 0)
-        e = launch_gather_wait(a.peer_ll[g->rank], a.y, epoch, done, g->rank, w->N, n_total, batch, y_dtype, g->status.as<uint32_t>(), stream);
     if (e != 0) { std::fprintf(stderr, "eoq_b200_gemv_gather: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
+    return EOQ_OK;
+}
+
+extern "C" eoq_error_t eoq_b200_gather_set_timeout_ms(eoq_b200_gather_t *g, uint32_t milliseconds)
+{
+    if (!g) return EOQ_ERR_NULL_PTR;
+    if (milliseconds == 0 || milliseconds > 60000) return EOQ_ERR_UNSUPPORTED;
+    int khz = 0, dev = g->device;
+    if (cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev) != cudaSuccess || khz <= 0) khz = 2000000;
+    g->limit_ticks = (long long)milliseconds * khz;
+    return EOQ_OK;
+}
+
+extern "C" eoq_error_t eoq_b200_gather_wait(eoq_b200_gather_t *g, uint32_t slot, uint32_t rows_per_rank, uint32_t batch,
+                                            int y_dtype, uint32_t rows_per_word, void *stream)
+{
+    if (!g) return EOQ_ERR_NULL_PTR;
+    if (slot >= g->slots || batch == 0 || batch > 8 || y_dtype < 0 || y_dtype > 2 || rows_per_rank == 0 ||
+        rows_per_word < 1 || rows_per_word > 3)
+        return EOQ_ERR_UNSUPPORTED;
+    static const size_t esz[3] = {2, 2, 4};
+    const size_t n_total = (size_t)rows_per_rank * g->world;
+    if ((size_t)batch * n_total * esz[y_dtype] > g->slot_bytes) return EOQ_ERR_BUFFER_TOO_SMALL;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return EOQ_ERR_CUDA;
+    if (dev != g->device) return EOQ_ERR_UNSUPPORTED;
+    GemvArgs a = {};
+    a.N = rows_per_rank;
+    a.Npad = (rows_per_rank + 32u * rows_per_word - 1u) / (32u * rows_per_word) * (32u * rows_per_word);
+    a.batch = batch; a.y_dtype = y_dtype;
+    a.world = g->world; a.rank = g->rank; a.row_offset = g->rank * rows_per_rank; a.n_total = (uint32_t)n_total;
+    a.peer_ll[g->rank] = reinterpret_cast<uint64_t *>(g->base[g->rank] + g->ll_off(slot));
+    a.y = g->base[g->rank] + (size_t)slot * g->slot_bytes;
+    a.gather_epoch = reinterpret_cast<uint32_t *>(g->base[g->rank] + g->epoch_off(slot));
+    a.gather_done = reinterpret_cast<uint32_t *>(g->base[g->rank] + g->done_off(slot));
+    a.gather_status = g->status.as<uint32_t>();
+    a.gather_g = rows_per_word;
+    a.gather_limit = g->limit_ticks;
+    const size_t wpr = y_dtype == EOQ_B200_F32 ? a.N : a.Npad / rows_per_word;
+    if ((size_t)batch * g->world * wpr > g->slot_elems) return EOQ_ERR_BUFFER_TOO_SMALL;
+    int e = launch_gather_wait(a, stream);
+    if (e != 0) { std::fprintf(stderr, "eoq_b200_gather_wait: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
     return EOQ_OK;
 }
 
@@ -950,6 +1051,8 @@ extern "C" eoq_error_t eoq_b200_gemv_host_async(eoq_b200_weight_t *w, const void
     if (batch == 0) return EOQ_OK;
     if (batch > 8 || x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2) return EOQ_ERR_UNSUPPORTED;
     static const size_t esz[3] = {2, 2, 4};
+    eoq_error_t drc = check_device(w, "eoq_b200_gemv_host");
+    if (drc != EOQ_OK) return drc;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     std::lock_guard<std::mutex> lock(w->mu);
     CU_TRY(cudaMemcpyAsync(w->xbuf.p, x, (size_t)batch * w->K * esz[x_dtype], cudaMemcpyHostToDevice, st));
@@ -982,7 +1085,10 @@ extern "C" eoq_error_t eoq_b200_weight_decode(eoq_b200_weight_t *w, uint8_t *d_s
     if (packed && w->bits != 4) return EOQ_ERR_UNSUPPORTED;
     if (d_dequant && w->kind != EOQ_B200_KIND_INT4_ABSMAX) return EOQ_ERR_UNSUPPORTED;
     if (out_dtype < 0 || out_dtype > 2) return EOQ_ERR_UNSUPPORTED;
+    eoq_error_t drc = check_device(w, "eoq_b200_weight_decode");
+    if (drc != EOQ_OK) return drc;
     DecodeArgs a;
+    a.head_bytes = w->head_bytes;
     a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
     a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
     a.status = w->status_word();
@@ -1089,8 +1195,18 @@ extern "C" eoq_error_t eoq_b200_gemv_static_scratch(eoq_b200_weight_t *w, const 
     if (batch == 0) return EOQ_OK;
     if (batch > 8) return EOQ_ERR_UNSUPPORTED;
     if (x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2) return EOQ_ERR_UNSUPPORTED;
+    eoq_error_t drc = check_device(w, "eoq_b200_gemv_static_scratch");
+    if (drc != EOQ_OK) return drc;
+    GemvArgs a = {};
+    weight_gemv_args(w, a);
+    a.x = x; a.y = y; a.bias = bias; a.batch = batch;
+    a.x_dtype = x_dtype; a.y_dtype = y_dtype;
+    // The scratch request is sized for the kernel that will run.  Two tiles per warp (the default INT4 layout): a few
+    // partial rows per pair of row blocks, at most four activation rows per launch.  One tile per warp: one partial row
+    // per column segment.  Layout of the array: [arrival counters, one u32 per row block, padded to 256 B][partial sums].
+    const bool pairs = gemv_takes_pairs(a, w->G, w->bits, w->kind);
     const uint32_t bt = batch <= 1 ? 1 : batch <= 2 ? 2 : batch <= 4 ? 4 : 8;
-    if (gemv_smem_bytes(w->K, w->p, bt, w->kind) > 227 * 1024) {
+    if (!pairs && gemv_smem_bytes(w->K, w->p, bt, w->kind) > 227 * 1024) {
         // same rule as eoq_b200_gemv: rows that do not fit shared memory together run in two halves
         if (bt == 1) return EOQ_ERR_UNSUPPORTED;
         static const size_t esz[3] = {2, 2, 4};
@@ -1101,9 +1217,9 @@ extern "C" eoq_error_t eoq_b200_gemv_static_scratch(eoq_b200_weight_t *w, const 
                                             batch - first, static_cast<uint8_t *>(y) + (size_t)first * w->N * esz[y_dtype],
                                             y_dtype, bias, stream);
     }
-    // layout of the array: [arrival counters, one u32 per row block, padded to 256 B][partial sums nseg x Npad x bt floats]
     const size_t counter_bytes = (((size_t)w->nrb * 4) + 255) & ~(size_t)255;
-    const size_t partial_bytes = w->nseg > 1 ? (size_t)w->nseg * w->Npad * bt * sizeof(float) : 0;
+    const size_t partial_bytes = pairs ? (size_t)pair_partial_slots(w->nrb, w->nseg) * w->Npad * std::min(bt, 4u) * sizeof(float)
+                               : w->nseg > 1 ? (size_t)w->nseg * w->Npad * bt * sizeof(float) : 0;
     if (counter_bytes + partial_bytes > kGemvStaticScratchBytes) {
         std::fprintf(stderr,
                      "eoq_b200_gemv_static_scratch: this weight needs %zu bytes of scratch for %u rows of x, the built-in array holds %zu; "
@@ -1117,16 +1233,10 @@ extern "C" eoq_error_t eoq_b200_gemv_static_scratch(eoq_b200_weight_t *w, const 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     // the array keeps whatever the last call left; the counters are the only part that must start at zero
     CU_TRY(cudaMemsetAsync(scratch, 0, counter_bytes, st));
-    GemvArgs a = {};
-    a.table = w->table.as<uint32_t>(); a.tiles = w->tiles.as<TileDesc>(); a.stream = w->stream.as<uint8_t>();
-    a.scales = w->scales.as<uint16_t>(); a.centroids = w->centroids.as<float>();
-    a.x = x; a.y = y; a.bias = bias;
+    // pair_partials stays null: the array cannot keep the "empty slot" pattern between calls, so the runs of a pair of row
+    // blocks meet through store, fence and ticket in `partials`
     a.partials = reinterpret_cast<float *>(scratch + counter_bytes);
     a.counters = reinterpret_cast<uint32_t *>(scratch);
-    a.status = w->status_word();
-    a.N = w->N; a.K = w->K; a.Npad = w->Npad; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles; a.nseg = w->nseg; a.batch = batch;
-    a.nrb = w->nrb; a.stage_bytes = w->stage_bytes; a.max_ncols = w->max_ncols; a.scales_t = w->scales_t.as<uint2>();
-    a.x_dtype = x_dtype; a.y_dtype = y_dtype;
     int e = launch_gemv(a, w->G, w->bits, w->kind, stream);
     if (e != 0) { std::fprintf(stderr, "eoq_b200_gemv_static_scratch: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
     return EOQ_OK;

@@ -23,6 +23,10 @@ namespace eoq {
 // Every lane has its own rANS stream: 32-bit state in [2^16, 2^32), 16-bit
 // renormalisation words, at most one word per step (precision <= 16).
 //
+// Stream: [heads: tile t's first head_bytes at t * head_bytes][tails, packed][padding]; head_bytes is 0, 1024
+// or 2048 and never more than the shortest tile, so the start of every tile is addressable from its index
+// alone and only the tail needs the descriptor.
+//
 // Tile bytes:  [32 x u32 initial states][rows of 32 x u16]
 // where row k holds, for lane l, that lane's k-th renormalisation word; lanes
 // that need fewer words than the longest lane are padded with zeros, and the
@@ -38,8 +42,8 @@ struct TileDesc {
     uint32_t col0;    // first column
     uint32_t ncols;   // columns (= rANS steps per lane), multiple of 16
     uint32_t seg;     // column-segment index (same for all row blocks); top bit: kTileDirectFlag
-    uint32_t off64;   // byte offset of the tile in the stream, divided by 64
-    uint32_t len64;   // bytes of the tile, divided by 64
+    uint32_t off64;   // byte offset in the stream of the tile's tail (its bytes past head_bytes), divided by 64
+    uint32_t len64;   // bytes of the whole tile (head + tail), divided by 64
 };
 
 constexpr uint32_t kMaxFreq = 511;
@@ -52,10 +56,11 @@ struct TiledWeights {
     uint32_t alphabet = 0;       // (1 << bits*G) slots in the joint symbol space
     uint32_t nrb = 0, nseg = 0;
     uint32_t max_drift = 0;      // largest distance (rows) between lanes' read positions in any tile
+    uint32_t head_bytes = 0;     // bytes of every tile kept in the fixed-stride head region of the stream
     std::vector<uint32_t> table;     // 1 << p entries
     std::vector<TileDesc> tiles;     // nrb * nseg
     std::vector<uint32_t> seg_start; // nseg + 1 column boundaries
-    std::vector<uint8_t>  stream;    // all tiles + 4096 bytes of tail padding (read-ahead never leaves it)
+    std::vector<uint8_t>  stream;    // heads, tails, then 4096 bytes of padding (read-ahead never leaves it)
 };
 
 // Host codec (rans_host.cpp) -------------------------------------------------
@@ -100,15 +105,25 @@ struct GemvArgs {
     // Pair kernel: row blocks, bytes of one staged-tile buffer (longest tile + one row, rounded to 128) and the
     // widest column segment; zero if the caller has not worked them out (the ring kernel is used then).
     uint32_t nrb, stage_bytes, max_ncols;
+    uint32_t head_bytes;        // bytes of every tile in the fixed-stride head region of the stream (TiledWeights::head_bytes)
     float *pair_partials;       // pair kernel: partial rows [slots][Npad][BT], every word 0xFFFFFFFF between launches; null: meet through `partials` with a fence
     const uint2 *scales_t;      // [K/group][Npad/3] words {s0 | s1 << 16, s2}: the fp16 scales of rows 3i..3i+2, zero past N; or null
-    // Fused all-gather of row-sharded outputs (world > 1): this rank's rows go into its own full-size output and,
-    // as 8-byte {value bits, epoch} words, into every peer's receive buffer; gather_wait_kernel on each rank
-    // unpacks what the others sent.  8-byte stores arrive whole, so no fence or separate flag is needed.
+    // Fused all-gather of row-sharded outputs (world > 1): a lane's finished rows go into this rank's own full-size
+    // output and, as 8-byte words, into every peer's receive buffer (plain stores over NVLink; an aligned 8-byte store
+    // arrives whole, so the epoch inside the word is the flag).  16-bit outputs: one word carries the `gather_g` rows of a
+    // lane, {v0 | v1 << 16, v2 | (epoch & 0xFFFF) << 16}; fp32 outputs: one word per value, {bits, epoch}.  Word index in a
+    // receive buffer: (b * world + sender) * words_per_rank + (local row / gather_g, or local row for fp32), with
+    // words_per_rank = Npad / gather_g (N for fp32).  The same kernel then waits, bounded by gather_limit clock ticks,
+    // for the words of the other ranks and unpacks them into its output, so the full vector is complete when the
+    // kernel is; the CTA that finishes last advances the slot's epoch.
     uint32_t world, rank;        // world <= 1: plain output into y
     uint32_t row_offset, n_total;// this shard's first row and the full row count: y index = b * n_total + row_offset + r
-    uint64_t *peer_ll[kMaxPeers];      // the slot's receive buffer on each rank, 8-byte words ([rank] unused)
-    const uint32_t *gather_epoch;      // local: gathers this slot has completed; this launch sends epoch + 1
+    uint64_t *peer_ll[kMaxPeers];      // the slot's receive buffer on each rank, 8-byte words ([rank]: this rank's own)
+    uint32_t *gather_epoch;            // local: gathers this slot has completed; this launch sends epoch + 1
+    uint32_t *gather_done;             // local: CTAs of this launch that have finished unpacking
+    uint32_t *gather_status;           // local: set nonzero when the wait for a peer gave up
+    uint32_t gather_g;                 // rows per lane of this weight's layout
+    long long gather_limit;            // clock ticks the wait for the peers may take
 };
 
 struct DecodeArgs {
@@ -121,6 +136,7 @@ struct DecodeArgs {
     uint8_t        *out_sym;    // packed nibbles [N, K/2] or bytes [N, K], or null
     void           *out_deq;    // [N, K] or null
     uint32_t N, K, group, p, ntiles;
+    uint32_t head_bytes;
     int packed, out_dtype;
 };
 
@@ -141,7 +157,8 @@ int launch_dequant_packed(const uint8_t *packed, const uint16_t *scales, uint32_
                           uint32_t group, uint32_t row_lo, uint32_t row_hi, void *out, int out_dtype, void *stream);
 int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *stream, const uint2 *scales_t, const void *x,
                    void *xhalf, float *partials, uint32_t *counters, void *y, const float *bias, uint32_t *status, uint32_t N,
-                   uint32_t K, uint32_t group, uint32_t p, uint32_t nseg, uint32_t nrb, uint32_t M, int x_dtype, int y_dtype, void *stream_);
+                   uint32_t K, uint32_t group, uint32_t p, uint32_t nseg, uint32_t nrb, uint32_t head_bytes, uint32_t M, int x_dtype, int y_dtype,
+                   void *stream_);
 uint32_t gemm_grid(uint32_t nrb, uint32_t nseg);
 size_t gemm_partial_bytes(uint32_t grid);
 size_t gemv_smem_bytes(uint32_t K, uint32_t p, uint32_t bt, uint32_t kind);
@@ -152,7 +169,6 @@ void set_pdl(int v);
 void set_gemv_pairs(int v);
 uint32_t pair_partial_slots(uint32_t nrb, uint32_t nseg);
 bool gemv_takes_pairs(const GemvArgs &a, uint32_t G, uint32_t bits, uint32_t kind);
-int launch_gather_wait(const void *ll, void *y, uint32_t *epoch, uint32_t *done, uint32_t rank, uint32_t rows_per_rank,
-                       uint32_t n_total, uint32_t batch, int y_dtype, uint32_t *status, void *stream);
+int launch_gather_wait(const GemvArgs &a, void *stream);
 
 }  // namespace eoq

@@ -245,9 +245,26 @@ __device__ __forceinline__ uint32_t lds_u16(uint32_t addr)
     return v;
 }
 
+// Where the bytes of one tile are: its first `hbytes` in the fixed-stride head region of the stream, the rest in
+// its tail; `tail` is biased by -hbytes so that byte b of the tile is head[b] below hbytes and tail[b] from there on.
+struct TileSrc {
+    const uint8_t *head, *tail;
+    uint32_t hbytes;
+    __device__ __forceinline__ const uint8_t *at(uint32_t b) const { return b < hbytes ? head + b : tail + b; }
+};
+__device__ __forceinline__ TileSrc tile_src(const uint8_t *stream, uint32_t head_bytes, uint32_t t, const TileDesc &d)
+{
+    TileSrc s;
+    s.head = stream + (size_t)t * head_bytes;
+    s.tail = stream + ((size_t)d.off64 << 6) - head_bytes;
+    s.hbytes = head_bytes;
+    return s;
+}
+
 struct WordState {            // per lane
     uint32_t w;               // the lane's next unread word
     const uint16_t *ptr;      // direct mode: where w came from
+    const uint16_t *head_end, *tail_row;   // direct mode: first address past the lane's head rows, and where its rows go on
     uint32_t koff, ring_lane; // ring mode: see above; ring_lane = shared address of the ring | lane*2
     uint32_t c64, c1;         // the constants 64 and 1 in registers the compiler cannot see through
 };
@@ -258,7 +275,7 @@ struct RingCtlT {             // per warp (all fields warp-uniform)
     uint32_t ring_base, bar0; // shared addresses
     uint32_t issued, ready;   // chunks issued / known complete since the kernel started
     uint32_t tile_first, tile_last, tile_bytes;  // chunk range [first, last) and byte length of the open tile
-    const uint8_t *src;       // global address of the open tile
+    TileSrc src;              // global addresses of the open tile
     uint32_t *status;
 };
 
@@ -294,7 +311,7 @@ __device__ __forceinline__ void ring_issue(RingCtlT<R> &r, uint32_t limit, uint3
             const uint32_t c = r.issued - r.tile_first, slot = r.issued % R::kChunks;
             const uint32_t bytes = min(R::kChunkBytes, r.tile_bytes - c * R::kChunkBytes);
             mbar_expect_tx(r.bar0 + slot * 8, bytes);
-            bulk_copy_g2s(r.ring_base + slot * R::kChunkBytes, r.src + (size_t)c * R::kChunkBytes, bytes, r.bar0 + slot * 8);
+            bulk_copy_g2s(r.ring_base + slot * R::kChunkBytes, r.src.at(c * R::kChunkBytes), bytes, r.bar0 + slot * 8);
         }
         r.issued++;
     }
@@ -333,8 +350,9 @@ __device__ __forceinline__ void ring_sync_step(RingCtlT<R> &r, const WordState &
 // can run well before the tile is decoded (before the kernel's prologue, or while the previous tile's
 // results are being written).  The whole tile goes through the ring, its 128-byte state header included.
 template <typename R>
-__device__ __forceinline__ void tile_open(RingCtlT<R> &r, const TileDesc &d, const uint8_t *base, uint32_t lane)
+__device__ __forceinline__ void tile_open(RingCtlT<R> &r, const TileDesc &d, const TileSrc &base, uint32_t lane)
 {
+    static_assert(1024u % R::kChunkBytes == 0, "a ring chunk may not straddle the end of a tile's head");
     const uint32_t bytes = d.len64 << 6;
     uint32_t ahead = 0;        // bytes already on their way through the ring
     if ((d.seg & kTileDirectFlag) == 0) {
@@ -347,14 +365,20 @@ __device__ __forceinline__ void tile_open(RingCtlT<R> &r, const TileDesc &d, con
     }
     // The rest of the tile is only asked into L2, and after the ring copies: when every warp of the grid opens its
     // tile at the same moment, the copies that are needed first must not queue behind megabytes of prefetch.
-    if (lane == 0 && bytes > ahead)
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + ahead), "r"(bytes - ahead) : "memory");
+    if (lane == 0 && bytes > ahead) {
+        if (ahead < base.hbytes) {
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base.head + ahead), "r"(base.hbytes - ahead) : "memory");
+            ahead = base.hbytes;
+        }
+        if (bytes > ahead)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base.tail + ahead), "r"(bytes - ahead) : "memory");
+    }
 }
 
 // Begin decoding an opened tile: wait for its first chunk, read the lane's state and first word.
 // Returns true if the tile runs in ring mode.
 template <typename R>
-__device__ __forceinline__ bool tile_begin(RingCtlT<R> &r, WordState &s, const TileDesc &d, const uint8_t *base, uint32_t lane, uint32_t &x)
+__device__ __forceinline__ bool tile_begin(RingCtlT<R> &r, WordState &s, const TileDesc &d, const TileSrc &base, uint32_t lane, uint32_t &x)
 {
     const bool ring = (d.seg & kTileDirectFlag) == 0;
     if (ring) {
@@ -366,8 +390,13 @@ __device__ __forceinline__ bool tile_begin(RingCtlT<R> &r, WordState &s, const T
         x = lds_u32(r.ring_base + (start & (R::kBytes - 1)) + lane * 4);
         s.w = lds_u16((s.koff & (R::kBytes - 1)) | s.ring_lane);
     } else {
-        x = __ldg(reinterpret_cast<const uint32_t *>(base) + lane);
-        s.ptr = reinterpret_cast<const uint16_t *>(base + 128) + lane;
+        // states and word rows straight from global memory; a lane's rows continue in the tail after the head
+        x = __ldg(reinterpret_cast<const uint32_t *>(base.at(0)) + lane);
+        s.head_end = reinterpret_cast<const uint16_t *>(base.head + base.hbytes) + lane;
+        s.tail_row = reinterpret_cast<const uint16_t *>(base.tail + base.hbytes) + lane;
+        s.ptr = base.hbytes > 128u ? reinterpret_cast<const uint16_t *>(base.head + 128) + lane
+                                   : reinterpret_cast<const uint16_t *>(base.tail + 128) + lane;
+        if (base.hbytes <= 128u) s.head_end = nullptr;
         s.w = __ldg(s.ptr);
     }
     return ring;
@@ -401,6 +430,7 @@ __device__ __forceinline__ void rans_renorm(uint32_t &x, WordState &s)
     } else if (x < 65536u) {
         x = (x << 16) | s.w;
         s.ptr += 32;
+        if (s.ptr == s.head_end) s.ptr = s.tail_row;
         s.w = __ldg(s.ptr);
     }
 }
@@ -418,6 +448,10 @@ __device__ __forceinline__ void rans_renorm(uint32_t &x, WordState &s)
 // arrive (a ticket on `counters`) adds them up in segment order, so results do
 // not depend on scheduling.
 // ---------------------------------------------------------------------------
+template <int G, int BT>
+__device__ __forceinline__ void write_rows(const GemvArgs &a, uint32_t row, const float (&y)[G][BT]);
+__device__ __forceinline__ void gather_finish(const GemvArgs &a);
+
 // The column loop of one tile: decode, unpack, multiply-accumulate, fold per scale group.
 template <int G, int BITS, int BT, int KIND, bool RING, int UNROLL, typename R>
 __device__ __forceinline__ void gemv_tile_columns(const GemvArgs &a, const TileDesc &d, const uint32_t *tab, const float *xs,
@@ -588,7 +622,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
         for (int u = 0; u < kXV; u++)
             if (tid + u * kThreads < nvec) xq[u] = __ldg(reinterpret_cast<const uint4 *>(a.x) + tid + u * kThreads);
     }
-    if (have) tile_open(ring, d, a.stream + ((size_t)d.off64 << 6), lane);
+    if (have) tile_open(ring, d, tile_src(a.stream, a.head_bytes, t, d), lane);
     EOQ_STAMP(6);
 
     if (x_vec) {
@@ -685,7 +719,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
         const TileDesc cur = d;
         uint32_t x;
         WordState ws;
-        const bool ring_mode = tile_begin(ring, ws, cur, a.stream + ((size_t)cur.off64 << 6), lane, x);
+        const bool ring_mode = tile_begin(ring, ws, cur, tile_src(a.stream, a.head_bytes, t, cur), lane, x);
         EOQ_STAMP(2);
         const uint32_t row = cur.row0 + lane * G;
         const uint32_t rb = cur.row0 / (32u * G);
@@ -707,7 +741,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
         have = t < a.ntiles;
         if (have) {
             d = a.tiles[t];
-            tile_open(ring, d, a.stream + ((size_t)d.off64 << 6), lane);
+            tile_open(ring, d, tile_src(a.stream, a.head_bytes, t, d), lane);
         }
 
         bool write_out = true;
@@ -755,45 +789,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
                 if (lane == 0) a.counters[rb] = 0u;
             }
         }
-        if (write_out && a.world > 1) {
-            // Row-sharded output with the all-gather fused in: the values go into this rank's copy of the full vector
-            // and, as {value bits, epoch} words, straight into every peer's receive buffer (plain 8-byte stores over
-            // NVLink, which arrive whole: the epoch in the word is the flag).
-            const uint32_t epoch = __ldcg(a.gather_epoch) + 1u;
-#pragma unroll
-            for (int j = 0; j < G; j++) {
-                const uint32_t r = row + j;
-                if (r < a.N) {
-                    const float bv = a.bias ? __ldg(a.bias + r) : 0.0f;
-#pragma unroll
-                    for (int b = 0; b < BT; b++)
-                        if ((uint32_t)b < a.batch) {
-                            const size_t idx = (size_t)b * a.n_total + a.row_offset + r;
-                            const float v = y[j][b] + bv;
-                            store_y(a.y, idx, v, a.y_dtype);
-                            const uint32_t bits = a.y_dtype == EOQ_B200_F16 ? (uint32_t)__half_as_ushort(__float2half_rn(v))
-                                                : a.y_dtype == EOQ_B200_BF16 ? (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v))
-                                                : __float_as_uint(v);
-                            for (uint32_t pr = 0; pr < a.world; pr++)
-                                if (pr != a.rank)
-                                    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(a.peer_ll[pr] + idx), "r"(bits), "r"(epoch) : "memory");
-                        }
-                }
-            }
-        } else if (write_out) {
-#pragma unroll
-            for (int j = 0; j < G; j++) {
-                const uint32_t r = row + j;
-                if (r < a.N) {
-                    const float bv = a.bias ? __ldg(a.bias + r) : 0.0f;
-#pragma unroll
-                    for (int b = 0; b < BT; b++)
-                        if ((uint32_t)b < a.batch) store_y(a.y, (size_t)b * a.N + r, y[j][b] + bv, a.y_dtype);
-                }
-            }
-        }
+        if (write_out) write_rows<G, BT>(a, row, y);     // bias, output type and, in row-sharded runs, the stores into the peers' buffers
         EOQ_STAMP(5);
     }
+    gather_finish(a);          // row-sharded runs: wait for the other ranks' rows and unpack them
 }
 
 // Programmatic dependent launch: the grid may be scheduled as soon as the previous kernel of the stream lets go of
@@ -978,27 +977,41 @@ template <int G, int BT>
 __device__ __forceinline__ void write_rows(const GemvArgs &a, uint32_t row, const float (&y)[G][BT])
 {
     if (a.world > 1) {
+        if (row >= a.N) return;
         const uint32_t epoch = __ldcg(a.gather_epoch) + 1u;
+        const bool f32 = a.y_dtype == EOQ_B200_F32;
+        const uint32_t wpr = f32 ? a.N : a.Npad / G;
+        float bv[G];
 #pragma unroll
-        for (int j = 0; j < G; j++) {
-            const uint32_t r = row + j;
-            if (r < a.N) {
-                const float bv = a.bias ? __ldg(a.bias + r) : 0.0f;
+        for (int j = 0; j < G; j++) bv[j] = (a.bias && row + j < a.N) ? __ldg(a.bias + row + j) : 0.0f;
 #pragma unroll
-                for (int b = 0; b < BT; b++)
-                    if ((uint32_t)b < a.batch) {
-                        const size_t idx = (size_t)b * a.n_total + a.row_offset + r;
-                        const float v = y[j][b] + bv;
-                        store_y(a.y, idx, v, a.y_dtype);
-                        const uint32_t bits = a.y_dtype == EOQ_B200_F16 ? (uint32_t)__half_as_ushort(__float2half_rn(v))
-                                            : a.y_dtype == EOQ_B200_BF16 ? (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v))
-                                            : __float_as_uint(v);
-                        for (uint32_t pr = 0; pr < a.world; pr++)
-                            if (pr != a.rank)
-                                asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(a.peer_ll[pr] + idx), "r"(bits), "r"(epoch) : "memory");
+        for (int b = 0; b < BT; b++)
+            if ((uint32_t)b < a.batch) {
+                uint32_t bits[3] = {0u, 0u, 0u};
+#pragma unroll
+                for (int j = 0; j < G; j++)
+                    if (row + j < a.N) {
+                        const float v = y[j][b] + bv[j];
+                        store_y(a.y, (size_t)b * a.n_total + a.row_offset + row + j, v, a.y_dtype);
+                        bits[j] = a.y_dtype == EOQ_B200_F16 ? (uint32_t)__half_as_ushort(__float2half_rn(v))
+                                : a.y_dtype == EOQ_B200_BF16 ? (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v))
+                                : __float_as_uint(v);
                     }
+                const size_t base = (size_t)(b * a.world + a.rank) * wpr;
+                if (f32) {
+#pragma unroll
+                    for (int j = 0; j < G; j++)
+                        if (row + j < a.N)
+                            for (uint32_t pr = 0; pr < a.world; pr++)
+                                if (pr != a.rank)
+                                    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(a.peer_ll[pr] + base + row + j), "r"(bits[j]), "r"(epoch) : "memory");
+                } else {
+                    const uint32_t lo = bits[0] | (bits[1] << 16), hi = bits[2] | (epoch << 16);
+                    for (uint32_t pr = 0; pr < a.world; pr++)
+                        if (pr != a.rank)
+                            asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(a.peer_ll[pr] + base + row / G), "r"(lo), "r"(hi) : "memory");
+                }
             }
-        }
     } else {
 #pragma unroll
         for (int j = 0; j < G; j++) {
@@ -1145,41 +1158,66 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
     uint32_t c64, c1;
     asm volatile("mov.b32 %0, 64;\n\tmov.b32 %1, 1;" : "=r"(c64), "=r"(c1));
 
-    TileDesc d[2];
-    bool has_b = false;
-    // Read a pair's descriptors and start the copy of the first kilobyte of both tiles.  Touches only this weight's
-    // read-only data.  Lane k * 8 + j owns chunk j of tile k, so copies are issued side by side.
-    auto chunk_copy = [&](bool first_only) {
+    // Geometry of the warp's pair.  Rows and columns follow from the pair's index alone (column boundaries are those of
+    // the host encoder: segment s starts at column floor(s * K/16 / nseg) * 16), and so do the addresses of the tiles'
+    // heads; only the tails need the descriptor ({off64, len64}, requested here and first used after the x loads).
+    struct PairGeo {
+        uint32_t t[2];        // tile indices (equal when the pair has no second row block)
+        uint32_t row0[2];     // first rows
+        uint32_t col0, ncols;
+        bool has_b;
+    } geo = {};
+    uint2 dl = make_uint2(0u, 0u);    // lanes 0..15: {off64, len64} of tile lane / 8
+    const uint32_t head_chunks = a.head_bytes / kChunk;
+    // Read-only data of this weight only.  Lane k * 8 + j owns chunk j of tile k, so copies are issued side by side.
+    auto open_pair = [&](uint32_t qq) {
+        const uint32_t rbp = qq / a.nseg, seg = qq - rbp * a.nseg, units = a.K / kColGranule;
+        geo.has_b = 2u * rbp + 1u < a.nrb;
+        geo.t[0] = (2u * rbp) * a.nseg + seg;
+        geo.t[1] = geo.has_b ? geo.t[0] + a.nseg : geo.t[0];
+        geo.row0[0] = 2u * rbp * (32u * G);
+        geo.row0[1] = geo.has_b ? geo.row0[0] + 32u * G : geo.row0[0];
+        // (64-bit division is a long software routine: it is kept for matrices so large that the products overflow)
+        if (((uint64_t)units * (a.nseg + 1u)) >> 32 == 0) {
+            geo.col0 = (seg * units / a.nseg) * kColGranule;
+            geo.ncols = ((seg + 1u) * units / a.nseg) * kColGranule - geo.col0;
+        } else {
+            geo.col0 = (uint32_t)((uint64_t)seg * units / a.nseg) * kColGranule;
+            geo.ncols = (uint32_t)(((uint64_t)seg + 1u) * units / a.nseg) * kColGranule - geo.col0;
+        }
+        if (lane < 2 * kMaxChunks) {
+            const uint32_t k = lane >> 3, j = lane & 7u, tk = k ? geo.t[1] : geo.t[0];
+            if (j < head_chunks) {
+                const uint32_t bar = bars + lane * 8;
+                mbar_expect_tx(bar, kChunk);
+                bulk_copy_g2s((k ? stage[1] : stage[0]) + j * kChunk, a.stream + (size_t)tk * a.head_bytes + j * kChunk, kChunk, bar);
+            }
+            dl = ldg_u32x2_pinned(reinterpret_cast<const uint2 *>(&a.tiles[tk].off64));
+        }
+    };
+    // The chunks behind the heads: their place in the stream comes from the descriptor.
+    auto tail_copy = [&]() {
         if (lane < 2 * kMaxChunks) {
             const uint32_t k = lane >> 3, j = lane & 7u;
-            if ((j == 0) == first_only) {
-                const uint32_t len64 = k ? d[1].len64 : d[0].len64, off64 = k ? d[1].off64 : d[0].off64, dst = k ? stage[1] : stage[0];
-                uint32_t bytes = len64 << 6;
+            if (j >= head_chunks) {
+                uint32_t bytes = dl.y << 6;
                 if (bytes + 64u > a.stage_bytes) { *a.status = 2u; bytes = a.stage_bytes - 64u; }   // cannot happen with a host-computed stage size
                 const uint32_t bar = bars + lane * 8, off = j * kChunk;
                 if (off < bytes) {
                     const uint32_t n = min(kChunk, bytes - off);
                     mbar_expect_tx(bar, n);
-                    bulk_copy_g2s(dst + off, a.stream + ((size_t)off64 << 6) + off, n, bar);
+                    bulk_copy_g2s((k ? stage[1] : stage[0]) + off, a.stream + ((size_t)dl.x << 6) + (off - a.head_bytes), n, bar);
                 } else {
                     mbar_arrive(bar);                   // nothing to copy: complete the phase by hand
                 }
             }
         }
     };
-    auto open_pair = [&](uint32_t qq) {
-        const uint32_t rbp = qq / a.nseg, seg = qq - rbp * a.nseg;
-        const uint32_t ta = (2u * rbp) * a.nseg + seg;
-        has_b = 2u * rbp + 1u < a.nrb;
-        d[0] = a.tiles[ta];
-        d[1] = a.tiles[has_b ? ta + a.nseg : ta];
-        chunk_copy(true);
-    };
     // The pair's columns of x: loaded into registers (four columns per lane and batch row, up to 256 columns), then
     // converted to fp32 [ncols][BT] in shared memory together with the 16-column sums the INT4 unpack needs.
     const bool x_vec = a.x_dtype != EOQ_B200_F32 && (reinterpret_cast<uintptr_t>(a.x) & 7u) == 0;
     auto load_x_segment = [&](bool then_rest) {
-        const uint32_t col0 = d[0].col0, ncols = d[0].ncols;
+        const uint32_t col0 = geo.col0, ncols = geo.ncols;
         for (uint32_t base = 0; base < ncols; base += 128u) {
             const uint32_t c = base + lane * 4u;
             const bool on = c < ncols;
@@ -1215,7 +1253,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                 }
             }
             // the bulk of the tiles is requested behind the first x loads, so that these do not queue behind megabytes
-            if (then_rest && base == 0) chunk_copy(false);
+            if (then_rest && base == 0) tail_copy();
 #pragma unroll
             for (int b = 0; b < BT; b++) {
                 float sum = (v[b][0] + v[b][1]) + (v[b][2] + v[b][3]);
@@ -1238,8 +1276,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
     // sixteen long; CTA c takes chunks c, c + gridDim.x, ...  A chunk holds neighbouring column segments of (mostly)
     // one pair of row blocks, whose results the CTA adds up in shared memory before anything goes to global memory.
     const uint32_t nchunks = ((npairs + kWarps * gridDim.x - 1u) / (kWarps * gridDim.x)) * gridDim.x;
-    auto chunk_lo = [&](uint32_t t) { return (uint32_t)((uint64_t)t * npairs / nchunks); };
-    auto chunk_of = [&](uint32_t qq) { return (uint32_t)((((uint64_t)qq + 1u) * nchunks - 1u) / npairs); };
+    const bool narrow = ((uint64_t)(npairs + 1u) * (nchunks + 1u)) >> 32 == 0;      // the products below fit 32 bits
+    auto chunk_lo = [&](uint32_t t) { return narrow ? t * npairs / nchunks : (uint32_t)((uint64_t)t * npairs / nchunks); };
+    auto chunk_of = [&](uint32_t qq) {
+        return narrow ? ((qq + 1u) * nchunks - 1u) / npairs : (uint32_t)((((uint64_t)qq + 1u) * nchunks - 1u) / npairs);
+    };
     uint32_t t = blockIdx.x;
     uint32_t cs = chunk_lo(t + 1) - chunk_lo(t);
     uint32_t q = chunk_lo(t) + warp;
@@ -1257,9 +1298,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
     // so their phase follows its own count, not the CTA's trip count
     for (uint32_t uses = 0; t < nchunks;) {
         const uint32_t parity = uses & 1u;
-        const TileDesc da = d[0], db = d[1];
-        const bool cur_b = has_b, cur_have = have;
-        const uint32_t row[2] = {da.row0 + lane * G, db.row0 + lane * G};
+        const PairGeo cur = geo;
+        const bool cur_b = cur.has_b, cur_have = have;
+        const uint32_t row[2] = {cur.row0[0] + lane * G, cur.row0[1] + lane * G};
+        const uint32_t len_a = __shfl_sync(0xffffffffu, dl.y, 0) << 6, len_b = __shfl_sync(0xffffffffu, dl.y, 8) << 6;   // tile bytes
         float y[2][G][BT];
 #pragma unroll
         for (int k = 0; k < 2; k++)
@@ -1279,12 +1321,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
 #pragma unroll
             for (int k = 0; k < 2; k++) {
                 sc_ptr[k] = a.scales_t + row[k] / G;
-                sc_cur[k] = ldg_u32x2_pinned(sc_ptr[k] + (size_t)(da.col0 / a.group) * sc_stride);
+                sc_cur[k] = ldg_u32x2_pinned(sc_ptr[k] + (size_t)(cur.col0 / a.group) * sc_stride);
                 sc_next[k] = make_uint2(0u, 0u);
             }
-            if ((da.col0 / a.group + 1) * a.group < da.col0 + da.ncols) {
+            if ((cur.col0 / a.group + 1) * a.group < cur.col0 + cur.ncols) {
 #pragma unroll
-                for (int k = 0; k < 2; k++) sc_next[k] = ldg_u32x2_pinned(sc_ptr[k] + (size_t)(da.col0 / a.group + 1) * sc_stride);
+                for (int k = 0; k < 2; k++) sc_next[k] = ldg_u32x2_pinned(sc_ptr[k] + (size_t)(cur.col0 / a.group + 1) * sc_stride);
             }
             PairChain ch[2];
 #pragma unroll
@@ -1295,9 +1337,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                 ch[k].w = lds_u16(ch[k].addr);
             }
             EOQ_STAMP(2);
-            uint32_t c = da.col0;
-            const uint32_t col0 = da.col0, cend = da.col0 + da.ncols;
-            const uint32_t nchunks0 = min(kMaxChunks, ((da.len64 << 6) + kChunk - 1) / kChunk), nchunks1 = min(kMaxChunks, ((db.len64 << 6) + kChunk - 1) / kChunk);
+            uint32_t c = cur.col0;
+            const uint32_t col0 = cur.col0, cend = cur.col0 + cur.ncols;
+            const uint32_t nchunks0 = min(kMaxChunks, (len_a + kChunk - 1) / kChunk), nchunks1 = min(kMaxChunks, (len_b + kChunk - 1) / kChunk);
             while (c < cend) {
                 const uint32_t g = c / a.group;
                 const uint32_t rstart = c, rend = min(cend, (g + 1) * a.group);
@@ -1369,7 +1411,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
         uint32_t early_ticket = 0;
         const uint32_t first_q = rbp * a.nseg;
         const uint32_t count = leader ? chunk_of(first_q + a.nseg - 1u) - chunk_of(first_q) + 1u : 1u;
-        if (leader && count > 1 && a.pair_partials && lane == 0) early_ticket = atomicAdd(a.counters + da.row0 / (32u * G), 1u);
+        if (leader && count > 1 && a.pair_partials && lane == 0) early_ticket = atomicAdd(a.counters + cur.row0[0] / (32u * G), 1u);
         __syncthreads();
 
         if (leader) {
@@ -1417,33 +1459,56 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                         for (int j = 0; j < G; j++)
 #pragma unroll
                             for (int b = 0; b < BT; b++) { own[k][j][b] = y[k][j][b]; y[k][j][b] = 0.0f; }
+                    // Up to kP slots are polled together: the loads of every slot still missing are issued before any of them
+                    // is tested, so a round costs one trip to the L2 however many slots it covers; the rows are added in
+                    // slot order all the same.
+                    constexpr int kP = G * BT <= 3 ? 4 : G * BT <= 6 ? 2 : 1;
                     const long long t0 = clock64();
-                    for (uint32_t s = 0; s < count; s++) {
-                        uint32_t v[2][G][BT];
-                        bool all = s == slot;
-                        while (!all) {
-                            all = true;
+                    for (uint32_t s0 = 0; s0 < count; s0 += kP) {
+                        uint32_t v[kP][2][G][BT];
+                        uint32_t pending = 0;
 #pragma unroll
-                            for (int k = 0; k < 2; k++)
+                        for (int u = 0; u < kP; u++)
+                            if (s0 + u < count && s0 + u != slot) pending |= 1u << u;
+                        while (pending) {
 #pragma unroll
-                                for (int j = 0; j < G; j++)
+                            for (int u = 0; u < kP; u++)
+                                if (pending >> u & 1u) {
 #pragma unroll
-                                    for (int b = 0; b < BT; b++) {
-                                        v[k][j][b] = 0u;
-                                        if (k == 0 || cur_b) {
-                                            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v[k][j][b])
-                                                         : "l"(slots + ((size_t)s * a.Npad + row[k]) * BT + j * BT + b) : "memory");
-                                            all = all && v[k][j][b] != kEmpty;
-                                        }
-                                    }
-                            if (!all && clock64() - t0 > (1ll << 31)) { *a.status = 3u; all = true; }   // ~1 s: give up, the host reports it
+                                    for (int k = 0; k < 2; k++)
+#pragma unroll
+                                        for (int j = 0; j < G; j++)
+#pragma unroll
+                                            for (int b = 0; b < BT; b++) {
+                                                v[u][k][j][b] = 0u;
+                                                if (k == 0 || cur_b)
+                                                    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v[u][k][j][b])
+                                                                 : "l"(slots + ((size_t)(s0 + u) * a.Npad + row[k]) * BT + j * BT + b) : "memory");
+                                            }
+                                }
+#pragma unroll
+                            for (int u = 0; u < kP; u++)
+                                if (pending >> u & 1u) {
+                                    bool all = true;
+#pragma unroll
+                                    for (int k = 0; k < 2; k++)
+#pragma unroll
+                                        for (int j = 0; j < G; j++)
+#pragma unroll
+                                            for (int b = 0; b < BT; b++) all = all && v[u][k][j][b] != kEmpty;
+                                    if (all) pending &= ~(1u << u);
+                                }
+                            if (pending && clock64() - t0 > (1ll << 31)) { *a.status = 3u; pending = 0; }   // ~1 s: give up, the host reports it
                         }
 #pragma unroll
-                        for (int k = 0; k < 2; k++)
+                        for (int u = 0; u < kP; u++)
+                            if (s0 + u < count)
 #pragma unroll
-                            for (int j = 0; j < G; j++)
+                                for (int k = 0; k < 2; k++)
 #pragma unroll
-                                for (int b = 0; b < BT; b++) y[k][j][b] += s == slot ? own[k][j][b] : __uint_as_float(v[k][j][b]);
+                                    for (int j = 0; j < G; j++)
+#pragma unroll
+                                        for (int b = 0; b < BT; b++) y[k][j][b] += s0 + u == slot ? own[k][j][b] : __uint_as_float(v[u][k][j][b]);
                     }
                     for (uint32_t s = 0; s < count; s++)
 #pragma unroll
@@ -1454,7 +1519,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
 #pragma unroll
                                 for (int b = 0; b < BT; b++) __stcg(slots + ((size_t)s * a.Npad + row[k]) * BT + j * BT + b, kEmpty);
                         }
-                    if (lane == 0) a.counters[da.row0 / (32u * G)] = 0u;
+                    if (lane == 0) a.counters[cur.row0[0] / (32u * G)] = 0u;
                 }
             } else if (count > 1) {
 #pragma unroll
@@ -1469,7 +1534,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                 __threadfence();
                 __syncwarp();
                 uint32_t ticket = 0;
-                if (lane == 0) ticket = atomicAdd(a.counters + da.row0 / (32u * G), 1u);
+                if (lane == 0) ticket = atomicAdd(a.counters + cur.row0[0] / (32u * G), 1u);
                 ticket = __shfl_sync(0xffffffffu, ticket, 0);
                 EOQ_STAMP(4);
                 last = ticket == count - 1u;
@@ -1504,7 +1569,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
 #pragma unroll
                                         for (int b = 0; b < BT; b++) y[k][j][b] += v[u][k][j][b];
                     }
-                    if (lane == 0) a.counters[da.row0 / (32u * G)] = 0u;
+                    if (lane == 0) a.counters[cur.row0[0] / (32u * G)] = 0u;
                 }
             }
             if (last) {
@@ -1527,6 +1592,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
             }
         }
     }
+    gather_finish(a);          // row-sharded runs: wait for the other ranks' rows and unpack them
 }
 
 static std::atomic<int> g_gemv_pairs{1};
@@ -1631,54 +1697,70 @@ int launch_gemv(const GemvArgs &a, uint32_t G, uint32_t bits, uint32_t kind, voi
 }
 
 // ---------------------------------------------------------------------------
-// Second half of the fused all-gather: unpack what the other ranks sent.  Every element of the slot's receive
-// buffer that another rank owns is polled until its word carries this gather's epoch, and its value is written
-// into the full output vector.  Polls are bounded (about a second), after which the status word is set.  The CTA
-// that finishes last advances the slot's epoch.
+// Second half of the fused all-gather: unpack what the other ranks sent (GemvArgs describes the words).  Every
+// word of the slot's receive buffer that another rank owns is polled until it carries this gather's epoch, and its
+// values are written into the full output vector.  The wait is bounded by a.gather_limit clock ticks, after which the
+// status word is set and the kernel carries on.  The CTA that finishes last advances the slot's epoch.  Called by all
+// threads of every CTA at the end of the fused GEMV kernels, and by gather_wait_kernel on its own.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) gather_wait_kernel(const uint2 *ll, void *y, uint32_t *epoch, uint32_t *done, uint32_t rank,
-                                                         uint32_t rows_per_rank, uint32_t n_total, uint32_t batch, int y_dtype,
-                                                         uint32_t *status)
+__device__ __forceinline__ void gather_finish(const GemvArgs &a)
 {
-    // Launched programmatically behind the GEMV: resident early, it lets the next kernel of the stream start its own
-    // set-up at once, and touches memory only after the GEMV has completed.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t want = *reinterpret_cast<const volatile uint32_t *>(epoch) + 1u;
-    const uint32_t total = batch * n_total;
+    if (a.world <= 1) return;
+    const uint32_t G = a.gather_g;
+    const uint32_t epoch = __ldcg(a.gather_epoch) + 1u;
+    const bool f32 = a.y_dtype == EOQ_B200_F32;
+    const uint32_t wpr = f32 ? a.N : a.Npad / G, used = f32 ? a.N : (a.N + G - 1u) / G;
+    const uint32_t per_b = (a.world - 1u) * used, total = a.batch * per_b;
+    const uint64_t *ll = a.peer_ll[a.rank];
     const long long t0 = clock64();
     bool gave_up = false;
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-        if ((i % n_total) / rows_per_rank == rank) continue;          // our own rows are already in place
-        uint32_t bits = 0, fl = 0;
+        const uint32_t b = i / per_b, rem = i - b * per_b, pi = rem / used, wi = rem - pi * used;
+        const uint32_t pr = pi + (pi >= a.rank ? 1u : 0u);
+        const uint64_t *src = ll + (size_t)(b * a.world + pr) * wpr + wi;
+        uint32_t lo = 0, hi = 0;
         while (!gave_up) {
-            asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits), "=r"(fl) : "l"(ll + i) : "memory");
-            if (fl == want) break;
-            if (clock64() - t0 > (1ll << 31)) gave_up = true;          // ~1 s at 2 GHz
+            asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "l"(src) : "memory");
+            if (f32 ? hi == epoch : (hi >> 16) == (epoch & 0xFFFFu)) break;
+            if (clock64() - t0 > a.gather_limit) gave_up = true;
         }
-        if (y_dtype == EOQ_B200_F32) reinterpret_cast<uint32_t *>(y)[i] = bits;
-        else reinterpret_cast<uint16_t *>(y)[i] = (uint16_t)bits;
+        if (gave_up) continue;
+        const size_t at = (size_t)b * a.n_total + (size_t)pr * a.N;
+        if (f32) {
+            reinterpret_cast<uint32_t *>(a.y)[at + wi] = lo;
+        } else {
+            uint16_t *dst = reinterpret_cast<uint16_t *>(a.y) + at;
+            const uint32_t r = wi * G;
+            dst[r] = (uint16_t)lo;
+            if (G > 1 && r + 1 < a.N) dst[r + 1] = (uint16_t)(lo >> 16);
+            if (G > 2 && r + 2 < a.N) dst[r + 2] = (uint16_t)hi;
+        }
     }
-    if (gave_up) *status = 4u;
+    if (gave_up) *a.gather_status = 4u;
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
-        if (atomicAdd(done, 1u) == gridDim.x - 1u) {
-            *done = 0u;
-            *epoch = want;
+        if (atomicAdd(a.gather_done, 1u) == gridDim.x - 1u) {
+            *a.gather_done = 0u;
+            *a.gather_epoch = epoch;
         }
     }
 }
 
-int launch_gather_wait(const void *ll, void *y, uint32_t *epoch, uint32_t *done, uint32_t rank, uint32_t rows_per_rank,
-                       uint32_t n_total, uint32_t batch, int y_dtype, uint32_t *status, void *stream)
+// The wait on its own: for receive buffers filled by something other than the GEMV of this launch.
+__global__ void __launch_bounds__(256) gather_wait_kernel(const GemvArgs a)
 {
-    const uint32_t total = batch * n_total;
-    // one element per thread where possible: a thread polls its elements one after the other, and a poll of a word a
-    // peer has just written takes a microsecond or two
-    const uint32_t grid = std::max(1u, std::min(128u, (total + 255u) / 256u));
-    cudaError_t e = launch_with_pdl(gather_wait_kernel, dim3(grid), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
-                                    reinterpret_cast<const uint2 *>(ll), y, epoch, done, rank, rows_per_rank, n_total, batch, y_dtype, status);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    gather_finish(a);
+}
+
+int launch_gather_wait(const GemvArgs &a, void *stream)
+{
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const uint32_t total = a.batch * a.n_total;
+    const uint32_t grid = max(1u, min(64u, (total + 255u) / 256u));
+    cudaError_t e = launch_with_pdl(gather_wait_kernel, dim3(grid), dim3(256), 0, st, a);
     g_launches++;
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
@@ -1706,7 +1788,7 @@ __global__ void __launch_bounds__(256) decode_tiles_kernel(const DecodeArgs a)
     const uint32_t mask = M - 1u, p = a.p, sgroups = K / a.group;
     for (uint32_t t = blockIdx.x + gridDim.x * warp; t < a.ntiles; t += gridDim.x * nwarps) {
         const TileDesc d = a.tiles[t];
-        const uint8_t *base = a.stream + ((size_t)d.off64 << 6);
+        const TileSrc base = tile_src(a.stream, a.head_bytes, t, d);
         uint32_t x;
         WordState ws;
         tile_open(ring, d, base, lane);
@@ -2077,6 +2159,7 @@ struct GemmArgs {
     uint32_t       *counters; // [nrb], zero between launches
     uint32_t       *status;
     uint32_t N, K, group, p, nseg, nrb, M;
+    uint32_t head_bytes;      // see TiledWeights::head_bytes
     int y_dtype;
 };
 
@@ -2272,7 +2355,7 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_addr), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    if (have) tile_open(ring, d, a.stream + ((size_t)d.off64 << 6), lane);
+    if (have) tile_open(ring, d, tile_src(a.stream, a.head_bytes, tile, d), lane);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -2308,7 +2391,7 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
             have = tile < g_hi;
             if (have) {
                 d = a.tiles[tile];
-                tile_open(ring, d, a.stream + ((size_t)d.off64 << 6), lane);
+                tile_open(ring, d, tile_src(a.stream, a.head_bytes, tile, d), lane);
             }
         }
         __syncwarp();
@@ -2325,7 +2408,7 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
         while (have) {
-            const uint8_t *base = a.stream + ((size_t)d.off64 << 6);
+            const TileSrc base = tile_src(a.stream, a.head_bytes, tile, d);
             const uint32_t d_tmem = tmem_base + (tile / a.nseg - rb0) * 128u;
             uint32_t x;
             WordState ws;
@@ -2335,7 +2418,9 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
             const uint32_t next = tile + nwarps;
             if (next < g_hi && lane == 0) {
                 const TileDesc nd = a.tiles[next];
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.stream + ((size_t)nd.off64 << 6)), "r"(nd.len64 << 6) : "memory");
+                if (a.head_bytes) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.stream + (size_t)next * a.head_bytes), "r"(a.head_bytes) : "memory");
+                if ((nd.len64 << 6) > a.head_bytes)
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.stream + ((size_t)nd.off64 << 6)), "r"((nd.len64 << 6) - a.head_bytes) : "memory");
             }
             const uint32_t row = d.row0 + lane * 3;
             // transposed copy of the scales: the three scales of a lane's rows for one group are one 8-byte word, the
@@ -2388,7 +2473,7 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
             have = tile < g_hi;
             if (have) {
                 d = a.tiles[tile];
-                tile_open(ring, d, a.stream + ((size_t)d.off64 << 6), lane);
+                tile_open(ring, d, tile_src(a.stream, a.head_bytes, tile, d), lane);
             }
         }
         GEMM_STAMP(3);
@@ -2495,7 +2580,8 @@ uint32_t gemm_grid(uint32_t nrb, uint32_t nseg)
 // x: [M, K] row-major, M <= 128.  fp32 and bf16 activations are first rounded to fp16 into `xhalf` ([128, K] fp16 scratch).
 int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *stream, const uint2 *scales_t, const void *x,
                    void *xhalf, float *partials, uint32_t *counters, void *y, const float *bias, uint32_t *status, uint32_t N,
-                   uint32_t K, uint32_t group, uint32_t p, uint32_t nseg, uint32_t nrb, uint32_t M, int x_dtype, int y_dtype, void *stream_)
+                   uint32_t K, uint32_t group, uint32_t p, uint32_t nseg, uint32_t nrb, uint32_t head_bytes, uint32_t M, int x_dtype, int y_dtype,
+                   void *stream_)
 {
     static std::mutex mu;
     static size_t attr_set[16] = {0};
@@ -2548,6 +2634,7 @@ int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *
     a.table = table; a.tiles = tiles; a.stream = stream; a.scales_t = scales_t; a.y = y; a.bias = bias;
     a.partials = partials; a.counters = counters; a.status = status;
     a.N = N; a.K = K; a.group = group; a.p = p; a.nseg = nseg; a.nrb = nrb; a.M = M;
+    a.head_bytes = head_bytes;
     a.y_dtype = y_dtype;
     e = launch_with_pdl(gemm_tiles_kernel, dim3(gemm_grid(nrb, nseg)), dim3(warps * 32), smem, st, a, xmap);
     g_launches++;

@@ -264,15 +264,24 @@ eoq_error_t build_tiled(const uint8_t *symbols, uint32_t N, uint32_t K, uint32_t
         out.tiles[t] = d;
     });
     for (uint32_t v : tile_drift) out.max_drift = std::max(out.max_drift, v);
-    size_t total = 0;
+    // Stream layout: [heads: ntiles x head_bytes][tails][padding].  The first head_bytes of every tile sit at a
+    // fixed stride, so a kernel can request them from the tile index alone, without a descriptor fetch in front;
+    // the rest of a tile (its tail) is packed behind and found through the descriptor.  head_bytes is a whole number
+    // of kilobytes no longer than the shortest tile (two at most: enough to cover the descriptor's round trip).
+    size_t shortest = ~(size_t)0;
+    for (size_t t = 0; t < ntiles; t++) shortest = std::min(shortest, tile_bytes[t].size());
+    const uint32_t H = shortest >= 2048 ? 2048u : shortest >= 1024 ? 1024u : 0u;
+    out.head_bytes = H;
+    size_t total = ntiles * (size_t)H;
     for (size_t t = 0; t < ntiles; t++) {
         if ((total >> 6) > 0xFFFFFFFFull) return EOQ_ERR_OVERFLOW;
         out.tiles[t].off64 = (uint32_t)(total >> 6);
-        total += tile_bytes[t].size();
+        total += tile_bytes[t].size() - H;
     }
     out.stream.assign(total + 4096, 0);
     parallel_for(ntiles, [&](size_t t) {
-        std::memcpy(out.stream.data() + ((size_t)out.tiles[t].off64 << 6), tile_bytes[t].data(), tile_bytes[t].size());
+        if (H) std::memcpy(out.stream.data() + t * (size_t)H, tile_bytes[t].data(), H);
+        std::memcpy(out.stream.data() + ((size_t)out.tiles[t].off64 << 6), tile_bytes[t].data() + H, tile_bytes[t].size() - H);
     });
     return EOQ_OK;
 }

@@ -34,11 +34,12 @@ GEMM_MAX_ROWS = 128
 
 
 class EOQWeight:
-    """Owner of one ``eoq_b200_weight_t``."""
+    """Owner of one ``eoq_b200_weight_t`` (resident on the device that was current when it was built)."""
 
     def __init__(self, handle: int, kind: int):
         self._h = C.c_void_p(handle)
         self.kind = kind
+        self.device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else None
         info = _lib.WeightInfo()
         _lib.check(_lib.lib().eoq_b200_weight_info(self._h, C.byref(info)), "eoq_b200_weight_info")
         self.info = info
@@ -127,6 +128,13 @@ class EOQWeight:
                    "eoq_b200_weight_from_rans")
         return cls(h.value, kind)
 
+    def _on_device(self, x: torch.Tensor, what: str):
+        """Context that makes the weight's device current; raises if x lives elsewhere (the kernels take raw pointers)."""
+        require_cuda(x, what)
+        if self.device is not None and x.device != self.device:
+            raise RuntimeError(f"{what}: the activations are on {x.device} but the weight lives on {self.device}")
+        return torch.cuda.device(x.device)
+
     # -- use -------------------------------------------------------------------
     def gemv(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """y = x @ W.T (+ bias) for x of shape (..., K) with at most 8 rows in total."""
@@ -142,11 +150,12 @@ class EOQWeight:
         b = None
         if bias is not None:
             b = bias.to(device=x.device, dtype=torch.float32).contiguous()
-        for lo in range(0, rows, 8):
-            hi = min(rows, lo + 8)
-            _lib.check(_lib.lib().eoq_b200_gemv(self._h, x2[lo:hi].data_ptr(), _DTYPES[x.dtype], hi - lo,
-                                                y[lo:hi].data_ptr(), _DTYPES[out_dtype],
-                                                b.data_ptr() if b is not None else None, _stream_ptr()), "eoq_b200_gemv")
+        with self._on_device(x, "EOQWeight.gemv"):
+            for lo in range(0, rows, 8):
+                hi = min(rows, lo + 8)
+                _lib.check(_lib.lib().eoq_b200_gemv(self._h, x2[lo:hi].data_ptr(), _DTYPES[x.dtype], hi - lo,
+                                                    y[lo:hi].data_ptr(), _DTYPES[out_dtype],
+                                                    b.data_ptr() if b is not None else None, _stream_ptr()), "eoq_b200_gemv")
         return y.reshape(*x.shape[:-1], self.rows)
 
     def gemm(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -165,8 +174,9 @@ class EOQWeight:
         b = None
         if bias is not None:
             b = bias.to(device=x.device, dtype=torch.float32).contiguous()
-        _lib.check(_lib.lib().eoq_b200_gemm(self._h, x2.data_ptr(), _DTYPES[x.dtype], x2.shape[0], y.data_ptr(), _DTYPES[out_dtype],
-                                            b.data_ptr() if b is not None else None, _stream_ptr()), "eoq_b200_gemm")
+        with self._on_device(x, "EOQWeight.gemm"):
+            _lib.check(_lib.lib().eoq_b200_gemm(self._h, x2.data_ptr(), _DTYPES[x.dtype], x2.shape[0], y.data_ptr(), _DTYPES[out_dtype],
+                                                b.data_ptr() if b is not None else None, _stream_ptr()), "eoq_b200_gemm")
         return y.reshape(*x.shape[:-1], self.rows)
 
     def status(self) -> int:
@@ -189,7 +199,7 @@ class EOQWeight:
 
     def decode_symbols(self, packed: bool = False, device=None) -> torch.Tensor:
         """Decoded symbols: uint8 [N, K], or packed two per byte [N, K/2] as QuantizedLinear stores them."""
-        dev = torch.device(device or "cuda")
+        dev = torch.device(device) if device is not None else (self.device or torch.device("cuda"))
         shape = (self.rows, self.cols // 2) if packed else (self.rows, self.cols)
         out = torch.empty(shape, dtype=torch.uint8, device=dev)
         with torch.cuda.device(dev):
@@ -199,7 +209,7 @@ class EOQWeight:
 
     def dequantize(self, dtype: torch.dtype = torch.float16, device=None) -> torch.Tensor:
         """Dense [N, K] matrix (INT4 kind): (sym - 7) * scale."""
-        dev = torch.device(device or "cuda")
+        dev = torch.device(device) if device is not None else (self.device or torch.device("cuda"))
         out = torch.empty((self.rows, self.cols), dtype=dtype, device=dev)
         with torch.cuda.device(dev):
             _lib.check(_lib.lib().eoq_b200_weight_decode(self._h, None, 0, out.data_ptr(), _DTYPES[dtype], _stream_ptr()),

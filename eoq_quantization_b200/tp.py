@@ -66,8 +66,8 @@ class PeerGather:
     through ``torch.distributed``.
 
     ``gemv(weight, x, n_total, slot)`` returns this rank's view of the full ``(rows, n_total)``
-    result once every rank's slice has arrived (the wait is a kernel on the current stream, so
-    the call itself does not block).  Consecutive calls must use different slots and all ranks
+    result once every rank's slice has arrived (the kernel that computes this rank's rows also
+    waits for the others' on the current stream, so the call itself does not block).  Consecutive calls must use different slots and all ranks
     must make the same calls in the same order.
     """
 
@@ -102,9 +102,10 @@ class PeerGather:
             row_offset = self.rank * weight.rows
         b = None if bias is None else bias.to(device=x.device, dtype=torch.float32).contiguous()
         lib = _lib.lib()
-        _lib.check(lib.eoq_b200_gemv_gather(weight._h, x2.data_ptr(), _DTYPES[x.dtype], rows, _DTYPES[out_dtype],
-                                            b.data_ptr() if b is not None else None, self._h, slot, row_offset, n_total,
-                                            _stream_ptr()), "eoq_b200_gemv_gather")
+        with weight._on_device(x, "PeerGather.gemv"):
+            _lib.check(lib.eoq_b200_gemv_gather(weight._h, x2.data_ptr(), _DTYPES[x.dtype], rows, _DTYPES[out_dtype],
+                                                b.data_ptr() if b is not None else None, self._h, slot, row_offset, n_total,
+                                                _stream_ptr()), "eoq_b200_gemv_gather")
         key = (slot, rows, n_total, out_dtype)
         view = self._views.get(key)
         if view is None:                        # wrap the slot once: no pointer queries while a stream is being captured

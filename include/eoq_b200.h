@@ -67,6 +67,9 @@ typedef struct {
     void           *progress_ud;
 } eoq_decode_opts_t;
 
+/* eoq_rans_v2.h:94 */
+#define EOQ_DECODE_OPTS_DEFAULT { 0, NULL, NULL }
+
 /* eoq_rans_v2.h:116-123.  Host buffers in, host buffer out.  Payload layout
  * [u16 freq x A][u32 block_offsets x B][blocks] (eoq_rans_v2.c:606-619).
  * Checks, in the reference's order: NULL -> zero length (OK) -> header ->
@@ -131,11 +134,20 @@ typedef struct {
     void                    *progress_ud;
 } eoq_parallel_opts_t;
 
+/* eoq_parallel_decode.h:80 */
+#define EOQ_PARALLEL_OPTS_DEFAULT { 0, NULL, NULL }
+
 /* eoq_parallel_decode.h:100-104.  Returns the first non-OK task result
  * (eoq_parallel_decode.c:290-300); num_tasks <= 0 is OK; NULL tasks with
  * num_tasks > 0 is EOQ_ERR_NULL_PTR (:155-156); tasks not started after a
  * cancel request get EOQ_ERR_THREAD (:72-82, :197-205). */
 eoq_error_t eoq_parallel_decode(eoq_decode_task_t *tasks, int num_tasks, const eoq_parallel_opts_t *opts);
+
+/* eoq_parallel_decode.h:106-111: default options. */
+static inline eoq_error_t eoq_parallel_decode_auto(eoq_decode_task_t *tasks, int num_tasks)
+{
+    return eoq_parallel_decode(tasks, num_tasks, NULL);
+}
 
 /* eoq_parallel_decode.h:121 */
 int eoq_detect_num_threads(void);
@@ -158,13 +170,25 @@ int eoq_cuda_decode_tensor_device(const uint8_t *d_compressed_stream, const uint
                                   uint8_t *d_output, uint32_t num_rans_blocks, uint32_t rans_block_size,
                                   uint32_t total_symbols, uint32_t precision_bits, void *cuda_stream);
 
-/* eoq_cuda_decompress.cu:864-1021: batch context (opaque here; at most 1024 tensors). */
-typedef struct eoq_cuda_batch_ctx eoq_cuda_batch_ctx_t;
-eoq_cuda_batch_ctx_t *eoq_cuda_batch_create(void *stream);      /* replaces the caller-allocated struct + _init (:882-887) */
+/* eoq_cuda_decompress.cu:864-1021: batch context, at most 1024 tensors.  As in the
+ * reference the caller owns the struct (stack or heap) and starts with
+ * eoq_cuda_batch_init; here it is small and its per-tensor staging lives behind `impl`,
+ * allocated by the first prepare_tensor and released by sync_and_free, after which the
+ * struct may be reused or simply dropped.  `stream` is a cudaStream_t kept as void*. */
+#define EOQ_CUDA_MAX_BATCH_TENSORS 1024                           /* :862 */
+typedef struct eoq_cuda_batch_ctx {
+    void    *impl;
+    void    *stream;
+    uint32_t n_tensors;
+    uint32_t reserved;
+} eoq_cuda_batch_ctx_t;
+void eoq_cuda_batch_init(eoq_cuda_batch_ctx_t *ctx, void *stream);                       /* :882-887 */
 int  eoq_cuda_batch_prepare_tensor(eoq_cuda_batch_ctx_t *ctx, const eoq_tensor_header_t *header,
                                    const uint8_t *compressed_host, uint8_t *d_output);   /* :900-975 */
 int  eoq_cuda_batch_launch(eoq_cuda_batch_ctx_t *ctx);           /* :985-1003 */
 int  eoq_cuda_batch_sync_and_free(eoq_cuda_batch_ctx_t *ctx);    /* :1008-1021 */
+/* Heap-allocated variants for bindings that cannot hold a C struct by value. */
+eoq_cuda_batch_ctx_t *eoq_cuda_batch_create(void *stream);
 void eoq_cuda_batch_destroy(eoq_cuda_batch_ctx_t *ctx);
 
 /* ===================================================================== *
@@ -221,10 +245,13 @@ typedef struct {
 /* The tiled layout on the host, before upload: lets a loader build it once,
  * keep it (the arrays may be written to a cache file) and inspect it without a
  * device.  Tile t: rows [row0, row0 + 32*G), columns [col0, col0 + ncols);
- * its bytes start at stream + 64*off64: 32 x u32 initial states, then rows of
- * 32 x u16 renormalisation words (lane l reads column l, top to bottom). */
+ * its bytes are 32 x u32 initial states, then rows of 32 x u16 renormalisation
+ * words (lane l reads column l, top to bottom).  The first head_bytes of tile
+ * t lie at stream + t*head_bytes (a fixed stride, so a kernel can fetch them
+ * from the tile index alone), the remaining 64*len64 - head_bytes at
+ * stream + 64*off64. */
 typedef struct eoq_b200_tiles eoq_b200_tiles_t;
-typedef struct { uint32_t row0, col0, ncols, seg, off64, len64; } eoq_b200_tile_desc_t;   /* len64: tile bytes / 64 */
+typedef struct { uint32_t row0, col0, ncols, seg, off64, len64; } eoq_b200_tile_desc_t;   /* len64: tile bytes (head + tail) / 64 */
 typedef struct {
     uint32_t rows, cols, padded_rows, group, kind, bits;
     uint32_t symbols_per_step, precision_bits;
@@ -234,6 +261,7 @@ typedef struct {
     const uint8_t *stream;
     uint64_t stream_bytes;
     uint32_t max_lane_drift;             /* largest gap, in word rows, between two lanes' read positions in any tile */
+    uint32_t head_bytes;                 /* 0, 1024 or 2048: bytes of every tile kept at the fixed stride */
 } eoq_b200_tiles_view_t;
 eoq_error_t eoq_b200_tiles_build(const uint8_t *symbols, const eoq_b200_weight_opts_t *opts, eoq_b200_tiles_t **out);
 eoq_error_t eoq_b200_tiles_view(const eoq_b200_tiles_t *t, eoq_b200_tiles_view_t *view);
@@ -295,17 +323,23 @@ eoq_error_t eoq_b200_gemm(eoq_b200_weight_t *w, const void *x, int x_dtype, uint
  * per GPU; rank r holds the weight rows [row_offset, row_offset + N) of an n_total-row layer.
  * Every rank creates a gather object (one device allocation of `slots` output buffers plus
  * flags), passes the 64-byte handle it gets to all other ranks by any means (the Python side
- * uses torch.distributed), and connects.  eoq_b200_gemv_gather then computes this rank's
- * rows, writes them into its own full-size output and sends them as 8-byte {value, epoch}
- * words straight into slot `slot` of every peer's receive buffer (plain stores over NVLink;
- * an 8-byte store arrives whole, so the epoch is the flag and no fence is needed); a small
- * kernel queued behind the GEMV polls the words the other ranks sent (bounded, ~1 s, then
- * eoq_b200_gather_status reports an error) and unpacks them.  After the call, work queued
- * on `stream` may read the full [batch, n_total] result at eoq_b200_gather_buffer(g, slot).
+ * uses torch.distributed), and connects.  eoq_b200_gemv_gather is ONE kernel: it computes this
+ * rank's rows, writes them into its own full-size output, sends them as 8-byte words straight
+ * into slot `slot` of every peer's receive buffer (plain stores over NVLink; an aligned 8-byte
+ * store arrives whole, so the epoch inside the word is the flag and no fence is needed; with
+ * 16-bit outputs one word carries the three rows of a lane plus a 16-bit epoch), and then waits
+ * for the words of the other ranks and unpacks them.  The wait is bounded (about a second, or
+ * eoq_b200_gather_set_timeout_ms); when it runs out the kernel returns all the same and
+ * eoq_b200_gather_status reports EOQ_ERR_CUDA once.  After the call, work queued on `stream`
+ * may read the full [batch, n_total] result at eoq_b200_gather_buffer(g, slot).
  * Rules: shards are equal and in rank order (row_offset = rank * N, n_total = world * N); all
  * ranks make the same sequence of calls; consecutive calls use different slots (a fast rank
  * may send the next gather while a slow one still unpacks the previous one);
- * batch * n_total * sizeof(y) <= slot_bytes; world <= 8. */
+ * batch * n_total * sizeof(y) <= slot_bytes; world <= 8; the weight, the gather object and the
+ * current device must be the same GPU (else EOQ_ERR_UNSUPPORTED, nothing is launched).
+ * eoq_b200_gather_wait is the second half on its own, for receive buffers that something else
+ * fills: it waits for `rows_per_rank` rows from every other rank in words of `rows_per_word`
+ * rows (1..3; fp32 outputs always use one word per value) and unpacks them into the slot. */
 #define EOQ_B200_IPC_HANDLE_BYTES 64
 typedef struct eoq_b200_gather eoq_b200_gather_t;
 eoq_error_t eoq_b200_gather_create(uint32_t world, uint32_t rank, uint32_t slots, size_t slot_bytes,
@@ -314,6 +348,9 @@ eoq_error_t eoq_b200_gather_connect(eoq_b200_gather_t *g, const void *all_handle
 void        eoq_b200_gather_destroy(eoq_b200_gather_t *g);
 void       *eoq_b200_gather_buffer(eoq_b200_gather_t *g, uint32_t slot);
 eoq_error_t eoq_b200_gather_status(eoq_b200_gather_t *g, void *stream);
+eoq_error_t eoq_b200_gather_set_timeout_ms(eoq_b200_gather_t *g, uint32_t milliseconds /* 1..60000 */);
+eoq_error_t eoq_b200_gather_wait(eoq_b200_gather_t *g, uint32_t slot, uint32_t rows_per_rank, uint32_t batch,
+                                 int y_dtype, uint32_t rows_per_word, void *stream);
 eoq_error_t eoq_b200_gemv_gather(eoq_b200_weight_t *w, const void *x, int x_dtype, uint32_t batch, int y_dtype,
                                  const float *bias, eoq_b200_gather_t *g, uint32_t slot, uint32_t row_offset,
                                  uint32_t n_total, void *stream);

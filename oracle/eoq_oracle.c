@@ -285,22 +285,25 @@ void orc_int4_linear(const uint8_t *packed /* [N, ceil(K/2)] */, const float *sc
  * G consecutive rows row0 + l*G + j and reads column l of the word rows.  Step:
  *   e = table[x & (2^p - 1)];  x = (e >> 23) * (x >> p) + (e & bias_mask);
  *   symbols = (e >> (23 - G*bits)) fields;  if x < 2^16: x = x << 16 | next word.
- * desc[t] = {row0, col0, ncols, seg, off64, len64}.  out is [rows, cols] bytes.
+ * desc[t] = {row0, col0, ncols, seg, off64, len64}.  Byte b of tile t is at
+ * stream[t * head_bytes + b] for b < head_bytes and at
+ * stream[64 * off64 + b - head_bytes] from there on.  out is [rows, cols] bytes.
  * ---------------------------------------------------------------------- */
 int orc_decode_tiles(const uint32_t *table, uint32_t p, uint32_t G, uint32_t bits,
                      const uint32_t *desc, uint32_t ntiles, const uint8_t *stream, size_t stream_bytes,
-                     uint32_t rows, uint32_t cols, uint8_t *out)
+                     uint32_t head_bytes, uint32_t rows, uint32_t cols, uint8_t *out)
 {
     if (!table || !desc || !stream || !out) return ORC_ERR_NULL_PTR;
     const uint32_t shift = 23 - G * bits, bias_mask = (1u << shift) - 1, fmask = (1u << bits) - 1;
     const uint32_t mask = (1u << p) - 1;
     for (uint32_t t = 0; t < ntiles; t++) {
         const uint32_t *d = desc + 6 * (size_t)t;
-        const size_t base = (size_t)d[4] << 6;
-        if (base + 128 > stream_bytes) return ORC_ERR_CORRUPT;
+        const size_t head = (size_t)t * head_bytes, tail = ((size_t)d[4] << 6) - head_bytes;
+#define ORC_TILE_AT(b) ((b) < head_bytes ? head + (b) : tail + (b))
+        if (ORC_TILE_AT((size_t)0) + 128 > stream_bytes) return ORC_ERR_CORRUPT;
         for (uint32_t l = 0; l < 32; l++) {
             uint32_t x;
-            memcpy(&x, stream + base + 4 * l, 4);
+            memcpy(&x, stream + ORC_TILE_AT((size_t)4 * l), 4);
             size_t k = 0;
             for (uint32_t c = 0; c < d[2]; c++) {
                 uint32_t e = table[x & mask];
@@ -310,7 +313,7 @@ int orc_decode_tiles(const uint32_t *table, uint32_t p, uint32_t G, uint32_t bit
                     if (r < rows) out[(size_t)r * cols + d[1] + c] = (uint8_t)((e >> (shift + bits * j)) & fmask);
                 }
                 if (x < 65536u) {
-                    size_t at = base + 128 + (k * 32 + l) * 2;
+                    size_t at = ORC_TILE_AT(128 + (k * 32 + l) * 2);
                     if (at + 2 > stream_bytes) return ORC_ERR_CORRUPT;
                     uint16_t w;
                     memcpy(&w, stream + at, 2);
@@ -319,6 +322,7 @@ int orc_decode_tiles(const uint32_t *table, uint32_t p, uint32_t G, uint32_t bit
                 }
             }
         }
+#undef ORC_TILE_AT
     }
     return ORC_OK;
 }

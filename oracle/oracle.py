@@ -28,11 +28,21 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = None
 
 
+def reference_dir(ref_root: Optional[str] = None) -> Optional[str]:
+    """Where a checkout of the reference project is: the argument, else ``$EOQ_REFERENCE_DIR``, else a directory
+    named ``reference`` beside this repository; None if there is none."""
+    for cand in (ref_root, os.environ.get("EOQ_REFERENCE_DIR"),
+                 os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "llamacpp_integration")):
+            return os.path.abspath(cand)
+    return None
+
+
 def build(ref_root: Optional[str] = None) -> None:
     """Compile ``liboracle.so`` and, when a reference tree is present, ``_ref``."""
     subprocess.run(["make", "-C", _HERE, "all"], check=True, capture_output=True)
-    ref_root = ref_root or "/root/reference"
-    if os.path.isdir(os.path.join(ref_root, "llamacpp_integration")):
+    ref_root = reference_dir(ref_root)
+    if ref_root:
         subprocess.run(["make", "-C", _HERE, "ref", f"REF={ref_root}"], check=True, capture_output=True)
 
 
@@ -40,7 +50,8 @@ def lib() -> C.CDLL:
     global _LIB
     if _LIB is None:
         path = os.path.join(_HERE, "_build", "liboracle.so")
-        if not os.path.exists(path):
+        src = os.path.join(_HERE, "eoq_oracle.c")
+        if not os.path.exists(path) or (os.path.exists(src) and os.path.getmtime(src) > os.path.getmtime(path)):
             build()
         L = C.CDLL(path)
         u8p, u16p, u32p, u64p, f32p = (C.POINTER(t) for t in (C.c_uint8, C.c_uint16, C.c_uint32, C.c_uint64, C.c_float))
@@ -371,19 +382,19 @@ class RefC:
 
 
 def decode_tiles(table: np.ndarray, p: int, g: int, bits: int, desc: np.ndarray, stream: np.ndarray,
-                 rows: int, cols: int) -> np.ndarray:
+                 rows: int, cols: int, head_bytes: int = 0) -> np.ndarray:
     """Scalar decode of the product's tiled device layout -> uint8 [rows, cols] (orc_decode_tiles)."""
     L = lib()
     L.orc_decode_tiles.restype = C.c_int
     L.orc_decode_tiles.argtypes = [C.POINTER(C.c_uint32), C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32),
-                                   C.c_uint32, C.POINTER(C.c_uint8), C.c_size_t, C.c_uint32, C.c_uint32,
+                                   C.c_uint32, C.POINTER(C.c_uint8), C.c_size_t, C.c_uint32, C.c_uint32, C.c_uint32,
                                    C.POINTER(C.c_uint8)]
     table = np.ascontiguousarray(table, np.uint32)
     desc = np.ascontiguousarray(desc, np.uint32).reshape(-1, 6)
     stream = np.ascontiguousarray(stream, np.uint8)
     out = np.full((rows, cols), 255, np.uint8)
     rc = L.orc_decode_tiles(_p(table, C.c_uint32), p, g, bits, _p(desc, C.c_uint32), desc.shape[0],
-                            _p(stream, C.c_uint8), stream.size, rows, cols, _p(out, C.c_uint8))
+                            _p(stream, C.c_uint8), stream.size, head_bytes, rows, cols, _p(out, C.c_uint8))
     if rc != 0:
         raise ValueError(f"orc_decode_tiles failed: {rc}")
     return out

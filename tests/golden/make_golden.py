@@ -20,8 +20,10 @@ import sys
 
 import numpy as np
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
 OUT = os.path.dirname(os.path.abspath(__file__))
+# the reference checkout: the argument, else $EOQ_REFERENCE_DIR, else a directory named `reference` beside this repository
+REF = (sys.argv[1] if len(sys.argv) > 1 else os.environ.get("EOQ_REFERENCE_DIR")
+       or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(OUT))), "reference"))
 sys.dont_write_bytecode = True
 sys.path.insert(0, REF)
 

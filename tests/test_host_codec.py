@@ -24,6 +24,7 @@ def test_library_exports_every_declared_symbol():
     hdr = open(os.path.join(ROOT, "include", "eoq_b200.h")).read()
     declared = set(re.findall(r"\b(eoq_(?:b200_|cuda_)?[a-z0-9_]+)\s*\(", hdr))
     declared -= {"eoq_progress_fn", "eoq_parallel_progress_fn"}
+    declared -= {"eoq_parallel_decode_auto"}        # a static inline wrapper in the header, as in the reference's header
     assert declared == set(L.EXPORTS), declared ^ set(L.EXPORTS)
     for name in declared:
         assert hasattr(lib, name), name
@@ -153,7 +154,7 @@ def _tiles(sym, kind, group, g=0, p=0, target=0):
                desc=np.ctypeslib.as_array(v.tiles, (v.num_tiles * 6,)).copy(),
                stream=np.ctypeslib.as_array(v.stream, (v.stream_bytes,)).copy(),
                G=v.symbols_per_step, p=v.precision_bits, bits=v.bits, nseg=v.num_col_segments, ntiles=v.num_tiles,
-               npad=v.padded_rows)
+               npad=v.padded_rows, head=v.head_bytes)
     lib.eoq_b200_tiles_free(h)
     return 0, got
 
@@ -170,7 +171,9 @@ def test_default_int4_layout_keeps_tiles_short_enough_to_stage_two_per_warp():
     desc = t["desc"].reshape(-1, 6)
     assert desc[:, 2].max() <= 112 and (desc[:, 2] % 16 == 0).all()
     assert (desc[:, 5].astype(np.int64) * 64).max() + 64 <= 8192          # eight one-kilobyte chunks per tile
-    assert np.array_equal(O.decode_tiles(t["table"], t["p"], t["G"], t["bits"], t["desc"], t["stream"], 1152, 4096), sym)
+    assert np.array_equal(O.decode_tiles(t["table"], t["p"], t["G"], t["bits"], t["desc"], t["stream"], 1152, 4096, t["head"]), sym)
+    # every tile of this layout is longer than two kilobytes, so two kilobytes of each sit at the fixed stride
+    assert t["head"] == 2048 and (desc[:, 4].astype(np.int64) * 64 >= t["ntiles"] * 2048).all()
 
 
 @pytest.mark.parametrize("n,k,g", [(24, 256, 3), (100, 512, 2), (33, 128, 1), (97, 384, 3), (1, 128, 3), (96, 128, 3)])
@@ -183,7 +186,7 @@ def test_tile_encoder_round_trips_through_oracle(n, k, g):
     assert t["npad"] % (32 * g) == 0 and t["ntiles"] == t["nseg"] * (t["npad"] // (32 * g))
     desc = t["desc"].reshape(-1, 6)
     assert (desc[:, 2] % 16 == 0).all() and desc[:, 2].min() > 0
-    out = O.decode_tiles(t["table"], t["p"], t["G"], t["bits"], t["desc"], t["stream"], n, k)
+    out = O.decode_tiles(t["table"], t["p"], t["G"], t["bits"], t["desc"], t["stream"], n, k, t["head"])
     assert np.array_equal(out, sym)
     # table: every entry has 1 <= freq <= 511 and bias < freq
     e = t["table"]
@@ -194,11 +197,11 @@ def test_tile_encoder_round_trips_through_oracle(n, k, g):
 def test_tile_encoder_degenerate_distributions_and_q5():
     rc, t = _tiles(np.full((40, 128), 7, np.uint8), L.KIND_INT4_ABSMAX, 128, 2)      # one symbol only: freq capped at 511
     assert rc == 0
-    assert (O.decode_tiles(t["table"], t["p"], t["G"], t["bits"], t["desc"], t["stream"], 40, 128) == 7).all()
+    assert (O.decode_tiles(t["table"], t["p"], t["G"], t["bits"], t["desc"], t["stream"], 40, 128, t["head"]) == 7).all()
     sym = np.clip(np.random.default_rng(3).normal(16, 5, (64, 256)), 0, 31).astype(np.uint8)
     rc, t = _tiles(sym, L.KIND_Q5_POLAR, 64)
     assert rc == 0 and t["bits"] == 5 and t["G"] == 2
-    assert np.array_equal(O.decode_tiles(t["table"], t["p"], t["G"], t["bits"], t["desc"], t["stream"], 64, 256), sym)
+    assert np.array_equal(O.decode_tiles(t["table"], t["p"], t["G"], t["bits"], t["desc"], t["stream"], 64, 256, t["head"]), sym)
 
 
 def test_tile_builder_rejects_what_it_cannot_tile():
