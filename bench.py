@@ -44,7 +44,22 @@ REPLICAS = 8                       # weight copies cycled through so that the wo
 WORKLOAD = "llama7b_mlp_pair_int4_g128_rans_b1"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the fused kernel, from the ncu capture
 # summarised under profiles/
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 22162176    # profiles/gemv_pairs_kernel__llama7b_mlp_pair.md, 11008 x 4096 launch
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 22162176    # 11008 x 4096 launch
+NCU_TRAFFIC_SOURCE = "profiles/gemv_pairs_kernel__llama7b_mlp_pair.md"
+SM_COUNT, SM_CLOCK_MHZ = 148, 1965
+# what one rANS step of a warp (32 lanes x 3 weights) costs inside the column loop of the fused kernel, from the ncu
+# capture in NCU_TRAFFIC_SOURCE: shared-memory wavefronts (the four sub-partitions of an SM share one pipe) and issue slots
+SMEM_WAVEFRONTS_PER_WARP_STEP, ISSUE_SLOTS_PER_WARP_STEP = 5.7, 19.5
+
+
+def issue_bound(n, k, alg_bytes):
+    """The floor the SM itself puts under one launch: every weight costs a third of a rANS step of its lane, and a step
+    of a warp cannot go faster than the shared-memory pipe and the issue slots allow, whatever the memory system does."""
+    warp_steps_per_subpartition = n * k / 96.0 / (SM_COUNT * 4)
+    cycles = warp_steps_per_subpartition * max(SMEM_WAVEFRONTS_PER_WARP_STEP * 4, ISSUE_SLOTS_PER_WARP_STEP)
+    us = cycles / SM_CLOCK_MHZ
+    return {"us": us, "gbs": alg_bytes / us / 1e3, "binding": "shared-memory pipe",
+            "cycles_per_warp_step": max(SMEM_WAVEFRONTS_PER_WARP_STEP * 4, ISSUE_SLOTS_PER_WARP_STEP)}
 
 
 def make_layer(n, k, seed):
@@ -58,11 +73,24 @@ def make_layer(n, k, seed):
     return (codes + 7).to(torch.uint8).numpy(), scale.half().numpy()
 
 
-def wire_bytes(sym, scales, n, k, batch=1):
-    """Bytes the reference's wire format needs for this tensor and one GEMV: stream + offsets + scales + x + y."""
-    from eoq_quantization_b200.core import rans_blocked as RB
-    data = RB.BlockedRANSEncoder(block_size=4096, precision_bits=12).encode(sym.ravel().astype(np.int64), 15)
+def wire_bytes(sym, scales, n, k, batch=1, impl="b200"):
+    """Bytes the reference's wire format needs for this tensor and one GEMV: stream + offsets + scales + x + y.
+    The two arms use their own encoder (the library's, or the CPU checker's in the reference arm, which must not
+    load the library); the encoders are byte-identical, so the count is the same."""
+    if impl == "reference":
+        from oracle import oracle as O
+        data = O.encode_blocked(sym.ravel().astype(np.int64), 15, 4096, 12)
+    else:
+        from eoq_quantization_b200.core import rans_blocked as RB
+        data = RB.BlockedRANSEncoder(block_size=4096, precision_bits=12).encode(sym.ravel().astype(np.int64), 15)
     return len(data.compressed_blocks) + 4 * data.num_blocks + scales.size * 2 + batch * (k + n) * 2, data
+
+
+def workload_config(world):
+    """The part of the JSON line that names the workload: the same object in both arms."""
+    return {"workload": WORKLOAD, "batch": 1, "group": GROUP, "shapes": [[N_UP, K_UP], [N_DN, K_DN]],
+            "l2": f"{REPLICAS} weight copies cycled so that the working set exceeds L2",
+            "parallelism": f"row-sharded tp{world}"}
 
 
 class ClockSampler:
@@ -111,9 +139,9 @@ class ClockSampler:
 
 
 def shutdown_distributed(world):
-    """Leave the process group without ever blocking the job: captured CUDA graphs that contain NCCL kernels can make
-    communicator teardown wait for ever, so the graphs are dropped first, the teardown gets a deadline, and a rank
-    that misses it exits on its own (rank 0 has printed its line by then)."""
+    """Leave the process group without blocking the job for ever: captured CUDA graphs that contain NCCL kernels can
+    make communicator teardown hang, so the graphs are dropped first and the teardown gets a deadline; a rank that
+    misses it says so and exits with a failure code."""
     if world <= 1:
         return
     import gc
@@ -122,7 +150,11 @@ def shutdown_distributed(world):
     sys.stdout.flush()
     gc.collect()
     torch.cuda.synchronize()
-    timer = threading.Timer(20.0, lambda: os._exit(0))
+    def give_up():
+        sys.stderr.write("bench.py: process-group teardown did not finish within 30 s\n")
+        sys.stderr.flush()
+        os._exit(17)
+    timer = threading.Timer(30.0, give_up)
     timer.daemon = True
     timer.start()
     try:
@@ -182,7 +214,7 @@ def run_reference_arm(args):
     if rank != 0:
         return
     layers = [(*make_layer(N_UP, K_UP, 1), N_UP, K_UP), (*make_layer(N_DN, K_DN, 2), N_DN, K_DN)]
-    alg = sum(wire_bytes(s, sc, n, k)[0] for s, sc, n, k in layers)
+    alg = sum(wire_bytes(s, sc, n, k, impl="reference")[0] for s, sc, n, k in layers)
     cpu = CpuReference(layers)
     xs = [torch.randn(1, K_UP), torch.randn(1, K_DN)]
     for _ in range(args.warmup):
@@ -196,7 +228,7 @@ def run_reference_arm(args):
     line = {"impl": "reference", "metric": "fused decode+INT4 GEMV effective HBM GB/s", "value": gbs, "unit": "GB/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u32 rANS state, fp32 accumulate",
-            "data": "synthetic", "config": {"workload": WORKLOAD, "batch": 1, "group": GROUP},
+            "data": "synthetic", "config": workload_config(args.gpus),
             "tokens_per_s": 1.0 / dt,
             "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cpu.cores, "kind": cpu.kind, "sample": sample},
             "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -383,8 +415,10 @@ def run_gpu_arm(args):
     up_alg = alg_bytes[0] / world
     roof = {"bound": "hbm", "kernel": "gemv_pairs_kernel<3,1,512>", "achieved": up_alg / (up_ms * 1e-3) / 1e9, "peak": peak,
             "unit": "GB/s", "frac": up_alg / (up_ms * 1e-3) / 1e9 / peak, "peak_source": peak_src,
-            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None, "launch_us": up_ms * 1e3, "algorithmic_bytes_per_launch": up_alg,
-            "fp16_gemv_bytes": N_UP * K_UP * 2 // world}
+            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
+            "traffic_source": "ncu capture of this kernel on this workload, summarised in " + NCU_TRAFFIC_SOURCE + " (not measured in this run)",
+            "launch_us": up_ms * 1e3, "algorithmic_bytes_per_launch": up_alg,
+            "fp16_gemv_bytes": N_UP * K_UP * 2 // world, "issue_bound": issue_bound(N_UP // world, K_UP, up_alg)}
 
     # end to end through the C ABI with host buffers (pinned x in, y out, every step)
     hx = [torch.randn(1, K_UP).half().pin_memory(), torch.randn(1, K_DN).half().pin_memory()]
@@ -448,10 +482,10 @@ def run_gpu_arm(args):
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "u32 rANS state, fp32 accumulate, fp16 in/out",
                 "data": "synthetic",
-                "config": {"workload": WORKLOAD, "batch": 1, "group": GROUP, "shapes": [[N_UP, K_UP], [N_DN, K_DN]],
-                           "l2": f"{REPLICAS} weight copies cycled (working set {REPLICAS * sum(s[0].info.stream_bytes for s in shards) >> 20} MiB per rank > L2)",
-                           "parallelism": f"row-sharded tp{world}" + (f" + {gather_mode}" if world > 1 else ""),
-                           "launch": launch_mode, "symbols_per_step": int(info.symbols_per_step), "precision_bits": int(info.precision_bits)},
+                "config": workload_config(world),
+                "setup": {"working_set_mib_per_rank": REPLICAS * sum(s[0].info.stream_bytes for s in shards) >> 20,
+                          "gather": gather_mode, "launch": launch_mode, "symbols_per_step": int(info.symbols_per_step),
+                          "precision_bits": int(info.precision_bits)},
                 "tokens_per_s": 1e3 / ms, "pct_of_hbm_peak": 100.0 * value / (peak * world),
                 "algorithmic_bytes_per_step": alg_step,
                 "tile_bytes_per_step": int(sum(s[0].info.stream_bytes + s[0].info.scale_bytes for s in shards)) * world,
@@ -808,6 +842,137 @@ def run_prefill_gemm(args, torch, _lib, lib, EOQWeight):
     print(json.dumps(line), flush=True)
 
 
+def run_wire_decode(args):
+    """Decode of the reference's wire format (independent rANS blocks, byte renormalisation), one JSON line per case:
+    config 1 as BASELINE words it (4096 x 4096 INT4 symbols, blocks of 4096, 12-bit table), the .eoq default (blocks of
+    256, 14-bit table) and an EOQ-GGUF-style payload (byte alphabet, 16-bit table, blocks of 256).
+    value  = symbols per second of the decode kernel on device-resident inputs (eoq_cuda_decode_tensor_device),
+             eight copies of the tensor cycled so that streams and outputs come from DRAM;
+    e2e    = the same through eoq_parallel_decode with host buffers (64-row tasks; payloads copied in and symbols
+             copied out inside the timed region);
+    beside them: the reference's own CUDA kernel (compiled from its source into oracle/_ref) on the same device
+    buffers, and its C decoder (eoq_parallel_decode.c) on the host cores."""
+    import ctypes as C
+    import torch
+    from eoq_quantization_b200 import _lib
+    from eoq_quantization_b200.core import rans_blocked as RB
+    from eoq_quantization_b200.core.rans import _normalize_frequencies
+    torch.cuda.set_device(0)
+    lib = _lib.lib()
+    peak, peak_src = measured_peak()
+    n = k = 4096
+    sym4, _ = make_layer(n, k, 3)
+    cases = [("config1_4096x4096_int4_block4096_p12", sym4.ravel(), 15, 4096, 12),
+             ("eoq_default_4096x4096_int4_block256_p14", sym4.ravel(), 15, 256, 14),
+             ("gguf_bytes_8Mi_block256_p16", (sym4[:, 0::2] | (sym4[:, 1::2] << 4)).ravel(), 256, 256, 16)]
+    ref_cuda = ref_c = None
+    if not args.no_cpu_baseline:
+        try:
+            from oracle import oracle as O
+            ref_cuda = O.RefCuda() if O.RefCuda.available() else None
+            ref_c = O.RefC() if O.RefC.available() else None
+        except Exception:
+            pass
+    copies = 8
+    for name, sym, alphabet, block, p in cases:
+        sym = np.ascontiguousarray(sym)
+        total = sym.size
+        data = RB.BlockedRANSEncoder(block_size=block, precision_bits=p).encode(sym.astype(np.int64), alphabet)
+        freq, cdf = _normalize_frequencies(np.asarray(data.freq_table, np.int64), p)
+        offs = np.asarray(data.block_offsets, np.uint32)
+        sizes = np.diff(np.append(offs.astype(np.int64), len(data.compressed_blocks))).astype(np.uint32)
+        info = np.zeros((1 << p, 4), np.uint16)                       # {symbol, freq, cum, pad} per slot
+        for s_ in range(alphabet):
+            info[cdf[s_]:cdf[s_ + 1]] = (s_, freq[s_] & 0xFFFF, cdf[s_], 0)
+        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.uint8).reshape(-1).copy()).cuda()
+        d_streams = [dev(np.frombuffer(data.compressed_blocks, np.uint8)) for _ in range(copies)]
+        d_outs = [torch.empty(total, dtype=torch.uint8, device="cuda") for _ in range(copies)]
+        d_offs, d_sizes, d_info = dev(offs), dev(sizes), dev(info)
+        st = torch.cuda.current_stream().cuda_stream
+        it = {"i": 0}
+
+        def ours():
+            i = it["i"] % copies; it["i"] += 1
+            rc = lib.eoq_cuda_decode_tensor_device(d_streams[i].data_ptr(), d_offs.data_ptr(), d_sizes.data_ptr(), d_info.data_ptr(),
+                                                   d_outs[i].data_ptr(), data.num_blocks, block, total, p, st)
+            assert rc == 0
+
+        def theirs():
+            i = it["i"] % copies; it["i"] += 1
+            assert ref_cuda.decode_device(d_streams[i].data_ptr(), d_offs.data_ptr(), d_sizes.data_ptr(), d_info.data_ptr(),
+                                          d_outs[i].data_ptr(), data.num_blocks, block, total, p, st) == 0
+
+        def timed(fn, reps):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / reps
+        reps = max(3, min(args.steps, 50))
+        ms = timed(ours, reps)
+        want = torch.from_numpy(sym.astype(np.uint8)).cuda()
+        assert all(torch.equal(o, want) for o in d_outs), "decoded symbols differ from the encoder's input"
+        line = {"metric": "wire-format rANS decode, symbols/s", "unit": "Gsym/s", "n_gpus": 1, "steps": reps, "warmup": 3,
+                "higher_is_better": True, "data": "synthetic", "dtype": "u32 rANS state, byte renormalisation, u8 symbols",
+                "config": {"workload": name, "symbols": int(total), "alphabet": alphabet, "block": block, "precision_bits": p,
+                           "l2": f"{copies} copies of stream and output cycled (> L2)"},
+                "value": total / (ms * 1e-3) / 1e9, "ms_per_step": ms, "compressed_bytes": len(data.compressed_blocks),
+                "bits_per_symbol": len(data.compressed_blocks) * 8 / total, "gpu_launches": reps}
+        traffic = len(data.compressed_blocks) + total + 8 * data.num_blocks
+        line["roofline"] = {"bound": "hbm", "kernel": "decode_v1_lanes_kernel", "achieved": traffic / (ms * 1e-3) / 1e9, "peak": peak,
+                            "unit": "GB/s", "frac": traffic / (ms * 1e-3) / 1e9 / peak, "peak_source": peak_src, "traffic": None,
+                            "algorithmic_bytes_per_launch": traffic, "note": "stream + block offsets and sizes read, one byte per symbol written"}
+        if ref_cuda is not None:
+            for o in d_outs:
+                o.zero_()
+            ms_ref = timed(theirs, max(3, reps // 4))
+            assert all(torch.equal(o, want) for o in d_outs), "the reference kernel's symbols differ"
+            line["reference_cuda_kernel"] = {"kernel": "eoq_rans_decode_blocks_kernel (llamacpp_integration/eoq_cuda_decompress.cu:235-302)",
+                                             "ms": ms_ref, "gsym_per_s": total / (ms_ref * 1e-3) / 1e9, "speedup": ms_ref / ms}
+        # end to end: host payloads -> eoq_parallel_decode -> host symbols, 64-row tasks
+        rows_per_task = 64
+        per = rows_per_task * (total // n)
+        tasks_n = total // per
+        tasks = (_lib.DecodeTask * tasks_n)()
+        keep = []
+        for i in range(tasks_n):
+            d = RB.BlockedRANSEncoder(block_size=block, precision_bits=p).encode(sym[i * per:(i + 1) * per].astype(np.int64), alphabet)
+            f_, _c = _normalize_frequencies(np.asarray(d.freq_table, np.int64), p)
+            body = f_.astype("<u2").tobytes() + np.asarray(d.block_offsets, "<u4").tobytes() + bytes(d.compressed_blocks)
+            h = _lib.TensorHeader(0, d.num_blocks, alphabet, p, block, len(body), per)
+            buf = (C.c_ubyte * len(body)).from_buffer_copy(body)
+            out = np.zeros(per, np.uint8)
+            keep.append((h, buf, out))
+            tasks[i].header = C.pointer(h); tasks[i].compressed_data = C.cast(buf, C.c_void_p)
+            tasks[i].compressed_size = len(body); tasks[i].output = out.ctypes.data; tasks[i].output_capacity = per
+        h2d = sum(len(b) for _, b, _ in keep)
+        popts = _lib.ParallelOpts(8, _lib.PARALLEL_PROGRESS_FN(), None)
+        for _ in range(2):
+            assert lib.eoq_parallel_decode(tasks, tasks_n, C.byref(popts)) == 0
+        t0 = time.perf_counter()
+        e2e_reps = 5
+        for _ in range(e2e_reps):
+            assert lib.eoq_parallel_decode(tasks, tasks_n, C.byref(popts)) == 0
+        e2e_s = (time.perf_counter() - t0) / e2e_reps
+        assert all(np.array_equal(o, sym[i * per:(i + 1) * per].astype(np.uint8)) for i, (_, _, o) in enumerate(keep))
+        line["e2e"] = {"value": total / e2e_s / 1e9, "unit": "Gsym/s", "ms_per_step": e2e_s * 1e3, "h2d_bytes_per_step": h2d,
+                       "d2h_bytes_per_step": int(total), "tasks": tasks_n, "note": "eoq_parallel_decode, pageable host buffers"}
+        if ref_c is not None:
+            items = [(np.array([getattr(h, f) for f, _ in _lib.TensorHeader._fields_], np.uint32), bytes(b)) for h, b, _ in keep]
+            rc, outs, dt = ref_c.parallel_decode(items, 0)
+            rc, outs, dt = ref_c.parallel_decode(items, 0)
+            assert rc == 0 and all(np.array_equal(o, sym[i * per:(i + 1) * per].astype(np.uint8)) for i, o in enumerate(outs))
+            line["cpu_baseline"] = {"value": total / dt / 1e9, "unit": "Gsym/s", "cores": ref_c.threads(), "kind": "reference",
+                                    "sample": f"the whole tensor once: eoq_parallel_decode.c over {tasks_n} tasks", "ms": dt * 1e3}
+        print(json.dumps(line), flush=True)
+        del d_streams, d_outs
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -818,7 +983,8 @@ def main():
     ap.add_argument("--eager", action="store_true", help="plain launches instead of CUDA graphs (for profilers)")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: how output slices are exchanged")
     ap.add_argument("--no-pdl", action="store_true", help="plain launches instead of programmatic dependent launches")
-    ap.add_argument("--workload", default="mlp_pair", choices=["mlp_pair", "decode_dequant", "polar_q5", "llama7b_step", "prefill_gemm"])
+    ap.add_argument("--workload", default="mlp_pair",
+                    choices=["mlp_pair", "decode_dequant", "polar_q5", "llama7b_step", "prefill_gemm", "wire_decode"])
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
                     help="pass a knob to eoq_b200_tune (e.g. gemv_pairs=0: the one-tile-per-warp ring kernel)")
     args = ap.parse_args()
@@ -833,16 +999,16 @@ def main():
         _lib.lib().eoq_b200_tune(b"pdl", 0)
     if args.workload == "llama7b_step":
         return run_llama_step(args)
+    if args.workload == "wire_decode":
+        return run_wire_decode(args)
     if args.workload != "mlp_pair":
         args.steps = min(args.steps, 50)
         return run_aux(args)
+    args.warmup = max(args.warmup, 3)                       # the same warm-up rule in both arms
     if args.impl == "reference":
-        if args.steps > 20:
-            args.steps = 20
-        args.warmup = min(args.warmup, 3)
+        args.steps = min(args.steps, 200)                   # ~0.13 s per step on 16 cores: the run stays within a minute
         run_reference_arm(args)
     else:
-        args.warmup = max(args.warmup, 3)
         run_gpu_arm(args)
 
 

@@ -100,55 +100,180 @@ eoq_error_t table_from_u16(const uint16_t *raw16, uint32_t alphabet, uint32_t p,
     return EOQ_OK;
 }
 
-// Device-side copy of one tensor's inputs, ready to launch.
-struct StagedTensor {
-    DeviceBuf stream, offsets, sizes, table, out;
-    Payload pl;
-    bool own_out = true;
-    uint8_t *d_out = nullptr;
+// One device allocation that serves a whole decode call (streams, block tables, frequencies, task descriptors,
+// outputs): the decode entry points make no allocation per tensor.  Allocations are kept in a small process-wide cache
+// between calls (grow-only, at most four, freed at exit), so a loader that decodes tensor after tensor allocates once.
+class DeviceArena {
+  public:
+    DeviceArena() = default;
+    DeviceArena(const DeviceArena &) = delete;
+    DeviceArena &operator=(const DeviceArena &) = delete;
+    ~DeviceArena() { release(); }
+    cudaError_t acquire(size_t bytes)
+    {
+        release();
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        {
+            std::lock_guard<std::mutex> lock(cache().mu);
+            auto &v = cache().free_list;
+            int best = -1;
+            for (int i = 0; i < (int)v.size(); i++)
+                if (v[i].dev == dev && v[i].cap >= bytes && (best < 0 || v[i].cap < v[best].cap)) best = i;
+            if (best < 0)                         // none large enough: recycle the largest of this device rather than keep both
+                for (int i = 0; i < (int)v.size(); i++)
+                    if (v[i].dev == dev && (best < 0 || v[i].cap > v[best].cap)) best = i;
+            if (best >= 0) { cur_ = v[best]; v.erase(v.begin() + best); }
+        }
+        if (cur_.p && cur_.cap < bytes) { cudaFree(cur_.p); cur_ = Block(); }
+        if (!cur_.p) {
+            const size_t cap = std::max<size_t>((bytes + (1u << 20)) & ~(size_t)((1u << 20) - 1), 4u << 20);
+            e = cudaMalloc(&cur_.p, cap);
+            if (e != cudaSuccess) { cur_ = Block(); return e; }
+            cur_.cap = cap; cur_.dev = dev;
+        }
+        return cudaSuccess;
+    }
+    void release()
+    {
+        if (!cur_.p) return;
+        std::lock_guard<std::mutex> lock(cache().mu);
+        if (cache().free_list.size() < 4) cache().free_list.push_back(cur_);
+        else cudaFree(cur_.p);
+        cur_ = Block();
+    }
+    uint8_t *base() const { return static_cast<uint8_t *>(cur_.p); }
+
+  private:
+    struct Block { void *p = nullptr; size_t cap = 0; int dev = 0; };
+    struct Cache { std::mutex mu; std::vector<Block> free_list; };
+    static Cache &cache() { static Cache *c = new Cache(); return *c; }      // never destroyed: no CUDA call after main
+    Block cur_;
 };
 
-eoq_error_t stage_tensor(const eoq_tensor_header_t *h, const uint8_t *comp, size_t comp_size, size_t out_cap,
-                         uint8_t *d_out_or_null, cudaStream_t st, StagedTensor &s)
+// One tensor of a decode call.
+struct V1Job {
+    Payload pl;                         // validated host views of the payload
+    std::vector<uint32_t> freq, cdf;    // normalised table
+    uint32_t out_elem_bytes = 1;
+    void *host_out = nullptr;           // where the symbols go on the host, or
+    void *dev_out = nullptr;            // the caller's device buffer
+    std::vector<uint8_t> own_payload;   // batch context: the caller's host bytes, kept until launch
+    // placement inside the arena
+    size_t at_stream = 0, at_offsets = 0, at_sizes = 0, at_freq = 0, at_table = 0, at_out = 0;
+    bool lanes = false;
+};
+
+eoq_error_t job_from_payload(const eoq_tensor_header_t *h, const uint8_t *comp, size_t comp_size, size_t out_cap, V1Job &j)
 {
-    eoq_error_t rc = parse_payload(h, comp, comp_size, out_cap, s.pl);
+    eoq_error_t rc = parse_payload(h, comp, comp_size, out_cap, j.pl);
     if (rc != EOQ_OK) return rc;
-    std::vector<V1Table> table;
-    rc = table_from_u16(s.pl.freq, s.pl.alphabet, s.pl.p, table);
-    if (rc != EOQ_OK) return rc;
-    if (!have_device()) return EOQ_ERR_CUDA;
-    const Payload &pl = s.pl;
-    if (s.stream.alloc(pl.stream_bytes) != cudaSuccess || s.offsets.alloc((size_t)pl.nblocks * 4) != cudaSuccess ||
-        s.sizes.alloc((size_t)pl.nblocks * 4) != cudaSuccess || s.table.alloc(table.size() * sizeof(V1Table)) != cudaSuccess)
-        return EOQ_ERR_ALLOC;
-    if (d_out_or_null) { s.own_out = false; s.d_out = d_out_or_null; }
-    else { if (s.out.alloc(pl.total) != cudaSuccess) return EOQ_ERR_ALLOC; s.d_out = s.out.as<uint8_t>(); }
-    CU_TRY(cudaMemcpyAsync(s.stream.p, pl.stream, pl.stream_bytes, cudaMemcpyHostToDevice, st));
-    CU_TRY(cudaMemcpyAsync(s.offsets.p, pl.offsets.data(), (size_t)pl.nblocks * 4, cudaMemcpyHostToDevice, st));
-    CU_TRY(cudaMemcpyAsync(s.sizes.p, pl.sizes.data(), (size_t)pl.nblocks * 4, cudaMemcpyHostToDevice, st));
-    CU_TRY(cudaMemcpyAsync(s.table.p, table.data(), table.size() * sizeof(V1Table), cudaMemcpyHostToDevice, st));
-    // the pageable sources above are consumed before cudaMemcpyAsync returns
-    return EOQ_OK;
+    std::vector<uint32_t> raw(j.pl.alphabet);
+    for (uint32_t s = 0; s < j.pl.alphabet; s++) { uint16_t v; std::memcpy(&v, j.pl.freq + s, 2); raw[s] = v; }
+    return normalize_reference(raw.data(), j.pl.alphabet, j.pl.p, j.freq, j.cdf);
 }
 
-eoq_error_t launch_staged(const StagedTensor &s, cudaStream_t st)
+// Decode `n` validated jobs: one arena, one upload of all metadata, the streams copied in, ONE launch of the lane kernel
+// over every job it serves (others run the one-thread-per-block kernel), results copied to the host buffers that ask
+// for it.  Asynchronous on `st`; the arena must stay acquired until the stream has been synchronised.
+eoq_error_t decode_jobs(V1Job **jobs, size_t n, cudaStream_t st, DeviceArena &arena)
 {
-    const Payload &pl = s.pl;
-    int e = launch_decode_v1(s.stream.as<uint8_t>(), s.offsets.as<uint32_t>(), s.sizes.as<uint32_t>(), s.table.as<V1Table>(),
-                             s.d_out, 1, pl.nblocks, pl.block, pl.total, pl.p, st);
-    if (e != 0) { std::fprintf(stderr, "eoq_b200: decode launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
+    if (n == 0) return EOQ_OK;
+    if (!have_device()) return EOQ_ERR_CUDA;
+    auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    // layout: [metadata blob: per job offsets, sizes, freq (or slot table); task descriptors; CTA map][streams][outputs]
+    std::vector<V1Task> tasks;
+    std::vector<size_t> task_job;
+    size_t meta = 0;
+    for (size_t i = 0; i < n; i++) {
+        V1Job &j = *jobs[i];
+        j.at_offsets = meta; meta = up(meta + (size_t)j.pl.nblocks * 4);
+        j.at_sizes = meta;   meta = up(meta + (size_t)j.pl.nblocks * 4);
+        j.at_freq = meta;    meta = up(meta + (size_t)j.pl.alphabet * 4);
+        V1Task t = {};
+        t.nblocks = j.pl.nblocks; t.block_size = j.pl.block; t.total = j.pl.total; t.p = j.pl.p; t.alphabet = j.pl.alphabet;
+        t.out_elem_bytes = j.out_elem_bytes;
+        t.stream = reinterpret_cast<const uint8_t *>((uintptr_t)0);       // alignment is that of the arena slice: always 256
+        j.lanes = v1_lanes_enabled() && v1_task_prepare(t);
+        if (j.lanes) { tasks.push_back(t); task_job.push_back(i); }
+        else { j.at_table = meta; meta = up(meta + ((size_t)8 << j.pl.p)); }
+    }
+    uint32_t warps_per_cta = 1, grid = 0;
+    size_t smem = 0;
+    if (!tasks.empty()) grid = v1_plan_ctas(tasks.data(), (uint32_t)tasks.size(), warps_per_cta, smem);
+    const size_t at_tasks = meta; meta = up(meta + tasks.size() * sizeof(V1Task));
+    const size_t at_cta = meta;   meta = up(meta + (size_t)grid * 4);
+    size_t total = meta;
+    for (size_t i = 0; i < n; i++) {
+        V1Job &j = *jobs[i];
+        j.at_stream = total; total = up(total + j.pl.stream_bytes + 16);
+        if (!j.dev_out) { j.at_out = total; total = up(total + (size_t)j.pl.total * j.out_elem_bytes + 32); }
+    }
+    if (arena.acquire(total) != cudaSuccess) return EOQ_ERR_ALLOC;
+    uint8_t *d = arena.base();
+    std::vector<uint8_t> blob(meta, 0);
+    for (size_t i = 0; i < n; i++) {
+        V1Job &j = *jobs[i];
+        std::memcpy(blob.data() + j.at_offsets, j.pl.offsets.data(), (size_t)j.pl.nblocks * 4);
+        std::memcpy(blob.data() + j.at_sizes, j.pl.sizes.data(), (size_t)j.pl.nblocks * 4);
+        std::memcpy(blob.data() + j.at_freq, j.freq.data(), (size_t)j.pl.alphabet * 4);
+        if (!j.lanes) {
+            std::vector<V1Table> table;
+            make_v1_table(j.freq, j.cdf, j.pl.p, table);
+            std::memcpy(blob.data() + j.at_table, table.data(), table.size() * sizeof(V1Table));
+        }
+    }
+    std::vector<uint32_t> cta_task(grid);
+    for (size_t k = 0; k < tasks.size(); k++) {
+        V1Job &j = *jobs[task_job[k]];
+        V1Task &t = tasks[k];
+        t.stream = d + j.at_stream; t.offsets = reinterpret_cast<const uint32_t *>(d + j.at_offsets);
+        t.sizes = reinterpret_cast<const uint32_t *>(d + j.at_sizes); t.freq = reinterpret_cast<const uint32_t *>(d + j.at_freq);
+        t.table = nullptr; t.out = j.dev_out ? j.dev_out : d + j.at_out;
+        const uint32_t last = k + 1 < tasks.size() ? tasks[k + 1].first_cta : grid;
+        for (uint32_t c = t.first_cta; c < last; c++) cta_task[c] = (uint32_t)k;
+    }
+    if (!tasks.empty()) {
+        std::memcpy(blob.data() + at_tasks, tasks.data(), tasks.size() * sizeof(V1Task));
+        std::memcpy(blob.data() + at_cta, cta_task.data(), (size_t)grid * 4);
+    }
+    // pageable sources are consumed before cudaMemcpyAsync returns
+    CU_TRY(cudaMemcpyAsync(d, blob.data(), meta, cudaMemcpyHostToDevice, st));
+    for (size_t i = 0; i < n; i++) {
+        V1Job &j = *jobs[i];
+        if (j.pl.stream_bytes) CU_TRY(cudaMemcpyAsync(d + j.at_stream, j.pl.stream, j.pl.stream_bytes, cudaMemcpyHostToDevice, st));
+    }
+    if (!tasks.empty()) {
+        int e = launch_decode_v1_lanes(reinterpret_cast<const V1Task *>(d + at_tasks), reinterpret_cast<const uint32_t *>(d + at_cta), grid,
+                                       warps_per_cta, smem, st);
+        if (e != 0) { std::fprintf(stderr, "eoq_b200: decode launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
+    }
+    for (size_t i = 0; i < n; i++) {
+        V1Job &j = *jobs[i];
+        void *out = j.dev_out ? j.dev_out : d + j.at_out;
+        if (!j.lanes) {
+            int e = launch_decode_v1(d + j.at_stream, reinterpret_cast<const uint32_t *>(d + j.at_offsets),
+                                     reinterpret_cast<const uint32_t *>(d + j.at_sizes), reinterpret_cast<const V1Table *>(d + j.at_table), out,
+                                     (int)j.out_elem_bytes, j.pl.nblocks, j.pl.block, j.pl.total, j.pl.p, j.pl.alphabet, st);
+            if (e != 0) { std::fprintf(stderr, "eoq_b200: decode launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
+        }
+        if (j.host_out) CU_TRY(cudaMemcpyAsync(j.host_out, out, (size_t)j.pl.total * j.out_elem_bytes, cudaMemcpyDeviceToHost, st));
+    }
     return EOQ_OK;
 }
 
 eoq_error_t decode_host_to_host(const eoq_tensor_header_t *h, const uint8_t *comp, size_t comp_size, void *output,
                                 size_t out_cap, cudaStream_t st)
 {
-    StagedTensor s;
-    eoq_error_t rc = stage_tensor(h, comp, comp_size, out_cap, nullptr, st, s);
+    V1Job job;
+    eoq_error_t rc = job_from_payload(h, comp, comp_size, out_cap, job);
     if (rc != EOQ_OK) return rc;
-    rc = launch_staged(s, st);
+    job.host_out = output;
+    V1Job *one = &job;
+    DeviceArena arena;
+    rc = decode_jobs(&one, 1, st, arena);
     if (rc != EOQ_OK) return rc;
-    CU_TRY(cudaMemcpyAsync(output, s.d_out, s.pl.total, cudaMemcpyDeviceToHost, st));
     CU_TRY(cudaStreamSynchronize(st));
     return EOQ_OK;
 }
@@ -212,67 +337,59 @@ extern "C" int eoq_decode_tensor(const eoq_tensor_header_t *header, const uint8_
     return (int)eoq_decode_tensor_v2(header, compressed, header->compressed_size, output, header->uncompressed_size, nullptr);
 }
 
-// Tensors are pipelined over a few CUDA streams: while one tensor decodes, the
-// next one's payload is uploaded.  A tensor counts as done, and the progress
-// callback runs (on the calling thread, so calls are serialised), when its
-// result has landed in the caller's output buffer.
+// Tensors are decoded in groups: the tasks of a group are validated on the host, uploaded together and decoded by ONE
+// kernel launch (every rANS block of every tensor of the group is a lane of that launch); their results are copied
+// back in task order, and the progress callback runs on the calling thread after each, so calls are serialised and
+// count up by one.  A group holds opts->num_threads tasks (the number of tasks the reference would have in flight),
+// or 64 when that is 0.  After a cancel request the group in flight completes and later groups are not started.
 extern "C" eoq_error_t eoq_parallel_decode(eoq_decode_task_t *tasks, int num_tasks, const eoq_parallel_opts_t *opts)
 {
     if (!tasks && num_tasks > 0) return EOQ_ERR_NULL_PTR;
     if (num_tasks <= 0) return EOQ_OK;
-    int lanes = opts ? opts->num_threads : 0;
-    if (lanes <= 0) lanes = 4;
-    lanes = std::min(std::min(lanes, num_tasks), 8);
+    int group = opts ? opts->num_threads : 0;
+    group = group <= 0 ? 64 : std::min(group, 256);
     eoq_parallel_progress_fn cb = opts ? opts->progress_cb : nullptr;
     void *ud = opts ? opts->progress_ud : nullptr;
-
-    struct Slot { cudaStream_t st = nullptr; std::unique_ptr<StagedTensor> staged; int task = -1; };
-    std::vector<Slot> slots((size_t)lanes);
-    bool streams_ok = have_device();
-    if (streams_ok)
-        for (auto &s : slots)
-            if (cudaStreamCreateWithFlags(&s.st, cudaStreamNonBlocking) != cudaSuccess) { streams_ok = false; break; }
+    cudaStream_t st = nullptr;
+    const bool device_ok = have_device() && cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) == cudaSuccess;
 
     int done = 0;
     bool cancelled = false;
-    auto retire = [&](Slot &s) {
-        if (s.task < 0) return;
-        eoq_decode_task_t &t = tasks[s.task];
-        if (t.result == EOQ_OK && s.staged && cudaStreamSynchronize(s.st) != cudaSuccess) t.result = EOQ_ERR_CUDA;
-        s.staged.reset();
-        s.task = -1;
-        done++;
-        if (cb && !cancelled && cb(done, num_tasks, ud)) cancelled = true;
-    };
-
-    for (int i = 0; i < num_tasks; i++) {
-        Slot &s = slots[(size_t)(i % lanes)];
-        retire(s);
-        eoq_decode_task_t &t = tasks[i];
-        if (cancelled) { t.result = EOQ_ERR_THREAD; continue; }      // eoq_parallel_decode.c:72-82
-        t.task_index = i;
-        s.task = i;
-        if (!t.header || !t.compressed_data || !t.output) { t.result = EOQ_ERR_NULL_PTR; continue; }
-        if (t.header->uncompressed_size == 0) { t.result = EOQ_OK; continue; }
-        s.staged.reset(new StagedTensor());
-        t.result = streams_ok ? stage_tensor(t.header, t.compressed_data, t.compressed_size, t.output_capacity, nullptr, s.st, *s.staged)
-                              : parse_payload(t.header, t.compressed_data, t.compressed_size, t.output_capacity, s.staged->pl);
-        if (t.result == EOQ_OK && !streams_ok) t.result = EOQ_ERR_CUDA;
-        if (t.result == EOQ_OK) t.result = launch_staged(*s.staged, s.st);
-        if (t.result == EOQ_OK &&
-            cudaMemcpyAsync(t.output, s.staged->d_out, s.staged->pl.total, cudaMemcpyDeviceToHost, s.st) != cudaSuccess)
-            t.result = EOQ_ERR_CUDA;
-        if (t.result != EOQ_OK) s.staged.reset();
+    DeviceArena arena;
+    for (int g0 = 0; g0 < num_tasks; g0 += group) {
+        const int g1 = std::min(num_tasks, g0 + group);
+        if (cancelled) {
+            for (int i = g0; i < g1; i++) tasks[i].result = EOQ_ERR_THREAD;          // eoq_parallel_decode.c:72-82
+            continue;
+        }
+        std::vector<std::unique_ptr<V1Job>> jobs;
+        std::vector<V1Job *> live;
+        std::vector<int> live_task;
+        for (int i = g0; i < g1; i++) {
+            eoq_decode_task_t &t = tasks[i];
+            t.task_index = i;
+            if (!t.header || !t.compressed_data || !t.output) { t.result = EOQ_ERR_NULL_PTR; continue; }
+            if (t.header->uncompressed_size == 0) { t.result = EOQ_OK; continue; }
+            std::unique_ptr<V1Job> j(new V1Job());
+            t.result = job_from_payload(t.header, t.compressed_data, t.compressed_size, t.output_capacity, *j);
+            if (t.result == EOQ_OK && !device_ok) t.result = EOQ_ERR_CUDA;
+            if (t.result != EOQ_OK) continue;
+            j->host_out = t.output;
+            live.push_back(j.get());
+            live_task.push_back(i);
+            jobs.push_back(std::move(j));
+        }
+        eoq_error_t rc = live.empty() ? EOQ_OK : decode_jobs(live.data(), live.size(), st, arena);
+        if (rc == EOQ_OK && !live.empty() && cudaStreamSynchronize(st) != cudaSuccess) rc = EOQ_ERR_CUDA;
+        if (rc != EOQ_OK)
+            for (int i : live_task) tasks[i].result = rc;
+        for (int i = g0; i < g1; i++) {
+            done++;
+            if (cb && !cancelled && cb(done, num_tasks, ud)) cancelled = true;
+        }
     }
-    // drain in task order so `done` counts up as the reference's does
-    for (int k = 0; k < lanes; k++) {
-        int oldest = -1;
-        for (int j = 0; j < lanes; j++)
-            if (slots[(size_t)j].task >= 0 && (oldest < 0 || slots[(size_t)j].task < slots[(size_t)oldest].task)) oldest = j;
-        if (oldest < 0) break;
-        retire(slots[(size_t)oldest]);
-    }
-    for (auto &s : slots) if (s.st) cudaStreamDestroy(s.st);
+    arena.release();
+    if (st) cudaStreamDestroy(st);
 
     for (int i = 0; i < num_tasks; i++)
         if (tasks[i].result != EOQ_OK) return tasks[i].result;        // eoq_parallel_decode.c:290-300
@@ -381,7 +498,11 @@ extern "C" int eoq_cuda_decode_tensor_device(const uint8_t *d_compressed_stream,
 }
 
 namespace {
-struct BatchImpl { std::vector<std::unique_ptr<StagedTensor>> tensors; };
+struct BatchImpl {
+    std::vector<std::unique_ptr<V1Job>> tensors;
+    DeviceArena arena;
+    bool launched = false;
+};
 BatchImpl *batch_impl(eoq_cuda_batch_ctx_t *ctx, bool make)
 {
     if (!ctx->impl && make) ctx->impl = new (std::nothrow) BatchImpl();
@@ -414,22 +535,26 @@ extern "C" int eoq_cuda_batch_prepare_tensor(eoq_cuda_batch_ctx_t *ctx, const eo
     if (header->uncompressed_size == 0) return 0;
     BatchImpl *impl = batch_impl(ctx, true);
     if (!impl) return -1;
-    std::unique_ptr<StagedTensor> s(new StagedTensor());
-    if (stage_tensor(header, compressed_host, header->compressed_size, header->uncompressed_size, d_output,
-                     reinterpret_cast<cudaStream_t>(ctx->stream), *s) != EOQ_OK)
-        return -1;
-    impl->tensors.push_back(std::move(s));
+    // the caller may release its host buffer after this call (the reference uploads here): keep a copy until launch
+    std::unique_ptr<V1Job> j(new V1Job());
+    j->own_payload.assign(compressed_host, compressed_host + header->compressed_size);
+    if (job_from_payload(header, j->own_payload.data(), header->compressed_size, header->uncompressed_size, *j) != EOQ_OK) return -1;
+    j->dev_out = d_output;
+    impl->tensors.push_back(std::move(j));
     ctx->n_tensors = (uint32_t)impl->tensors.size();
     return 0;
 }
 
+// One kernel launch decodes every prepared tensor (eoq_cuda_decompress.cu:985-1003 launches one kernel per tensor).
 extern "C" int eoq_cuda_batch_launch(eoq_cuda_batch_ctx_t *ctx)
 {
     if (!ctx) return -1;
     BatchImpl *impl = batch_impl(ctx, false);
-    if (!impl) return 0;
-    for (auto &s : impl->tensors)
-        if (launch_staged(*s, reinterpret_cast<cudaStream_t>(ctx->stream)) != EOQ_OK) return -1;
+    if (!impl || impl->tensors.empty() || impl->launched) return 0;
+    std::vector<V1Job *> live;
+    for (auto &t : impl->tensors) live.push_back(t.get());
+    if (decode_jobs(live.data(), live.size(), reinterpret_cast<cudaStream_t>(ctx->stream), impl->arena) != EOQ_OK) return -1;
+    impl->launched = true;
     return 0;
 }
 
@@ -438,8 +563,8 @@ extern "C" int eoq_cuda_batch_sync_and_free(eoq_cuda_batch_ctx_t *ctx)
     if (!ctx) return -1;
     int rc = 0;
     BatchImpl *impl = batch_impl(ctx, false);
-    if (impl && !impl->tensors.empty() && cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(ctx->stream)) != cudaSuccess) rc = -1;
-    delete impl;                   // frees the staging copies; outputs belong to the caller
+    if (impl && impl->launched && cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(ctx->stream)) != cudaSuccess) rc = -1;
+    delete impl;                   // releases the staging arena; outputs belong to the caller
     ctx->impl = nullptr;
     ctx->n_tensors = 0;
     return rc;
@@ -481,28 +606,22 @@ extern "C" eoq_error_t eoq_b200_decode_blocked(const uint32_t *freq, uint32_t al
         if (sizes[b] && 1u + data[lo] > sizes[b]) return EOQ_ERR_CORRUPT_STREAM;
         if (sizes[b] && data[lo] > 4) return EOQ_ERR_UNSUPPORTED;                  // state wider than 32 bits
     }
-    std::vector<V1Table> table;
-    make_v1_table(f, cdf, precision_bits, table);
     if (!have_device()) return EOQ_ERR_CUDA;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    DeviceBuf d_data, d_off, d_sizes, d_table, d_out;
-    if (d_data.alloc(data_len) != cudaSuccess || d_off.alloc((size_t)num_blocks * 4) != cudaSuccess ||
-        d_sizes.alloc((size_t)num_blocks * 4) != cudaSuccess || d_table.alloc(table.size() * sizeof(V1Table)) != cudaSuccess)
-        return EOQ_ERR_ALLOC;
-    void *dst = out;
-    if (!out_on_device) {
-        if (d_out.alloc((size_t)num_symbols * out_elem_bytes) != cudaSuccess) return EOQ_ERR_ALLOC;
-        dst = d_out.p;
-    }
-    CU_TRY(cudaMemcpyAsync(d_data.p, data, data_len, cudaMemcpyHostToDevice, st));
-    CU_TRY(cudaMemcpyAsync(d_off.p, offsets, (size_t)num_blocks * 4, cudaMemcpyHostToDevice, st));
-    CU_TRY(cudaMemcpyAsync(d_sizes.p, sizes.data(), (size_t)num_blocks * 4, cudaMemcpyHostToDevice, st));
-    CU_TRY(cudaMemcpyAsync(d_table.p, table.data(), table.size() * sizeof(V1Table), cudaMemcpyHostToDevice, st));
-    int e = launch_decode_v1(d_data.as<uint8_t>(), d_off.as<uint32_t>(), d_sizes.as<uint32_t>(), d_table.as<V1Table>(), dst,
-                             out_elem_bytes, num_blocks, block_size, num_symbols, precision_bits, st);
-    if (e != 0) return EOQ_ERR_CUDA;
-    if (!out_on_device) CU_TRY(cudaMemcpyAsync(out, dst, (size_t)num_symbols * out_elem_bytes, cudaMemcpyDeviceToHost, st));
-    CU_TRY(cudaStreamSynchronize(st));   // the staging buffers are freed on return
+    V1Job job;
+    job.pl.alphabet = alphabet; job.pl.p = precision_bits; job.pl.block = block_size; job.pl.total = num_symbols;
+    job.pl.nblocks = num_blocks; job.pl.stream = data; job.pl.stream_bytes = (uint32_t)data_len;
+    job.pl.offsets.assign(offsets, offsets + num_blocks);
+    job.pl.sizes = std::move(sizes);
+    job.freq = std::move(f);
+    job.cdf = std::move(cdf);
+    job.out_elem_bytes = (uint32_t)out_elem_bytes;
+    if (out_on_device) job.dev_out = out; else job.host_out = out;
+    V1Job *one = &job;
+    DeviceArena arena;
+    eoq_error_t rc = decode_jobs(&one, 1, st, arena);
+    if (rc != EOQ_OK) return rc;
+    CU_TRY(cudaStreamSynchronize(st));   // the staging arena goes back to the cache on return
     return EOQ_OK;
 }
 
@@ -1142,6 +1261,7 @@ extern "C" int eoq_b200_tune(const char *key, int value)
     if (std::strcmp(key, "gemm_warps") == 0) { set_gemm_warps(value); return 0; }
     if (std::strcmp(key, "pdl") == 0) { set_pdl(value); return 0; }
     if (std::strcmp(key, "gemv_pairs") == 0) { set_gemv_pairs(value); return 0; }
+    if (std::strcmp(key, "v1_lanes") == 0) { set_v1_lanes(value); return 0; }
     return -1;
 }
 

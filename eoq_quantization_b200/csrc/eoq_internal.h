@@ -146,7 +146,28 @@ int launch_gemv(const GemvArgs &a, uint32_t G, uint32_t bits, uint32_t kind, voi
 int launch_decode_tiles(const DecodeArgs &a, uint32_t G, uint32_t bits, uint32_t kind, void *stream);
 int launch_decode_v1(const uint8_t *d_stream, const uint32_t *d_offsets, const uint32_t *d_sizes,
                      const V1Table *d_table, void *d_out, int out_elem_bytes, uint32_t nblocks,
-                     uint32_t block_size, uint32_t total, uint32_t p, void *stream);
+                     uint32_t block_size, uint32_t total, uint32_t p, uint32_t alphabet, void *stream);
+void set_v1_lanes(int v);
+bool v1_lanes_enabled();
+
+// One tensor of a batched wire-format decode (decode_v1_lanes_kernel); lives in device memory during the launch.
+// All pointers are device pointers.  Either `freq` (normalised frequencies, u32 x alphabet: the kernel builds its
+// table from them) or `table` (a caller's slot table in the reference's {symbol, freq, cum} form) is set.
+struct V1Task {
+    const uint8_t  *stream;
+    const uint32_t *offsets, *sizes;   // per block: first byte in `stream`, byte count
+    const uint32_t *freq;
+    const void     *table;
+    void           *out;
+    uint32_t nblocks, block_size, total, p, alphabet, out_elem_bytes;
+    uint32_t sym_bits, packed, first_cta, pad_;   // filled by v1_task_prepare / v1_plan_ctas
+};
+static_assert(sizeof(V1Task) % 4 == 0 && sizeof(V1Task) <= 256 * 4, "copied into shared memory one word per thread");
+bool   v1_task_prepare(V1Task &t);
+size_t v1_task_smem(const V1Task &t, uint32_t warps);
+uint32_t v1_plan_ctas(V1Task *tasks, uint32_t ntasks, uint32_t &warps_per_cta, size_t &smem);
+int launch_decode_v1_lanes(const V1Task *d_tasks, const uint32_t *d_cta_task, uint32_t grid, uint32_t warps_per_cta, size_t smem,
+                           void *stream);
 int launch_decode_v1_syminfo(const uint8_t *d_stream, const uint32_t *d_offsets, const uint32_t *d_sizes,
                              const eoq_sym_info_packed *d_info, uint8_t *d_out, uint32_t nblocks,
                              uint32_t block_size, uint32_t total, uint32_t p, void *stream);

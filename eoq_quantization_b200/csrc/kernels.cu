@@ -908,9 +908,10 @@ __host__ __device__ inline uint32_t pair_region_bytes(uint32_t stage, uint32_t m
     // they are) and its 16-column sums
     return 2u * stage + 128u + ((max_ncols * bt * xbytes + (max_ncols / 16u) * bt * 4u + 127u) & ~127u);
 }
+constexpr uint32_t kPairJobBytes = 512;    // sixteen 32-byte notices "this warp adds up a pair of row blocks and wants help"
 static size_t pair_smem_bytes(uint32_t p, uint32_t bt, uint32_t stage, uint32_t max_ncols, uint32_t warps, uint32_t xbytes = 4)
 {
-    return ((size_t)4 << p) + 128 + (size_t)warps * pair_region_bytes(stage, max_ncols, bt, xbytes);
+    return ((size_t)4 << p) + 128 + kPairJobBytes + (size_t)warps * pair_region_bytes(stage, max_ncols, bt, xbytes);
 }
 
 // Bounded wait on try_wait: the warp is suspended by the hardware between polls instead of spinning through issue
@@ -1130,7 +1131,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
     const uint32_t tab_addr = smem_addr(smem), tab_bar = tab_addr + tab_bytes;
     constexpr uint32_t kXBytes = XH ? 2u : 4u;
     const uint32_t region = pair_region_bytes(a.stage_bytes, a.max_ncols, BT, kXBytes);
-    uint8_t *mine = smem + tab_bytes + 128 + (size_t)warp * region;
+    uint32_t *jobs = reinterpret_cast<uint32_t *>(smem + tab_bytes + 128);        // [warp][8]: valid, count, slot, row0 a, row0 b, has b
+    uint8_t *mine = smem + tab_bytes + 128 + kPairJobBytes + (size_t)warp * region;
     const uint32_t stage[2] = {smem_addr(mine), smem_addr(mine) + a.stage_bytes};
     const uint32_t bars = stage[0] + 2u * a.stage_bytes;       // [chain][chunk], 8 bytes each
     float *xs = reinterpret_cast<float *>(mine + 2u * a.stage_bytes + 128);
@@ -1277,6 +1279,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
     // one pair of row blocks, whose results the CTA adds up in shared memory before anything goes to global memory.
     const uint32_t nchunks = ((npairs + kWarps * gridDim.x - 1u) / (kWarps * gridDim.x)) * gridDim.x;
     const bool narrow = ((uint64_t)(npairs + 1u) * (nchunks + 1u)) >> 32 == 0;      // the products below fit 32 bits
+    // Matrices much wider than tall: the segments of a pair of row blocks are spread over many CTAs (more than six
+    // partial rows to add up).  Then the elected warp does not poll them alone: it posts a notice and all warps of its CTA
+    // take a share of the slots (see below).  The condition is the same for every CTA of the grid.
+    const bool coop = a.pair_partials && (uint64_t)a.nseg * nchunks > 6ull * npairs;
     auto chunk_lo = [&](uint32_t t) { return narrow ? t * npairs / nchunks : (uint32_t)((uint64_t)t * npairs / nchunks); };
     auto chunk_of = [&](uint32_t qq) {
         return narrow ? ((qq + 1u) * nchunks - 1u) / npairs : (uint32_t)((((uint64_t)qq + 1u) * nchunks - 1u) / npairs);
@@ -1300,6 +1306,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
         const uint32_t parity = uses & 1u;
         const PairGeo cur = geo;
         const bool cur_b = cur.has_b, cur_have = have;
+        if (coop && lane == 0) jobs[warp * 8] = 0u;
         const uint32_t row[2] = {cur.row0[0] + lane * G, cur.row0[1] + lane * G};
         const uint32_t len_a = __shfl_sync(0xffffffffu, dl.y, 0) << 6, len_b = __shfl_sync(0xffffffffu, dl.y, 8) << 6;   // tile bytes
         float y[2][G][BT];
@@ -1451,6 +1458,29 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                                 __stcg(dst + j * BT + b, bits == kEmpty ? 0x7FC00000u : bits);     // a NaN stays a NaN
                             }
                     }
+                } else if (coop) {
+                    // post the notice; the CTA adds the runs' rows up together below, this warp writes the result.  Its own
+                    // row goes into its slot like everyone else's, so that the order of the additions does not depend on who
+                    // was elected.
+#pragma unroll
+                    for (int k = 0; k < 2; k++) {
+                        if (k == 1 && !cur_b) continue;
+                        uint32_t *dst = slots + ((size_t)slot * a.Npad + row[k]) * BT;
+#pragma unroll
+                        for (int j = 0; j < G; j++)
+#pragma unroll
+                            for (int b = 0; b < BT; b++) {
+                                const uint32_t bits = __float_as_uint(y[k][j][b]);
+                                __stcg(dst + j * BT + b, bits == kEmpty ? 0x7FC00000u : bits);
+                                y[k][j][b] = 0.0f;
+                            }
+                    }
+                    if (lane == 0) {
+                        jobs[warp * 8 + 1] = count; jobs[warp * 8 + 2] = slot; jobs[warp * 8 + 3] = cur.row0[0];
+                        jobs[warp * 8 + 4] = cur.row0[1]; jobs[warp * 8 + 5] = cur_b ? 1u : 0u;
+                        jobs[warp * 8] = 1u;
+                    }
+                    last = false;
                 } else {
                     float own[2][G][BT];
 #pragma unroll
@@ -1575,6 +1605,90 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
             if (last) {
                 write_rows<G, BT>(a, row[0], y[0]);
                 if (cur_b) write_rows<G, BT>(a, row[1], y[1]);
+            }
+        }
+        if (coop) {
+            // Every notice is served by the whole CTA: warp w polls slots w, w + 16, ... (all its loads of a round in
+            // flight together), empties them, and leaves its share of the sum in its second stage buffer; the warp that
+            // posted the notice adds the shares in warp order to its own row and writes the result.  Which warp takes which
+            // slot is fixed by the geometry, so results are the same from run to run.
+            constexpr uint32_t kEmpty = 0xFFFFFFFFu;
+            uint32_t *slots = reinterpret_cast<uint32_t *>(a.pair_partials);
+            __syncthreads();
+            for (uint32_t jw = 0; jw < (uint32_t)kWarps; jw++) {
+                if (jobs[jw * 8] == 0u) continue;              // same answer in every warp
+                const uint32_t jcount = jobs[jw * 8 + 1];
+                const uint32_t jrow[2] = {jobs[jw * 8 + 3] + lane * G, jobs[jw * 8 + 4] + lane * G};
+                const bool jb = jobs[jw * 8 + 5] != 0u;
+                float share[2][G][BT];
+#pragma unroll
+                for (int k = 0; k < 2; k++)
+#pragma unroll
+                    for (int j = 0; j < G; j++)
+#pragma unroll
+                        for (int b = 0; b < BT; b++) share[k][j][b] = 0.0f;
+                const long long t0 = clock64();
+                for (uint32_t sl = warp; sl < jcount; sl += kWarps) {
+                    uint32_t v[2][G][BT];
+                    bool all = false;
+                    while (!all) {
+                        all = true;
+#pragma unroll
+                        for (int k = 0; k < 2; k++)
+#pragma unroll
+                            for (int j = 0; j < G; j++)
+#pragma unroll
+                                for (int b = 0; b < BT; b++) {
+                                    v[k][j][b] = 0u;
+                                    if (k == 0 || jb)
+                                        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v[k][j][b])
+                                                     : "l"(slots + ((size_t)sl * a.Npad + jrow[k]) * BT + j * BT + b) : "memory");
+                                }
+#pragma unroll
+                        for (int k = 0; k < 2; k++)
+#pragma unroll
+                            for (int j = 0; j < G; j++)
+#pragma unroll
+                                for (int b = 0; b < BT; b++)
+                                    if (k == 0 || jb) all = all && v[k][j][b] != kEmpty;
+                        if (!all && clock64() - t0 > (1ll << 31)) { *a.status = 3u; all = true; }   // ~1 s: give up, the host reports it
+                    }
+#pragma unroll
+                    for (int k = 0; k < 2; k++) {
+                        if (k == 1 && !jb) continue;
+#pragma unroll
+                        for (int j = 0; j < G; j++)
+#pragma unroll
+                            for (int b = 0; b < BT; b++) {
+                                share[k][j][b] += __uint_as_float(v[k][j][b]);
+                                __stcg(slots + ((size_t)sl * a.Npad + jrow[k]) * BT + j * BT + b, kEmpty);
+                            }
+                    }
+                }
+                float *help = reinterpret_cast<float *>(mine + a.stage_bytes);
+#pragma unroll
+                for (int k = 0; k < 2; k++)
+#pragma unroll
+                    for (int j = 0; j < G; j++)
+#pragma unroll
+                        for (int b = 0; b < BT; b++) help[((k * G + j) * BT + b) * 32 + lane] = share[k][j][b];
+                __syncthreads();
+                if (warp == jw) {
+                    for (uint32_t w = 0; w < (uint32_t)kWarps; w++) {
+                        const float *hw = reinterpret_cast<const float *>(smem + tab_bytes + 128 + kPairJobBytes + (size_t)w * region + a.stage_bytes);
+#pragma unroll
+                        for (int k = 0; k < 2; k++)
+#pragma unroll
+                            for (int j = 0; j < G; j++)
+#pragma unroll
+                                for (int b = 0; b < BT; b++) y[k][j][b] += hw[((k * G + j) * BT + b) * 32 + lane];
+                    }
+                    // every slot is empty again; the counter goes back to zero for the next launch
+                    if (lane == 0) a.counters[jobs[jw * 8 + 3] / (32u * G)] = 0u;
+                    write_rows<G, BT>(a, jrow[0], y[0]);
+                    if (jb) write_rows<G, BT>(a, jrow[1], y[1]);
+                }
+                __syncthreads();
             }
         }
         EOQ_STAMP(5);
@@ -1946,12 +2060,18 @@ __global__ void __launch_bounds__(128) decode_v1_kernel(const uint8_t *__restric
     }
 }
 
+static std::atomic<int> g_v1_lanes{1};
+void set_v1_lanes(int v) { g_v1_lanes.store(v != 0); }
+bool v1_lanes_enabled() { return g_v1_lanes.load() != 0; }
+int launch_decode_v1_lanes_single(V1Task t, void *stream);
+
 int launch_decode_v1(const uint8_t *d_stream, const uint32_t *d_offsets, const uint32_t *d_sizes,
                      const V1Table *d_table, void *d_out, int out_elem_bytes, uint32_t nblocks,
-                     uint32_t block_size, uint32_t total, uint32_t p, void *stream)
+                     uint32_t block_size, uint32_t total, uint32_t p, uint32_t alphabet, void *stream)
 {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     if (nblocks == 0) return 0;
+    (void)alphabet;
     const uint32_t grid = (nblocks + 127) / 128;
     const size_t tbytes = (size_t)8 << p;
     const bool shared = tbytes <= 128 * 1024 && nblocks >= 1024;
@@ -1969,6 +2089,340 @@ int launch_decode_v1(const uint8_t *d_stream, const uint32_t *d_offsets, const u
     else return (int)cudaErrorInvalidValue;
 #undef EOQ_LAUNCH_V1
     if (e != cudaSuccess) return (int)e;
+    g_launches++;
+    return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// Wire-format decode, one independent rANS block per LANE.
+//
+// A warp takes 32 consecutive blocks.  Everything a step touches is in shared memory:
+//   * the decode table, in one of two forms chosen by the host: PACKED, one 32-bit entry per slot
+//     {freq - 1 : p bits | slot - cum : p bits | symbol} when 2 p + symbol bits <= 32 (16 KB at p = 12, 64 KB at
+//     p = 14), else TWO-LEVEL, slot -> symbol (u8 / u16) and symbol -> {freq, cum};
+//   * the bytes of the 32 streams: each lane owns a 128-byte ring, stored word-interleaved ([word][lane], so lane l
+//     only ever touches bank l and byte reads never conflict) and filled 32 bytes at a time by asynchronous 4-byte
+//     copies (cp.async) issued two chunks ahead of the read position; the two bytes a step may consume are
+//     requested at the top of the step, next to the table look-up, not after the state update.
+// Decoded symbols are collected in registers and leave as whole 32-byte sectors.  Every global read stays inside
+// [block start rounded down to 4, block end): the words wholly inside come by cp.async, the last partial word by
+// byte loads.
+// ---------------------------------------------------------------------------
+constexpr uint32_t kV1RingBytes = 128, kV1ChunkBytes = 32;
+
+__device__ __forceinline__ uint32_t v1_ring_addr(uint32_t ring, uint32_t lane, uint32_t pos)
+{
+    // byte `pos` of the lane's stream: word (pos / 4) mod 32 of the ring, column `lane`
+    return ring + (((pos >> 2) & (kV1RingBytes / 4 - 1)) << 7) + (lane << 2) + (pos & 3u);
+}
+
+__device__ __forceinline__ uint32_t lds_u8(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+// Request chunk `c` (stream bytes [32 c, 32 c + 32)) of a lane's block into its ring.
+__device__ __forceinline__ void v1_issue_chunk_nocommit(const uint8_t *stream, uint32_t ring, uint32_t lane, uint32_t c, uint32_t lo4,
+                                                        uint32_t end)
+{
+    const uint32_t end4 = end & ~3u;
+#pragma unroll
+    for (uint32_t i = 0; i < kV1ChunkBytes / 4; i++) {
+        const uint32_t w = c * kV1ChunkBytes + i * 4u;
+        const uint32_t dst = v1_ring_addr(ring, lane, w);
+        if (w >= lo4 && w + 4u <= end4) {
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(stream + w) : "memory");
+        } else if (w >= lo4 && w < end) {          // the block's last, partial word
+            for (uint32_t k = 0; k < 4u && w + k < end; k++)
+                asm volatile("st.shared.u8 [%0], %1;" ::"r"(dst + k), "r"((uint32_t)stream[w + k]) : "memory");
+        }
+    }
+}
+__device__ __forceinline__ void v1_issue_chunk(const uint8_t *stream, uint32_t ring, uint32_t lane, uint32_t c, uint32_t lo4,
+                                               uint32_t end)
+{
+    v1_issue_chunk_nocommit(stream, ring, lane, c, lo4, end);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+// The blocks of one lane's warp: decode, collect, store.  `tab` is the CTA's table in shared memory.
+template <typename OutT, bool PACKED>
+__device__ __forceinline__ void v1_decode_lane(const V1Task &a, uint8_t *tab, uint32_t ring, uint32_t lane, uint32_t b)
+{
+    const uint32_t p = a.p, mask = (1u << p) - 1u, low = 1u << (p + 8);
+    const uint32_t *packed = reinterpret_cast<const uint32_t *>(tab);
+    const uint2 *info = reinterpret_cast<const uint2 *>(tab);                                   // two-level: [alphabet] {freq, cum}
+    const uint16_t *symtab = reinterpret_cast<const uint16_t *>(tab + (size_t)a.alphabet * 8u);   // two-level: [1 << p]
+    const uint32_t bytes = a.sizes[b];
+    if (bytes == 0) return;
+    const uint32_t start = a.offsets[b], end = start + bytes, lo4 = start & ~3u;
+    const uint32_t first = b * a.block_size, n = min(a.block_size, a.total - first);
+
+    // the first three chunks, then the header: one byte of state length, the state big-endian
+    uint32_t c_next = start / kV1ChunkBytes;
+    for (int i = 0; i < 3; i++) v1_issue_chunk(a.stream, ring, lane, c_next++, lo4, end);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    const uint32_t state_len = lds_u8(v1_ring_addr(ring, lane, start));
+    if (1u + state_len > bytes || state_len > 4u) return;      // rejected on the host before launch
+    uint32_t x = 0;
+    for (uint32_t i = 0; i < state_len; i++) x = (x << 8) | lds_u8(v1_ring_addr(ring, lane, start + 1u + i));
+    uint32_t pos = start + 1u + state_len;
+
+    constexpr uint32_t kPer = 32u / sizeof(OutT);                // symbols per 32-byte sector
+    OutT *dst = reinterpret_cast<OutT *>(a.out) + first;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(dst) & 31u) == 0;
+    const uint32_t symmask = (1u << a.sym_bits) - 1u;
+    const uint32_t lane_col = ring + (lane << 2);
+
+    // The eight stream bytes around the read position live in two registers (words wi and wi + 1 of the stream), so
+    // the bytes a renormalisation takes come from a byte permute, not from a load behind the state update; the next word
+    // is fetched from the ring when the position crosses a word, one step before anything can need it.
+    auto ring_word = [&](uint32_t w) { return lds_u32(lane_col + ((w & (kV1RingBytes / 4 - 1)) << 7)); };
+    uint32_t wi = pos >> 2, cur = ring_word(wi), nxt = ring_word(wi + 1u);
+
+    auto step = [&]() -> uint32_t {
+        const uint32_t slot = x & mask;
+        uint32_t sym;
+        if (PACKED) {
+            const uint32_t e = packed[slot];
+            sym = e & symmask;
+            x = ((e >> (32u - p)) + 1u) * (x >> p) + ((e >> a.sym_bits) & mask);
+        } else {
+            sym = symtab[slot];
+            const uint2 fc = info[min(sym, a.alphabet - 1u)];      // a caller's table may name symbols past the alphabet: stay in the array
+            x = fc.x * (x >> p) + slot - fc.y;
+        }
+        // bytes pos and pos + 1, first one in the higher half; 0, 1 or 2 of them are taken (p <= 16), never past the block
+        const uint32_t two = __byte_perm(cur, nxt, (pos & 3u) * 0x11u + 1u) & 0xFFFFu;
+        uint32_t take = (x < low ? 1u : 0u) + (x < (low >> 8) ? 1u : 0u);
+        take = min(take, end - pos);
+        x = (x << (8u * take)) | (two >> (16u - 8u * take));
+        pos += take;
+        if ((pos >> 2) != wi) { cur = nxt; wi++; nxt = ring_word(wi + 1u); }
+        if (x < low && pos < end) {
+            // only a corrupt stream gets here: read on like the reference decoder, byte by byte and inside the block
+            while (x < low && pos < end) { x = (x << 8) | a.stream[pos]; pos++; }
+            wi = pos >> 2;
+            cur = nxt = 0u;
+            for (uint32_t k = 0; k < 8u; k++) {
+                const uint32_t at = wi * 4u + k;
+                const uint32_t byte = at >= start && at < end ? a.stream[at] : 0u;
+                if (k < 4u) cur |= byte << (8u * k); else nxt |= byte << (8u * (k - 4u));
+            }
+        }
+        return sym;
+    };
+    auto keep_ahead = [&]() {
+        // Called every 8 steps (<= 16 bytes).  On entry the chunk under `pos` and the next one are complete; a chunk is
+        // requested as soon as the position is within two chunks of it, and every call closes one copy group, so that
+        // "all but the two latest groups" is exactly "everything requested two calls ago", the latest moment it is needed.
+        if ((pos / kV1ChunkBytes) + 3u > c_next) v1_issue_chunk_nocommit(a.stream, ring, lane, c_next++, lo4, end);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 2;" ::: "memory");
+    };
+
+    uint32_t i = 0;
+    if (vec_ok) {
+        for (; i + kPer <= n; i += kPer) {
+            uint32_t w[8];
+#pragma unroll
+            for (uint32_t g = 0; g < kPer / 8u; g++) {
+                keep_ahead();
+#pragma unroll
+                for (uint32_t k = 0; k < 8u; k++) {
+                    const uint32_t sym = step();
+                    const uint32_t idx = g * 8u + k;
+                    if (sizeof(OutT) == 1) {
+                        if ((idx & 3u) == 0) w[idx >> 2] = sym; else w[idx >> 2] |= sym << (8u * (idx & 3u));
+                    } else {
+                        if ((idx & 1u) == 0) w[idx >> 1] = sym; else w[idx >> 1] |= sym << 16;
+                    }
+                }
+            }
+            uint4 *o = reinterpret_cast<uint4 *>(dst + i);
+            o[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            o[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+    }
+    for (; i < n; i++) {
+        if ((i & 7u) == 0) keep_ahead();
+        dst[i] = (OutT)step();
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// Grid: the CTAs of all tasks back to back; cta_task[blockIdx.x] says whose blocks a CTA decodes.  Each CTA builds its
+// task's table in shared memory: from the normalised frequencies (a warp-wide prefix sum, then every warp fills the
+// slot ranges of its share of the symbols, lanes side by side), or from a caller's slot table in the reference's
+// {symbol, freq, cum} form.
+__device__ __forceinline__ void v1_lanes_body(const V1Task &a, uint8_t *v1_smem)
+{
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const uint32_t p = a.p, M = 1u << p;
+    // shared memory: [rings: nwarps x 4 KB][table][cdf: alphabet + 1 words]
+    const uint32_t ring = smem_addr(v1_smem) + warp * (kV1RingBytes * 32u);
+    uint8_t *tab = v1_smem + (size_t)nwarps * kV1RingBytes * 32u;
+    uint32_t *packed = reinterpret_cast<uint32_t *>(tab);
+    uint2 *info = reinterpret_cast<uint2 *>(tab);
+    uint16_t *symtab = reinterpret_cast<uint16_t *>(tab + (size_t)a.alphabet * 8u);
+    const size_t tab_bytes = a.packed ? ((size_t)4 << p) : ((size_t)a.alphabet * 8u + ((size_t)2 << p));
+    uint32_t *cdf = reinterpret_cast<uint32_t *>(tab + ((tab_bytes + 15u) & ~(size_t)15u));
+    if (a.freq) {
+        if (warp == 0) {
+            // exclusive prefix sum of the frequencies: each lane sums a run of symbols, the runs are scanned by shuffles
+            const uint32_t per = (a.alphabet + 31u) / 32u, lo = min(a.alphabet, lane * per), hi = min(a.alphabet, lo + per);
+            uint32_t sum = 0;
+            for (uint32_t s = lo; s < hi; s++) sum += a.freq[s];
+            uint32_t incl = sum;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const uint32_t o = __shfl_up_sync(0xffffffffu, incl, d);
+                if ((int)lane >= d) incl += o;
+            }
+            uint32_t run = incl - sum;
+            for (uint32_t s = lo; s < hi; s++) { cdf[s] = run; run += a.freq[s]; }
+            if (lane == 31) cdf[a.alphabet] = incl;
+        }
+        __syncthreads();
+        for (uint32_t s = warp; s < a.alphabet; s += nwarps) {
+            const uint32_t c = cdf[s], f = cdf[s + 1] - c;
+            if (!a.packed && lane == 0) info[s] = make_uint2(f, c);
+            for (uint32_t k = lane; k < f && c + k < M; k += 32u) {
+                if (a.packed) packed[c + k] = ((f - 1u) << (32u - p)) | (k << a.sym_bits) | s;
+                else symtab[c + k] = (uint16_t)s;
+            }
+        }
+    } else {
+        const uint2 *src = reinterpret_cast<const uint2 *>(a.table);           // x: symbol | freq << 16, y: cum
+        for (uint32_t s0 = tid; s0 < M; s0 += blockDim.x * 4u) {                // four independent loads in flight per thread
+            uint2 e[4];
+#pragma unroll
+            for (uint32_t u = 0; u < 4u; u++)
+                if (s0 + u * blockDim.x < M) e[u] = __ldg(src + s0 + u * blockDim.x);
+#pragma unroll
+            for (uint32_t u = 0; u < 4u; u++) {
+                const uint32_t slot = s0 + u * blockDim.x;
+                if (slot >= M) continue;
+                const uint32_t sym = e[u].x & 0xFFFFu, freq = e[u].x >> 16, cum = e[u].y & 0xFFFFu;
+                if (a.packed) {
+                    packed[slot] = ((freq - 1u) << (32u - p)) | (((slot - cum) & (M - 1u)) << a.sym_bits) | (sym & ((1u << a.sym_bits) - 1u));
+                } else {
+                    symtab[slot] = (uint16_t)sym;
+                    if (sym < a.alphabet) info[sym] = make_uint2(freq, cum);       // every slot of a symbol writes the same pair
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    const uint32_t b = ((blockIdx.x - a.first_cta) * nwarps + warp) * 32u + lane;
+    if (b >= a.nblocks) return;
+    if (a.out_elem_bytes == 1) {
+        if (a.packed) v1_decode_lane<uint8_t, true>(a, tab, ring, lane, b); else v1_decode_lane<uint8_t, false>(a, tab, ring, lane, b);
+    } else {
+        if (a.packed) v1_decode_lane<uint16_t, true>(a, tab, ring, lane, b); else v1_decode_lane<uint16_t, false>(a, tab, ring, lane, b);
+    }
+}
+
+__global__ void __launch_bounds__(256, 2) decode_v1_lanes_kernel(const V1Task *__restrict__ tasks, const uint32_t *__restrict__ cta_task)
+{
+    extern __shared__ __align__(128) uint8_t v1_smem[];
+    __shared__ V1Task a;
+    if (threadIdx.x < sizeof(V1Task) / 4)
+        reinterpret_cast<uint32_t *>(&a)[threadIdx.x] = reinterpret_cast<const uint32_t *>(tasks + cta_task[blockIdx.x])[threadIdx.x];
+    __syncthreads();
+    v1_lanes_body(a, v1_smem);
+}
+
+// One tensor, its description passed by value: for entry points that may neither allocate nor copy (device pointers in,
+// asynchronous launch out).
+__global__ void __launch_bounds__(256, 2) decode_v1_lanes_single_kernel(const V1Task a)
+{
+    extern __shared__ __align__(128) uint8_t v1_smem[];
+    v1_lanes_body(a, v1_smem);
+}
+
+// Fill in what the kernel derives from a task's parameters; false if the lane kernel does not take it (stream not
+// 4-byte aligned, alphabet above 4096, table too large for shared memory): the caller then uses the one-thread-per-
+// block kernel.
+bool v1_task_prepare(V1Task &t)
+{
+    if ((reinterpret_cast<uintptr_t>(t.stream) & 3u) != 0 || t.p == 0 || t.p > 16 || t.alphabet == 0 || t.alphabet > 4096u) return false;
+    if (t.out_elem_bytes != 1 && t.out_elem_bytes != 2) return false;
+    t.sym_bits = 1;
+    while ((1u << t.sym_bits) < t.alphabet) t.sym_bits++;
+    t.packed = 2u * t.p + t.sym_bits <= 32u ? 1u : 0u;
+    return v1_task_smem(t, 8) != 0;
+}
+
+size_t v1_task_smem(const V1Task &t, uint32_t warps)
+{
+    const size_t table = t.packed ? ((size_t)4 << t.p) : ((size_t)t.alphabet * 8u + ((size_t)2 << t.p));
+    const size_t total = (size_t)warps * kV1RingBytes * 32u + ((table + 15u) & ~(size_t)15u) + ((size_t)t.alphabet + 1u) * 4u;
+    return total <= 200 * 1024 ? total : 0;
+}
+
+// Launch the lane kernel over `ntasks` prepared tasks.  `d_tasks` / `d_cta_task` are device copies the caller has
+// already queued on `stream` (host arrays given for sizing): tasks[i].first_cta must be set from v1_plan_ctas.
+uint32_t v1_plan_ctas(V1Task *tasks, uint32_t ntasks, uint32_t &warps_per_cta, size_t &smem)
+{
+    uint64_t total_warps = 0;
+    for (uint32_t i = 0; i < ntasks; i++) total_warps += (tasks[i].nblocks + 31u) / 32u;
+    const uint32_t sms = (uint32_t)std::max(1, device_sm_count());
+    warps_per_cta = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>(8, (total_warps + sms - 1u) / sms));   // spread over the SMs first
+    uint32_t cta = 0;
+    smem = 0;
+    for (uint32_t i = 0; i < ntasks; i++) {
+        tasks[i].first_cta = cta;
+        cta += ((tasks[i].nblocks + 31u) / 32u + warps_per_cta - 1u) / warps_per_cta;
+        smem = std::max(smem, v1_task_smem(tasks[i], warps_per_cta));
+    }
+    return cta;
+}
+
+int launch_decode_v1_lanes_single(V1Task t, void *stream)
+{
+    static std::mutex mu;
+    static bool attr_set[16] = {false};
+    uint32_t warps = 1;
+    size_t smem = 0;
+    const uint32_t grid = v1_plan_ctas(&t, 1, warps, smem);
+    if (grid == 0) return 0;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!attr_set[dev & 15]) {
+            e = cudaFuncSetAttribute(decode_v1_lanes_single_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e != cudaSuccess) return (int)e;
+            attr_set[dev & 15] = true;
+        }
+    }
+    decode_v1_lanes_single_kernel<<<grid, warps * 32u, smem, reinterpret_cast<cudaStream_t>(stream)>>>(t);
+    g_launches++;
+    return (int)cudaGetLastError();
+}
+
+int launch_decode_v1_lanes(const V1Task *d_tasks, const uint32_t *d_cta_task, uint32_t grid, uint32_t warps_per_cta, size_t smem, void *stream)
+{
+    static std::mutex mu;
+    static bool attr_set[16] = {false};
+    if (grid == 0) return 0;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!attr_set[dev & 15]) {
+            e = cudaFuncSetAttribute(decode_v1_lanes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e != cudaSuccess) return (int)e;
+            attr_set[dev & 15] = true;
+        }
+    }
+    decode_v1_lanes_kernel<<<grid, warps_per_cta * 32u, smem, reinterpret_cast<cudaStream_t>(stream)>>>(d_tasks, d_cta_task);
     g_launches++;
     return (int)cudaGetLastError();
 }
@@ -2011,6 +2465,13 @@ int launch_decode_v1_syminfo(const uint8_t *d_stream, const uint32_t *d_offsets,
                              uint32_t block_size, uint32_t total, uint32_t p, void *stream)
 {
     if (nblocks == 0) return 0;
+    if (g_v1_lanes.load()) {
+        // the reference's entry point does not say how many symbols the table has: bytes are written, so at most 256
+        V1Task t = {};
+        t.stream = d_stream; t.offsets = d_offsets; t.sizes = d_sizes; t.freq = nullptr; t.table = d_info; t.out = d_out;
+        t.nblocks = nblocks; t.block_size = block_size; t.total = total; t.p = p; t.alphabet = 256; t.out_elem_bytes = 1;
+        if (v1_task_prepare(t)) return launch_decode_v1_lanes_single(t, stream);
+    }
     decode_v1_syminfo_kernel<<<(nblocks + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
         d_stream, d_offsets, d_sizes, d_info, d_out, nblocks, block_size, total, p);
     g_launches++;

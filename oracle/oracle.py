@@ -44,6 +44,11 @@ def build(ref_root: Optional[str] = None) -> None:
     ref_root = reference_dir(ref_root)
     if ref_root:
         subprocess.run(["make", "-C", _HERE, "ref", f"REF={ref_root}"], check=True, capture_output=True)
+        import shutil
+        if shutil.which("nvcc") or os.path.exists("/usr/local/cuda/bin/nvcc"):
+            nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+            # the reference's CUDA decoder, for timing beside this project's kernel; failure to build it is not an error
+            subprocess.run(["make", "-C", _HERE, "ref_cuda", f"REF={ref_root}", f"NVCC={nvcc}"], check=False, capture_output=True)
 
 
 def lib() -> C.CDLL:
@@ -379,6 +384,28 @@ class RefC:
         rc = self.v2.eoq_parallel_decode(tasks, n, C.byref(opts))
         dt = time.perf_counter() - t0
         return rc, [o[:int(h[6])] for o, (h, _) in zip(outs, items)], dt
+
+
+class RefCuda:
+    """ctypes view of the reference's CUDA decoder (llamacpp_integration/eoq_cuda_decompress.cu:529-567) compiled by
+    `make -C oracle ref_cuda`: device pointers in, asynchronous launch of its one-thread-per-block kernel."""
+
+    def __init__(self):
+        path = os.path.join(_HERE, "_ref", "libeoq_ref_cuda.so")
+        if not os.path.exists(path):
+            raise FileNotFoundError("oracle/_ref/libeoq_ref_cuda.so is not built (make -C oracle ref_cuda)")
+        self.lib = C.CDLL(path)
+        vp = C.c_void_p
+        self.lib.eoq_cuda_decode_tensor_device.restype = C.c_int
+        self.lib.eoq_cuda_decode_tensor_device.argtypes = [vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, vp]
+
+    @staticmethod
+    def available() -> bool:
+        return os.path.exists(os.path.join(_HERE, "_ref", "libeoq_ref_cuda.so"))
+
+    def decode_device(self, d_stream, d_offsets, d_sizes, d_sym_info, d_out, nblocks, block_size, total, p, stream) -> int:
+        return int(self.lib.eoq_cuda_decode_tensor_device(d_stream, d_offsets, d_sizes, d_sym_info, d_out, nblocks, block_size,
+                                                          total, p, stream))
 
 
 def decode_tiles(table: np.ndarray, p: int, g: int, bits: int, desc: np.ndarray, stream: np.ndarray,

@@ -28,6 +28,7 @@ sys.dont_write_bytecode = True
 sys.path.insert(0, REF)
 
 import torch  # noqa: E402
+import torch.nn.functional as F  # noqa: E402
 
 from core import rans as R  # noqa: E402
 from core import rans_blocked as RB  # noqa: E402
@@ -216,7 +217,65 @@ def eoq_container():
     print("sample.eoq:", os.path.getsize(path), "bytes,", list(tensors))
 
 
+def fullsize():
+    """The BASELINE shapes at full size.  The matrices are too large to commit, so the fixture holds what pins them:
+    hashes of what the reference's quantisers make of the seeded weights (recipes.py regenerates the weights), the
+    hash and length of the reference-encoded config-1 container, and the reference's own dequantise-then-linear
+    outputs (whole vectors for the GEMV shapes, 32 evenly spaced output columns for the prefill shapes)."""
+    import recipes as RC
+    d = {}
+    for name, (n, k, seed, sigma) in RC.INT4_SHAPES.items():
+        w = RC.weight(n, k, seed, sigma)
+        qt = U.quantize_absmax(w, 4, 128)
+        codes = qt.data.to(torch.int8).reshape(n, k)
+        s16 = qt.scale.to(torch.float16)
+        d[name + "/sha_codes"] = np.array(RC.sha(codes))
+        d[name + "/sha_scales16"] = np.array(RC.sha(s16))
+        qt16 = U.QuantizedTensor(data=qt.data, scale=s16.float(), zero_point=qt.zero_point, bits=4, shape=qt.shape, block_size=128)
+        deq = U.dequantize(qt16).reshape(n, k)                     # what a loader sees: scales went through fp16
+        if name.startswith(("up_", "down_4096")):
+            for batch in (1, 4):
+                x = RC.activations(batch, k, seed * 10 + batch)
+                d[f"{name}/y_fp32_b{batch}"] = F.linear(x.float(), deq).numpy()          # fp32 accumulate, the parity bar
+                d[f"{name}/y_fp16_b{batch}"] = F.linear(x, deq.half()).float().numpy()   # the reference's own composition
+        if "shard" in name:
+            stride = n // 32
+            for m in (16, 64, 256, 2048):
+                x = RC.activations(m, k, seed * 10 + m, torch.bfloat16)
+                d[f"{name}/y_m{m}"] = F.linear(x.float(), deq[::stride]).numpy()
+            d[name + "/stride"] = np.array(stride)
+        if name.startswith("square"):
+            sym = (codes.flatten().numpy().astype(np.int64) + 7)
+            data = RB.BlockedRANSEncoder(block_size=4096, precision_bits=12).encode(sym, 15)
+            ser = RB.serialize_blocked_rans(data)
+            d[name + "/rans_len"] = np.array(len(ser))
+            d[name + "/sha_rans"] = np.array(RC.sha(np.frombuffer(ser, np.uint8)))
+            d[name + "/sha_dequant16"] = np.array(RC.sha(deq.half()))
+            # the bridge of core/rans_bitpacked.py (block 256, p 14) on the first SLICE_ROWS rows
+            rows = RC.BRIDGE_ROWS
+            ct = RBP.compress_tensor_rans("w", qt.data.flatten()[: rows * k], qt.scale.flatten()[: rows * k // 128], 4, 128, (rows, k))
+            d[name + "/bridge_rans"] = np.frombuffer(ct.rans_bytes, np.uint8).copy()
+            d[name + "/bridge_scales"] = np.frombuffer(ct.scales_bytes, np.uint8).copy()
+        print("fullsize:", name)
+    name, n, k, seed, sigma = RC.POLAR_SHAPE
+    w = RC.polar_weight(n, k, seed, sigma)
+    rows = RC.SLICE_ROWS
+    r = PQ.polar_quantize(w[:rows], bits=5, block_size=64, use_qjl=False)
+    deq = PQ.polar_dequantize(r).float()
+    d[name + "/sha_codes_slice"] = np.array(RC.sha(r.codes))
+    d[name + "/sha_norms_slice"] = np.array(RC.sha(r.norms))
+    for batch in (1, 4, 8):
+        x = RC.activations(batch, k, seed * 10 + batch)
+        d[f"{name}/y_slice_b{batch}"] = F.linear(x.float(), deq).numpy()
+    np.savez_compressed(os.path.join(OUT, "ref_fullsize.npz"), **d)
+    print("ref_fullsize:", os.path.getsize(os.path.join(OUT, "ref_fullsize.npz")), "bytes")
+
+
 if __name__ == "__main__":
+    sys.path.insert(0, OUT)
+    if len(sys.argv) > 2 and sys.argv[2] == "fullsize":
+        fullsize()
+        raise SystemExit(0)
     eoq_container()
     xval_vectors()
     normalisation()
@@ -224,3 +283,4 @@ if __name__ == "__main__":
     tensors()
     linears()
     polar()
+    fullsize()

@@ -413,6 +413,29 @@ def test_fused_gemv_four_rows_on_a_wide_layer(dt, batch):
         assert O.rel_l2(w.gemv(x[r:r + 1], bias=bias, out_dtype=torch.float32).cpu().numpy(), ref[r:r + 1]) < TOL
 
 
+@pytest.mark.parametrize("n,k,batch", [(2752, 4096, 1), (1024, 11008, 1), (1376, 4096, 2), (512, 11008, 1), (512, 11008, 4), (96, 8192, 1)])
+def test_fused_gemv_on_row_shards_much_wider_than_tall(n, k, batch):
+    """The row shards of the Llama-7B MLP pair over four and eight GPUs.  The segments of one pair of row blocks are
+    spread over dozens of CTAs here, so the warp elected to add their partial rows up has the whole CTA help it; the
+    result must match dequantise-then-matmul and be the same from run to run."""
+    g = torch.Generator(device="cuda").manual_seed(n + k + batch)
+    wt = torch.randn(n, k, device="cuda", generator=g) * 0.02
+    blocks = wt.view(-1, 128)
+    scale = (blocks.abs().amax(dim=1) / 7).clamp(min=1e-10)
+    codes = (blocks / scale[:, None]).round().clamp(-7, 7).to(torch.int8).view(n, k)
+    s16 = scale.half()
+    w = EOQWeight.from_symbols((codes + 7).to(torch.uint8), s16)
+    dense = (codes.float().view(-1, 128) * s16.float()[:, None]).view(n, k)
+    x = torch.randn(batch, k, device="cuda", generator=g).half()
+    bias = torch.randn(n, device="cuda", generator=g)
+    ref = (x.float() @ dense.T + bias).cpu().numpy()
+    y0 = w.gemv(x, bias=bias, out_dtype=torch.float32)
+    assert O.rel_l2(y0.cpu().numpy(), ref) < 1e-5
+    for _ in range(5):
+        assert torch.equal(w.gemv(x, bias=bias, out_dtype=torch.float32), y0)
+    assert w.status() == 0
+
+
 @pytest.mark.parametrize("n,k,batch", [(22016, 4096, 1), (32000, 4096, 2), (7680, 2048, 4)])
 def test_fused_gemv_over_several_waves_of_tile_pairs(n, k, batch):
     """Shapes whose tile pairs outnumber the resident warps (the gate/up projection and the vocabulary head of the

@@ -282,3 +282,23 @@ def test_eoq_container_reader_parses_reference_file(tmp_path):
     bad.write_bytes(body + struct.pack("<I", zlib.crc32(body) & 0xFFFFFFFF))
     with pytest.raises(ValueError, match="magic"):
         EF.read_eoq(bad)
+
+
+def test_polar_quantize_on_the_host_is_the_reference_bit_for_bit():
+    """core/polar_quant.py:141-264: codes, fp16 norms, centroids, the Hadamard matrix and the dequantised matrix
+    equal what the imported reference produced from the same weight."""
+    import torch
+    from eoq_quantization_b200.core import polar_quant as PQ
+    z = _z("ref_polar")
+    r = PQ.polar_quantize(torch.from_numpy(z["w"]), bits=5, block_size=64, use_qjl=False)
+    assert r.codes.dtype == torch.int8 and r.norms.dtype == torch.float16 and r.shape == (16, 256) and r.n_elements == 4096
+    assert np.array_equal(r.codes.numpy(), z["codes"]) and np.array_equal(r.norms.numpy(), z["norms"])
+    assert np.array_equal(PQ._ensure_centroids(5).numpy(), z["centroids5"])
+    assert np.array_equal(PQ.hadamard_matrix(64).numpy(), z["hadamard64"])
+    deq = PQ.polar_dequantize(r)
+    assert deq.dtype == torch.float16 and np.array_equal(deq.float().numpy(), z["dequant"])
+    # chunking the nearest-centroid search does not change a single code
+    r2 = PQ.polar_quantize(torch.from_numpy(z["w"]), bits=5, block_size=64, use_qjl=False, chunk_blocks=7)
+    assert torch.equal(r2.codes, r.codes)
+    with pytest.raises(ValueError):
+        PQ.hadamard_matrix(48)
