@@ -459,6 +459,22 @@ def run_gpu_arm(args):
            "note": ("y is pinned: the kernel stores its results into host memory itself, x goes in by a copy" +
                     ("; per-rank output slices are read back, no gather on the host path" if world > 1 else ""))}
 
+    extras = {}
+    if not args.no_extras:
+        # the other multi-GPU configurations, appended to the headline line (each guarded: a failure here must not lose the headline)
+        del shards
+        torch.cuda.empty_cache()
+        for key, fn in (("llama7b_step", lambda: measure_llama_step(world, rank, 10, args.gather, world == 1)),
+                        ("prefill_tp", lambda: measure_prefill_tp(world, rank, 5))):
+            try:
+                extras[key] = fn()
+            except Exception as exc:                               # pragma: no cover
+                extras[key] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+            torch.cuda.empty_cache()
+        lo_, hi_ = shard_rows(N_UP, world, rank)
+        shards = [EOQWeight.replicas(1, layers[0][0][lo_:hi_], layers[0][1][lo_ * (K_UP // GROUP):hi_ * (K_UP // GROUP)]),
+                  EOQWeight.replicas(1, layers[1][0][shard_rows(N_DN, world, rank)[0]:shard_rows(N_DN, world, rank)[1]],
+                                     layers[1][1][shard_rows(N_DN, world, rank)[0] * (K_DN // GROUP):shard_rows(N_DN, world, rank)[1] * (K_DN // GROUP)])]
     if rank == 0:
         cpu_line = None
         if world == 1 and not args.no_cpu_baseline:
@@ -492,6 +508,7 @@ def run_gpu_arm(args):
                 "clocks": clocks.summary(), "roofline": roof, "e2e": e2e, "gpu_launches": int(launches_timed) * world}
         if cpu_line:
             line["cpu_baseline"] = cpu_line
+        line.update(extras)
         print(json.dumps(line), flush=True)
     g_full = g_one = g_up = None                                 # drop the captured graphs before the communicator goes
     shutdown_distributed(world)
@@ -605,16 +622,25 @@ def run_llama_step(args):
     with dense fp16 weights (torch matmul) is timed beside it."""
     import torch
     import torch.distributed as dist
-    import torch.nn.functional as F
-    from eoq_quantization_b200.fused import EOQWeight
-    from eoq_quantization_b200.tp import gather_rows, shard_rows
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    line = measure_llama_step(world, rank, min(args.steps, 50), args.gather, world == 1 and not args.no_cpu_baseline)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    shutdown_distributed(world)
+
+
+def measure_llama_step(world, rank, steps, gather, with_fp16):
+    """One measurement of the Llama-7B-shape decode step on an initialised process group; returns the JSON object."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from eoq_quantization_b200.fused import EOQWeight
+    from eoq_quantization_b200.tp import gather_rows, shard_rows
     H, NH, HD, FF, V, L, KV = 4096, 32, 128, 11008, 32000, 32, 1024
     shapes = {"qkv": (3 * H, H), "o": (H, H), "gate_up": (2 * FF, H), "down": (H, FF)}
     layers, alg_layer = {}, 0
@@ -643,7 +669,7 @@ def run_llama_step(args):
     # rotation: 129 gathers per step, so consecutive gathers never share a slot, also across steps); the attention
     # output, which no GEMV produces, goes through a library all-gather
     pg, call_no = None, [0]
-    if world > 1 and args.gather == "peer":
+    if world > 1 and gather == "peer":
         from eoq_quantization_b200.tp import PeerGather
         pg = PeerGather(slot_bytes=V * 2, slots=3)
 
@@ -709,7 +735,6 @@ def run_llama_step(args):
             ms = float(t.item())
         return ms, mode
 
-    steps = min(args.steps, 50)
     ms, mode = timed(lambda: step(x0, lin_eoq), steps)
     if pg is not None:
         pg.check()                                               # no gather may have given up waiting for a peer
@@ -718,8 +743,9 @@ def run_llama_step(args):
             "config": {"workload": "llama7b_decode_step_int4_g128_rans", "layers": L, "hidden": H, "kv_len": KV,
                        "launch": mode, "parallelism": f"row-sharded tp{world}" + ("" if world == 1 else
                                                    " + gather fused into the GEMVs" if pg is not None else " + nccl all-gather")},
+            "gathers_per_step": 0 if world == 1 else 4 * L + 1 + L,
             "algorithmic_weight_bytes_per_step": alg_step, "weight_gbs": alg_step / (ms * 1e-3) / 1e9}
-    if world == 1 and not args.no_cpu_baseline:
+    if with_fp16:
         # dense fp16 comparator: same step, weights as fp16 matrices (one copy per layer)
         del layers
         torch.cuda.empty_cache()
@@ -732,9 +758,65 @@ def run_llama_step(args):
         line["fp16_dense_ms_per_step"] = ms16
         line["fp16_dense_tokens_per_s"] = 1e3 / ms16
         line["speedup_vs_fp16_dense"] = ms16 / ms
-    if rank == 0:
-        print(json.dumps(line), flush=True)
-    shutdown_distributed(world)
+        del dense, dhead
+    if pg is not None:
+        pg.close()
+    return line
+
+
+def measure_prefill_tp(world, rank, steps):
+    """Llama-70B-shape gate/up projection (28672 x 8192, INT4 g128 rANS-coded, N(0, 0.015)) row-sharded over the ranks:
+    per M, the fused decode + tensor-core GEMM of this rank's rows followed by the all-gather of the output slices
+    (NCCL); device time, max over ranks.  Every rank's shard is drawn from the same distribution (its own seed)."""
+    import torch
+    import torch.distributed as dist
+    from eoq_quantization_b200 import _lib
+    from eoq_quantization_b200.fused import EOQWeight
+    lib = _lib.lib()
+    n_total, k = 28672, 8192
+    n = n_total // world
+    rng = np.random.default_rng(100 + rank)
+    res = {}
+    chunk = 3584                                                    # encode in shards of the 8-rank size to bound host memory
+    ws = []
+    for lo in range(0, n, chunk):
+        w = (rng.standard_normal((min(chunk, n - lo), k)) * 0.015).astype(np.float32)
+        sc = np.maximum(np.abs(w.reshape(-1, GROUP)).max(axis=1) / 7.0, 1e-10).astype(np.float32)
+        sym = (np.clip(np.round(w.reshape(-1, GROUP) / sc[:, None]), -7, 7) + 7).astype(np.uint8).reshape(w.shape)
+        ws.append(EOQWeight.from_symbols(sym, sc.astype(np.float16)))
+        del w, sym
+    for m in (16, 64, 256, 2048):
+        x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+        ys = [torch.empty(m, wi.rows, device="cuda", dtype=torch.bfloat16) for wi in ws]
+        full = torch.empty(world, m, n, device="cuda", dtype=torch.bfloat16) if world > 1 else None
+
+        def run():
+            st = torch.cuda.current_stream().cuda_stream
+            for wi, y in zip(ws, ys):
+                _lib.check(lib.eoq_b200_gemm(wi._h, x.data_ptr(), _lib.BF16, m, y.data_ptr(), _lib.BF16, None, st), "gemm")
+            if world > 1:
+                local = ys[0] if len(ys) == 1 else torch.cat(ys, dim=1)
+                dist.all_gather_into_tensor(full, local.contiguous())
+        for _ in range(3):
+            run()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(3, min(steps, 10))
+        e0.record()
+        for _ in range(reps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / reps * 1e3
+        if world > 1:
+            t = torch.tensor([us], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            us = float(t.item())
+        res[f"M{m}"] = {"us": us, "tflops": 2.0 * m * n_total * k / us / 1e6}
+    return {"workload": "llama70b_gate_up_28672x8192_int4_g128_rans, bf16 x", "parallelism": f"row-sharded tp{world}" +
+            (" + nccl all-gather of [M, rows / ranks] slices" if world > 1 else ""), "rows_per_rank": n, "per_m": res}
 
 
 def run_prefill_gemm(args, torch, _lib, lib, EOQWeight):
@@ -814,8 +896,8 @@ def run_prefill_gemm(args, torch, _lib, lib, EOQWeight):
                 torch.cuda.synchronize()
                 print(json.dumps({"workload": "prefill_gemm eager", "shape": [n, k], "M": m, "launches": max(args.steps, 1)}), flush=True)
                 return
-            if m <= 256:
-                us = graph_us(fused, 12, warm=len(ws))
+            if True:                                                       # every M runs fused: 512 rows share one pass
+                us = graph_us(fused, 12 if m <= 256 else 4, warm=len(ws))
                 want = (xh.float() @ dense.float().t())
                 err = float((y.float() - want).norm() / want.norm())
                 assert err < 8e-3, f"fused GEMM mismatch {err}"            # bf16 output rounding ~ 4e-3
@@ -980,6 +1062,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="headline line only: skip the Llama-7B step and the prefill GEMM")
     ap.add_argument("--eager", action="store_true", help="plain launches instead of CUDA graphs (for profilers)")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: how output slices are exchanged")
     ap.add_argument("--no-pdl", action="store_true", help="plain launches instead of programmatic dependent launches")

@@ -26,6 +26,9 @@ EOQ_ERR_UNSUPPORTED = -9
 
 KIND_INT4_ABSMAX = 0
 KIND_Q5_POLAR = 1
+KIND_INT2_ABSMAX, KIND_INT3_ABSMAX, KIND_INT8_ABSMAX = 2, 3, 4
+#: kind of the symmetric absmax code of a given width (symbol = code + qmax)
+INT_KINDS = {2: KIND_INT2_ABSMAX, 3: KIND_INT3_ABSMAX, 4: KIND_INT4_ABSMAX, 8: KIND_INT8_ABSMAX}
 F16, BF16, F32 = 0, 1, 2
 
 #: every symbol include/eoq_b200.h declares
@@ -43,8 +46,10 @@ EXPORTS = [
     "eoq_b200_gather_create", "eoq_b200_gather_connect", "eoq_b200_gather_destroy", "eoq_b200_gather_buffer",
     "eoq_b200_gather_status", "eoq_b200_gather_set_timeout_ms", "eoq_b200_gather_wait", "eoq_b200_gemv_gather", "eoq_b200_gemv_static_scratch", "eoq_b200_gemv_host", "eoq_b200_gemv_host_async", "eoq_b200_weight_decode",
     "eoq_b200_dequant_packed",
-    "eoq_b200_weight_status", "eoq_b200_tune", "eoq_b200_launch_count",
+    "eoq_b200_weight_status",
 ]
+#: exported for this project's benchmarks and tests only (declared in csrc/eoq_internal.h, not in the public header)
+INTERNAL_EXPORTS = ["eoq_b200_tune", "eoq_b200_launch_count"]
 
 
 class EOQError(RuntimeError):

@@ -8,9 +8,7 @@ from ..fused import dequant_packed, require_cuda
 
 
 def _unpack(packed: torch.Tensor, out_features: int, in_features: int, bits: int) -> torch.Tensor:
-    # codes are recovered exactly from the dense kernel output with unit scales
-    ones = torch.ones((out_features * in_features + 127) // 128, dtype=torch.float16, device=packed.device)
-    return dequant_packed(packed, ones, out_features, in_features, bits, 128).to(torch.int8)
+    return dequant_packed(packed, None, out_features, in_features, bits, 128, dtype=torch.int8)      # the kernel writes the codes
 
 
 def unpack_4bit_fast(packed: torch.Tensor, out_features: int, in_features: int) -> torch.Tensor:

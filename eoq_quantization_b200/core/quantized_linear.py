@@ -105,7 +105,7 @@ class QuantizedLinear(nn.Module):
 
     # -- GPU paths ---------------------------------------------------------------
     def _fusable(self) -> bool:
-        return (self.bits == 4 and self.in_features % 16 == 0 and self.block_size % 16 == 0
+        return (self.bits in (2, 3, 4, 8) and self.in_features % 16 == 0 and self.block_size % 16 == 0
                 and self.in_features % self.block_size == 0)
 
     def eoq_weight(self) -> EOQWeight:
@@ -114,7 +114,7 @@ class QuantizedLinear(nn.Module):
         key = (self.packed_weight.data_ptr(), self.scales.data_ptr(), self.packed_weight._version, self.scales._version)
         if self._eoq is None or self._eoq_key != key:
             with torch.cuda.device(self.packed_weight.device):
-                self._eoq = EOQWeight.from_int4_packed(self.packed_weight, self.scales, self.in_features, group=self.block_size)
+                self._eoq = EOQWeight.from_packed(self.packed_weight, self.scales, self.in_features, self.bits, group=self.block_size)
             self._eoq_key = key
         return self._eoq
 
@@ -136,7 +136,7 @@ class QuantizedLinear(nn.Module):
             # activations, one dequantisation amortises over enough rows for a library GEMM to win
             if rows <= 8:
                 return self.eoq_weight().gemv(x, self.bias_param)
-            if x.dtype != torch.float32:
+            if x.dtype != torch.float32 and self.bits == 4:          # the tensor-core kernel is built for the 4-bit layout
                 return self.eoq_weight().gemm(x, self.bias_param)
         weight = dequant_packed(self.packed_weight, self.scales, self.out_features, self.in_features, self.bits,
                                 self.block_size, dtype=x.dtype if x.dtype in (torch.float16, torch.bfloat16) else torch.float32)

@@ -667,6 +667,7 @@ struct eoq_b200_weight {
     size_t pair_partial_bytes = 0;
     DeviceBuf table, tiles, stream, scales, centroids, partials, counters, status, xbuf, ybuf, biasbuf;
     DeviceBuf gemm_x, gemm_partials, gemm_counters;   // scratch of the tensor-core path, allocated by its first call
+    uint32_t gemm_rows = 0;                           // activation rows per pass that scratch was sized for
     // The status word the kernels set when a bounded wait expires lives in pinned host memory that the device writes
     // directly (pinned allocations are device-addressable): a healthy launch never touches it, and reading it after a
     // stream synchronise needs no copy.  Debug builds with per-warp time stamps keep it at the head of a device buffer.
@@ -687,13 +688,26 @@ struct eoq_b200_weight {
 
 namespace {
 
+uint32_t public_kind(uint32_t family, uint32_t bits)
+{
+    if (family != EOQ_B200_KIND_INT4_ABSMAX) return family;
+    return bits == 2 ? EOQ_B200_KIND_INT2_ABSMAX : bits == 3 ? EOQ_B200_KIND_INT3_ABSMAX : bits == 8 ? EOQ_B200_KIND_INT8_ABSMAX : EOQ_B200_KIND_INT4_ABSMAX;
+}
+
 eoq_error_t resolve_opts(const eoq_b200_weight_opts_t *o, uint32_t &bits, uint32_t &G, uint32_t &p, uint32_t &target, uint8_t &pad)
 {
     if (!o) return EOQ_ERR_NULL_PTR;
     if (o->kind == EOQ_B200_KIND_INT4_ABSMAX) { bits = 4; G = o->symbols_per_step ? o->symbols_per_step : 3; pad = 7; }
     else if (o->kind == EOQ_B200_KIND_Q5_POLAR) { bits = 5; G = o->symbols_per_step ? o->symbols_per_step : 2; pad = 16; if (!o->centroids) return EOQ_ERR_NULL_PTR; }
+    else if (o->kind == EOQ_B200_KIND_INT2_ABSMAX || o->kind == EOQ_B200_KIND_INT3_ABSMAX || o->kind == EOQ_B200_KIND_INT8_ABSMAX) {
+        // the other widths the reference's packers know (core/weight_packing.py:35-51): one layout each
+        bits = o->kind == EOQ_B200_KIND_INT2_ABSMAX ? 2 : o->kind == EOQ_B200_KIND_INT3_ABSMAX ? 3 : 8;
+        const uint32_t g = bits == 8 ? 1 : 3;
+        if (o->symbols_per_step && o->symbols_per_step != g) return EOQ_ERR_UNSUPPORTED;
+        G = g; pad = (uint8_t)((1u << (bits - 1)) - 1u);
+    }
     else return EOQ_ERR_UNSUPPORTED;
-    if (G < 1 || G > (bits == 4 ? 3u : 2u)) return EOQ_ERR_UNSUPPORTED;
+    if (G < 1 || G > (bits <= 4 ? 3u : bits == 8 ? 1u : 2u)) return EOQ_ERR_UNSUPPORTED;
     p = o->precision_bits ? o->precision_bits : std::min(16u, std::max(12u, bits * G + 1));   // INT4 x 3: 13 bits, a 32 KB table
     if (p > 14 || p < bits * G) return EOQ_ERR_UNSUPPORTED;        // table must fit shared memory beside x
     target = o->target_tiles;
@@ -716,7 +730,7 @@ eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const 
     w->partial_bytes = tw.nseg > 1 ? (size_t)tw.nseg * tw.Npad * 8 * sizeof(float) : 0;
     // INT4 x 3 weights run through the pair kernel, which meets in a few partial rows; the ring kernel's scratch (one
     // row per column segment) is allocated by the first call that needs it (see ring_scratch)
-    const bool pairs_layout = tw.kind == EOQ_B200_KIND_INT4_ABSMAX && tw.G == 3;
+    const bool pairs_layout = tw.kind == EOQ_B200_KIND_INT4_ABSMAX && tw.bits == 4 && tw.G == 3;
     if (w->table.alloc(tw.table.size() * 4) != cudaSuccess || w->tiles.alloc(tw.tiles.size() * sizeof(TileDesc)) != cudaSuccess ||
         w->stream.alloc(tw.stream.size()) != cudaSuccess || w->scales.alloc(w->scale_bytes) != cudaSuccess ||
         (!pairs_layout && w->partials.alloc(w->partial_bytes) != cudaSuccess) || w->counters.alloc((size_t)tw.nrb * 4) != cudaSuccess ||
@@ -779,7 +793,7 @@ extern "C" eoq_error_t eoq_b200_tiles_build(const uint8_t *symbols, const eoq_b2
         const int sms = have_device() ? device_sm_count() : 0;
         const uint32_t warps = (uint32_t)(sms > 0 ? sms : 148) * 16;      // one wave of 16-warp CTAs
         target = warps;
-        if (opts->kind == EOQ_B200_KIND_INT4_ABSMAX && G == 3) {
+        if (opts->kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 4 && G == 3) {
             // The pair kernel gives every warp two vertically adjacent tiles and stages them whole in shared memory,
             // which holds tiles of up to 7 x 16 columns: take the fewest waves of pairs whose column segments are
             // that narrow, and as many segments as fill those waves.
@@ -794,7 +808,9 @@ extern "C" eoq_error_t eoq_b200_tiles_build(const uint8_t *symbols, const eoq_b2
         }
     }
     std::unique_ptr<eoq_b200_tiles> t(new eoq_b200_tiles());
-    rc = build_tiled(symbols, opts->rows, opts->cols, bits, G, p, opts->group, opts->kind, target, pad, t->tw);
+    // inside the library the integer widths are one family (the kernels are templated on the field width)
+    const uint32_t family = opts->kind == EOQ_B200_KIND_Q5_POLAR ? EOQ_B200_KIND_Q5_POLAR : EOQ_B200_KIND_INT4_ABSMAX;
+    rc = build_tiled(symbols, opts->rows, opts->cols, bits, G, p, opts->group, family, target, pad, t->tw);
     if (rc != EOQ_OK) return rc;
     *out = t.release();
     return EOQ_OK;
@@ -804,7 +820,7 @@ extern "C" eoq_error_t eoq_b200_tiles_view(const eoq_b200_tiles_t *t, eoq_b200_t
 {
     if (!t || !v) return EOQ_ERR_NULL_PTR;
     const TiledWeights &tw = t->tw;
-    v->rows = tw.N; v->cols = tw.K; v->padded_rows = tw.Npad; v->group = tw.group; v->kind = tw.kind; v->bits = tw.bits;
+    v->rows = tw.N; v->cols = tw.K; v->padded_rows = tw.Npad; v->group = tw.group; v->kind = public_kind(tw.kind, tw.bits); v->bits = tw.bits;
     v->symbols_per_step = tw.G; v->precision_bits = tw.p;
     v->num_tiles = (uint32_t)tw.tiles.size(); v->num_col_segments = tw.nseg;
     v->table = tw.table.data();
@@ -879,7 +895,7 @@ extern "C" void eoq_b200_weight_destroy(eoq_b200_weight_t *w) { delete w; }
 extern "C" eoq_error_t eoq_b200_weight_info(const eoq_b200_weight_t *w, eoq_b200_weight_info_t *info)
 {
     if (!w || !info) return EOQ_ERR_NULL_PTR;
-    info->rows = w->N; info->cols = w->K; info->padded_rows = w->Npad; info->group = w->group; info->kind = w->kind;
+    info->rows = w->N; info->cols = w->K; info->padded_rows = w->Npad; info->group = w->group; info->kind = public_kind(w->kind, w->bits);
     info->symbols_per_step = w->G; info->precision_bits = w->p; info->alphabet = w->alphabet;
     info->num_tiles = w->ntiles; info->num_col_segments = w->nseg;
     info->stream_bytes = w->stream_bytes;
@@ -971,18 +987,29 @@ extern "C" eoq_error_t eoq_b200_gemm(eoq_b200_weight_t *w, const void *x, int x_
     eoq_error_t drc = check_device(w, "eoq_b200_gemm");
     if (drc != EOQ_OK) return drc;
     static const size_t esz[3] = {2, 2, 4};
+    const uint32_t per_pass = std::min(m, kGemmRowsPerPass);
     {
         std::lock_guard<std::mutex> lock(w->mu);
-        if (!w->gemm_x.p) {
-            // fp16 copy of up to 128 fp32 or bf16 activation rows, one fp32 partial tile pair per CTA, one arrival counter per row block
-            CU_TRY(w->gemm_x.alloc((size_t)128 * w->K * 2));
-            CU_TRY(w->gemm_partials.alloc(gemm_partial_bytes(gemm_grid(w->nrb, w->nseg))));
+        if (!w->gemm_x.p || w->gemm_rows < per_pass) {
+            // fp16 copy of one pass of fp32 or bf16 activation rows, one fp32 partial tile pair per CTA and 128-row token tile, one
+            // arrival counter per row block.  Sized by the rows of a pass; a later call with more rows allocates again (outside
+            // stream capture), after everything queued on the old scratch has finished.
+            if (w->gemm_x.p) {
+                CU_TRY(cudaDeviceSynchronize());
+                cudaFree(w->gemm_x.p); w->gemm_x.p = nullptr;
+                cudaFree(w->gemm_partials.p); w->gemm_partials.p = nullptr;
+                cudaFree(w->gemm_counters.p); w->gemm_counters.p = nullptr;
+            }
+            const uint32_t rows = per_pass <= 128 ? 128 : kGemmRowsPerPass;
+            CU_TRY(w->gemm_x.alloc((size_t)rows * w->K * 2));
+            CU_TRY(w->gemm_partials.alloc(gemm_partial_bytes(gemm_grid(w->nrb, w->nseg), rows)));
             CU_TRY(w->gemm_counters.alloc((size_t)w->nrb * 4));
             CU_TRY(cudaMemset(w->gemm_counters.p, 0, (size_t)w->nrb * 4));
+            w->gemm_rows = rows;
         }
     }
-    for (uint32_t m0 = 0; m0 < m; m0 += 128) {     // 128 activation rows share one pass over the compressed weight
-        const uint32_t mb = std::min(128u, m - m0);
+    for (uint32_t m0 = 0; m0 < m; m0 += kGemmRowsPerPass) {     // up to 512 activation rows share one pass over the compressed weight
+        const uint32_t mb = std::min(kGemmRowsPerPass, m - m0);
         int e = launch_gemm_tc(w->table.as<uint32_t>(), w->tiles.as<TileDesc>(), w->stream.as<uint8_t>(), w->scales_t.as<uint2>(),
                                static_cast<const uint8_t *>(x) + (size_t)m0 * w->K * esz[x_dtype], w->gemm_x.p,
                                w->gemm_partials.as<float>(), w->gemm_counters.as<uint32_t>(),
@@ -1202,7 +1229,7 @@ extern "C" eoq_error_t eoq_b200_weight_decode(eoq_b200_weight_t *w, uint8_t *d_s
     if (!w) return EOQ_ERR_NULL_PTR;
     if (!d_sym && !d_dequant) return EOQ_OK;
     if (packed && w->bits != 4) return EOQ_ERR_UNSUPPORTED;
-    if (d_dequant && w->kind != EOQ_B200_KIND_INT4_ABSMAX) return EOQ_ERR_UNSUPPORTED;
+    if (d_dequant && w->kind != EOQ_B200_KIND_INT4_ABSMAX) return EOQ_ERR_UNSUPPORTED;      // any integer width dequantises; polar does not
     if (out_dtype < 0 || out_dtype > 2) return EOQ_ERR_UNSUPPORTED;
     eoq_error_t drc = check_device(w, "eoq_b200_weight_decode");
     if (drc != EOQ_OK) return drc;
@@ -1222,10 +1249,10 @@ extern "C" eoq_error_t eoq_b200_dequant_packed(const uint8_t *d_packed, const ui
                                                uint32_t bits, uint32_t group, uint32_t row_lo, uint32_t row_hi, void *d_out,
                                                int out_dtype, void *stream)
 {
-    if (!d_packed || !d_scales_fp16 || !d_out) return EOQ_ERR_NULL_PTR;
+    if (!d_packed || !d_out || (!d_scales_fp16 && out_dtype != EOQ_B200_I8)) return EOQ_ERR_NULL_PTR;   // codes alone need no scales
     if (bits < 2 || bits > 8 || group == 0 || cols == 0) return EOQ_ERR_INVALID_HEADER;
     if (row_lo > row_hi || row_hi > rows) return EOQ_ERR_INVALID_HEADER;
-    if (out_dtype < 0 || out_dtype > 2) return EOQ_ERR_UNSUPPORTED;
+    if (out_dtype < 0 || out_dtype > EOQ_B200_I8) return EOQ_ERR_UNSUPPORTED;
     if (!have_device()) return EOQ_ERR_CUDA;
     // row stride of QuantizedLinear.packed_weight (core/quantized_linear.py:49-66)
     const uint32_t row_bytes = bits == 4 ? (cols + 1) / 2 : bits == 2 ? (cols + 3) / 4 : cols;

@@ -10,6 +10,18 @@
 
 #include "../../include/eoq_b200.h"
 
+// Exported for this project's own benchmarks and tests, not part of the public interface:
+// eoq_b200_tune sets a diagnostic knob and returns 0 if the key is known --
+//   "gemv_ctas_per_sm" (0 = as many CTAs of the one-tile-per-warp GEMV kernel as fit on an SM),
+//   "gemv_pairs" (1 = 4-bit weights with three symbols per step run through the kernel that decodes two tiles per
+//                 warp, the default; 0 = always the one-tile-per-warp kernel),
+//   "gemm_warps" (warps per CTA of the tensor-core kernel, 2..16; 0 = as many as fit),
+//   "pdl" (1 = programmatic stream serialisation for the fused kernels, the default; 0 = plain launches),
+//   "v1_lanes" (1 = the lane-per-block wire-format decoder, the default; 0 = the one-thread-per-block kernel);
+// eoq_b200_launch_count is the number of kernels this library has launched since it was loaded.
+extern "C" int eoq_b200_tune(const char *key, int value);
+extern "C" uint64_t eoq_b200_launch_count(void);
+
 namespace eoq {
 
 // ---------------------------------------------------------------------------
@@ -181,7 +193,8 @@ int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *
                    uint32_t K, uint32_t group, uint32_t p, uint32_t nseg, uint32_t nrb, uint32_t head_bytes, uint32_t M, int x_dtype, int y_dtype,
                    void *stream_);
 uint32_t gemm_grid(uint32_t nrb, uint32_t nseg);
-size_t gemm_partial_bytes(uint32_t grid);
+size_t gemm_partial_bytes(uint32_t grid, uint32_t m);
+constexpr uint32_t kGemmRowsPerPass = 512;      // activation rows one launch of the tensor-core kernel takes
 size_t gemv_smem_bytes(uint32_t K, uint32_t p, uint32_t bt, uint32_t kind);
 uint64_t launch_counter();
 void set_gemv_ctas_per_sm(int v);

@@ -79,19 +79,22 @@ struct Fmt {
 //            once per scale group (the product is exact in fp32, and the sums
 //            cancel to ~2^-15 relative);
 //   b <  15: the constant would swamp the sum, so subtract it first (exact).
-template <int B>
+// The same holds for fields of any width (2-, 3-, 8-bit symmetric codes: symbol = code + qmax, qmax = 2^(bits-1) - 1).
+template <int B, int BITS = 4>
 struct Int4Field {
-    static constexpr uint32_t kMask = 0xFu << B;
+    static constexpr uint32_t kMask = ((1u << BITS) - 1u) << B;
     static constexpr uint32_t kMagic = (uint32_t)(150 - B) << 23;       // exponent of 2^(23-B)
     static constexpr float kBase = (float)(1u << (23 - B));
+    static constexpr float kQmax = (float)((1u << (BITS - 1)) - 1u);
+    static constexpr float kOffset = kBase + kQmax;                     // the float that stands for code 0
     static constexpr bool kPreSubtract = B < 15;
-    static constexpr float kCorr = kPreSubtract ? 0.0f : kBase + 7.0f;
+    static constexpr float kCorr = kPreSubtract ? 0.0f : kOffset;
     // `magic` is kMagic held in a register: the mask is the instruction's one immediate, so with the
     // exponent in a register the extraction stays a single LOP3
     __device__ __forceinline__ static float value(uint32_t e, uint32_t magic)
     {
         float m = __uint_as_float((e & kMask) | magic);
-        if (kPreSubtract) m -= kBase + 7.0f;
+        if (kPreSubtract) m -= kOffset;
         return m;
     }
     __device__ __forceinline__ static uint32_t magic_reg()
@@ -459,9 +462,10 @@ __device__ __forceinline__ void gemv_tile_columns(const GemvArgs &a, const TileD
                                                   uint32_t sgroups, uint32_t &x, WordState &ws, RingCtlT<R> &ring, float (&y)[G][BT])
 {
     using F = Fmt<G, BITS>;
-    const uint32_t magic0 = Int4Field<F::field_bit(0)>::magic_reg();
-    const uint32_t magic1 = Int4Field<F::field_bit(G > 1 ? 1 : 0)>::magic_reg();
-    const uint32_t magic2 = Int4Field<F::field_bit(G > 2 ? 2 : 0)>::magic_reg();
+    constexpr int kFB = KIND == EOQ_B200_KIND_INT4_ABSMAX ? BITS : 4;      // field width of the integer kinds
+    const uint32_t magic0 = Int4Field<F::field_bit(0), kFB>::magic_reg();
+    const uint32_t magic1 = Int4Field<F::field_bit(G > 1 ? 1 : 0), kFB>::magic_reg();
+    const uint32_t magic2 = Int4Field<F::field_bit(G > 2 ? 2 : 0), kFB>::magic_reg();
     const uint32_t tab_addr = smem_addr(tab);
         uint32_t c = d.col0;
         const uint32_t cend = c + d.ncols;
@@ -511,27 +515,27 @@ __device__ __forceinline__ void gemv_tile_columns(const GemvArgs &a, const TileD
                         }
                     }
                     if (KIND == EOQ_B200_KIND_INT4_ABSMAX) {
-                        using F0 = Int4Field<F::field_bit(0)>;
-                        using F1 = Int4Field<F::field_bit(G > 1 ? 1 : 0)>;
-                        using F2 = Int4Field<F::field_bit(G > 2 ? 2 : 0)>;
+                        using F0 = Int4Field<F::field_bit(0), kFB>;
+                        using F1 = Int4Field<F::field_bit(G > 1 ? 1 : 0), kFB>;
+                        using F2 = Int4Field<F::field_bit(G > 2 ? 2 : 0), kFB>;
                         constexpr uint32_t kM1 = (G > 1) ? F1::kMask : 0u, kM2 = (G > 2) ? F2::kMask : 0u;
                         uint32_t u0, u1, u2;
                         rans_step_int4<F0::kMask, kM1, kM2>(tab_addr, x, mask, p, F::kBiasMask, magic0, magic1, magic2, u0, u1, u2);
                         {
                             float m = __uint_as_float(u0);
-                            if (F0::kPreSubtract) m -= F0::kBase + 7.0f;
+                            if (F0::kPreSubtract) m -= F0::kOffset;
 #pragma unroll
                             for (int b = 0; b < BT; b++) acc[0][b] = fmaf(m, xv[s][b], acc[0][b]);
                         }
                         if (G > 1) {
                             float m = __uint_as_float(u1);
-                            if (F1::kPreSubtract) m -= F1::kBase + 7.0f;
+                            if (F1::kPreSubtract) m -= F1::kOffset;
 #pragma unroll
                             for (int b = 0; b < BT; b++) acc[G > 1 ? 1 : 0][b] = fmaf(m, xv[s][b], acc[G > 1 ? 1 : 0][b]);
                         }
                         if (G > 2) {
                             float m = __uint_as_float(u2);
-                            if (F2::kPreSubtract) m -= F2::kBase + 7.0f;
+                            if (F2::kPreSubtract) m -= F2::kOffset;
 #pragma unroll
                             for (int b = 0; b < BT; b++) acc[G > 2 ? 2 : 0][b] = fmaf(m, xv[s][b], acc[G > 2 ? 2 : 0][b]);
                         }
@@ -559,9 +563,9 @@ __device__ __forceinline__ void gemv_tile_columns(const GemvArgs &a, const TileD
                 for (uint32_t u = rstart / 16; u < rend / 16; u++)
 #pragma unroll
                     for (int b = 0; b < BT; b++) rs[b] += aux[u * BT + b];
-                const float corr[3] = {Int4Field<F::field_bit(0)>::kCorr,
-                                       Int4Field<F::field_bit(G > 1 ? 1 : 0)>::kCorr,
-                                       Int4Field<F::field_bit(G > 2 ? 2 : 0)>::kCorr};
+                const float corr[3] = {Int4Field<F::field_bit(0), kFB>::kCorr,
+                                       Int4Field<F::field_bit(G > 1 ? 1 : 0), kFB>::kCorr,
+                                       Int4Field<F::field_bit(G > 2 ? 2 : 0), kFB>::kCorr};
 #pragma unroll
                 for (int j = 0; j < G; j++)
 #pragma unroll
@@ -1803,6 +1807,10 @@ int launch_gemv(const GemvArgs &a, uint32_t G, uint32_t bits, uint32_t kind, voi
         if (G == 2) return launch_gemv_bt<2, 4, EOQ_B200_KIND_INT4_ABSMAX>(a, st);
         if (G == 3) return launch_gemv_bt<3, 4, EOQ_B200_KIND_INT4_ABSMAX>(a, st);
     }
+    // the other symmetric integer codes (kernels are templated on the field width; the kind tag is the integer family's)
+    if (kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 2 && G == 3) return launch_gemv_bt<3, 2, EOQ_B200_KIND_INT4_ABSMAX>(a, st);
+    if (kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 3 && G == 3) return launch_gemv_bt<3, 3, EOQ_B200_KIND_INT4_ABSMAX>(a, st);
+    if (kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 8 && G == 1) return launch_gemv_bt<1, 8, EOQ_B200_KIND_INT4_ABSMAX>(a, st);
     if (kind == EOQ_B200_KIND_Q5_POLAR && bits == 5) {
         if (G == 1) return launch_gemv_bt<1, 5, EOQ_B200_KIND_Q5_POLAR>(a, st);
         if (G == 2) return launch_gemv_bt<2, 5, EOQ_B200_KIND_Q5_POLAR>(a, st);
@@ -1954,7 +1962,7 @@ __global__ void __launch_bounds__(256) decode_tiles_kernel(const DecodeArgs a)
                     const float sc = half_bits_to_float(__ldg(a.scales + (size_t)r * sgroups + c / a.group));
                     float v[16];
 #pragma unroll
-                    for (int s = 0; s < 16; s++) v[s] = (float)((int)sym[j][s] - 7) * sc;
+                    for (int s = 0; s < 16; s++) v[s] = (float)((int)sym[j][s] - (int)((1u << (BITS - 1)) - 1u)) * sc;
                     const size_t o = (size_t)r * K + c;
                     if (a.out_dtype == EOQ_B200_F32) {
                         float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(a.out_deq) + o);
@@ -2007,6 +2015,9 @@ int launch_decode_tiles(const DecodeArgs &a, uint32_t G, uint32_t bits, uint32_t
         if (G == 2) return launch_decode_tiles_t<2, 4, EOQ_B200_KIND_INT4_ABSMAX>(a, st);
         if (G == 3) return launch_decode_tiles_t<3, 4, EOQ_B200_KIND_INT4_ABSMAX>(a, st);
     }
+    if (kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 2 && G == 3) return launch_decode_tiles_t<3, 2, EOQ_B200_KIND_INT4_ABSMAX>(a, st);
+    if (kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 3 && G == 3) return launch_decode_tiles_t<3, 3, EOQ_B200_KIND_INT4_ABSMAX>(a, st);
+    if (kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 8 && G == 1) return launch_decode_tiles_t<1, 8, EOQ_B200_KIND_INT4_ABSMAX>(a, st);
     if (kind == EOQ_B200_KIND_Q5_POLAR && bits == 5) {
         if (G == 1) return launch_decode_tiles_t<1, 5, EOQ_B200_KIND_Q5_POLAR>(a, st);
         if (G == 2) return launch_decode_tiles_t<2, 5, EOQ_B200_KIND_Q5_POLAR>(a, st);
@@ -2525,7 +2536,8 @@ __global__ void dequant_packed_kernel(const uint8_t *__restrict__ packed, const 
         else if (bits == 2) code = (int)((rowp[c >> 2] >> ((c & 3) * 2)) & 0x3) - 1;
         else code = (int)(int8_t)rowp[c];
         const uint64_t flat = (uint64_t)r * K + c;
-        store_y(out, i, (float)code * half_bits_to_float(__ldg(scales + flat / group)), out_dtype);
+        if (out_dtype == EOQ_B200_I8) reinterpret_cast<int8_t *>(out)[i] = (int8_t)code;          // the codes themselves, no scale
+        else store_y(out, i, (float)code * half_bits_to_float(__ldg(scales + flat / group)), out_dtype);
     }
 }
 
@@ -2566,20 +2578,22 @@ int launch_dequant_packed(const uint8_t *packed, const uint16_t *scales, uint32_
 // ---------------------------------------------------------------------------
 constexpr int kGemmMaxThreads = 512;
 constexpr uint32_t kGemmTokens = 128, kGemmRows = 96;
+constexpr uint32_t kGemmMaxM = 512;          // activation rows one pass takes: up to four 128-row tiles share every decoded piece
 constexpr uint32_t kXPieceBytes = kGemmTokens * 16 * 2, kWPieceBytes = kGemmRows * 16 * 2;
 constexpr uint32_t kGemmAccs = 4, kTmemCols = 128 * kGemmAccs;   // four accumulators, 128 columns apart (96 used): all of TMEM
 constexpr uint32_t kGemmMaxContrib = 160, kGemmCtlBytes = 384 + 2 * kGemmMaxContrib * 4;   // 1664: keeps the pieces 128-byte aligned
 constexpr uint32_t kGemmSlotFloats = kGemmTokens * kGemmRows;
 
-// bytes of one warp's X staging piece: the staged token rows, rounded up to 8
-__host__ __device__ inline uint32_t gemm_x_stride(uint32_t m) { return ((m + 7u) & ~7u) * 32u; }
+// bytes of one warp's X staging piece: up to 128 token rows rounded up to 8; more rows are staged as whole 128-row tiles
+__host__ __device__ inline uint32_t gemm_x_stride(uint32_t m) { return m <= kGemmTokens ? ((m + 7u) & ~7u) * 32u : ((m + 127u) / 128u) * kXPieceBytes; }
+__host__ __device__ inline uint32_t gemm_m_tiles(uint32_t m) { return (m + kGemmTokens - 1u) / kGemmTokens; }
 
 size_t gemm_smem_bytes(uint32_t p, uint32_t warps, uint32_t m)
 {
     // the last warp's MMA reads a full 128-row piece: keep that much behind the last staged piece
     return smem_table_bytes(p) + kGemmCtlBytes + (size_t)warps * (kWPieceBytes + gemm_x_stride(m)) + kXPieceBytes + ring_smem_bytes<RingSmall>(warps);
 }
-size_t gemm_partial_bytes(uint32_t grid) { return (size_t)grid * 2 * kGemmSlotFloats * sizeof(float); }
+size_t gemm_partial_bytes(uint32_t grid, uint32_t m) { return (size_t)grid * 2 * gemm_m_tiles(m) * kGemmSlotFloats * sizeof(float); }
 
 // K-major, no-swizzle shared-memory matrix descriptor: start address, leading (K) and stride (row-group) byte offsets
 // in units of 16 bytes, descriptor version 1.
@@ -2648,13 +2662,18 @@ struct GemmWarp {             // per warp, warp-uniform
 // Two tiled bulk copies bring one X piece: box = [rows of the batch rounded up to 8] x [8 columns = 16 bytes] each, so
 // that shared memory holds it as K-major core matrices (8 rows x 16 bytes, contiguous); rows past the batch are
 // filled with zeros by the copy.  Columns c..c+7 land at dst, c+8..c+15 behind them.
-__device__ __forceinline__ void gemm_fetch_x(const CUtensorMap *xmap, uint32_t dst, uint32_t half_bytes, uint32_t c, uint32_t bar)
+// With more than 128 token rows the same is done once per 128-row tile (rows past the batch of the last tile read as zeros).
+__device__ __forceinline__ void gemm_fetch_x(const CUtensorMap *xmap, uint32_t dst, uint32_t half_bytes, uint32_t c, uint32_t bar,
+                                             uint32_t m_tiles)
 {
-    mbar_expect_tx(bar, 2u * half_bytes);
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(xmap)), "r"(c), "r"(0), "r"(bar) : "memory");
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst + half_bytes), "l"(reinterpret_cast<uint64_t>(xmap)), "r"(c + 8u), "r"(0), "r"(bar) : "memory");
+    mbar_expect_tx(bar, 2u * half_bytes * m_tiles);
+    for (uint32_t j = 0; j < m_tiles; j++) {
+        const uint32_t at = dst + j * 2u * half_bytes, row = j * kGemmTokens;
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                     ::"r"(at), "l"(reinterpret_cast<uint64_t>(xmap)), "r"(c), "r"(row), "r"(bar) : "memory");
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                     ::"r"(at + half_bytes), "l"(reinterpret_cast<uint64_t>(xmap)), "r"(c + 8u), "r"(row), "r"(bar) : "memory");
+    }
 }
 
 // Decode 16 columns of the warp's tile into its W piece.  A few steps in, once the previous MMA is known to have read
@@ -2662,7 +2681,8 @@ __device__ __forceinline__ void gemm_fetch_x(const CUtensorMap *xmap, uint32_t d
 template <bool RING>
 __device__ __forceinline__ void gemm_decode_piece(uint32_t tab_addr, uint32_t &x, WordState &ws, uint32_t mask, uint32_t p,
                                                   const float (&sc)[3], const GemmWarp &gw, const CUtensorMap *xmap, uint32_t c,
-                                                  uint32_t x_half_bytes, uint32_t lane, uint32_t *status, bool &dead, long long (&cyc)[4])
+                                                  uint32_t x_half_bytes, uint32_t m_tiles, uint32_t lane, uint32_t *status, bool &dead,
+                                                  long long (&cyc)[4])
 {
     using F = Fmt<3, 4>;
     using F0 = Int4Field<F::field_bit(0)>;
@@ -2685,7 +2705,7 @@ __device__ __forceinline__ void gemm_decode_piece(uint32_t tab_addr, uint32_t &x
                 {
                     GEMM_CYC_BEGIN();
                     if (gw.np > 0) gemm_wait(gw.mma_bar, (gw.np - 1u) & 1u, status, dead);
-                    if (lane == 0) gemm_fetch_x(xmap, gw.xp, x_half_bytes, c, gw.x_bar);
+                    if (lane == 0) gemm_fetch_x(xmap, gw.xp, x_half_bytes, c, gw.x_bar, m_tiles);
                     __syncwarp();
                     GEMM_CYC_END(cyc[0]);
                 }
@@ -2733,12 +2753,13 @@ __device__ __forceinline__ void gemm_sum_partials(const GemmArgs &a, uint32_t rb
 {
     constexpr uint32_t kU = 6;                       // float4 loads in flight per thread and contributor
     const uint32_t nvec = a.M * (kGemmRows / 4);
+    const size_t slot_floats = (size_t)gemm_m_tiles(a.M) * kGemmSlotFloats;
     for (uint32_t v0 = threadIdx.x; v0 < nvec; v0 += blockDim.x * kU) {
         float4 acc[kU];
 #pragma unroll
         for (uint32_t u = 0; u < kU; u++) acc[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         for (uint32_t k = 0; k < n; k++) {
-            const float4 *src = reinterpret_cast<const float4 *>(a.partials + (size_t)contrib[k] * kGemmSlotFloats);
+            const float4 *src = reinterpret_cast<const float4 *>(a.partials + (size_t)contrib[k] * slot_floats);
             float4 t[kU];
 #pragma unroll
             for (uint32_t u = 0; u < kU; u++) {
@@ -2798,8 +2819,10 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
     const uint32_t rb_first = t_lo / a.nseg, rb_last = (t_hi - 1u) / a.nseg;
     RingCtlT<RingSmall> ring;
     ring_setup(ring, ring_area, warp, nwarps, lane, a.status);
+    // up to four 128-row token tiles share one decoded piece, each with its own accumulator: 4 / m_tiles row blocks in flight
+    const uint32_t m_tiles = gemm_m_tiles(a.M), rbs_in_flight = kGemmAccs / m_tiles;
     uint32_t tile = t_lo + warp;
-    const uint32_t g0_hi = min(t_hi, (rb_first + kGemmAccs) * a.nseg);
+    const uint32_t g0_hi = min(t_hi, (rb_first + rbs_in_flight) * a.nseg);
     bool have = tile < g0_hi;
     TileDesc d;
     if (have) d = a.tiles[tile];           // requested here, needed by tile_open below
@@ -2837,15 +2860,15 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
     gw.x_bar = x_bar0 + warp * 8;
     gw.np = 0;
     long long cyc[4] = {0, 0, 0, 0};      // debug builds: cycles in the per-piece synchronisation points
-    const uint32_t x_half_bytes = gemm_x_stride(a.M) / 2;      // one 8-column half of an X piece
+    const uint32_t x_half_bytes = gemm_x_stride(a.M) / (2u * m_tiles);      // one 8-column half of one token tile of an X piece
     // warps 0..7: warp w owns TMEM lanes 32*(w%4).. (tokens) and columns 48*(w/4).. (weight rows of a block) of every
     // accumulator; it clears them before a group and reads them back after it
     const uint32_t tok = (warp & 3u) * 32u + lane, col0 = (warp >> 2) * 48u;
     const uint32_t taddr_w = tmem_base + (((warp & 3u) * 32u) << 16) + col0;
 
     uint32_t grp = 0;
-    for (uint32_t rb0 = rb_first; t_lo < t_hi && rb0 <= rb_last; rb0 += kGemmAccs, grp++) {
-        const uint32_t g_lo = max(t_lo, rb0 * a.nseg), g_hi = min(t_hi, (rb0 + kGemmAccs) * a.nseg);
+    for (uint32_t rb0 = rb_first; t_lo < t_hi && rb0 <= rb_last; rb0 += rbs_in_flight, grp++) {
+        const uint32_t g_lo = max(t_lo, rb0 * a.nseg), g_hi = min(t_hi, (rb0 + rbs_in_flight) * a.nseg);
         const uint32_t nparts = (g_hi - 1u) / a.nseg - rb0 + 1u;
         if (grp > 0) {
             tile = g_lo + warp;
@@ -2857,7 +2880,7 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
         }
         __syncwarp();
         if (warp < 8) {
-            for (uint32_t pa = 0; pa < nparts; pa++)
+            for (uint32_t pa = 0; pa < nparts * m_tiles; pa++)
 #pragma unroll
                 for (uint32_t i = 0; i < 3; i++)
                     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
@@ -2870,7 +2893,7 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
 
         while (have) {
             const TileSrc base = tile_src(a.stream, a.head_bytes, tile, d);
-            const uint32_t d_tmem = tmem_base + (tile / a.nseg - rb0) * 128u;
+            const uint32_t d_tmem = tmem_base + (tile / a.nseg - rb0) * m_tiles * 128u;
             uint32_t x;
             WordState ws;
             const bool ring_mode = tile_begin(ring, ws, d, base, lane, x);
@@ -2906,9 +2929,9 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
                         ring_sync_step(ring, ws, lane);
                         GEMM_CYC_END(cyc[1]);
                     }
-                    gemm_decode_piece<true>(tab_addr, x, ws, mask, p, sc, gw, &xmap, c, x_half_bytes, lane, a.status, dead, cyc);
+                    gemm_decode_piece<true>(tab_addr, x, ws, mask, p, sc, gw, &xmap, c, x_half_bytes, m_tiles, lane, a.status, dead, cyc);
                 } else {
-                    gemm_decode_piece<false>(tab_addr, x, ws, mask, p, sc, gw, &xmap, c, x_half_bytes, lane, a.status, dead, cyc);
+                    gemm_decode_piece<false>(tab_addr, x, ws, mask, p, sc, gw, &xmap, c, x_half_bytes, m_tiles, lane, a.status, dead, cyc);
                 }
                 {
                     GEMM_CYC_BEGIN();
@@ -2920,8 +2943,10 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
                 {
                     GEMM_CYC_BEGIN();
                     if (lane == 0) {
-                        // X piece: 8-row groups 128 bytes apart, its two column halves x_half_bytes apart
-                        umma_f16(d_tmem, umma_desc(gw.xp, x_half_bytes, 128), umma_desc(gw.wp, 128, 256), idesc, 1u);
+                        // X piece: 8-row groups 128 bytes apart, its two column halves x_half_bytes apart; one MMA per token
+                        // tile, all on the same decoded W piece
+                        for (uint32_t j = 0; j < m_tiles; j++)
+                            umma_f16(d_tmem + j * 128u, umma_desc(gw.xp + j * 2u * x_half_bytes, x_half_bytes, 128), umma_desc(gw.wp, 128, 256), idesc, 1u);
                         umma_commit(gw.mma_bar);
                     }
                     __syncwarp();
@@ -2953,30 +2978,34 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
             const bool full = max(t_lo, rb * a.nseg) == rb * a.nseg && min(t_hi, (rb + 1) * a.nseg) == (rb + 1) * a.nseg;
             shared_any |= !full;
             if (warp < 8) {
-                float *slot = a.partials + ((size_t)blockIdx.x * 2 + (rb == rb_first ? 0u : 1u)) * kGemmSlotFloats + (size_t)tok * kGemmRows + col0;
+                const size_t slot_floats = (size_t)m_tiles * kGemmSlotFloats;
+                for (uint32_t j = 0; j < m_tiles; j++) {
+                    const uint32_t token = j * kGemmTokens + tok;
+                    float *slot = a.partials + ((size_t)blockIdx.x * 2 + (rb == rb_first ? 0u : 1u)) * slot_floats + (size_t)token * kGemmRows + col0;
 #pragma unroll
-                for (uint32_t i = 0; i < 3; i++) {
-                    uint32_t r[16];
-                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                                 : "r"(taddr_w + pa * 128u + i * 16u) : "memory");
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (tok < a.M) {
-                        if (full) {
-                            const uint32_t n0 = rb * kGemmRows + col0 + i * 16u;
-                            float v[16];
+                    for (uint32_t i = 0; i < 3; i++) {
+                        uint32_t r[16];
+                        asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                                       "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                                     : "r"(taddr_w + (pa * m_tiles + j) * 128u + i * 16u) : "memory");
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (token < a.M) {
+                            if (full) {
+                                const uint32_t n0 = rb * kGemmRows + col0 + i * 16u;
+                                float v[16];
 #pragma unroll
-                            for (uint32_t q = 0; q < 16; q++) v[q] = __uint_as_float(r[q]) + (a.bias && n0 + q < a.N ? __ldg(a.bias + n0 + q) : 0.0f);
-                            gemm_store16(a.y, (size_t)tok * a.N + n0, v, n0, a.N, a.y_dtype);
-                        } else {
+                                for (uint32_t q = 0; q < 16; q++) v[q] = __uint_as_float(r[q]) + (a.bias && n0 + q < a.N ? __ldg(a.bias + n0 + q) : 0.0f);
+                                gemm_store16(a.y, (size_t)token * a.N + n0, v, n0, a.N, a.y_dtype);
+                            } else {
 #pragma unroll
-                            for (uint32_t q = 0; q < 16; q += 4)
-                                __stcg(reinterpret_cast<float4 *>(slot + i * 16u + q),
-                                       make_float4(__uint_as_float(r[q]), __uint_as_float(r[q + 1]), __uint_as_float(r[q + 2]), __uint_as_float(r[q + 3])));
+                                for (uint32_t q = 0; q < 16; q += 4)
+                                    __stcg(reinterpret_cast<float4 *>(slot + i * 16u + q),
+                                           make_float4(__uint_as_float(r[q]), __uint_as_float(r[q + 1]), __uint_as_float(r[q + 2]), __uint_as_float(r[q + 3])));
+                            }
                         }
+                        __syncwarp();      // lanes past the batch skipped the stores: rejoin before the next aligned load
                     }
-                    __syncwarp();      // lanes past the batch skipped the stores: rejoin before the next aligned load
                 }
             }
         }
@@ -3046,7 +3075,7 @@ int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *
 {
     static std::mutex mu;
     static size_t attr_set[16] = {0};
-    if (M == 0 || M > kGemmTokens) return (int)cudaErrorInvalidValue;
+    if (M == 0 || M > kGemmMaxM) return (int)cudaErrorInvalidValue;
     uint32_t warps = 16;
     const int want = g_gemm_warps.load();
     if (want >= 2 && want <= 16) warps = (uint32_t)want;
@@ -3088,7 +3117,7 @@ int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *
     }
     CUtensorMap xmap;
     const cuuint64_t gdim[2] = {K, M}, gstride[1] = {(cuuint64_t)K * 2};
-    const cuuint32_t box[2] = {8, gemm_x_stride(M) / 32}, estride[2] = {1, 1};
+    const cuuint32_t box[2] = {8, M <= kGemmTokens ? gemm_x_stride(M) / 32 : kGemmTokens}, estride[2] = {1, 1};
     if (encode(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x16), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return (int)cudaErrorInvalidValue;

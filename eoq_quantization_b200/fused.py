@@ -15,6 +15,7 @@ import torch
 from . import _lib
 
 _DTYPES = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
+_I8 = 3        # EOQ_B200_I8: eoq_b200_dequant_packed writes the signed codes
 _NP_DTYPES = {np.dtype(np.float16): _lib.F16, np.dtype(np.float32): _lib.F32}
 
 
@@ -112,6 +113,22 @@ class EOQWeight:
         pk = packed.detach().cpu().numpy() if isinstance(packed, torch.Tensor) else np.asarray(packed)
         sym = np.stack([pk & 0x0F, pk >> 4], axis=-1).reshape(pk.shape[0], -1)[:, :in_features]
         return cls.from_symbols(sym, scales_fp16, kind=_lib.KIND_INT4_ABSMAX, group=group, **kw)
+
+    @classmethod
+    def from_packed(cls, packed, scales_fp16, in_features: int, bits: int, *, group: int = 128, **kw) -> "EOQWeight":
+        """packed: QuantizedLinear.packed_weight of any width the fused kernels serve (core/quantized_linear.py:49-66):
+        4 bits two per byte, 2 bits four per byte (low bits first), 3 and 8 bits one signed code per byte."""
+        if bits not in _lib.INT_KINDS:
+            raise ValueError(f"no fused layout for {bits}-bit weights")
+        pk = packed.detach().cpu().numpy() if isinstance(packed, torch.Tensor) else np.asarray(packed)
+        qmax = (1 << (bits - 1)) - 1
+        if bits == 4:
+            sym = np.stack([pk & 0x0F, pk >> 4], axis=-1).reshape(pk.shape[0], -1)
+        elif bits == 2:
+            sym = np.stack([(pk >> s) & 0x03 for s in (0, 2, 4, 6)], axis=-1).reshape(pk.shape[0], -1)
+        else:
+            sym = (pk.view(np.int8).astype(np.int16) + qmax).astype(np.uint8)
+        return cls.from_symbols(np.ascontiguousarray(sym[:, :in_features]), scales_fp16, kind=_lib.INT_KINDS[bits], group=group, **kw)
 
     @classmethod
     def from_rans(cls, rans_bytes: bytes, scales_fp16, shape, *, kind: int = _lib.KIND_INT4_ABSMAX, group: int = 128,
@@ -219,13 +236,15 @@ class EOQWeight:
 
 def dequant_packed(packed: torch.Tensor, scales: torch.Tensor, rows: int, cols: int, bits: int, group: int,
                    row_lo: int = 0, row_hi: Optional[int] = None, dtype: torch.dtype = torch.float32) -> torch.Tensor:
-    """Dense rows [row_lo, row_hi) of a packed QuantizedLinear weight, computed by the library's kernel."""
+    """Dense rows [row_lo, row_hi) of a packed QuantizedLinear weight, computed by the library's kernel; with
+    dtype torch.int8 the signed codes themselves (scales may then be None)."""
     require_cuda(packed, "dequant_packed")
     row_hi = rows if row_hi is None else row_hi
     pk = packed.contiguous()
-    sc = scales.to(device=packed.device, dtype=torch.float16).contiguous()
+    sc = None if scales is None else scales.to(device=packed.device, dtype=torch.float16).contiguous()
     out = torch.empty((row_hi - row_lo, cols), dtype=dtype, device=packed.device)
+    code = _I8 if dtype == torch.int8 else _DTYPES[dtype]
     with torch.cuda.device(packed.device):
-        _lib.check(_lib.lib().eoq_b200_dequant_packed(pk.data_ptr(), sc.data_ptr(), rows, cols, bits, group, row_lo, row_hi,
-                                                      out.data_ptr(), _DTYPES[dtype], _stream_ptr()), "eoq_b200_dequant_packed")
+        _lib.check(_lib.lib().eoq_b200_dequant_packed(pk.data_ptr(), sc.data_ptr() if sc is not None else None, rows, cols, bits, group,
+                                                      row_lo, row_hi, out.data_ptr(), code, _stream_ptr()), "eoq_b200_dequant_packed")
     return out

@@ -217,10 +217,16 @@ typedef struct eoq_b200_weight eoq_b200_weight_t;
 
 #define EOQ_B200_KIND_INT4_ABSMAX 0   /* w = (sym - 7) * scale[flat/group], core/quantized_linear.py:189-217 */
 #define EOQ_B200_KIND_Q5_POLAR    1   /* w_block = norm/sqrt(d) * (centroid[sym] @ H), core/polar_quant.py:216-264 */
+/* The other symmetric absmax widths a mixed-bit model uses (core/weight_packing.py:35-51, bits_fn of
+ * core/rans_bitpacked.py:161-251): symbol = code + qmax, qmax = 2^(bits-1) - 1, w = (sym - qmax) * scale. */
+#define EOQ_B200_KIND_INT2_ABSMAX 2   /* symbols 0..2,   three weights per rANS step */
+#define EOQ_B200_KIND_INT3_ABSMAX 3   /* symbols 0..6,   three weights per rANS step */
+#define EOQ_B200_KIND_INT8_ABSMAX 4   /* symbols 0..254, one weight per rANS step */
 
 #define EOQ_B200_F16  0
 #define EOQ_B200_BF16 1
 #define EOQ_B200_F32  2
+#define EOQ_B200_I8   3   /* eoq_b200_dequant_packed only: the signed codes, unscaled */
 
 typedef struct {
     uint32_t kind;             /* EOQ_B200_KIND_* */
@@ -405,7 +411,9 @@ eoq_error_t eoq_b200_weight_decode(eoq_b200_weight_t *w, uint8_t *d_symbols_or_p
 /* Dequantise QuantizedLinear's in-memory form on the GPU, any shape and any
  * bit width the reference stores (2 and 4 packed, others one int8 per code):
  * rows [row_lo, row_hi) of d_packed [rows, row_bytes] with scales indexed over
- * the flattened matrix -> dense [row_hi-row_lo, cols] in out_dtype.  Behind
+ * the flattened matrix -> dense [row_hi-row_lo, cols] in out_dtype; with
+ * out_dtype EOQ_B200_I8 the signed codes are written instead (int8, scales may
+ * be NULL: unpack_4bit_fast / unpack_2bit_fast, core/fast_dequant.py:9-44).  Behind
  * core/fast_dequant.py:47-87, core/quantized_matmul.py:123-225 and
  * QuantizedLinear._dequantize_weight (core/quantized_linear.py:189-217).
  * Device pointers; asynchronous. */
@@ -418,18 +426,6 @@ eoq_error_t eoq_b200_dequant_packed(const uint8_t *d_packed, const uint16_t *d_s
  * The kernels never spin without a limit, so a fault in the copy engine ends in this error
  * rather than in a hang. */
 eoq_error_t eoq_b200_weight_status(eoq_b200_weight_t *w, void *stream);
-
-/* Diagnostic knob for sweeps; returns 0 if the key is known.  Keys:
- * "gemv_ctas_per_sm" (0 = as many CTAs of the one-tile-per-warp GEMV kernel as fit on an SM),
- * "gemv_pairs" (1 = INT4 weights with three symbols per step run through the kernel that decodes two
- * tiles per warp, the default; 0 = always the one-tile-per-warp kernel),
- * "gemm_warps" (warps per CTA of the tensor-core kernel, 2..16; 0 = as many as fit),
- * "pdl" (1 = launch the fused kernels with programmatic stream serialisation so that their
- * set-up overlaps the previous kernel's tail, the default; 0 = plain launches). */
-int eoq_b200_tune(const char *key, int value);
-
-/* Number of kernels launched by this library since load (for benchmarks). */
-uint64_t eoq_b200_launch_count(void);
 
 #ifdef __cplusplus
 }

@@ -110,3 +110,56 @@ def test_polar_linear_matches_the_reference_dequantised_weight():
     x = torch.from_numpy(rng.standard_normal((2, 256)).astype(np.float32)).cuda()
     assert O.rel_l2(other(x).float().cpu().numpy(), x.cpu().numpy() @ dense4.T) < 2e-3
     assert "vram=" in repr(other) and other.vram_bytes() > 0
+
+
+@pytest.mark.parametrize("bits", [2, 3, 8])
+def test_other_integer_widths_stay_on_the_fused_path(bits):
+    """Mixed-bit models (bits_fn of core/rans_bitpacked.py:161-251) quantise some tensors to 2, 3 or 8 bits: their
+    symbols are tiled and entropy-coded like the 4-bit ones and run through the same fused decode + GEMV.  Checked
+    against the reference's own codes, scales and dequantised matrix (tests/golden/ref_tensor.npz)."""
+    from eoq_quantization_b200 import _lib as L
+    from eoq_quantization_b200.fused import EOQWeight
+    z = _z("ref_tensor")
+    key = f"bits{bits}"
+    codes = z[key + "/codes"].reshape(24, 256)
+    qmax = (1 << (bits - 1)) - 1
+    sym = (codes + qmax).astype(np.uint8)
+    s16 = np.frombuffer(z[key + "/scales_bytes"].tobytes(), np.float16)
+    w = EOQWeight.from_symbols(sym, s16, kind=L.INT_KINDS[bits])
+    assert w.info.kind == L.INT_KINDS[bits] and w.info.symbols_per_step == (1 if bits == 8 else 3)
+    assert np.array_equal(w.decode_symbols().cpu().numpy(), sym)
+    dense = z[key + "/dequant"].reshape(24, 256)
+    assert np.array_equal(w.dequantize(torch.float32).cpu().numpy(), dense)          # bit-exact with the reference's dequantize
+    rng = np.random.default_rng(bits)
+    for rows, dt in ((1, torch.float16), (2, torch.float32), (4, torch.bfloat16), (8, torch.float32)):
+        x = torch.from_numpy(rng.standard_normal((rows, 256)).astype(np.float32)).to(dt).cuda()
+        y = w.gemv(x, out_dtype=torch.float32)
+        want = x.float().cpu().numpy().astype(np.float64) @ dense.astype(np.float64).T
+        # narrow codes sit high in the float mantissa (the unpack is one logic instruction), which costs fp32 activations a
+        # few bits of headroom: 2e-5 at two bits, far inside the 1e-3 bar
+        assert O.rel_l2(y.cpu().numpy(), want) < 1e-4, (rows, dt)
+    # a larger matrix with several column segments and row blocks, against the oracle's quantiser
+    n, k = 500, 1536
+    wt = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    c2, s2 = O.quantize_absmax(wt, bits, 128)
+    w2 = EOQWeight.from_symbols((c2 + qmax).astype(np.uint8), s2.astype(np.float16), kind=L.INT_KINDS[bits])
+    dense2 = (c2.reshape(-1, 128) * s2.astype(np.float16).astype(np.float32)[:, None]).reshape(n, k)
+    x = torch.from_numpy(rng.standard_normal((3, k)).astype(np.float32)).cuda().half()
+    y = w2.gemv(x, out_dtype=torch.float32)
+    assert O.rel_l2(y.cpu().numpy(), x.float().cpu().numpy().astype(np.float64) @ dense2.astype(np.float64).T) < 1e-4
+    assert w2.status() == 0
+    assert w2.info.bits_per_weight < bits + 0.3
+
+
+def test_quantized_linear_of_other_widths_runs_fused():
+    from eoq_quantization_b200.core.quantized_linear import QuantizedLinear
+    torch.manual_seed(3)
+    lin = nn.Linear(512, 96, bias=True)
+    x = torch.randn(2, 512)
+    for bits in (2, 3, 8):
+        ql = QuantizedLinear.from_float(lin, bits=bits, block_size=128).cuda()
+        assert ql._fusable()
+        y = ql(x.cuda())
+        want = torch.nn.functional.linear(x.cuda(), ql._dequantize_weight(), ql.bias_param)
+        assert O.rel_l2(y.cpu().numpy(), want.cpu().numpy()) < 1e-4, bits
+        assert ql.eoq_weight().info.symbols_per_step == (1 if bits == 8 else 3)
