@@ -44,7 +44,7 @@ REPLICAS = 8                       # weight copies cycled through so that the wo
 WORKLOAD = "llama7b_mlp_pair_int4_g128_rans_b1"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the fused kernel, from the ncu capture
 # summarised under profiles/
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 22162176    # 11008 x 4096 launch
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 22170880    # 11008 x 4096 launch
 NCU_TRAFFIC_SOURCE = "profiles/gemv_pairs_kernel__llama7b_mlp_pair.md"
 SM_COUNT, SM_CLOCK_MHZ = 148, 1965
 # what one rANS step of a warp (32 lanes x 3 weights) costs inside the column loop of the fused kernel, from the ncu
@@ -995,7 +995,7 @@ def run_wire_decode(args):
             e1.record()
             torch.cuda.synchronize()
             return e0.elapsed_time(e1) / reps
-        reps = max(3, min(args.steps, 50))
+        reps = max(copies, min(args.steps, 50))                       # every copy is decoded at least once
         ms = timed(ours, reps)
         want = torch.from_numpy(sym.astype(np.uint8)).cuda()
         assert all(torch.equal(o, want) for o in d_outs), "decoded symbols differ from the encoder's input"

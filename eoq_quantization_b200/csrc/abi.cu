@@ -670,15 +670,11 @@ struct eoq_b200_weight {
     uint32_t gemm_rows = 0;                           // activation rows per pass that scratch was sized for
     // The status word the kernels set when a bounded wait expires lives in pinned host memory that the device writes
     // directly (pinned allocations are device-addressable): a healthy launch never touches it, and reading it after a
-    // stream synchronise needs no copy.  Debug builds with per-warp time stamps keep it at the head of a device buffer.
+    // stream synchronise needs no copy.
     uint32_t *status_host = nullptr, *status_dev = nullptr;
     uint32_t *status_word()
     {
-#ifdef EOQ_STAMPS
-        return status.as<uint32_t>();
-#else
         return status_dev;
-#endif
     }
     ~eoq_b200_weight() { if (status_host) cudaFreeHost(status_host); }
     size_t stream_bytes = 0, scale_bytes = 0, partial_bytes = 0;
@@ -708,7 +704,9 @@ eoq_error_t resolve_opts(const eoq_b200_weight_opts_t *o, uint32_t &bits, uint32
     }
     else return EOQ_ERR_UNSUPPORTED;
     if (G < 1 || G > (bits <= 4 ? 3u : bits == 8 ? 1u : 2u)) return EOQ_ERR_UNSUPPORTED;
-    p = o->precision_bits ? o->precision_bits : std::min(16u, std::max(12u, bits * G + 1));   // INT4 x 3: 13 bits, a 32 KB table
+    // INT4 x 3: 13 bits, a 32 KB table; 8-bit codes: 255 symbols want the finest table shared memory holds (at 12 bits the
+    // rare symbols would all be rounded up to a frequency of 1 and the stream would be larger than the codes)
+    p = o->precision_bits ? o->precision_bits : bits * G == 8 ? 14u : std::min(16u, std::max(12u, bits * G + 1));
     if (p > 14 || p < bits * G) return EOQ_ERR_UNSUPPORTED;        // table must fit shared memory beside x
     target = o->target_tiles;
     return EOQ_OK;
@@ -734,11 +732,7 @@ eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const 
     if (w->table.alloc(tw.table.size() * 4) != cudaSuccess || w->tiles.alloc(tw.tiles.size() * sizeof(TileDesc)) != cudaSuccess ||
         w->stream.alloc(tw.stream.size()) != cudaSuccess || w->scales.alloc(w->scale_bytes) != cudaSuccess ||
         (!pairs_layout && w->partials.alloc(w->partial_bytes) != cudaSuccess) || w->counters.alloc((size_t)tw.nrb * 4) != cudaSuccess ||
-#ifdef EOQ_STAMPS
-        w->status.alloc(4u << 20) != cudaSuccess ||
-#else
         w->status.alloc(4) != cudaSuccess ||
-#endif
         w->xbuf.alloc((size_t)8 * tw.K * 4) != cudaSuccess || w->ybuf.alloc((size_t)8 * tw.N * 4) != cudaSuccess ||
         w->biasbuf.alloc((size_t)tw.N * 4) != cudaSuccess)
         return EOQ_ERR_ALLOC;
@@ -1267,19 +1261,10 @@ extern "C" eoq_error_t eoq_b200_weight_status(eoq_b200_weight_t *w, void *stream
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     std::lock_guard<std::mutex> lock(w->mu);
     if (!w->status_host) return EOQ_ERR_ALLOC;
-#ifdef EOQ_STAMPS
-    CU_TRY(cudaMemcpyAsync(w->status_host, w->status.p, 4, cudaMemcpyDeviceToHost, st));
-#endif
     CU_TRY(cudaStreamSynchronize(st));
     return *static_cast<volatile uint32_t *>(w->status_host) ? EOQ_ERR_CUDA : EOQ_OK;
 }
 
-#ifdef EOQ_STAMPS
-extern "C" int eoq_b200_debug_read_stamps(eoq_b200_weight_t *w, void *host, size_t bytes)
-{
-    return cudaMemcpy(host, w->status.as<uint8_t>() + 64, bytes, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 extern "C" int eoq_b200_tune(const char *key, int value)
 {

@@ -40,26 +40,6 @@ int device_sm_count()
 #endif
 constexpr int kThreads = EOQ_GEMV_THREADS;
 
-// Debug builds only (-DEOQ_STAMPS): per-warp phase timestamps (ns) written behind the status word.
-#ifdef EOQ_STAMPS
-__device__ __forceinline__ unsigned long long stamp_now() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define EOQ_STAMP(slot) do { if (lane == 0) reinterpret_cast<unsigned long long *>(a.status + 16)[(size_t)(blockIdx.x * kWarps + warp) * 8 + (slot)] = stamp_now(); } while (0)
-#else
-#define EOQ_STAMP(slot) do { } while (0)
-#endif
-#ifdef EOQ_STAMPS
-#define GEMM_STAMP(slot) do { if (lane == 0) reinterpret_cast<unsigned long long *>(a.status + 16)[(size_t)(blockIdx.x * 16 + warp) * 8 + (slot)] = stamp_now(); } while (0)
-#define GEMM_CYC_BEGIN() const long long cyc0__ = clock64()
-#define GEMM_CYC_END(acc) (acc) += clock64() - cyc0__
-#define GEMM_CYC_WRITE(slot, v) do { if (lane == 0) reinterpret_cast<unsigned long long *>(a.status + 16)[(size_t)(148 * 16 + blockIdx.x * 16 + warp) * 8 + (slot)] = (unsigned long long)(v); } while (0)
-#else
-#define GEMM_STAMP(slot) do { } while (0)
-#define GEMM_CYC_BEGIN() do { } while (0)
-#define GEMM_CYC_END(acc) do { } while (0)
-#define GEMM_CYC_WRITE(slot, v) do { } while (0)
-#endif
-
-
 // ---------------------------------------------------------------------------
 // Table-entry geometry for G weights of BITS bits per rANS step.
 // ---------------------------------------------------------------------------
@@ -594,7 +574,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t K = a.K, M = 1u << a.p;
-    EOQ_STAMP(0);
     // Prologue: everything that has to come from global memory is requested before anything is waited for --
     // the decode table (one bulk copy onto a barrier), x (vector loads into registers) and this warp's first tile
     // (descriptor, L2 prefetch, first ring chunks) -- so the prologue costs about one memory round trip.
@@ -627,7 +606,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
             if (tid + u * kThreads < nvec) xq[u] = __ldg(reinterpret_cast<const uint4 *>(a.x) + tid + u * kThreads);
     }
     if (have) tile_open(ring, d, tile_src(a.stream, a.head_bytes, t, d), lane);
-    EOQ_STAMP(6);
 
     if (x_vec) {
         // 8 columns per vector: convert, store as fp32 [K][BT], and (INT4) add up 16-column sums with the neighbour lane
@@ -689,7 +667,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
     if (KIND == EOQ_B200_KIND_Q5_POLAR)
         for (uint32_t i = tid; i < 32 * 32; i += kThreads) aux[i] = __ldg(a.centroids + (i >> 5));
     __syncthreads();
-    EOQ_STAMP(7);
     if (KIND == EOQ_B200_KIND_Q5_POLAR) {
         // x'' = H64 x / 64 per 64-column block (unnormalised Sylvester butterflies), so that
         // W_block . x_block = norm * sum_j centroid[code_j] * x''_j   (core/polar_quant.py:242-262)
@@ -718,13 +695,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
     mbar_wait_bounded(tab_bar, 0u, a.status);
     const uint32_t mask = M - 1u, p = a.p;
     const uint32_t sgroups = K / a.group;
-    EOQ_STAMP(1);
     while (have) {
         const TileDesc cur = d;
         uint32_t x;
         WordState ws;
         const bool ring_mode = tile_begin(ring, ws, cur, tile_src(a.stream, a.head_bytes, t, cur), lane, x);
-        EOQ_STAMP(2);
         const uint32_t row = cur.row0 + lane * G;
         const uint32_t rb = cur.row0 / (32u * G);
         const uint32_t seg = cur.seg & ~kTileDirectFlag;
@@ -738,7 +713,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
         if (ring_mode) gemv_tile_columns<G, BITS, BT, KIND, true, kUnroll>(a, cur, tab, xs, aux, lane, row, mask, p, sgroups, x, ws, ring, y);
         else gemv_tile_columns<G, BITS, BT, KIND, false, 1>(a, cur, tab, xs, aux, lane, row, mask, p, sgroups, x, ws, ring, y);
         tile_end(ring, ring_mode);
-        EOQ_STAMP(3);
 
         // the next tile's copies start now and overlap the write-back of this one
         t += gridDim.x * kWarps;
@@ -760,7 +734,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
             uint32_t ticket = 0;
             if (lane == 0) ticket = atomicAdd(a.counters + rb, 1u);
             ticket = __shfl_sync(0xffffffffu, ticket, 0);
-            EOQ_STAMP(4);
             write_out = ticket == a.nseg - 1;
             if (write_out) {
                 // last warp of the row block: add the segments' partial sums, always in segment order;
@@ -794,7 +767,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_tiles_kernel(const GemvArgs a
             }
         }
         if (write_out) write_rows<G, BT>(a, row, y);     // bias, output type and, in row-sharded runs, the stores into the peers' buffers
-        EOQ_STAMP(5);
     }
     gather_finish(a);          // row-sharded runs: wait for the other ranks' rows and unpack them
 }
@@ -1128,7 +1100,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
     extern __shared__ __align__(128) uint8_t pair_smem[];
     uint8_t *smem = pair_smem;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    EOQ_STAMP(0);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const uint32_t tab_bytes = 4u << a.p;
@@ -1296,12 +1267,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
     uint32_t q = chunk_lo(t) + warp;
     bool have = warp < cs;
     if (have) open_pair(q);
-    EOQ_STAMP(6);
     __syncthreads();                                   // the table barrier is initialised before anyone polls it
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    EOQ_STAMP(1);
     if (have) load_x_segment(true);
-    EOQ_STAMP(7);
     mbar_wait_suspended(tab_bar, 0u, a.status);
 
     // `uses` counts the pairs this warp has opened: a warp that sits out a short chunk does not arm its barriers,
@@ -1347,7 +1315,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                 ch[k].addr = stage[k] + 128u + lane * 2u;
                 ch[k].w = lds_u16(ch[k].addr);
             }
-            EOQ_STAMP(2);
             uint32_t c = cur.col0;
             const uint32_t col0 = cur.col0, cend = cur.col0 + cur.ncols;
             const uint32_t nchunks0 = min(kMaxChunks, (len_a + kChunk - 1) / kChunk), nchunks1 = min(kMaxChunks, (len_b + kChunk - 1) / kChunk);
@@ -1403,7 +1370,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                 }
             }
             __syncwarp();
-            EOQ_STAMP(3);
             // this warp's sums go into its first stage buffer, which nothing reads any more: [tile][row j][batch][lane]
             float *red = reinterpret_cast<float *>(mine);
 #pragma unroll
@@ -1447,7 +1413,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                 constexpr uint32_t kEmpty = 0xFFFFFFFFu;
                 uint32_t *slots = reinterpret_cast<uint32_t *>(a.pair_partials);
                 const uint32_t ticket = __shfl_sync(0xffffffffu, early_ticket, 0);
-                EOQ_STAMP(4);
                 last = ticket == count - 1u;
                 if (!last) {
 #pragma unroll
@@ -1570,7 +1535,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                 uint32_t ticket = 0;
                 if (lane == 0) ticket = atomicAdd(a.counters + cur.row0[0] / (32u * G), 1u);
                 ticket = __shfl_sync(0xffffffffu, ticket, 0);
-                EOQ_STAMP(4);
                 last = ticket == count - 1u;
                 if (last) {
                     __threadfence();
@@ -1695,7 +1659,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pairs_kernel(const GemvArgs a
                 __syncthreads();
             }
         }
-        EOQ_STAMP(5);
 
         t += gridDim.x;
         if (t < nchunks) {
@@ -2681,8 +2644,7 @@ __device__ __forceinline__ void gemm_fetch_x(const CUtensorMap *xmap, uint32_t d
 template <bool RING>
 __device__ __forceinline__ void gemm_decode_piece(uint32_t tab_addr, uint32_t &x, WordState &ws, uint32_t mask, uint32_t p,
                                                   const float (&sc)[3], const GemmWarp &gw, const CUtensorMap *xmap, uint32_t c,
-                                                  uint32_t x_half_bytes, uint32_t m_tiles, uint32_t lane, uint32_t *status, bool &dead,
-                                                  long long (&cyc)[4])
+                                                  uint32_t x_half_bytes, uint32_t m_tiles, uint32_t lane, uint32_t *status, bool &dead)
 {
     using F = Fmt<3, 4>;
     using F0 = Int4Field<F::field_bit(0)>;
@@ -2703,11 +2665,9 @@ __device__ __forceinline__ void gemm_decode_piece(uint32_t tab_addr, uint32_t &x
             if (half == 0 && s == 3) {
                 // the previous MMA was issued four steps ago: it has read both staging pieces by now
                 {
-                    GEMM_CYC_BEGIN();
                     if (gw.np > 0) gemm_wait(gw.mma_bar, (gw.np - 1u) & 1u, status, dead);
                     if (lane == 0) gemm_fetch_x(xmap, gw.xp, x_half_bytes, c, gw.x_bar, m_tiles);
                     __syncwarp();
-                    GEMM_CYC_END(cyc[0]);
                 }
             }
         }
@@ -2805,7 +2765,6 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
     // Everything that has to come from global memory is requested before anything is waited for: the decode table
     // (bulk copy onto a barrier), then each warp's first tile (descriptor, L2 prefetch, first ring chunks).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     // see launch_with_pdl
-    GEMM_STAMP(0);
     if (tid == 0) {
         mbar_init(tab_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -2848,7 +2807,6 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
     gemm_wait(tab_bar, 0u, a.status, dead);
     // nothing above read an input of this call or wrote global memory; X, bias, Y and the scratch come after this
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    GEMM_STAMP(1);
 
     const uint32_t mask = (1u << a.p) - 1u, p = a.p, tab_addr = smem_addr(tab);
     // fp32 accumulate, A = X and B = W both fp16 and K-major, N = 96, M = 128
@@ -2859,7 +2817,6 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
     gw.mma_bar = mma_bar0 + warp * 8;
     gw.x_bar = x_bar0 + warp * 8;
     gw.np = 0;
-    long long cyc[4] = {0, 0, 0, 0};      // debug builds: cycles in the per-piece synchronisation points
     const uint32_t x_half_bytes = gemm_x_stride(a.M) / (2u * m_tiles);      // one 8-column half of one token tile of an X piece
     // warps 0..7: warp w owns TMEM lanes 32*(w%4).. (tokens) and columns 48*(w/4).. (weight rows of a block) of every
     // accumulator; it clears them before a group and reads them back after it
@@ -2897,7 +2854,6 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
             uint32_t x;
             WordState ws;
             const bool ring_mode = tile_begin(ring, ws, d, base, lane, x);
-            if (gw.np == 0) GEMM_STAMP(2);
             // ask L2 for the warp's next tile while this one decodes
             const uint32_t next = tile + nwarps;
             if (next < g_hi && lane == 0) {
@@ -2925,23 +2881,18 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
                 }
                 if (ring_mode) {
                     {
-                        GEMM_CYC_BEGIN();
                         ring_sync_step(ring, ws, lane);
-                        GEMM_CYC_END(cyc[1]);
                     }
-                    gemm_decode_piece<true>(tab_addr, x, ws, mask, p, sc, gw, &xmap, c, x_half_bytes, m_tiles, lane, a.status, dead, cyc);
+                    gemm_decode_piece<true>(tab_addr, x, ws, mask, p, sc, gw, &xmap, c, x_half_bytes, m_tiles, lane, a.status, dead);
                 } else {
-                    gemm_decode_piece<false>(tab_addr, x, ws, mask, p, sc, gw, &xmap, c, x_half_bytes, m_tiles, lane, a.status, dead, cyc);
+                    gemm_decode_piece<false>(tab_addr, x, ws, mask, p, sc, gw, &xmap, c, x_half_bytes, m_tiles, lane, a.status, dead);
                 }
                 {
-                    GEMM_CYC_BEGIN();
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     gemm_wait(gw.x_bar, gw.np & 1u, a.status, dead);
-                    GEMM_CYC_END(cyc[2]);
                 }
                 {
-                    GEMM_CYC_BEGIN();
                     if (lane == 0) {
                         // X piece: 8-row groups 128 bytes apart, its two column halves x_half_bytes apart; one MMA per token
                         // tile, all on the same decoded W piece
@@ -2950,7 +2901,6 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
                         umma_commit(gw.mma_bar);
                     }
                     __syncwarp();
-                    GEMM_CYC_END(cyc[3]);
                 }
                 gw.np++;
             }
@@ -2962,13 +2912,11 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
                 tile_open(ring, d, tile_src(a.stream, a.head_bytes, tile, d), lane);
             }
         }
-        GEMM_STAMP(3);
         // every MMA this warp issued for the group is behind this commit
         if (lane == 0) umma_commit(grp_bar);
         __syncwarp();
         gemm_wait(grp_bar, grp & 1u, a.status, dead);
         __syncwarp();
-        GEMM_STAMP(4);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
         // a CTA's first row block and its last are the only ones it can share with other CTAs: partial slots 0 and 1
@@ -3009,7 +2957,6 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
                 }
             }
         }
-        GEMM_STAMP(5);
         if (shared_any) {
             // tickets: the last contributor of a row block to arrive adds the partial tiles, always in CTA order
             __threadfence();
@@ -3040,15 +2987,12 @@ __global__ void __launch_bounds__(kGemmMaxThreads, 1) gemm_tiles_kernel(const Ge
             }
             __syncthreads();
             const uint32_t n0 = flag[0], n1 = flag[1];
-            GEMM_STAMP(6);
             if (n0 | n1) __threadfence();
             if (n0) gemm_sum_partials(a, rb_first, contrib, n0);
             if (n1) gemm_sum_partials(a, rb_last, contrib + kGemmMaxContrib, n1);
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
-    GEMM_STAMP(7);
-    GEMM_CYC_WRITE(0, cyc[0]); GEMM_CYC_WRITE(1, cyc[1]); GEMM_CYC_WRITE(2, cyc[2]); GEMM_CYC_WRITE(3, cyc[3]); GEMM_CYC_WRITE(4, gw.np);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     __syncwarp();
