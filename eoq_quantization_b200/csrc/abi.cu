@@ -176,8 +176,8 @@ eoq_error_t job_from_payload(const eoq_tensor_header_t *h, const uint8_t *comp, 
 
 // Decode `n` validated jobs: one arena, one upload of all metadata, the streams copied in, ONE launch of the lane kernel
 // over every job it serves (others run the one-thread-per-block kernel), results copied to the host buffers that ask
-// for it.  Asynchronous on `st`; the arena must stay acquired until the stream has been synchronised.
-eoq_error_t decode_jobs(V1Job **jobs, size_t n, cudaStream_t st, DeviceArena &arena)
+// for it (with copy_out false they stay in the arena, at at_out, for the caller to fetch).  Asynchronous on `st`; the arena must stay acquired until the stream has been synchronised.
+eoq_error_t decode_jobs(V1Job **jobs, size_t n, cudaStream_t st, DeviceArena &arena, bool copy_out = true)
 {
     if (n == 0) return EOQ_OK;
     if (!have_device()) return EOQ_ERR_CUDA;
@@ -258,7 +258,7 @@ eoq_error_t decode_jobs(V1Job **jobs, size_t n, cudaStream_t st, DeviceArena &ar
                                      (int)j.out_elem_bytes, j.pl.nblocks, j.pl.block, j.pl.total, j.pl.p, j.pl.alphabet, st);
             if (e != 0) { std::fprintf(stderr, "eoq_b200: decode launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
         }
-        if (j.host_out) CU_TRY(cudaMemcpyAsync(j.host_out, out, (size_t)j.pl.total * j.out_elem_bytes, cudaMemcpyDeviceToHost, st));
+        if (j.host_out && copy_out) CU_TRY(cudaMemcpyAsync(j.host_out, out, (size_t)j.pl.total * j.out_elem_bytes, cudaMemcpyDeviceToHost, st));
     }
     return EOQ_OK;
 }
@@ -338,16 +338,20 @@ extern "C" int eoq_decode_tensor(const eoq_tensor_header_t *header, const uint8_
 }
 
 // Tensors are decoded in groups: the tasks of a group are validated on the host, uploaded together and decoded by ONE
-// kernel launch (every rANS block of every tensor of the group is a lane of that launch); their results are copied
-// back in task order, and the progress callback runs on the calling thread after each, so calls are serialised and
-// count up by one.  A group holds opts->num_threads tasks (the number of tasks the reference would have in flight),
-// or 64 when that is 0.  After a cancel request the group in flight completes and later groups are not started.
+// kernel launch (every rANS block of every tensor of the group is a lane of that launch).  A group is as many tasks as
+// fit 256 tasks and 256 MB of symbols, whatever opts->num_threads says: the launch is only efficient when it is wide.
+// Results are then delivered in task order, opts->num_threads tasks at a time (the number of tasks the reference would
+// have in flight; 64 when it is 0): their symbols are copied to the callers' buffers, then the progress callback runs
+// on the calling thread for each, so calls are serialised and count up by one.  After a cancel request the tasks being
+// delivered complete; the rest get EOQ_ERR_THREAD and their buffers are not written, decoded on the device or not.
 extern "C" eoq_error_t eoq_parallel_decode(eoq_decode_task_t *tasks, int num_tasks, const eoq_parallel_opts_t *opts)
 {
     if (!tasks && num_tasks > 0) return EOQ_ERR_NULL_PTR;
     if (num_tasks <= 0) return EOQ_OK;
-    int group = opts ? opts->num_threads : 0;
-    group = group <= 0 ? 64 : std::min(group, 256);
+    int deliver = opts ? opts->num_threads : 0;
+    deliver = deliver <= 0 ? 64 : std::min(deliver, 256);
+    constexpr int kGroupTasks = 256;
+    constexpr uint64_t kGroupSymbols = 256ull << 20;
     eoq_parallel_progress_fn cb = opts ? opts->progress_cb : nullptr;
     void *ud = opts ? opts->progress_ud : nullptr;
     cudaStream_t st = nullptr;
@@ -356,15 +360,23 @@ extern "C" eoq_error_t eoq_parallel_decode(eoq_decode_task_t *tasks, int num_tas
     int done = 0;
     bool cancelled = false;
     DeviceArena arena;
-    for (int g0 = 0; g0 < num_tasks; g0 += group) {
-        const int g1 = std::min(num_tasks, g0 + group);
+    for (int g0 = 0; g0 < num_tasks;) {
+        int g1 = g0;
+        uint64_t symbols = 0;
+        while (g1 < num_tasks && g1 - g0 < kGroupTasks) {
+            const uint64_t add = tasks[g1].header ? tasks[g1].header->uncompressed_size : 0;
+            if (g1 > g0 && symbols + add > kGroupSymbols) break;
+            symbols += add;
+            g1++;
+        }
         if (cancelled) {
             for (int i = g0; i < g1; i++) tasks[i].result = EOQ_ERR_THREAD;          // eoq_parallel_decode.c:72-82
+            g0 = g1;
             continue;
         }
         std::vector<std::unique_ptr<V1Job>> jobs;
         std::vector<V1Job *> live;
-        std::vector<int> live_task;
+        std::vector<V1Job *> job_of(g1 - g0, nullptr);
         for (int i = g0; i < g1; i++) {
             eoq_decode_task_t &t = tasks[i];
             t.task_index = i;
@@ -376,17 +388,34 @@ extern "C" eoq_error_t eoq_parallel_decode(eoq_decode_task_t *tasks, int num_tas
             if (t.result != EOQ_OK) continue;
             j->host_out = t.output;
             live.push_back(j.get());
-            live_task.push_back(i);
+            job_of[i - g0] = j.get();
             jobs.push_back(std::move(j));
         }
-        eoq_error_t rc = live.empty() ? EOQ_OK : decode_jobs(live.data(), live.size(), st, arena);
-        if (rc == EOQ_OK && !live.empty() && cudaStreamSynchronize(st) != cudaSuccess) rc = EOQ_ERR_CUDA;
-        if (rc != EOQ_OK)
-            for (int i : live_task) tasks[i].result = rc;
-        for (int i = g0; i < g1; i++) {
-            done++;
-            if (cb && !cancelled && cb(done, num_tasks, ud)) cancelled = true;
+        eoq_error_t rc = live.empty() ? EOQ_OK : decode_jobs(live.data(), live.size(), st, arena, /*copy_out=*/false);
+        for (int d0 = g0; d0 < g1; d0 += deliver) {
+            const int d1 = std::min(g1, d0 + deliver);
+            if (cancelled) {
+                for (int i = d0; i < d1; i++) tasks[i].result = EOQ_ERR_THREAD;
+                continue;
+            }
+            eoq_error_t drc = rc;
+            bool any = false;
+            for (int i = d0; i < d1 && drc == EOQ_OK; i++) {
+                const V1Job *j = job_of[i - g0];
+                if (!j) continue;
+                any = true;
+                if (cudaMemcpyAsync(j->host_out, arena.base() + j->at_out, (size_t)j->pl.total * j->out_elem_bytes, cudaMemcpyDeviceToHost, st) != cudaSuccess)
+                    drc = EOQ_ERR_CUDA;
+            }
+            if (drc == EOQ_OK && any && cudaStreamSynchronize(st) != cudaSuccess) drc = EOQ_ERR_CUDA;
+            for (int i = d0; i < d1; i++) {
+                if (job_of[i - g0] && drc != EOQ_OK) tasks[i].result = drc;
+                done++;
+                if (cb && !cancelled && cb(done, num_tasks, ud)) cancelled = true;
+            }
         }
+        if (!live.empty()) cudaStreamSynchronize(st);            // the arena is reused by the next group
+        g0 = g1;
     }
     arena.release();
     if (st) cudaStreamDestroy(st);

@@ -2072,15 +2072,14 @@ int launch_decode_v1(const uint8_t *d_stream, const uint32_t *d_offsets, const u
 //
 // A warp takes 32 consecutive blocks.  Everything a step touches is in shared memory:
 //   * the decode table, in one of two forms chosen by the host: PACKED, one 32-bit entry per slot
-//     {freq - 1 : p bits | slot - cum : p bits | symbol} when 2 p + symbol bits <= 32 (16 KB at p = 12, 64 KB at
-//     p = 14), else TWO-LEVEL, slot -> symbol (u8 / u16) and symbol -> {freq, cum};
+//     {freq - 1 : p bits | symbol | slot - cum : p bits} when 2 p + symbol bits <= 32 (16 KB at p = 12, 64 KB at
+//     p = 14), else TWO-LEVEL, slot -> symbol (u16) and symbol -> {freq, cum};
 //   * the bytes of the 32 streams: each lane owns a 128-byte ring, stored word-interleaved ([word][lane], so lane l
-//     only ever touches bank l and byte reads never conflict) and filled 32 bytes at a time by asynchronous 4-byte
-//     copies (cp.async) issued two chunks ahead of the read position; the two bytes a step may consume are
-//     requested at the top of the step, next to the table look-up, not after the state update.
+//     only ever touches bank l and reads never conflict) and filled 32 bytes at a time by asynchronous 4-byte
+//     copies (cp.async) issued two chunks ahead of the read position.
 // Decoded symbols are collected in registers and leave as whole 32-byte sectors.  Every global read stays inside
-// [block start rounded down to 4, block end): the words wholly inside come by cp.async, the last partial word by
-// byte loads.
+// [chunk of the block's first byte, block end): whole words by plain copies, the block's last partial word by a copy
+// with a source size.
 // ---------------------------------------------------------------------------
 constexpr uint32_t kV1RingBytes = 128, kV1ChunkBytes = 32;
 
@@ -2097,116 +2096,178 @@ __device__ __forceinline__ uint32_t lds_u8(uint32_t addr)
     return v;
 }
 
-// Request chunk `c` (stream bytes [32 c, 32 c + 32)) of a lane's block into its ring.
-__device__ __forceinline__ void v1_issue_chunk_nocommit(const uint8_t *stream, uint32_t ring, uint32_t lane, uint32_t c, uint32_t lo4,
-                                                        uint32_t end)
+__device__ __forceinline__ uint2 lds_v2(uint32_t addr)
 {
-    const uint32_t end4 = end & ~3u;
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t msb_index(uint32_t v)      // 31 - clz(v); 0xFFFFFFFF for 0
+{
+    uint32_t m;
+    asm("bfind.u32 %0, %1;" : "=r"(m) : "r"(v));
+    return m;
+}
+
+// Request chunk `c` (stream bytes [32 c, 32 c + 32)) of a lane's block into its ring.  Words wholly below `end` are
+// copied whole, the block's last, partial word with a source size (the rest of the ring word is zero-filled), words at
+// or past `end` not at all; a chunk may begin before the block does (never before the stream: offsets are >= 0).
+__device__ __forceinline__ void v1_issue_chunk_edge(const uint8_t *stream, uint32_t lane_col, uint32_t c, uint32_t end)
+{
+    const uint32_t dst = lane_col + ((c & 3u) << 10);
+    const uint8_t *src = stream + (size_t)c * kV1ChunkBytes;
 #pragma unroll
     for (uint32_t i = 0; i < kV1ChunkBytes / 4; i++) {
         const uint32_t w = c * kV1ChunkBytes + i * 4u;
-        const uint32_t dst = v1_ring_addr(ring, lane, w);
-        if (w >= lo4 && w + 4u <= end4) {
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(stream + w) : "memory");
-        } else if (w >= lo4 && w < end) {          // the block's last, partial word
-            for (uint32_t k = 0; k < 4u && w + k < end; k++)
-                asm volatile("st.shared.u8 [%0], %1;" ::"r"(dst + k), "r"((uint32_t)stream[w + k]) : "memory");
+        if (w < end) {
+            const uint32_t sz = min(4u, end - w);
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst + i * 128u), "l"(src + i * 4u), "r"(sz) : "memory");
         }
     }
 }
-__device__ __forceinline__ void v1_issue_chunk(const uint8_t *stream, uint32_t ring, uint32_t lane, uint32_t c, uint32_t lo4,
-                                               uint32_t end)
+// The same for a chunk that lies wholly inside the block's words: eight copies at constant offsets.
+__device__ __forceinline__ void v1_issue_chunk_inner(const uint8_t *stream, uint32_t lane_col, uint32_t c)
 {
-    v1_issue_chunk_nocommit(stream, ring, lane, c, lo4, end);
-    asm volatile("cp.async.commit_group;" ::: "memory");
+    const uint32_t dst = lane_col + ((c & 3u) << 10);
+    const uint8_t *src = stream + (size_t)c * kV1ChunkBytes;
+#pragma unroll
+    for (uint32_t i = 0; i < kV1ChunkBytes / 4; i++)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + i * 128u), "l"(src + i * 4u) : "memory");
 }
 
-// The blocks of one lane's warp: decode, collect, store.  `tab` is the CTA's table in shared memory.
+// The block of one lane: decode, collect, store.  `tab` is the CTA's table in shared memory, `live` the lanes of the
+// warp that have a block (they vote together).
+//
+// Read position: the stream bytes around it live in two registers, words wi and wi + 1 of the stream, and the byte
+// offset k inside that window is kept as the selector of the byte permute that extracts the next two bytes into the
+// top half of a register: sel = k * 0x1100 + 0x0100 (result byte 3 = window byte k, byte 2 = k + 1).
+//
+// A step in the common case is straight-line code: table look-up, state update, the number of bytes to take from the
+// position of the state's highest set bit, one funnel shift that moves them in, one multiply-add that advances the
+// selector; every second step the window moves on by a word if the offset has passed 4.  That form is exact while
+// the state is in [2^(p+8), 2^(p+16)) at the top of a step and two bytes are left: both hold for a group of eight
+// steps if they hold at its start with sixteen bytes left (a state in range comes out of the update at 2^8 or more,
+// so two bytes bring it back in range).  The warp votes once per group; near the end of the blocks, and for streams
+// that are not well-formed, the group runs the careful form of the step instead, which counts bytes against the end
+// of the block and reads on byte by byte when two bytes were not enough, like the reference decoder.
 template <typename OutT, bool PACKED>
-__device__ __forceinline__ void v1_decode_lane(const V1Task &a, uint8_t *tab, uint32_t ring, uint32_t lane, uint32_t b)
+__device__ __forceinline__ void v1_decode_lane(const V1Task &a, uint8_t *tab, uint32_t ring, uint32_t lane, uint32_t b, uint32_t live)
 {
     const uint32_t p = a.p, mask = (1u << p) - 1u, low = 1u << (p + 8);
-    const uint32_t *packed = reinterpret_cast<const uint32_t *>(tab);
-    const uint2 *info = reinterpret_cast<const uint2 *>(tab);                                   // two-level: [alphabet] {freq, cum}
-    const uint16_t *symtab = reinterpret_cast<const uint16_t *>(tab + (size_t)a.alphabet * 8u);   // two-level: [1 << p]
+    const uint32_t tab_addr = smem_addr(tab);                                  // packed: [1 << p] words; two-level: [alphabet] {freq, cum}
+    const uint32_t symtab_addr = tab_addr + a.alphabet * 8u;                   // two-level: [1 << p] u16
     const uint32_t bytes = a.sizes[b];
-    if (bytes == 0) return;
-    const uint32_t start = a.offsets[b], end = start + bytes, lo4 = start & ~3u;
-    const uint32_t first = b * a.block_size, n = min(a.block_size, a.total - first);
+    const uint32_t start = a.offsets[b], end = start + bytes;
+    const uint32_t first = b * a.block_size;
+    uint32_t n = min(a.block_size, a.total - first);
+    const uint32_t lane_col = ring + (lane << 2);
+    auto ring_word = [&](uint32_t w) { return lds_u32(lane_col + ((w & (kV1RingBytes / 4 - 1)) << 7)); };
 
     // the first three chunks, then the header: one byte of state length, the state big-endian
     uint32_t c_next = start / kV1ChunkBytes;
-    for (int i = 0; i < 3; i++) v1_issue_chunk(a.stream, ring, lane, c_next++, lo4, end);
+    for (int i = 0; i < 3; i++) {
+        v1_issue_chunk_edge(a.stream, lane_col, c_next++, end);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-    const uint32_t state_len = lds_u8(v1_ring_addr(ring, lane, start));
-    if (1u + state_len > bytes || state_len > 4u) return;      // rejected on the host before launch
+    const uint32_t state_len = bytes ? lds_u8(v1_ring_addr(ring, lane, start)) : 0u;
+    if (bytes == 0 || 1u + state_len > bytes || state_len > 4u) n = 0;      // rejected on the host before launch; takes no step that counts
     uint32_t x = 0;
-    for (uint32_t i = 0; i < state_len; i++) x = (x << 8) | lds_u8(v1_ring_addr(ring, lane, start + 1u + i));
-    uint32_t pos = start + 1u + state_len;
+    for (uint32_t i = 0; i < state_len && n; i++) x = (x << 8) | lds_u8(v1_ring_addr(ring, lane, start + 1u + i));
+    const uint32_t pos0 = n ? start + 1u + state_len : end;
+    uint32_t wi = pos0 >> 2, sel = (pos0 & 3u) * 0x1100u + 0x0100u, cur = ring_word(wi), nxt = ring_word(wi + 1u);
 
     constexpr uint32_t kPer = 32u / sizeof(OutT);                // symbols per 32-byte sector
     OutT *dst = reinterpret_cast<OutT *>(a.out) + first;
     const bool vec_ok = (reinterpret_cast<uintptr_t>(dst) & 31u) == 0;
-    const uint32_t symmask = (1u << a.sym_bits) - 1u;
-    const uint32_t lane_col = ring + (lane << 2);
+    const uint32_t symmask = (1u << a.sym_bits) - 1u, fshift = 32u - p, top = p + 15u, last_sym = a.alphabet - 1u;
 
-    // The eight stream bytes around the read position live in two registers (words wi and wi + 1 of the stream), so
-    // the bytes a renormalisation takes come from a byte permute, not from a load behind the state update; the next word
-    // is fetched from the ring when the position crosses a word, one step before anything can need it.
-    auto ring_word = [&](uint32_t w) { return lds_u32(lane_col + ((w & (kV1RingBytes / 4 - 1)) << 7)); };
-    uint32_t wi = pos >> 2, cur = ring_word(wi), nxt = ring_word(wi + 1u);
-
-    auto step = [&]() -> uint32_t {
-        const uint32_t slot = x & mask;
-        uint32_t sym;
+    auto look_up = [&]() -> uint32_t {                          // x <- freq * (x >> p) + slot - cum; returns the symbol
+        const uint32_t xs = x >> p;
         if (PACKED) {
-            const uint32_t e = packed[slot];
-            sym = e & symmask;
-            x = ((e >> (32u - p)) + 1u) * (x >> p) + ((e >> a.sym_bits) & mask);
-        } else {
-            sym = symtab[slot];
-            const uint2 fc = info[min(sym, a.alphabet - 1u)];      // a caller's table may name symbols past the alphabet: stay in the array
-            x = fc.x * (x >> p) + slot - fc.y;
+            const uint32_t e = lds_u32(tab_addr + ((x & mask) << 2));      // {freq - 1 | symbol | slot - cum}
+            x = (e >> fshift) * xs + ((e & mask) + xs);
+            return (e >> p) & symmask;
         }
+        const uint32_t slot = x & mask;
+        const uint32_t sym = lds_u16(symtab_addr + (slot << 1));
+        const uint2 fc = lds_v2(tab_addr + (min(sym, last_sym) << 3));     // a caller's table may name symbols past the alphabet: stay in the array
+        x = fc.x * xs + (slot - fc.y);
+        return sym;
+    };
+    auto move_window = [&]() {
+        if (sel >= 0x4500u) { sel -= 0x4400u; cur = nxt; wi++; nxt = ring_word(wi + 1u); }
+    };
+    auto step = [&]() -> uint32_t {                             // exact under the conditions voted on per group
+        const uint32_t sym = look_up();
+        const uint32_t two = __byte_perm(cur, nxt, sel);
+        const uint32_t t8 = (top - msb_index(x)) & 0x18u;      // 0, 8 or 16 bits to take
+        x = __funnelshift_l(two, x, t8);
+        sel += t8 * 0x220u;
+        return sym;
+    };
+    auto careful_step = [&](bool counts) -> uint32_t {
+        const uint32_t pos = wi * 4u + (sel >> 12);
+        const uint32_t sym = look_up();
         // bytes pos and pos + 1, first one in the higher half; 0, 1 or 2 of them are taken (p <= 16), never past the block
-        const uint32_t two = __byte_perm(cur, nxt, (pos & 3u) * 0x11u + 1u) & 0xFFFFu;
+        const uint32_t two = __byte_perm(cur, nxt, sel) >> 16;
         uint32_t take = (x < low ? 1u : 0u) + (x < (low >> 8) ? 1u : 0u);
         take = min(take, end - pos);
         x = (x << (8u * take)) | (two >> (16u - 8u * take));
-        pos += take;
-        if ((pos >> 2) != wi) { cur = nxt; wi++; nxt = ring_word(wi + 1u); }
-        if (x < low && pos < end) {
+        sel += take * 0x1100u;
+        move_window();
+        uint32_t at = pos + take;
+        if (counts && x < low && at < end) {
             // only a corrupt stream gets here: read on like the reference decoder, byte by byte and inside the block
-            while (x < low && pos < end) { x = (x << 8) | a.stream[pos]; pos++; }
-            wi = pos >> 2;
+            while (x < low && at < end) { x = (x << 8) | a.stream[at]; at++; }
+            wi = at >> 2;
+            sel = (at & 3u) * 0x1100u + 0x0100u;
             cur = nxt = 0u;
             for (uint32_t k = 0; k < 8u; k++) {
-                const uint32_t at = wi * 4u + k;
-                const uint32_t byte = at >= start && at < end ? a.stream[at] : 0u;
+                const uint32_t q = wi * 4u + k;
+                const uint32_t byte = q >= start && q < end ? a.stream[q] : 0u;
                 if (k < 4u) cur |= byte << (8u * k); else nxt |= byte << (8u * (k - 4u));
             }
         }
         return sym;
     };
-    auto keep_ahead = [&]() {
-        // Called every 8 steps (<= 16 bytes).  On entry the chunk under `pos` and the next one are complete; a chunk is
-        // requested as soon as the position is within two chunks of it, and every call closes one copy group, so that
-        // "all but the two latest groups" is exactly "everything requested two calls ago", the latest moment it is needed.
-        if ((pos / kV1ChunkBytes) + 3u > c_next) v1_issue_chunk_nocommit(a.stream, ring, lane, c_next++, lo4, end);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 2;" ::: "memory");
-    };
 
-    uint32_t i = 0;
-    if (vec_ok) {
-        for (; i + kPer <= n; i += kPer) {
-            uint32_t w[8];
+    const uint32_t n_warp = __reduce_max_sync(live, n);
+    const uint32_t end4 = end & ~3u;
+    for (uint32_t i = 0; i < n_warp; i += kPer) {
+        uint32_t w[8];
 #pragma unroll
-            for (uint32_t g = 0; g < kPer / 8u; g++) {
-                keep_ahead();
+        for (uint32_t g = 0; g < kPer / 8u; g++) {
+            // Every 8 steps (<= 16 bytes).  Here the chunk under the position and the next one are complete; a chunk is
+            // requested as soon as the position is within two chunks of it, and every group of steps closes one copy group,
+            // so that "all but the two latest groups" is exactly "everything requested two groups ago", the latest moment it
+            // is needed.
+            const uint32_t pos = wi * 4u + (sel >> 12);
+            const bool counts = i + g * 8u < n;                 // a lane past its block only keeps the warp company
+            if (counts && (pos / kV1ChunkBytes) + 3u > c_next) {
+                if (c_next * kV1ChunkBytes + kV1ChunkBytes <= end4) v1_issue_chunk_inner(a.stream, lane_col, c_next);
+                else v1_issue_chunk_edge(a.stream, lane_col, c_next, end);
+                c_next++;
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 2;" ::: "memory");
+            const bool plain = !counts || (end - pos >= 16u && pos <= end && (x >> (p + 8u)) - 1u < 255u);
+            if (__all_sync(live, plain)) {
 #pragma unroll
                 for (uint32_t k = 0; k < 8u; k++) {
                     const uint32_t sym = step();
+                    if (k & 1u) move_window();
+                    const uint32_t idx = g * 8u + k;
+                    if (sizeof(OutT) == 1) {
+                        if ((idx & 3u) == 0) w[idx >> 2] = sym; else w[idx >> 2] |= sym << (8u * (idx & 3u));
+                    } else {
+                        if ((idx & 1u) == 0) w[idx >> 1] = sym; else w[idx >> 1] |= sym << 16;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (uint32_t k = 0; k < 8u; k++) {
+                    const uint32_t sym = careful_step(counts);
                     const uint32_t idx = g * 8u + k;
                     if (sizeof(OutT) == 1) {
                         if ((idx & 3u) == 0) w[idx >> 2] = sym; else w[idx >> 2] |= sym << (8u * (idx & 3u));
@@ -2215,14 +2276,17 @@ __device__ __forceinline__ void v1_decode_lane(const V1Task &a, uint8_t *tab, ui
                     }
                 }
             }
+        }
+        if (vec_ok && i + kPer <= n) {
             uint4 *o = reinterpret_cast<uint4 *>(dst + i);
             o[0] = make_uint4(w[0], w[1], w[2], w[3]);
             o[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        } else if (i < n) {
+            // the tail of a tensor's last block, or an output that does not start on a sector
+#pragma unroll
+            for (uint32_t k = 0; k < kPer; k++)
+                if (i + k < n) dst[i + k] = (OutT)(w[k * sizeof(OutT) / 4u] >> (8u * sizeof(OutT) * (k % (4u / sizeof(OutT)))));
         }
-    }
-    for (; i < n; i++) {
-        if ((i & 7u) == 0) keep_ahead();
-        dst[i] = (OutT)step();
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
@@ -2264,39 +2328,57 @@ __device__ __forceinline__ void v1_lanes_body(const V1Task &a, uint8_t *v1_smem)
             const uint32_t c = cdf[s], f = cdf[s + 1] - c;
             if (!a.packed && lane == 0) info[s] = make_uint2(f, c);
             for (uint32_t k = lane; k < f && c + k < M; k += 32u) {
-                if (a.packed) packed[c + k] = ((f - 1u) << (32u - p)) | (k << a.sym_bits) | s;
+                if (a.packed) packed[c + k] = ((f - 1u) << (32u - p)) | (s << p) | k;
                 else symtab[c + k] = (uint16_t)s;
             }
         }
     } else {
-        const uint2 *src = reinterpret_cast<const uint2 *>(a.table);           // x: symbol | freq << 16, y: cum
-        for (uint32_t s0 = tid; s0 < M; s0 += blockDim.x * 4u) {                // four independent loads in flight per thread
-            uint2 e[4];
+        // The caller's slot table, {symbol | freq << 16, cum} per slot: every CTA reads all of it once (from L2 after the
+        // first), so what matters is bytes in flight: sixteen independent 16-byte loads (two slots each) per thread and
+        // round, 64 KB per round and 256-thread CTA.
+        auto put = [&](uint32_t slot, uint32_t e0, uint32_t e1) {
+            const uint32_t sym = e0 & 0xFFFFu, freq = e0 >> 16, cum = e1 & 0xFFFFu;
+            if (a.packed) {
+                packed[slot] = ((freq - 1u) << (32u - p)) | ((sym & ((1u << a.sym_bits) - 1u)) << p) | ((slot - cum) & (M - 1u));
+            } else {
+                symtab[slot] = (uint16_t)sym;
+                if (sym < a.alphabet && slot == cum) info[sym] = make_uint2(freq, cum);       // a symbol's first slot speaks for it
+            }
+        };
+        if ((reinterpret_cast<uintptr_t>(a.table) & 15u) == 0 && M >= 2u) {
+            const uint4 *src = reinterpret_cast<const uint4 *>(a.table);
+            const uint32_t pairs = M >> 1;
+            constexpr uint32_t kInFlight = 16;
+            for (uint32_t q0 = tid; q0 < pairs; q0 += blockDim.x * kInFlight) {
+                uint4 e[kInFlight];
 #pragma unroll
-            for (uint32_t u = 0; u < 4u; u++)
-                if (s0 + u * blockDim.x < M) e[u] = __ldg(src + s0 + u * blockDim.x);
+                for (uint32_t u = 0; u < kInFlight; u++)
+                    if (q0 + u * blockDim.x < pairs) e[u] = __ldg(src + q0 + u * blockDim.x);
 #pragma unroll
-            for (uint32_t u = 0; u < 4u; u++) {
-                const uint32_t slot = s0 + u * blockDim.x;
-                if (slot >= M) continue;
-                const uint32_t sym = e[u].x & 0xFFFFu, freq = e[u].x >> 16, cum = e[u].y & 0xFFFFu;
-                if (a.packed) {
-                    packed[slot] = ((freq - 1u) << (32u - p)) | (((slot - cum) & (M - 1u)) << a.sym_bits) | (sym & ((1u << a.sym_bits) - 1u));
-                } else {
-                    symtab[slot] = (uint16_t)sym;
-                    if (sym < a.alphabet) info[sym] = make_uint2(freq, cum);       // every slot of a symbol writes the same pair
+                for (uint32_t u = 0; u < kInFlight; u++) {
+                    const uint32_t q = q0 + u * blockDim.x;
+                    if (q >= pairs) continue;
+                    put(2u * q, e[u].x, e[u].y);
+                    put(2u * q + 1u, e[u].z, e[u].w);
                 }
+            }
+        } else {
+            const uint2 *src = reinterpret_cast<const uint2 *>(a.table);
+            for (uint32_t slot = tid; slot < M; slot += blockDim.x) {
+                const uint2 e = __ldg(src + slot);
+                put(slot, e.x, e.y);
             }
         }
     }
     __syncthreads();
 
     const uint32_t b = ((blockIdx.x - a.first_cta) * nwarps + warp) * 32u + lane;
+    const uint32_t live = __ballot_sync(0xffffffffu, b < a.nblocks);
     if (b >= a.nblocks) return;
     if (a.out_elem_bytes == 1) {
-        if (a.packed) v1_decode_lane<uint8_t, true>(a, tab, ring, lane, b); else v1_decode_lane<uint8_t, false>(a, tab, ring, lane, b);
+        if (a.packed) v1_decode_lane<uint8_t, true>(a, tab, ring, lane, b, live); else v1_decode_lane<uint8_t, false>(a, tab, ring, lane, b, live);
     } else {
-        if (a.packed) v1_decode_lane<uint16_t, true>(a, tab, ring, lane, b); else v1_decode_lane<uint16_t, false>(a, tab, ring, lane, b);
+        if (a.packed) v1_decode_lane<uint16_t, true>(a, tab, ring, lane, b, live); else v1_decode_lane<uint16_t, false>(a, tab, ring, lane, b, live);
     }
 }
 

@@ -148,7 +148,9 @@ def test_other_integer_widths_stay_on_the_fused_path(bits):
     y = w2.gemv(x, out_dtype=torch.float32)
     assert O.rel_l2(y.cpu().numpy(), x.float().cpu().numpy().astype(np.float64) @ dense2.astype(np.float64).T) < 1e-4
     assert w2.status() == 0
-    assert w2.info.bits_per_weight < bits + 0.3
+    # stream bytes only; a 32-row tile of 8-bit codes is short, so its 128 bytes of initial states and the padding to the
+    # longest lane weigh more than on the 96-row tiles of the narrow widths
+    assert w2.info.bits_per_weight < bits + (0.8 if bits == 8 else 0.3)
 
 
 def test_quantized_linear_of_other_widths_runs_fused():
