@@ -766,8 +766,8 @@ def measure_llama_step(world, rank, steps, gather, with_fp16):
 
 def measure_prefill_tp(world, rank, steps):
     """Llama-70B-shape gate/up projection (28672 x 8192, INT4 g128 rANS-coded, N(0, 0.015)) row-sharded over the ranks:
-    per M, the fused decode + tensor-core GEMM of this rank's rows followed by the all-gather of the output slices
-    (NCCL); device time, max over ranks.  Every rank's shard is drawn from the same distribution (its own seed)."""
+    per M, EOQWeight.linear on this rank's rows (the fused decode + tensor-core GEMM up to 128 rows of activations, decode
+    to bf16 + library GEMM beyond) followed by the all-gather of the output slices (NCCL); device time, max over ranks.  Every rank's shard is drawn from the same distribution (its own seed)."""
     import torch
     import torch.distributed as dist
     from eoq_quantization_b200 import _lib
@@ -785,15 +785,15 @@ def measure_prefill_tp(world, rank, steps):
         sym = (np.clip(np.round(w.reshape(-1, GROUP) / sc[:, None]), -7, 7) + 7).astype(np.uint8).reshape(w.shape)
         ws.append(EOQWeight.from_symbols(sym, sc.astype(np.float16)))
         del w, sym
-    for m in (16, 64, 256, 2048):
+    from eoq_quantization_b200.fused import GEMM_MAX_ROWS
+    for m in (16, 64, 128, 256, 2048):
         x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
-        ys = [torch.empty(m, wi.rows, device="cuda", dtype=torch.bfloat16) for wi in ws]
         full = torch.empty(world, m, n, device="cuda", dtype=torch.bfloat16) if world > 1 else None
 
         def run():
-            st = torch.cuda.current_stream().cuda_stream
-            for wi, y in zip(ws, ys):
-                _lib.check(lib.eoq_b200_gemm(wi._h, x.data_ptr(), _lib.BF16, m, y.data_ptr(), _lib.BF16, None, st), "gemm")
+            # EOQWeight.linear is the call a module makes: fused decode + tensor-core MMA up to GEMM_MAX_ROWS rows,
+            # one fused decode + dequantise to 16 bits and a library GEMM beyond
+            ys = [wi.linear(x) for wi in ws]
             if world > 1:
                 local = ys[0] if len(ys) == 1 else torch.cat(ys, dim=1)
                 dist.all_gather_into_tensor(full, local.contiguous())
@@ -802,11 +802,38 @@ def measure_prefill_tp(world, rank, steps):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+        # one replayed graph per M (compute kernels + the collective), so that the device time is not the host's launch rate;
+        # plain launches if the capture is refused
+        launch = "cuda-graph"
+        graph = torch.cuda.CUDAGraph()
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                run()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph):
+                run()
+            replay = graph.replay
+        except Exception as exc:                                    # noqa: BLE001 -- any capture failure means eager timing
+            launch = f"eager ({type(exc).__name__})"
+            replay = run
+        ok = torch.tensor([1.0 if launch == "cuda-graph" else 0.0], device="cuda")
+        if world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)                 # every rank must take the same route
+        if float(ok.item()) == 0.0:
+            replay, launch = run, launch if launch != "cuda-graph" else "eager (another rank could not capture)"
+        for _ in range(2):
+            replay()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         reps = max(3, min(steps, 10))
         e0.record()
         for _ in range(reps):
-            run()
+            replay()
         e1.record()
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) / reps * 1e3
@@ -814,7 +841,9 @@ def measure_prefill_tp(world, rank, steps):
             t = torch.tensor([us], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             us = float(t.item())
-        res[f"M{m}"] = {"us": us, "tflops": 2.0 * m * n_total * k / us / 1e6}
+        res[f"M{m}"] = {"us": us, "tflops": 2.0 * m * n_total * k / us / 1e6,
+                        "path": "fused decode + tcgen05 MMA" if m <= GEMM_MAX_ROWS else "fused decode to bf16, then library GEMM",
+                        "launch": launch}
     return {"workload": "llama70b_gate_up_28672x8192_int4_g128_rans, bf16 x", "parallelism": f"row-sharded tp{world}" +
             (" + nccl all-gather of [M, rows / ranks] slices" if world > 1 else ""), "rows_per_rank": n, "per_m": res}
 
@@ -1055,6 +1084,60 @@ def run_wire_decode(args):
         del d_streams, d_outs
 
 
+def run_model_load(args):
+    """Load time of one Llama-7B-shape transformer block (wq, wk, wv, wo 4096 x 4096; gate, up 11008 x 4096; down
+    4096 x 11008: 202 M INT4 weights) from the reference's wire format (`RANS` containers, 256-symbol blocks, p = 14,
+    as an `.eoq` file holds them) to resident entropy-coded tiles, by phase:
+      wire decode   -- BlockedRANSDecoder.decode_all: payload to the device, lane kernel, symbols back to the host;
+      tile encode   -- EOQWeight.from_symbols: host tile encoder (all cores) + upload of tiles, scales and tables;
+      from_rans     -- EOQWeight.from_rans: both in one call, what `EOQLinear` and `load_eoq_to_device` use.
+    One JSON line; a 32-block model is 32 times this plus embeddings (not coded)."""
+    import torch
+    from eoq_quantization_b200.core import rans_blocked as RB
+    from eoq_quantization_b200.fused import EOQWeight
+    torch.cuda.set_device(0)
+    shapes = [("wq", 4096, 4096), ("wk", 4096, 4096), ("wv", 4096, 4096), ("wo", 4096, 4096),
+              ("gate", 11008, 4096), ("up", 11008, 4096), ("down", 4096, 11008)]
+    layers = []
+    for i, (name, n, k) in enumerate(shapes):
+        sym, scales = make_layer(n, k, 40 + i)
+        t0 = time.perf_counter()
+        data = RB.BlockedRANSEncoder(256, 14).encode(sym.reshape(-1), 15)
+        enc_s = time.perf_counter() - t0
+        layers.append((name, n, k, sym, scales, data, RB.serialize_blocked_rans(data), enc_s))
+    EOQWeight.from_symbols(layers[0][3][:256], layers[0][4][:256 * 4096 // GROUP])       # context, arena and kernels warm
+    RB.BlockedRANSDecoder().decode_all(layers[0][5])
+    tot = {"wire_decode_s": 0.0, "tile_encode_s": 0.0, "from_rans_s": 0.0, "wire_encode_s": 0.0}
+    per_layer, weights, wire, keep = {}, 0, 0, []
+    for name, n, k, sym, scales, data, raw, enc_s in layers:
+        t0 = time.perf_counter()
+        got = RB.BlockedRANSDecoder().decode_all(data)
+        t1 = time.perf_counter()
+        w1 = EOQWeight.from_symbols(sym, scales)
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        w2 = EOQWeight.from_rans(raw, scales, (n, k))
+        torch.cuda.synchronize()
+        t3 = time.perf_counter()
+        assert np.array_equal(np.asarray(got, dtype=np.uint8), sym.reshape(-1))
+        assert torch.equal(w2.decode_symbols(), w1.decode_symbols())
+        per_layer[name] = {"shape": [n, k], "wire_decode_ms": (t1 - t0) * 1e3, "tile_encode_ms": (t2 - t1) * 1e3,
+                           "from_rans_ms": (t3 - t2) * 1e3, "wire_encode_ms": enc_s * 1e3}
+        tot["wire_decode_s"] += t1 - t0; tot["tile_encode_s"] += t2 - t1; tot["from_rans_s"] += t3 - t2; tot["wire_encode_s"] += enc_s
+        weights += n * k
+        wire += len(raw)
+        keep = [w1, w2]
+    line = {"metric": "model load: reference wire format to resident tiles, symbols/s", "unit": "Gsym/s", "n_gpus": 1,
+            "higher_is_better": True, "data": "synthetic", "dtype": "u32 rANS state",
+            "config": {"workload": "llama7b_block_load_int4_g128_block256_p14", "weights_per_block": weights,
+                       "wire_bytes_per_block": wire, "host_threads": os.cpu_count()},
+            "value": weights / tot["from_rans_s"] / 1e9, "block_load_s": tot["from_rans_s"],
+            "model_32_blocks_s": 32 * tot["from_rans_s"], "phases_s": tot, "per_layer": per_layer,
+            "note": "from_rans = wire decode on the GPU + host tile encoder + upload; wire_encode is the host encoder "
+                    "behind BlockedRANSEncoder.encode (conversion time, not load time)"}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1067,7 +1150,7 @@ def main():
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: how output slices are exchanged")
     ap.add_argument("--no-pdl", action="store_true", help="plain launches instead of programmatic dependent launches")
     ap.add_argument("--workload", default="mlp_pair",
-                    choices=["mlp_pair", "decode_dequant", "polar_q5", "llama7b_step", "prefill_gemm", "wire_decode"])
+                    choices=["mlp_pair", "decode_dequant", "polar_q5", "llama7b_step", "prefill_gemm", "wire_decode", "model_load"])
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
                     help="pass a knob to eoq_b200_tune (e.g. gemv_pairs=0: the one-tile-per-warp ring kernel)")
     args = ap.parse_args()
@@ -1084,6 +1167,8 @@ def main():
         return run_llama_step(args)
     if args.workload == "wire_decode":
         return run_wire_decode(args)
+    if args.workload == "model_load":
+        return run_model_load(args)
     if args.workload != "mlp_pair":
         args.steps = min(args.steps, 50)
         return run_aux(args)

@@ -59,15 +59,7 @@ class EOQLinear(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         require_cuda(x, "EOQLinear.forward")
-        rows = x.numel() // max(self.in_features, 1)
-        if x.dtype in (torch.float16, torch.bfloat16, torch.float32) and rows >= 1:
-            if rows <= 8:
-                return self.eoq.gemv(x, self.bias_param)
-            if x.dtype != torch.float32 and self.in_features % 16 == 0:
-                return self.eoq.gemm(x, self.bias_param)
-        dt = x.dtype if x.dtype in (torch.float16, torch.bfloat16) else torch.float32
-        bias = None if self.bias_param is None else self.bias_param.to(x.dtype)
-        return F.linear(x, self.eoq.dequantize(dt).to(x.dtype), bias)
+        return self.eoq.linear(x, self.bias_param)
 
     def memory_bytes(self) -> dict:
         info = self.eoq.info

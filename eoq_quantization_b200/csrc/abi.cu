@@ -829,6 +829,8 @@ extern "C" eoq_error_t eoq_b200_tiles_build(const uint8_t *symbols, const eoq_b2
             }
             target = nseg * nrb;
         }
+        // by default no tile is narrower than 64 columns (an explicit target_tiles may go down to 32)
+        target = std::min<uint32_t>(target, std::max(1u, opts->cols / 64) * ((opts->rows + 32 * G - 1) / (32 * G)));
     }
     std::unique_ptr<eoq_b200_tiles> t(new eoq_b200_tiles());
     // inside the library the integer widths are one family (the kernels are templated on the field width)

@@ -164,7 +164,7 @@ eoq_error_t build_tiled(const uint8_t *symbols, uint32_t N, uint32_t K, uint32_t
     const uint32_t nrb = Npad / rows_per_tile;
     const uint32_t units = K / kColGranule;
     uint32_t nseg = target_tiles / nrb;
-    nseg = std::max<uint32_t>(1, std::min<uint32_t>(nseg, std::max<uint32_t>(1, units / 4)));
+    nseg = std::max<uint32_t>(1, std::min<uint32_t>(nseg, std::max<uint32_t>(1, units / 2)));      // tiles of at least 32 columns
 
     out = TiledWeights();
     out.N = N; out.K = K; out.Npad = Npad; out.G = G; out.bits = bits; out.p = p; out.group = group; out.kind = kind;

@@ -29,8 +29,10 @@ def require_cuda(t: torch.Tensor, what: str) -> None:
                            "(there is no CPU path)")
 
 
-# Rows up to which the reference-API modules use the fused tensor-core path: it decodes the weight once per 128 rows,
-# while the modules also keep the packed INT4 copy, from which one dequantisation + a library GEMM is cheaper beyond.
+# Rows up to which the fused tensor-core path is used.  Every 96-row block of the weight re-reads all of X from L2
+# while it is decoded (the accumulators of 96 rows x 512 tokens fill tensor memory), so beyond this many rows one
+# decode to fp16 plus a library GEMM, whose tiles share X across 256 rows and more, is faster: measured cross-over
+# between 128 and 256 rows on 3584 x 8192 and 1024 x 28672.
 GEMM_MAX_ROWS = 128
 
 
@@ -195,6 +197,22 @@ class EOQWeight:
             _lib.check(_lib.lib().eoq_b200_gemm(self._h, x2.data_ptr(), _DTYPES[x.dtype], x2.shape[0], y.data_ptr(), _DTYPES[out_dtype],
                                                 b.data_ptr() if b is not None else None, _stream_ptr()), "eoq_b200_gemm")
         return y.reshape(*x.shape[:-1], self.rows)
+
+    def linear(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """y = x @ W.T (+ bias) in x.dtype by the fastest route built for the number of rows: up to 8 the fused
+        decode + GEMV; up to GEMM_MAX_ROWS of 16-bit activations on 4-bit weights the fused decode + tensor-core MMA;
+        beyond, the weight is decoded to a dense matrix once (fused decode + dequantise kernel) for a library GEMM."""
+        require_cuda(x, "EOQWeight.linear")
+        rows = x.numel() // max(self.cols, 1)
+        if rows >= 1 and x.dtype in _DTYPES:
+            if rows <= 8:
+                return self.gemv(x, bias)
+            if rows <= GEMM_MAX_ROWS and x.dtype != torch.float32 and self.kind == _lib.KIND_INT4_ABSMAX and self.cols % 16 == 0:
+                return self.gemm(x, bias)
+        dt = x.dtype if x.dtype in (torch.float16, torch.bfloat16) else torch.float32
+        with self._on_device(x, "EOQWeight.linear"):
+            w = self.dequantize(dt, device=x.device)
+        return torch.nn.functional.linear(x, w.to(x.dtype), None if bias is None else bias.to(x.dtype))
 
     def status(self) -> int:
         """0, or the status word a kernel left after a bounded wait gave up (synchronises the current stream)."""

@@ -165,3 +165,25 @@ def test_quantized_linear_of_other_widths_runs_fused():
         want = torch.nn.functional.linear(x.cuda(), ql._dequantize_weight(), ql.bias_param)
         assert O.rel_l2(y.cpu().numpy(), want.cpu().numpy()) < 1e-4, bits
         assert ql.eoq_weight().info.symbols_per_step == (1 if bits == 8 else 3)
+
+
+def test_linear_picks_a_route_by_the_number_of_rows_and_all_routes_agree():
+    """EOQWeight.linear: fused GEMV (<= 8 rows), fused tensor-core GEMM (<= GEMM_MAX_ROWS), decode + library GEMM beyond;
+    each against the dense matrix the oracle's dequantiser gives (tolerance: fp16 operands on the tensor-core routes)."""
+    from eoq_quantization_b200.fused import GEMM_MAX_ROWS, EOQWeight
+    rng = np.random.default_rng(5)
+    n, k = 300, 1024
+    wt = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    codes, scales = O.quantize_absmax(wt, 4, 128)
+    w = EOQWeight.from_symbols((codes + 7).astype(np.uint8), scales.astype(np.float16))
+    dense = (codes.reshape(-1, 128) * scales.astype(np.float16).astype(np.float32)[:, None]).reshape(n, k).astype(np.float64)
+    bias = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).cuda()
+    for rows in (1, 8, 9, GEMM_MAX_ROWS, GEMM_MAX_ROWS + 1, 300):
+        for dt in (torch.float16, torch.bfloat16, torch.float32):
+            x = torch.from_numpy(rng.standard_normal((rows, k)).astype(np.float32)).cuda().to(dt)
+            y = w.linear(x, bias)
+            assert y.dtype == dt and y.shape == (rows, n)
+            want = x.float().cpu().numpy().astype(np.float64) @ dense.T + bias.cpu().numpy()
+            tol = 1e-5 if dt == torch.float32 and rows <= 8 else 6e-3 if dt == torch.bfloat16 else 2e-3
+            assert O.rel_l2(y.float().cpu().numpy(), want) < tol, (rows, dt)
+    assert w.status() == 0

@@ -55,6 +55,42 @@ def test_decode_tensor_v2_matches_oracle(n):
         assert lib.eoq_cuda_decode_tensor(C.byref(h), body.ctypes.data, out2.ctypes.data, None) == 0
 
 
+@pytest.mark.parametrize("alphabet,p,block,n", [
+    (2, 8, 8, 100), (2, 9, 7, 1000), (3, 8, 50, 333), (5, 8, 33, 5000), (15, 12, 4096, 9000), (16, 14, 256, 70001),
+    (31, 14, 100, 12345), (200, 12, 1000, 40000), (256, 16, 256, 66000), (256, 12, 31, 3000), (1000, 16, 512, 50000),
+    (4096, 16, 2048, 100000), (4096, 13, 300, 30000), (5000, 16, 256, 20000)])
+def test_blocked_decoder_over_alphabets_precisions_and_block_sizes(alphabet, p, block, n):
+    """Streams from the oracle's encoder, decoded on the GPU: both table forms of the lane kernel (one packed word per
+    slot; slot -> symbol -> {freq, cum}), 8- and 16-bit symbols, blocks that end inside a group of eight steps or inside a
+    32-byte sector of the output, short last blocks, and the one-thread-per-block kernel (alphabets above 4096).
+
+    Both sides get a table that already sums to 2**p: normalising it again is the identity, so the test does not depend
+    on how ties are ordered when a residual is dealt out (numpy's argsort leaves that open above 16 symbols; the oracle
+    breaks ties by symbol index like the reference's C decoders)."""
+    rng = np.random.default_rng(alphabet * 31 + p)
+    sym = np.clip(rng.normal(alphabet / 2, max(alphabet / 7, 0.6), n), 0, alphabet - 1).astype(np.int64)
+    if alphabet > 2:
+        sym[rng.integers(0, n, n // 50)] = rng.integers(0, alphabet, n // 50)      # rare symbols get frequency 1
+    freq, _ = O.normalize(np.bincount(sym, minlength=alphabet), p)
+    t = O.Table(freq, p)
+    assert np.array_equal(t.freq, freq)
+    parts, offs, at = [], [], 0
+    for b in range(0, n, block):
+        enc = t.encode(sym[b:b + block])
+        assert np.array_equal(t.decode(enc, len(sym[b:b + block])), sym[b:b + block])   # the oracle round-trips its own stream
+        offs.append(at); parts.append(enc); at += len(enc)
+    stream = b"".join(parts)
+    nb = len(offs)
+    data = RB.BlockedRANSData(compressed_blocks=stream, block_offsets=offs, freq_table=freq.astype(np.int64),
+                              num_symbols=n, block_size=block, num_blocks=nb, alphabet_size=alphabet, precision_bits=p)
+    dec = RB.BlockedRANSDecoder()
+    assert np.array_equal(dec.decode_all(data), sym)
+    for b in (0, nb // 2, nb - 1):
+        assert np.array_equal(dec.decode_block(data, b), sym[b * block:(b + 1) * block])
+    data_ours, offs_ours = RB.encode_blocks(freq.astype(np.int64), p, sym, block)   # and our encoder writes the same bytes
+    assert bytes(data_ours) == stream and list(offs_ours) == offs
+
+
 def test_corrupt_stream_stays_in_bounds():
     """Garbage inside a block is not detected (as in the reference) but decoding terminates
     and never writes outside the output."""
