@@ -1089,8 +1089,9 @@ def run_model_load(args):
     4096 x 11008: 202 M INT4 weights) from the reference's wire format (`RANS` containers, 256-symbol blocks, p = 14,
     as an `.eoq` file holds them) to resident entropy-coded tiles, by phase:
       wire decode   -- BlockedRANSDecoder.decode_all: payload to the device, lane kernel, symbols back to the host;
-      tile encode   -- EOQWeight.from_symbols: host tile encoder (all cores) + upload of tiles, scales and tables;
-      from_rans     -- EOQWeight.from_rans: both in one call, what `EOQLinear` and `load_eoq_to_device` use.
+      tile encode   -- EOQWeight.from_symbols: symbols to the device, tile encoder kernels, scales and tables uploaded;
+      from_rans     -- EOQWeight.from_rans: wire decode and tile encode on the device in one call (the symbols never
+                       visit the host), what `EOQLinear` and `load_eoq_to_device` use.
     One JSON line; a 32-block model is 32 times this plus embeddings (not coded)."""
     import torch
     from eoq_quantization_b200.core import rans_blocked as RB
@@ -1133,8 +1134,9 @@ def run_model_load(args):
                        "wire_bytes_per_block": wire, "host_threads": os.cpu_count()},
             "value": weights / tot["from_rans_s"] / 1e9, "block_load_s": tot["from_rans_s"],
             "model_32_blocks_s": 32 * tot["from_rans_s"], "phases_s": tot, "per_layer": per_layer,
-            "note": "from_rans = wire decode on the GPU + host tile encoder + upload; wire_encode is the host encoder "
-                    "behind BlockedRANSEncoder.encode (conversion time, not load time)"}
+            "note": "from_rans = payload to the device + wire decode + tile encoder kernels, symbols never on the host; "
+                    "wire_decode = BlockedRANSDecoder.decode_all to a host array; tile_encode = from_symbols from a host array; "
+                    "wire_encode is the host encoder behind BlockedRANSEncoder.encode (conversion time, not load time)"}
     print(json.dumps(line), flush=True)
 
 

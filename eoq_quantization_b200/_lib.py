@@ -41,7 +41,7 @@ EXPORTS = [
     "eoq_cuda_batch_sync_and_free", "eoq_cuda_batch_destroy",
     "eoq_b200_decode_blocked", "eoq_b200_encode_blocked",
     "eoq_b200_tiles_build", "eoq_b200_tiles_view", "eoq_b200_tiles_free",
-    "eoq_b200_weight_from_tiles", "eoq_b200_weight_from_symbols", "eoq_b200_weight_from_rans", "eoq_b200_weight_destroy",
+    "eoq_b200_weight_from_tiles", "eoq_b200_weight_from_symbols", "eoq_b200_weight_from_device_symbols", "eoq_b200_weight_from_rans", "eoq_b200_weight_destroy",
     "eoq_b200_weight_info", "eoq_b200_gemv", "eoq_b200_gemm",
     "eoq_b200_gather_create", "eoq_b200_gather_connect", "eoq_b200_gather_destroy", "eoq_b200_gather_buffer",
     "eoq_b200_gather_status", "eoq_b200_gather_set_timeout_ms", "eoq_b200_gather_wait", "eoq_b200_gemv_gather", "eoq_b200_gemv_static_scratch", "eoq_b200_gemv_host", "eoq_b200_gemv_host_async", "eoq_b200_weight_decode",
@@ -49,7 +49,7 @@ EXPORTS = [
     "eoq_b200_weight_status",
 ]
 #: exported for this project's benchmarks and tests only (declared in csrc/eoq_internal.h, not in the public header)
-INTERNAL_EXPORTS = ["eoq_b200_tune", "eoq_b200_launch_count"]
+INTERNAL_EXPORTS = ["eoq_b200_tune", "eoq_b200_launch_count", "eoq_b200_weight_read"]
 
 
 class EOQError(RuntimeError):
@@ -149,6 +149,7 @@ def lib() -> C.CDLL:
         "eoq_b200_tiles_free": (None, [vp]),
         "eoq_b200_weight_from_tiles": (C.c_int, [vp, vp, vp, C.POINTER(vp)]),
         "eoq_b200_weight_from_symbols": (C.c_int, [vp, vp, C.POINTER(WeightOpts), C.POINTER(vp)]),
+        "eoq_b200_weight_from_device_symbols": (C.c_int, [vp, vp, C.POINTER(WeightOpts), C.POINTER(vp)]),
         "eoq_b200_weight_from_rans": (C.c_int, [vp, C.c_size_t, vp, C.POINTER(WeightOpts), C.POINTER(vp)]),
         "eoq_b200_weight_destroy": (None, [vp]),
         "eoq_b200_weight_info": (C.c_int, [vp, C.POINTER(WeightInfo)]),
@@ -171,6 +172,7 @@ def lib() -> C.CDLL:
         "eoq_b200_weight_status": (C.c_int, [vp, vp]),
         "eoq_b200_tune": (C.c_int, [C.c_char_p, C.c_int]),
         "eoq_b200_launch_count": (C.c_uint64, []),
+        "eoq_b200_weight_read": (C.c_uint64, [vp, C.c_int, vp, C.c_uint64]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)

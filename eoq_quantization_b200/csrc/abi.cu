@@ -741,7 +741,9 @@ eoq_error_t resolve_opts(const eoq_b200_weight_opts_t *o, uint32_t &bits, uint32
     return EOQ_OK;
 }
 
-eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const float *centroids, eoq_b200_weight_t **out)
+// `built` (optional): the stream already on the device, `built_bytes` long (tw.stream is then empty); it is taken over.
+eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const float *centroids, eoq_b200_weight_t **out,
+                          DeviceBuf *built = nullptr, size_t built_bytes = 0)
 {
     std::unique_ptr<eoq_b200_weight> w(new eoq_b200_weight());
     CU_TRY(cudaGetDevice(&w->device));
@@ -752,14 +754,14 @@ eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const 
         w->stage_bytes = std::max(w->stage_bytes, ((d.len64 << 6) + 64u + 127u) & ~127u);
         w->max_ncols = std::max(w->max_ncols, d.ncols);
     }
-    w->stream_bytes = tw.stream.size();
+    w->stream_bytes = built ? built_bytes : tw.stream.size();
     w->scale_bytes = (size_t)tw.N * (tw.K / tw.group) * 2;
     w->partial_bytes = tw.nseg > 1 ? (size_t)tw.nseg * tw.Npad * 8 * sizeof(float) : 0;
     // INT4 x 3 weights run through the pair kernel, which meets in a few partial rows; the ring kernel's scratch (one
     // row per column segment) is allocated by the first call that needs it (see ring_scratch)
     const bool pairs_layout = tw.kind == EOQ_B200_KIND_INT4_ABSMAX && tw.bits == 4 && tw.G == 3;
     if (w->table.alloc(tw.table.size() * 4) != cudaSuccess || w->tiles.alloc(tw.tiles.size() * sizeof(TileDesc)) != cudaSuccess ||
-        w->stream.alloc(tw.stream.size()) != cudaSuccess || w->scales.alloc(w->scale_bytes) != cudaSuccess ||
+        (!built && w->stream.alloc(tw.stream.size()) != cudaSuccess) || w->scales.alloc(w->scale_bytes) != cudaSuccess ||
         (!pairs_layout && w->partials.alloc(w->partial_bytes) != cudaSuccess) || w->counters.alloc((size_t)tw.nrb * 4) != cudaSuccess ||
         w->status.alloc(4) != cudaSuccess ||
         w->xbuf.alloc((size_t)8 * tw.K * 4) != cudaSuccess || w->ybuf.alloc((size_t)8 * tw.N * 4) != cudaSuccess ||
@@ -771,7 +773,8 @@ eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const 
     }
     CU_TRY(cudaMemcpy(w->table.p, tw.table.data(), tw.table.size() * 4, cudaMemcpyHostToDevice));
     CU_TRY(cudaMemcpy(w->tiles.p, tw.tiles.data(), tw.tiles.size() * sizeof(TileDesc), cudaMemcpyHostToDevice));
-    CU_TRY(cudaMemcpy(w->stream.p, tw.stream.data(), tw.stream.size(), cudaMemcpyHostToDevice));
+    if (built) { w->stream.p = built->p; built->p = nullptr; }
+    else CU_TRY(cudaMemcpy(w->stream.p, tw.stream.data(), tw.stream.size(), cudaMemcpyHostToDevice));
     CU_TRY(cudaMemcpy(w->scales.p, scales, w->scale_bytes, cudaMemcpyHostToDevice));
     if (pairs_layout) {
         w->pair_partial_bytes = (size_t)pair_partial_slots(tw.nrb, tw.nseg) * tw.Npad * 4 * sizeof(float);
@@ -803,6 +806,125 @@ eoq_error_t upload_weight(const TiledWeights &tw, const uint16_t *scales, const 
 }  // namespace
 
 struct eoq_b200_tiles { TiledWeights tw; };
+extern "C" eoq_error_t eoq_b200_tiles_build(const uint8_t *symbols, const eoq_b200_weight_opts_t *opts, eoq_b200_tiles_t **out);
+extern "C" void eoq_b200_tiles_free(eoq_b200_tiles_t *t);
+
+// How many tiles a weight is cut into when the caller does not say.
+static uint32_t default_target_tiles(const eoq_b200_weight_opts_t *opts, uint32_t bits, uint32_t G)
+{
+    const int sms = have_device() ? device_sm_count() : 0;
+    const uint32_t warps = (uint32_t)(sms > 0 ? sms : 148) * 16;      // one wave of 16-warp CTAs
+    uint32_t target = warps;
+    if (opts->kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 4 && G == 3) {
+        // The pair kernel gives every warp two vertically adjacent tiles and stages them whole in shared memory,
+        // which holds tiles of up to 7 x 16 columns: take the fewest waves of pairs whose column segments are
+        // that narrow, and as many segments as fill those waves.
+        const uint32_t nrb = (opts->rows + 32 * G - 1) / (32 * G), nrbp = (nrb + 1) / 2;
+        const uint32_t units = opts->cols / 16, need = (units + 6) / 7;
+        uint32_t nseg = 1;
+        for (uint32_t waves = 1; waves <= 64; waves++) {
+            nseg = std::max(1u, waves * warps / nrbp);
+            if (nseg >= need) break;
+        }
+        target = nseg * nrb;
+    }
+    // by default no tile is narrower than 64 columns (an explicit target_tiles may go down to 32)
+    return std::min<uint32_t>(target, std::max(1u, opts->cols / 64) * ((opts->rows + 32 * G - 1) / (32 * G)));
+}
+
+// The tiled layout built on the device from symbols that are already there (one per byte, row-major [rows, cols], in
+// memory this library allocated: 256-byte aligned): joint-symbol counts by a kernel, frequencies and table on the host
+// (a few thousand numbers), every tile encoded by one warp, the stream laid out on the host from the tiles' sizes and
+// filled by a scatter kernel.  Byte-identical to build_tiled.  EOQ_ERR_UNSUPPORTED (nothing launched) when a tile has
+// 65536 columns or more or the scratch would pass 4 GB: the caller then encodes on the host.
+static eoq_error_t build_tiled_device(const uint8_t *d_sym, const eoq_b200_weight_opts_t *opts, TiledWeights &tw, DeviceBuf &stream,
+                                      size_t &stream_bytes, cudaStream_t st)
+{
+    uint32_t bits, G, p, target; uint8_t pad;
+    eoq_error_t rc = resolve_opts(opts, bits, G, p, target, pad);
+    if (rc != EOQ_OK) return rc;
+    if (opts->rows == 0 || opts->cols == 0 || opts->group == 0) return EOQ_ERR_INVALID_HEADER;
+    if (target == 0) target = default_target_tiles(opts, bits, G);
+    const uint32_t family = opts->kind == EOQ_B200_KIND_Q5_POLAR ? EOQ_B200_KIND_Q5_POLAR : EOQ_B200_KIND_INT4_ABSMAX;
+    rc = tiled_geometry(opts->rows, opts->cols, bits, G, p, opts->group, family, target, tw);
+    if (rc != EOQ_OK) return rc;
+    const size_t ntiles = tw.tiles.size();
+    uint32_t max_ncols = 0;
+    for (const TileDesc &d : tw.tiles) max_ncols = std::max(max_ncols, d.ncols);
+    const size_t scratch_bytes = ntiles * (size_t)max_ncols * 128u;
+    if (max_ncols >= 65536u || scratch_bytes > (4ull << 30)) return EOQ_ERR_UNSUPPORTED;
+
+    auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    const size_t at_counts = 0, at_fc = up(at_counts + (size_t)tw.alphabet * 8), at_tiles = up(at_fc + (size_t)tw.alphabet * 8),
+                 at_state = up(at_tiles + ntiles * sizeof(TileDesc)), at_count = up(at_state + ntiles * 128), at_info = up(at_count + ntiles * 128),
+                 at_scratch = up(at_info + ntiles * 8), total_tmp = at_scratch + scratch_bytes;
+    DeviceArena tmp;
+    if (tmp.acquire(total_tmp) != cudaSuccess) return EOQ_ERR_ALLOC;
+    uint8_t *d = tmp.base();
+
+    CU_TRY(cudaMemsetAsync(d + at_counts, 0, (size_t)tw.alphabet * 8, st));
+    if (launch_tile_hist(d_sym, tw.N, tw.K, tw.Npad, G, bits, reinterpret_cast<unsigned long long *>(d + at_counts), st) != 0) return EOQ_ERR_CUDA;
+    std::vector<uint64_t> count(tw.alphabet);
+    CU_TRY(cudaMemcpyAsync(count.data(), d + at_counts, (size_t)tw.alphabet * 8, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    std::vector<uint32_t> freq, cum;
+    rc = tiled_table(count, tw, freq, cum);
+    if (rc != EOQ_OK) return rc;
+    std::vector<uint32_t> fc((size_t)tw.alphabet * 2);
+    for (uint32_t s = 0; s < tw.alphabet; s++) { fc[2 * s] = freq[s] ? freq[s] : 1u; fc[2 * s + 1] = cum[s]; }   // absent symbols never occur
+    CU_TRY(cudaMemcpyAsync(d + at_fc, fc.data(), fc.size() * 4, cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaMemcpyAsync(d + at_tiles, tw.tiles.data(), ntiles * sizeof(TileDesc), cudaMemcpyHostToDevice, st));
+    TileEncodeArgs ea = {};
+    ea.sym = d_sym; ea.tiles = reinterpret_cast<const TileDesc *>(d + at_tiles); ea.freq_cum = reinterpret_cast<const uint2 *>(d + at_fc);
+    ea.scratch = reinterpret_cast<uint32_t *>(d + at_scratch); ea.state = reinterpret_cast<uint32_t *>(d + at_state);
+    ea.count = reinterpret_cast<uint32_t *>(d + at_count); ea.info = reinterpret_cast<uint2 *>(d + at_info);
+    ea.N = tw.N; ea.K = tw.K; ea.G = G; ea.bits = bits; ea.p = p; ea.ntiles = (uint32_t)ntiles; ea.max_ncols = max_ncols;
+    if (launch_tile_encode(ea, st) != 0) return EOQ_ERR_CUDA;
+    std::vector<uint32_t> info(ntiles * 2);
+    CU_TRY(cudaMemcpyAsync(info.data(), d + at_info, ntiles * 8, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    for (size_t t = 0; t < ntiles; t++) {
+        const uint32_t rows = info[2 * t], drift = info[2 * t + 1];
+        tw.tiles[t].len64 = (128u + rows * 64u) >> 6;
+        if (drift > kMaxRingDrift) tw.tiles[t].seg |= kTileDirectFlag;
+        tw.max_drift = std::max(tw.max_drift, drift);
+    }
+    rc = tiled_layout(tw, stream_bytes);
+    if (rc != EOQ_OK) return rc;
+    if (stream.alloc(stream_bytes) != cudaSuccess) return EOQ_ERR_ALLOC;
+    CU_TRY(cudaMemsetAsync(stream.p, 0, stream_bytes, st));
+    CU_TRY(cudaMemcpyAsync(d + at_tiles, tw.tiles.data(), ntiles * sizeof(TileDesc), cudaMemcpyHostToDevice, st));
+    TileScatterArgs sa = {};
+    sa.tiles = reinterpret_cast<const TileDesc *>(d + at_tiles); sa.scratch = ea.scratch; sa.state = ea.state; sa.count = ea.count;
+    sa.stream = stream.as<uint8_t>(); sa.head_bytes = tw.head_bytes; sa.ntiles = (uint32_t)ntiles; sa.max_ncols = max_ncols;
+    if (launch_tile_scatter(sa, st) != 0) return EOQ_ERR_CUDA;
+    CU_TRY(cudaStreamSynchronize(st));
+    return EOQ_OK;
+}
+
+// A weight from symbols in device memory (this library's own allocation).  Falls back to the host encoder, through a
+// copy of the symbols, where the device encoder declines.
+static eoq_error_t weight_from_device_symbols(const uint8_t *d_sym, const uint16_t *scales_fp16, const eoq_b200_weight_opts_t *opts,
+                                              eoq_b200_weight_t **out)
+{
+    TiledWeights tw;
+    DeviceBuf stream;
+    size_t stream_bytes = 0;
+    eoq_error_t rc = build_tiled_device(d_sym, opts, tw, stream, stream_bytes, nullptr);
+    if (rc == EOQ_ERR_UNSUPPORTED && tw.N != 0) {
+        std::vector<uint8_t> host((size_t)opts->rows * opts->cols);
+        CU_TRY(cudaMemcpy(host.data(), d_sym, host.size(), cudaMemcpyDeviceToHost));
+        eoq_b200_tiles_t *t = nullptr;
+        rc = eoq_b200_tiles_build(host.data(), opts, &t);
+        if (rc != EOQ_OK) return rc;
+        rc = upload_weight(t->tw, scales_fp16, opts->kind == EOQ_B200_KIND_Q5_POLAR ? opts->centroids : nullptr, out);
+        eoq_b200_tiles_free(t);
+        return rc;
+    }
+    if (rc != EOQ_OK) return rc;
+    return upload_weight(tw, scales_fp16, opts->kind == EOQ_B200_KIND_Q5_POLAR ? opts->centroids : nullptr, out, &stream, stream_bytes);
+}
+
 
 extern "C" eoq_error_t eoq_b200_tiles_build(const uint8_t *symbols, const eoq_b200_weight_opts_t *opts, eoq_b200_tiles_t **out)
 {
@@ -812,26 +934,7 @@ extern "C" eoq_error_t eoq_b200_tiles_build(const uint8_t *symbols, const eoq_b2
     eoq_error_t rc = resolve_opts(opts, bits, G, p, target, pad);
     if (rc != EOQ_OK) return rc;
     if (opts->rows == 0 || opts->cols == 0 || opts->group == 0) return EOQ_ERR_INVALID_HEADER;
-    if (target == 0) {
-        const int sms = have_device() ? device_sm_count() : 0;
-        const uint32_t warps = (uint32_t)(sms > 0 ? sms : 148) * 16;      // one wave of 16-warp CTAs
-        target = warps;
-        if (opts->kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 4 && G == 3) {
-            // The pair kernel gives every warp two vertically adjacent tiles and stages them whole in shared memory,
-            // which holds tiles of up to 7 x 16 columns: take the fewest waves of pairs whose column segments are
-            // that narrow, and as many segments as fill those waves.
-            const uint32_t nrb = (opts->rows + 32 * G - 1) / (32 * G), nrbp = (nrb + 1) / 2;
-            const uint32_t units = opts->cols / 16, need = (units + 6) / 7;
-            uint32_t nseg = 1;
-            for (uint32_t waves = 1; waves <= 64; waves++) {
-                nseg = std::max(1u, waves * warps / nrbp);
-                if (nseg >= need) break;
-            }
-            target = nseg * nrb;
-        }
-        // by default no tile is narrower than 64 columns (an explicit target_tiles may go down to 32)
-        target = std::min<uint32_t>(target, std::max(1u, opts->cols / 64) * ((opts->rows + 32 * G - 1) / (32 * G)));
-    }
+    if (target == 0) target = default_target_tiles(opts, bits, G);
     std::unique_ptr<eoq_b200_tiles> t(new eoq_b200_tiles());
     // inside the library the integer widths are one family (the kernels are templated on the field width)
     const uint32_t family = opts->kind == EOQ_B200_KIND_Q5_POLAR ? EOQ_B200_KIND_Q5_POLAR : EOQ_B200_KIND_INT4_ABSMAX;
@@ -880,12 +983,30 @@ extern "C" eoq_error_t eoq_b200_weight_from_symbols(const uint8_t *symbols, cons
         eoq_error_t rc = resolve_opts(opts, bits, G, p, target, pad);
         return rc != EOQ_OK ? rc : EOQ_ERR_CUDA;
     }
-    eoq_b200_tiles_t *t = nullptr;
-    eoq_error_t rc = eoq_b200_tiles_build(symbols, opts, &t);
-    if (rc != EOQ_OK) return rc;
-    rc = upload_weight(t->tw, scales_fp16, opts->kind == EOQ_B200_KIND_Q5_POLAR ? opts->centroids : nullptr, out);
-    eoq_b200_tiles_free(t);
-    return rc;
+    // the symbols go to the device and the tiles are encoded there (the host encoder, which the device encoder matches
+    // byte for byte, stays behind eoq_b200_tiles_build for callers without a device at hand)
+    if (opts->rows == 0 || opts->cols == 0) return EOQ_ERR_INVALID_HEADER;
+    const size_t n = (size_t)opts->rows * opts->cols;
+    DeviceArena sym;
+    if (sym.acquire(n) != cudaSuccess) return EOQ_ERR_ALLOC;
+    CU_TRY(cudaMemcpy(sym.base(), symbols, n, cudaMemcpyHostToDevice));
+    return weight_from_device_symbols(sym.base(), scales_fp16, opts, out);
+}
+
+extern "C" eoq_error_t eoq_b200_weight_from_device_symbols(const uint8_t *d_symbols, const uint16_t *scales_fp16,
+                                                           const eoq_b200_weight_opts_t *opts, eoq_b200_weight_t **out)
+{
+    if (!d_symbols || !scales_fp16 || !opts || !out) return EOQ_ERR_NULL_PTR;
+    *out = nullptr;
+    if (!have_device()) return EOQ_ERR_CUDA;
+    if (opts->rows == 0 || opts->cols == 0) return EOQ_ERR_INVALID_HEADER;
+    if ((reinterpret_cast<uintptr_t>(d_symbols) & 3u) == 0) return weight_from_device_symbols(d_symbols, scales_fp16, opts, out);
+    // the counting kernel reads four symbols at a time: an odd base address goes through an aligned copy
+    const size_t n = (size_t)opts->rows * opts->cols;
+    DeviceArena sym;
+    if (sym.acquire(n) != cudaSuccess) return EOQ_ERR_ALLOC;
+    CU_TRY(cudaMemcpy(sym.base(), d_symbols, n, cudaMemcpyDeviceToDevice));
+    return weight_from_device_symbols(sym.base(), scales_fp16, opts, out);
 }
 
 extern "C" eoq_error_t eoq_b200_weight_from_rans(const uint8_t *c, size_t size, const uint16_t *scales_fp16,
@@ -908,11 +1029,14 @@ extern "C" eoq_error_t eoq_b200_weight_from_rans(const uint8_t *c, size_t size, 
     std::memcpy(offs.data(), c + 32 + (size_t)a * 4, (size_t)nb * 4);
     eoq_error_t rc = normalize_reference(raw.data(), a, p, freq, cdf);
     if (rc != EOQ_OK) return rc;
-    std::vector<uint8_t> sym(n);
+    if (!have_device()) return EOQ_ERR_CUDA;
+    // decoded into device memory and encoded into tiles there: the symbols never visit the host
+    DeviceArena sym;
+    if (sym.acquire(n) != cudaSuccess) return EOQ_ERR_ALLOC;
     rc = eoq_b200_decode_blocked(freq.data(), a, p, c + 32 + (size_t)a * 4 + (size_t)nb * 4, dsz, offs.data(), nb, bs, n,
-                                 sym.data(), 1, 0, nullptr);
+                                 sym.base(), 1, 1, nullptr);
     if (rc != EOQ_OK) return rc;
-    return eoq_b200_weight_from_symbols(sym.data(), scales_fp16, opts, out);
+    return weight_from_device_symbols(sym.base(), scales_fp16, opts, out);
 }
 
 extern "C" void eoq_b200_weight_destroy(eoq_b200_weight_t *w) { delete w; }
@@ -1296,6 +1420,17 @@ extern "C" eoq_error_t eoq_b200_weight_status(eoq_b200_weight_t *w, void *stream
     return *static_cast<volatile uint32_t *>(w->status_host) ? EOQ_ERR_CUDA : EOQ_OK;
 }
 
+
+// Test hook (not in the public header): copy a resident weight's tile stream (what = 0), tile descriptors (1) or decode
+// table (2) to the host; returns the bytes that part has, copies min(bytes, capacity).
+extern "C" uint64_t eoq_b200_weight_read(eoq_b200_weight_t *w, int what, void *host, uint64_t capacity)
+{
+    if (!w) return 0;
+    const void *src = what == 0 ? w->stream.p : what == 1 ? w->tiles.p : what == 2 ? w->table.p : nullptr;
+    const uint64_t bytes = what == 0 ? w->stream_bytes : what == 1 ? (uint64_t)w->ntiles * sizeof(TileDesc) : what == 2 ? ((uint64_t)4 << w->p) : 0;
+    if (src && host && cudaMemcpy(host, src, (size_t)std::min(bytes, capacity), cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
+    return bytes;
+}
 
 extern "C" int eoq_b200_tune(const char *key, int value)
 {

@@ -21,6 +21,8 @@
 // eoq_b200_launch_count is the number of kernels this library has launched since it was loaded.
 extern "C" int eoq_b200_tune(const char *key, int value);
 extern "C" uint64_t eoq_b200_launch_count(void);
+struct eoq_b200_weight;
+extern "C" uint64_t eoq_b200_weight_read(eoq_b200_weight *w, int what, void *host, uint64_t capacity);   // test hook, see abi.cu
 
 namespace eoq {
 
@@ -85,6 +87,14 @@ eoq_error_t normalize_reference(const uint32_t *raw, uint32_t alphabet, uint32_t
 // Wire-format ("v1") block encoder, byte-identical to core/rans.py:210-276.
 void encode_block_v1(const uint32_t *freq, const uint32_t *cdf, uint32_t p,
                      const uint32_t *syms, uint32_t n, std::vector<uint8_t> &out);
+
+// The pieces of build_tiled that do not touch the symbols, shared with the device-side tile encoder: geometry
+// (padded rows, row blocks, column segments, tile descriptors without sizes), joint-symbol frequencies and decode table
+// from the joint symbols' counts, and the stream layout (head_bytes, every off64, total bytes) from the tiles' len64.
+eoq_error_t tiled_geometry(uint32_t N, uint32_t K, uint32_t bits, uint32_t G, uint32_t p, uint32_t group, uint32_t kind,
+                           uint32_t target_tiles, TiledWeights &out);
+eoq_error_t tiled_table(const std::vector<uint64_t> &count, TiledWeights &out, std::vector<uint32_t> &freq, std::vector<uint32_t> &cum);
+eoq_error_t tiled_layout(TiledWeights &out, size_t &total);
 
 // Build the tiled layout from one symbol per byte, row-major [N, K].
 eoq_error_t build_tiled(const uint8_t *symbols, uint32_t N, uint32_t K, uint32_t bits, uint32_t G,
@@ -204,5 +214,27 @@ void set_gemv_pairs(int v);
 uint32_t pair_partial_slots(uint32_t nrb, uint32_t nseg);
 bool gemv_takes_pairs(const GemvArgs &a, uint32_t G, uint32_t bits, uint32_t kind);
 int launch_gather_wait(const GemvArgs &a, void *stream);
+
+// Device-side tile encoder (kernels.cu): joint-symbol counts; per-tile encode into a scratch of max_ncols x 32 words
+// per tile; scatter into the laid-out stream.  `sym` is one symbol per byte, row-major [N, K], K a multiple of 16.
+struct TileEncodeArgs {
+    const uint8_t *sym;
+    const TileDesc *tiles;        // row0, col0, ncols of every tile
+    const uint2 *freq_cum;        // per joint symbol {freq, cum}
+    uint32_t *scratch;            // [ntiles][max_ncols][32] {word | step << 16}
+    uint32_t *state, *count;      // [ntiles][32]
+    uint2 *info;                  // [ntiles] {rows of 32 words (even), drift}
+    uint32_t N, K, G, bits, p, ntiles, max_ncols;
+};
+struct TileScatterArgs {
+    const TileDesc *tiles;        // with off64 and len64
+    const uint32_t *scratch, *state, *count;
+    uint8_t *stream;              // zero-filled
+    uint32_t head_bytes, ntiles, max_ncols;
+};
+int launch_tile_hist(const uint8_t *sym, uint32_t N, uint32_t K, uint32_t Npad, uint32_t G, uint32_t bits, unsigned long long *counts,
+                     void *stream);
+int launch_tile_encode(const TileEncodeArgs &a, void *stream);
+int launch_tile_scatter(const TileScatterArgs &a, void *stream);
 
 }  // namespace eoq

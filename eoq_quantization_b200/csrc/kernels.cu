@@ -3157,4 +3157,119 @@ int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
+
+// ---------------------------------------------------------------------------
+// Device-side tile encoder: the tiled layout built on the GPU from symbols that are already there (a tensor decoded
+// from the wire format, or symbols copied in), byte-identical to the host builder (rans_host.cpp: build_tiled).
+//
+//   tile_hist_kernel     counts the joint symbols (G codes of `bits` bits per rANS step); the host turns the counts into
+//                        frequencies and the decode table (a few thousand numbers);
+//   tile_encode_kernel   one warp per tile, one lane per rANS stream: walks the tile's columns right to left, pushes
+//                        16-bit words into a scratch column {word | step << 16}, leaves the final states, the word
+//                        counts, the tile's row count (longest lane, rounded up to even) and how far the lanes' read
+//                        positions drift apart;
+//   tile_scatter_kernel  after the host has laid the tiles out (head region, packed tails): writes states and word rows
+//                        to their place in the stream, words in decode order (last pushed first), zeros past a lane's end.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) tile_hist_kernel(const uint8_t *__restrict__ sym, uint32_t N, uint32_t K, uint32_t Npad,
+                                                          uint32_t G, uint32_t bits, unsigned long long *__restrict__ counts)
+{
+    extern __shared__ uint32_t hist[];
+    const uint32_t alphabet = 1u << (bits * G), mask = (1u << bits) - 1u;
+    for (uint32_t i = threadIdx.x; i < alphabet; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    const uint64_t quads = (uint64_t)(Npad / G) * (K / 4);            // four columns of one row group per item
+    for (uint64_t q = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t rg = (uint32_t)(q / (K / 4)), c = (uint32_t)(q % (K / 4)) * 4u;
+        uint32_t v[4] = {0, 0, 0, 0};
+        for (uint32_t j = 0; j < G; j++) {
+            const uint32_t r = rg * G + j;
+            const uint32_t w = *reinterpret_cast<const uint32_t *>(sym + (size_t)(r < N ? r : r % N) * K + c);
+#pragma unroll
+            for (uint32_t u = 0; u < 4; u++) v[u] |= ((w >> (8u * u)) & mask) << (bits * j);
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < 4; u++) atomicAdd(&hist[v[u]], 1u);
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < alphabet; i += blockDim.x)
+        if (hist[i]) atomicAdd(&counts[i], (unsigned long long)hist[i]);
+}
+
+__global__ void __launch_bounds__(128) tile_encode_kernel(const TileEncodeArgs a)
+{
+    const uint32_t lane = threadIdx.x & 31u, t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= a.ntiles) return;
+    const TileDesc d = a.tiles[t];
+    const uint32_t mask = (1u << a.bits) - 1u;
+    const uint8_t *src[3] = {nullptr, nullptr, nullptr};
+    for (uint32_t j = 0; j < a.G; j++) {
+        const uint32_t r = d.row0 + lane * a.G + j;
+        src[j] = a.sym + (size_t)(r < a.N ? r : r % a.N) * a.K + d.col0;
+    }
+    uint32_t *col = a.scratch + (size_t)t * a.max_ncols * 32u + lane;       // this lane's pushed words, [k][lane]
+    uint32_t x = 1u << 16, cnt = 0;
+    for (uint32_t c = d.ncols; c-- > 0;) {
+        uint32_t v = 0;
+        for (uint32_t j = 0; j < a.G; j++) v |= ((uint32_t)src[j][c] & mask) << (a.bits * j);
+        const uint2 fc = __ldg(a.freq_cum + v);
+        if ((unsigned long long)x >= ((unsigned long long)fc.x << (32u - a.p))) {
+            col[(size_t)cnt * 32u] = (x & 0xFFFFu) | (c << 16);
+            cnt++;
+            x >>= 16;
+        }
+        x = ((x / fc.x) << a.p) + (x % fc.x) + fc.y;
+    }
+    a.state[(size_t)t * 32u + lane] = x;
+    a.count[(size_t)t * 32u + lane] = cnt;
+    const uint32_t longest = (__reduce_max_sync(0xffffffffu, cnt) + 1u) & ~1u;
+    // drift: the lanes' read positions after each step, in decode order (the word pushed last is read first)
+    uint32_t pos = 0, drift = 0;
+    for (uint32_t c = 0; c < d.ncols; c++) {
+        if (pos < cnt && (col[(size_t)(cnt - 1u - pos) * 32u] >> 16) == c) pos++;
+        drift = max(drift, __reduce_max_sync(0xffffffffu, pos) - __reduce_min_sync(0xffffffffu, pos));
+    }
+    if (lane == 0) a.info[t] = make_uint2(longest, drift);
+}
+
+__global__ void __launch_bounds__(128) tile_scatter_kernel(const TileScatterArgs a)
+{
+    const uint32_t lane = threadIdx.x & 31u, t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= a.ntiles) return;
+    const TileDesc d = a.tiles[t];
+    const uint32_t H = a.head_bytes, rows = ((d.len64 << 6) - 128u) >> 6;
+    uint8_t *head = a.stream + (size_t)t * H, *tail = a.stream + ((size_t)d.off64 << 6) - H;
+    auto at = [&](uint32_t b) { return b < H ? head + b : tail + b; };          // byte b of the tile
+    *reinterpret_cast<uint32_t *>(at(4u * lane)) = a.state[(size_t)t * 32u + lane];
+    const uint32_t cnt = a.count[(size_t)t * 32u + lane];
+    const uint32_t *col = a.scratch + (size_t)t * a.max_ncols * 32u + lane;
+    for (uint32_t k = 0; k < rows; k++) {
+        const uint16_t w = k < cnt ? (uint16_t)col[(size_t)(cnt - 1u - k) * 32u] : (uint16_t)0;
+        *reinterpret_cast<uint16_t *>(at(128u + k * 64u + lane * 2u)) = w;
+    }
+}
+
+int launch_tile_hist(const uint8_t *sym, uint32_t N, uint32_t K, uint32_t Npad, uint32_t G, uint32_t bits, unsigned long long *counts,
+                     void *stream)
+{
+    const uint32_t grid = (uint32_t)std::max(1, device_sm_count()) * 4u;
+    tile_hist_kernel<<<grid, 256, sizeof(uint32_t) << (bits * G), reinterpret_cast<cudaStream_t>(stream)>>>(sym, N, K, Npad, G, bits, counts);
+    g_launches++;
+    return (int)cudaGetLastError();
+}
+
+int launch_tile_encode(const TileEncodeArgs &a, void *stream)
+{
+    tile_encode_kernel<<<(a.ntiles + 3u) / 4u, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+    g_launches++;
+    return (int)cudaGetLastError();
+}
+
+int launch_tile_scatter(const TileScatterArgs &a, void *stream)
+{
+    tile_scatter_kernel<<<(a.ntiles + 3u) / 4u, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+    g_launches++;
+    return (int)cudaGetLastError();
+}
+
 }  // namespace eoq

@@ -148,12 +148,10 @@ static void parallel_for(size_t n, const std::function<void(size_t)> &fn)
     for (auto &t : pool) t.join();
 }
 
-eoq_error_t build_tiled(const uint8_t *symbols, uint32_t N, uint32_t K, uint32_t bits, uint32_t G,
-                        uint32_t p, uint32_t group, uint32_t kind, uint32_t target_tiles,
-                        uint8_t pad_symbol, TiledWeights &out)
+// Geometry of the tiled layout: padded rows, row blocks, column segments.
+eoq_error_t tiled_geometry(uint32_t N, uint32_t K, uint32_t bits, uint32_t G, uint32_t p, uint32_t group, uint32_t kind,
+                           uint32_t target_tiles, TiledWeights &out)
 {
-    (void)pad_symbol;
-    if (!symbols) return EOQ_ERR_NULL_PTR;
     if (N == 0 || K == 0) return EOQ_ERR_INVALID_HEADER;
     if (G < 1 || G > 3 || bits < 1 || bits * G > 12 || p < bits * G || p > 16) return EOQ_ERR_UNSUPPORTED;
     if (K % kColGranule || group == 0 || K % group || group % kColGranule) return EOQ_ERR_UNSUPPORTED;
@@ -172,6 +170,61 @@ eoq_error_t build_tiled(const uint8_t *symbols, uint32_t N, uint32_t K, uint32_t
     out.nrb = nrb; out.nseg = nseg;
     out.seg_start.resize(nseg + 1);
     for (uint32_t s = 0; s <= nseg; s++) out.seg_start[s] = (uint32_t)((uint64_t)s * units / nseg) * kColGranule;
+    out.tiles.resize((size_t)nrb * nseg);
+    for (size_t t = 0; t < out.tiles.size(); t++) {
+        const uint32_t rb = (uint32_t)(t / nseg), seg = (uint32_t)(t % nseg);
+        TileDesc &d = out.tiles[t];
+        d.row0 = rb * rows_per_tile; d.col0 = out.seg_start[seg]; d.ncols = out.seg_start[seg + 1] - d.col0; d.seg = seg; d.off64 = 0; d.len64 = 0;
+    }
+    return EOQ_OK;
+}
+
+// Joint-symbol frequencies and the decode table from the counts of the joint symbols.
+eoq_error_t tiled_table(const std::vector<uint64_t> &count, TiledWeights &out, std::vector<uint32_t> &freq, std::vector<uint32_t> &cum)
+{
+    eoq_error_t rc = normalize_joint(count, out.p, freq);
+    if (rc != EOQ_OK) return rc;
+    cum.assign(out.alphabet + 1, 0);
+    for (uint32_t s = 0; s < out.alphabet; s++) cum[s + 1] = cum[s] + freq[s];
+    const uint32_t M = 1u << out.p, sym_shift = 23 - out.bits * out.G;
+    out.table.assign(M, (1u << 23));   // unreachable slots: freq 1, symbol 0, bias 0
+    for (uint32_t s = 0; s < out.alphabet; s++)
+        for (uint32_t k = 0; k < freq[s]; k++)
+            out.table[cum[s] + k] = (freq[s] << 23) | (s << sym_shift) | k;
+    return EOQ_OK;
+}
+
+// Stream layout from the tiles' byte counts (len64 set): [heads: ntiles x head_bytes][tails][padding].  The first
+// head_bytes of every tile sit at a fixed stride, so a kernel can request them from the tile index alone, without a
+// descriptor fetch in front; the rest of a tile (its tail) is packed behind and found through the descriptor.
+// head_bytes is a whole number of kilobytes no longer than the shortest tile (two at most: enough to cover the
+// descriptor's round trip).  Sets head_bytes and every off64; `total` is the stream's size with its 4096 bytes of padding.
+eoq_error_t tiled_layout(TiledWeights &out, size_t &total)
+{
+    const size_t ntiles = out.tiles.size();
+    size_t shortest = ~(size_t)0;
+    for (size_t t = 0; t < ntiles; t++) shortest = std::min(shortest, (size_t)out.tiles[t].len64 << 6);
+    const uint32_t H = shortest >= 2048 ? 2048u : shortest >= 1024 ? 1024u : 0u;
+    out.head_bytes = H;
+    total = ntiles * (size_t)H;
+    for (size_t t = 0; t < ntiles; t++) {
+        if ((total >> 6) > 0xFFFFFFFFull) return EOQ_ERR_OVERFLOW;
+        out.tiles[t].off64 = (uint32_t)(total >> 6);
+        total += ((size_t)out.tiles[t].len64 << 6) - H;
+    }
+    total += 4096;
+    return EOQ_OK;
+}
+
+eoq_error_t build_tiled(const uint8_t *symbols, uint32_t N, uint32_t K, uint32_t bits, uint32_t G,
+                        uint32_t p, uint32_t group, uint32_t kind, uint32_t target_tiles,
+                        uint8_t pad_symbol, TiledWeights &out)
+{
+    (void)pad_symbol;
+    if (!symbols) return EOQ_ERR_NULL_PTR;
+    eoq_error_t rc = tiled_geometry(N, K, bits, G, p, group, kind, target_tiles, out);
+    if (rc != EOQ_OK) return rc;
+    const uint32_t Npad = out.Npad, nseg = out.nseg;
 
     // joint symbols, [Npad/G][K]
     const size_t njoint = (size_t)(Npad / G) * K;
@@ -202,26 +255,17 @@ eoq_error_t build_tiled(const uint8_t *symbols, uint32_t N, uint32_t K, uint32_t
         });
         for (auto &pc : part) for (uint32_t s = 0; s < out.alphabet; s++) count[s] += pc[s];
     }
-    std::vector<uint32_t> freq;
-    eoq_error_t rc = normalize_joint(count, p, freq);
+    std::vector<uint32_t> freq, cum;
+    rc = tiled_table(count, out, freq, cum);
     if (rc != EOQ_OK) return rc;
-    std::vector<uint32_t> cum(out.alphabet + 1, 0);
-    for (uint32_t s = 0; s < out.alphabet; s++) cum[s + 1] = cum[s] + freq[s];
-
-    const uint32_t M = 1u << p, sym_shift = 23 - bits * G;
-    out.table.assign(M, (1u << 23));   // unreachable slots: freq 1, symbol 0, bias 0
-    for (uint32_t s = 0; s < out.alphabet; s++)
-        for (uint32_t k = 0; k < freq[s]; k++)
-            out.table[cum[s] + k] = (freq[s] << 23) | (s << sym_shift) | k;
 
     // encode every tile: 32 independent lane streams each
-    const size_t ntiles = (size_t)nrb * nseg;
-    out.tiles.resize(ntiles);
+    const size_t ntiles = out.tiles.size();
     std::vector<std::vector<uint8_t>> tile_bytes(ntiles);
     std::vector<uint32_t> tile_drift(ntiles, 0);
     parallel_for(ntiles, [&](size_t t) {
-        const uint32_t rb = (uint32_t)(t / nseg), seg = (uint32_t)(t % nseg);
-        const uint32_t col0 = out.seg_start[seg], ncols = out.seg_start[seg + 1] - col0;
+        const uint32_t rb = (uint32_t)(t / nseg);
+        const uint32_t col0 = out.tiles[t].col0, ncols = out.tiles[t].ncols;
         std::vector<uint16_t> words[32];
         std::vector<uint8_t> took(32 * (size_t)ncols, 0);    // took[l*ncols + c] = lane l reads a word after step c
         uint32_t state[32];
@@ -259,26 +303,15 @@ eoq_error_t build_tiled(const uint8_t *symbols, uint32_t N, uint32_t K, uint32_t
             drift = std::max(drift, hi - lo);
         }
         tile_drift[t] = drift;
-        TileDesc d;
-        d.row0 = rb * rows_per_tile; d.col0 = col0; d.ncols = ncols; d.seg = seg | (drift > kMaxRingDrift ? kTileDirectFlag : 0u); d.off64 = 0; d.len64 = (uint32_t)(tb.size() >> 6);
-        out.tiles[t] = d;
+        if (drift > kMaxRingDrift) out.tiles[t].seg |= kTileDirectFlag;
+        out.tiles[t].len64 = (uint32_t)(tb.size() >> 6);
     });
     for (uint32_t v : tile_drift) out.max_drift = std::max(out.max_drift, v);
-    // Stream layout: [heads: ntiles x head_bytes][tails][padding].  The first head_bytes of every tile sit at a
-    // fixed stride, so a kernel can request them from the tile index alone, without a descriptor fetch in front;
-    // the rest of a tile (its tail) is packed behind and found through the descriptor.  head_bytes is a whole number
-    // of kilobytes no longer than the shortest tile (two at most: enough to cover the descriptor's round trip).
-    size_t shortest = ~(size_t)0;
-    for (size_t t = 0; t < ntiles; t++) shortest = std::min(shortest, tile_bytes[t].size());
-    const uint32_t H = shortest >= 2048 ? 2048u : shortest >= 1024 ? 1024u : 0u;
-    out.head_bytes = H;
-    size_t total = ntiles * (size_t)H;
-    for (size_t t = 0; t < ntiles; t++) {
-        if ((total >> 6) > 0xFFFFFFFFull) return EOQ_ERR_OVERFLOW;
-        out.tiles[t].off64 = (uint32_t)(total >> 6);
-        total += tile_bytes[t].size() - H;
-    }
-    out.stream.assign(total + 4096, 0);
+    size_t total = 0;
+    rc = tiled_layout(out, total);
+    if (rc != EOQ_OK) return rc;
+    const uint32_t H = out.head_bytes;
+    out.stream.assign(total, 0);
     parallel_for(ntiles, [&](size_t t) {
         if (H) std::memcpy(out.stream.data() + t * (size_t)H, tile_bytes[t].data(), H);
         std::memcpy(out.stream.data() + ((size_t)out.tiles[t].off64 << 6), tile_bytes[t].data() + H, tile_bytes[t].size() - H);

@@ -110,20 +110,46 @@ class EOQWeight:
         return out
 
     @classmethod
+    def from_device_symbols(cls, symbols: torch.Tensor, scales_fp16, *, kind: int = _lib.KIND_INT4_ABSMAX, group: int = 128,
+                            symbols_per_step: int = 0, precision_bits: int = 0, target_tiles: int = 0,
+                            centroids: Optional[Sequence[float]] = None) -> "EOQWeight":
+        """symbols: uint8 [N, K] on a CUDA device; counted, encoded into tiles and laid out there (no copy to the host)."""
+        require_cuda(symbols, "EOQWeight.from_device_symbols")
+        sym = symbols.detach().to(torch.uint8).contiguous()
+        sc = scales_fp16.detach().cpu().numpy() if isinstance(scales_fp16, torch.Tensor) else np.asarray(scales_fp16)
+        sc = np.ascontiguousarray(sc.astype(np.float16, copy=False))
+        n, k = sym.shape
+        o, keep = cls._opts(kind, n, k, group, symbols_per_step, precision_bits, target_tiles, centroids)
+        h = C.c_void_p()
+        with torch.cuda.device(sym.device):
+            torch.cuda.current_stream().synchronize()          # the library encodes on the default stream
+            _lib.check(_lib.lib().eoq_b200_weight_from_device_symbols(sym.data_ptr(), sc.ctypes.data, C.byref(o), C.byref(h)),
+                       "eoq_b200_weight_from_device_symbols")
+            return cls(h.value, kind)
+
+    @classmethod
     def from_int4_packed(cls, packed, scales_fp16, in_features: int, *, group: int = 128, **kw) -> "EOQWeight":
         """packed: QuantizedLinear.packed_weight, uint8 [N, K/2], low nibble = even column, value code+7."""
-        pk = packed.detach().cpu().numpy() if isinstance(packed, torch.Tensor) else np.asarray(packed)
-        sym = np.stack([pk & 0x0F, pk >> 4], axis=-1).reshape(pk.shape[0], -1)[:, :in_features]
-        return cls.from_symbols(sym, scales_fp16, kind=_lib.KIND_INT4_ABSMAX, group=group, **kw)
+        return cls.from_packed(packed, scales_fp16, in_features, 4, group=group, **kw)
 
     @classmethod
     def from_packed(cls, packed, scales_fp16, in_features: int, bits: int, *, group: int = 128, **kw) -> "EOQWeight":
         """packed: QuantizedLinear.packed_weight of any width the fused kernels serve (core/quantized_linear.py:49-66):
-        4 bits two per byte, 2 bits four per byte (low bits first), 3 and 8 bits one signed code per byte."""
+        4 bits two per byte, 2 bits four per byte (low bits first), 3 and 8 bits one signed code per byte.  A tensor on
+        a CUDA device is unpacked and encoded there."""
         if bits not in _lib.INT_KINDS:
             raise ValueError(f"no fused layout for {bits}-bit weights")
-        pk = packed.detach().cpu().numpy() if isinstance(packed, torch.Tensor) else np.asarray(packed)
         qmax = (1 << (bits - 1)) - 1
+        if isinstance(packed, torch.Tensor) and packed.is_cuda:
+            pk = packed.detach()
+            if bits == 4:
+                sym = torch.stack([pk & 0x0F, pk >> 4], dim=-1).reshape(pk.shape[0], -1)
+            elif bits == 2:
+                sym = torch.stack([(pk >> s) & 0x03 for s in (0, 2, 4, 6)], dim=-1).reshape(pk.shape[0], -1)
+            else:
+                sym = (pk.view(torch.int8).to(torch.int16) + qmax).to(torch.uint8)
+            return cls.from_device_symbols(sym[:, :in_features], scales_fp16, kind=_lib.INT_KINDS[bits], group=group, **kw)
+        pk = packed.detach().cpu().numpy() if isinstance(packed, torch.Tensor) else np.asarray(packed)
         if bits == 4:
             sym = np.stack([pk & 0x0F, pk >> 4], axis=-1).reshape(pk.shape[0], -1)
         elif bits == 2:

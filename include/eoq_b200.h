@@ -279,6 +279,14 @@ void        eoq_b200_tiles_free(eoq_b200_tiles_t *t);
 eoq_error_t eoq_b200_weight_from_symbols(const uint8_t *symbols, const uint16_t *scales_fp16,
                                          const eoq_b200_weight_opts_t *opts, eoq_b200_weight_t **out);
 
+/* The same from symbols that are already in the current device's memory (one byte
+ * per weight, row-major N x K): counted, encoded into tiles and laid out on the
+ * device, byte-identical to what eoq_b200_tiles_build makes on the host.  Scales
+ * on the host.  eoq_b200_weight_from_symbols and eoq_b200_weight_from_rans take
+ * this route themselves after copying / decoding their input to the device. */
+eoq_error_t eoq_b200_weight_from_device_symbols(const uint8_t *d_symbols, const uint16_t *scales_fp16,
+                                                const eoq_b200_weight_opts_t *opts, eoq_b200_weight_t **out);
+
 /* Upload tiles built by eoq_b200_tiles_build to the current device (may be called
  * repeatedly, e.g. once per GPU that holds a replica).  centroids: polar only. */
 eoq_error_t eoq_b200_weight_from_tiles(const eoq_b200_tiles_t *tiles, const uint16_t *scales_fp16,
