@@ -1389,6 +1389,7 @@ extern "C" eoq_error_t eoq_b200_weight_decode(eoq_b200_weight_t *w, uint8_t *d_s
     a.status = w->status_word();
     a.out_sym = d_sym; a.out_deq = d_dequant; a.N = w->N; a.K = w->K; a.group = w->group; a.p = w->p; a.ntiles = w->ntiles;
     a.packed = packed; a.out_dtype = out_dtype;
+    a.scales_t = w->scales_t.as<uint2>(); a.nseg = w->nseg; a.nrb = w->nrb; a.Npad = w->Npad; a.stage_bytes = w->stage_bytes;
     int e = launch_decode_tiles(a, w->G, w->bits, w->kind, stream);
     if (e != 0) { std::fprintf(stderr, "eoq_b200_weight_decode: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
     return EOQ_OK;

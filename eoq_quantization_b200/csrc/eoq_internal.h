@@ -160,6 +160,10 @@ struct DecodeArgs {
     uint32_t N, K, group, p, ntiles;
     uint32_t head_bytes;
     int packed, out_dtype;
+    // the pair layout's extras (4-bit weights, three codes per step): set, they let the dequantised matrix come from
+    // the two-tiles-per-warp kernel
+    const uint2 *scales_t = nullptr;      // [K / group][Npad / 3] {s0 | s1 << 16, s2}
+    uint32_t nseg = 0, nrb = 0, Npad = 0, stage_bytes = 0;
 };
 
 int  device_sm_count();

@@ -1953,6 +1953,212 @@ __global__ void __launch_bounds__(256) decode_tiles_kernel(const DecodeArgs a)
     }
 }
 
+// ---------------------------------------------------------------------------
+// The dequantised matrix of a 4-bit weight in the pair layout (three codes per step, tiles that fit the staging
+// buffers): the structure of the fused GEMV without the product.  One 16-warp CTA per SM; a warp takes two
+// vertically adjacent tiles, stages them whole (kilobyte chunks on their own mbarriers) and runs their two rANS chains
+// side by side; a code becomes a float with one logic instruction (the field sits in mantissa bits), (code - 7) * scale
+// is one exact subtraction and one multiplication, and a lane's sixteen columns of a row leave as one 32-byte sector.
+// About half the instructions per weight of the one-tile-per-warp kernel above, which is bound by instruction issue.
+// ---------------------------------------------------------------------------
+// One 32-byte store (a whole sector, one request) to a 32-byte aligned address.
+__device__ __forceinline__ void stg_256(void *p, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t a4, uint32_t a5, uint32_t a6, uint32_t a7)
+{
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(a4), "r"(a5), "r"(a6), "r"(a7)
+                 : "memory");
+}
+
+template <int OUT>
+__global__ void __launch_bounds__(512, 1) dequant_pairs_kernel(const DecodeArgs a)
+{
+    constexpr int G = 3, kWarps = 16;
+    constexpr uint32_t kChunk = 1024, kMaxChunks = 8;
+    using F = Fmt<G, 4>;
+    using F0 = Int4Field<F::field_bit(0)>;
+    using F1 = Int4Field<F::field_bit(1)>;
+    using F2 = Int4Field<F::field_bit(2)>;
+    extern __shared__ __align__(128) uint8_t dq_smem[];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t tab_bytes = 4u << a.p;
+    const uint32_t tab_addr = smem_addr(dq_smem), tab_bar = tab_addr + tab_bytes;
+    const uint32_t region = 2u * a.stage_bytes + 128u;
+    const uint32_t stage[2] = {tab_addr + tab_bytes + 128u + warp * region, tab_addr + tab_bytes + 128u + warp * region + a.stage_bytes};
+    const uint32_t bars = stage[0] + 2u * a.stage_bytes;       // [chain][chunk], 8 bytes each
+    if (tid == 0) {
+        mbar_init(tab_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_expect_tx(tab_bar, tab_bytes);
+        for (uint32_t off = 0; off < tab_bytes; off += 16384u)
+            bulk_copy_g2s(tab_addr + off, reinterpret_cast<const uint8_t *>(a.table) + off, min(16384u, tab_bytes - off), tab_bar);
+    }
+    if (lane < 2 * kMaxChunks) {
+        mbar_init(bars + lane * 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const uint32_t nrbp = (a.nrb + 1u) / 2u, npairs = nrbp * a.nseg;
+    const uint32_t mask = (1u << a.p) - 1u, p = a.p;
+    const uint32_t magic0 = F0::magic_reg(), magic1 = F1::magic_reg(), magic2 = F2::magic_reg();
+    uint32_t c64, c1;
+    asm volatile("mov.b32 %0, 64;\n\tmov.b32 %1, 1;" : "=r"(c64), "=r"(c1));
+    const uint32_t head_chunks = a.head_bytes / kChunk, sc_stride = a.Npad / G;
+    constexpr uint32_t kEsz = OUT == EOQ_B200_F32 ? 4u : 2u;
+    mbar_wait_suspended(tab_bar, 0u, a.status);
+
+    uint32_t uses = 0;
+    // pair q goes to CTA q mod grid: every SM gets its share even when there are fewer pairs than warps
+    for (uint32_t q = blockIdx.x + gridDim.x * warp; q < npairs; q += gridDim.x * kWarps, uses++) {
+        const uint32_t parity = uses & 1u;
+        const uint32_t rbp = q / a.nseg, seg = q - rbp * a.nseg;
+        const bool has_b = 2u * rbp + 1u < a.nrb;
+        const uint32_t t0 = 2u * rbp * a.nseg + seg, t1 = has_b ? t0 + a.nseg : t0;
+        // lane k * 8 + j owns chunk j of tile k: descriptor, then the copy (head region or tail)
+        uint2 cols = make_uint2(0u, 0u), dl = make_uint2(0u, 0u);
+        if (lane < 2 * kMaxChunks) {
+            const uint32_t k = lane >> 3, j = lane & 7u, tk = k ? t1 : t0;
+            cols = make_uint2(__ldg(&a.tiles[tk].col0), __ldg(&a.tiles[tk].ncols));      // (the pair starts 4 bytes into a 24-byte record: two loads)
+            dl = ldg_u32x2_pinned(reinterpret_cast<const uint2 *>(&a.tiles[tk].off64));
+            uint32_t bytes = dl.y << 6;
+            if (bytes + 64u > a.stage_bytes) { *a.status = 2u; bytes = a.stage_bytes - 64u; }   // cannot happen with a host-computed stage size
+            const uint32_t bar = bars + lane * 8, off = j * kChunk;
+            if (off < bytes) {
+                const uint32_t n = min(kChunk, bytes - off);
+                mbar_expect_tx(bar, n);
+                const uint8_t *src = j < head_chunks ? a.stream + (size_t)tk * a.head_bytes + off
+                                                     : a.stream + ((size_t)dl.x << 6) + (off - a.head_bytes);
+                bulk_copy_g2s((k ? stage[1] : stage[0]) + off, src, n, bar);
+            } else {
+                mbar_arrive(bar);                       // nothing to copy: complete the phase by hand
+            }
+        }
+        const uint32_t col0 = __shfl_sync(0xffffffffu, cols.x, 0), ncols = __shfl_sync(0xffffffffu, cols.y, 0);
+        const uint32_t len_a = __shfl_sync(0xffffffffu, dl.y, 0) << 6, len_b = __shfl_sync(0xffffffffu, dl.y, 8) << 6;
+        const uint32_t nch[2] = {min(kMaxChunks, (len_a + kChunk - 1) / kChunk), min(kMaxChunks, (len_b + kChunk - 1) / kChunk)};
+        const uint32_t row[2] = {2u * rbp * (32u * G) + lane * G, (2u * rbp + (has_b ? 1u : 0u)) * (32u * G) + lane * G};
+        // transposed scales: one 8-byte word holds the three scales of a lane's rows for one group (zero past row N)
+        const uint2 *sc_ptr[2] = {a.scales_t + row[0] / G, a.scales_t + row[1] / G};
+        uint2 sc_next[2];
+        float sc[2][G];
+#pragma unroll
+        for (int k = 0; k < 2; k++) sc_next[k] = ldg_u32x2_pinned(sc_ptr[k] + (size_t)(col0 / a.group) * sc_stride);
+        PairChain ch[2];
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            mbar_wait_suspended(bars + k * 64, parity, a.status);
+            ch[k].x = lds_u32(stage[k] + lane * 4u);
+            ch[k].addr = stage[k] + 128u + lane * 2u;
+            ch[k].w = lds_u16(ch[k].addr);
+        }
+        const uint32_t cend = col0 + ncols;
+        for (uint32_t c = col0; c < cend; c += 16) {
+            if (c == col0 || c % a.group == 0) {
+                // a new scale group: take the scales requested a group ago, request the next
+#pragma unroll
+                for (int k = 0; k < 2; k++) {
+                    sc[k][0] = half_bits_to_float((uint16_t)sc_next[k].x);
+                    sc[k][1] = half_bits_to_float((uint16_t)(sc_next[k].x >> 16));
+                    sc[k][2] = half_bits_to_float((uint16_t)sc_next[k].y);
+                }
+                const uint32_t g = c / a.group;
+                if ((g + 1) * a.group < cend) {
+#pragma unroll
+                    for (int k = 0; k < 2; k++) sc_next[k] = ldg_u32x2_pinned(sc_ptr[k] + (size_t)(g + 1) * sc_stride);
+                }
+            }
+            uint32_t held[2][G][4];                                  // 16-bit outputs: the first eight columns, packed
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                float v[2][G][8];
+#pragma unroll
+                for (int s = 0; s < 8; s++) {
+                    uint32_t u[2][3];
+                    rans_step_int4<F0::kMask, F1::kMask, F2::kMask>(tab_addr, ch[0].x, mask, p, F::kBiasMask, magic0, magic1, magic2, u[0][0], u[0][1], u[0][2]);
+                    rans_step_int4<F0::kMask, F1::kMask, F2::kMask>(tab_addr, ch[1].x, mask, p, F::kBiasMask, magic0, magic1, magic2, u[1][0], u[1][1], u[1][2]);
+#pragma unroll
+                    for (int k = 0; k < 2; k++) {
+                        v[k][0][s] = (__uint_as_float(u[k][0]) - F0::kOffset) * sc[k][0];
+                        v[k][1][s] = (__uint_as_float(u[k][1]) - F1::kOffset) * sc[k][1];
+                        v[k][2][s] = (__uint_as_float(u[k][2]) - F2::kOffset) * sc[k][2];
+                    }
+                    staged_renorm(ch[0].x, ch[0].w, ch[0].addr, c64, c1);
+                    staged_renorm(ch[1].x, ch[1].w, ch[1].addr, c64, c1);
+                }
+                if (half == 0) {
+                    // After s steps no lane has read past word row s, and chunk j holds rows 16 j - 2 .. 16 j + 13:
+                    // waiting for chunk j eight steps before column 16 j is always early enough.
+                    const uint32_t j = (c - col0) / 16u + 1u;
+                    if (j < nch[0]) mbar_wait_suspended(bars + j * 8, parity, a.status);
+                    if (j < nch[1]) mbar_wait_suspended(bars + 64 + j * 8, parity, a.status);
+                }
+#pragma unroll
+                for (int k = 0; k < 2; k++) {
+                    if (k == 1 && !has_b) continue;
+#pragma unroll
+                    for (int j = 0; j < G; j++) {
+                        const uint32_t r = row[k] + j;
+                        if (OUT == EOQ_B200_F32) {
+                            if (r < a.N)
+                                stg_256(reinterpret_cast<float *>(a.out_deq) + (size_t)r * a.K + c + half * 8,
+                                        __float_as_uint(v[k][j][0]), __float_as_uint(v[k][j][1]), __float_as_uint(v[k][j][2]), __float_as_uint(v[k][j][3]),
+                                        __float_as_uint(v[k][j][4]), __float_as_uint(v[k][j][5]), __float_as_uint(v[k][j][6]), __float_as_uint(v[k][j][7]));
+                        } else {
+                            uint32_t pk[4];
+#pragma unroll
+                            for (int s = 0; s < 4; s++) {
+                                if (OUT == EOQ_B200_F16) {
+                                    const __half2 h = __floats2half2_rn(v[k][j][2 * s], v[k][j][2 * s + 1]);
+                                    pk[s] = *reinterpret_cast<const uint32_t *>(&h);
+                                } else {
+                                    const __nv_bfloat162 h = __floats2bfloat162_rn(v[k][j][2 * s], v[k][j][2 * s + 1]);
+                                    pk[s] = *reinterpret_cast<const uint32_t *>(&h);
+                                }
+                            }
+                            if (half == 0) {
+#pragma unroll
+                                for (int s = 0; s < 4; s++) held[k][j][s] = pk[s];
+                            } else if (r < a.N) {
+                                stg_256(reinterpret_cast<uint8_t *>(a.out_deq) + ((size_t)r * a.K + c) * kEsz,
+                                        held[k][j][0], held[k][j][1], held[k][j][2], held[k][j][3], pk[0], pk[1], pk[2], pk[3]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+}
+
+// Whether the pair form serves this call: the dequantised matrix alone, of a weight laid out for the pair kernel.
+static bool dequant_takes_pairs(const DecodeArgs &a, uint32_t G, uint32_t bits, uint32_t kind)
+{
+    if (!(kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 4 && G == 3) || !a.out_deq || a.out_sym || !a.scales_t || a.stage_bytes == 0) return false;
+    if (a.group % 16u != 0 || a.K % 16u != 0) return false;
+    const size_t smem = ((size_t)4 << a.p) + 128 + (size_t)16 * (2u * a.stage_bytes + 128u);
+    return smem <= 227 * 1024 && (size_t)8 * 1024 >= a.stage_bytes;
+}
+
+static int launch_dequant_pairs(const DecodeArgs &a, cudaStream_t st)
+{
+    const size_t smem = ((size_t)4 << a.p) + 128 + (size_t)16 * (2u * a.stage_bytes + 128u);
+    const uint32_t npairs = ((a.nrb + 1u) / 2u) * a.nseg;
+    const uint32_t grid = max(1u, min((uint32_t)device_sm_count(), npairs));
+    cudaError_t e = cudaSuccess;
+#define EOQ_LAUNCH_DQ(O)                                                                                          \
+    do {                                                                                                          \
+        e = cudaFuncSetAttribute(dequant_pairs_kernel<O>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e == cudaSuccess) dequant_pairs_kernel<O><<<grid, 512, smem, st>>>(a);                                \
+    } while (0)
+    if (a.out_dtype == EOQ_B200_F16) EOQ_LAUNCH_DQ(EOQ_B200_F16);
+    else if (a.out_dtype == EOQ_B200_BF16) EOQ_LAUNCH_DQ(EOQ_B200_BF16);
+    else EOQ_LAUNCH_DQ(EOQ_B200_F32);
+#undef EOQ_LAUNCH_DQ
+    if (e != cudaSuccess) return (int)e;
+    g_launches++;
+    return (int)cudaGetLastError();
+}
+
 template <int G, int BITS, int KIND>
 static int launch_decode_tiles_t(const DecodeArgs &a, cudaStream_t st)
 {
@@ -1973,6 +2179,7 @@ static int launch_decode_tiles_t(const DecodeArgs &a, cudaStream_t st)
 int launch_decode_tiles(const DecodeArgs &a, uint32_t G, uint32_t bits, uint32_t kind, void *stream)
 {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (dequant_takes_pairs(a, G, bits, kind)) return launch_dequant_pairs(a, st);
     if (kind == EOQ_B200_KIND_INT4_ABSMAX && bits == 4) {
         if (G == 1) return launch_decode_tiles_t<1, 4, EOQ_B200_KIND_INT4_ABSMAX>(a, st);
         if (G == 2) return launch_decode_tiles_t<2, 4, EOQ_B200_KIND_INT4_ABSMAX>(a, st);

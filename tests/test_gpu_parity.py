@@ -564,3 +564,22 @@ def test_host_buffer_gemv_async_two_weights_one_sync():
     for w, x, y, packed, s16, n, k in cases:
         ref = O.int4_linear(packed, s16.astype(np.float32), n, k, 128, x.float().numpy())
         assert O.rel_l2(y.float().numpy(), ref) < TOL
+
+
+@pytest.mark.parametrize("n,k", [(96, 256), (500, 1536), (1000, 11008), (4096, 4096), (193, 4096)])
+def test_dequantised_matrix_in_every_dtype_is_the_reference_product(n, k):
+    """``EOQWeight.dequantize`` (the two-tiles-per-warp kernel for the default 4-bit layout; odd numbers of row blocks,
+    ragged last rows, 96- and 112-column tiles): fp32 equals code * scale bit for bit (core/utils.py:130-161), and the
+    16-bit outputs are that product rounded once."""
+    rng = np.random.default_rng(n + k)
+    wt = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    codes, scales = O.quantize_absmax(wt, 4, 128)
+    s16 = scales.astype(np.float16)
+    w = EOQWeight.from_symbols((codes + 7).astype(np.uint8), s16)
+    dense = (codes.reshape(-1, 128).astype(np.float32) * s16.astype(np.float32)[:, None]).reshape(n, k)
+    got = w.dequantize(torch.float32)
+    assert np.array_equal(got.cpu().numpy(), dense)
+    ref = torch.from_numpy(dense)
+    assert torch.equal(w.dequantize(torch.float16).cpu(), ref.half())
+    assert torch.equal(w.dequantize(torch.bfloat16).cpu(), ref.bfloat16())
+    assert w.status() == 0
