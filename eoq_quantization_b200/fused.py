@@ -29,11 +29,12 @@ def require_cuda(t: torch.Tensor, what: str) -> None:
                            "(there is no CPU path)")
 
 
-# Rows up to which the fused tensor-core path is used.  Every 96-row block of the weight re-reads all of X from L2
-# while it is decoded (the accumulators of 96 rows x 512 tokens fill tensor memory), so beyond this many rows one
-# decode to fp16 plus a library GEMM, whose tiles share X across 256 rows and more, is faster: measured cross-over
-# between 128 and 256 rows on 3584 x 8192 and 1024 x 28672.
-GEMM_MAX_ROWS = 128
+# Rows up to which `linear` and the reference-API modules use a fused kernel.  Up to 8 rows that is the fused decode +
+# GEMV.  Beyond, the weight is decoded once to a 16-bit matrix (1.0 T symbols/s, the matrix stays in the 126 MB L2) for a
+# library GEMM: measured faster than the fused decode + tensor-core kernel (`EOQWeight.gemm`, still there to be called)
+# at every row count, 34 against 39 us at 16 rows and 37 against 92 us at 256 rows on 3584 x 8192, because that
+# kernel decodes one tile per warp through a word ring, at about half the rate of the two-tiles-per-warp decoders.
+GEMM_MAX_ROWS = 8
 
 
 class EOQWeight:
@@ -226,8 +227,9 @@ class EOQWeight:
 
     def linear(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         """y = x @ W.T (+ bias) in x.dtype by the fastest route built for the number of rows: up to 8 the fused
-        decode + GEMV; up to GEMM_MAX_ROWS of 16-bit activations on 4-bit weights the fused decode + tensor-core MMA;
-        beyond, the weight is decoded to a dense matrix once (fused decode + dequantise kernel) for a library GEMM."""
+        decode + GEMV; beyond GEMM_MAX_ROWS the weight is decoded to a dense matrix once (fused decode + dequantise
+        kernel) for a library GEMM.  (Between the two, were GEMM_MAX_ROWS raised above 8, 16-bit activations on 4-bit
+        weights would take the fused decode + tensor-core kernel, `gemm`.)"""
         require_cuda(x, "EOQWeight.linear")
         rows = x.numel() // max(self.cols, 1)
         if rows >= 1 and x.dtype in _DTYPES:
