@@ -12,7 +12,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..fused import GEMM_MAX_ROWS, EOQWeight, dequant_packed, require_cuda
+from ..fused import GEMM_MAX_ROWS, EOQWeight, dequant_packed, fused_rows, require_cuda
 
 
 class QuantizedLinear(nn.Module):
@@ -130,13 +130,13 @@ class QuantizedLinear(nn.Module):
         require_cuda(x, "QuantizedLinear.forward")
         require_cuda(self.packed_weight, "QuantizedLinear.forward")
         rows = x.numel() // max(self.in_features, 1)
-        if self._fusable() and 1 <= rows <= GEMM_MAX_ROWS and x.dtype in (torch.float16, torch.bfloat16, torch.float32):
-            # up to 8 rows: fused decode + GEMV (fp32 accumulate, any of the three dtypes); up to GEMM_MAX_ROWS of
-            # 16-bit activations: fused decode + tensor-core MMA (operands fp16); beyond that, and for fp32
-            # activations, one dequantisation amortises over enough rows for a library GEMM to win
-            if rows <= 8:
+        if self._fusable() and rows >= 1 and x.dtype in (torch.float16, torch.bfloat16, torch.float32):
+            # up to fused_rows (4 rows of 16-bit activations, 8 of fp32): fused decode + GEMV, fp32 accumulate; beyond
+            # that one dequantisation amortises over enough rows for a library GEMM to win (the fused tensor-core
+            # kernel would take 9..GEMM_MAX_ROWS rows of 16-bit activations if that constant were raised)
+            if rows <= fused_rows(x.dtype):
                 return self.eoq_weight().gemv(x, self.bias_param)
-            if x.dtype != torch.float32 and self.bits == 4:          # the tensor-core kernel is built for the 4-bit layout
+            if 8 < rows <= GEMM_MAX_ROWS and x.dtype != torch.float32 and self.bits == 4:          # the tensor-core kernel is built for the 4-bit layout
                 return self.eoq_weight().gemm(x, self.bias_param)
         weight = dequant_packed(self.packed_weight, self.scales, self.out_features, self.in_features, self.bits,
                                 self.block_size, dtype=x.dtype if x.dtype in (torch.float16, torch.bfloat16) else torch.float32)

@@ -10,7 +10,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..fused import GEMM_MAX_ROWS, EOQWeight, dequant_packed, require_cuda
+from ..fused import GEMM_MAX_ROWS, EOQWeight, dequant_packed, fused_rows, require_cuda
 
 _SUPPORTED_BITS = (2, 4, 8)
 _MEMORY_THRESHOLD = 16 * 1024 * 1024
@@ -134,13 +134,13 @@ class QuantizedLinearFast(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         require_cuda(x, "QuantizedLinearFast.forward")
         rows = x.numel() // max(self.in_features, 1)
-        if self.strategy == "auto" and self._fusable() and 1 <= rows <= GEMM_MAX_ROWS and x.dtype in (torch.float16, torch.bfloat16, torch.float32):
-            # up to 8 rows: fused decode + GEMV (fp32 accumulate, any of the three dtypes); up to GEMM_MAX_ROWS of
-            # 16-bit activations: fused decode + tensor-core MMA (operands fp16); beyond that, and for fp32
-            # activations, one dequantisation amortises over enough rows for a library GEMM to win
-            if rows <= 8:
+        if self.strategy == "auto" and self._fusable() and rows >= 1 and x.dtype in (torch.float16, torch.bfloat16, torch.float32):
+            # up to fused_rows (4 rows of 16-bit activations, 8 of fp32): fused decode + GEMV, fp32 accumulate; beyond
+            # that one dequantisation amortises over enough rows for a library GEMM to win (the fused tensor-core
+            # kernel would take 9..GEMM_MAX_ROWS rows of 16-bit activations if that constant were raised)
+            if rows <= fused_rows(x.dtype):
                 return self.eoq_weight().gemv(x, self.bias_param)
-            if x.dtype != torch.float32:
+            if 8 < rows <= GEMM_MAX_ROWS and x.dtype != torch.float32:
                 return self.eoq_weight().gemm(x, self.bias_param)
         out = quantized_matmul(x, self.packed_weight, self.scales, self.out_features, self.in_features, bits=self.bits,
                                block_size=self.block_size, strategy=self.strategy, chunk_rows=self.chunk_rows)

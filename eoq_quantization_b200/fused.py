@@ -29,12 +29,20 @@ def require_cuda(t: torch.Tensor, what: str) -> None:
                            "(there is no CPU path)")
 
 
-# Rows up to which `linear` and the reference-API modules use a fused kernel.  Up to 8 rows that is the fused decode +
-# GEMV.  Beyond, the weight is decoded once to a 16-bit matrix (1.0 T symbols/s, the matrix stays in the 126 MB L2) for a
-# library GEMM: measured faster than the fused decode + tensor-core kernel (`EOQWeight.gemm`, still there to be called)
-# at every row count, 34 against 39 us at 16 rows and 37 against 92 us at 256 rows on 3584 x 8192, because that
-# kernel decodes one tile per warp through a word ring, at about half the rate of the two-tiles-per-warp decoders.
-GEMM_MAX_ROWS = 8
+# Rows up to which `linear` and the reference-API modules use the fused decode + GEMV: four rows of 16-bit activations
+# (one launch), eight of fp32 activations.  Beyond, the weight is decoded once to a dense matrix (1.0 T symbols/s; a
+# 16-bit matrix stays in the 126 MB L2) for a library GEMM.  Measured, graph replay, fp16: 11008 x 4096 at 4 / 5 / 8 rows
+# 33.9 / 51.8 / 63.8 us fused (a second launch from the fifth row on) against 47.4 / 47.5 / 47.7 us decode + GEMM;
+# 4096 x 4096: 28.7 / 42.8 / 52.8 against 26.8; at 16 rows and more the fused decode + tensor-core kernel
+# (`EOQWeight.gemm`, still there to be called) loses as well, 39 against 34 us at 16 rows and 92 against 37 us at 256
+# rows on 3584 x 8192: it decodes one tile per warp through a word ring, at half the rate of the two-tiles-per-warp decoders.
+GEMV_MAX_ROWS = {torch.float16: 4, torch.bfloat16: 4, torch.float32: 8}
+GEMM_MAX_ROWS = 8       # rows up to which the tensor-core kernel would be preferred to decode + library GEMM: none above the GEMV's
+
+
+def fused_rows(dtype: torch.dtype) -> int:
+    """Activation rows up to which the fused decode + GEMV is the fastest route for this activation type."""
+    return GEMV_MAX_ROWS.get(dtype, 0)
 
 
 class EOQWeight:
@@ -226,16 +234,16 @@ class EOQWeight:
         return y.reshape(*x.shape[:-1], self.rows)
 
     def linear(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """y = x @ W.T (+ bias) in x.dtype by the fastest route built for the number of rows: up to 8 the fused
-        decode + GEMV; beyond GEMM_MAX_ROWS the weight is decoded to a dense matrix once (fused decode + dequantise
-        kernel) for a library GEMM.  (Between the two, were GEMM_MAX_ROWS raised above 8, 16-bit activations on 4-bit
-        weights would take the fused decode + tensor-core kernel, `gemm`.)"""
+        """y = x @ W.T (+ bias) in x.dtype by the fastest route built for the number of rows: up to `fused_rows` the
+        fused decode + GEMV; beyond, the weight is decoded to a dense matrix once (fused decode + dequantise kernel)
+        for a library GEMM.  (Were GEMM_MAX_ROWS raised above 8, 16-bit activations on 4-bit weights would take the
+        fused decode + tensor-core kernel, `gemm`, up to that many rows.)"""
         require_cuda(x, "EOQWeight.linear")
         rows = x.numel() // max(self.cols, 1)
         if rows >= 1 and x.dtype in _DTYPES:
-            if rows <= 8:
+            if rows <= fused_rows(x.dtype):
                 return self.gemv(x, bias)
-            if rows <= GEMM_MAX_ROWS and x.dtype != torch.float32 and self.kind == _lib.KIND_INT4_ABSMAX and self.cols % 16 == 0:
+            if 8 < rows <= GEMM_MAX_ROWS and x.dtype != torch.float32 and self.kind == _lib.KIND_INT4_ABSMAX and self.cols % 16 == 0:
                 return self.gemm(x, bias)
         dt = x.dtype if x.dtype in (torch.float16, torch.bfloat16) else torch.float32
         with self._on_device(x, "EOQWeight.linear"):
