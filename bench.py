@@ -16,7 +16,13 @@ value   = algorithmic bytes per step / device time per step (CUDA events, max ov
 e2e     = the same metric through the C ABI with HOST buffers (eoq_b200_gemv_host): x copied in
           from pinned memory and y copied out inside the timed region, every step.
 N > 1   : each layer is sharded by output rows over the ranks (strong scaling); a step is the
-          two local products plus the NCCL all-gather of the output slices.
+          two local products plus the gather of the output slices, fused into the GEMV kernels
+          (peer stores over NVLink; --gather nccl: an NCCL all-gather per layer instead).
+extras  : unless --no-extras, the line also carries `llama7b_step` (a Llama-7B-shape decode step,
+          row-sharded like the headline) and `prefill_tp` (the Llama-70B gate/up projection at
+          M = 16 ... 2048 tokens, row-sharded, with the all-gather of the output slices).
+--workload wire_decode | decode_dequant | polar_q5 | llama7b_step | prefill_gemm | model_load :
+          the other configurations, one JSON line each (single GPU).
 --impl reference : the reference's CPU path for the same step -- eoq_parallel_decode
           (compiled from the reference's C sources when available, else the C restatement)
           followed by torch dequantise + F.linear -- on the host cores.
