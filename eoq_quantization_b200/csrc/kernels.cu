@@ -1720,6 +1720,7 @@ static int launch_gemv_pairs(const GemvArgs &a, cudaStream_t st)
     constexpr int THREADS = 512;
     auto kern = gemv_pairs_kernel<G, BT, THREADS, XH>;
     if (a.stage_bytes == 0 || a.stage_bytes > 8192u || a.max_ncols == 0 || a.nrb == 0 || !a.scales_t) return -1;   // eight 1 KB chunks per tile
+    if (a.stage_bytes < 2u * G * BT * 128u) return -1;      // a tile buffer also holds the warp's sums after the loop: [2][G][BT][32] floats
     const size_t smem = pair_smem_bytes(a.p, BT, a.stage_bytes, a.max_ncols, THREADS / 32, XH ? 2 : 4);
     if (smem > 227 * 1024) return -1;
     int dev = 0;

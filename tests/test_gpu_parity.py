@@ -583,3 +583,23 @@ def test_dequantised_matrix_in_every_dtype_is_the_reference_product(n, k):
     assert torch.equal(w.dequantize(torch.float16).cpu(), ref.half())
     assert torch.equal(w.dequantize(torch.bfloat16).cpu(), ref.bfloat16())
     assert w.status() == 0
+
+
+@pytest.mark.parametrize("rows", [1, 2, 4, 8])
+def test_fused_gemv_on_short_tiles_of_wide_short_matrices(rows):
+    """Low-entropy codes make tiles much shorter than the buffers' later use (the warp's sums, its share of a cooperative
+    meeting: 3 KB at four activation rows), and a matrix much wider than tall takes the cooperative meeting: the buffers
+    have a floor that covers both.  Checked against the oracle's dequantise-then-matmul."""
+    rng = np.random.default_rng(rows)
+    n, k = 150, 8192
+    codes = np.where(rng.random((n, k)) < 0.9, 0, rng.integers(-7, 8, (n, k))).astype(np.int64)       # nine codes in ten are zero
+    scales = (rng.random(n * k // 128) * 0.01 + 0.001).astype(np.float16)
+    w = EOQWeight.from_symbols((codes + 7).astype(np.uint8), scales)
+    assert w.info.bits_per_weight < 2.0
+    dense = (codes.reshape(-1, 128).astype(np.float32) * scales.astype(np.float32)[:, None]).reshape(n, k).astype(np.float64)
+    for dt in (torch.float16, torch.float32):
+        x = torch.from_numpy(rng.standard_normal((rows, k)).astype(np.float32)).cuda().to(dt)
+        y = w.gemv(x, out_dtype=torch.float32).cpu().numpy()
+        assert O.rel_l2(y, x.float().cpu().numpy().astype(np.float64) @ dense.T) < 1e-3
+        assert np.array_equal(y, w.gemv(x, out_dtype=torch.float32).cpu().numpy())              # and the same bits again
+    assert w.status() == 0

@@ -164,16 +164,22 @@ def test_default_int4_layout_keeps_tiles_short_enough_to_stage_two_per_warp():
     the default layout of an INT4 weight (three symbols per step) must respect that for wide matrices too, and still
     decode back to the symbols it was built from."""
     rng = np.random.default_rng(5)
-    codes, _ = O.quantize_absmax((rng.standard_normal((1152, 4096)) * 0.02).astype(np.float32), 4, 128)
+    n = 4608
+    codes, _ = O.quantize_absmax((rng.standard_normal((n, 4096)) * 0.02).astype(np.float32), 4, 128)
     sym = (codes + 7).astype(np.uint8)
     rc, t = _tiles(sym, L.KIND_INT4_ABSMAX, 128)
     assert rc == 0 and t["G"] == 3
     desc = t["desc"].reshape(-1, 6)
-    assert desc[:, 2].max() <= 112 and (desc[:, 2] % 16 == 0).all()
+    assert desc[:, 2].max() <= 112 and desc[:, 2].min() >= 64 and (desc[:, 2] % 16 == 0).all()
     assert (desc[:, 5].astype(np.int64) * 64).max() + 64 <= 8192          # eight one-kilobyte chunks per tile
-    assert np.array_equal(O.decode_tiles(t["table"], t["p"], t["G"], t["bits"], t["desc"], t["stream"], 1152, 4096, t["head"]), sym)
+    assert np.array_equal(O.decode_tiles(t["table"], t["p"], t["G"], t["bits"], t["desc"], t["stream"], n, 4096, t["head"]), sym)
     # every tile of this layout is longer than two kilobytes, so two kilobytes of each sit at the fixed stride
     assert t["head"] == 2048 and (desc[:, 4].astype(np.int64) * 64 >= t["ntiles"] * 2048).all()
+    # a matrix so small that tile pairs of 32 columns still fit one wave of warps gets those (one kilobyte at the stride)
+    rc, t = _tiles(sym[:1152], L.KIND_INT4_ABSMAX, 128)
+    desc = t["desc"].reshape(-1, 6)
+    assert rc == 0 and (desc[:, 2] == 32).all() and t["head"] == 1024 and t["ntiles"] == 12 * 128
+    assert np.array_equal(O.decode_tiles(t["table"], t["p"], t["G"], t["bits"], t["desc"], t["stream"], 1152, 4096, t["head"]), sym[:1152])
 
 
 @pytest.mark.parametrize("n,k,g", [(24, 256, 3), (100, 512, 2), (33, 128, 1), (97, 384, 3), (1, 128, 3), (96, 128, 3)])
