@@ -595,7 +595,7 @@ def test_fused_gemv_on_short_tiles_of_wide_short_matrices(rows):
     codes = np.where(rng.random((n, k)) < 0.9, 0, rng.integers(-7, 8, (n, k))).astype(np.int64)       # nine codes in ten are zero
     scales = (rng.random(n * k // 128) * 0.01 + 0.001).astype(np.float16)
     w = EOQWeight.from_symbols((codes + 7).astype(np.uint8), scales)
-    assert w.info.bits_per_weight < 2.0
+    assert w.info.bits_per_weight < 3.0              # tiles of about a kilobyte
     dense = (codes.reshape(-1, 128).astype(np.float32) * scales.astype(np.float32)[:, None]).reshape(n, k).astype(np.float64)
     for dt in (torch.float16, torch.float32):
         x = torch.from_numpy(rng.standard_normal((rows, k)).astype(np.float32)).cuda().to(dt)
