@@ -668,16 +668,34 @@ extern "C" eoq_error_t eoq_b200_encode_blocked(const uint32_t *freq, uint32_t al
     if (sum != (1ull << precision_bits)) return EOQ_ERR_INVALID_HEADER;
     for (uint32_t i = 0; i < num_symbols; i++) if (symbols[i] >= alphabet) return EOQ_ERR_CORRUPT_STREAM;
     const uint32_t nb = (uint32_t)(((uint64_t)num_symbols + block_size - 1) / block_size);
+    // blocks are independent streams: ranges of blocks are encoded on the host's cores (one range, on the calling thread,
+    // for small inputs), then laid out back to back in block order
+    const size_t nranges = num_symbols < (1u << 18) ? 1 : std::min<size_t>(nb, 256);
+    std::vector<std::vector<uint8_t>> bytes(nranges);
+    std::vector<uint32_t> sizes(nb);
+    auto encode_range = [&](size_t r) {
+        const uint32_t lo = (uint32_t)((uint64_t)nb * r / nranges), hi = (uint32_t)((uint64_t)nb * (r + 1) / nranges);
+        std::vector<uint8_t> blk;
+        for (uint32_t b = lo; b < hi; b++) {
+            const uint32_t first = b * block_size, n = std::min(block_size, num_symbols - first);
+            encode_block_v1(freq, cdf.data(), precision_bits, symbols + first, n, blk);
+            sizes[b] = (uint32_t)blk.size();
+            bytes[r].insert(bytes[r].end(), blk.begin(), blk.end());
+        }
+    };
+    if (nranges == 1) encode_range(0); else parallel_for(nranges, encode_range);
     size_t at = 0;
-    std::vector<uint8_t> blk;
-    for (uint32_t b = 0; b < nb; b++) {
-        const uint32_t first = b * block_size, n = std::min(block_size, num_symbols - first);
-        encode_block_v1(freq, cdf.data(), precision_bits, symbols + first, n, blk);
-        if (at + blk.size() > *out_len) return EOQ_ERR_BUFFER_TOO_SMALL;
-        if (at > 0xFFFFFFFFull) return EOQ_ERR_OVERFLOW;
-        offsets[b] = (uint32_t)at;
-        std::memcpy(out + at, blk.data(), blk.size());
-        at += blk.size();
+    for (size_t r = 0; r < nranges; r++) {
+        const uint32_t lo = (uint32_t)((uint64_t)nb * r / nranges), hi = (uint32_t)((uint64_t)nb * (r + 1) / nranges);
+        if (at + bytes[r].size() > *out_len) return EOQ_ERR_BUFFER_TOO_SMALL;
+        size_t off = at;
+        for (uint32_t b = lo; b < hi; b++) {
+            if (off > 0xFFFFFFFFull) return EOQ_ERR_OVERFLOW;
+            offsets[b] = (uint32_t)off;
+            off += sizes[b];
+        }
+        if (!bytes[r].empty()) std::memcpy(out + at, bytes[r].data(), bytes[r].size());
+        at += bytes[r].size();
     }
     *out_len = at;
     return EOQ_OK;

@@ -4,6 +4,7 @@
 #include <cstddef>
 #include <cstdint>
 #include <string>
+#include <functional>
 #include <vector>
 
 #include <vector_types.h>
@@ -87,6 +88,9 @@ eoq_error_t normalize_reference(const uint32_t *raw, uint32_t alphabet, uint32_t
 // Wire-format ("v1") block encoder, byte-identical to core/rans.py:210-276.
 void encode_block_v1(const uint32_t *freq, const uint32_t *cdf, uint32_t p,
                      const uint32_t *syms, uint32_t n, std::vector<uint8_t> &out);
+
+// fn(0) ... fn(n - 1) on the host's cores (at most 64 threads, joined before it returns).
+void parallel_for(size_t n, const std::function<void(size_t)> &fn);
 
 // The pieces of build_tiled that do not touch the symbols, shared with the device-side tile encoder: geometry
 // (padded rows, row blocks, column segments, tile descriptors without sizes), joint-symbol frequencies and decode table

@@ -135,7 +135,7 @@ static eoq_error_t normalize_joint(const std::vector<uint64_t> &count, uint32_t 
     return EOQ_OK;
 }
 
-static void parallel_for(size_t n, const std::function<void(size_t)> &fn)
+void parallel_for(size_t n, const std::function<void(size_t)> &fn)
 {
     unsigned hw = std::thread::hardware_concurrency();
     size_t nt = std::min<size_t>(hw ? hw : 4, std::max<size_t>(n, 1));
