@@ -522,7 +522,7 @@ def run_gpu_arm(args):
 
 # --------------------------------------------------------------------------- secondary workloads
 def run_aux(args):
-    """Single-GPU timings of the other BASELINE configurations (one JSON line each):
+    """Single-GPU timings of the other benchmark configurations (one JSON line each):
     decode_dequant -- 4096 x 4096 INT4 g128: decode the tiles to packed INT4 and to the fp16 dequantised matrix;
     polar_q5       -- 14336 x 4096 PolarQuant Q5 (per-64 norms), fused decode+GEMV at batch 1, 4, 8."""
     import torch
@@ -620,7 +620,7 @@ def run_aux(args):
 
 
 def run_llama_step(args):
-    """Llama-7B-shape decode step, random init (BASELINE config 4): 32 layers, hidden 4096, 32 heads, SwiGLU 11008,
+    """Llama-7B-shape decode step, random init (configuration 4 of the benchmark set): 32 layers, hidden 4096, 32 heads, SwiGLU 11008,
     vocabulary 32000, KV length 1024, batch 1.  Every linear is INT4 g128 entropy-coded and runs through the fused
     kernel; norms, rotary embedding, attention (torch SDPA) and the activation are torch ops.  All 32 layers hold
     their own copy of the tiles in HBM (one set of values, 32 uploads), so every byte of weight is read from DRAM.
@@ -961,7 +961,7 @@ def run_prefill_gemm(args, torch, _lib, lib, EOQWeight):
 
 def run_wire_decode(args):
     """Decode of the reference's wire format (independent rANS blocks, byte renormalisation), one JSON line per case:
-    config 1 as BASELINE words it (4096 x 4096 INT4 symbols, blocks of 4096, 12-bit table), the .eoq default (blocks of
+    configuration 1 of the benchmark set (4096 x 4096 INT4 symbols, blocks of 4096, 12-bit table), the .eoq default (blocks of
     256, 14-bit table) and an EOQ-GGUF-style payload (byte alphabet, 16-bit table, blocks of 256).
     value  = symbols per second of the decode kernel on device-resident inputs (eoq_cuda_decode_tensor_device),
              eight copies of the tensor cycled so that streams and outputs come from DRAM;

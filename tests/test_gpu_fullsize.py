@@ -1,4 +1,4 @@
-"""The BASELINE configurations at full size, checked against what the imported reference made of the same seeded
+"""The benchmark configurations at full size, checked against what the imported reference made of the same seeded
 inputs (tests/golden/ref_fullsize.npz, written by tests/golden/make_golden.py; tests/golden/recipes.py regenerates
 the inputs).  Hashes pin the quantised inputs to the reference's quantisers bit for bit; outputs are compared with
 the reference's dequantise-then-linear results: decoded symbols and dequantised matrices bit-exact, products within
