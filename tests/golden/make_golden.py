@@ -218,7 +218,7 @@ def eoq_container():
 
 
 def fullsize():
-    """The BASELINE shapes at full size.  The matrices are too large to commit, so the fixture holds what pins them:
+    """The benchmark shapes at full size.  The matrices are too large to commit, so the fixture holds what pins them:
     hashes of what the reference's quantisers make of the seeded weights (recipes.py regenerates the weights), the
     hash and length of the reference-encoded config-1 container, and the reference's own dequantise-then-linear
     outputs (whole vectors for the GEMV shapes, 32 evenly spaced output columns for the prefill shapes)."""

@@ -1,4 +1,4 @@
-"""Seeded synthetic inputs of the BASELINE configurations, shared by the fixture generator (which feeds them to the
+"""Seeded synthetic inputs of the benchmark configurations, shared by the fixture generator (which feeds them to the
 imported reference) and by the tests (which feed them to the library and compare with what the reference made of
 them).  CPU generators only, so both sides see the same numbers wherever they run."""
 from __future__ import annotations
@@ -8,7 +8,7 @@ import hashlib
 import numpy as np
 import torch
 
-#: name -> (rows, cols, seed, sigma); INT4 symmetric absmax, group 128, as BASELINE words configs 1, 2 and 5
+#: name -> (rows, cols, seed, sigma); INT4 symmetric absmax, group 128, as the benchmark set words configurations 1, 2 and 5
 INT4_SHAPES = {
     "square_4096x4096": (4096, 4096, 101, 0.02),          # config 1
     "up_11008x4096": (11008, 4096, 102, 0.02),            # config 2

@@ -402,7 +402,7 @@ def test_polar_q5_gemv_matches_reference_dequant():
 
 # ---------------------------------------------------------------- full-size properties
 def test_full_size_gate_projection_round_trip_and_gemv():
-    """BASELINE shape 11008 x 4096: decode == original symbols (bit-exact, 45 M symbols) and the fused
+    """Headline shape 11008 x 4096: decode == original symbols (bit-exact, 45 M symbols) and the fused
     GEMV agrees with dequantise-then-matmul computed by torch on the same device."""
     n, k = 11008, 4096
     g = torch.Generator(device="cuda").manual_seed(0)
@@ -494,7 +494,7 @@ def test_fused_gemv_over_several_waves_of_tile_pairs(n, k, batch):
 
 
 def test_full_size_polar_q5_gemv_batches():
-    """BASELINE shape 14336 x 4096, N(0, 0.015) with 0.1 % outliers at 8 sigma, PolarQuant Q5 with
+    """Benchmark shape 14336 x 4096, N(0, 0.015) with 0.1 % outliers at 8 sigma, PolarQuant Q5 with
     per-64 norms (core/polar_quant.py:138-264 restated in torch on the GPU as the checker): symbols
     round-trip bit-exactly and the fused GEMV matches the reference's fp16 dequantised weight."""
     z = _z("ref_polar")
