@@ -21,7 +21,7 @@ N > 1   : each layer is sharded by output rows over the ranks (strong scaling); 
 extras  : unless --no-extras, the line also carries `llama7b_step` (a Llama-7B-shape decode step,
           row-sharded like the headline) and `prefill_tp` (the Llama-70B gate/up projection at
           M = 16 ... 2048 tokens, row-sharded, with the all-gather of the output slices).
---workload wire_decode | decode_dequant | polar_q5 | llama7b_step | prefill_gemm | model_load :
+--workload wire_decode | decode_dequant | polar_q5 | llama7b_step | prefill_gemm | model_load | packed_gemv :
           the other configurations, one JSON line each (single GPU).
 --impl reference : the reference's CPU path for the same step -- eoq_parallel_decode
           (compiled from the reference's C sources when available, else the C restatement)
@@ -575,6 +575,94 @@ def run_aux(args):
 
     if args.workload == "prefill_gemm":
         return run_prefill_gemm(args, torch, _lib, lib, EOQWeight)
+
+    if args.workload == "packed_gemv":
+        # QuantizedLinear's forward for up to 32 rows of fp16 activations: one pass over the packed codes the module keeps
+        # in HBM (no entropy coding) with warp-level tensor-core products, beside the entropy-coded fused GEMV and a dense fp16 GEMV of the same layers; graph replay over 8
+        # copies of each layer (> L2), both layers of the MLP pair per step
+        from eoq_quantization_b200.fused import gemv_packed
+        shapes = [(11008, 4096), (4096, 11008)]
+        res = {}
+        copies = 8
+        for bits in (4, 8, 2):
+            layers = []
+            for li, (n, k) in enumerate(shapes):
+                g = torch.Generator().manual_seed(10 + li)
+                w = torch.randn(n, k, generator=g) * 0.02
+                qmax = (1 << (bits - 1)) - 1
+                blocks = w.view(-1, GROUP)
+                scale = (blocks.abs().amax(dim=1) / qmax).clamp(min=1e-10)
+                codes = (blocks / scale[:, None]).round().clamp(-qmax, qmax).to(torch.int16).view(n, k)
+                if bits == 4:
+                    u = (codes + qmax).to(torch.uint8); pk = u[:, 0::2] | (u[:, 1::2] << 4)
+                elif bits == 2:
+                    u = (codes + qmax).to(torch.uint8); pk = u[:, 0::4] | (u[:, 1::4] << 2) | (u[:, 2::4] << 4) | (u[:, 3::4] << 6)
+                else:
+                    pk = codes.to(torch.int8).view(torch.uint8)
+                dense = (codes.float().view(-1, GROUP) * scale.half().float()[:, None]).view(n, k)
+                layers.append((n, k, [pk.contiguous().cuda().clone() for _ in range(copies)], scale.half().cuda(), dense))
+            per_b = {}
+            for batch in (1, 4, 8, 16, 32):
+                xs = [torch.randn(batch, k, device="cuda").half() for (_, k) in shapes]
+                y = gemv_packed(layers[0][2][0], layers[0][3], shapes[0][0], shapes[0][1], bits, GROUP, xs[0], out_dtype=torch.float32)
+                want = xs[0].float().cpu().double() @ layers[0][4].double().T
+                err = float((y.cpu().double() - want).norm() / want.norm())
+                assert err < 1e-4, f"packed GEMV check failed: {err}"
+                i = [0]
+
+                def step():
+                    c = i[0] % copies
+                    i[0] += 1
+                    for (n, k, pks, sc, _), x in zip(layers, xs):
+                        gemv_packed(pks[c], sc, n, k, bits, GROUP, x)
+                for _ in range(3):
+                    step()
+                torch.cuda.synchronize()
+                gph = torch.cuda.CUDAGraph()
+                side = torch.cuda.Stream()
+                with torch.cuda.stream(side):
+                    i[0] = 0
+                    with torch.cuda.graph(gph):
+                        for _ in range(copies):
+                            step()
+                torch.cuda.synchronize()
+                ms = timed(gph.replay, max(3, args.steps // copies)) / copies
+                nbytes = sum(p[2][0].numel() + p[3].numel() * 2 + (p[0] + p[1]) * batch * 2 for p in layers)
+                per_b[f"batch{batch}"] = {"us_per_step": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peak,
+                                          "bytes_per_step": nbytes, "rel_l2_vs_dequantise_then_matmul": err}
+            res[f"int{bits}"] = per_b
+        # comparators on the 4-bit layers: dense fp16 GEMV (torch) and the entropy-coded fused GEMV
+        xs = [torch.randn(1, k, device="cuda").half() for (_, k) in shapes]
+        dense16 = [[torch.randn(n, k, device="cuda", dtype=torch.float16) for _ in range(4)] for (n, k) in shapes]
+        j = [0]
+
+        def dense_step():
+            c = j[0] % 4
+            j[0] += 1
+            for ws_, x in zip(dense16, xs):
+                torch.nn.functional.linear(x, ws_[c])
+        for _ in range(3):
+            dense_step()
+        torch.cuda.synchronize()
+        gd = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            j[0] = 0
+            with torch.cuda.graph(gd):
+                for _ in range(4):
+                    dense_step()
+        torch.cuda.synchronize()
+        dense_us = timed(gd.replay, max(3, args.steps // 4)) / 4 * 1e3
+        line = {"metric": "packed-code GEMV (QuantizedLinear forward, few rows) effective HBM GB/s", "unit": "GB/s", "n_gpus": 1,
+                "steps": args.steps, "data": "synthetic", "higher_is_better": True, "dtype": "packed integer codes, fp32 accumulate, fp16 in/out",
+                "config": {"workload": "llama7b_mlp_pair_packed_g128", "shapes": shapes, "l2": f"{copies} copies of each layer cycled (> L2)",
+                           "launch": "cuda-graph"},
+                "value": res["int4"]["batch1"]["gbs"], "ms_per_step": res["int4"]["batch1"]["us_per_step"] / 1e3,
+                "roofline": {"bound": "hbm", "kernel": "gemv_packed_mma_kernel<4,fp16,1>", "achieved": res["int4"]["batch1"]["gbs"], "peak": peak,
+                             "unit": "GB/s", "frac": res["int4"]["batch1"]["frac_of_hbm_peak"], "peak_source": peak_src, "traffic": None},
+                "per_width": res, "fp16_dense_us_per_step": dense_us}
+        print(json.dumps(line), flush=True)
+        return
 
     # polar_q5
     n, k, d = 14336, 4096, 64
@@ -1164,7 +1252,7 @@ def main():
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: how output slices are exchanged")
     ap.add_argument("--no-pdl", action="store_true", help="plain launches instead of programmatic dependent launches")
     ap.add_argument("--workload", default="mlp_pair",
-                    choices=["mlp_pair", "decode_dequant", "polar_q5", "llama7b_step", "prefill_gemm", "wire_decode", "model_load"])
+                    choices=["mlp_pair", "decode_dequant", "polar_q5", "llama7b_step", "prefill_gemm", "wire_decode", "model_load", "packed_gemv"])
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
                     help="pass a knob to eoq_b200_tune (e.g. gemv_pairs=0: the one-tile-per-warp ring kernel)")
     args = ap.parse_args()

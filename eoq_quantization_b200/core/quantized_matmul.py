@@ -10,7 +10,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..fused import GEMM_MAX_ROWS, EOQWeight, dequant_packed, fused_rows, require_cuda
+from ..fused import GEMM_MAX_ROWS, EOQWeight, dequant_packed, fused_rows, gemv_packed, PACKED_TENSOR_ROWS, packed_gemv_rows, require_cuda
 
 _SUPPORTED_BITS = (2, 4, 8)
 _MEMORY_THRESHOLD = 16 * 1024 * 1024
@@ -134,6 +134,11 @@ class QuantizedLinearFast(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         require_cuda(x, "QuantizedLinearFast.forward")
         rows = x.numel() // max(self.in_features, 1)
+        if self.strategy == "auto" and x.dtype in (torch.float16, torch.bfloat16) and \
+                1 <= rows <= PACKED_TENSOR_ROWS == packed_gemv_rows(self.in_features, self.bits, self.block_size, x.dtype):
+            # one pass over the packed codes on the tensor cores (HBM-bound), see QuantizedLinear.forward
+            return gemv_packed(self.packed_weight, self.scales, self.out_features, self.in_features, self.bits, self.block_size,
+                               x, self.bias_param)
         if self.strategy == "auto" and self._fusable() and rows >= 1 and x.dtype in (torch.float16, torch.bfloat16, torch.float32):
             # up to fused_rows (4 rows of 16-bit activations, 8 of fp32): fused decode + GEMV, fp32 accumulate; beyond
             # that one dequantisation amortises over enough rows for a library GEMM to win (the fused tensor-core

@@ -1441,6 +1441,30 @@ extern "C" eoq_error_t eoq_b200_dequant_packed(const uint8_t *d_packed, const ui
     return EOQ_OK;
 }
 
+extern "C" eoq_error_t eoq_b200_gemv_packed(const uint8_t *d_packed, const uint16_t *d_scales_fp16, uint32_t rows, uint32_t cols,
+                                            uint32_t bits, uint32_t group, const void *x, int x_dtype, uint32_t batch, void *y,
+                                            int y_dtype, const float *bias, void *stream)
+{
+    if (!d_packed || !d_scales_fp16 || !x || !y) return EOQ_ERR_NULL_PTR;
+    if (batch == 0 || rows == 0) return EOQ_OK;
+    if (x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2) return EOQ_ERR_UNSUPPORTED;
+    if (bits < 2 || bits > 8 || group == 0 || cols == 0) return EOQ_ERR_INVALID_HEADER;
+    // a lane takes sixteen aligned bytes of a row, in pieces of eight columns of one scale group: other shapes go through
+    // the dequantise kernel
+    const uint32_t per16 = bits == 4 ? 32u : bits == 2 ? 64u : 16u;
+    if (cols % per16 || group % 8u || cols % group || (reinterpret_cast<uintptr_t>(d_packed) & 15u)) return EOQ_ERR_UNSUPPORTED;
+    PackedGemvArgs a = {};
+    a.packed = d_packed; a.scales = d_scales_fp16; a.x = x; a.y = y; a.bias = bias;
+    a.N = rows; a.K = cols; a.group = group; a.batch = batch; a.bits = bits; a.x_dtype = x_dtype; a.y_dtype = y_dtype;
+    // row stride of QuantizedLinear.packed_weight (core/quantized_linear.py:49-66)
+    a.row_bytes = bits == 4 ? cols / 2 : bits == 2 ? cols / 4 : cols;
+    if (batch > gemv_packed_rows(a)) return EOQ_ERR_UNSUPPORTED;
+    if (!have_device()) return EOQ_ERR_CUDA;
+    int e = launch_gemv_packed(a, stream);
+    if (e != 0) { std::fprintf(stderr, "eoq_b200_gemv_packed: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
+    return EOQ_OK;
+}
+
 extern "C" eoq_error_t eoq_b200_weight_status(eoq_b200_weight_t *w, void *stream)
 {
     if (!w) return EOQ_ERR_NULL_PTR;

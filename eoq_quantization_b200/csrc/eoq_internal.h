@@ -204,6 +204,18 @@ int launch_decode_v1_syminfo(const uint8_t *d_stream, const uint32_t *d_offsets,
 int launch_decode_v1_resume(const uint8_t *d_block, uint32_t stream_end, const V1Table *d_table,
                             uint32_t *d_state_pos /* [2]: state, pos */, uint8_t *d_out, uint32_t count,
                             uint32_t p, void *stream);
+// GEMV on QuantizedLinear's in-memory form (packed codes, fp16 scales): see gemv_packed_kernel.
+struct PackedGemvArgs {
+    const uint8_t *packed;      // [N][row_bytes]
+    const uint16_t *scales;     // fp16 bits, [N][K / group]
+    const void *x;              // [batch][K]
+    void *y;                    // [batch][N]
+    const float *bias;          // [N] or null
+    uint32_t N, K, group, row_bytes, batch, bits;
+    int x_dtype, y_dtype;
+};
+uint32_t gemv_packed_rows(const PackedGemvArgs &a);
+int launch_gemv_packed(const PackedGemvArgs &a, void *stream);
 int launch_dequant_packed(const uint8_t *packed, const uint16_t *scales, uint32_t K, uint32_t row_bytes, uint32_t bits,
                           uint32_t group, uint32_t row_lo, uint32_t row_hi, void *out, int out_dtype, void *stream);
 int launch_gemm_tc(const uint32_t *table, const TileDesc *tiles, const uint8_t *stream, const uint2 *scales_t, const void *x,

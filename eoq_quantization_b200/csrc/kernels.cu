@@ -2807,6 +2807,362 @@ int launch_dequant_packed(const uint8_t *packed, const uint16_t *scales, uint32_
 }
 
 // ---------------------------------------------------------------------------
+// GEMV straight from QuantizedLinear's in-memory form (packed codes + fp16 scales, no entropy coding): the module's
+// forward for up to eight activation rows (core/quantized_linear.py:219-228 dequantises the whole matrix and calls a
+// GEMM).  General form (any float activations, groups that are multiples of 8 columns): every weight byte is read once,
+// coalesced; a warp takes kPackedRows output rows, a lane sixteen bytes of each per trip (the next trip's requested
+// before this one's are consumed), in pieces of eight columns whose activations come through L1 (the same eight serve
+// all the warp's rows).  A code becomes a float by a shift and one logic instruction: it is placed in the top mantissa
+// bits of 128.0 (nibbles, 2-bit) or assembled by a byte permute into 32768.0 + u (byte codes), and one exact
+// subtraction leaves the signed code; products and sums in fp32, the group's scale applied once per eight columns.
+// ---------------------------------------------------------------------------
+constexpr int kPackedRows = 2, kPackedWarps = 8;
+
+template <int BITS, int BT>
+__global__ void __launch_bounds__(kPackedWarps * 32) gemv_packed_kernel(const PackedGemvArgs a)
+{
+    constexpr uint32_t kCols = BITS == 4 ? 32u : BITS == 2 ? 64u : 16u;      // columns in a lane's 16-byte load
+    constexpr uint32_t kSub = kCols / 8u, kSpan = 32u * kCols;               // eight-column pieces per load; columns a warp covers per trip
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t row0 = (blockIdx.x * kPackedWarps + warp) * kPackedRows;
+    if (row0 >= a.N) return;
+    const uint32_t sgroups = a.K / a.group;
+    // the float that stands for code 0: 128 + qmax for codes stored as code + qmax; 32768 + 128 for signed bytes (u = code ^ 0x80)
+    const float offset = BITS == 8 ? 32768.0f + 128.0f : 128.0f + (float)((1u << (BITS - 1)) - 1u);
+    uint32_t magic;
+    asm volatile("mov.b32 %0, %1;" : "=r"(magic) : "n"(0x43000000));      // 128.0f; in a register so that the mask stays the immediate
+    const bool x_vec = a.x_dtype != EOQ_B200_F32 && (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0;
+    const uint8_t *src[kPackedRows];
+    const uint16_t *srow[kPackedRows];
+#pragma unroll
+    for (int r = 0; r < kPackedRows; r++) {
+        const uint32_t row = min(row0 + r, a.N - 1u);
+        src[r] = a.packed + (size_t)row * a.row_bytes;
+        srow[r] = a.scales + (size_t)row * sgroups;
+    }
+    float acc[kPackedRows][BT];
+#pragma unroll
+    for (int r = 0; r < kPackedRows; r++)
+#pragma unroll
+        for (int b = 0; b < BT; b++) acc[r][b] = 0.0f;
+
+    // the weights are what comes from DRAM: a lane's sixteen bytes of the next trip are requested before this trip's
+    // are consumed
+    uint32_t wc[kPackedRows][4], wn[kPackedRows][4];
+    auto load_w = [&](uint32_t c, uint32_t (&w)[kPackedRows][4]) {
+#pragma unroll
+        for (int r = 0; r < kPackedRows; r++) {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (c < a.K) v = __ldg(reinterpret_cast<const uint4 *>(src[r] + (size_t)c * BITS / 8u));
+            w[r][0] = v.x; w[r][1] = v.y; w[r][2] = v.z; w[r][3] = v.w;
+        }
+    };
+    uint32_t c = lane * kCols;
+    load_w(c, wc);
+    for (; c < a.K; c += kSpan) {
+        load_w(c + kSpan, wn);
+#pragma unroll
+        for (uint32_t sub = 0; sub < kSub; sub++) {
+            const uint32_t cc = c + sub * 8u;
+            float xv[BT][8];
+#pragma unroll
+            for (int b = 0; b < BT; b++) {
+                if ((uint32_t)b < a.batch) {
+                    const size_t i0 = (size_t)b * a.K + cc;
+                    if (x_vec) {
+                        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(a.x) + i0));
+                        const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (int h = 0; h < 4; h++) {
+                            if (a.x_dtype == EOQ_B200_F16) {
+                                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&q[h]));
+                                xv[b][2 * h] = f.x; xv[b][2 * h + 1] = f.y;
+                            } else {
+                                xv[b][2 * h] = __uint_as_float(q[h] << 16); xv[b][2 * h + 1] = __uint_as_float(q[h] & 0xFFFF0000u);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; i++) xv[b][i] = load_x(a.x, i0 + i, a.x_dtype);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) xv[b][i] = 0.0f;
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < kPackedRows; r++) {
+                const float s = half_bits_to_float(__ldg(srow[r] + cc / a.group));
+                // the eight codes of this piece: one word of nibbles, half a word of 2-bit codes, two words of bytes
+                const uint32_t w0 = BITS == 4 ? wc[r][sub] : BITS == 2 ? wc[r][sub >> 1] >> (16u * (sub & 1u)) : wc[r][2 * sub] ^ 0x80808080u;
+                const uint32_t w1 = BITS == 8 ? wc[r][(2 * sub + 1) & 3] ^ 0x80808080u : 0u;
+                float p[BT];
+#pragma unroll
+                for (int b = 0; b < BT; b++) p[b] = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    uint32_t t;
+                    if (BITS == 4) {
+                        const uint32_t sh = i < 4 ? w0 << (16 - 4 * i) : w0 >> (4 * i - 16);
+                        asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t) : "r"(sh), "n"(0x000F0000), "r"(magic));       // (sh & mask) | 128.0f
+                    } else if (BITS == 2) {
+                        const uint32_t sh = w0 << (16 - 2 * i);
+                        asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t) : "r"(sh), "n"(0x00030000), "r"(magic));
+                    } else {
+                        // {0x47, 0x00, byte i, 0x00} = 32768.0f + u
+                        t = __byte_perm(i < 4 ? w0 : w1, 0x47000000u, 0x7404u | ((uint32_t)(i & 3) << 4));
+                    }
+                    const float m = __uint_as_float(t) - offset;              // exact: the signed code
+#pragma unroll
+                    for (int b = 0; b < BT; b++) p[b] = fmaf(m, xv[b][i], p[b]);
+                }
+#pragma unroll
+                for (int b = 0; b < BT; b++) acc[r][b] = fmaf(s, p[b], acc[r][b]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < kPackedRows; r++)
+#pragma unroll
+            for (int q = 0; q < 4; q++) wc[r][q] = wn[r][q];
+    }
+#pragma unroll
+    for (int r = 0; r < kPackedRows; r++)
+#pragma unroll
+        for (int b = 0; b < BT; b++) {
+            float v = acc[r][b];
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+            const uint32_t row = row0 + r;
+            if (lane == 0 && row < a.N && (uint32_t)b < a.batch)
+                store_y(a.y, (size_t)b * a.N + row, v + (a.bias ? __ldg(a.bias + row) : 0.0f), a.y_dtype);
+        }
+}
+
+// The same product on the warp-level tensor-core path, for 16-bit activations and scale groups that are multiples
+// of 128 columns: D[16 weight rows x 8 activation rows] += A[16 x 16] * B[16 x 8] (mma.sync m16n8k16, fp32
+// accumulate).  The contraction index is a dummy, so the sixteen "k" positions of one instruction need not be
+// sixteen adjacent columns: lane (g, t) takes 32 adjacent columns of weight rows g and g + 8 (sixteen bytes of
+// nibbles: whole sectors per row across a quad) and the same 32 columns of activation row g, and feeds them in the
+// order in which the codes come out of the words cheapest: (word >> 4i) & 0x000F000F puts codes i and i + 4 into
+// the two halves of a register, OR with 0x6400 (fp16 1024) or 0x4300 (bf16 128) makes them the exact values
+// 1024 + code or 128 + code, one packed subtraction the exact signed code.  The activations are paired the same
+// way with one byte permute per register.  A quad of lanes covers 128 columns per trip (a "span"); the spans of a
+// 16-row tile are dealt to the eight warps of the CTA, each folds its per-span accumulator into the total with the
+// rows' fp16 scales (fp32), and the eight totals meet in shared memory.
+constexpr int kMmaWarps = 8;
+
+template <bool BF16>
+__device__ __forceinline__ void mma_m16n8k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    if (BF16)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    else
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// two codes, already sitting in the low bits of the two halves of v, to two exact signed 16-bit floats
+template <bool BF16>
+__device__ __forceinline__ uint32_t codes_to_pair(uint32_t v, uint32_t mask, uint32_t q)
+{
+    const uint32_t magic = BF16 ? 0x43004300u : 0x64006400u;
+    const uint32_t biased = (v & mask) | magic, off = magic | q | (q << 16);
+    uint32_t r;
+    if (BF16) asm("sub.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(biased), "r"(off));
+    else asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(biased), "r"(off));
+    return r;
+}
+
+template <int BITS, bool BF16, int NB>
+__global__ void __launch_bounds__(kMmaWarps * 32) gemv_packed_mma_kernel(const PackedGemvArgs a)
+{
+    static_assert(BITS == 2 || BITS == 4 || (BITS == 8 && !BF16), "byte codes + 128 do not fit a bf16 mantissa");
+    constexpr int kWords = BITS;                                   // 32-bit words that hold a lane's 32 columns of one row
+    constexpr int kBatch = BITS == 8 ? 2 : 4;                      // spans whose weights are in flight together
+    __shared__ float red[kMmaWarps][NB][16][8];
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3u;
+    const uint32_t row0 = blockIdx.x * 16u;
+    const uint32_t ra = min(row0 + g, a.N - 1u), rb = min(row0 + g + 8u, a.N - 1u);
+    const uint32_t sgroups = a.K / a.group, nspans = a.K >> 7;
+    const uint8_t *pa = a.packed + (size_t)ra * a.row_bytes + t * (4u * BITS);
+    const uint8_t *pb = a.packed + (size_t)rb * a.row_bytes + t * (4u * BITS);
+    const uint16_t *sa = a.scales + (size_t)ra * sgroups, *sb = a.scales + (size_t)rb * sgroups;
+    const uint16_t *xr[NB];
+    bool has_x[NB];
+#pragma unroll
+    for (int n = 0; n < NB; n++) {
+        has_x[n] = 8u * n + g < a.batch;
+        xr[n] = reinterpret_cast<const uint16_t *>(a.x) + (size_t)min(8u * n + g, a.batch - 1u) * a.K + t * 32u;
+    }
+    float tot[NB][4];
+#pragma unroll
+    for (int n = 0; n < NB; n++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) tot[n][i] = 0.0f;
+
+    // The weights and scales do not depend on the kernel before this one in the stream, the activations may: the
+    // first batch of weight loads is in flight before the dependency wait (programmatic dependent launch).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    bool waited = false;
+    for (uint32_t s0 = warp; s0 < nspans; s0 += kMmaWarps * kBatch) {
+        // kBatch spans of both rows requested before the first is consumed: one DRAM round trip per batch
+        uint32_t wa[kBatch][kWords], wb[kBatch][kWords];
+        float sca[kBatch], scb[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; u++) {
+            const uint32_t s = s0 + u * kMmaWarps;
+            const size_t off = (size_t)s * (16u * BITS);
+            if (s < nspans) {
+                if (BITS == 2) {
+                    const uint2 va = __ldg(reinterpret_cast<const uint2 *>(pa + off)), vb = __ldg(reinterpret_cast<const uint2 *>(pb + off));
+                    wa[u][0] = va.x; wa[u][1] = va.y; wb[u][0] = vb.x; wb[u][1] = vb.y;
+                } else {
+#pragma unroll
+                    for (int h = 0; h < kWords / 4; h++) {
+                        const uint4 va = __ldg(reinterpret_cast<const uint4 *>(pa + off) + h), vb = __ldg(reinterpret_cast<const uint4 *>(pb + off) + h);
+                        wa[u][4 * h] = va.x; wa[u][4 * h + 1] = va.y; wa[u][4 * h + 2] = va.z; wa[u][4 * h + 3] = va.w;
+                        wb[u][4 * h] = vb.x; wb[u][4 * h + 1] = vb.y; wb[u][4 * h + 2] = vb.z; wb[u][4 * h + 3] = vb.w;
+                    }
+                }
+                const uint32_t gi = (s << 7) / a.group;
+                sca[u] = half_bits_to_float(__ldg(sa + gi)); scb[u] = half_bits_to_float(__ldg(sb + gi));
+            }
+        }
+        if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
+#pragma unroll
+        for (int u = 0; u < kBatch; u++) {
+            const uint32_t s = s0 + u * kMmaWarps;
+            if (s >= nspans) break;
+            // the codes of both rows as signed 16-bit floats, in the order they come out of the words
+            uint32_t ha[16], hb[16];
+#pragma unroll
+            for (int j = 0; j < kWords; j++) {
+                if (BITS == 4) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        ha[4 * j + i] = codes_to_pair<BF16>(wa[u][j] >> (4 * i), 0x000F000Fu, 7u);      // columns 8j + i and 8j + i + 4
+                        hb[4 * j + i] = codes_to_pair<BF16>(wb[u][j] >> (4 * i), 0x000F000Fu, 7u);
+                    }
+                } else if (BITS == 2) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        ha[8 * j + i] = codes_to_pair<BF16>(wa[u][j] >> (2 * i), 0x00030003u, 1u);      // columns 16j + i and 16j + i + 8
+                        hb[8 * j + i] = codes_to_pair<BF16>(wb[u][j] >> (2 * i), 0x00030003u, 1u);
+                    }
+                } else {
+                    // signed bytes: u = code + 128 in the low byte of each half under 0x64, i.e. 1024 + u; columns 4j + 2i, + 1
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        ha[2 * j + i] = codes_to_pair<BF16>(__byte_perm(wa[u][j] ^ 0x80808080u, 0u, i ? 0x4342u : 0x4140u), 0x00FF00FFu, 128u);
+                        hb[2 * j + i] = codes_to_pair<BF16>(__byte_perm(wb[u][j] ^ 0x80808080u, 0u, i ? 0x4342u : 0x4140u), 0x00FF00FFu, 128u);
+                    }
+                }
+            }
+#pragma unroll
+            for (int n = 0; n < NB; n++) {
+                uint32_t q[16];
+                if (has_x[n]) {
+#pragma unroll
+                    for (int h = 0; h < 4; h++) {
+                        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(xr[n] + ((size_t)s << 7)) + h);
+                        q[4 * h] = v.x; q[4 * h + 1] = v.y; q[4 * h + 2] = v.z; q[4 * h + 3] = v.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int h = 0; h < 16; h++) q[h] = 0u;
+                }
+                // the activations in the weights' order: register i of the 16 holds the two columns that ha[i] holds
+                uint32_t xp[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    if (BITS == 4) {            // j = i / 4, columns 8j + (i & 3) and + 4: halves of q[4j + (i & 3) / 2] and q[4j + 2 + (i & 3) / 2]
+                        const int j = i >> 2, k = (i & 3) >> 1;
+                        xp[i] = __byte_perm(q[4 * j + k], q[4 * j + 2 + k], (i & 1) ? 0x7632u : 0x5410u);
+                    } else if (BITS == 2) {     // j = i / 8, columns 16j + (i & 7) and + 8
+                        const int j = i >> 3, k = (i & 7) >> 1;
+                        xp[i] = __byte_perm(q[8 * j + k], q[8 * j + 4 + k], (i & 1) ? 0x7632u : 0x5410u);
+                    } else {
+                        xp[i] = q[i];
+                    }
+                }
+                float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int m = 0; m < 8; m++)
+                    mma_m16n8k16<BF16>(c, ha[2 * m], hb[2 * m], ha[2 * m + 1], hb[2 * m + 1], xp[2 * m], xp[2 * m + 1]);
+                tot[n][0] = fmaf(sca[u], c[0], tot[n][0]); tot[n][1] = fmaf(sca[u], c[1], tot[n][1]);
+                tot[n][2] = fmaf(scb[u], c[2], tot[n][2]); tot[n][3] = fmaf(scb[u], c[3], tot[n][3]);
+            }
+        }
+    }
+    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
+#pragma unroll
+    for (int n = 0; n < NB; n++) {
+        red[warp][n][g][2 * t] = tot[n][0]; red[warp][n][g][2 * t + 1] = tot[n][1];
+        red[warp][n][g + 8][2 * t] = tot[n][2]; red[warp][n][g + 8][2 * t + 1] = tot[n][3];
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < NB * 128u; i += kMmaWarps * 32u) {
+        const uint32_t n = i >> 7, r = (i >> 3) & 15u, b = 8u * n + (i & 7u), row = row0 + r;
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kMmaWarps; w++) v += red[w][n][r][i & 7u];
+        if (row < a.N && b < a.batch) store_y(a.y, (size_t)b * a.N + row, v + (a.bias ? __ldg(a.bias + row) : 0.0f), a.y_dtype);
+    }
+}
+
+// bits: 2 and 4 as packed by QuantizedLinear (low bits first, code + qmax), anything else one signed code per byte.
+// K a multiple of the group and of the columns in sixteen bytes (32 nibbles, 64 two-bit codes, 16 bytes), the group a
+// multiple of 8, packed rows 16-byte aligned: checked by the caller.
+// Activation rows one launch takes: 32 on the tensor-core form (16-bit activations, 16-byte aligned, against scale
+// groups of whole 128-column spans; byte codes only with fp16), 8 otherwise.
+uint32_t gemv_packed_rows(const PackedGemvArgs &a)
+{
+    const bool byte_codes = a.bits != 2 && a.bits != 4;
+    const bool tensor = a.x_dtype != EOQ_B200_F32 && a.K % 128u == 0 && a.group % 128u == 0 &&
+                        !(byte_codes && a.x_dtype == EOQ_B200_BF16) && (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0;
+    return tensor ? 32u : 8u;
+}
+
+int launch_gemv_packed(const PackedGemvArgs &a, void *stream)
+{
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (gemv_packed_rows(a) > 8u) {
+        const uint32_t tiles = (a.N + 15u) / 16u;
+        cudaError_t e = cudaSuccess;
+#define EOQ_LAUNCH_MMA(B, H)                                                                                             \
+    do {                                                                                                                 \
+        if (a.batch <= 8) e = launch_with_pdl(gemv_packed_mma_kernel<B, H, 1>, dim3(tiles), dim3(kMmaWarps * 32), 0, st, a);                          \
+        else if (a.batch <= 16) e = launch_with_pdl(gemv_packed_mma_kernel<B, H, 2>, dim3(tiles), dim3(kMmaWarps * 32), 0, st, a);                    \
+        else e = launch_with_pdl(gemv_packed_mma_kernel<B, H, 4>, dim3(tiles), dim3(kMmaWarps * 32), 0, st, a);                                       \
+    } while (0)
+        const bool bf = a.x_dtype == EOQ_B200_BF16;
+        if (a.bits == 4) { if (bf) EOQ_LAUNCH_MMA(4, true); else EOQ_LAUNCH_MMA(4, false); }
+        else if (a.bits == 2) { if (bf) EOQ_LAUNCH_MMA(2, true); else EOQ_LAUNCH_MMA(2, false); }
+        else EOQ_LAUNCH_MMA(8, false);
+#undef EOQ_LAUNCH_MMA
+        g_launches++;
+        return (int)e;
+    }
+    if (a.batch > 8) return (int)cudaErrorInvalidValue;
+    const uint32_t grid = (a.N + kPackedWarps * kPackedRows - 1u) / (kPackedWarps * kPackedRows);
+    const uint32_t bt = a.batch <= 1 ? 1u : a.batch <= 2 ? 2u : a.batch <= 4 ? 4u : 8u;
+#define EOQ_LAUNCH_PACKED(B)                                                                                             \
+    do {                                                                                                                 \
+        if (bt == 1) gemv_packed_kernel<B, 1><<<grid, kPackedWarps * 32, 0, st>>>(a);                                    \
+        else if (bt == 2) gemv_packed_kernel<B, 2><<<grid, kPackedWarps * 32, 0, st>>>(a);                               \
+        else if (bt == 4) gemv_packed_kernel<B, 4><<<grid, kPackedWarps * 32, 0, st>>>(a);                               \
+        else gemv_packed_kernel<B, 8><<<grid, kPackedWarps * 32, 0, st>>>(a);                                            \
+    } while (0)
+    if (a.bits == 4) EOQ_LAUNCH_PACKED(4);
+    else if (a.bits == 2) EOQ_LAUNCH_PACKED(2);
+    else EOQ_LAUNCH_PACKED(8);
+#undef EOQ_LAUNCH_PACKED
+    g_launches++;
+    return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
 // Fused decode -> fp16 operand pieces -> tcgen05 MMA (accumulator in tensor memory), for up to 128 activation rows.
 //
 //   Y[m, n] = sum_k X[m, k] * W[n, k]        (INT4 weights, 3 per step, 96-row tiles)

@@ -38,6 +38,7 @@ def require_cuda(t: torch.Tensor, what: str) -> None:
 # rows on 3584 x 8192: it decodes one tile per warp through a word ring, at half the rate of the two-tiles-per-warp decoders.
 GEMV_MAX_ROWS = {torch.float16: 4, torch.bfloat16: 4, torch.float32: 8}
 GEMM_MAX_ROWS = 8       # rows up to which the tensor-core kernel would be preferred to decode + library GEMM: none above the GEMV's
+PACKED_TENSOR_ROWS = 32       # activation rows the tensor-core form of the packed GEMV takes per launch
 
 
 def fused_rows(dtype: torch.dtype) -> int:
@@ -302,3 +303,51 @@ def dequant_packed(packed: torch.Tensor, scales: torch.Tensor, rows: int, cols: 
         _lib.check(_lib.lib().eoq_b200_dequant_packed(pk.data_ptr(), sc.data_ptr() if sc is not None else None, rows, cols, bits, group,
                                                       row_lo, row_hi, out.data_ptr(), code, _stream_ptr()), "eoq_b200_dequant_packed")
     return out
+
+
+def packed_gemv_rows(cols: int, bits: int, group: int, dtype: torch.dtype = torch.float16) -> int:
+    """Activation rows `gemv_packed` takes for this shape: 32 on its tensor-core form (16-bit activations against
+    scale groups of whole 128-column spans; byte codes only with fp16), 8 on the general form, 0 if it does not apply."""
+    if not (2 <= bits <= 8 and group > 0 and cols % group == 0):
+        return 0
+    byte_codes = bits not in (2, 4)
+    if dtype in (torch.float16, torch.bfloat16) and cols % 128 == 0 and group % 128 == 0 and not (byte_codes and dtype == torch.bfloat16):
+        return PACKED_TENSOR_ROWS
+    per16 = 32 if bits == 4 else 64 if bits == 2 else 16                 # codes in the sixteen bytes a lane loads
+    return 8 if cols % per16 == 0 and group % 8 == 0 else 0
+
+
+def packed_gemv_applies(cols: int, bits: int, group: int, dtype: torch.dtype = torch.float16, rows: int = 1) -> bool:
+    """Whether `gemv_packed` takes this shape and row count (else: `dequant_packed` and a GEMM)."""
+    return 1 <= rows <= packed_gemv_rows(cols, bits, group, dtype)
+
+
+def gemv_packed(packed: torch.Tensor, scales: torch.Tensor, rows: int, cols: int, bits: int, group: int, x: torch.Tensor,
+                bias: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """y = x @ W.T (+ bias) for at most `packed_gemv_rows` rows of x, straight from a packed QuantizedLinear weight
+    (codes + fp16 scales resident on the device): one pass over the packed bytes, fp32 accumulation, no dense matrix
+    in between."""
+    require_cuda(packed, "gemv_packed")
+    require_cuda(x, "gemv_packed")
+    if x.device != packed.device:
+        raise RuntimeError(f"gemv_packed: the activations are on {x.device} but the weight lives on {packed.device}")
+    if x.shape[-1] != cols:
+        raise ValueError(f"expected last dimension {cols}, got {x.shape[-1]}")
+    if x.dtype not in _DTYPES:
+        raise TypeError(f"unsupported activation dtype {x.dtype}")
+    x2 = x.reshape(-1, cols).contiguous()
+    n = x2.shape[0]
+    if x2.data_ptr() % 16:
+        x2 = x2.clone()
+    if n > packed_gemv_rows(cols, bits, group, x.dtype):
+        raise ValueError(f"at most {packed_gemv_rows(cols, bits, group, x.dtype)} rows per call for this shape and dtype")
+    pk = packed.contiguous()
+    sc = scales.to(device=packed.device, dtype=torch.float16).contiguous()
+    out_dtype = out_dtype or x.dtype
+    y = torch.empty((n, rows), dtype=out_dtype, device=x.device)
+    b = None if bias is None else bias.to(device=x.device, dtype=torch.float32).contiguous()
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().eoq_b200_gemv_packed(pk.data_ptr(), sc.data_ptr(), rows, cols, bits, group, x2.data_ptr(), _DTYPES[x.dtype], n,
+                                                   y.data_ptr(), _DTYPES[out_dtype], b.data_ptr() if b is not None else None, _stream_ptr()),
+                   "eoq_b200_gemv_packed")
+    return y.reshape(*x.shape[:-1], rows)

@@ -429,6 +429,23 @@ eoq_error_t eoq_b200_dequant_packed(const uint8_t *d_packed, const uint16_t *d_s
                                     uint32_t bits, uint32_t group, uint32_t row_lo, uint32_t row_hi, void *d_out,
                                     int out_dtype, void *stream);
 
+/* y = x @ W.T (+ bias) straight from QuantizedLinear's in-memory form, for up
+ * to 8 (or 32, see below) activation rows: what QuantizedLinear.forward computes by dequantising
+ * the whole matrix and calling a GEMM (core/quantized_linear.py:219-228), as
+ * one pass over the packed codes (2 and 4 bits packed low bits first with the
+ * code + qmax, any other width one signed code per byte) and the fp16 scales,
+ * fp32 accumulation.  Needs cols a multiple of the group and of the codes in
+ * sixteen bytes (32 at 4 bits, 64 at 2 bits, 16 otherwise), the group a multiple
+ * of 8 and d_packed 16-byte aligned (EOQ_ERR_UNSUPPORTED otherwise: use
+ * eoq_b200_dequant_packed and a GEMM).  x [batch, cols] and y [batch, rows] in
+ * EOQ_B200_F16 / BF16 / F32; device pointers; asynchronous.  With 16-bit
+ * activations (16-byte aligned; fp16 only for byte codes), cols a multiple of
+ * 128 and the group a multiple of 128 the product runs on the tensor cores and
+ * takes up to 32 rows; more rows than the form in use takes: EOQ_ERR_UNSUPPORTED. */
+eoq_error_t eoq_b200_gemv_packed(const uint8_t *d_packed, const uint16_t *d_scales_fp16, uint32_t rows, uint32_t cols,
+                                 uint32_t bits, uint32_t group, const void *x, int x_dtype, uint32_t batch, void *y,
+                                 int y_dtype, const float *bias, void *stream);
+
 /* Synchronises `stream` and reports whether any kernel that used this weight gave up on a
  * bounded wait for its staged data (EOQ_ERR_CUDA; outputs of that launch are then invalid).
  * The kernels never spin without a limit, so a fault in the copy engine ends in this error

@@ -1,0 +1,89 @@
+"""``eoq_b200_gemv_packed``: the GEMV straight from QuantizedLinear's in-memory form (packed codes + fp16 scales), against
+the oracle's dequantise-then-matmul (core/quantized_linear.py:189-228), for every bit width the reference packs."""
+import numpy as np
+import pytest
+import torch
+
+from eoq_quantization_b200 import _lib as L
+from eoq_quantization_b200.core.quantized_linear import QuantizedLinear
+from eoq_quantization_b200.fused import gemv_packed, packed_gemv_applies, packed_gemv_rows
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _pack(codes: np.ndarray, bits: int) -> np.ndarray:
+    """Rows of codes as QuantizedLinear.packed_weight holds them (core/quantized_linear.py:49-66)."""
+    qmax = (1 << (bits - 1)) - 1
+    if bits == 4:
+        u = (codes + qmax).astype(np.uint8)
+        return (u[:, 0::2] | (u[:, 1::2] << 4)).astype(np.uint8)
+    if bits == 2:
+        u = (codes + qmax).astype(np.uint8)
+        return (u[:, 0::4] | (u[:, 1::4] << 2) | (u[:, 2::4] << 4) | (u[:, 3::4] << 6)).astype(np.uint8)
+    return codes.astype(np.int8).view(np.uint8)
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 8])
+@pytest.mark.parametrize("n,k,group", [(1, 128, 128), (101, 256, 64), (300, 1536, 128), (1000, 4096, 128), (77, 11008, 128)])
+def test_packed_gemv_matches_dequantise_then_matmul(bits, n, k, group):
+    rng = np.random.default_rng(bits * 1000 + n + k)
+    wt = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    codes, scales = O.quantize_absmax(wt, bits, group)
+    s16 = scales.astype(np.float16)
+    dense = (codes.reshape(-1, group).astype(np.float64) * s16.astype(np.float64)[:, None]).reshape(n, k)
+    packed = torch.from_numpy(_pack(codes, bits)).cuda()
+    sc = torch.from_numpy(s16).cuda()
+    bias = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).cuda()
+    assert packed_gemv_applies(k, bits, group)
+    for dt in (torch.float16, torch.bfloat16, torch.float32):
+        # 32 rows on the tensor-core form (16-bit activations, groups of whole 128-column spans), 8 on the general one
+        most = packed_gemv_rows(k, bits, group, dt)
+        assert most == (32 if dt != torch.float32 and group % 128 == 0 and not (bits not in (2, 4) and dt == torch.bfloat16) else 8)
+        for rows in (1, 2, 3, 4, 7, 8, 9, 16, 17, 32):
+            x = torch.from_numpy(rng.standard_normal((rows, k)).astype(np.float32)).cuda().to(dt)
+            if rows > most:
+                with pytest.raises(ValueError):
+                    gemv_packed(packed, sc, n, k, bits, group, x, bias)
+                continue
+            y = gemv_packed(packed, sc, n, k, bits, group, x, bias, out_dtype=torch.float32)
+            want = x.float().cpu().numpy().astype(np.float64) @ dense.T + bias.cpu().numpy()
+            # general form: codes ride in a float of magnitude 2**7 (2**15 for byte codes) whose constant is taken out per
+            # eight columns, which leaves about 1e-5 of relative error on a single output; tensor-core form: exact
+            # products, fp32 accumulation
+            assert O.rel_l2(y.cpu().numpy(), want) < 3e-5, (rows, dt)
+            assert torch.equal(y, gemv_packed(packed, sc, n, k, bits, group, x, bias, out_dtype=torch.float32))
+            if dt != torch.float32:
+                yh = gemv_packed(packed, sc, n, k, bits, group, x)
+                assert yh.dtype == dt and yh.shape == (rows, n)
+    # a view that starts two bytes into its allocation is realigned, not refused
+    x = torch.from_numpy(rng.standard_normal(k + 1).astype(np.float32)).cuda().half()[1:].reshape(1, k)
+    y = gemv_packed(packed, sc, n, k, bits, group, x, bias, out_dtype=torch.float32)
+    assert O.rel_l2(y.cpu().numpy(), x.float().cpu().numpy().astype(np.float64) @ dense.T + bias.cpu().numpy()) < 3e-5
+
+
+def test_quantized_linear_forward_takes_the_packed_route_for_few_rows():
+    """The module's forward for up to 32 rows of 16-bit activations is the packed GEMV (no entropy-coded copy is built);
+    more rows go through dequantise + GEMM; fp32 activations and shapes the kernel does not take go the other routes."""
+    rng = np.random.default_rng(0)
+    lin = torch.nn.Linear(512, 200, bias=True)
+    ql = QuantizedLinear.from_float(lin, bits=4, block_size=128).cuda()
+    dense = ql._dequantize_weight().double().cpu().numpy()
+    for dt, tol in ((torch.float16, 1e-3), (torch.bfloat16, 6e-3)):
+        for rows in (1, 5, 8, 9, 32, 40):
+            n0 = L.lib().eoq_b200_launch_count()
+            x = torch.from_numpy(rng.standard_normal((rows, 512)).astype(np.float32)).cuda().to(dt)
+            y = ql(x)
+            want = x.double().cpu().numpy() @ dense.T + ql.bias_param.double().cpu().numpy()
+            assert y.dtype == dt and O.rel_l2(y.double().cpu().numpy(), want) < tol, (dt, rows)
+            assert L.lib().eoq_b200_launch_count() == n0 + 1                   # one kernel of this library either way
+    assert ql._eoq is None
+    x = torch.from_numpy(rng.standard_normal((3, 512)).astype(np.float32)).cuda()
+    want = x.double().cpu().numpy() @ dense.T + ql.bias_param.double().cpu().numpy()
+    assert O.rel_l2(ql(x).double().cpu().numpy(), want) < 1e-5
+    assert not packed_gemv_applies(100, 4, 100) and not packed_gemv_applies(260, 4, 130)
+    assert packed_gemv_applies(4096, 4, 128, torch.float16, 32) and not packed_gemv_applies(4096, 4, 128, torch.float32, 9)
+    odd = QuantizedLinear.from_float(torch.nn.Linear(100, 30, bias=False), bits=4, block_size=100).cuda()
+    x = torch.from_numpy(rng.standard_normal((2, 100)).astype(np.float32)).cuda()
+    want = x.double().cpu().numpy() @ odd._dequantize_weight().double().cpu().numpy().T
+    assert O.rel_l2(odd(x).double().cpu().numpy(), want) < 1e-5
