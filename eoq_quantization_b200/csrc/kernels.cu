@@ -2947,9 +2947,9 @@ __global__ void __launch_bounds__(kPackedWarps * 32) gemv_packed_kernel(const Pa
 // the two halves of a register, OR with 0x6400 (fp16 1024) or 0x4300 (bf16 128) makes them the exact values
 // 1024 + code or 128 + code, one packed subtraction the exact signed code.  The activations are paired the same
 // way with one byte permute per register.  A quad of lanes covers 128 columns per trip (a "span"); the spans of a
-// 16-row tile are dealt to the eight warps of the CTA, each folds its per-span accumulator into the total with the
-// rows' fp16 scales (fp32), and the eight totals meet in shared memory.
-constexpr int kMmaWarps = 8;
+// 16-row tile are dealt to the 8 or 16 warps of the CTA, each folds its per-span accumulator into the total with the
+// rows' fp16 scales (fp32), and the warps' totals meet in shared memory.
+constexpr int kMmaMaxWarps = 16;
 
 template <bool BF16>
 __device__ __forceinline__ void mma_m16n8k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
@@ -2974,26 +2974,86 @@ __device__ __forceinline__ uint32_t codes_to_pair(uint32_t v, uint32_t mask, uin
     return r;
 }
 
+// For fp16 the odd positions of a word are taken without a shift: (w & 0x00F000F0) | 0x6400 is 1024 + 16 code, one
+// fused multiply-add (x 1/16, - 71) the signed code; the 2-bit codes likewise with 1/4, 1/16, 1/64.
+template <bool BF16>
+__device__ __forceinline__ uint32_t scaled_pair(uint32_t v, uint32_t mask, uint32_t mul, uint32_t sub)
+{
+    static_assert(!BF16, "a bf16 mantissa has no room above bit 6");
+    const uint32_t biased = (v & mask) | 0x64006400u;
+    uint32_t r;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(biased), "r"(mul | (mul << 16)), "r"(sub | (sub << 16)));
+    return r;
+}
+
+// the 16 registers of signed 16-bit float pairs of a lane's 32 columns of one row, in the order the words give them
+template <int BITS, bool BF16>
+__device__ __forceinline__ void unpack_span(const uint32_t (&w)[BITS], uint32_t (&h)[16])
+{
+#pragma unroll
+    for (int j = 0; j < BITS; j++) {
+        if (BITS == 4) {                // register 4j + i: columns 8j + i and 8j + i + 4
+            if (BF16) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) h[4 * j + i] = codes_to_pair<BF16>(w[j] >> (4 * i), 0x000F000Fu, 7u);
+            } else {
+                const uint32_t u = w[j] >> 8;
+                h[4 * j + 0] = codes_to_pair<false>(w[j], 0x000F000Fu, 7u);
+                h[4 * j + 1] = scaled_pair<false>(w[j], 0x00F000F0u, 0x2C00u, 0xD470u);       // (1024 + 16 c) / 16 - 71
+                h[4 * j + 2] = codes_to_pair<false>(u, 0x000F000Fu, 7u);
+                h[4 * j + 3] = scaled_pair<false>(u, 0x00F000F0u, 0x2C00u, 0xD470u);
+            }
+        } else if (BITS == 2) {         // register 8j + i: columns 16j + i and 16j + i + 8
+            if (BF16) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) h[8 * j + i] = codes_to_pair<BF16>(w[j] >> (2 * i), 0x00030003u, 1u);
+            } else {
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    const uint32_t u = w[j] >> (8 * half);
+                    h[8 * j + 4 * half + 0] = codes_to_pair<false>(u, 0x00030003u, 1u);
+                    h[8 * j + 4 * half + 1] = scaled_pair<false>(u, 0x000C000Cu, 0x3400u, 0xDC04u);   // / 4 - 257
+                    h[8 * j + 4 * half + 2] = scaled_pair<false>(u, 0x00300030u, 0x2C00u, 0xD410u);   // / 16 - 65
+                    h[8 * j + 4 * half + 3] = scaled_pair<false>(u, 0x00C000C0u, 0x2400u, 0xCC40u);   // / 64 - 17
+                }
+            }
+        } else {                        // signed bytes: u = code + 128 under 0x64 is 1024 + u; register 2j + i: columns 4j + 2i, + 1
+#pragma unroll
+            for (int i = 0; i < 2; i++)
+                h[2 * j + i] = codes_to_pair<BF16>(__byte_perm(w[j] ^ 0x80808080u, 0u, i ? 0x4342u : 0x4140u), 0x00FF00FFu, 128u);
+        }
+    }
+}
+
+// The next span's weights and scales are requested before this span's are consumed (two register sets, used
+// alternately).  Lanes whose activation row does not exist read zeros from a constant block instead of branching.
+__device__ const uint4 kZeroBlock[4] = {};
+
 template <int BITS, bool BF16, int NB>
-__global__ void __launch_bounds__(kMmaWarps * 32) gemv_packed_mma_kernel(const PackedGemvArgs a)
+__global__ void __launch_bounds__(BITS == 8 ? 256 : 512, NB > 1 ? 1 : BITS == 8 ? 3 : 2) gemv_packed_mma_kernel(const PackedGemvArgs a)
 {
     static_assert(BITS == 2 || BITS == 4 || (BITS == 8 && !BF16), "byte codes + 128 do not fit a bf16 mantissa");
-    constexpr int kWords = BITS;                                   // 32-bit words that hold a lane's 32 columns of one row
-    constexpr int kBatch = BITS == 8 ? 2 : 4;                      // spans whose weights are in flight together
-    __shared__ float red[kMmaWarps][NB][16][8];
-    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3u;
+    constexpr int kRows = 2;                                       // a lane's weight rows: g and g + 8 of the tile
+    __shared__ float red[kMmaMaxWarps][NB][16][8];
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5, g = lane >> 2, t = lane & 3u;
     const uint32_t row0 = blockIdx.x * 16u;
-    const uint32_t ra = min(row0 + g, a.N - 1u), rb = min(row0 + g + 8u, a.N - 1u);
-    const uint32_t sgroups = a.K / a.group, nspans = a.K >> 7;
-    const uint8_t *pa = a.packed + (size_t)ra * a.row_bytes + t * (4u * BITS);
-    const uint8_t *pb = a.packed + (size_t)rb * a.row_bytes + t * (4u * BITS);
-    const uint16_t *sa = a.scales + (size_t)ra * sgroups, *sb = a.scales + (size_t)rb * sgroups;
+    const uint32_t sgroups = a.K / a.group, nspans = a.K >> 7, gspans = a.group >> 7;
+    const uint8_t *pw[kRows];
+    const uint16_t *ps[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; r++) {
+        const uint32_t row = min(row0 + r * 8u + g, a.N - 1u);
+        pw[r] = a.packed + (size_t)row * a.row_bytes + t * (4u * BITS);
+        ps[r] = a.scales + (size_t)row * sgroups;
+    }
+    // a lane's 64 bytes of activation row 8n + g per span, or the zero block with no stride where that row does not exist
     const uint16_t *xr[NB];
-    bool has_x[NB];
+    uint32_t xstep[NB];
 #pragma unroll
     for (int n = 0; n < NB; n++) {
-        has_x[n] = 8u * n + g < a.batch;
-        xr[n] = reinterpret_cast<const uint16_t *>(a.x) + (size_t)min(8u * n + g, a.batch - 1u) * a.K + t * 32u;
+        const bool has = 8u * n + g < a.batch;
+        xr[n] = has ? reinterpret_cast<const uint16_t *>(a.x) + (size_t)(8u * n + g) * a.K + t * 32u : reinterpret_cast<const uint16_t *>(kZeroBlock);
+        xstep[n] = has ? 128u : 0u;
     }
     float tot[NB][4];
 #pragma unroll
@@ -3001,112 +3061,87 @@ __global__ void __launch_bounds__(kMmaWarps * 32) gemv_packed_mma_kernel(const P
 #pragma unroll
         for (int i = 0; i < 4; i++) tot[n][i] = 0.0f;
 
+    auto load_span = [&](uint32_t s, uint32_t (&w)[kRows][BITS], uint16_t (&sc)[kRows]) {
+        if (s >= nspans) return;
+        const uint32_t off = s * (16u * BITS), gi = gspans == 1u ? s : s / gspans;
+#pragma unroll
+        for (int r = 0; r < kRows; r++) {
+            if (BITS == 2) {
+                const uint2 v = __ldg(reinterpret_cast<const uint2 *>(pw[r] + off));
+                w[r][0] = v.x; w[r][1] = v.y;
+            } else {
+#pragma unroll
+                for (int h = 0; h < BITS / 4; h++) {
+                    const uint4 v = __ldg(reinterpret_cast<const uint4 *>(pw[r] + off) + h);
+                    w[r][4 * h] = v.x; w[r][4 * h + 1] = v.y; w[r][4 * h + 2] = v.z; w[r][4 * h + 3] = v.w;
+                }
+            }
+            sc[r] = __ldg(ps[r] + gi);
+        }
+    };
+    auto compute_span = [&](uint32_t s, const uint32_t (&w)[kRows][BITS], const uint16_t (&sc)[kRows]) {
+        uint32_t h0[16], h1[16];
+        unpack_span<BITS, BF16>(w[0], h0);
+        unpack_span<BITS, BF16>(w[1], h1);
+#pragma unroll
+        for (int n = 0; n < NB; n++) {
+            uint32_t q[16];
+#pragma unroll
+            for (int h = 0; h < 4; h++) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(xr[n] + s * xstep[n]) + h);
+                q[4 * h] = v.x; q[4 * h + 1] = v.y; q[4 * h + 2] = v.z; q[4 * h + 3] = v.w;
+            }
+            // the activations in the weights' order: register r of the 16 holds the two columns that h0[r] holds
+            uint32_t xp[16];
+#pragma unroll
+            for (int r = 0; r < 16; r++) {
+                if (BITS == 4) {            // j = r / 4, columns 8j + (r & 3) and + 4: halves of q[4j + (r & 3) / 2] and q[4j + 2 + (r & 3) / 2]
+                    const int j = r >> 2, k = (r & 3) >> 1;
+                    xp[r] = __byte_perm(q[4 * j + k], q[4 * j + 2 + k], (r & 1) ? 0x7632u : 0x5410u);
+                } else if (BITS == 2) {     // j = r / 8, columns 16j + (r & 7) and + 8
+                    const int j = r >> 3, k = (r & 7) >> 1;
+                    xp[r] = __byte_perm(q[8 * j + k], q[8 * j + 4 + k], (r & 1) ? 0x7632u : 0x5410u);
+                } else {
+                    xp[r] = q[r];
+                }
+            }
+            // two accumulators: consecutive instructions do not wait for one another
+            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f}, d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int m = 0; m < 8; m += 2) {
+                mma_m16n8k16<BF16>(c, h0[2 * m], h1[2 * m], h0[2 * m + 1], h1[2 * m + 1], xp[2 * m], xp[2 * m + 1]);
+                mma_m16n8k16<BF16>(d, h0[2 * m + 2], h1[2 * m + 2], h0[2 * m + 3], h1[2 * m + 3], xp[2 * m + 2], xp[2 * m + 3]);
+            }
+            const float fa = half_bits_to_float(sc[0]), fb = half_bits_to_float(sc[1]);
+            tot[n][0] = fmaf(fa, c[0] + d[0], tot[n][0]); tot[n][1] = fmaf(fa, c[1] + d[1], tot[n][1]);
+            tot[n][2] = fmaf(fb, c[2] + d[2], tot[n][2]); tot[n][3] = fmaf(fb, c[3] + d[3], tot[n][3]);
+        }
+    };
+
     // The weights and scales do not depend on the kernel before this one in the stream, the activations may: the
-    // first batch of weight loads is in flight before the dependency wait (programmatic dependent launch).
+    // first span's weight loads are in flight before the dependency wait (programmatic dependent launch).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    bool waited = false;
-    for (uint32_t s0 = warp; s0 < nspans; s0 += kMmaWarps * kBatch) {
-        // kBatch spans of both rows requested before the first is consumed: one DRAM round trip per batch
-        uint32_t wa[kBatch][kWords], wb[kBatch][kWords];
-        float sca[kBatch], scb[kBatch];
-#pragma unroll
-        for (int u = 0; u < kBatch; u++) {
-            const uint32_t s = s0 + u * kMmaWarps;
-            const size_t off = (size_t)s * (16u * BITS);
-            if (s < nspans) {
-                if (BITS == 2) {
-                    const uint2 va = __ldg(reinterpret_cast<const uint2 *>(pa + off)), vb = __ldg(reinterpret_cast<const uint2 *>(pb + off));
-                    wa[u][0] = va.x; wa[u][1] = va.y; wb[u][0] = vb.x; wb[u][1] = vb.y;
-                } else {
-#pragma unroll
-                    for (int h = 0; h < kWords / 4; h++) {
-                        const uint4 va = __ldg(reinterpret_cast<const uint4 *>(pa + off) + h), vb = __ldg(reinterpret_cast<const uint4 *>(pb + off) + h);
-                        wa[u][4 * h] = va.x; wa[u][4 * h + 1] = va.y; wa[u][4 * h + 2] = va.z; wa[u][4 * h + 3] = va.w;
-                        wb[u][4 * h] = vb.x; wb[u][4 * h + 1] = vb.y; wb[u][4 * h + 2] = vb.z; wb[u][4 * h + 3] = vb.w;
-                    }
-                }
-                const uint32_t gi = (s << 7) / a.group;
-                sca[u] = half_bits_to_float(__ldg(sa + gi)); scb[u] = half_bits_to_float(__ldg(sb + gi));
-            }
-        }
-        if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
-#pragma unroll
-        for (int u = 0; u < kBatch; u++) {
-            const uint32_t s = s0 + u * kMmaWarps;
-            if (s >= nspans) break;
-            // the codes of both rows as signed 16-bit floats, in the order they come out of the words
-            uint32_t ha[16], hb[16];
-#pragma unroll
-            for (int j = 0; j < kWords; j++) {
-                if (BITS == 4) {
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        ha[4 * j + i] = codes_to_pair<BF16>(wa[u][j] >> (4 * i), 0x000F000Fu, 7u);      // columns 8j + i and 8j + i + 4
-                        hb[4 * j + i] = codes_to_pair<BF16>(wb[u][j] >> (4 * i), 0x000F000Fu, 7u);
-                    }
-                } else if (BITS == 2) {
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        ha[8 * j + i] = codes_to_pair<BF16>(wa[u][j] >> (2 * i), 0x00030003u, 1u);      // columns 16j + i and 16j + i + 8
-                        hb[8 * j + i] = codes_to_pair<BF16>(wb[u][j] >> (2 * i), 0x00030003u, 1u);
-                    }
-                } else {
-                    // signed bytes: u = code + 128 in the low byte of each half under 0x64, i.e. 1024 + u; columns 4j + 2i, + 1
-#pragma unroll
-                    for (int i = 0; i < 2; i++) {
-                        ha[2 * j + i] = codes_to_pair<BF16>(__byte_perm(wa[u][j] ^ 0x80808080u, 0u, i ? 0x4342u : 0x4140u), 0x00FF00FFu, 128u);
-                        hb[2 * j + i] = codes_to_pair<BF16>(__byte_perm(wb[u][j] ^ 0x80808080u, 0u, i ? 0x4342u : 0x4140u), 0x00FF00FFu, 128u);
-                    }
-                }
-            }
-#pragma unroll
-            for (int n = 0; n < NB; n++) {
-                uint32_t q[16];
-                if (has_x[n]) {
-#pragma unroll
-                    for (int h = 0; h < 4; h++) {
-                        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(xr[n] + ((size_t)s << 7)) + h);
-                        q[4 * h] = v.x; q[4 * h + 1] = v.y; q[4 * h + 2] = v.z; q[4 * h + 3] = v.w;
-                    }
-                } else {
-#pragma unroll
-                    for (int h = 0; h < 16; h++) q[h] = 0u;
-                }
-                // the activations in the weights' order: register i of the 16 holds the two columns that ha[i] holds
-                uint32_t xp[16];
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    if (BITS == 4) {            // j = i / 4, columns 8j + (i & 3) and + 4: halves of q[4j + (i & 3) / 2] and q[4j + 2 + (i & 3) / 2]
-                        const int j = i >> 2, k = (i & 3) >> 1;
-                        xp[i] = __byte_perm(q[4 * j + k], q[4 * j + 2 + k], (i & 1) ? 0x7632u : 0x5410u);
-                    } else if (BITS == 2) {     // j = i / 8, columns 16j + (i & 7) and + 8
-                        const int j = i >> 3, k = (i & 7) >> 1;
-                        xp[i] = __byte_perm(q[8 * j + k], q[8 * j + 4 + k], (i & 1) ? 0x7632u : 0x5410u);
-                    } else {
-                        xp[i] = q[i];
-                    }
-                }
-                float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-                for (int m = 0; m < 8; m++)
-                    mma_m16n8k16<BF16>(c, ha[2 * m], hb[2 * m], ha[2 * m + 1], hb[2 * m + 1], xp[2 * m], xp[2 * m + 1]);
-                tot[n][0] = fmaf(sca[u], c[0], tot[n][0]); tot[n][1] = fmaf(sca[u], c[1], tot[n][1]);
-                tot[n][2] = fmaf(scb[u], c[2], tot[n][2]); tot[n][3] = fmaf(scb[u], c[3], tot[n][3]);
-            }
-        }
+    uint32_t wc[kRows][BITS], wn[kRows][BITS];
+    uint16_t scc[kRows], scn[kRows];
+    load_span(warp, wc, scc);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (uint32_t s = warp; s < nspans; s += 2u * nwarps) {
+        load_span(s + nwarps, wn, scn);
+        compute_span(s, wc, scc);
+        if (s + nwarps >= nspans) break;
+        load_span(s + 2u * nwarps, wc, scc);
+        compute_span(s + nwarps, wn, scn);
     }
-    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
 #pragma unroll
     for (int n = 0; n < NB; n++) {
         red[warp][n][g][2 * t] = tot[n][0]; red[warp][n][g][2 * t + 1] = tot[n][1];
         red[warp][n][g + 8][2 * t] = tot[n][2]; red[warp][n][g + 8][2 * t + 1] = tot[n][3];
     }
     __syncthreads();
-    for (uint32_t i = threadIdx.x; i < NB * 128u; i += kMmaWarps * 32u) {
+    for (uint32_t i = threadIdx.x; i < NB * 128u; i += blockDim.x) {
         const uint32_t n = i >> 7, r = (i >> 3) & 15u, b = 8u * n + (i & 7u), row = row0 + r;
         float v = 0.0f;
-#pragma unroll
-        for (int w = 0; w < kMmaWarps; w++) v += red[w][n][r][i & 7u];
+        for (uint32_t w = 0; w < nwarps; w++) v += red[w][n][r][i & 7u];
         if (row < a.N && b < a.batch) store_y(a.y, (size_t)b * a.N + row, v + (a.bias ? __ldg(a.bias + row) : 0.0f), a.y_dtype);
     }
 }
@@ -3116,6 +3151,9 @@ __global__ void __launch_bounds__(kMmaWarps * 32) gemv_packed_mma_kernel(const P
 // multiple of 8, packed rows 16-byte aligned: checked by the caller.
 // Activation rows one launch takes: 32 on the tensor-core form (16-bit activations, 16-byte aligned, against scale
 // groups of whole 128-column spans; byte codes only with fp16), 8 otherwise.
+static std::atomic<int> g_packed_warps{0};              // 0 = by shape; "packed_warps" in eoq_b200_tune
+void set_packed_warps(int v) { g_packed_warps.store(v == 4 || v == 8 || v == 16 ? v : 0); }
+
 uint32_t gemv_packed_rows(const PackedGemvArgs &a)
 {
     const bool byte_codes = a.bits != 2 && a.bits != 4;
@@ -3128,13 +3166,20 @@ int launch_gemv_packed(const PackedGemvArgs &a, void *stream)
 {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     if (gemv_packed_rows(a) > 8u) {
-        const uint32_t tiles = (a.N + 15u) / 16u;
+        // warps per CTA (they share the tile's spans): 16 where the row is long enough to give each two spans and the
+        // registers of the form in use let two such CTAs share an SM (measured on 11008 x 4096 and 4096 x 11008 at
+        // 2 and 4 bits: 21.6 us for the pair against 25.3 with 8), else 8, 4 for short rows
+        const uint32_t tiles = (a.N + 15u) / 16u, nspans = a.K >> 7;
+        const bool slim = (a.bits == 2 || a.bits == 4) && a.batch <= 8u;
+        uint32_t warps = nspans >= 32u && slim ? 16u : nspans >= 16u ? 8u : 4u;
+        if (g_packed_warps.load()) warps = (uint32_t)g_packed_warps.load();
+        if (a.bits != 2 && a.bits != 4) warps = std::min(warps, 8u);         // the byte-code kernels are built for 256 threads
         cudaError_t e = cudaSuccess;
 #define EOQ_LAUNCH_MMA(B, H)                                                                                             \
     do {                                                                                                                 \
-        if (a.batch <= 8) e = launch_with_pdl(gemv_packed_mma_kernel<B, H, 1>, dim3(tiles), dim3(kMmaWarps * 32), 0, st, a);                          \
-        else if (a.batch <= 16) e = launch_with_pdl(gemv_packed_mma_kernel<B, H, 2>, dim3(tiles), dim3(kMmaWarps * 32), 0, st, a);                    \
-        else e = launch_with_pdl(gemv_packed_mma_kernel<B, H, 4>, dim3(tiles), dim3(kMmaWarps * 32), 0, st, a);                                       \
+        if (a.batch <= 8) e = launch_with_pdl(gemv_packed_mma_kernel<B, H, 1>, dim3(tiles), dim3(warps * 32u), 0, st, a); \
+        else if (a.batch <= 16) e = launch_with_pdl(gemv_packed_mma_kernel<B, H, 2>, dim3(tiles), dim3(warps * 32u), 0, st, a); \
+        else e = launch_with_pdl(gemv_packed_mma_kernel<B, H, 4>, dim3(tiles), dim3(warps * 32u), 0, st, a);             \
     } while (0)
         const bool bf = a.x_dtype == EOQ_B200_BF16;
         if (a.bits == 4) { if (bf) EOQ_LAUNCH_MMA(4, true); else EOQ_LAUNCH_MMA(4, false); }
