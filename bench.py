@@ -840,6 +840,29 @@ def measure_llama_step(world, rank, steps, gather, with_fp16):
             "gathers_per_step": 0 if world == 1 else 4 * L + 1 + L,
             "algorithmic_weight_bytes_per_step": alg_step, "weight_gbs": alg_step / (ms * 1e-3) / 1e9}
     if with_fp16:
+        # the same step on the codes as QuantizedLinear keeps them (packed INT4 + fp16 scales, no entropy coding: 4.125
+        # bit/weight resident instead of ~3.7), multiplied straight from the packed form; one copy per layer
+        from eoq_quantization_b200.fused import gemv_packed
+        packed = {}
+        for i, (name, (n, k)) in enumerate(list(shapes.items()) + [("head", (V, H))]):
+            sym, scales = make_layer(n, k, 20 if name == "head" else 10 + i)
+            u = torch.from_numpy(sym).cuda()
+            pk = (u[:, 0::2] | (u[:, 1::2] << 4)).contiguous()
+            sc = torch.from_numpy(scales).cuda()
+            packed[name] = ([pk.clone() for _ in range(1 if name == "head" else L)], sc, n, k)
+            del u, pk
+
+        def lin_packed(name, i, x):
+            pks, sc, n, k = packed[name]
+            return gemv_packed(pks[i], sc, n, k, 4, GROUP, x)
+        y_eoq, y_pk = step(x0, lin_eoq), step(x0, lin_packed)
+        err = float((y_eoq.float() - y_pk.float()).norm() / y_eoq.float().norm())
+        assert err < 2e-2, f"packed and entropy-coded steps disagree: {err}"      # same weights, fp16 hand-offs between 129 linears
+        msp, _ = timed(lambda: step(x0, lin_packed), steps)
+        line["packed_int4_ms_per_step"] = msp
+        line["packed_int4_tokens_per_s"] = 1e3 / msp
+        line["packed_vs_entropy_coded_rel_l2"] = err
+        del packed
         # dense fp16 comparator: same step, weights as fp16 matrices (one copy per layer)
         del layers
         torch.cuda.empty_cache()
@@ -852,6 +875,7 @@ def measure_llama_step(world, rank, steps, gather, with_fp16):
         line["fp16_dense_ms_per_step"] = ms16
         line["fp16_dense_tokens_per_s"] = 1e3 / ms16
         line["speedup_vs_fp16_dense"] = ms16 / ms
+        line["packed_int4_speedup_vs_fp16_dense"] = ms16 / line["packed_int4_ms_per_step"]
         del dense, dhead
     if pg is not None:
         pg.close()
