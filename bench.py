@@ -631,6 +631,47 @@ def run_aux(args):
                 per_b[f"batch{batch}"] = {"us_per_step": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peak,
                                           "bytes_per_step": nbytes, "rel_l2_vs_dequantise_then_matmul": err}
             res[f"int{bits}"] = per_b
+        # beyond 32 rows the modules dequantise the packed codes to a 16-bit matrix and call a library GEMM: the
+        # dequantisation alone (4-bit, both layers, fp16 out) and the pair at 64 and 256 rows
+        from eoq_quantization_b200.fused import dequant_packed
+        lay4 = []
+        for li, (n, k) in enumerate(shapes):
+            pk = torch.randint(0, 255, (n, k // 2), dtype=torch.uint8, device="cuda")
+            lay4.append((n, k, [pk.clone() for _ in range(copies)], (torch.rand(n * k // GROUP, device="cuda") * 0.01).half()))
+        deq = {}
+        for rows in (0, 64, 256):
+            xs = [torch.randn(max(rows, 1), k, device="cuda").half() for (_, k) in shapes]
+            i = [0]
+
+            def dstep():
+                c = i[0] % copies
+                i[0] += 1
+                for (n, k, pks, sc), x in zip(lay4, xs):
+                    wd = dequant_packed(pks[c], sc, n, k, 4, GROUP, dtype=torch.float16)
+                    if rows:
+                        torch.nn.functional.linear(x, wd)
+            for _ in range(3):
+                dstep()
+            torch.cuda.synchronize()
+            gq = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                i[0] = 0
+                with torch.cuda.graph(gq):
+                    for _ in range(copies):
+                        dstep()
+            torch.cuda.synchronize()
+            deq["dequantise_only_us" if rows == 0 else f"dequantise_then_gemm_{rows}_rows_us"] = timed(gq.replay, max(3, args.steps // copies)) / copies * 1e3
+        deq["dequantised_bytes_written"] = sum(n * k * 2 for (n, k) in shapes)
+        lib.eoq_b200_tune(b"dequant_vec", 0)                           # the general (any shape) kernel on the same layers
+        xs, i[0] = [torch.randn(1, k, device="cuda").half() for (_, k) in shapes], 0
+        rows = 0
+        for _ in range(3):
+            dstep()
+        torch.cuda.synchronize()
+        deq["dequantise_only_general_kernel_us"] = timed(dstep, 16) * 1e3
+        lib.eoq_b200_tune(b"dequant_vec", 1)
+        del lay4
         # comparators on the 4-bit layers: dense fp16 GEMV (torch) and the entropy-coded fused GEMV
         xs = [torch.randn(1, k, device="cuda").half() for (_, k) in shapes]
         dense16 = [[torch.randn(n, k, device="cuda", dtype=torch.float16) for _ in range(4)] for (n, k) in shapes]
@@ -660,7 +701,7 @@ def run_aux(args):
                 "value": res["int4"]["batch1"]["gbs"], "ms_per_step": res["int4"]["batch1"]["us_per_step"] / 1e3,
                 "roofline": {"bound": "hbm", "kernel": "gemv_packed_mma_kernel<4,fp16,1>", "achieved": res["int4"]["batch1"]["gbs"], "peak": peak,
                              "unit": "GB/s", "frac": res["int4"]["batch1"]["frac_of_hbm_peak"], "peak_source": peak_src, "traffic": None},
-                "per_width": res, "fp16_dense_us_per_step": dense_us}
+                "per_width": res, "beyond_32_rows_int4": deq, "fp16_dense_us_per_step": dense_us}
         print(json.dumps(line), flush=True)
         return
 

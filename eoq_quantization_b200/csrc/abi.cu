@@ -1496,6 +1496,7 @@ extern "C" int eoq_b200_tune(const char *key, int value)
     if (std::strcmp(key, "gemv_pairs") == 0) { set_gemv_pairs(value); return 0; }
     if (std::strcmp(key, "v1_lanes") == 0) { set_v1_lanes(value); return 0; }
     if (std::strcmp(key, "packed_warps") == 0) { set_packed_warps(value); return 0; }
+    if (std::strcmp(key, "dequant_vec") == 0) { set_dequant_vec(value); return 0; }
     return -1;
 }
 

@@ -216,6 +216,7 @@ struct PackedGemvArgs {
 };
 uint32_t gemv_packed_rows(const PackedGemvArgs &a);
 void set_packed_warps(int v);
+void set_dequant_vec(int v);
 int launch_gemv_packed(const PackedGemvArgs &a, void *stream);
 int launch_dequant_packed(const uint8_t *packed, const uint16_t *scales, uint32_t K, uint32_t row_bytes, uint32_t bits,
                           uint32_t group, uint32_t row_lo, uint32_t row_hi, void *out, int out_dtype, void *stream);

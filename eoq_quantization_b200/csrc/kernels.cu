@@ -2794,11 +2794,93 @@ __global__ void dequant_packed_kernel(const uint8_t *__restrict__ packed, const 
     }
 }
 
+static std::atomic<int> g_dequant_vec{1};               // "dequant_vec" = 0 in eoq_b200_tune: the general kernel for every shape
+void set_dequant_vec(int v) { g_dequant_vec.store(v != 0); }
+
+// The same for float outputs when K and the group are multiples of 8 and the buffers are aligned: a thread takes the
+// eight columns of one 4-byte word of nibbles (2 bytes of 2-bit codes, 8 signed bytes), which share a scale, and writes
+// them with one 16-byte store (two for fp32), so a warp reads 128 contiguous bytes and writes 512.  A code becomes a
+// float by one logic operation and one exact subtraction (the code in the low mantissa bits of 2^23); the product
+// with the scale is the reference's fp32 product, rounded once to the output type.
+template <int BITS>
+__global__ void __launch_bounds__(256) dequant_packed_vec_kernel(const uint8_t *__restrict__ packed, const uint16_t *__restrict__ scales,
+                                                                 uint32_t K, uint32_t row_bytes, uint32_t group, uint32_t row_lo,
+                                                                 uint32_t nrows, void *__restrict__ out, int out_dtype)
+{
+    // blockIdx.x, threadIdx.x: the eight-column piece of the row; blockIdx.y (strided): the row.  No division but the
+    // one that finds the scale (the groups run over the flattened matrix; whole groups per row in the common case).
+    const uint32_t kpieces = K >> 3, piece = blockIdx.x * blockDim.x + threadIdx.x, c = piece << 3;
+    if (piece >= kpieces) return;
+    const uint32_t per_row = K % group == 0 ? K / group : 0u, cg = c / group;
+    constexpr int kR = 4;                                          // rows per trip: their loads are in flight together
+    for (uint32_t r0 = blockIdx.y * kR; r0 < nrows; r0 += gridDim.y * kR) {
+        uint32_t w[kR][2];
+        uint16_t sb[kR];
+#pragma unroll
+        for (int j = 0; j < kR; j++) {
+            if (r0 + j < nrows) {
+                const uint32_t r = row_lo + r0 + j;
+                const uint8_t *src = packed + (size_t)r * row_bytes;
+                const uint64_t si = per_row ? (uint64_t)r * per_row + cg : ((uint64_t)r * K + c) / group;
+                sb[j] = __ldg(scales + si);
+                if (BITS == 4) w[j][0] = __ldg(reinterpret_cast<const uint32_t *>(src + (c >> 1)));
+                else if (BITS == 2) w[j][0] = __ldg(reinterpret_cast<const uint16_t *>(src + (c >> 2)));
+                else { const uint2 v2 = __ldg(reinterpret_cast<const uint2 *>(src + c)); w[j][0] = v2.x; w[j][1] = v2.y; }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kR; j++) {
+            if (r0 + j >= nrows) break;
+            const uint64_t p = (uint64_t)(r0 + j) * kpieces + piece;
+            const float s = half_bits_to_float(sb[j]);
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                // the code in the low mantissa bits of 2^23, minus 2^23 + its offset (7, 1; signed bytes: code + 128 after the XOR)
+                if (BITS == 4) v[i] = (__uint_as_float(0x4B000000u | ((w[j][0] >> (4 * i)) & 15u)) - 8388615.0f) * s;
+                else if (BITS == 2) v[i] = (__uint_as_float(0x4B000000u | ((w[j][0] >> (2 * i)) & 3u)) - 8388609.0f) * s;
+                else v[i] = (__uint_as_float(0x4B000000u | ((((i < 4 ? w[j][0] : w[j][1]) >> (8 * (i & 3))) & 255u) ^ 128u)) - 8388736.0f) * s;
+            }
+            if (out_dtype == EOQ_B200_F32) {
+                float4 *dst = reinterpret_cast<float4 *>(out) + 2 * p;
+                dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+                dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+            } else {
+                uint4 o;
+                uint32_t *q = &o.x;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    if (out_dtype == EOQ_B200_F16) {
+                        const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+                        q[i] = *reinterpret_cast<const uint32_t *>(&h);
+                    } else {
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                        q[i] = *reinterpret_cast<const uint32_t *>(&h);
+                    }
+                }
+                reinterpret_cast<uint4 *>(out)[p] = o;
+            }
+        }
+    }
+}
+
 int launch_dequant_packed(const uint8_t *packed, const uint16_t *scales, uint32_t K, uint32_t row_bytes, uint32_t bits,
                           uint32_t group, uint32_t row_lo, uint32_t row_hi, void *out, int out_dtype, void *stream)
 {
     const uint64_t count = (uint64_t)(row_hi - row_lo) * K;
     if (count == 0) return 0;
+    const uint32_t word = bits == 4 ? 4u : bits == 2 ? 2u : 8u;                  // bytes that hold eight codes
+    if (g_dequant_vec.load() && out_dtype != EOQ_B200_I8 && K % 8u == 0 && group % 8u == 0 && row_bytes % word == 0 &&
+        (reinterpret_cast<uintptr_t>(packed) & (word - 1u)) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0) {
+        const uint32_t nrows = row_hi - row_lo;
+        const dim3 vgrid((K / 8u + 255u) / 256u, std::min((nrows + 3u) / 4u, 65535u));
+        cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+        if (bits == 4) dequant_packed_vec_kernel<4><<<vgrid, 256, 0, st>>>(packed, scales, K, row_bytes, group, row_lo, nrows, out, out_dtype);
+        else if (bits == 2) dequant_packed_vec_kernel<2><<<vgrid, 256, 0, st>>>(packed, scales, K, row_bytes, group, row_lo, nrows, out, out_dtype);
+        else dequant_packed_vec_kernel<8><<<vgrid, 256, 0, st>>>(packed, scales, K, row_bytes, group, row_lo, nrows, out, out_dtype);
+        g_launches++;
+        return (int)cudaGetLastError();
+    }
     const uint32_t grid = (uint32_t)std::min<uint64_t>((count + 255) / 256, (uint64_t)device_sm_count() * 16);
     dequant_packed_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(packed, scales, K, row_bytes, bits, group,
                                                                                      row_lo, count, out, out_dtype);

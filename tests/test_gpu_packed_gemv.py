@@ -6,7 +6,7 @@ import torch
 
 from eoq_quantization_b200 import _lib as L
 from eoq_quantization_b200.core.quantized_linear import QuantizedLinear
-from eoq_quantization_b200.fused import gemv_packed, packed_gemv_applies, packed_gemv_rows
+from eoq_quantization_b200.fused import dequant_packed, gemv_packed, packed_gemv_applies, packed_gemv_rows
 from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -87,3 +87,26 @@ def test_quantized_linear_forward_takes_the_packed_route_for_few_rows():
     x = torch.from_numpy(rng.standard_normal((2, 100)).astype(np.float32)).cuda()
     want = x.double().cpu().numpy() @ odd._dequantize_weight().double().cpu().numpy().T
     assert O.rel_l2(odd(x).double().cpu().numpy(), want) < 1e-5
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 8])
+@pytest.mark.parametrize("n,k,group", [(37, 256, 128), (64, 200, 80), (5, 4096, 128), (33, 100, 50), (300, 1536, 64)])
+def test_dequantised_rows_of_packed_codes_are_the_reference_product(bits, n, k, group):
+    """`dequant_packed` (core/quantized_linear.py:189-217: codes.float() * scales.float(), scales indexed over the
+    flattened matrix, so groups may straddle rows): bit-exact in fp32, rounded once for 16-bit outputs; the vector
+    form (K and group multiples of 8) and the general form, whole matrices and row ranges."""
+    rng = np.random.default_rng(bits + n + k)
+    qmax = (1 << (bits - 1)) - 1
+    codes = rng.integers(-qmax, qmax + 1, size=(n, k)).astype(np.int64)
+    s16 = (rng.random(n * k // group).astype(np.float32) * 0.05 + 1e-3).astype(np.float16)
+    want = (codes.reshape(-1, group).astype(np.float32) * s16.astype(np.float32)[:, None]).reshape(n, k)
+    packed = torch.from_numpy(_pack(codes, bits)).cuda()
+    sc = torch.from_numpy(s16).cuda()
+    for lo, hi in ((0, n), (n // 3, n - 1)):
+        got = dequant_packed(packed, sc, n, k, bits, group, lo, hi)
+        assert got.dtype == torch.float32 and np.array_equal(got.cpu().numpy(), want[lo:hi])
+        for dt in (torch.float16, torch.bfloat16):
+            got = dequant_packed(packed, sc, n, k, bits, group, lo, hi, dtype=dt)
+            assert torch.equal(got.cpu(), torch.from_numpy(want[lo:hi]).to(dt))
+        got = dequant_packed(packed, None, n, k, bits, group, lo, hi, dtype=torch.int8)
+        assert np.array_equal(got.cpu().numpy(), codes[lo:hi].astype(np.int8))
