@@ -3099,10 +3099,21 @@ __device__ __forceinline__ void unpack_span(const uint32_t (&w)[BITS], uint32_t 
                     h[8 * j + 4 * half + 3] = scaled_pair<false>(u, 0x00C000C0u, 0x2400u, 0xCC40u);   // / 64 - 17
                 }
             }
-        } else {                        // signed bytes: u = code + 128 under 0x64 is 1024 + u; register 2j + i: columns 4j + 2i, + 1
+        } else if (!BF16) {             // signed bytes: u = code + 128 under 0x64 is 1024 + u; register 2j + i: columns 4j + 2i, + 1
 #pragma unroll
             for (int i = 0; i < 2; i++)
-                h[2 * j + i] = codes_to_pair<BF16>(__byte_perm(w[j] ^ 0x80808080u, 0u, i ? 0x4342u : 0x4140u), 0x00FF00FFu, 128u);
+                h[2 * j + i] = codes_to_pair<false>(__byte_perm(w[j] ^ 0x80808080u, 0u, i ? 0x4342u : 0x4140u), 0x00FF00FFu, 128u);
+        } else {
+            // 128 + u needs nine significant bits, a bf16 has eight: the byte goes under 0x4B (2^23 + u as an fp32), one
+            // exact subtraction gives the code, and two codes are packed into a bf16 pair (|code| <= 128: exact)
+            const uint32_t u = w[j] ^ 0x80808080u;
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540u | (2 * i))) - 8388736.0f;
+                const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540u | (2 * i + 1))) - 8388736.0f;
+                const __nv_bfloat162 b = __floats2bfloat162_rn(f0, f1);
+                h[2 * j + i] = *reinterpret_cast<const uint32_t *>(&b);
+            }
         }
     }
 }
@@ -3114,7 +3125,7 @@ __device__ const uint4 kZeroBlock[4] = {};
 template <int BITS, bool BF16, int NB>
 __global__ void __launch_bounds__(BITS == 8 ? 256 : 512, NB > 1 ? 1 : BITS == 8 ? 3 : 2) gemv_packed_mma_kernel(const PackedGemvArgs a)
 {
-    static_assert(BITS == 2 || BITS == 4 || (BITS == 8 && !BF16), "byte codes + 128 do not fit a bf16 mantissa");
+    static_assert(BITS == 2 || BITS == 4 || BITS == 8, "two or four bits packed, or one code per byte");
     constexpr int kRows = 2;                                       // a lane's weight rows: g and g + 8 of the tile
     __shared__ float red[kMmaMaxWarps][NB][16][8];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5, g = lane >> 2, t = lane & 3u;
@@ -3232,15 +3243,13 @@ __global__ void __launch_bounds__(BITS == 8 ? 256 : 512, NB > 1 ? 1 : BITS == 8 
 // K a multiple of the group and of the columns in sixteen bytes (32 nibbles, 64 two-bit codes, 16 bytes), the group a
 // multiple of 8, packed rows 16-byte aligned: checked by the caller.
 // Activation rows one launch takes: 32 on the tensor-core form (16-bit activations, 16-byte aligned, against scale
-// groups of whole 128-column spans; byte codes only with fp16), 8 otherwise.
+// groups of whole 128-column spans), 8 otherwise.
 static std::atomic<int> g_packed_warps{0};              // 0 = by shape; "packed_warps" in eoq_b200_tune
 void set_packed_warps(int v) { g_packed_warps.store(v == 4 || v == 8 || v == 16 ? v : 0); }
 
 uint32_t gemv_packed_rows(const PackedGemvArgs &a)
 {
-    const bool byte_codes = a.bits != 2 && a.bits != 4;
-    const bool tensor = a.x_dtype != EOQ_B200_F32 && a.K % 128u == 0 && a.group % 128u == 0 &&
-                        !(byte_codes && a.x_dtype == EOQ_B200_BF16) && (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0;
+    const bool tensor = a.x_dtype != EOQ_B200_F32 && a.K % 128u == 0 && a.group % 128u == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0;
     return tensor ? 32u : 8u;
 }
 
@@ -3266,7 +3275,7 @@ int launch_gemv_packed(const PackedGemvArgs &a, void *stream)
         const bool bf = a.x_dtype == EOQ_B200_BF16;
         if (a.bits == 4) { if (bf) EOQ_LAUNCH_MMA(4, true); else EOQ_LAUNCH_MMA(4, false); }
         else if (a.bits == 2) { if (bf) EOQ_LAUNCH_MMA(2, true); else EOQ_LAUNCH_MMA(2, false); }
-        else EOQ_LAUNCH_MMA(8, false);
+        else { if (bf) EOQ_LAUNCH_MMA(8, true); else EOQ_LAUNCH_MMA(8, false); }
 #undef EOQ_LAUNCH_MMA
         g_launches++;
         return (int)e;

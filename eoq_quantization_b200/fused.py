@@ -307,11 +307,10 @@ def dequant_packed(packed: torch.Tensor, scales: torch.Tensor, rows: int, cols: 
 
 def packed_gemv_rows(cols: int, bits: int, group: int, dtype: torch.dtype = torch.float16) -> int:
     """Activation rows `gemv_packed` takes for this shape: 32 on its tensor-core form (16-bit activations against
-    scale groups of whole 128-column spans; byte codes only with fp16), 8 on the general form, 0 if it does not apply."""
+    scale groups of whole 128-column spans), 8 on the general form, 0 if it does not apply."""
     if not (2 <= bits <= 8 and group > 0 and cols % group == 0):
         return 0
-    byte_codes = bits not in (2, 4)
-    if dtype in (torch.float16, torch.bfloat16) and cols % 128 == 0 and group % 128 == 0 and not (byte_codes and dtype == torch.bfloat16):
+    if dtype in (torch.float16, torch.bfloat16) and cols % 128 == 0 and group % 128 == 0:
         return PACKED_TENSOR_ROWS
     per16 = 32 if bits == 4 else 64 if bits == 2 else 16                 # codes in the sixteen bytes a lane loads
     return 8 if cols % per16 == 0 and group % 8 == 0 else 0

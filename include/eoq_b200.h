@@ -439,7 +439,7 @@ eoq_error_t eoq_b200_dequant_packed(const uint8_t *d_packed, const uint16_t *d_s
  * of 8 and d_packed 16-byte aligned (EOQ_ERR_UNSUPPORTED otherwise: use
  * eoq_b200_dequant_packed and a GEMM).  x [batch, cols] and y [batch, rows] in
  * EOQ_B200_F16 / BF16 / F32; device pointers; asynchronous.  With 16-bit
- * activations (16-byte aligned; fp16 only for byte codes), cols a multiple of
+ * activations (16-byte aligned), cols a multiple of
  * 128 and the group a multiple of 128 the product runs on the tensor cores and
  * takes up to 32 rows; more rows than the form in use takes: EOQ_ERR_UNSUPPORTED. */
 eoq_error_t eoq_b200_gemv_packed(const uint8_t *d_packed, const uint16_t *d_scales_fp16, uint32_t rows, uint32_t cols,

@@ -39,7 +39,7 @@ def test_packed_gemv_matches_dequantise_then_matmul(bits, n, k, group):
     for dt in (torch.float16, torch.bfloat16, torch.float32):
         # 32 rows on the tensor-core form (16-bit activations, groups of whole 128-column spans), 8 on the general one
         most = packed_gemv_rows(k, bits, group, dt)
-        assert most == (32 if dt != torch.float32 and group % 128 == 0 and not (bits not in (2, 4) and dt == torch.bfloat16) else 8)
+        assert most == (32 if dt != torch.float32 and group % 128 == 0 else 8)
         for rows in (1, 2, 3, 4, 7, 8, 9, 16, 17, 32):
             x = torch.from_numpy(rng.standard_normal((rows, k)).astype(np.float32)).cuda().to(dt)
             if rows > most:
