@@ -3044,6 +3044,18 @@ __device__ __forceinline__ void mma_m16n8k16(float (&c)[4], uint32_t a0, uint32_
                      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// the first instruction of a chain: D = A * B + 0 (the zeros are operands, not four registers to clear)
+template <bool BF16>
+__device__ __forceinline__ void mma_m16n8k16_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    if (BF16)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                     : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+    else
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                     : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
 // two codes, already sitting in the low bits of the two halves of v, to two exact signed 16-bit floats
 template <bool BF16>
 __device__ __forceinline__ uint32_t codes_to_pair(uint32_t v, uint32_t mask, uint32_t q)
@@ -3199,9 +3211,11 @@ __global__ void __launch_bounds__(BITS == 8 ? 256 : 512, NB > 1 ? 1 : BITS == 8 
                 }
             }
             // two accumulators: consecutive instructions do not wait for one another
-            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f}, d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float c[4], d[4];
+            mma_m16n8k16_first<BF16>(c, h0[0], h1[0], h0[1], h1[1], xp[0], xp[1]);
+            mma_m16n8k16_first<BF16>(d, h0[2], h1[2], h0[3], h1[3], xp[2], xp[3]);
 #pragma unroll
-            for (int m = 0; m < 8; m += 2) {
+            for (int m = 2; m < 8; m += 2) {
                 mma_m16n8k16<BF16>(c, h0[2 * m], h1[2 * m], h0[2 * m + 1], h1[2 * m + 1], xp[2 * m], xp[2 * m + 1]);
                 mma_m16n8k16<BF16>(d, h0[2 * m + 2], h1[2 * m + 2], h0[2 * m + 3], h1[2 * m + 3], xp[2 * m + 2], xp[2 * m + 3]);
             }
