@@ -3130,8 +3130,8 @@ __device__ __forceinline__ void unpack_span(const uint32_t (&w)[BITS], uint32_t 
     }
 }
 
-// The next span's weights and scales are requested before this span's are consumed (two register sets, used
-// alternately).  Lanes whose activation row does not exist read zeros from a constant block instead of branching.
+// The weights and scales of the next kDepth - 1 spans are requested before this span's are consumed (register sets in
+// rotation).  Lanes whose activation row does not exist read zeros from a constant block instead of branching.
 __device__ const uint4 kZeroBlock[4] = {};
 
 template <int BITS, bool BF16, int NB>
@@ -3139,6 +3139,7 @@ __global__ void __launch_bounds__(BITS == 8 ? 256 : 512, NB > 1 ? 1 : BITS == 8 
 {
     static_assert(BITS == 2 || BITS == 4 || BITS == 8, "two or four bits packed, or one code per byte");
     constexpr int kRows = 2;                                       // a lane's weight rows: g and g + 8 of the tile
+    constexpr int kDepth = 2;                                      // register sets of weights: kDepth - 1 spans requested ahead
     __shared__ float red[kMmaMaxWarps][NB][16][8];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5, g = lane >> 2, t = lane & 3u;
     const uint32_t row0 = blockIdx.x * 16u;
@@ -3228,16 +3229,19 @@ __global__ void __launch_bounds__(BITS == 8 ? 256 : 512, NB > 1 ? 1 : BITS == 8 
     // The weights and scales do not depend on the kernel before this one in the stream, the activations may: the
     // first span's weight loads are in flight before the dependency wait (programmatic dependent launch).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    uint32_t wc[kRows][BITS], wn[kRows][BITS];
-    uint16_t scc[kRows], scn[kRows];
-    load_span(warp, wc, scc);
+    uint32_t wbuf[kDepth][kRows][BITS];
+    uint16_t sbuf[kDepth][kRows];
+#pragma unroll
+    for (int d = 0; d < kDepth - 1; d++) load_span(warp + d * nwarps, wbuf[d], sbuf[d]);
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    for (uint32_t s = warp; s < nspans; s += 2u * nwarps) {
-        load_span(s + nwarps, wn, scn);
-        compute_span(s, wc, scc);
-        if (s + nwarps >= nspans) break;
-        load_span(s + 2u * nwarps, wc, scc);
-        compute_span(s + nwarps, wn, scn);
+    for (uint32_t s = warp; s < nspans; s += kDepth * nwarps) {
+#pragma unroll
+        for (int d = 0; d < kDepth; d++) {                          // register sets in rotation: every index below is static
+            const uint32_t sd = s + d * nwarps;
+            if (sd >= nspans) break;
+            load_span(sd + (kDepth - 1) * nwarps, wbuf[(d + kDepth - 1) % kDepth], sbuf[(d + kDepth - 1) % kDepth]);
+            compute_span(sd, wbuf[d], sbuf[d]);
+        }
     }
 #pragma unroll
     for (int n = 0; n < NB; n++) {
@@ -3259,7 +3263,42 @@ __global__ void __launch_bounds__(BITS == 8 ? 256 : 512, NB > 1 ? 1 : BITS == 8 
 // Activation rows one launch takes: 32 on the tensor-core form (16-bit activations, 16-byte aligned, against scale
 // groups of whole 128-column spans), 8 otherwise.
 static std::atomic<int> g_packed_warps{0};              // 0 = by shape; "packed_warps" in eoq_b200_tune
-void set_packed_warps(int v) { g_packed_warps.store(v == 4 || v == 8 || v == 16 ? v : 0); }
+void set_packed_warps(int v) { g_packed_warps.store(v >= 1 && v <= 16 ? v : 0); }
+
+// Warps per CTA of the tensor-core form (they share a tile's spans).  The CTAs are short, so a grid that needs a second,
+// partly filled round of CTAs loses that fraction of the machine: take the most warps per CTA with which the whole
+// grid is resident at once (given the registers the compiler gave this instantiation) and every warp still has two
+// spans; when no choice fits, the one with the most resident warps per SM.
+template <typename Kern>
+static cudaError_t launch_packed_mma(Kern kern, uint32_t fixed_warps, uint32_t tiles, uint32_t nspans, cudaStream_t st, const PackedGemvArgs &a)
+{
+    // byte codes and more than eight activation rows (more registers, longer spans of work per warp): 8 warps measured best
+    if (fixed_warps) {
+        const uint32_t w = g_packed_warps.load() ? std::min((uint32_t)g_packed_warps.load(), fixed_warps) : nspans >= 16u ? fixed_warps : 4u;
+        return launch_with_pdl(kern, dim3(tiles), dim3(w * 32u), 0, st, a);
+    }
+    const uint32_t max_warps = 16;
+    static std::atomic<int> regs{0};                             // per instantiation
+    if (regs.load() == 0) {
+        cudaFuncAttributes fa;
+        cudaError_t e = cudaFuncGetAttributes(&fa, kern);
+        if (e != cudaSuccess) return e;
+        regs.store(std::max(fa.numRegs, 16));
+    }
+    const uint32_t per_thread = ((uint32_t)regs.load() + 7u) & ~7u, sms = (uint32_t)device_sm_count();
+    static const uint32_t kChoices[] = {16, 12, 10, 8, 6, 5, 4};
+    uint32_t warps = 0, best_resident = 0, fallback = 4;
+    for (uint32_t w : kChoices) {
+        if (w > max_warps || (2u * w > nspans && w > 4u)) continue;
+        const uint32_t ctas = std::min(64u / w, 65536u / (per_thread * 32u * w));
+        if (ctas == 0) continue;
+        if (!warps && tiles <= sms * ctas) warps = w;
+        if (w * ctas > best_resident) { best_resident = w * ctas; fallback = w; }
+    }
+    if (!warps) warps = fallback;
+    if (g_packed_warps.load()) warps = std::min((uint32_t)g_packed_warps.load(), max_warps);
+    return launch_with_pdl(kern, dim3(tiles), dim3(warps * 32u), 0, st, a);
+}
 
 uint32_t gemv_packed_rows(const PackedGemvArgs &a)
 {
@@ -3271,20 +3310,13 @@ int launch_gemv_packed(const PackedGemvArgs &a, void *stream)
 {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     if (gemv_packed_rows(a) > 8u) {
-        // warps per CTA (they share the tile's spans): 16 where the row is long enough to give each two spans and the
-        // registers of the form in use let two such CTAs share an SM (measured on 11008 x 4096 and 4096 x 11008 at
-        // 2 and 4 bits: 21.6 us for the pair against 25.3 with 8), else 8, 4 for short rows
         const uint32_t tiles = (a.N + 15u) / 16u, nspans = a.K >> 7;
-        const bool slim = (a.bits == 2 || a.bits == 4) && a.batch <= 8u;
-        uint32_t warps = nspans >= 32u && slim ? 16u : nspans >= 16u ? 8u : 4u;
-        if (g_packed_warps.load()) warps = (uint32_t)g_packed_warps.load();
-        if (a.bits != 2 && a.bits != 4) warps = std::min(warps, 8u);         // the byte-code kernels are built for 256 threads
         cudaError_t e = cudaSuccess;
 #define EOQ_LAUNCH_MMA(B, H)                                                                                             \
     do {                                                                                                                 \
-        if (a.batch <= 8) e = launch_with_pdl(gemv_packed_mma_kernel<B, H, 1>, dim3(tiles), dim3(warps * 32u), 0, st, a); \
-        else if (a.batch <= 16) e = launch_with_pdl(gemv_packed_mma_kernel<B, H, 2>, dim3(tiles), dim3(warps * 32u), 0, st, a); \
-        else e = launch_with_pdl(gemv_packed_mma_kernel<B, H, 4>, dim3(tiles), dim3(warps * 32u), 0, st, a);             \
+        if (a.batch <= 8) e = launch_packed_mma(gemv_packed_mma_kernel<B, H, 1>, B == 8 ? 8u : 0u, tiles, nspans, st, a);  \
+        else if (a.batch <= 16) e = launch_packed_mma(gemv_packed_mma_kernel<B, H, 2>, 8u, tiles, nspans, st, a);        \
+        else e = launch_packed_mma(gemv_packed_mma_kernel<B, H, 4>, 8u, tiles, nspans, st, a);                           \
     } while (0)
         const bool bf = a.x_dtype == EOQ_B200_BF16;
         if (a.bits == 4) { if (bf) EOQ_LAUNCH_MMA(4, true); else EOQ_LAUNCH_MMA(4, false); }
