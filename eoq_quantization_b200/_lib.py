@@ -45,7 +45,7 @@ EXPORTS = [
     "eoq_b200_weight_info", "eoq_b200_gemv", "eoq_b200_gemm",
     "eoq_b200_gather_create", "eoq_b200_gather_connect", "eoq_b200_gather_destroy", "eoq_b200_gather_buffer",
     "eoq_b200_gather_status", "eoq_b200_gather_set_timeout_ms", "eoq_b200_gather_wait", "eoq_b200_gemv_gather", "eoq_b200_gemv_static_scratch", "eoq_b200_gemv_host", "eoq_b200_gemv_host_async", "eoq_b200_weight_decode",
-    "eoq_b200_dequant_packed", "eoq_b200_gemv_packed",
+    "eoq_b200_dequant_packed", "eoq_b200_gemv_packed", "eoq_b200_gemv_polar_codes",
     "eoq_b200_weight_status",
 ]
 #: exported for this project's benchmarks and tests only (declared in csrc/eoq_internal.h, not in the public header)
@@ -170,6 +170,7 @@ def lib() -> C.CDLL:
         "eoq_b200_dequant_packed": (C.c_int, [vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                               C.c_uint32, vp, C.c_int, vp]),
         "eoq_b200_gemv_packed": (C.c_int, [vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, vp, C.c_int, C.c_uint32, vp, C.c_int, vp, vp]),
+        "eoq_b200_gemv_polar_codes": (C.c_int, [vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, vp, C.c_uint32, vp, C.c_int, vp, vp]),
         "eoq_b200_weight_status": (C.c_int, [vp, vp]),
         "eoq_b200_tune": (C.c_int, [C.c_char_p, C.c_int]),
         "eoq_b200_launch_count": (C.c_uint64, []),

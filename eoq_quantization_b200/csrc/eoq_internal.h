@@ -214,6 +214,17 @@ struct PackedGemvArgs {
     uint32_t N, K, group, row_bytes, batch, bits;
     int x_dtype, y_dtype;
 };
+struct PolarCodesArgs {
+    const uint8_t *codes;       // [N][K], one centroid index per byte
+    const uint16_t *norms;      // fp16 bits, [N][K / block]
+    const float *centroids;     // [entries]
+    const float *xrot;          // [batch][K]: activations rotated per block and divided by sqrt(block)
+    void *y;                    // [batch][N]
+    const float *bias;          // [N] or null
+    uint32_t N, K, block_shift, batch, entries;
+    int y_dtype;
+};
+int launch_gemv_polar_codes(const PolarCodesArgs &a, void *stream);
 uint32_t gemv_packed_rows(const PackedGemvArgs &a);
 void set_packed_warps(int v);
 void set_dequant_vec(int v);

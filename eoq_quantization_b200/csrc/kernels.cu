@@ -3345,6 +3345,118 @@ int launch_gemv_packed(const PackedGemvArgs &a, void *stream)
 }
 
 // ---------------------------------------------------------------------------
+// GEMV straight from PolarLinear's in-memory form (kernels/polar_engine.py:144-360: one code per byte, fp16 norm per
+// block, a table of 2^bits centroids), for up to eight activation rows:
+//   y[n] = sum over blocks b of norm[n, b] * sum_j centroid[code[n, b, j]] * xr[b, j]
+// where xr is the caller's activation block rotated by the block's Hadamard matrix and divided by sqrt(block) (H is
+// symmetric, so x . (c H) = (x H) . c: the rotation is done once per call on the activations, never on the weights).
+// A warp takes two rows, a lane sixteen codes of each per trip (one 16-byte load, the next trip's requested before
+// this one's are consumed); the centroid table sits in shared memory once per lane (entry e of lane l at word
+// 32 e + l), so the 32 look-ups of a step hit 32 different banks whatever the codes are; a code becomes a table
+// offset by one shift and one mask.  fp32 throughout.
+// ---------------------------------------------------------------------------
+template <int BT>
+__global__ void __launch_bounds__(256) gemv_polar_codes_kernel(const PolarCodesArgs a)
+{
+    extern __shared__ float polar_lut[];
+    for (uint32_t i = threadIdx.x; i < a.entries * 32u; i += blockDim.x) polar_lut[i] = __ldg(a.centroids + (i >> 5));
+    __syncthreads();
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t row0 = (blockIdx.x * (blockDim.x >> 5) + warp) * 2u;
+    if (row0 >= a.N) return;
+    const uint32_t lut_lane = (uint32_t)__cvta_generic_to_shared(polar_lut) + lane * 4u, emask = (a.entries - 1u) << 7;
+    const uint32_t blocks_per_row = a.K >> a.block_shift;
+    const uint8_t *src[2];
+    const uint16_t *nrm[2];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        const uint32_t row = min(row0 + r, a.N - 1u);
+        src[r] = a.codes + (size_t)row * a.K;
+        nrm[r] = a.norms + (size_t)row * blocks_per_row;
+    }
+    float acc[2][BT];
+#pragma unroll
+    for (int r = 0; r < 2; r++)
+#pragma unroll
+        for (int b = 0; b < BT; b++) acc[r][b] = 0.0f;
+    uint32_t wc[2][4], wn[2][4];
+    auto load_w = [&](uint32_t c, uint32_t (&w)[2][4]) {
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (c < a.K) v = __ldg(reinterpret_cast<const uint4 *>(src[r] + c));
+            w[r][0] = v.x; w[r][1] = v.y; w[r][2] = v.z; w[r][3] = v.w;
+        }
+    };
+    uint32_t c = lane * 16u;
+    load_w(c, wc);
+    for (; c < a.K; c += 512u) {
+        load_w(c + 512u, wn);
+        const uint32_t blk = c >> a.block_shift;                    // the lane's sixteen columns lie in one block (block >= 16)
+        const float n0 = half_bits_to_float(__ldg(nrm[0] + blk)), n1 = half_bits_to_float(__ldg(nrm[1] + blk));
+        float p[2][BT];
+#pragma unroll
+        for (int r = 0; r < 2; r++)
+#pragma unroll
+            for (int b = 0; b < BT; b++) p[r][b] = 0.0f;
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            float xv[BT][4];
+#pragma unroll
+            for (int b = 0; b < BT; b++) {
+                float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if ((uint32_t)b < a.batch) v = __ldg(reinterpret_cast<const float4 *>(a.xrot + (size_t)b * a.K + c + 4u * q));
+                xv[b][0] = v.x; xv[b][1] = v.y; xv[b][2] = v.z; xv[b][3] = v.w;
+            }
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const uint32_t w = wc[r][q];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint32_t off = (i == 0 ? w << 7 : w >> (8 * i - 7)) & emask;         // 128 * code
+                    float cv;
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(cv) : "r"(lut_lane + off));
+#pragma unroll
+                    for (int b = 0; b < BT; b++) p[r][b] = fmaf(cv, xv[b][i], p[r][b]);
+                }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < BT; b++) { acc[0][b] = fmaf(n0, p[0][b], acc[0][b]); acc[1][b] = fmaf(n1, p[1][b], acc[1][b]); }
+#pragma unroll
+        for (int r = 0; r < 2; r++)
+#pragma unroll
+            for (int q = 0; q < 4; q++) wc[r][q] = wn[r][q];
+    }
+#pragma unroll
+    for (int r = 0; r < 2; r++)
+#pragma unroll
+        for (int b = 0; b < BT; b++) {
+            float v = acc[r][b];
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+            const uint32_t row = row0 + r;
+            if (lane == 0 && row < a.N && (uint32_t)b < a.batch)
+                store_y(a.y, (size_t)b * a.N + row, v + (a.bias ? __ldg(a.bias + row) : 0.0f), a.y_dtype);
+        }
+}
+
+// K a multiple of 16 and of the block, the block a power of two >= 16, entries a power of two <= 256, codes and xrot
+// 16-byte aligned, batch <= 8: checked by the caller.
+int launch_gemv_polar_codes(const PolarCodesArgs &a, void *stream)
+{
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const uint32_t warps = 8, grid = (a.N + warps * 2u - 1u) / (warps * 2u);
+    const size_t smem = (size_t)a.entries * 128u;
+    if (a.batch <= 1) gemv_polar_codes_kernel<1><<<grid, warps * 32, smem, st>>>(a);
+    else if (a.batch <= 2) gemv_polar_codes_kernel<2><<<grid, warps * 32, smem, st>>>(a);
+    else if (a.batch <= 4) gemv_polar_codes_kernel<4><<<grid, warps * 32, smem, st>>>(a);
+    else gemv_polar_codes_kernel<8><<<grid, warps * 32, smem, st>>>(a);
+    g_launches++;
+    return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
 // Fused decode -> fp16 operand pieces -> tcgen05 MMA (accumulator in tensor memory), for up to 128 activation rows.
 //
 //   Y[m, n] = sum_k X[m, k] * W[n, k]        (INT4 weights, 3 per step, 96-row tiles)

@@ -2,10 +2,11 @@
 
 Buffers, constructors and the result type of ``forward`` are the reference's.  Where the reference rebuilds the
 weight 64 rows at a time with torch operations (centroid look-up, inverse Hadamard, norm) and multiplies, this
-module keeps the codes entropy-coded in HBM and runs the fused decode + GEMV kernel: the activations are rotated
-once per call (H is symmetric, so x . (c H) = (x H) . c) and the weight is never materialised.  The fused path
-covers the configuration the hot path is built for -- 5-bit codes, blocks of 64 -- with up to 8 rows of x per
-call; other configurations and larger batches dequantise with torch operations on the same device.
+module rotates the activations once per call (H is symmetric, so x . (c H) = (x H) . c) and never materialises the
+weight: up to 8 rows of x are multiplied from an entropy-coded copy of the codes by the fused decode + GEMV kernel
+in the configuration that path is built for (5-bit codes, blocks of 64; ``entropy_coded = False`` turns it off), and
+straight from the byte codes the module holds in every other configuration the reference builds (any bit width,
+any block size from 16).  Larger batches dequantise with torch operations on the same device.
 """
 from __future__ import annotations
 
@@ -18,7 +19,7 @@ import torch.nn.functional as F
 
 from .. import _lib
 from ..core.polar_quant import _ensure_centroids, hadamard_matrix, polar_quantize
-from ..fused import EOQWeight, require_cuda
+from ..fused import EOQWeight, gemv_polar_codes, polar_codes_gemv_applies, require_cuda
 
 
 class PolarLinear(nn.Module):
@@ -38,6 +39,10 @@ class PolarLinear(nn.Module):
             self.bias = None
         self._eoq: Optional[EOQWeight] = None
         self._eoq_key = None
+        # True: where the entropy-coded path exists (5-bit codes, blocks of 64) forward multiplies from the entropy-coded
+        # copy of the codes (`eoq_weight()`; 47 / 65 / 115 us for 14336 x 4096 at 1 / 4 / 8 rows); False: always from the
+        # byte codes (37 / 83 / 154 us under graph replay, plus the launches of the rotation when called eagerly)
+        self.entropy_coded = True
 
     _hadamard = staticmethod(lambda n: hadamard_matrix(n).clone())
 
@@ -106,9 +111,14 @@ class PolarLinear(nn.Module):
         x2 = x.reshape(-1, self.in_features)
         if self.awq_scales is not None:                       # W / s applied to x instead: (x / s) W^T
             x2 = x2.float() / self.awq_scales.float().unsqueeze(0)
-        if self._fusable() and x2.shape[0] <= 8:
+        if self.entropy_coded and self._fusable() and x2.shape[0] <= 8:
             xin = x2 if x2.dtype in (torch.float16, torch.bfloat16, torch.float32) else x2.float()
             out = self.eoq_weight().gemv(xin, out_dtype=torch.float32)
+        elif polar_codes_gemv_applies(self.in_features, self.bits, self.block_size, x2.shape[0]):
+            # up to 8 rows of every other configuration the reference builds (its default is 4 bits, blocks of 128): one
+            # pass over the byte codes this module keeps resident, activations rotated once per call
+            out = gemv_polar_codes(self.codes, self.norms, self.centroids, self.H, self.out_features, self.in_features, self.bits,
+                                   self.block_size, x2)
         else:
             out = torch.empty(x2.shape[0], self.out_features, device=x.device, dtype=torch.float32)
             xf = x2.float()

@@ -95,13 +95,17 @@ def test_polar_linear_matches_the_reference_dequantised_weight():
     assert layer._fusable()
     dense = z["dequant"].astype(np.float64)                            # the reference's polar_dequantize
     rng = np.random.default_rng(3)
-    for rows in (1, 4, 8, 20):
-        x = torch.from_numpy(rng.standard_normal((rows, k)).astype(np.float32)).cuda()
-        y = layer(x)
-        assert y.dtype == torch.float16 and y.shape == (rows, n)
-        want = x.cpu().numpy().astype(np.float64) @ dense.T + np.linspace(-1, 1, n)
-        assert O.rel_l2(y.float().cpu().numpy(), want) < 2e-3          # fp16 output
-    # a configuration outside the fused path (4 bits, blocks of 128) still answers, through torch on the device
+    assert layer.entropy_coded                                         # the default where that path exists
+    for entropy_coded in (False, True):                                # from the byte codes; from the entropy-coded copy
+        layer.entropy_coded = entropy_coded
+        for rows in (1, 4, 8, 20):
+            x = torch.from_numpy(rng.standard_normal((rows, k)).astype(np.float32)).cuda()
+            y = layer(x)
+            assert y.dtype == torch.float16 and y.shape == (rows, n)
+            want = x.cpu().numpy().astype(np.float64) @ dense.T + np.linspace(-1, 1, n)
+            assert O.rel_l2(y.float().cpu().numpy(), want) < 2e-3          # fp16 output
+        assert (layer._eoq is not None) == entropy_coded
+    # a configuration the entropy-coded path is not built for (4 bits, blocks of 128): the byte-code kernel takes it
     lin = nn.Linear(256, 24, bias=False)
     other = PolarLinear.from_linear(lin, bits=4, block_size=128).cuda()
     assert not other._fusable()

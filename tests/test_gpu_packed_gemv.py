@@ -6,7 +6,8 @@ import torch
 
 from eoq_quantization_b200 import _lib as L
 from eoq_quantization_b200.core.quantized_linear import QuantizedLinear
-from eoq_quantization_b200.fused import dequant_packed, gemv_packed, packed_gemv_applies, packed_gemv_rows
+from eoq_quantization_b200.fused import (dequant_packed, gemv_packed, gemv_polar_codes, packed_gemv_applies, packed_gemv_rows,
+                                         polar_codes_gemv_applies)
 from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -110,3 +111,31 @@ def test_dequantised_rows_of_packed_codes_are_the_reference_product(bits, n, k, 
             assert torch.equal(got.cpu(), torch.from_numpy(want[lo:hi]).to(dt))
         got = dequant_packed(packed, None, n, k, bits, group, lo, hi, dtype=torch.int8)
         assert np.array_equal(got.cpu().numpy(), codes[lo:hi].astype(np.int8))
+
+
+@pytest.mark.parametrize("bits", [3, 4, 5, 8])
+@pytest.mark.parametrize("n,k,block", [(1, 64, 64), (37, 256, 16), (300, 1536, 128), (1000, 4096, 64), (77, 11008, 32)])
+def test_polar_byte_codes_gemv_matches_the_dequantised_weight(bits, n, k, block):
+    """`gemv_polar_codes` against the reference's dequantisation of the same buffers (kernels/polar_engine.py:257-264:
+    centroids[codes] / sqrt(block) @ H * norm), fp64 on the host; random codes, norms and centroids."""
+    from eoq_quantization_b200.core.polar_quant import hadamard_matrix
+    rng = np.random.default_rng(bits * 100 + n + block)
+    codes = rng.integers(0, 1 << bits, size=(n, k)).astype(np.int8 if bits < 8 else np.uint8)
+    norms = (rng.random(n * k // block).astype(np.float32) * 2 + 0.1).astype(np.float16)
+    cent = np.sort(rng.standard_normal(1 << bits)).astype(np.float32)
+    H = hadamard_matrix(block).double().numpy()
+    vals = cent.astype(np.float64)[codes.astype(np.uint8).astype(np.int64)].reshape(-1, block) / np.sqrt(block)
+    dense = ((vals @ H) * norms.astype(np.float64)[:, None]).reshape(n, k)
+    cd, nr, ct = torch.from_numpy(codes.view(np.int8)).cuda(), torch.from_numpy(norms).cuda(), torch.from_numpy(cent).cuda()
+    Ht = hadamard_matrix(block).cuda()
+    bias = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).cuda()
+    for rows in (1, 2, 3, 4, 5, 8):
+        assert polar_codes_gemv_applies(k, bits, block, rows)
+        for dt in (torch.float16, torch.bfloat16, torch.float32):
+            x = torch.from_numpy(rng.standard_normal((rows, k)).astype(np.float32)).cuda().to(dt)
+            y = gemv_polar_codes(cd, nr, ct, Ht, n, k, bits, block, x, bias)
+            want = x.float().cpu().numpy().astype(np.float64) @ dense.T + bias.cpu().numpy()
+            assert y.dtype == torch.float32 and O.rel_l2(y.cpu().numpy(), want) < 1e-5, (rows, dt)
+    assert not polar_codes_gemv_applies(k, bits, block, 9) and not polar_codes_gemv_applies(100, bits, 50)
+    with pytest.raises(ValueError):
+        gemv_polar_codes(cd, nr, ct, Ht, n, k, bits, block, torch.zeros(9, k, device="cuda"))
