@@ -744,32 +744,33 @@ def run_aux(args):
     # (torch) + one pass over the codes per step; 4 copies cycled like the tiles above
     from eoq_quantization_b200.fused import gemv_polar_codes
     cds = [codes.clone() for _ in range(4)]
-    byte_codes = {}
-    for batch in (1, 4, 8):
-        x = torch.randn(batch, k, device="cuda", generator=g).half()
-        want = ws[0].gemv(x, out_dtype=torch.float32)
-        got = gemv_polar_codes(cds[0], norms, cent, H, n, k, 5, d, x)
-        err = float((got - want).norm() / want.norm())
-        assert err < 1e-4, f"byte-code polar GEMV differs from the entropy-coded one: {err}"
-        it = {"i": 0}
+    byte_codes = {"tensor_cores": {}, "cuda_cores": {}}
+    for form, tc in (("tensor_cores", True), ("cuda_cores", False)):
+        for batch in (1, 4, 8):
+            x = torch.randn(batch, k, device="cuda", generator=g).half()
+            want = ws[0].gemv(x, out_dtype=torch.float32)
+            got = gemv_polar_codes(cds[0], norms, cent, n, k, 5, d, x, tensor_cores=tc)
+            err = float((got - want).norm() / want.norm())
+            assert err < 1e-4, f"byte-code polar GEMV differs from the entropy-coded one: {err}"
+            it = {"i": 0}
 
-        def run_codes():
-            i = it["i"] % len(cds); it["i"] += 1
-            gemv_polar_codes(cds[i], norms, cent, H, n, k, 5, d, x, out_dtype=torch.float16)
-        for _ in range(3):
-            run_codes()
-        torch.cuda.synchronize()
-        gph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()        # rotation (torch) + kernel, one replayed graph over the 4 copies
-        with torch.cuda.stream(side):
-            it["i"] = 0
-            with torch.cuda.graph(gph):
-                for _ in range(len(cds)):
-                    run_codes()
-        torch.cuda.synchronize()
-        ms = timed(gph.replay, max(3, args.steps // len(cds))) / len(cds)
-        nbytes = n * k + norms.numel() * 2 + batch * (n * 2 + k * 6)
-        byte_codes[f"batch{batch}"] = {"ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9, "pct_of_peak": 100 * nbytes / (ms * 1e-3) / 1e9 / peak,
-                                       "rel_l2_vs_entropy_coded": err}
+            def run_codes():
+                i = it["i"] % len(cds); it["i"] += 1
+                gemv_polar_codes(cds[i], norms, cent, n, k, 5, d, x, out_dtype=torch.float16, tensor_cores=tc)
+            for _ in range(3):
+                run_codes()
+            torch.cuda.synchronize()
+            gph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()        # rotation (torch) + kernel, one replayed graph over the 4 copies
+            with torch.cuda.stream(side):
+                it["i"] = 0
+                with torch.cuda.graph(gph):
+                    for _ in range(len(cds)):
+                        run_codes()
+            torch.cuda.synchronize()
+            ms = timed(gph.replay, max(3, args.steps // len(cds))) / len(cds)
+            nbytes = n * k + norms.numel() * 2 + batch * (n * 2 + k * 6)
+            byte_codes[form][f"batch{batch}"] = {"ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9, "pct_of_peak": 100 * nbytes / (ms * 1e-3) / 1e9 / peak,
+                                                 "rel_l2_vs_entropy_coded": err}
     line = {"metric": "fused decode+Q5 polar GEMV effective HBM GB/s", "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
             "data": "synthetic", "config": {"workload": "polar_q5_14336x4096_g64", "l2": "4 weight copies cycled"},
             "value": res["batch1"]["gbs"], "ms_per_step": res["batch1"]["ms"], "batches": res, "peak": peak,

@@ -1466,22 +1466,30 @@ extern "C" eoq_error_t eoq_b200_gemv_packed(const uint8_t *d_packed, const uint1
 }
 
 extern "C" eoq_error_t eoq_b200_gemv_polar_codes(const uint8_t *d_codes, const uint16_t *d_norms_fp16, const float *d_centroids,
-                                                 uint32_t rows, uint32_t cols, uint32_t bits, uint32_t block, const float *d_xrot,
-                                                 uint32_t batch, void *y, int y_dtype, const float *bias, void *stream)
+                                                 uint32_t rows, uint32_t cols, uint32_t bits, uint32_t block, const void *x, int x_dtype,
+                                                 uint32_t batch, void *d_scratch, void *y, int y_dtype, const float *bias,
+                                                 int tensor_cores, void *stream)
 {
-    if (!d_codes || !d_norms_fp16 || !d_centroids || !d_xrot || !y) return EOQ_ERR_NULL_PTR;
+    if (!d_codes || !d_norms_fp16 || !d_centroids || !x || !y || !d_scratch) return EOQ_ERR_NULL_PTR;
     if (batch == 0 || rows == 0) return EOQ_OK;
-    if (y_dtype < 0 || y_dtype > 2 || batch > 8) return EOQ_ERR_UNSUPPORTED;
+    if (x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2 || batch > 8) return EOQ_ERR_UNSUPPORTED;
     if (bits < 1 || bits > 8 || block == 0 || cols == 0) return EOQ_ERR_INVALID_HEADER;
+    // one row alone is quickest on the CUDA cores, several on the tensor cores (a quad of lanes takes 64 columns of one block)
+    const bool split = tensor_cores < 0 ? batch >= 2 && block >= 64u : tensor_cores != 0;
     // a lane takes sixteen codes of one block with one aligned load
-    if ((block & (block - 1u)) || block < 16u || cols % block || ((reinterpret_cast<uintptr_t>(d_codes) | reinterpret_cast<uintptr_t>(d_xrot)) & 15u))
+    if ((block & (block - 1u)) || block < (split ? 64u : 16u) || block > 4096u || cols % block ||
+        ((reinterpret_cast<uintptr_t>(d_codes) | reinterpret_cast<uintptr_t>(d_scratch)) & 15u))
         return EOQ_ERR_UNSUPPORTED;
     if (!have_device()) return EOQ_ERR_CUDA;
     PolarCodesArgs a = {};
-    a.codes = d_codes; a.norms = d_norms_fp16; a.centroids = d_centroids; a.xrot = d_xrot; a.y = y; a.bias = bias;
+    a.codes = d_codes; a.norms = d_norms_fp16; a.centroids = d_centroids; a.y = y; a.bias = bias;
+    if (split) a.xsplit = static_cast<const uint16_t *>(d_scratch);
+    else a.xrot = static_cast<const float *>(d_scratch);
     a.N = rows; a.K = cols; a.batch = batch; a.entries = 1u << bits; a.y_dtype = y_dtype;
     for (a.block_shift = 4; (1u << a.block_shift) < block; a.block_shift++) {}
-    int e = launch_gemv_polar_codes(a, stream);
+    int e = launch_polar_rotate(x, x_dtype, cols, a.block_shift, batch, split ? nullptr : static_cast<float *>(d_scratch),
+                                split ? static_cast<uint16_t *>(d_scratch) : nullptr, stream);
+    if (e == 0) e = launch_gemv_polar_codes(a, stream);
     if (e != 0) { std::fprintf(stderr, "eoq_b200_gemv_polar_codes: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
     return EOQ_OK;
 }

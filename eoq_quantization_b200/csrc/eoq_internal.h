@@ -219,12 +219,14 @@ struct PolarCodesArgs {
     const uint16_t *norms;      // fp16 bits, [N][K / block]
     const float *centroids;     // [entries]
     const float *xrot;          // [batch][K]: activations rotated per block and divided by sqrt(block)
+    const uint16_t *xsplit;     // or (tensor-core form) fp16 bits [2][batch][K]: the fp16 nearest to each rotated activation, then the remainder
     void *y;                    // [batch][N]
     const float *bias;          // [N] or null
     uint32_t N, K, block_shift, batch, entries;
     int y_dtype;
 };
 int launch_gemv_polar_codes(const PolarCodesArgs &a, void *stream);
+int launch_polar_rotate(const void *x, int x_dtype, uint32_t K, uint32_t block_shift, uint32_t batch, float *out32, uint16_t *out_split, void *stream);
 uint32_t gemv_packed_rows(const PackedGemvArgs &a);
 void set_packed_warps(int v);
 void set_dequant_vec(int v);

@@ -3269,13 +3269,13 @@ void set_packed_warps(int v) { g_packed_warps.store(v >= 1 && v <= 16 ? v : 0); 
 // partly filled round of CTAs loses that fraction of the machine: take the most warps per CTA with which the whole
 // grid is resident at once (given the registers the compiler gave this instantiation) and every warp still has two
 // spans; when no choice fits, the one with the most resident warps per SM.
-template <typename Kern>
-static cudaError_t launch_packed_mma(Kern kern, uint32_t fixed_warps, uint32_t tiles, uint32_t nspans, cudaStream_t st, const PackedGemvArgs &a)
+template <typename Kern, typename Args>
+static cudaError_t launch_packed_mma(Kern kern, uint32_t fixed_warps, uint32_t tiles, uint32_t nspans, cudaStream_t st, const Args &a, size_t smem = 0)
 {
     // byte codes and more than eight activation rows (more registers, longer spans of work per warp): 8 warps measured best
     if (fixed_warps) {
         const uint32_t w = g_packed_warps.load() ? std::min((uint32_t)g_packed_warps.load(), fixed_warps) : nspans >= 16u ? fixed_warps : 4u;
-        return launch_with_pdl(kern, dim3(tiles), dim3(w * 32u), 0, st, a);
+        return launch_with_pdl(kern, dim3(tiles), dim3(w * 32u), smem, st, a);
     }
     const uint32_t max_warps = 16;
     static std::atomic<int> regs{0};                             // per instantiation
@@ -3297,7 +3297,7 @@ static cudaError_t launch_packed_mma(Kern kern, uint32_t fixed_warps, uint32_t t
     }
     if (!warps) warps = fallback;
     if (g_packed_warps.load()) warps = std::min((uint32_t)g_packed_warps.load(), max_warps);
-    return launch_with_pdl(kern, dim3(tiles), dim3(warps * 32u), 0, st, a);
+    return launch_with_pdl(kern, dim3(tiles), dim3(warps * 32u), smem, st, a);
 }
 
 uint32_t gemv_packed_rows(const PackedGemvArgs &a)
@@ -3355,6 +3355,51 @@ int launch_gemv_packed(const PackedGemvArgs &a, void *stream)
 // 32 e + l), so the 32 look-ups of a step hit 32 different banks whatever the codes are; a code becomes a table
 // offset by one shift and one mask.  fp32 throughout.
 // ---------------------------------------------------------------------------
+// The rotation of the activations: every block of 2^shift columns of x times the normalised Hadamard matrix of that
+// order (Sylvester construction, core/polar_quant.py:104-120) and divided by sqrt(block), i.e. a fast Walsh-Hadamard
+// transform in shared memory scaled by 1 / block.  One CTA per activation row and stretch of columns.  Output: fp32
+// [batch][K], or with `split` two fp16 planes [2][batch][K] (the fp16 nearest to the value, then to the remainder).
+__global__ void __launch_bounds__(1024) polar_rotate_kernel(const void *__restrict__ x, int x_dtype, uint32_t K, uint32_t shift, uint32_t batch,
+                                                           float *__restrict__ out32, uint16_t *__restrict__ out_split)
+{
+    extern __shared__ float rot[];
+    const uint32_t b = blockIdx.y, width = blockDim.x * 4u, c0 = blockIdx.x * width;      // width: a multiple of the block
+    const uint32_t count = min(width, K - c0);
+    for (uint32_t i = threadIdx.x; i < count; i += blockDim.x) rot[i] = load_x(x, (size_t)b * K + c0 + i, x_dtype);
+    __syncthreads();
+    for (uint32_t h = 1; h < (1u << shift); h <<= 1) {
+        for (uint32_t i = threadIdx.x; i < count / 2u; i += blockDim.x) {
+            const uint32_t lo = ((i & ~(h - 1u)) << 1) | (i & (h - 1u)), hi = lo + h;      // the pairs (j, j + h) of one butterfly stage
+            const float u = rot[lo], v = rot[hi];
+            rot[lo] = u + v; rot[hi] = u - v;
+        }
+        __syncthreads();
+    }
+    const float scale = 1.0f / (float)(1u << shift);
+    for (uint32_t i = threadIdx.x; i < count; i += blockDim.x) {
+        const float v = rot[i] * scale;
+        const size_t o = (size_t)b * K + c0 + i;
+        if (out_split) {
+            const __half hi = __float2half_rn(v);
+            out_split[o] = __half_as_ushort(hi);
+            out_split[(size_t)batch * K + o] = __half_as_ushort(__float2half_rn(v - __half2float(hi)));
+        } else {
+            out32[o] = v;
+        }
+    }
+}
+
+int launch_polar_rotate(const void *x, int x_dtype, uint32_t K, uint32_t block_shift, uint32_t batch, float *out32, uint16_t *out_split, void *stream)
+{
+    // a CTA's stretch of columns: whole blocks, 1024 columns where the block allows
+    const uint32_t block = 1u << block_shift, width = std::max(block, 1024u), threads = width / 4u;
+    if (threads > 1024u) return (int)cudaErrorInvalidValue;
+    polar_rotate_kernel<<<dim3((K + width - 1u) / width, batch), threads, width * 4u, reinterpret_cast<cudaStream_t>(stream)>>>(
+        x, x_dtype, K, block_shift, batch, out32, out_split);
+    g_launches++;
+    return (int)cudaGetLastError();
+}
+
 template <int BT>
 __global__ void __launch_bounds__(256) gemv_polar_codes_kernel(const PolarCodesArgs a)
 {
@@ -3441,13 +3486,129 @@ __global__ void __launch_bounds__(256) gemv_polar_codes_kernel(const PolarCodesA
         }
 }
 
-// K a multiple of 16 and of the block, the block a power of two >= 16, entries a power of two <= 256, codes and xrot
-// 16-byte aligned, batch <= 8: checked by the caller.
+// The same product on the warp-level tensor cores, for blocks of 64 columns and more.  The operands of
+// mma.sync.m16n8k16 are fp16, a centroid and a rotated activation are fp32: each is split into the fp16 nearest to it
+// and the fp16 nearest to the remainder (c = c_hi + c_lo to about 2^-22), and the product is taken as
+// c_hi x_hi + (c_hi x_lo + c_lo x_hi), three instructions per sixteen columns with fp32 accumulation; the term left
+// out is 2^-22 of the result.  The centroid table holds both halves of an entry in one 32-bit word, once per lane
+// (conflict-free, as above); two look-ups and two byte permutes give the pair registers {hi_a, hi_b}, {lo_a, lo_b} of
+// two adjacent columns, which is the order the activations are stored in, so they need no permutation.  Lane (g, t)
+// takes sixteen codes of rows g and g + 8 per 64-column span (one 16-byte load each, the next span's requested
+// before this one's are consumed) and the same sixteen columns of activation row g from the caller's split copy
+// (xsplit: [hi | lo][batch][K] fp16).  A CTA is a 16-row tile; its warps share the spans and meet in shared memory.
+__global__ void __launch_bounds__(512) gemv_polar_mma_kernel(const PolarCodesArgs a)
+{
+    extern __shared__ uint32_t polar_lut2[];                     // [entries][32 lanes]: lo << 16 | hi
+    __shared__ float red[kMmaMaxWarps][16][8];
+    for (uint32_t i = threadIdx.x; i < a.entries * 32u; i += blockDim.x) {
+        const float c = __ldg(a.centroids + (i >> 5));
+        const __half hi = __float2half_rn(c), lo = __float2half_rn(c - __half2float(hi));
+        polar_lut2[i] = (uint32_t)__half_as_ushort(hi) | ((uint32_t)__half_as_ushort(lo) << 16);
+    }
+    __syncthreads();
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5, g = lane >> 2, t = lane & 3u;
+    const uint32_t row0 = blockIdx.x * 16u, nspans = a.K >> 6, blocks_per_row = a.K >> a.block_shift;
+    const uint32_t lut_lane = (uint32_t)__cvta_generic_to_shared(polar_lut2) + lane * 4u, emask = (a.entries - 1u) << 7;
+    const uint8_t *pw[2];
+    const uint16_t *pn[2];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        const uint32_t row = min(row0 + r * 8u + g, a.N - 1u);
+        pw[r] = a.codes + (size_t)row * a.K + t * 16u;
+        pn[r] = a.norms + (size_t)row * blocks_per_row;
+    }
+    // activation row g: its hi and lo halves, or the zero block with no stride where that row does not exist
+    const bool has = g < a.batch;
+    const uint16_t *xh = has ? a.xsplit + (size_t)g * a.K + t * 16u : reinterpret_cast<const uint16_t *>(kZeroBlock);
+    const uint16_t *xl = has ? xh + (size_t)a.batch * a.K : xh;
+    const uint32_t xstep = has ? 64u : 0u;
+    float tot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+
+    auto load_span = [&](uint32_t s, uint32_t (&w)[2][4], uint16_t (&nr)[2]) {
+        if (s >= nspans) return;
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(pw[r] + s * 64u));
+            w[r][0] = v.x; w[r][1] = v.y; w[r][2] = v.z; w[r][3] = v.w;
+            nr[r] = __ldg(pn[r] + ((s << 6) >> a.block_shift));
+        }
+    };
+    auto compute_span = [&](uint32_t s, const uint32_t (&w)[2][4], const uint16_t (&nr)[2]) {
+        uint32_t xq[2][8];                                        // [hi, lo][pair of adjacent columns]
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint4 vh = __ldg(reinterpret_cast<const uint4 *>(xh + s * xstep) + h), vl = __ldg(reinterpret_cast<const uint4 *>(xl + s * xstep) + h);
+            xq[0][4 * h] = vh.x; xq[0][4 * h + 1] = vh.y; xq[0][4 * h + 2] = vh.z; xq[0][4 * h + 3] = vh.w;
+            xq[1][4 * h] = vl.x; xq[1][4 * h + 1] = vl.y; xq[1][4 * h + 2] = vl.z; xq[1][4 * h + 3] = vl.w;
+        }
+        uint32_t hi[2][8], lo[2][8];                              // [row g, row g + 8][pair]: columns 2 pair, 2 pair + 1 of the lane's sixteen
+#pragma unroll
+        for (int r = 0; r < 2; r++)
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+#pragma unroll
+                for (int p = 0; p < 2; p++) {
+                    const uint32_t wj = w[r][j];
+                    const uint32_t oa = (p == 0 ? wj << 7 : wj >> 9) & emask, ob = (p == 0 ? wj >> 1 : wj >> 17) & emask;      // 128 * code
+                    uint32_t ea, eb;
+                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(ea) : "r"(lut_lane + oa));
+                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(eb) : "r"(lut_lane + ob));
+                    hi[r][2 * j + p] = __byte_perm(ea, eb, 0x5410u);
+                    lo[r][2 * j + p] = __byte_perm(ea, eb, 0x7632u);
+                }
+        float c[4], d[4];
+        mma_m16n8k16_first<false>(c, hi[0][0], hi[1][0], hi[0][1], hi[1][1], xq[0][0], xq[0][1]);
+        mma_m16n8k16_first<false>(d, hi[0][0], hi[1][0], hi[0][1], hi[1][1], xq[1][0], xq[1][1]);
+        mma_m16n8k16<false>(d, lo[0][0], lo[1][0], lo[0][1], lo[1][1], xq[0][0], xq[0][1]);
+#pragma unroll
+        for (int m = 1; m < 4; m++) {
+            mma_m16n8k16<false>(c, hi[0][2 * m], hi[1][2 * m], hi[0][2 * m + 1], hi[1][2 * m + 1], xq[0][2 * m], xq[0][2 * m + 1]);
+            mma_m16n8k16<false>(d, hi[0][2 * m], hi[1][2 * m], hi[0][2 * m + 1], hi[1][2 * m + 1], xq[1][2 * m], xq[1][2 * m + 1]);
+            mma_m16n8k16<false>(d, lo[0][2 * m], lo[1][2 * m], lo[0][2 * m + 1], lo[1][2 * m + 1], xq[0][2 * m], xq[0][2 * m + 1]);
+        }
+        const float fa = half_bits_to_float(nr[0]), fb = half_bits_to_float(nr[1]);
+        tot[0] = fmaf(fa, c[0] + d[0], tot[0]); tot[1] = fmaf(fa, c[1] + d[1], tot[1]);
+        tot[2] = fmaf(fb, c[2] + d[2], tot[2]); tot[3] = fmaf(fb, c[3] + d[3], tot[3]);
+    };
+
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    uint32_t wbuf[2][2][4];
+    uint16_t nbuf[2][2];
+    load_span(warp, wbuf[0], nbuf[0]);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (uint32_t s = warp; s < nspans; s += 2u * nwarps) {
+#pragma unroll
+        for (int dd = 0; dd < 2; dd++) {
+            const uint32_t sd = s + dd * nwarps;
+            if (sd >= nspans) break;
+            load_span(sd + nwarps, wbuf[dd ^ 1], nbuf[dd ^ 1]);
+            compute_span(sd, wbuf[dd], nbuf[dd]);
+        }
+    }
+    red[warp][g][2 * t] = tot[0]; red[warp][g][2 * t + 1] = tot[1];
+    red[warp][g + 8][2 * t] = tot[2]; red[warp][g + 8][2 * t + 1] = tot[3];
+    __syncthreads();
+    if (threadIdx.x < 128u) {
+        const uint32_t r = threadIdx.x >> 3, b = threadIdx.x & 7u, row = row0 + r;
+        float v = 0.0f;
+        for (uint32_t w = 0; w < nwarps; w++) v += red[w][r][b];
+        if (row < a.N && b < a.batch) store_y(a.y, (size_t)b * a.N + row, v + (a.bias ? __ldg(a.bias + row) : 0.0f), a.y_dtype);
+    }
+}
+
+// K a multiple of 16 and of the block, the block a power of two >= 16, entries a power of two <= 256, codes and the
+// activations 16-byte aligned, batch <= 8: checked by the caller.  With a split copy of the activations (xsplit) and
+// blocks of 64 columns or more: the tensor-core form.
 int launch_gemv_polar_codes(const PolarCodesArgs &a, void *stream)
 {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const size_t smem = (size_t)a.entries * 128u;                   // the table, once per lane
+    if (a.xsplit) {
+        const cudaError_t e = launch_packed_mma(gemv_polar_mma_kernel, 0u, (a.N + 15u) / 16u, a.K >> 6, st, a, smem);
+        g_launches++;
+        return (int)e;
+    }
     const uint32_t warps = 8, grid = (a.N + warps * 2u - 1u) / (warps * 2u);
-    const size_t smem = (size_t)a.entries * 128u;
     if (a.batch <= 1) gemv_polar_codes_kernel<1><<<grid, warps * 32, smem, st>>>(a);
     else if (a.batch <= 2) gemv_polar_codes_kernel<2><<<grid, warps * 32, smem, st>>>(a);
     else if (a.batch <= 4) gemv_polar_codes_kernel<4><<<grid, warps * 32, smem, st>>>(a);

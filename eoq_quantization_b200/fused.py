@@ -7,7 +7,6 @@ into ``libeoq_b200.so``.
 from __future__ import annotations
 
 import ctypes as C
-import math
 from typing import Optional, Sequence
 
 import numpy as np
@@ -355,34 +354,39 @@ def gemv_packed(packed: torch.Tensor, scales: torch.Tensor, rows: int, cols: int
 
 def polar_codes_gemv_applies(cols: int, bits: int, block: int, rows: int = 1) -> bool:
     """Whether `gemv_polar_codes` takes this configuration and row count."""
-    return 1 <= rows <= 8 and 1 <= bits <= 8 and block >= 16 and block & (block - 1) == 0 and cols % block == 0
+    return 1 <= rows <= 8 and 1 <= bits <= 8 and 16 <= block <= 4096 and block & (block - 1) == 0 and cols % block == 0
 
 
-def gemv_polar_codes(codes: torch.Tensor, norms: torch.Tensor, centroids: torch.Tensor, hadamard: torch.Tensor, rows: int, cols: int,
+def gemv_polar_codes(codes: torch.Tensor, norms: torch.Tensor, centroids: torch.Tensor, rows: int, cols: int,
                      bits: int, block: int, x: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                     out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+                     out_dtype: torch.dtype = torch.float32, tensor_cores: Optional[bool] = None) -> torch.Tensor:
     """y = x @ W.T (+ bias) for at most 8 rows of x, straight from PolarLinear's buffers (one centroid index per byte, fp16
-    norms, fp32 centroids; kernels/polar_engine.py:144-360): x is rotated once (every block times the symmetric Hadamard
-    matrix, divided by sqrt(block)), the weight is never materialised, fp32 throughout."""
+    norms, fp32 centroids; kernels/polar_engine.py:144-360): x is rotated once per call (every block times the symmetric
+    normalised Hadamard matrix, divided by sqrt(block)), the weight is never materialised.  `tensor_cores`: True (blocks
+    of 64 columns and more: centroids and activations as two fp16 halves each, fp32 accumulation, within about 1e-6 of
+    the fp32 form), False (CUDA cores, fp32 throughout), None: the quicker of the two for this row count."""
     require_cuda(codes, "gemv_polar_codes")
     require_cuda(x, "gemv_polar_codes")
     if x.device != codes.device:
         raise RuntimeError(f"gemv_polar_codes: the activations are on {x.device} but the weight lives on {codes.device}")
     if x.shape[-1] != cols:
         raise ValueError(f"expected last dimension {cols}, got {x.shape[-1]}")
-    x2 = x.reshape(-1, cols)
+    if x.dtype not in _DTYPES:
+        raise TypeError(f"unsupported activation dtype {x.dtype}")
+    x2 = x.reshape(-1, cols).contiguous()
     n = x2.shape[0]
-    if not polar_codes_gemv_applies(cols, bits, block, n):
-        raise ValueError("at most 8 rows, blocks that are powers of two >= 16 and divide the row")
-    xrot = (x2.float().reshape(n, cols // block, block) @ hadamard.to(device=x.device, dtype=torch.float32)).reshape(n, cols)
-    xrot = (xrot / math.sqrt(block)).contiguous()
+    if not polar_codes_gemv_applies(cols, bits, block, n) or (tensor_cores and block < 64):
+        raise ValueError("at most 8 rows; blocks that are powers of two from 16 (tensor cores: 64) to 4096 and divide the row")
     cd = codes.reshape(-1)[:rows * cols].contiguous().view(torch.uint8)
     nr = norms.to(device=codes.device, dtype=torch.float16).contiguous()
     ct = centroids.to(device=codes.device, dtype=torch.float32).contiguous()
+    scratch = torch.empty((n, cols), dtype=torch.float32, device=x.device)          # the rotated activations
     y = torch.empty((n, rows), dtype=out_dtype, device=x.device)
     b = None if bias is None else bias.to(device=x.device, dtype=torch.float32).contiguous()
     with torch.cuda.device(x.device):
-        _lib.check(_lib.lib().eoq_b200_gemv_polar_codes(cd.data_ptr(), nr.data_ptr(), ct.data_ptr(), rows, cols, bits, block, xrot.data_ptr(), n,
-                                                        y.data_ptr(), _DTYPES[out_dtype], b.data_ptr() if b is not None else None, _stream_ptr()),
+        _lib.check(_lib.lib().eoq_b200_gemv_polar_codes(cd.data_ptr(), nr.data_ptr(), ct.data_ptr(), rows, cols, bits, block, x2.data_ptr(),
+                                                        _DTYPES[x.dtype], n, scratch.data_ptr(), y.data_ptr(), _DTYPES[out_dtype],
+                                                        b.data_ptr() if b is not None else None,
+                                                        -1 if tensor_cores is None else int(tensor_cores), _stream_ptr()),
                    "eoq_b200_gemv_polar_codes")
     return y.reshape(*x.shape[:-1], rows)

@@ -3,10 +3,10 @@
 Buffers, constructors and the result type of ``forward`` are the reference's.  Where the reference rebuilds the
 weight 64 rows at a time with torch operations (centroid look-up, inverse Hadamard, norm) and multiplies, this
 module rotates the activations once per call (H is symmetric, so x . (c H) = (x H) . c) and never materialises the
-weight: up to 8 rows of x are multiplied from an entropy-coded copy of the codes by the fused decode + GEMV kernel
-in the configuration that path is built for (5-bit codes, blocks of 64; ``entropy_coded = False`` turns it off), and
-straight from the byte codes the module holds in every other configuration the reference builds (any bit width,
-any block size from 16).  Larger batches dequantise with torch operations on the same device.
+weight: up to 8 rows of x are multiplied straight from the byte codes the module holds (any bit width and block size
+the reference builds; one row on the CUDA cores, several on the tensor cores), or, with ``entropy_coded = True`` and
+the configuration that path is built for (5-bit codes, blocks of 64), from an entropy-coded copy of the codes by
+the fused decode + GEMV kernel.  Larger batches dequantise with torch operations on the same device.
 """
 from __future__ import annotations
 
@@ -39,10 +39,10 @@ class PolarLinear(nn.Module):
             self.bias = None
         self._eoq: Optional[EOQWeight] = None
         self._eoq_key = None
-        # True: where the entropy-coded path exists (5-bit codes, blocks of 64) forward multiplies from the entropy-coded
-        # copy of the codes (`eoq_weight()`; 47 / 65 / 115 us for 14336 x 4096 at 1 / 4 / 8 rows); False: always from the
-        # byte codes (37 / 83 / 154 us under graph replay, plus the launches of the rotation when called eagerly)
-        self.entropy_coded = True
+        # False: forward multiplies straight from the byte codes this module holds anyway (14336 x 4096 at 5 bits: 34 / 39 /
+        # 40 us at 1 / 4 / 8 rows); True: from an entropy-coded copy (`eoq_weight()`, about 4.6 instead of 8 bits per
+        # weight if the byte codes are then dropped; 48 / 64 / 116 us) where that path exists (5-bit codes, blocks of 64)
+        self.entropy_coded = False
 
     _hadamard = staticmethod(lambda n: hadamard_matrix(n).clone())
 
@@ -115,10 +115,11 @@ class PolarLinear(nn.Module):
             xin = x2 if x2.dtype in (torch.float16, torch.bfloat16, torch.float32) else x2.float()
             out = self.eoq_weight().gemv(xin, out_dtype=torch.float32)
         elif polar_codes_gemv_applies(self.in_features, self.bits, self.block_size, x2.shape[0]):
-            # up to 8 rows of every other configuration the reference builds (its default is 4 bits, blocks of 128): one
-            # pass over the byte codes this module keeps resident, activations rotated once per call
-            out = gemv_polar_codes(self.codes, self.norms, self.centroids, self.H, self.out_features, self.in_features, self.bits,
-                                   self.block_size, x2)
+            # up to 8 rows: one pass over the byte codes this module keeps resident (any bit width and block size the
+            # reference builds), activations rotated once per call
+            xin = x2 if x2.dtype in (torch.float16, torch.bfloat16, torch.float32) else x2.float()
+            out = gemv_polar_codes(self.codes, self.norms, self.centroids, self.out_features, self.in_features, self.bits,
+                                   self.block_size, xin)
         else:
             out = torch.empty(x2.shape[0], self.out_features, device=x.device, dtype=torch.float32)
             xf = x2.float()

@@ -447,15 +447,19 @@ eoq_error_t eoq_b200_gemv_packed(const uint8_t *d_packed, const uint16_t *d_scal
                                  int y_dtype, const float *bias, void *stream);
 
 /* y = x @ W.T (+ bias) straight from PolarLinear's in-memory form (kernels/polar_engine.py:144-360: one centroid index
- * per byte, one fp16 norm per block of each row, 2^bits fp32 centroids), for up to 8 activation rows, fp32 throughout.
- * d_xrot is x [batch, cols] in fp32 with every block of `block` columns multiplied by the block's Hadamard matrix and
- * divided by sqrt(block) (the matrix is symmetric, so the rotation moves from the weights to the activations; the
- * reference applies it to every dequantised weight block, kernels/polar_engine.py:257-264).  Needs block a power of
- * two >= 16 that divides cols, d_codes and d_xrot 16-byte aligned (EOQ_ERR_UNSUPPORTED otherwise).  Device pointers;
+ * per byte, one fp16 norm per block of each row, 2^bits fp32 centroids), for up to 8 activation rows.  Two launches:
+ * the activations are rotated once (every block of `block` columns times the block's normalised Hadamard matrix,
+ * divided by sqrt(block): the matrix is symmetric, so the rotation the reference applies to every dequantised weight
+ * block, kernels/polar_engine.py:257-264, moves to x) into d_scratch (batch * cols * 4 bytes, 16-byte aligned, the
+ * caller's), then one pass over the codes.  tensor_cores = 0: CUDA cores, fp32 throughout, block a power of two >= 16;
+ * 1: tensor cores (centroids and rotated activations as two fp16 halves each, fp32 accumulation: within about 1e-6 of
+ * the fp32 form), block >= 64; -1: the quicker of the two for this batch.  The block must divide cols and be at most
+ * 4096; d_codes 16-byte aligned (EOQ_ERR_UNSUPPORTED otherwise).  x in EOQ_B200_F16 / BF16 / F32.  Device pointers;
  * asynchronous. */
 eoq_error_t eoq_b200_gemv_polar_codes(const uint8_t *d_codes, const uint16_t *d_norms_fp16, const float *d_centroids,
-                                      uint32_t rows, uint32_t cols, uint32_t bits, uint32_t block, const float *d_xrot,
-                                      uint32_t batch, void *y, int y_dtype, const float *bias, void *stream);
+                                      uint32_t rows, uint32_t cols, uint32_t bits, uint32_t block, const void *x, int x_dtype,
+                                      uint32_t batch, void *d_scratch, void *y, int y_dtype, const float *bias,
+                                      int tensor_cores, void *stream);
 
 /* Synchronises `stream` and reports whether any kernel that used this weight gave up on a
  * bounded wait for its staged data (EOQ_ERR_CUDA; outputs of that launch are then invalid).

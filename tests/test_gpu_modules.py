@@ -95,7 +95,7 @@ def test_polar_linear_matches_the_reference_dequantised_weight():
     assert layer._fusable()
     dense = z["dequant"].astype(np.float64)                            # the reference's polar_dequantize
     rng = np.random.default_rng(3)
-    assert layer.entropy_coded                                         # the default where that path exists
+    assert not layer.entropy_coded                                     # the default: straight from the byte codes
     for entropy_coded in (False, True):                                # from the byte codes; from the entropy-coded copy
         layer.entropy_coded = entropy_coded
         for rows in (1, 4, 8, 20):
