@@ -746,9 +746,9 @@ def run_aux(args):
     cds = [codes.clone() for _ in range(4)]
     byte_codes = {"tensor_cores": {}, "cuda_cores": {}}
     for form, tc in (("tensor_cores", True), ("cuda_cores", False)):
-        for batch in (1, 4, 8):
+        for batch in (1, 4, 8, 16, 32) if tc else (1, 4, 8):
             x = torch.randn(batch, k, device="cuda", generator=g).half()
-            want = ws[0].gemv(x, out_dtype=torch.float32)
+            want = torch.cat([ws[0].gemv(x[lo:lo + 8], out_dtype=torch.float32) for lo in range(0, batch, 8)])
             got = gemv_polar_codes(cds[0], norms, cent, n, k, 5, d, x, tensor_cores=tc)
             err = float((got - want).norm() / want.norm())
             assert err < 1e-4, f"byte-code polar GEMV differs from the entropy-coded one: {err}"

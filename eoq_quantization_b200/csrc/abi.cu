@@ -1472,10 +1472,11 @@ extern "C" eoq_error_t eoq_b200_gemv_polar_codes(const uint8_t *d_codes, const u
 {
     if (!d_codes || !d_norms_fp16 || !d_centroids || !x || !y || !d_scratch) return EOQ_ERR_NULL_PTR;
     if (batch == 0 || rows == 0) return EOQ_OK;
-    if (x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2 || batch > 8) return EOQ_ERR_UNSUPPORTED;
+    if (x_dtype < 0 || x_dtype > 2 || y_dtype < 0 || y_dtype > 2) return EOQ_ERR_UNSUPPORTED;
     if (bits < 1 || bits > 8 || block == 0 || cols == 0) return EOQ_ERR_INVALID_HEADER;
     // one row alone is quickest on the CUDA cores, several on the tensor cores (a quad of lanes takes 64 columns of one block)
     const bool split = tensor_cores < 0 ? batch >= 2 && block >= 64u : tensor_cores != 0;
+    if (batch > (split ? 32u : 8u)) return EOQ_ERR_UNSUPPORTED;
     // a lane takes sixteen codes of one block with one aligned load
     if ((block & (block - 1u)) || block < (split ? 64u : 16u) || block > 4096u || cols % block ||
         ((reinterpret_cast<uintptr_t>(d_codes) | reinterpret_cast<uintptr_t>(d_scratch)) & 15u))

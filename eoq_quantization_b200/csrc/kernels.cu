@@ -3496,10 +3496,11 @@ __global__ void __launch_bounds__(256) gemv_polar_codes_kernel(const PolarCodesA
 // takes sixteen codes of rows g and g + 8 per 64-column span (one 16-byte load each, the next span's requested
 // before this one's are consumed) and the same sixteen columns of activation row g from the caller's split copy
 // (xsplit: [hi | lo][batch][K] fp16).  A CTA is a 16-row tile; its warps share the spans and meet in shared memory.
+template <int NB>
 __global__ void __launch_bounds__(512) gemv_polar_mma_kernel(const PolarCodesArgs a)
 {
     extern __shared__ uint32_t polar_lut2[];                     // [entries][32 lanes]: lo << 16 | hi
-    __shared__ float red[kMmaMaxWarps][16][8];
+    __shared__ float red[kMmaMaxWarps][NB][16][8];
     for (uint32_t i = threadIdx.x; i < a.entries * 32u; i += blockDim.x) {
         const float c = __ldg(a.centroids + (i >> 5));
         const __half hi = __float2half_rn(c), lo = __float2half_rn(c - __half2float(hi));
@@ -3517,12 +3518,19 @@ __global__ void __launch_bounds__(512) gemv_polar_mma_kernel(const PolarCodesArg
         pw[r] = a.codes + (size_t)row * a.K + t * 16u;
         pn[r] = a.norms + (size_t)row * blocks_per_row;
     }
-    // activation row g: its hi and lo halves, or the zero block with no stride where that row does not exist
-    const bool has = g < a.batch;
-    const uint16_t *xh = has ? a.xsplit + (size_t)g * a.K + t * 16u : reinterpret_cast<const uint16_t *>(kZeroBlock);
-    const uint16_t *xl = has ? xh + (size_t)a.batch * a.K : xh;
-    const uint32_t xstep = has ? 64u : 0u;
-    float tot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    // activation rows 8n + g: their hi and lo halves, or the zero block with no stride where a row does not exist
+    const uint16_t *xh[NB], *xl[NB];
+    uint32_t xstep[NB];
+    float tot[NB][4];
+#pragma unroll
+    for (int n = 0; n < NB; n++) {
+        const bool has = 8u * n + g < a.batch;
+        xh[n] = has ? a.xsplit + (size_t)(8u * n + g) * a.K + t * 16u : reinterpret_cast<const uint16_t *>(kZeroBlock);
+        xl[n] = has ? xh[n] + (size_t)a.batch * a.K : xh[n];
+        xstep[n] = has ? 64u : 0u;
+#pragma unroll
+        for (int i = 0; i < 4; i++) tot[n][i] = 0.0f;
+    }
 
     auto load_span = [&](uint32_t s, uint32_t (&w)[2][4], uint16_t (&nr)[2]) {
         if (s >= nspans) return;
@@ -3534,13 +3542,6 @@ __global__ void __launch_bounds__(512) gemv_polar_mma_kernel(const PolarCodesArg
         }
     };
     auto compute_span = [&](uint32_t s, const uint32_t (&w)[2][4], const uint16_t (&nr)[2]) {
-        uint32_t xq[2][8];                                        // [hi, lo][pair of adjacent columns]
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const uint4 vh = __ldg(reinterpret_cast<const uint4 *>(xh + s * xstep) + h), vl = __ldg(reinterpret_cast<const uint4 *>(xl + s * xstep) + h);
-            xq[0][4 * h] = vh.x; xq[0][4 * h + 1] = vh.y; xq[0][4 * h + 2] = vh.z; xq[0][4 * h + 3] = vh.w;
-            xq[1][4 * h] = vl.x; xq[1][4 * h + 1] = vl.y; xq[1][4 * h + 2] = vl.z; xq[1][4 * h + 3] = vl.w;
-        }
         uint32_t hi[2][8], lo[2][8];                              // [row g, row g + 8][pair]: columns 2 pair, 2 pair + 1 of the lane's sixteen
 #pragma unroll
         for (int r = 0; r < 2; r++)
@@ -3556,19 +3557,29 @@ __global__ void __launch_bounds__(512) gemv_polar_mma_kernel(const PolarCodesArg
                     hi[r][2 * j + p] = __byte_perm(ea, eb, 0x5410u);
                     lo[r][2 * j + p] = __byte_perm(ea, eb, 0x7632u);
                 }
-        float c[4], d[4];
-        mma_m16n8k16_first<false>(c, hi[0][0], hi[1][0], hi[0][1], hi[1][1], xq[0][0], xq[0][1]);
-        mma_m16n8k16_first<false>(d, hi[0][0], hi[1][0], hi[0][1], hi[1][1], xq[1][0], xq[1][1]);
-        mma_m16n8k16<false>(d, lo[0][0], lo[1][0], lo[0][1], lo[1][1], xq[0][0], xq[0][1]);
-#pragma unroll
-        for (int m = 1; m < 4; m++) {
-            mma_m16n8k16<false>(c, hi[0][2 * m], hi[1][2 * m], hi[0][2 * m + 1], hi[1][2 * m + 1], xq[0][2 * m], xq[0][2 * m + 1]);
-            mma_m16n8k16<false>(d, hi[0][2 * m], hi[1][2 * m], hi[0][2 * m + 1], hi[1][2 * m + 1], xq[1][2 * m], xq[1][2 * m + 1]);
-            mma_m16n8k16<false>(d, lo[0][2 * m], lo[1][2 * m], lo[0][2 * m + 1], lo[1][2 * m + 1], xq[0][2 * m], xq[0][2 * m + 1]);
-        }
         const float fa = half_bits_to_float(nr[0]), fb = half_bits_to_float(nr[1]);
-        tot[0] = fmaf(fa, c[0] + d[0], tot[0]); tot[1] = fmaf(fa, c[1] + d[1], tot[1]);
-        tot[2] = fmaf(fb, c[2] + d[2], tot[2]); tot[3] = fmaf(fb, c[3] + d[3], tot[3]);
+#pragma unroll
+        for (int n = 0; n < NB; n++) {
+            uint32_t xq[2][8];                                    // [hi, lo][pair of adjacent columns]
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const uint4 vh = __ldg(reinterpret_cast<const uint4 *>(xh[n] + s * xstep[n]) + h), vl = __ldg(reinterpret_cast<const uint4 *>(xl[n] + s * xstep[n]) + h);
+                xq[0][4 * h] = vh.x; xq[0][4 * h + 1] = vh.y; xq[0][4 * h + 2] = vh.z; xq[0][4 * h + 3] = vh.w;
+                xq[1][4 * h] = vl.x; xq[1][4 * h + 1] = vl.y; xq[1][4 * h + 2] = vl.z; xq[1][4 * h + 3] = vl.w;
+            }
+            float c[4], d[4];
+            mma_m16n8k16_first<false>(c, hi[0][0], hi[1][0], hi[0][1], hi[1][1], xq[0][0], xq[0][1]);
+            mma_m16n8k16_first<false>(d, hi[0][0], hi[1][0], hi[0][1], hi[1][1], xq[1][0], xq[1][1]);
+            mma_m16n8k16<false>(d, lo[0][0], lo[1][0], lo[0][1], lo[1][1], xq[0][0], xq[0][1]);
+#pragma unroll
+            for (int m = 1; m < 4; m++) {
+                mma_m16n8k16<false>(c, hi[0][2 * m], hi[1][2 * m], hi[0][2 * m + 1], hi[1][2 * m + 1], xq[0][2 * m], xq[0][2 * m + 1]);
+                mma_m16n8k16<false>(d, hi[0][2 * m], hi[1][2 * m], hi[0][2 * m + 1], hi[1][2 * m + 1], xq[1][2 * m], xq[1][2 * m + 1]);
+                mma_m16n8k16<false>(d, lo[0][2 * m], lo[1][2 * m], lo[0][2 * m + 1], lo[1][2 * m + 1], xq[0][2 * m], xq[0][2 * m + 1]);
+            }
+            tot[n][0] = fmaf(fa, c[0] + d[0], tot[n][0]); tot[n][1] = fmaf(fa, c[1] + d[1], tot[n][1]);
+            tot[n][2] = fmaf(fb, c[2] + d[2], tot[n][2]); tot[n][3] = fmaf(fb, c[3] + d[3], tot[n][3]);
+        }
     };
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -3585,30 +3596,42 @@ __global__ void __launch_bounds__(512) gemv_polar_mma_kernel(const PolarCodesArg
             compute_span(sd, wbuf[dd], nbuf[dd]);
         }
     }
-    red[warp][g][2 * t] = tot[0]; red[warp][g][2 * t + 1] = tot[1];
-    red[warp][g + 8][2 * t] = tot[2]; red[warp][g + 8][2 * t + 1] = tot[3];
+#pragma unroll
+    for (int n = 0; n < NB; n++) {
+        red[warp][n][g][2 * t] = tot[n][0]; red[warp][n][g][2 * t + 1] = tot[n][1];
+        red[warp][n][g + 8][2 * t] = tot[n][2]; red[warp][n][g + 8][2 * t + 1] = tot[n][3];
+    }
     __syncthreads();
-    if (threadIdx.x < 128u) {
-        const uint32_t r = threadIdx.x >> 3, b = threadIdx.x & 7u, row = row0 + r;
+    for (uint32_t i = threadIdx.x; i < NB * 128u; i += blockDim.x) {
+        const uint32_t n = i >> 7, r = (i >> 3) & 15u, b = 8u * n + (i & 7u), row = row0 + r;
         float v = 0.0f;
-        for (uint32_t w = 0; w < nwarps; w++) v += red[w][r][b];
+        for (uint32_t w = 0; w < nwarps; w++) v += red[w][n][r][i & 7u];
         if (row < a.N && b < a.batch) store_y(a.y, (size_t)b * a.N + row, v + (a.bias ? __ldg(a.bias + row) : 0.0f), a.y_dtype);
     }
 }
 
 // K a multiple of 16 and of the block, the block a power of two >= 16, entries a power of two <= 256, codes and the
 // activations 16-byte aligned, batch <= 8: checked by the caller.  With a split copy of the activations (xsplit) and
-// blocks of 64 columns or more: the tensor-core form.
+// blocks of 64 columns or more: the tensor-core form, batch <= 32.
 int launch_gemv_polar_codes(const PolarCodesArgs &a, void *stream)
 {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const size_t smem = (size_t)a.entries * 128u;                   // the table, once per lane
     if (a.xsplit) {
-        const cudaError_t e = launch_packed_mma(gemv_polar_mma_kernel, 0u, (a.N + 15u) / 16u, a.K >> 6, st, a, smem);
+        const uint32_t tiles = (a.N + 15u) / 16u, nspans = a.K >> 6;
+        cudaError_t e = cudaSuccess;
+        if (a.batch <= 8) e = launch_packed_mma(gemv_polar_mma_kernel<1>, 0u, tiles, nspans, st, a, smem);
+        else if (a.batch <= 16) e = launch_packed_mma(gemv_polar_mma_kernel<2>, 0u, tiles, nspans, st, a, smem);
+        else {
+            // 32 KB of meeting space beside a table of up to 32 KB: past the 48 KB a kernel gets without asking
+            if (smem > 16u * 1024u) e = cudaFuncSetAttribute(gemv_polar_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e == cudaSuccess) e = launch_packed_mma(gemv_polar_mma_kernel<4>, 0u, tiles, nspans, st, a, smem);
+        }
         g_launches++;
         return (int)e;
     }
     const uint32_t warps = 8, grid = (a.N + warps * 2u - 1u) / (warps * 2u);
+    if (a.batch > 8) return (int)cudaErrorInvalidValue;
     if (a.batch <= 1) gemv_polar_codes_kernel<1><<<grid, warps * 32, smem, st>>>(a);
     else if (a.batch <= 2) gemv_polar_codes_kernel<2><<<grid, warps * 32, smem, st>>>(a);
     else if (a.batch <= 4) gemv_polar_codes_kernel<4><<<grid, warps * 32, smem, st>>>(a);

@@ -353,14 +353,16 @@ def gemv_packed(packed: torch.Tensor, scales: torch.Tensor, rows: int, cols: int
 
 
 def polar_codes_gemv_applies(cols: int, bits: int, block: int, rows: int = 1) -> bool:
-    """Whether `gemv_polar_codes` takes this configuration and row count."""
-    return 1 <= rows <= 8 and 1 <= bits <= 8 and 16 <= block <= 4096 and block & (block - 1) == 0 and cols % block == 0
+    """Whether `gemv_polar_codes` takes this configuration and row count (8 rows on the CUDA cores, 32 on the tensor
+    cores, which need blocks of 64 columns and more)."""
+    return (1 <= rows <= (32 if block >= 64 else 8) and 1 <= bits <= 8 and 16 <= block <= 4096 and block & (block - 1) == 0 and
+            cols % block == 0)
 
 
 def gemv_polar_codes(codes: torch.Tensor, norms: torch.Tensor, centroids: torch.Tensor, rows: int, cols: int,
                      bits: int, block: int, x: torch.Tensor, bias: Optional[torch.Tensor] = None,
                      out_dtype: torch.dtype = torch.float32, tensor_cores: Optional[bool] = None) -> torch.Tensor:
-    """y = x @ W.T (+ bias) for at most 8 rows of x, straight from PolarLinear's buffers (one centroid index per byte, fp16
+    """y = x @ W.T (+ bias) for at most 8 rows of x (32 on the tensor cores), straight from PolarLinear's buffers (one centroid index per byte, fp16
     norms, fp32 centroids; kernels/polar_engine.py:144-360): x is rotated once per call (every block times the symmetric
     normalised Hadamard matrix, divided by sqrt(block)), the weight is never materialised.  `tensor_cores`: True (blocks
     of 64 columns and more: centroids and activations as two fp16 halves each, fp32 accumulation, within about 1e-6 of
@@ -375,8 +377,8 @@ def gemv_polar_codes(codes: torch.Tensor, norms: torch.Tensor, centroids: torch.
         raise TypeError(f"unsupported activation dtype {x.dtype}")
     x2 = x.reshape(-1, cols).contiguous()
     n = x2.shape[0]
-    if not polar_codes_gemv_applies(cols, bits, block, n) or (tensor_cores and block < 64):
-        raise ValueError("at most 8 rows; blocks that are powers of two from 16 (tensor cores: 64) to 4096 and divide the row")
+    if not polar_codes_gemv_applies(cols, bits, block, n) or (tensor_cores and block < 64) or (tensor_cores is False and n > 8):
+        raise ValueError("at most 8 rows (tensor cores: 32); blocks that are powers of two from 16 (tensor cores: 64) to 4096 and divide the row")
     cd = codes.reshape(-1)[:rows * cols].contiguous().view(torch.uint8)
     nr = norms.to(device=codes.device, dtype=torch.float16).contiguous()
     ct = centroids.to(device=codes.device, dtype=torch.float32).contiguous()

@@ -3,8 +3,8 @@
 Buffers, constructors and the result type of ``forward`` are the reference's.  Where the reference rebuilds the
 weight 64 rows at a time with torch operations (centroid look-up, inverse Hadamard, norm) and multiplies, this
 module rotates the activations once per call (H is symmetric, so x . (c H) = (x H) . c) and never materialises the
-weight: up to 8 rows of x are multiplied straight from the byte codes the module holds (any bit width and block size
-the reference builds; one row on the CUDA cores, several on the tensor cores), or, with ``entropy_coded = True`` and
+weight: up to 32 rows of x (8 for blocks below 64 columns) are multiplied straight from the byte codes the module holds
+(any bit width and block size the reference builds; one row on the CUDA cores, several on the tensor cores), or, with ``entropy_coded = True`` and
 the configuration that path is built for (5-bit codes, blocks of 64), from an entropy-coded copy of the codes by
 the fused decode + GEMV kernel.  Larger batches dequantise with torch operations on the same device.
 """
@@ -115,8 +115,8 @@ class PolarLinear(nn.Module):
             xin = x2 if x2.dtype in (torch.float16, torch.bfloat16, torch.float32) else x2.float()
             out = self.eoq_weight().gemv(xin, out_dtype=torch.float32)
         elif polar_codes_gemv_applies(self.in_features, self.bits, self.block_size, x2.shape[0]):
-            # up to 8 rows: one pass over the byte codes this module keeps resident (any bit width and block size the
-            # reference builds), activations rotated once per call
+            # up to 8 rows (32 with blocks of 64 columns and more): one pass over the byte codes this module keeps resident
+            # (any bit width and block size the reference builds), activations rotated once per call
             xin = x2 if x2.dtype in (torch.float16, torch.bfloat16, torch.float32) else x2.float()
             out = gemv_polar_codes(self.codes, self.norms, self.centroids, self.out_features, self.in_features, self.bits,
                                    self.block_size, xin)

@@ -447,7 +447,8 @@ eoq_error_t eoq_b200_gemv_packed(const uint8_t *d_packed, const uint16_t *d_scal
                                  int y_dtype, const float *bias, void *stream);
 
 /* y = x @ W.T (+ bias) straight from PolarLinear's in-memory form (kernels/polar_engine.py:144-360: one centroid index
- * per byte, one fp16 norm per block of each row, 2^bits fp32 centroids), for up to 8 activation rows.  Two launches:
+ * per byte, one fp16 norm per block of each row, 2^bits fp32 centroids), for up to 8 activation rows on the CUDA cores
+ * and 32 on the tensor cores.  Two launches:
  * the activations are rotated once (every block of `block` columns times the block's normalised Hadamard matrix,
  * divided by sqrt(block): the matrix is symmetric, so the rotation the reference applies to every dequantised weight
  * block, kernels/polar_engine.py:257-264, moves to x) into d_scratch (batch * cols * 4 bytes, 16-byte aligned, the

@@ -128,18 +128,21 @@ def test_polar_byte_codes_gemv_matches_the_dequantised_weight(bits, n, k, block)
     dense = ((vals @ H) * norms.astype(np.float64)[:, None]).reshape(n, k)
     cd, nr, ct = torch.from_numpy(codes.view(np.int8)).cuda(), torch.from_numpy(norms).cuda(), torch.from_numpy(cent).cuda()
     bias = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).cuda()
-    for rows in (1, 2, 3, 4, 5, 8):
+    for rows in (1, 2, 3, 4, 5, 8) + ((9, 16, 17, 32) if block >= 64 else ()):
         assert polar_codes_gemv_applies(k, bits, block, rows)
         for dt in (torch.float16, torch.bfloat16, torch.float32):
             x = torch.from_numpy(rng.standard_normal((rows, k)).astype(np.float32)).cuda().to(dt)
             want = x.float().cpu().numpy().astype(np.float64) @ dense.T + bias.cpu().numpy()
-            for tensor_cores in ((True, False, None) if block >= 64 else (False, None)):
+            for tensor_cores in (((True, False, None) if rows <= 8 else (True, None)) if block >= 64 else (False, None)):
                 y = gemv_polar_codes(cd, nr, ct, n, k, bits, block, x, bias, tensor_cores=tensor_cores)
                 assert y.dtype == torch.float32 and O.rel_l2(y.cpu().numpy(), want) < 1e-5, (rows, dt, tensor_cores)
             assert gemv_polar_codes(cd, nr, ct, n, k, bits, block, x, out_dtype=dt).dtype == dt
-    assert not polar_codes_gemv_applies(k, bits, block, 9) and not polar_codes_gemv_applies(100, bits, 50)
+    most = 32 if block >= 64 else 8
+    assert not polar_codes_gemv_applies(k, bits, block, most + 1) and not polar_codes_gemv_applies(100, bits, 50)
     with pytest.raises(ValueError):
-        gemv_polar_codes(cd, nr, ct, n, k, bits, block, torch.zeros(9, k, device="cuda"))
+        gemv_polar_codes(cd, nr, ct, n, k, bits, block, torch.zeros(most + 1, k, device="cuda"))
+    with pytest.raises(ValueError):
+        gemv_polar_codes(cd, nr, ct, n, k, bits, block, torch.zeros(9, k, device="cuda"), tensor_cores=False)
     if block < 64:
         with pytest.raises(ValueError):
             gemv_polar_codes(cd, nr, ct, n, k, bits, block, x, tensor_cores=True)
