@@ -602,7 +602,8 @@ def run_aux(args):
                 dense = (codes.float().view(-1, GROUP) * scale.half().float()[:, None]).view(n, k)
                 layers.append((n, k, [pk.contiguous().cuda().clone() for _ in range(copies)], scale.half().cuda(), dense))
             per_b = {}
-            for batch, xdt in [(b, torch.float16) for b in (1, 4, 8, 16, 32)] + ([(1, torch.bfloat16)] if bits == 8 else []):
+            for batch, xdt in ([(b, torch.float16) for b in (1, 4, 8, 16, 32)] + ([(1, torch.bfloat16)] if bits == 8 else []) +
+                               ([(1, torch.float32), (8, torch.float32)] if bits == 4 else [])):
                 xs = [torch.randn(batch, k, device="cuda").to(xdt) for (_, k) in shapes]
                 y = gemv_packed(layers[0][2][0], layers[0][3], shapes[0][0], shapes[0][1], bits, GROUP, xs[0], out_dtype=torch.float32)
                 want = xs[0].float().cpu().double() @ layers[0][4].double().T
@@ -628,7 +629,7 @@ def run_aux(args):
                 torch.cuda.synchronize()
                 ms = timed(gph.replay, max(3, args.steps // copies)) / copies
                 nbytes = sum(p[2][0].numel() + p[3].numel() * 2 + (p[0] + p[1]) * batch * 2 for p in layers)
-                per_b[f"batch{batch}" + ("" if xdt == torch.float16 else "_bf16")] = {"us_per_step": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peak,
+                per_b[f"batch{batch}" + {torch.float16: "", torch.bfloat16: "_bf16", torch.float32: "_fp32"}[xdt]] = {"us_per_step": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peak,
                                           "bytes_per_step": nbytes, "rel_l2_vs_dequantise_then_matmul": err}
             res[f"int{bits}"] = per_b
         # beyond 32 rows the modules dequantise the packed codes to a 16-bit matrix and call a library GEMM: the

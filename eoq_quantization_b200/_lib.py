@@ -169,7 +169,7 @@ def lib() -> C.CDLL:
         "eoq_b200_weight_decode": (C.c_int, [vp, vp, C.c_int, vp, C.c_int, vp]),
         "eoq_b200_dequant_packed": (C.c_int, [vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                               C.c_uint32, vp, C.c_int, vp]),
-        "eoq_b200_gemv_packed": (C.c_int, [vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, vp, C.c_int, C.c_uint32, vp, C.c_int, vp, vp]),
+        "eoq_b200_gemv_packed": (C.c_int, [vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, vp, C.c_int, C.c_uint32, vp, vp, C.c_int, vp, vp]),
         "eoq_b200_gemv_polar_codes": (C.c_int, [vp, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, vp, C.c_int, C.c_uint32, vp, vp, C.c_int, vp, C.c_int, vp]),
         "eoq_b200_weight_status": (C.c_int, [vp, vp]),
         "eoq_b200_tune": (C.c_int, [C.c_char_p, C.c_int]),

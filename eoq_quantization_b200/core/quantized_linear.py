@@ -130,12 +130,12 @@ class QuantizedLinear(nn.Module):
         require_cuda(x, "QuantizedLinear.forward")
         require_cuda(self.packed_weight, "QuantizedLinear.forward")
         rows = x.numel() // max(self.in_features, 1)
-        if x.dtype in (torch.float16, torch.bfloat16) and \
+        if x.dtype in (torch.float16, torch.bfloat16, torch.float32) and \
                 1 <= rows <= PACKED_TENSOR_ROWS == packed_gemv_rows(self.in_features, self.bits, self.block_size, x.dtype):
-            # up to 32 rows of 16-bit activations: one pass over the packed codes this module keeps resident, codes
-            # to exact 16-bit floats in registers and warp-level tensor-core products (bound by HBM); the
+            # up to 32 rows: one pass over the packed codes this module keeps resident, codes to exact 16-bit floats in
+            # registers and warp-level tensor-core products (fp32 activations as two fp16 halves each); the
             # entropy-coded form of the same weight (`eoq_weight()`) trades that speed for 7-15 % less memory and is
-            # what `EOQLinear` holds.  fp32 activations and other group sizes take the routes below.
+            # what `EOQLinear` holds.  Other group sizes take the routes below.
             return gemv_packed(self.packed_weight, self.scales, self.out_features, self.in_features, self.bits, self.block_size,
                                x, self.bias_param)
         if self._fusable() and rows >= 1 and x.dtype in (torch.float16, torch.bfloat16, torch.float32):

@@ -134,7 +134,7 @@ class QuantizedLinearFast(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         require_cuda(x, "QuantizedLinearFast.forward")
         rows = x.numel() // max(self.in_features, 1)
-        if self.strategy == "auto" and x.dtype in (torch.float16, torch.bfloat16) and \
+        if self.strategy == "auto" and x.dtype in (torch.float16, torch.bfloat16, torch.float32) and \
                 1 <= rows <= PACKED_TENSOR_ROWS == packed_gemv_rows(self.in_features, self.bits, self.block_size, x.dtype):
             # one pass over the packed codes on the tensor cores (HBM-bound), see QuantizedLinear.forward
             return gemv_packed(self.packed_weight, self.scales, self.out_features, self.in_features, self.bits, self.block_size,

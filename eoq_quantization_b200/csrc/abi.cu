@@ -1442,8 +1442,8 @@ extern "C" eoq_error_t eoq_b200_dequant_packed(const uint8_t *d_packed, const ui
 }
 
 extern "C" eoq_error_t eoq_b200_gemv_packed(const uint8_t *d_packed, const uint16_t *d_scales_fp16, uint32_t rows, uint32_t cols,
-                                            uint32_t bits, uint32_t group, const void *x, int x_dtype, uint32_t batch, void *y,
-                                            int y_dtype, const float *bias, void *stream)
+                                            uint32_t bits, uint32_t group, const void *x, int x_dtype, uint32_t batch, void *d_scratch,
+                                            void *y, int y_dtype, const float *bias, void *stream)
 {
     if (!d_packed || !d_scales_fp16 || !x || !y) return EOQ_ERR_NULL_PTR;
     if (batch == 0 || rows == 0) return EOQ_OK;
@@ -1458,8 +1458,16 @@ extern "C" eoq_error_t eoq_b200_gemv_packed(const uint8_t *d_packed, const uint1
     a.N = rows; a.K = cols; a.group = group; a.batch = batch; a.bits = bits; a.x_dtype = x_dtype; a.y_dtype = y_dtype;
     // row stride of QuantizedLinear.packed_weight (core/quantized_linear.py:49-66)
     a.row_bytes = bits == 4 ? cols / 2 : bits == 2 ? cols / 4 : cols;
+    // fp32 activations reach the tensor cores as two fp16 halves, written into the caller's scratch by one small launch
+    const bool split = x_dtype == EOQ_B200_F32 && d_scratch && (reinterpret_cast<uintptr_t>(d_scratch) & 15u) == 0 &&
+                       cols % 128u == 0 && group % 128u == 0;
+    if (split) a.xsplit = static_cast<const uint16_t *>(d_scratch);
     if (batch > gemv_packed_rows(a)) return EOQ_ERR_UNSUPPORTED;
     if (!have_device()) return EOQ_ERR_CUDA;
+    if (split) {
+        int e = launch_polar_rotate(x, x_dtype, cols, 0, batch, nullptr, static_cast<uint16_t *>(d_scratch), stream);      // block of 1: no rotation, only the split
+        if (e != 0) { std::fprintf(stderr, "eoq_b200_gemv_packed: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
+    }
     int e = launch_gemv_packed(a, stream);
     if (e != 0) { std::fprintf(stderr, "eoq_b200_gemv_packed: launch failed: %s\n", cudaGetErrorString((cudaError_t)e)); return EOQ_ERR_CUDA; }
     return EOQ_OK;

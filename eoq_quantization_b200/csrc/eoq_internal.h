@@ -209,6 +209,7 @@ struct PackedGemvArgs {
     const uint8_t *packed;      // [N][row_bytes]
     const uint16_t *scales;     // fp16 bits, [N][K / group]
     const void *x;              // [batch][K]
+    const uint16_t *xsplit;     // fp32 activations on the tensor cores: fp16 bits [2][batch][K], the nearest fp16 and the nearest to the remainder
     void *y;                    // [batch][N]
     const float *bias;          // [N] or null
     uint32_t N, K, group, row_bytes, batch, bits;

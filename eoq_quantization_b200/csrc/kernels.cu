@@ -3134,10 +3134,11 @@ __device__ __forceinline__ void unpack_span(const uint32_t (&w)[BITS], uint32_t 
 // rotation).  Lanes whose activation row does not exist read zeros from a constant block instead of branching.
 __device__ const uint4 kZeroBlock[4] = {};
 
-template <int BITS, bool BF16, int NB>
-__global__ void __launch_bounds__(BITS == 8 ? 256 : 512, NB > 1 ? 1 : BITS == 8 ? 3 : 2) gemv_packed_mma_kernel(const PackedGemvArgs a)
+template <int BITS, bool BF16, int NB, bool SPLIT = false>
+__global__ void __launch_bounds__(BITS == 8 ? 256 : 512, NB > 1 || SPLIT ? 1 : BITS == 8 ? 3 : 2) gemv_packed_mma_kernel(const PackedGemvArgs a)
 {
     static_assert(BITS == 2 || BITS == 4 || BITS == 8, "two or four bits packed, or one code per byte");
+    static_assert(!(SPLIT && BF16), "the two halves of an fp32 activation are fp16");
     constexpr int kRows = 2;                                       // a lane's weight rows: g and g + 8 of the tile
     constexpr int kDepth = 2;                                      // register sets of weights: kDepth - 1 spans requested ahead
     __shared__ float red[kMmaMaxWarps][NB][16][8];
@@ -3158,7 +3159,7 @@ __global__ void __launch_bounds__(BITS == 8 ? 256 : 512, NB > 1 ? 1 : BITS == 8 
 #pragma unroll
     for (int n = 0; n < NB; n++) {
         const bool has = 8u * n + g < a.batch;
-        xr[n] = has ? reinterpret_cast<const uint16_t *>(a.x) + (size_t)(8u * n + g) * a.K + t * 32u : reinterpret_cast<const uint16_t *>(kZeroBlock);
+        xr[n] = has ? (SPLIT ? a.xsplit : reinterpret_cast<const uint16_t *>(a.x)) + (size_t)(8u * n + g) * a.K + t * 32u : reinterpret_cast<const uint16_t *>(kZeroBlock);
         xstep[n] = has ? 128u : 0u;
     }
     float tot[NB][4];
@@ -3189,16 +3190,14 @@ __global__ void __launch_bounds__(BITS == 8 ? 256 : 512, NB > 1 ? 1 : BITS == 8 
         uint32_t h0[16], h1[16];
         unpack_span<BITS, BF16>(w[0], h0);
         unpack_span<BITS, BF16>(w[1], h1);
-#pragma unroll
-        for (int n = 0; n < NB; n++) {
+        // the activations in the weights' order: register r of the 16 holds the two columns that h0[r] holds
+        auto load_xp = [&](const uint16_t *src, uint32_t (&xp)[16]) {
             uint32_t q[16];
 #pragma unroll
             for (int h = 0; h < 4; h++) {
-                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(xr[n] + s * xstep[n]) + h);
+                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(src) + h);
                 q[4 * h] = v.x; q[4 * h + 1] = v.y; q[4 * h + 2] = v.z; q[4 * h + 3] = v.w;
             }
-            // the activations in the weights' order: register r of the 16 holds the two columns that h0[r] holds
-            uint32_t xp[16];
 #pragma unroll
             for (int r = 0; r < 16; r++) {
                 if (BITS == 4) {            // j = r / 4, columns 8j + (r & 3) and + 4: halves of q[4j + (r & 3) / 2] and q[4j + 2 + (r & 3) / 2]
@@ -3211,14 +3210,31 @@ __global__ void __launch_bounds__(BITS == 8 ? 256 : 512, NB > 1 ? 1 : BITS == 8 
                     xp[r] = q[r];
                 }
             }
-            // two accumulators: consecutive instructions do not wait for one another
-            float c[4], d[4];
-            mma_m16n8k16_first<BF16>(c, h0[0], h1[0], h0[1], h1[1], xp[0], xp[1]);
-            mma_m16n8k16_first<BF16>(d, h0[2], h1[2], h0[3], h1[3], xp[2], xp[3]);
+        };
 #pragma unroll
-            for (int m = 2; m < 8; m += 2) {
-                mma_m16n8k16<BF16>(c, h0[2 * m], h1[2 * m], h0[2 * m + 1], h1[2 * m + 1], xp[2 * m], xp[2 * m + 1]);
-                mma_m16n8k16<BF16>(d, h0[2 * m + 2], h1[2 * m + 2], h0[2 * m + 3], h1[2 * m + 3], xp[2 * m + 2], xp[2 * m + 3]);
+        for (int n = 0; n < NB; n++) {
+            uint32_t xp[16];
+            float c[4], d[4];
+            load_xp(xr[n] + s * xstep[n], xp);
+            if (!SPLIT) {
+                // two accumulators: consecutive instructions do not wait for one another
+                mma_m16n8k16_first<BF16>(c, h0[0], h1[0], h0[1], h1[1], xp[0], xp[1]);
+                mma_m16n8k16_first<BF16>(d, h0[2], h1[2], h0[3], h1[3], xp[2], xp[3]);
+#pragma unroll
+                for (int m = 2; m < 8; m += 2) {
+                    mma_m16n8k16<BF16>(c, h0[2 * m], h1[2 * m], h0[2 * m + 1], h1[2 * m + 1], xp[2 * m], xp[2 * m + 1]);
+                    mma_m16n8k16<BF16>(d, h0[2 * m + 2], h1[2 * m + 2], h0[2 * m + 3], h1[2 * m + 3], xp[2 * m + 2], xp[2 * m + 3]);
+                }
+            } else {
+                // fp32 activations as two fp16 halves (the nearest fp16, then the nearest to the remainder): the codes are
+                // exact, so code * hi + code * lo is the fp32 product to about 2^-22; one accumulator per half
+                mma_m16n8k16_first<false>(c, h0[0], h1[0], h0[1], h1[1], xp[0], xp[1]);
+#pragma unroll
+                for (int m = 1; m < 8; m++) mma_m16n8k16<false>(c, h0[2 * m], h1[2 * m], h0[2 * m + 1], h1[2 * m + 1], xp[2 * m], xp[2 * m + 1]);
+                load_xp(xr[n] + (xstep[n] ? (size_t)a.batch * a.K : 0u) + s * xstep[n], xp);
+                mma_m16n8k16_first<false>(d, h0[0], h1[0], h0[1], h1[1], xp[0], xp[1]);
+#pragma unroll
+                for (int m = 1; m < 8; m++) mma_m16n8k16<false>(d, h0[2 * m], h1[2 * m], h0[2 * m + 1], h1[2 * m + 1], xp[2 * m], xp[2 * m + 1]);
             }
             const float fa = half_bits_to_float(sc[0]), fb = half_bits_to_float(sc[1]);
             tot[n][0] = fmaf(fa, c[0] + d[0], tot[n][0]); tot[n][1] = fmaf(fa, c[1] + d[1], tot[n][1]);
@@ -3260,8 +3276,8 @@ __global__ void __launch_bounds__(BITS == 8 ? 256 : 512, NB > 1 ? 1 : BITS == 8 
 // bits: 2 and 4 as packed by QuantizedLinear (low bits first, code + qmax), anything else one signed code per byte.
 // K a multiple of the group and of the columns in sixteen bytes (32 nibbles, 64 two-bit codes, 16 bytes), the group a
 // multiple of 8, packed rows 16-byte aligned: checked by the caller.
-// Activation rows one launch takes: 32 on the tensor-core form (16-bit activations, 16-byte aligned, against scale
-// groups of whole 128-column spans), 8 otherwise.
+// Activation rows one launch takes: 32 on the tensor-core form (16-bit activations, 16-byte aligned, or fp32 ones with a
+// split copy, against scale groups of whole 128-column spans), 8 otherwise.
 static std::atomic<int> g_packed_warps{0};              // 0 = by shape; "packed_warps" in eoq_b200_tune
 void set_packed_warps(int v) { g_packed_warps.store(v >= 1 && v <= 16 ? v : 0); }
 
@@ -3302,7 +3318,8 @@ static cudaError_t launch_packed_mma(Kern kern, uint32_t fixed_warps, uint32_t t
 
 uint32_t gemv_packed_rows(const PackedGemvArgs &a)
 {
-    const bool tensor = a.x_dtype != EOQ_B200_F32 && a.K % 128u == 0 && a.group % 128u == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0;
+    const bool tensor = a.K % 128u == 0 && a.group % 128u == 0 &&
+                        (a.x_dtype == EOQ_B200_F32 ? a.xsplit != nullptr : (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0);
     return tensor ? 32u : 8u;
 }
 
@@ -3319,6 +3336,18 @@ int launch_gemv_packed(const PackedGemvArgs &a, void *stream)
         else e = launch_packed_mma(gemv_packed_mma_kernel<B, H, 4>, 8u, tiles, nspans, st, a);                           \
     } while (0)
         const bool bf = a.x_dtype == EOQ_B200_BF16;
+        if (a.x_dtype == EOQ_B200_F32) {
+#define EOQ_LAUNCH_SPLIT(B)                                                                                              \
+    do {                                                                                                                 \
+        if (a.batch <= 8) e = launch_packed_mma(gemv_packed_mma_kernel<B, false, 1, true>, 8u, tiles, nspans, st, a);    \
+        else if (a.batch <= 16) e = launch_packed_mma(gemv_packed_mma_kernel<B, false, 2, true>, 8u, tiles, nspans, st, a); \
+        else e = launch_packed_mma(gemv_packed_mma_kernel<B, false, 4, true>, 8u, tiles, nspans, st, a);                 \
+    } while (0)
+            if (a.bits == 4) EOQ_LAUNCH_SPLIT(4);
+            else if (a.bits == 2) EOQ_LAUNCH_SPLIT(2);
+            else EOQ_LAUNCH_SPLIT(8);
+#undef EOQ_LAUNCH_SPLIT
+        } else
         if (a.bits == 4) { if (bf) EOQ_LAUNCH_MMA(4, true); else EOQ_LAUNCH_MMA(4, false); }
         else if (a.bits == 2) { if (bf) EOQ_LAUNCH_MMA(2, true); else EOQ_LAUNCH_MMA(2, false); }
         else { if (bf) EOQ_LAUNCH_MMA(8, true); else EOQ_LAUNCH_MMA(8, false); }

@@ -306,11 +306,11 @@ def dequant_packed(packed: torch.Tensor, scales: torch.Tensor, rows: int, cols: 
 
 
 def packed_gemv_rows(cols: int, bits: int, group: int, dtype: torch.dtype = torch.float16) -> int:
-    """Activation rows `gemv_packed` takes for this shape: 32 on its tensor-core form (16-bit activations against
-    scale groups of whole 128-column spans), 8 on the general form, 0 if it does not apply."""
+    """Activation rows `gemv_packed` takes for this shape: 32 on its tensor-core form (scale groups of whole 128-column
+    spans; fp32 activations go in as two fp16 halves each), 8 on the general form, 0 if it does not apply."""
     if not (2 <= bits <= 8 and group > 0 and cols % group == 0):
         return 0
-    if dtype in (torch.float16, torch.bfloat16) and cols % 128 == 0 and group % 128 == 0:
+    if dtype in _DTYPES and cols % 128 == 0 and group % 128 == 0:
         return PACKED_TENSOR_ROWS
     per16 = 32 if bits == 4 else 64 if bits == 2 else 16                 # codes in the sixteen bytes a lane loads
     return 8 if cols % per16 == 0 and group % 8 == 0 else 0
@@ -345,8 +345,11 @@ def gemv_packed(packed: torch.Tensor, scales: torch.Tensor, rows: int, cols: int
     out_dtype = out_dtype or x.dtype
     y = torch.empty((n, rows), dtype=out_dtype, device=x.device)
     b = None if bias is None else bias.to(device=x.device, dtype=torch.float32).contiguous()
+    # fp32 activations on the tensor-core form: room for their two fp16 halves
+    scratch = torch.empty((n, cols), dtype=torch.float32, device=x.device) if x.dtype == torch.float32 and cols % 128 == 0 and group % 128 == 0 else None
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().eoq_b200_gemv_packed(pk.data_ptr(), sc.data_ptr(), rows, cols, bits, group, x2.data_ptr(), _DTYPES[x.dtype], n,
+                                                   scratch.data_ptr() if scratch is not None else None,
                                                    y.data_ptr(), _DTYPES[out_dtype], b.data_ptr() if b is not None else None, _stream_ptr()),
                    "eoq_b200_gemv_packed")
     return y.reshape(*x.shape[:-1], rows)

@@ -438,13 +438,17 @@ eoq_error_t eoq_b200_dequant_packed(const uint8_t *d_packed, const uint16_t *d_s
  * sixteen bytes (32 at 4 bits, 64 at 2 bits, 16 otherwise), the group a multiple
  * of 8 and d_packed 16-byte aligned (EOQ_ERR_UNSUPPORTED otherwise: use
  * eoq_b200_dequant_packed and a GEMM).  x [batch, cols] and y [batch, rows] in
- * EOQ_B200_F16 / BF16 / F32; device pointers; asynchronous.  With 16-bit
- * activations (16-byte aligned), cols a multiple of
- * 128 and the group a multiple of 128 the product runs on the tensor cores and
- * takes up to 32 rows; more rows than the form in use takes: EOQ_ERR_UNSUPPORTED. */
+ * EOQ_B200_F16 / BF16 / F32; device pointers; asynchronous.  With cols a
+ * multiple of 128 and the group a multiple of 128 the product runs on the tensor
+ * cores and takes up to 32 rows: 16-bit activations (16-byte aligned) as they
+ * are, fp32 activations as two fp16 halves each (the nearest fp16 and the nearest
+ * to the remainder; the codes are exact, so the products carry about 2^-22),
+ * which one extra small launch writes into d_scratch (batch * cols * 4 bytes,
+ * 16-byte aligned, the caller's; NULL: fp32 activations take the general form).
+ * More rows than the form in use takes: EOQ_ERR_UNSUPPORTED. */
 eoq_error_t eoq_b200_gemv_packed(const uint8_t *d_packed, const uint16_t *d_scales_fp16, uint32_t rows, uint32_t cols,
-                                 uint32_t bits, uint32_t group, const void *x, int x_dtype, uint32_t batch, void *y,
-                                 int y_dtype, const float *bias, void *stream);
+                                 uint32_t bits, uint32_t group, const void *x, int x_dtype, uint32_t batch, void *d_scratch,
+                                 void *y, int y_dtype, const float *bias, void *stream);
 
 /* y = x @ W.T (+ bias) straight from PolarLinear's in-memory form (kernels/polar_engine.py:144-360: one centroid index
  * per byte, one fp16 norm per block of each row, 2^bits fp32 centroids), for up to 8 activation rows on the CUDA cores

@@ -40,7 +40,7 @@ def test_packed_gemv_matches_dequantise_then_matmul(bits, n, k, group):
     for dt in (torch.float16, torch.bfloat16, torch.float32):
         # 32 rows on the tensor-core form (16-bit activations, groups of whole 128-column spans), 8 on the general one
         most = packed_gemv_rows(k, bits, group, dt)
-        assert most == (32 if dt != torch.float32 and group % 128 == 0 else 8)
+        assert most == (32 if group % 128 == 0 else 8)
         for rows in (1, 2, 3, 4, 7, 8, 9, 16, 17, 32):
             x = torch.from_numpy(rng.standard_normal((rows, k)).astype(np.float32)).cuda().to(dt)
             if rows > most:
@@ -78,12 +78,13 @@ def test_quantized_linear_forward_takes_the_packed_route_for_few_rows():
             want = x.double().cpu().numpy() @ dense.T + ql.bias_param.double().cpu().numpy()
             assert y.dtype == dt and O.rel_l2(y.double().cpu().numpy(), want) < tol, (dt, rows)
             assert L.lib().eoq_b200_launch_count() == n0 + 1                   # one kernel of this library either way
-    assert ql._eoq is None
-    x = torch.from_numpy(rng.standard_normal((3, 512)).astype(np.float32)).cuda()
+    x = torch.from_numpy(rng.standard_normal((3, 512)).astype(np.float32)).cuda()       # fp32: two fp16 halves per activation
     want = x.double().cpu().numpy() @ dense.T + ql.bias_param.double().cpu().numpy()
     assert O.rel_l2(ql(x).double().cpu().numpy(), want) < 1e-5
+    assert ql._eoq is None
     assert not packed_gemv_applies(100, 4, 100) and not packed_gemv_applies(260, 4, 130)
-    assert packed_gemv_applies(4096, 4, 128, torch.float16, 32) and not packed_gemv_applies(4096, 4, 128, torch.float32, 9)
+    assert packed_gemv_applies(4096, 4, 128, torch.float16, 32) and packed_gemv_applies(4096, 4, 128, torch.float32, 32)
+    assert not packed_gemv_applies(4096, 4, 64, torch.float32, 9)
     odd = QuantizedLinear.from_float(torch.nn.Linear(100, 30, bias=False), bits=4, block_size=100).cuda()
     x = torch.from_numpy(rng.standard_normal((2, 100)).astype(np.float32)).cuda()
     want = x.double().cpu().numpy() @ odd._dequantize_weight().double().cpu().numpy().T
