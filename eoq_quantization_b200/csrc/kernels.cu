@@ -3294,14 +3294,23 @@ static cudaError_t launch_packed_mma(Kern kern, uint32_t fixed_warps, uint32_t t
         return launch_with_pdl(kern, dim3(tiles), dim3(w * 32u), smem, st, a);
     }
     const uint32_t max_warps = 16;
-    static std::atomic<int> regs{0};                             // per instantiation
-    if (regs.load() == 0) {
-        cudaFuncAttributes fa;
-        cudaError_t e = cudaFuncGetAttributes(&fa, kern);
-        if (e != cudaSuccess) return e;
-        regs.store(std::max(fa.numRegs, 16));
+    // registers per kernel, asked once (kernels of one signature share this function: the key is the kernel, not its type)
+    static std::mutex mu;
+    static std::vector<std::pair<const void *, int>> known;
+    int regs = 0;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        for (const auto &kv : known)
+            if (kv.first == reinterpret_cast<const void *>(kern)) regs = kv.second;
+        if (regs == 0) {
+            cudaFuncAttributes fa;
+            cudaError_t e = cudaFuncGetAttributes(&fa, kern);
+            if (e != cudaSuccess) return e;
+            regs = std::max(fa.numRegs, 16);
+            known.emplace_back(reinterpret_cast<const void *>(kern), regs);
+        }
     }
-    const uint32_t per_thread = ((uint32_t)regs.load() + 7u) & ~7u, sms = (uint32_t)device_sm_count();
+    const uint32_t per_thread = ((uint32_t)regs + 7u) & ~7u, sms = (uint32_t)device_sm_count();
     static const uint32_t kChoices[] = {16, 12, 10, 8, 6, 5, 4};
     uint32_t warps = 0, best_resident = 0, fallback = 4;
     for (uint32_t w : kChoices) {
